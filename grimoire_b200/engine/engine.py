@@ -1,0 +1,243 @@
+"""Engine: one model on one device (one rank of a TP/PP group) with its KV pool, activation
+buffers, chunked prefill, batched decode / verify and the replayable decode graph.
+
+API parity with the reference's ``struct Grimoire`` (grimoire.cpp:2299-4500): ``prefill``,
+``decode_batch``, ``decode_solo`` (= graph replay), ``argmax_token``, ``release``, slot admission,
+``build_graph``/``step`` (grimoire.cpp:23640-23723: token / position live in device memory so the
+recording stays valid).  The differences are structural: pooled 16-token int8 pages instead of
+per-slot KV copies, one universal M-row forward, CUDA graphs instead of SYCL command graphs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from ..models.dense import Buffers, DenseModel, RowBatch
+from ..ops import core as K
+from ..ops.core import PAGE
+from .kv import KvPool, OutOfPages, SeqSlot
+
+
+@dataclass
+class EngineLimits:
+    max_slots: int = 8               # conversation slots (GRIMOIRE_SEQ_SLOTS / MAX_BATCH)
+    max_ctx: int = 8192              # per-request context cap (--ctx)
+    prefill_chunk: int = 4096        # GRIMOIRE_PREFILL_CHUNK
+    max_decode_rows: int = 64        # rows of one batched decode / verify step
+    kv_pages: int = 0                # 0 = max_slots * max_ctx / 16
+
+
+class Engine:
+    def __init__(self, model: DenseModel, limits: Optional[EngineLimits] = None):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.device
+        self.limits = limits or EngineLimits()
+        lim = self.limits
+        n_attn = self.cfg.num_attention_layers()
+        pages = lim.kv_pages or (lim.max_slots * ((lim.max_ctx + PAGE - 1) // PAGE))
+        self.kv = KvPool(n_attn, model.geom.Hkv, model.geom.D, pages, lim.max_slots, lim.max_ctx, self.device)
+        chunk = min(lim.prefill_chunk, lim.max_ctx)
+        self.prefill_buf: Optional[Buffers] = None
+        self._prefill_rows = chunk
+        self.decode_buf = model.make_buffers(lim.max_decode_rows, lim.max_decode_rows)
+        # device-resident step inputs (graph replay reads these)
+        i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=self.device)
+        self.d_tokens, self.d_row_seq, self.d_row_pos = i32(lim.max_decode_rows), i32(lim.max_decode_rows), i32(lim.max_decode_rows)
+        pin = self.device.type == "cuda"
+        self.h_stage = torch.zeros(3, lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
+        self.h_next = torch.zeros(lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
+        self.graphs: dict[tuple[int, int], "torch.cuda.CUDAGraph"] = {}
+        self.counters = {"prefill_rows": 0, "decode_steps": 0, "decode_rows": 0, "graph_replays": 0, "kernel_launches": 0}
+
+    # ------------------------------------------------------------------------------------------
+    # slots
+    # ------------------------------------------------------------------------------------------
+    def open(self, slot: Optional[int] = None) -> SeqSlot:
+        return self.kv.open_slot(slot)
+
+    def release(self, seq: SeqSlot) -> None:
+        self.kv.release(seq)
+
+    # ------------------------------------------------------------------------------------------
+    # prefill (one sequence, chunked)
+    # ------------------------------------------------------------------------------------------
+    def _ensure_prefill_buf(self):
+        if self.prefill_buf is None:
+            self.prefill_buf = self.model.make_buffers(self._prefill_rows, 1, dense_kv_tokens=self.limits.max_ctx)
+
+    def prefill(self, seq: SeqSlot, tokens: Sequence[int] | torch.Tensor, want_logits: bool = True) -> Optional[torch.Tensor]:
+        """Append ``tokens`` to the sequence in chunks of ``prefill_chunk`` rows; returns the fp32
+        logits of the last token (device tensor [V]) when ``want_logits``."""
+        self._ensure_prefill_buf()
+        if not torch.is_tensor(tokens):
+            tokens = torch.tensor(list(tokens), dtype=torch.int32)
+        tokens = tokens.to(torch.int32)
+        n = int(tokens.shape[0])
+        if n == 0:
+            return None
+        if seq.length + n > self.limits.max_ctx:
+            raise OutOfPages(f"prompt of {seq.length + n} tokens exceeds the context cap {self.limits.max_ctx}")
+        self.kv.ensure(seq, seq.length + n)
+        tok_dev = tokens.to(self.device, non_blocking=True)
+        logits = None
+        done = 0
+        while done < n:
+            m = min(self._prefill_rows, n - done)
+            pos0 = seq.length
+            rows = torch.arange(pos0, pos0 + m, dtype=torch.int32, device=self.device)
+            rb = RowBatch(tok_dev[done: done + m], torch.full((m,), seq.slot, dtype=torch.int32, device=self.device), rows,
+                          mode="prefill", q_pos0=pos0, seq_slot=seq.slot,
+                          logits_rows=torch.tensor([m - 1], device=self.device))
+            out = self.model.forward(rb, self.prefill_buf, self.kv.layers, self.kv.table)
+            seq.length += m
+            done += m
+            self.counters["prefill_rows"] += m
+            logits = out
+        seq.tokens.extend(int(t) for t in tokens.tolist())
+        return logits[0] if want_logits else None
+
+    # ------------------------------------------------------------------------------------------
+    # batched decode / verify rows
+    # ------------------------------------------------------------------------------------------
+    def _stage_rows(self, tokens, slots, positions) -> int:
+        M = len(tokens)
+        st = self.h_stage
+        st[0, :M] = torch.as_tensor(tokens, dtype=torch.int32)
+        st[1, :M] = torch.as_tensor(slots, dtype=torch.int32)
+        st[2, :M] = torch.as_tensor(positions, dtype=torch.int32)
+        self.d_tokens[:M].copy_(st[0, :M], non_blocking=True)
+        self.d_row_seq[:M].copy_(st[1, :M], non_blocking=True)
+        self.d_row_pos[:M].copy_(st[2, :M], non_blocking=True)
+        return M
+
+    def _splits_for(self, M: int, max_len: int) -> int:
+        return K.decode_splits(max_len, M, self.model.geom.Hkv)
+
+    def _run_rows(self, M: int, splits: int) -> torch.Tensor:
+        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits)
+        logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
+        K.argmax_rows(logits, self.decode_buf.next_ids[:M])
+        return logits
+
+    def decode_rows(self, tokens: Sequence[int], seqs: Sequence[SeqSlot], positions: Sequence[int],
+                    use_graph: bool = True, return_logits: bool = False):
+        """One step over M rows; row i appends ``tokens[i]`` at ``positions[i]`` of ``seqs[i]`` and
+        returns the greedy next token per row (host list).  Rows of one sequence with consecutive
+        positions form a speculative verify block."""
+        M = len(tokens)
+        if M == 0:
+            return []
+        if M > self.limits.max_decode_rows:
+            raise ValueError("too many rows for one step")
+        max_len = 0
+        for s, p in zip(seqs, positions):
+            self.kv.ensure(s, p + 1)
+            max_len = max(max_len, p + 1)
+        self._stage_rows(tokens, [s.slot for s in seqs], positions)
+        splits = self._splits_for(M, max_len)
+        if use_graph and self.device.type == "cuda":
+            key = (M, splits)
+            g = self.graphs.get(key)
+            if g is None:
+                g = self._capture(M, splits)
+            g.replay()
+            self.counters["graph_replays"] += 1
+        else:
+            self._run_rows(M, splits)
+        self.h_next[:M].copy_(self.decode_buf.next_ids[:M], non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.counters["decode_steps"] += 1
+        self.counters["decode_rows"] += M
+        out = self.h_next[:M].tolist()
+        if return_logits:
+            return out, self.decode_buf.logits[:M]
+        return out
+
+    def commit_rows(self, seqs: Sequence[SeqSlot], tokens: Sequence[int], positions: Sequence[int]) -> None:
+        """Record that rows were appended (host bookkeeping after an accepted step)."""
+        for s, t, p in zip(seqs, tokens, positions):
+            if p == s.length:
+                s.length += 1
+                s.tokens.append(int(t))
+
+    def _capture(self, M: int, splits: int):
+        # warm the allocator / workspace outside capture, then record
+        self._run_rows(M, splits)
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run_rows(M, splits)
+        self.graphs[(M, splits)] = g
+        return g
+
+    # ------------------------------------------------------------------------------------------
+    # self-feeding decode graph (token and position stay on the device between steps)
+    # ------------------------------------------------------------------------------------------
+    def build_step_graph(self, seqs: Sequence[SeqSlot], first_tokens: Sequence[int], steps_ahead: int):
+        """Record one decode step for ``seqs`` that feeds its own arg-max back as the next input and
+        bumps the positions on the device, so ``steps_ahead`` replays need no host round trip (the
+        reference's build_graph/step contract, grimoire.cpp:23640-23723).  Pages for the next
+        ``steps_ahead`` positions are mapped up front.  Returns the graph; tokens are read with
+        ``read_next``."""
+        M = len(seqs)
+        max_len = 0
+        for s in seqs:
+            self.kv.ensure(s, s.length + steps_ahead + 1)
+            max_len = max(max_len, s.length + steps_ahead + 1)
+        self._stage_rows(first_tokens, [s.slot for s in seqs], [s.length for s in seqs])
+        splits = self._splits_for(M, max_len)
+
+        def body():
+            self._run_rows(M, splits)
+            self.d_tokens[:M].copy_(self.decode_buf.next_ids[:M])
+            self.d_row_pos[:M].add_(1)
+
+        saved = (self.d_tokens[:M].clone(), self.d_row_pos[:M].clone())
+        body()                       # warm-up outside capture (also sizes the workspace)
+        torch.cuda.current_stream().synchronize()
+        self.d_tokens[:M].copy_(saved[0]); self.d_row_pos[:M].copy_(saved[1])
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body()
+        self.d_tokens[:M].copy_(saved[0]); self.d_row_pos[:M].copy_(saved[1])
+        torch.cuda.current_stream().synchronize()
+        return g
+
+    def read_next(self, M: int) -> list[int]:
+        self.h_next[:M].copy_(self.decode_buf.next_ids[:M])
+        torch.cuda.current_stream().synchronize()
+        return self.h_next[:M].tolist()
+
+    # ------------------------------------------------------------------------------------------
+    # convenience: greedy generation for one sequence (CLI / tests)
+    # ------------------------------------------------------------------------------------------
+    def generate(self, prompt: Sequence[int], max_new: int, eos: Optional[int] = None, use_graph: bool = True,
+                 collect_logits: bool = False):
+        seq = self.open()
+        out, logit_trace = [], []
+        try:
+            logits = self.prefill(seq, prompt)
+            tok = int(K.ref.argmax_lowest(logits[None].float().cpu())[0]) if self.device.type != "cuda" else int(
+                K.argmax_rows(logits[None], torch.zeros(1, dtype=torch.int32, device=self.device))[0])
+            if collect_logits:
+                logit_trace.append(logits.float().cpu().clone())
+            for _ in range(max_new):
+                out.append(tok)
+                if eos is not None and tok == eos:
+                    break
+                if len(out) == max_new:
+                    break
+                pos = seq.length
+                res = self.decode_rows([tok], [seq], [pos], use_graph=use_graph, return_logits=collect_logits)
+                nxt = res[0] if collect_logits else res
+                if collect_logits:
+                    logit_trace.append(res[1][0].float().cpu().clone())
+                self.commit_rows([seq], [tok], [pos])
+                tok = int(nxt[0])
+        finally:
+            self.release(seq)
+        return (out, logit_trace) if collect_logits else out

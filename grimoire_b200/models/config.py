@@ -1,0 +1,208 @@
+"""Model description: one dataclass for every architecture the engine runs, plus the named
+configurations the benchmarks use.
+
+Field names follow the HF ``config.json`` keys the reference parses into ``Qwen35Config``
+(include/b70/qwen35.hpp:70-294, src/qwen35_loader.cpp:330-640): dense attention decoders
+(Qwen3-style), Gated-DeltaNet hybrids (3 linear-attention layers : 1 gated full-attention layer),
+MoE FFNs with an optional shared expert, and an optional MTP draft head.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Optional
+
+FULL_ATTN = "full_attention"
+LINEAR_ATTN = "linear_attention"
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen3"
+    hidden_size: int = 256
+    num_hidden_layers: int = 2
+    num_attention_heads: int = 4
+    num_key_value_heads: int = 2
+    head_dim: int = 64
+    vocab_size: int = 4096
+    intermediate_size: int = 768
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    partial_rotary_factor: float = 1.0
+    tie_word_embeddings: bool = False
+    attn_output_gate: bool = False          # q_proj emits [q | gate] per head
+    qk_norm: bool = False                   # per-head RMSNorm of q and k before RoPE
+    norm_zero_centered: bool = False        # (1 + w) convention of the Qwen3.5 family
+    sliding_window: int = 0
+    attention_bias: bool = False
+    softmax_scale: Optional[float] = None
+    layer_types: list[str] = field(default_factory=list)
+    # Gated DeltaNet
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
+    gdn_chunk: int = 64
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    # MTP draft head
+    mtp_num_hidden_layers: int = 0
+    # quantization of the projections in a synthetic / converted model
+    quant: str = "int4"
+    quant_group: int = 128
+
+    def __post_init__(self):
+        if not self.layer_types:
+            self.layer_types = [FULL_ATTN] * self.num_hidden_layers
+        if len(self.layer_types) != self.num_hidden_layers:
+            raise ValueError("layer_types length must equal num_hidden_layers")
+
+    # ---- derived ----
+    @property
+    def rot_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
+
+    @property
+    def norm_offset(self) -> float:
+        return 1.0 if self.norm_zero_centered else 0.0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim * (2 if self.attn_output_gate else 1)
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def is_attention_layer(self, i: int) -> bool:
+        return self.layer_types[i] == FULL_ATTN
+
+    def num_attention_layers(self) -> int:
+        return sum(1 for t in self.layer_types if t == FULL_ATTN)
+
+    def param_count(self) -> int:
+        H = self.hidden_size
+        n = self.vocab_size * H * (1 if self.tie_word_embeddings else 2)
+        for i in range(self.num_hidden_layers):
+            if self.is_attention_layer(i):
+                n += H * (self.q_size + 2 * self.kv_size) + self.num_attention_heads * self.head_dim * H
+            else:
+                kd = self.linear_num_key_heads * self.linear_key_head_dim
+                vd = self.linear_num_value_heads * self.linear_value_head_dim
+                n += H * (2 * kd + vd) + H * vd + 2 * H * self.linear_num_value_heads + vd * H
+            if self.is_moe:
+                n += self.num_experts * 3 * H * self.moe_intermediate_size + H * self.num_experts
+                n += 3 * H * self.shared_expert_intermediate_size
+            else:
+                n += 3 * H * self.intermediate_size
+        return n
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self), indent=1)
+
+    @staticmethod
+    def from_hf(cfg: dict) -> "ModelConfig":
+        """Build from a HF ``config.json`` dict (nested ``text_config`` handled like
+        src/qwen35_loader.cpp:271-316)."""
+        if "text_config" in cfg and isinstance(cfg["text_config"], dict):
+            inner = dict(cfg["text_config"])
+            for k in ("tie_word_embeddings",):
+                if k in cfg and k not in inner:
+                    inner[k] = cfg[k]
+            cfg = inner
+        mt = cfg.get("model_type", "qwen3")
+        rp = cfg.get("rope_parameters") or cfg.get("rope_scaling") or {}
+        n_layers = int(cfg["num_hidden_layers"])
+        heads = int(cfg["num_attention_heads"])
+        hd = int(cfg.get("head_dim") or cfg["hidden_size"] // heads)
+        lt = list(cfg.get("layer_types") or [])
+        lt = [LINEAR_ATTN if t in ("linear_attention", "linear") else FULL_ATTN for t in lt]
+        family35 = mt.startswith("qwen3_5") or mt.startswith("qwen3_next") or mt.startswith("qwen3.5")
+        return ModelConfig(
+            model_type=mt,
+            hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
+            num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd,
+            vocab_size=int(cfg["vocab_size"]), intermediate_size=int(cfg.get("intermediate_size", 0)),
+            rms_norm_eps=float(cfg.get("rms_norm_eps", 1e-6)),
+            rope_theta=float(rp.get("rope_theta", cfg.get("rope_theta", 1e6))),
+            partial_rotary_factor=float(rp.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 1.0))),
+            tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+            attn_output_gate=bool(cfg.get("attn_output_gate", family35)),
+            qk_norm=bool(cfg.get("qk_norm", mt.startswith("qwen3"))),
+            norm_zero_centered=bool(cfg.get("norm_zero_centered", family35)),
+            sliding_window=int(cfg.get("sliding_window") or 0),
+            attention_bias=bool(cfg.get("attention_bias", False)),
+            layer_types=lt,
+            linear_num_key_heads=int(cfg.get("linear_num_key_heads", 0)),
+            linear_num_value_heads=int(cfg.get("linear_num_value_heads", 0)),
+            linear_key_head_dim=int(cfg.get("linear_key_head_dim", 0)),
+            linear_value_head_dim=int(cfg.get("linear_value_head_dim", 0)),
+            linear_conv_kernel_dim=int(cfg.get("linear_conv_kernel_dim", 4)),
+            num_experts=int(cfg.get("num_experts", 0)), num_experts_per_tok=int(cfg.get("num_experts_per_tok", 0)),
+            moe_intermediate_size=int(cfg.get("moe_intermediate_size", 0)),
+            shared_expert_intermediate_size=int(cfg.get("shared_expert_intermediate_size", 0)),
+            norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
+            mtp_num_hidden_layers=int(cfg.get("mtp_num_hidden_layers", 0)),
+        )
+
+    @staticmethod
+    def from_dir(path: str | Path) -> "ModelConfig":
+        return ModelConfig.from_hf(json.loads((Path(path) / "config.json").read_text()))
+
+
+# ---------------------------------------------------------------------------------------------
+# named configurations
+# ---------------------------------------------------------------------------------------------
+def tiny_dense() -> ModelConfig:
+    """2 layers, hidden 256, 4q/2kv x 64, FFN 768, vocab 4096, tied embeddings, int4 g128."""
+    return ModelConfig(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       vocab_size=4096, intermediate_size=768, tie_word_embeddings=True, rope_theta=1e6)
+
+
+def dense_27b(layers: int = 64) -> ModelConfig:
+    """27B-class dense decoder: 64 layers, hidden 5120, 40q/8kv x 128, FFN 17408, vocab 151936."""
+    return ModelConfig(hidden_size=5120, num_hidden_layers=layers, num_attention_heads=40, num_key_value_heads=8,
+                       head_dim=128, vocab_size=151936, intermediate_size=17408, rope_theta=1e6)
+
+
+def small_dense(layers: int = 4) -> ModelConfig:
+    """A small GPU test model with 27B-like ratios (hidden 1024, 8q/2kv x 128, FFN 2816)."""
+    return ModelConfig(hidden_size=1024, num_hidden_layers=layers, num_attention_heads=8, num_key_value_heads=2,
+                       head_dim=128, vocab_size=8192, intermediate_size=2816, rope_theta=1e6)
+
+
+def hybrid_moe_80b(layers: int = 48) -> ModelConfig:
+    """Hybrid linear-attention MoE, 80B total / 3B active: 3 Gated DeltaNet layers then 1 gated
+    full-attention layer; 512 experts x FFN 512, top-10 + 1 shared expert."""
+    lt = [FULL_ATTN if (i % 4) == 3 else LINEAR_ATTN for i in range(layers)]
+    return ModelConfig(model_type="qwen3_next", hidden_size=2048, num_hidden_layers=layers, num_attention_heads=16,
+                       num_key_value_heads=2, head_dim=256, vocab_size=151936, intermediate_size=0,
+                       partial_rotary_factor=0.25, attn_output_gate=True, qk_norm=True, norm_zero_centered=True,
+                       layer_types=lt, linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                       linear_value_head_dim=128, linear_conv_kernel_dim=4, gdn_chunk=64, num_experts=512,
+                       num_experts_per_tok=10, moe_intermediate_size=512, shared_expert_intermediate_size=512,
+                       quant="fp8_block")
+
+
+def tiny_hybrid_moe(layers: int = 4) -> ModelConfig:
+    lt = [FULL_ATTN if (i % 4) == 3 else LINEAR_ATTN for i in range(layers)]
+    return ModelConfig(model_type="qwen3_next", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=0,
+                       partial_rotary_factor=1.0, attn_output_gate=True, qk_norm=True, norm_zero_centered=True,
+                       layer_types=lt, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64,
+                       linear_value_head_dim=64, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=128, quant="fp8_block")
+
+
+PRESETS = {"tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+           "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}

@@ -1,0 +1,255 @@
+"""Dense attention decoder (Qwen3-style): weights + the universal M-row forward pass.
+
+One function serves prompt prefill, batched decode and speculative verify, exactly as the
+reference's ``prefill(tokens, next_tokens, seqb)`` does (grimoire.cpp:20263-23631: "a batched
+decode is a prefill whose M rows belong to M different conversations"); the rows' (sequence,
+position) pairs and the attention mode are the only difference.
+
+Per layer (compare forward(), grimoire.cpp:14986-15616, ~29 launches per layer there; 8 here):
+  rmsnorm -> fused q|k|v projection -> norm/RoPE/int8 page write -> attention -> o_proj (+= h)
+  rmsnorm -> fused gate|up projection with SwiGLU epilogue -> down_proj (+= h)
+Under tensor parallelism the two row-parallel projections hand their partial sums to the fused
+all-reduce (parallel/tp.py) instead of accumulating into ``h`` directly.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..formats.codecs import Fmt
+from ..formats.quantize import QuantWeight, quantize
+from ..formats.w4_tile_layout import concat_rows, interleave_gate_up_q
+from ..ops import core as K
+from ..ops import ref
+from ..ops.linear import BF16Linear, W4Linear
+from ..ops.workspace import Workspace
+from .config import ModelConfig
+
+
+@dataclass
+class DenseLayer:
+    in_norm: torch.Tensor
+    post_norm: torch.Tensor
+    qkv: W4Linear
+    o: W4Linear
+    gate_up: W4Linear
+    down: W4Linear
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+
+
+@dataclass
+class RowBatch:
+    """What one forward pass works on.  ``mode`` is 'decode' (every row is its own (seq, pos)
+    over the paged cache: decode / batched decode / verify) or 'prefill' (all rows are
+    consecutive positions q_pos0.. of ONE sequence ``seq_slot``)."""
+
+    tokens: torch.Tensor                 # int32 [M]
+    row_seq: torch.Tensor                # int32 [M]
+    row_pos: torch.Tensor                # int32 [M]
+    mode: str = "decode"
+    q_pos0: int = 0
+    seq_slot: int = 0
+    splits: int = 1
+    logits_rows: Optional[torch.Tensor] = None   # int64 indices of rows that need logits (None = all)
+
+
+class Buffers:
+    """Activation buffers for up to ``max_rows`` rows (allocated once; graph-capture safe)."""
+
+    def __init__(self, cfg: ModelConfig, geom: K.AttnGeom, I_local: int, max_rows: int, max_logit_rows: int, device,
+                 dense_kv_tokens: int = 0):
+        H = cfg.hidden_size
+        bf, f32 = torch.bfloat16, torch.float32
+        mk = lambda *s, dt: torch.zeros(*s, dtype=dt, device=device)
+        qsz = geom.Hq * geom.D * (2 if geom.q_gated else 1)
+        self.h = mk(max_rows, H, dt=f32)
+        self.x = mk(max_rows, H, dt=bf)
+        self.qkv = mk(max_rows, qsz + 2 * geom.Hkv * geom.D, dt=bf)
+        self.q = mk(max_rows, geom.Hq * geom.D, dt=bf)
+        self.gate = mk(max_rows, geom.Hq * geom.D, dt=bf) if geom.q_gated else None
+        self.attn = mk(max_rows, geom.Hq * geom.D, dt=bf)
+        self.act = mk(max_rows, I_local, dt=bf)
+        self.partial = mk(max_rows, H, dt=f32)
+        self.xf = mk(max_logit_rows, H, dt=bf)
+        self.logits = mk(max_logit_rows, cfg.vocab_size, dt=f32)
+        self.next_ids = mk(max_logit_rows, dt=torch.int32)
+        self.dense_k = mk(dense_kv_tokens, geom.Hkv * geom.D, dt=bf) if dense_kv_tokens else None
+        self.dense_v = mk(dense_kv_tokens, geom.Hkv * geom.D, dt=bf) if dense_kv_tokens else None
+        self.max_rows = max_rows
+        self.max_logit_rows = max_logit_rows
+
+
+class DenseModel:
+    def __init__(self, cfg: ModelConfig, device, tp_rank: int = 0, tp_world: int = 1,
+                 workspace: Optional[Workspace] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.tp_rank, self.tp_world = tp_rank, tp_world
+        self.ws = workspace or Workspace(device)
+        if cfg.num_attention_heads % tp_world or cfg.num_key_value_heads % tp_world or cfg.intermediate_size % tp_world:
+            raise ValueError("tensor parallel degree must divide heads, kv heads and the FFN width")
+        self.Hq = cfg.num_attention_heads // tp_world
+        self.Hkv = cfg.num_key_value_heads // tp_world
+        self.I = cfg.intermediate_size // tp_world
+        self.geom = K.AttnGeom(self.Hq, self.Hkv, cfg.head_dim, cfg.rot_dim,
+                               cfg.softmax_scale or ref.softmax_scale(cfg.head_dim), cfg.attn_output_gate,
+                               cfg.sliding_window, cfg.rms_norm_eps, cfg.norm_offset)
+        self.inv_freq = ref.rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
+        self.layers: list[DenseLayer] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head = None
+        self.tp = None          # parallel.tp.TensorParallel when tp_world > 1
+
+    # ------------------------------------------------------------------------------------------
+    # construction
+    # ------------------------------------------------------------------------------------------
+    def _quant(self, w: torch.Tensor) -> QuantWeight:
+        cfg = self.cfg
+        return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
+
+    def _shard_rows(self, w: torch.Tensor, heads: int, per: int) -> torch.Tensor:
+        """rows of a column-parallel weight owned by this rank (whole heads)."""
+        n = heads // self.tp_world * per
+        return w[self.tp_rank * n: (self.tp_rank + 1) * n]
+
+    def add_layer_from_dense(self, wq, wk, wv, wo, wg, wu, wd, in_norm, post_norm, q_norm=None, k_norm=None):
+        """Quantize + shard + tile one layer from full-precision logical weights (``[out][in]``)."""
+        cfg, dev, W, r = self.cfg, self.device, self.tp_world, self.tp_rank
+        D = cfg.head_dim
+        qper = D * (2 if cfg.attn_output_gate else 1)
+        wq_s = self._shard_rows(wq, cfg.num_attention_heads, qper)
+        wk_s = self._shard_rows(wk, cfg.num_key_value_heads, D)
+        wv_s = self._shard_rows(wv, cfg.num_key_value_heads, D)
+        kq = cfg.num_attention_heads * D // W
+        wo_s = wo[:, r * kq: (r + 1) * kq]
+        I = cfg.intermediate_size // W
+        wg_s, wu_s = wg[r * I: (r + 1) * I], wu[r * I: (r + 1) * I]
+        wd_s = wd[:, r * I: (r + 1) * I]
+        qkv = concat_rows([self._quant(wq_s), self._quant(wk_s), self._quant(wv_s)])
+        gu = interleave_gate_up_q(self._quant(wg_s), self._quant(wu_s))
+        f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
+        i = len(self.layers)
+        self.layers.append(DenseLayer(
+            f32(in_norm), f32(post_norm),
+            W4Linear(qkv, dev, f"L{i}.qkv", workspace=self.ws),
+            W4Linear(self._quant(wo_s), dev, f"L{i}.o", workspace=self.ws),
+            W4Linear(gu, dev, f"L{i}.gate_up", swiglu=True, workspace=self.ws),
+            W4Linear(self._quant(wd_s), dev, f"L{i}.down", workspace=self.ws),
+            f32(q_norm), f32(k_norm)))
+
+    def set_embeddings(self, embed: torch.Tensor, final_norm: torch.Tensor, lm_head: Optional[torch.Tensor]):
+        dev = self.device
+        self.embed = embed.to(device=dev, dtype=torch.bfloat16).contiguous()
+        self.final_norm = final_norm.to(device=dev, dtype=torch.float32).contiguous()
+        if lm_head is None or self.cfg.tie_word_embeddings:
+            # tied: the head aliases the embedding table and is never quantized (grimoire.cpp:3492-3495)
+            self.lm_head = BF16Linear(self.embed, dev, "lm_head(tied)")
+        else:
+            self.lm_head = W4Linear(self._quant(lm_head), dev, "lm_head", workspace=self.ws)
+
+    @staticmethod
+    def random(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, std: float = 0.02,
+               gen_device=None, workspace: Optional[Workspace] = None) -> "DenseModel":
+        """Random-init weights N(0, std) of the named architecture, quantized to int4 (the synthetic
+        checkpoints of the benchmarks).  Every rank draws the same logical matrices and keeps its
+        shard, so TP results can be compared with a single-GPU run token for token."""
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
+        gdev = torch.device(gen_device or device)
+        g = torch.Generator(device=gdev)
+        H, D = cfg.hidden_size, cfg.head_dim
+        qrows = cfg.num_attention_heads * D * (2 if cfg.attn_output_gate else 1)
+
+        def rnd(n, k, tag):
+            g.manual_seed(seed * 1000003 + tag)
+            return torch.randn(n, k, generator=g, device=gdev, dtype=torch.float32) * std
+
+        ones = torch.ones(H)
+        for i in range(cfg.num_hidden_layers):
+            t = i * 16
+            m.add_layer_from_dense(rnd(qrows, H, t + 1), rnd(cfg.kv_size, H, t + 2), rnd(cfg.kv_size, H, t + 3),
+                                   rnd(H, cfg.num_attention_heads * D, t + 4), rnd(cfg.intermediate_size, H, t + 5),
+                                   rnd(cfg.intermediate_size, H, t + 6), rnd(H, cfg.intermediate_size, t + 7),
+                                   ones if not cfg.norm_zero_centered else torch.zeros(H),
+                                   ones if not cfg.norm_zero_centered else torch.zeros(H),
+                                   torch.ones(D) if cfg.qk_norm else None, torch.ones(D) if cfg.qk_norm else None)
+        emb = rnd(cfg.vocab_size, H, 900001)
+        head = None if cfg.tie_word_embeddings else rnd(cfg.vocab_size, H, 900002)
+        m.set_embeddings(emb, ones if not cfg.norm_zero_centered else torch.zeros(H), head)
+        return m
+
+    @staticmethod
+    def from_state_dict(cfg: ModelConfig, sd: dict, device, tp_rank: int = 0, tp_world: int = 1,
+                        workspace: Optional[Workspace] = None) -> "DenseModel":
+        """Build from HF-named full-precision tensors (``[out][in]``), quantizing to int4."""
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}."
+            g = lambda k: sd.get(p + k)
+            m.add_layer_from_dense(g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight"),
+                                   g("self_attn.o_proj.weight"), g("mlp.gate_proj.weight"), g("mlp.up_proj.weight"),
+                                   g("mlp.down_proj.weight"), g("input_layernorm.weight"),
+                                   g("post_attention_layernorm.weight"), g("self_attn.q_norm.weight"),
+                                   g("self_attn.k_norm.weight"))
+        m.set_embeddings(sd["model.embed_tokens.weight"], sd["model.norm.weight"], sd.get("lm_head.weight"))
+        return m
+
+    def weight_bytes(self) -> int:
+        n = self.lm_head.nbytes()
+        for l in self.layers:
+            n += l.qkv.nbytes() + l.o.nbytes() + l.gate_up.nbytes() + l.down.nbytes()
+        return n
+
+    def make_buffers(self, max_rows: int, max_logit_rows: int, dense_kv_tokens: int = 0) -> Buffers:
+        return Buffers(self.cfg, self.geom, self.I, max_rows, max_logit_rows, self.device, dense_kv_tokens)
+
+    # ------------------------------------------------------------------------------------------
+    # forward over M rows
+    # ------------------------------------------------------------------------------------------
+    def _row_parallel(self, lin, x, h):
+        if self.tp_world == 1:
+            lin(x, h, "add_f32")
+        else:
+            self.tp.row_parallel_add(lin, x, h)
+
+    def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
+        """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
+        cfg, geom = self.cfg, self.geom
+        M = rb.tokens.shape[0]
+        eps, off = cfg.rms_norm_eps, cfg.norm_offset
+        h, x = buf.h[:M], buf.x[:M]
+        qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]
+        gate = buf.gate[:M] if buf.gate is not None else None
+        K.embed(rb.tokens, self.embed, h)
+        prefill = rb.mode == "prefill"
+        T = rb.q_pos0 + M
+        for li, L in enumerate(self.layers):
+            kvl = kv_layers[li]
+            K.add_rmsnorm(h, L.in_norm, x, eps, off)
+            L.qkv(x, qkv, "bf16")
+            if prefill:
+                if rb.q_pos0 > 0:
+                    K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
+                K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
+                               gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+                K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
+            else:
+                K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
+                K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+            self._row_parallel(L.o, attn, h)
+            K.add_rmsnorm(h, L.post_norm, x, eps, off)
+            L.gate_up(x, act, "swiglu")
+            self._row_parallel(L.down, act, h)
+        # head
+        if rb.logits_rows is None:
+            hsel, n = h, M
+        else:
+            n = rb.logits_rows.shape[0]
+            hsel = h.index_select(0, rb.logits_rows) if n != M else h
+        xf, logits = buf.xf[:n], buf.logits[:n]
+        K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
+        self.lm_head(xf, logits, "f32")
+        return logits

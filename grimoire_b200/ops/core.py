@@ -1,0 +1,282 @@
+"""Python wrappers of the non-GEMM kernels: norms, RoPE + paged int8 KV write, paged decode /
+verify attention, flash prefill, embedding, arg-max.  Each function runs the sm_100a kernel for
+CUDA tensors and the fp32 PyTorch reference (``ops.ref``) for CPU tensors; on a CUDA tensor a
+missing native library raises instead of falling back.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _native
+from . import ref
+from .workspace import Workspace
+
+PAGE = 16
+
+
+def _c(v):
+    return ctypes.c_int(int(v))
+
+
+def _f(v):
+    return ctypes.c_float(float(v))
+
+
+# ---------------------------------------------------------------------------------------------
+# norms
+# ---------------------------------------------------------------------------------------------
+def add_rmsnorm(h: torch.Tensor, w: torch.Tensor, x_out: torch.Tensor, eps: float, offset: float,
+                delta: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta`` (optional, fp32 or bf16); ``x_out = rms(h) * (offset + w)`` as bf16.
+
+    h: fp32 [M][H] residual stream, updated in place.  Reference: launch_rmsnorm_residual*
+    (src/ops.cpp:205-313)."""
+    M, H = h.shape
+    if not h.is_cuda:
+        if delta is not None:
+            h.add_(delta.float())
+        x_out.copy_(ref.rmsnorm(h, w, eps, offset).to(x_out.dtype))
+        return x_out
+    dd = 0 if delta is None else (1 if delta.dtype == torch.float32 else 2)
+    x16 = x_out if x_out.dtype == torch.bfloat16 else None
+    x32 = x_out if x_out.dtype == torch.float32 else None
+    code = _native.cuda().grm_add_rmsnorm(_native.ptr(h), _native.ptr(delta), _c(dd), _native.ptr(w), _native.ptr(x16),
+                                          _native.ptr(x32), _c(M), _c(H), _c(h.stride(0)),
+                                          _c(delta.stride(0) if delta is not None else 0), _c(x_out.stride(0)), _f(eps),
+                                          _f(offset), _native.stream_ptr())
+    _native.check(code, "add_rmsnorm")
+    return x_out
+
+
+def rmsnorm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, heads: int, D: int, eps: float, offset: float,
+                  z: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMSNorm (fp32 in, bf16 out) with optional ``* silu(z)`` (GDN gated output norm)."""
+    rows = x.shape[0]
+    if not x.is_cuda:
+        y = ref.head_rmsnorm(x.float().reshape(rows, heads, D), w, eps, offset)
+        if z is not None:
+            y = y * torch.nn.functional.silu(z.float().reshape(rows, heads, D))
+        out.copy_(y.reshape(rows, heads * D).to(out.dtype))
+        return out
+    code = _native.cuda().grm_rmsnorm_heads(_native.ptr(x), _native.ptr(z), _native.ptr(w), _native.ptr(out), _c(rows),
+                                            _c(heads), _c(D), _c(x.stride(0)), _c(z.stride(0) if z is not None else 0),
+                                            _c(out.stride(0)), _f(eps), _f(offset), _native.stream_ptr())
+    _native.check(code, "rmsnorm_heads")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# paged int8 KV cache (one layer)
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class KvLayer:
+    """int8 K/V pages of one layer: pages [P][Hkv][16][D] int8, scales [P][Hkv][16] fp32."""
+
+    k: torch.Tensor
+    v: torch.Tensor
+    ks: torch.Tensor
+    vs: torch.Tensor
+
+    @staticmethod
+    def alloc(pages: int, Hkv: int, D: int, device) -> "KvLayer":
+        mk = lambda *s, dt: torch.zeros(*s, dtype=dt, device=device)
+        return KvLayer(mk(pages, Hkv, PAGE, D, dt=torch.int8), mk(pages, Hkv, PAGE, D, dt=torch.int8),
+                       mk(pages, Hkv, PAGE, dt=torch.float32), mk(pages, Hkv, PAGE, dt=torch.float32))
+
+    def bytes_per_token(self) -> int:
+        Hkv, D = self.k.shape[1], self.k.shape[3]
+        return 2 * Hkv * D + 2 * Hkv * 4
+
+
+@dataclass
+class AttnGeom:
+    Hq: int
+    Hkv: int
+    D: int
+    rot: int
+    scale: float
+    q_gated: bool = False
+    window: int = 0
+    norm_eps: float = 1e-6
+    norm_offset: float = 0.0
+
+
+def rope_kvwrite(qkv: torch.Tensor, row_pos: torch.Tensor, row_seq: Optional[torch.Tensor],
+                 block_table: Optional[torch.Tensor], inv_freq: torch.Tensor, geom: AttnGeom, q_out: torch.Tensor,
+                 kv: Optional[KvLayer], q_norm_w=None, k_norm_w=None, gate_out=None, k_out=None, v_out=None):
+    """Split the fused q|k|v rows, q/k norm, RoPE, write q (bf16) and int8 K/V pages (+ dense bf16
+    K/V for the prefill attention of the current chunk).  See rope_kv.cu."""
+    M = qkv.shape[0]
+    Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
+    if not qkv.is_cuda:
+        qs = 2 * D if geom.q_gated else D
+        x = qkv.float()
+        qg = x[:, : Hq * qs].reshape(M, Hq, qs)
+        q = qg[..., :D]
+        if geom.q_gated and gate_out is not None:
+            gate_out.copy_(qg[..., D:].reshape(M, Hq * D).to(gate_out.dtype))
+        k = x[:, Hq * qs: Hq * qs + Hkv * D].reshape(M, Hkv, D)
+        v = x[:, Hq * qs + Hkv * D:].reshape(M, Hkv, D)
+        q = ref.head_rmsnorm(q, q_norm_w, geom.norm_eps, geom.norm_offset)
+        k = ref.head_rmsnorm(k, k_norm_w, geom.norm_eps, geom.norm_offset)
+        q = ref.apply_rope(q, row_pos, inv_freq, geom.rot)
+        k = ref.apply_rope(k, row_pos, inv_freq, geom.rot)
+        q_out.copy_(q.reshape(M, Hq * D).to(q_out.dtype))
+        if k_out is not None:
+            k_out.copy_(k.reshape(M, Hkv * D).to(k_out.dtype))
+            v_out.copy_(v.reshape(M, Hkv * D).to(v_out.dtype))
+        if kv is not None and row_seq is not None:
+            kq, ksc = ref.quant_i8_rows(k)
+            vq, vsc = ref.quant_i8_rows(v)
+            for m in range(M):
+                s, p = int(row_seq[m]), int(row_pos[m])
+                if s < 0:
+                    continue
+                page = int(block_table[s, p // PAGE])
+                if page < 0:
+                    continue
+                kv.k[page, :, p % PAGE] = kq[m]
+                kv.v[page, :, p % PAGE] = vq[m]
+                kv.ks[page, :, p % PAGE] = ksc[m]
+                kv.vs[page, :, p % PAGE] = vsc[m]
+        return q_out
+    lib = _native.cuda()
+    code = lib.grm_rope_kvwrite(
+        _native.ptr(qkv), _c(qkv.stride(0)), _native.ptr(row_pos), _native.ptr(row_seq), _native.ptr(block_table),
+        _c(block_table.stride(0) if block_table is not None else 0), _native.ptr(inv_freq), _native.ptr(q_norm_w),
+        _native.ptr(k_norm_w), _f(geom.norm_eps), _f(geom.norm_offset), _native.ptr(q_out), _c(q_out.stride(0)),
+        _native.ptr(gate_out), _native.ptr(k_out), _native.ptr(v_out), _c(k_out.stride(0) if k_out is not None else 0),
+        _native.ptr(kv.k if kv else None), _native.ptr(kv.v if kv else None), _native.ptr(kv.ks if kv else None),
+        _native.ptr(kv.vs if kv else None), _c(M), _c(Hq), _c(Hkv), _c(D), _c(geom.rot), _c(1 if geom.q_gated else 0),
+        _native.stream_ptr())
+    _native.check(code, "rope_kvwrite")
+    return q_out
+
+
+def gather_kv_dense(kv: KvLayer, pages_of_seq: torch.Tensor, T: int, out_k: torch.Tensor, out_v: torch.Tensor):
+    """Dequantize the first T cached tokens of one sequence into dense bf16 [T][Hkv*D] buffers."""
+    Hkv, D = kv.k.shape[1], kv.k.shape[3]
+    if T <= 0:
+        return
+    if not kv.k.is_cuda:
+        for name, pages, scales, out in (("k", kv.k, kv.ks, out_k), ("v", kv.v, kv.vs, out_v)):
+            npg = (T + PAGE - 1) // PAGE
+            idx = pages_of_seq[:npg].long()
+            d = pages[idx].float() * scales[idx][..., None]           # [npg][Hkv][16][D]
+            d = d.permute(0, 2, 1, 3).reshape(npg * PAGE, Hkv * D)[:T]
+            out[:T].copy_(d.to(out.dtype))
+        return
+    lib = _native.cuda()
+    for pages, scales, out in ((kv.k, kv.ks, out_k), (kv.v, kv.vs, out_v)):
+        code = lib.grm_kv_gather_dequant(_native.ptr(pages), _native.ptr(scales), _native.ptr(pages_of_seq), _native.ptr(out),
+                                         _c(T), _c(Hkv), _c(D), _c(out.stride(0)), _native.stream_ptr())
+        _native.check(code, "kv_gather_dequant")
+
+
+def decode_splits(max_len: int, M: int, Hkv: int) -> int:
+    """Split-KV factor: enough CTAs to fill 148 SMs, at least 2 pages per split."""
+    pages = max(1, (max_len + PAGE - 1) // PAGE)
+    want = max(1, (4 * 148) // max(1, M * Hkv))
+    cap = int(max(1, min(want, pages // 2 if pages >= 2 else 1, 64)))
+    s = 1
+    while s * 2 <= cap:     # powers of two only: the decode graphs are keyed by (rows, splits)
+        s *= 2
+    return s
+
+
+def paged_decode_attn(q: torch.Tensor, row_seq: torch.Tensor, row_pos: torch.Tensor, block_table: torch.Tensor,
+                      kv: KvLayer, geom: AttnGeom, out: torch.Tensor, splits: int, ws: Optional[Workspace],
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of M (sequence, position) rows over the paged int8 cache; see attn_decode.cu."""
+    M = q.shape[0]
+    Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
+    if not q.is_cuda:
+        for m in range(M):
+            s, p = int(row_seq[m]), int(row_pos[m])
+            T = p + 1
+            npg = (T + PAGE - 1) // PAGE
+            idx = block_table[s, :npg].long()
+            kd = (kv.k[idx].float() * kv.ks[idx][..., None]).permute(0, 2, 1, 3).reshape(npg * PAGE, Hkv, D)[:T]
+            vd = (kv.v[idx].float() * kv.vs[idx][..., None]).permute(0, 2, 1, 3).reshape(npg * PAGE, Hkv, D)[:T]
+            o = ref.attention_rows(q[m: m + 1].float().reshape(1, Hq, D), kd, vd, torch.tensor([p]), geom.scale,
+                                   geom.window).reshape(Hq * D)
+            if gate is not None:
+                o = o * torch.sigmoid(gate[m].float())
+            out[m].copy_(o.to(out.dtype))
+        return out
+    part_o = part_ml = counters = None
+    if splits > 1:
+        part_o = ws.get("attn_part_o", M * Hq * splits * D, torch.float32)
+        part_ml = ws.get("attn_part_ml", M * Hq * splits * 2, torch.float32)
+        counters = ws.get("attn_counters", 4096, torch.int32, zero=True)
+        if M * Hkv > 4096:
+            raise ValueError("too many (row, kv head) pairs for the attention counters")
+    code = _native.cuda().grm_paged_decode_attn(
+        _native.ptr(q), _c(q.stride(0)), _native.ptr(row_seq), _native.ptr(row_pos), _native.ptr(block_table),
+        _c(block_table.stride(0)), _native.ptr(kv.k), _native.ptr(kv.v), _native.ptr(kv.ks), _native.ptr(kv.vs),
+        _native.ptr(gate), _native.ptr(out), _c(out.stride(0)), _native.ptr(part_o), _native.ptr(part_ml),
+        _native.ptr(counters), _c(M), _c(Hq), _c(Hkv), _c(D), _c(splits), _c(geom.window), _f(geom.scale),
+        _native.stream_ptr())
+    _native.check(code, "paged_decode_attn")
+    return out
+
+
+def flash_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, geom: AttnGeom, out: torch.Tensor, q_pos0: int,
+                  gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of one sequence's M new rows over its T = q_pos0 + M dense bf16 keys."""
+    M = q.shape[0]
+    T = q_pos0 + M
+    Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
+    if not q.is_cuda:
+        o = ref.attention_rows(q.float().reshape(M, Hq, D), k[:T].float().reshape(T, Hkv, D),
+                               v[:T].float().reshape(T, Hkv, D), torch.arange(q_pos0, T), geom.scale, geom.window)
+        o = o.reshape(M, Hq * D)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float())
+        out.copy_(o.to(out.dtype))
+        return out
+    code = _native.cuda().grm_flash_prefill(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
+                                            _native.ptr(gate), _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq),
+                                            _c(Hkv), _c(D), _c(q_pos0), _c(geom.window), _f(geom.scale),
+                                            _native.stream_ptr())
+    _native.check(code, "flash_prefill")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# embedding / head glue
+# ---------------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, h_out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """bf16 table [V][H] -> fp32 residual rows (reference: launch_embed, src/ops.cpp:684)."""
+    if not ids.is_cuda:
+        h_out.copy_(table[ids.long()].float() * scale)
+        return h_out
+    M, H = h_out.shape
+    code = _native.cuda().grm_embed(_native.ptr(ids), _native.ptr(table), _native.ptr(h_out), _c(M), _c(H), _c(table.shape[0]),
+                                    _c(h_out.stride(0)), _f(scale), _native.stream_ptr())
+    _native.check(code, "embed")
+    return h_out
+
+
+def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> torch.Tensor:
+    """Greedy token per row, ties to the lowest index (reference: launch_argmax, src/ops.cpp:611)."""
+    if not logits.is_cuda:
+        out_ids.copy_(ref.argmax_lowest(logits.float()))
+        return out_ids
+    M, V = logits.shape
+    code = _native.cuda().grm_argmax(_native.ptr(logits), _native.ptr(out_ids), None, _c(M), _c(V), _c(logits.stride(0)),
+                                     _native.stream_ptr())
+    _native.check(code, "argmax")
+    return out_ids
+
+
+def status_read(clear: bool = True) -> tuple[int, int, int]:
+    """(first error code, detail, count) from the device status block; (0,0,0) when clean."""
+    buf = (ctypes.c_uint * 8)()
+    code = _native.cuda().grm_status_read(buf, _c(1 if clear else 0), _native.stream_ptr())
+    _native.check(code, "status_read")
+    return int(buf[0]), int(buf[1]), int(buf[2])

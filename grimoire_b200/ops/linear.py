@@ -1,0 +1,168 @@
+"""Quantized linear layers: the python face of smallm_w4.cu, dequant.cu and gemm_tcgen05.cu.
+
+``W4Linear`` is the int4-g128 projection.  ``forward`` picks the kernel by row count, the way the
+reference's ``mm()`` dispatcher does (grimoire.cpp:21042-21370: GEMV / small-M DPAS / large-M
+GEMM): M <= 64 rows run the weight-streaming small-M kernel, larger M dequantizes the weight once
+into the shared bf16 scratch and runs the tcgen05 GEMM.  Epilogues are part of the kernels:
+``bf16`` store, ``f32`` store, ``add_f32`` (residual stream ``h += y``) and ``swiglu`` (fused
+gate|up weight, rows interleaved per 16).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ..formats.quantize import QuantWeight
+from ..formats.w4_tile_layout import W4Tiled, tile_w4
+from .workspace import Workspace, default_workspace
+
+EPI = {"bf16": 0, "f32": 1, "add_f32": 2, "swiglu": 3, "rs_push": 4}
+SMALLM_MAX = 64
+_SMS = 148
+
+
+def _c(v):
+    return ctypes.c_int(int(v))
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, epi: str = "bf16", bn: int = 0,
+              max_ctas: int = 0, peer_out: Optional[list[int]] = None, my_rank: int = 0) -> torch.Tensor:
+    """out = a[M][K] @ b[N][K]^T on the tcgen05 kernel (bf16 in, fp32 accumulate in TMEM)."""
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    M, K = a.shape
+    N = b.shape[0]
+    lib = _native.cuda()
+    world = 0
+    parr = None
+    if peer_out is not None:
+        world = len(peer_out)
+        parr = (ctypes.c_void_p * world)(*peer_out)
+    code = lib.grm_gemm_bf16(_native.ptr(a), _c(a.stride(0)), _native.ptr(b), _c(b.stride(0)), _native.ptr(out),
+                             _c(out.stride(0)), _c(M), _c(N), _c(K), _c(EPI[epi]), _c(bn), _c(max_ctas), parr,
+                             _c(world), _c(my_rank), _native.stream_ptr())
+    _native.check(code, f"gemm_bf16 M={M} N={N} K={K} epi={epi}")
+    return out
+
+
+class W4Linear:
+    """int4 group-quantized ``[N][K]`` projection resident on one device."""
+
+    def __init__(self, qw: QuantWeight, device, name: str = "", swiglu: bool = False,
+                 workspace: Optional[Workspace] = None):
+        self.name = name
+        self.N, self.K, self.group = qw.N, qw.K, qw.group
+        self.swiglu = swiglu                       # rows are gate/up interleaved per 16
+        self.device = torch.device(device)
+        self.ws = workspace or default_workspace(device)
+        if self.device.type == "cuda":
+            t = tile_w4(qw).to(self.device)
+            self.tiled: Optional[W4Tiled] = t
+            self.Np = t.N
+            self.w_ref = None
+        else:
+            self.tiled = None
+            self.Np = qw.N
+            self.w_ref = qw.dequant()              # fp32 oracle weights for the CPU path
+        self.out_features = self.N // 2 if swiglu else self.N
+
+    def nbytes(self) -> int:
+        return self.tiled.nbytes() if self.tiled is not None else self.w_ref.numel() * 4
+
+    # -- kernel selection ---------------------------------------------------------------------
+    def _plan_smallm(self, M: int):
+        tiles32 = self.Np // 32
+        rows = 32 if (self.swiglu or tiles32 >= 2 * _SMS) and M <= 16 else 16
+        if self.swiglu:
+            rows = 32
+        tiles = self.Np // rows
+        G = self.K // self.group
+        ksplit = 1
+        if tiles < _SMS and G >= 16:
+            want = min(G // 8, max(1, (2 * _SMS) // tiles))
+            while want > 1 and G % want:
+                want -= 1
+            ksplit = max(1, want)
+        return rows, ksplit, tiles
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
+        """x bf16 [M][K] -> out (dtype/shape by ``epi``); returns ``out``."""
+        M = x.shape[0]
+        if self.swiglu and epi != "swiglu":
+            raise ValueError("a gate|up interleaved weight must run with the swiglu epilogue")
+        if self.device.type != "cuda":
+            return self._forward_ref(x, out, epi)
+        t = self.tiled
+        lib = _native.cuda()
+        if M <= SMALLM_MAX:
+            rows, ksplit, tiles = self._plan_smallm(M)
+            scratch = counters = None
+            if ksplit > 1:
+                mt = (M + 7) // 8
+                scratch = self.ws.get("smallm_scratch", ksplit * tiles * (rows // 16) * mt * 128, torch.float32)
+                counters = self.ws.get("smallm_counters", 8192, torch.int32, zero=True)
+            code = lib.grm_smallm_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out),
+                                     _native.ptr(scratch), _native.ptr(counters), _c(M), _c(t.N), _c(t.K),
+                                     _c(x.stride(0)), _c(out.stride(0)), _c(t.group), _c(EPI[epi]), _c(rows),
+                                     _c(ksplit), _native.stream_ptr())
+            _native.check(code, f"smallm_w4 {self.name} M={M} N={t.N} K={t.K}")
+            return out
+        wbuf = self.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
+        code = lib.grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
+                                  _c(t.K), _native.stream_ptr())
+        _native.check(code, f"dequant_w4 {self.name}")
+        return gemm_bf16(x, wbuf[: self.N], out, epi)
+
+    __call__ = forward
+
+    def _forward_ref(self, x, out, epi):
+        y = x.bfloat16().float() @ self.w_ref.t()
+        if epi == "swiglu":
+            I = self.N // 2
+            y3 = y.reshape(x.shape[0], I // 16, 2, 16)
+            y = (torch.nn.functional.silu(y3[:, :, 0]) * y3[:, :, 1]).reshape(x.shape[0], I)
+            out.copy_(y.to(out.dtype))
+        elif epi == "add_f32":
+            out.add_(y)
+        else:
+            out.copy_(y.to(out.dtype))
+        return out
+
+
+class BF16Linear:
+    """Unquantized bf16 ``[N][K]`` projection (tied lm_head, router, small gate projections).
+
+    M <= 8 rows stream the weight through gemv_bf16.cu; more rows run the tcgen05 GEMM."""
+
+    def __init__(self, w: torch.Tensor, device, name: str = ""):
+        self.name = name
+        self.w = w.to(device=device, dtype=torch.bfloat16).contiguous()
+        self.N, self.K = self.w.shape
+        self.device = torch.device(device)
+        self.swiglu = False
+        self.out_features = self.N
+
+    def nbytes(self) -> int:
+        return self.w.numel() * 2
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
+        M = x.shape[0]
+        if self.device.type != "cuda":
+            y = x.bfloat16().float() @ self.w.float().t()
+            if epi == "add_f32":
+                out.add_(y)
+            else:
+                out.copy_(y.to(out.dtype))
+            return out
+        if M <= 8 and epi in ("bf16", "f32", "add_f32"):
+            code = _native.cuda().grm_gemv_bf16(_native.ptr(self.w), _native.ptr(x), _native.ptr(out), _c(M), _c(self.N),
+                                                _c(self.K), _c(self.w.stride(0)), _c(x.stride(0)), _c(out.stride(0)),
+                                                _c(0 if epi == "bf16" else 1), _c(1 if epi == "add_f32" else 0),
+                                                _native.stream_ptr())
+            _native.check(code, f"gemv_bf16 {self.name}")
+            return out
+        return gemm_bf16(x, self.w, out, epi)
+
+    __call__ = forward

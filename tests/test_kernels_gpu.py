@@ -1,0 +1,282 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op (tier T5 of the reference's
+test strategy: kernel-vs-host-reference on device).  Shapes exercise every tail path: M in
+{1,2,7,8,9,16,17,33,64}, N / K not multiples of the tile, ragged pages."""
+import math
+
+import pytest
+import torch
+
+from grimoire_b200.formats.codecs import Fmt
+from grimoire_b200.formats.quantize import quantize
+from grimoire_b200.formats.w4_tile_layout import interleave_gate_up_q
+from grimoire_b200.ops import core as K
+from grimoire_b200.ops import ref
+from grimoire_b200.ops.linear import BF16Linear, W4Linear, gemm_bf16
+from grimoire_b200.ops.workspace import Workspace
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _assert_clean():
+    code, detail, n = K.status_read()
+    assert code == 0, f"device status: code={code} detail={detail:#x} count={n}"
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,Kd,group", [(256, 512, 128), (96, 1024, 64), (2048, 2048, 128)])
+def test_smallm_w4_matches_fp32(M, N, Kd, group):
+    torch.manual_seed(M * 131 + N)
+    w = torch.randn(N, Kd) * 0.02
+    qw = quantize(w, Fmt.INT4, group=group)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    x = (torch.randn(M, Kd) * 0.5).to(DEV).bfloat16()
+    want = ref.linear_dequant(x.cpu(), qw.dequant())
+    out32 = torch.empty(M, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, out32, "f32")
+    got = out32[:, :N].cpu()
+    assert torch.allclose(got, want, atol=2e-3, rtol=1e-3), float((got - want).abs().max())
+    out16 = torch.empty(M, lin.Np, dtype=torch.bfloat16, device=DEV)
+    lin(x, out16, "bf16")
+    assert torch.allclose(out16[:, :N].float().cpu(), want, atol=2e-2, rtol=2e-2)
+    h = torch.ones(M, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, h, "add_f32")
+    assert torch.allclose(h[:, :N].cpu(), want + 1.0, atol=2e-3, rtol=1e-3)
+    _assert_clean()
+
+
+def test_smallm_w4_rows_are_batch_invariant():
+    """Row r of a batch must be bit-identical to the same row run alone (batched == sequential)."""
+    torch.manual_seed(0)
+    qw = quantize(torch.randn(1024, 1024) * 0.02, Fmt.INT4)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    x = torch.randn(13, 1024, device=DEV).bfloat16()
+    full = torch.empty(13, 1024, dtype=torch.float32, device=DEV)
+    lin(x, full, "f32")
+    for r in (0, 5, 12):
+        one = torch.empty(1, 1024, dtype=torch.float32, device=DEV)
+        lin(x[r: r + 1], one, "f32")
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("M", [1, 8, 24])
+def test_smallm_w4_swiglu_and_splitk(M):
+    torch.manual_seed(3)
+    I, H = 512, 1024
+    g = quantize(torch.randn(I, H) * 0.02, Fmt.INT4)
+    u = quantize(torch.randn(I, H) * 0.02, Fmt.INT4)
+    lin = W4Linear(interleave_gate_up_q(g, u), DEV, "gu", swiglu=True, workspace=Workspace(DEV))
+    x = torch.randn(M, H, device=DEV).bfloat16()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    lin(x, out, "swiglu")
+    xc = x.cpu()
+    want = ref.swiglu(ref.linear_dequant(xc, g.dequant()), ref.linear_dequant(xc, u.dequant()))
+    assert torch.allclose(out.float().cpu(), want, atol=3e-3, rtol=2e-2)
+    # short-N long-K shape takes the grid split-K path (scratch + counters); run twice: the counters
+    # must be back at zero after the first call
+    d = quantize(torch.randn(64, 4096) * 0.02, Fmt.INT4)
+    ws = Workspace(DEV)
+    lind = W4Linear(d, DEV, "d", workspace=ws)
+    assert lind._plan_smallm(M)[1] > 1
+    xd = torch.randn(M, 4096, device=DEV).bfloat16()
+    wantd = ref.linear_dequant(xd.cpu(), d.dequant())
+    for _ in range(2):
+        od = torch.empty(M, 64, dtype=torch.float32, device=DEV)
+        lind(xd, od, "f32")
+        assert torch.allclose(od.cpu(), wantd, atol=3e-3, rtol=1e-3)
+    assert int(ws.get("smallm_counters", 8192, torch.int32).abs().sum()) == 0
+    _assert_clean()
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (128, 256, 512), (300, 384, 320), (1024, 1280, 1024), (77, 96, 136),
+                                    (4096, 512, 256)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_tcgen05_matches_fp32(M, N, Kd, bn):
+    torch.manual_seed(M + N + Kd)
+    a = (torch.randn(M, Kd, device=DEV) * 0.5).bfloat16()
+    b = (torch.randn(N, Kd, device=DEV) * 0.05).bfloat16()
+    want = a.float() @ b.float().t()
+    out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    gemm_bf16(a, b, out, "f32", bn=bn)
+    _assert_clean()
+    err = float((out - want).abs().max())
+    assert torch.allclose(out, want, atol=2e-3, rtol=1e-3), err
+    o16 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    gemm_bf16(a, b, o16, "bf16", bn=bn)
+    assert torch.allclose(o16.float(), want, atol=3e-2, rtol=2e-2)
+    h = torch.full((M, N), 2.0, dtype=torch.float32, device=DEV)
+    gemm_bf16(a, b, h, "add_f32", bn=bn)
+    assert torch.allclose(h, want + 2.0, atol=2e-3, rtol=1e-3)
+    _assert_clean()
+
+
+def test_gemm_tcgen05_swiglu_and_few_ctas():
+    torch.manual_seed(9)
+    M, I, H = 256, 512, 384
+    a = (torch.randn(M, H, device=DEV) * 0.5).bfloat16()
+    g = (torch.randn(I, H, device=DEV) * 0.05).bfloat16()
+    u = (torch.randn(I, H, device=DEV) * 0.05).bfloat16()
+    from grimoire_b200.formats.w4_tile_layout import interleave_gate_up
+    b = interleave_gate_up(g, u).contiguous()
+    out = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    # 3 CTAs for 16 tiles: every CTA walks several tiles, exercising both TMEM buffers and phase flips
+    gemm_bf16(a, b, out, "swiglu", bn=128, max_ctas=3)
+    want = ref.swiglu(a.float() @ g.float().t(), a.float() @ u.float().t())
+    assert torch.allclose(out.float(), want, atol=2e-2, rtol=2e-2)
+    _assert_clean()
+
+
+def test_w4_prefill_path_dequant_gemm():
+    torch.manual_seed(11)
+    N, Kd, M = 512, 1024, 200
+    qw = quantize(torch.randn(N, Kd) * 0.02, Fmt.INT4)
+    lin = W4Linear(qw, DEV, "p", workspace=Workspace(DEV))
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    lin(x, out, "f32")
+    wbf = qw.dequant().bfloat16().float()     # the GEMM sees bf16-rounded dequantized weights
+    want = x.float().cpu() @ wbf.t()
+    assert torch.allclose(out.cpu(), want, atol=3e-3, rtol=1e-3)
+    _assert_clean()
+
+
+@pytest.mark.parametrize("M,H", [(1, 256), (5, 5120), (33, 2048)])
+def test_add_rmsnorm(M, H):
+    torch.manual_seed(1)
+    h = torch.randn(M, H, device=DEV)
+    d32 = torch.randn(M, H, device=DEV)
+    w = torch.randn(H, device=DEV) * 0.1
+    for delta, off in ((None, 0.0), (d32, 1.0), (d32.bfloat16(), 1.0)):
+        hh = h.clone()
+        x = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.add_rmsnorm(hh, w, x, 1e-6, off, delta)
+        hr = h.clone() if delta is None else h + delta.float()
+        want = ref.rmsnorm(hr, w, 1e-6, off)
+        assert torch.allclose(hh, hr, atol=1e-6)
+        assert torch.allclose(x.float(), want, atol=2e-2, rtol=1e-2)
+
+
+def test_gemv_bf16_and_argmax_embed():
+    torch.manual_seed(2)
+    w = torch.randn(1000, 512) * 0.05
+    lin = BF16Linear(w, DEV)
+    for M in (1, 3, 8):
+        x = torch.randn(M, 512, device=DEV).bfloat16()
+        out = torch.empty(M, 1000, dtype=torch.float32, device=DEV)
+        lin(x, out, "f32")
+        want = x.float().cpu() @ w.bfloat16().float().t()
+        assert torch.allclose(out.cpu(), want, atol=2e-3, rtol=1e-3)
+    logits = torch.randn(4, 151936, device=DEV)
+    logits[1, 77] = 50.0
+    logits[1, 99999] = 50.0            # tie -> lowest index
+    ids = torch.zeros(4, dtype=torch.int32, device=DEV)
+    K.argmax_rows(logits, ids)
+    assert ids.cpu().tolist() == ref.argmax_lowest(logits.cpu()).tolist() and int(ids[1]) == 77
+    table = torch.randn(100, 64, device=DEV).bfloat16()
+    tok = torch.tensor([3, 99, 0], dtype=torch.int32, device=DEV)
+    h = torch.empty(3, 64, device=DEV)
+    K.embed(tok, table, h)
+    assert torch.equal(h, table[tok.long()].float())
+
+
+def _mk_kv(S, max_ctx, Hkv, D):
+    pages = S * (max_ctx // 16)
+    kv = K.KvLayer.alloc(pages, Hkv, D, DEV)
+    table = torch.arange(pages, dtype=torch.int32).reshape(S, max_ctx // 16)
+    # shuffle pages so the block table is really used
+    perm = torch.randperm(pages)
+    table = perm[table.long()].to(torch.int32)
+    return kv, table.to(DEV)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,rot,gated,qk", [(8, 2, 128, 128, False, False), (4, 2, 64, 64, False, True),
+                                                    (16, 2, 256, 64, True, True), (5, 1, 128, 128, False, False)])
+def test_rope_kvwrite_and_paged_decode(Hq, Hkv, D, rot, gated, qk):
+    torch.manual_seed(5)
+    S, max_ctx = 3, 256
+    geom = K.AttnGeom(Hq, Hkv, D, rot, 1.0 / math.sqrt(D), gated, 0, 1e-6, 1.0 if qk else 0.0)
+    kv, table = _mk_kv(S, max_ctx, Hkv, D)
+    kv_c = K.KvLayer(kv.k.cpu(), kv.v.cpu(), kv.ks.cpu(), kv.vs.cpu())
+    inv = ref.rope_inv_freq(rot, 1e6)
+    qn = (torch.randn(D) * 0.1) if qk else None
+    kn = (torch.randn(D) * 0.1) if qk else None
+    lens = [37, 200, 16]
+    qsz = Hq * D * (2 if gated else 1)
+    ws = Workspace(DEV)
+    # fill the caches token by token in a few row batches, on both devices
+    for start in range(0, max(lens), 50):
+        rows = [(s, p) for s in range(S) for p in range(start, min(start + 50, lens[s]))]
+        if not rows:
+            continue
+        M = len(rows)
+        qkv = (torch.randn(M, qsz + 2 * Hkv * D) * 0.7).bfloat16()
+        rs = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+        rp = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+        q_g = torch.empty(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+        g_g = torch.empty(M, Hq * D, dtype=torch.bfloat16, device=DEV) if gated else None
+        K.rope_kvwrite(qkv.to(DEV), rp.to(DEV), rs.to(DEV), table, inv.to(DEV), geom, q_g, kv,
+                       None if qn is None else qn.to(DEV), None if kn is None else kn.to(DEV), g_g)
+        q_c = torch.empty(M, Hq * D, dtype=torch.bfloat16)
+        g_c = torch.empty(M, Hq * D, dtype=torch.bfloat16) if gated else None
+        K.rope_kvwrite(qkv, rp, rs, table.cpu(), inv, geom, q_c, kv_c, qn, kn, g_c)
+        assert torch.allclose(q_g.float().cpu(), q_c.float(), atol=3e-2, rtol=2e-2)
+    # cache contents: int8 codes may differ by one step where rounding sits on a tie; dequantized values agree
+    for s in range(S):
+        npg = (lens[s] + 15) // 16
+        idx = table[s, :npg].long()
+        for a, sa, b, sb in ((kv.k, kv.ks, kv_c.k, kv_c.ks), (kv.v, kv.vs, kv_c.v, kv_c.vs)):
+            da = (a[idx].float() * sa[idx][..., None]).cpu().permute(0, 2, 1, 3).reshape(npg * 16, Hkv, D)[: lens[s]]
+            db = (b[idx.cpu()].float() * sb[idx.cpu()][..., None]).permute(0, 2, 1, 3).reshape(npg * 16, Hkv, D)[: lens[s]]
+            assert torch.allclose(da, db, atol=0.05, rtol=0.02)
+    # decode rows: last position of each sequence + a 4-row verify block on sequence 1
+    rows = [(0, lens[0] - 1), (1, lens[1] - 1), (2, lens[2] - 1)] + [(1, p) for p in range(100, 104)]
+    M = len(rows)
+    q = (torch.randn(M, Hq * D) * 0.7).bfloat16()
+    gate = (torch.randn(M, Hq * D)).bfloat16() if gated else None
+    rs = torch.tensor([r[0] for r in rows], dtype=torch.int32)
+    rp = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    kv_gc = K.KvLayer(kv.k.cpu(), kv.v.cpu(), kv.ks.cpu(), kv.vs.cpu())    # same cache bytes for the oracle
+    want = torch.empty(M, Hq * D, dtype=torch.float32)
+    K.paged_decode_attn(q, rs, rp, table.cpu(), kv_gc, geom, want, 1, None, gate)
+    for splits in (1, 3, 8):
+        out = torch.zeros(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+        for _ in range(2):   # twice: split counters must return to zero
+            K.paged_decode_attn(q.to(DEV), rs.to(DEV), rp.to(DEV), table, kv, geom, out, splits, ws,
+                                None if gate is None else gate.to(DEV))
+        assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), (splits, float((out.float().cpu() - want).abs().max()))
+    _assert_clean()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64), (4, 1, 256)])
+@pytest.mark.parametrize("M,pos0,window", [(64, 0, 0), (200, 0, 0), (100, 77, 0), (130, 300, 128)])
+def test_flash_prefill(Hq, Hkv, D, M, pos0, window):
+    torch.manual_seed(7)
+    T = pos0 + M
+    geom = K.AttnGeom(Hq, Hkv, D, D, 1.0 / math.sqrt(D), False, window)
+    q = (torch.randn(M, Hq * D) * 0.8).bfloat16()
+    k = (torch.randn(T + 5, Hkv * D) * 0.8).bfloat16()
+    v = (torch.randn(T + 5, Hkv * D) * 0.8).bfloat16()
+    want = torch.empty(M, Hq * D, dtype=torch.float32)
+    K.flash_prefill(q, k, v, geom, want, pos0)
+    out = torch.zeros(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+    K.flash_prefill(q.to(DEV), k.to(DEV), v.to(DEV), geom, out, pos0)
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
+
+
+def test_kv_gather_dequant():
+    torch.manual_seed(8)
+    Hkv, D = 2, 128
+    kv, table = _mk_kv(2, 128, Hkv, D)
+    kv.k.copy_(torch.randint(-127, 128, kv.k.shape, dtype=torch.int8))
+    kv.ks.copy_(torch.rand(kv.ks.shape) * 0.01)
+    kv.v.copy_(torch.randint(-127, 128, kv.v.shape, dtype=torch.int8))
+    kv.vs.copy_(torch.rand(kv.vs.shape) * 0.01)
+    T = 77
+    ok = torch.zeros(T, Hkv * D, dtype=torch.bfloat16, device=DEV)
+    ov = torch.zeros(T, Hkv * D, dtype=torch.bfloat16, device=DEV)
+    K.gather_kv_dense(kv, table[1], T, ok, ov)
+    kvc = K.KvLayer(kv.k.cpu(), kv.v.cpu(), kv.ks.cpu(), kv.vs.cpu())
+    ck = torch.zeros(T, Hkv * D, dtype=torch.bfloat16)
+    cv = torch.zeros(T, Hkv * D, dtype=torch.bfloat16)
+    K.gather_kv_dense(kvc, table[1].cpu(), T, ck, cv)
+    assert torch.equal(ok.cpu(), ck) and torch.equal(ov.cpu(), cv)
