@@ -19,6 +19,7 @@ namespace {
 constexpr int kPage = 16;
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
+constexpr int kMaxSplits = 64;
 
 struct DecParams {
   const bf16* q; int ld_q;
@@ -73,20 +74,51 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   const int tok_in_page = lane >> 1, half = lane & 1;
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
 
-  for (int pg = pbeg + warp; pg < pend; pg += kWarps) {
-    const int page = bt[pg];
-    const size_t pbase = ((size_t)page * p.Hkv + kvh) * kPage;
+  // K of the first page is fetched before the loop; inside, the V rows of the current page and the K
+  // rows of the next page are requested before the QK math so the loads overlap the arithmetic.
+  uint4 kreg[HD / 16];
+  float ksc = 0.f, vsc = 0.f;
+  int pg = pbeg + warp;
+  if (pg < pend) {
+    const size_t pb = ((size_t)bt[pg] * p.Hkv + kvh) * kPage;
+    const int8_t* kp = p.k_pages + (pb + tok_in_page) * D + half * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) kreg[c] = *reinterpret_cast<const uint4*>(kp + c * 16);
+    ksc = p.k_scale[pb + tok_in_page];
+    vsc = p.v_scale[pb + tok_in_page];
+  }
+  for (; pg < pend; pg += kWarps) {
+    const size_t pbase = ((size_t)bt[pg] * p.Hkv + kvh) * kPage;
     const int tok = pg * kPage + tok_in_page;
     const bool valid = tok < len && tok >= first;
+    // V rows of this page (lane = 4 dims of every token row)
+    const int8_t* vp = p.v_pages + pbase * D + lane * DPL;
+    uint32_t vraw[kPage][(DPL + 3) / 4];
+#pragma unroll
+    for (int j = 0; j < kPage; ++j) {
+      if (DPL == 4) vraw[j][0] = *reinterpret_cast<const uint32_t*>(vp + j * D);
+      else if (DPL == 8) { const uint2 w8 = *reinterpret_cast<const uint2*>(vp + j * D); vraw[j][0] = w8.x; vraw[j][(DPL + 3) / 4 - 1] = w8.y; }
+      else vraw[j][0] = *reinterpret_cast<const unsigned short*>(vp + j * D);
+    }
+    uint4 kcur[HD / 16];
+#pragma unroll
+    for (int c = 0; c < HD / 16; ++c) kcur[c] = kreg[c];
+    const float ksc_c = ksc, vsc_c = vsc;
+    if (pg + kWarps < pend) {
+      const size_t pb = ((size_t)bt[pg + kWarps] * p.Hkv + kvh) * kPage;
+      const int8_t* kp = p.k_pages + (pb + tok_in_page) * D + half * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 16; ++c) kreg[c] = *reinterpret_cast<const uint4*>(kp + c * 16);
+      ksc = p.k_scale[pb + tok_in_page];
+      vsc = p.v_scale[pb + tok_in_page];
+    }
     // ---- QK ----
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) s[g] = 0.f;
-    const int8_t* kp = p.k_pages + (pbase + tok_in_page) * D + half * HD;
 #pragma unroll
     for (int c = 0; c < HD / 16; ++c) {
-      const uint4 kv = *reinterpret_cast<const uint4*>(kp + c * 16);
-      const uint32_t wds[4] = {kv.x, kv.y, kv.z, kv.w};
+      const uint32_t wds[4] = {kcur[c].x, kcur[c].y, kcur[c].z, kcur[c].w};
 #pragma unroll
       for (int wv = 0; wv < 4; ++wv) {
 #pragma unroll
@@ -98,13 +130,11 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
         }
       }
     }
-    const float ksc = p.k_scale[pbase + tok_in_page];
-    const float vsc = p.v_scale[pbase + tok_in_page];
     float alpha[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float sg = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
-      sg = valid ? sg * ksc : -INFINITY;
+      sg = valid ? sg * ksc_c : -INFINITY;
       float mx = sg;
 #pragma unroll
       for (int off = 2; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -113,7 +143,7 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
       const float pr = (sg == -INFINITY) ? 0.f : __expf(sg - mnew);
       m[g] = mnew;
       l[g] = l[g] * alpha[g] + (half == 0 ? pr : 0.f);
-      if (half == 0) ps[warp][g][tok_in_page] = valid ? pr * vsc : 0.f;
+      if (half == 0) ps[warp][g][tok_in_page] = valid ? pr * vsc_c : 0.f;
     }
     __syncwarp();
     // ---- PV ----
@@ -121,23 +151,11 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     for (int g = 0; g < G; ++g)
 #pragma unroll
       for (int d = 0; d < DPL; ++d) o[g][d] *= alpha[g];
-    const int8_t* vp = p.v_pages + pbase * D + lane * DPL;
-#pragma unroll 4
+#pragma unroll
     for (int j = 0; j < kPage; ++j) {
       float vf[DPL];
-      if (DPL == 4) {
-        const uint32_t w4 = *reinterpret_cast<const uint32_t*>(vp + j * D);
 #pragma unroll
-        for (int d = 0; d < 4; ++d) vf[d] = (float)(int8_t)((w4 >> (8 * d)) & 0xff);
-      } else if (DPL == 8) {
-        const uint2 w8 = *reinterpret_cast<const uint2*>(vp + j * D);
-#pragma unroll
-        for (int d = 0; d < 4; ++d) { vf[d] = (float)(int8_t)((w8.x >> (8 * d)) & 0xff); vf[4 + d] = (float)(int8_t)((w8.y >> (8 * d)) & 0xff); }
-      } else {
-        const unsigned short w2 = *reinterpret_cast<const unsigned short*>(vp + j * D);
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) vf[d] = (float)(int8_t)((w2 >> (8 * d)) & 0xff);
-      }
+      for (int d = 0; d < DPL; ++d) vf[d] = (float)(int8_t)((vraw[j][d >> 2] >> (8 * (d & 3))) & 0xff);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         const float pj = ps[warp][g][j];
@@ -194,18 +212,34 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // Last CTA of this (row, kv head): merge the splits in split order.  The per-split (max, sum) pairs
+  // are staged in shared memory first so the long loop only carries independent loads.
   const size_t base = ((size_t)row * p.Hkv + kvh) * nsplit;
+  float* wts = &sm_o[0][0][0];            // reuse: [G][kMaxSplits] weights
+  for (int i = tid; i < G * nsplit; i += kThreads) {
+    const int g = i / nsplit, sp = i % nsplit;
+    wts[g * kMaxSplits + sp] = __ldcg(&p.part_ml[((base + sp) * G + g) * 2]);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float M_ = -INFINITY;
+    for (int sp = 0; sp < nsplit; ++sp) M_ = fmaxf(M_, wts[tid * kMaxSplits + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float ms = wts[tid * kMaxSplits + sp];
+      const float f = (ms == -INFINITY) ? 0.f : __expf(ms - M_);
+      wts[tid * kMaxSplits + sp] = f;
+      L += __ldcg(&p.part_ml[((base + sp) * G + tid) * 2 + 1]) * f;
+    }
+    sm_ml[0][tid][0] = L;
+  }
+  __syncthreads();
   for (int i = tid; i < G * D; i += kThreads) {
     const int g = i / D, d = i % D;
-    float M_ = -INFINITY;
-    for (int sp = 0; sp < nsplit; ++sp) M_ = fmaxf(M_, __ldcg(&p.part_ml[((base + sp) * G + g) * 2]));
-    float L = 0.f, O = 0.f;
-    for (int sp = 0; sp < nsplit; ++sp) {
-      const float ms = __ldcg(&p.part_ml[((base + sp) * G + g) * 2]);
-      const float f = (ms == -INFINITY) ? 0.f : __expf(ms - M_);
-      L += __ldcg(&p.part_ml[((base + sp) * G + g) * 2 + 1]) * f;
-      O += __ldcg(&p.part_o[((base + sp) * G + g) * D + d]) * f;
-    }
+    float O = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < nsplit; ++sp) O = fmaf(__ldcg(&p.part_o[((base + sp) * G + g) * D + d]), wts[g * kMaxSplits + sp], O);
+    const float L = sm_ml[0][g][0];
     float r = L > 0.f ? O / L : 0.f;
     const size_t oi = (size_t)row * p.ld_o + (size_t)(kvh * G + g) * D + d;
     if (p.gate) r *= sigmoid_f(__bfloat162float(p.gate[oi]));
@@ -242,7 +276,7 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
                                   const void* v_scale, const void* gate, void* out, int ld_o, void* part_o, void* part_ml,
                                   void* counters, int M, int Hq, int Hkv, int D, int splits, int window, float scale,
                                   void* stream) {
-  if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1) return -2;
+  if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1 || splits > kMaxSplits) return -2;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return -2;
   DecParams p;
   p.q = (const bf16*)q; p.ld_q = ld_q; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos;

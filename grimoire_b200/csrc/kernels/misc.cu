@@ -26,38 +26,50 @@ __global__ void embed_kernel(const int* __restrict__ ids, const bf16* __restrict
 }
 
 // ties resolve to the lowest index (greedy decoding must be reproducible across batchings).
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out_id,
-                                                      float* __restrict__ out_val, int V, int ld) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
-  const int row = blockIdx.x;
+__device__ __forceinline__ void amax_combine(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+}
+
+constexpr int kArgChunks = 64;
+
+// Stage 1: grid (kArgChunks, M), each CTA scans a slice of the vocabulary with coalesced loads;
+// the last CTA to arrive for a row folds the kArgChunks partial (value, index) pairs.
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out_id,
+                                                     float* __restrict__ out_val, float* __restrict__ part_val,
+                                                     int* __restrict__ part_idx, unsigned int* __restrict__ counters, int V,
+                                                     int ld) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ int s_last;
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int per = (V + kArgChunks - 1) / kArgChunks;
+  const int lo = chunk * per, hi = min(V, lo + per);
   const float* p = logits + (size_t)row * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = p[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
+  for (int i = lo + threadIdx.x; i < hi; i += 256) amax_combine(best, bi, p[i], i);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-  }
+  for (int o = 16; o > 0; o >>= 1) amax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { sv[warp] = best; si[warp] = bi; }
   __syncthreads();
-  if (warp == 0) {
-    best = lane < (blockDim.x >> 5) ? sv[lane] : -INFINITY;
-    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (lane == 0) { out_id[row] = bi; if (out_val) out_val[row] = best; }
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) amax_combine(best, bi, sv[w], si[w]);
+    part_val[row * kArgChunks + chunk] = best;
+    part_idx[row * kArgChunks + chunk] = bi;
+    __threadfence();
+    const unsigned int prev = atomicAdd(&counters[row], 1u);
+    s_last = (prev == kArgChunks - 1);
+    if (s_last) counters[row] = 0u;
   }
+  __syncthreads();
+  if (!s_last || warp != 0) return;
+  __threadfence();
+  best = -INFINITY; bi = 0x7fffffff;
+  for (int c = lane; c < kArgChunks; c += 32) amax_combine(best, bi, __ldcg(&part_val[row * kArgChunks + c]), __ldcg(&part_idx[row * kArgChunks + c]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax_combine(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (lane == 0) { out_id[row] = bi; if (out_val) out_val[row] = best; }
 }
 
 // out[0]=sum of squares, [1]=max abs, [2]=#nan, [3]=#inf  (fp32 input)
@@ -98,8 +110,13 @@ GRM_API int grm_embed(const void* ids, const void* table, void* h, int M, int H,
   GRM_LAUNCH_RET();
 }
 
-GRM_API int grm_argmax(const void* logits, void* out_id, void* out_val, int M, int V, int ld, void* stream) {
-  argmax_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, (int*)out_id, (float*)out_val, V, ld);
+// part_val / part_idx: M*64 floats / ints of scratch; counters: M zeroed uints (left at zero).
+GRM_API int grm_argmax(const void* logits, void* out_id, void* out_val, void* part_val, void* part_idx, void* counters, int M,
+                       int V, int ld, void* stream) {
+  if (!part_val || !part_idx || !counters || M < 1) return -2;
+  dim3 grid(kArgChunks, M);
+  argmax_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)logits, (int*)out_id, (float*)out_val, (float*)part_val,
+                                                        (int*)part_idx, (unsigned int*)counters, V, ld);
   GRM_LAUNCH_RET();
 }
 

@@ -28,8 +28,9 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
+constexpr int kRing = 8;                // bulk-copy stages in flight per warp
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_AR_ADD = 4 };
 
 struct W4Params {
   const uint4* w;
@@ -42,7 +43,23 @@ struct W4Params {
   int ldx, ldo;
   int g64;                  // group size / 64 (1, 2 or 4)
   int ksplit;               // grid-level K slices
+  // ---- fused tensor-parallel all-reduce (EPI_AR_ADD): out(fp32) += sum over ranks of the partials ----
+  float* ar_recv[8];        // rank p's receive region: [2 parity][world][tiles][NV] floats (peer-mapped)
+  unsigned int* ar_flags[8];// rank p's arrival flags:   [tiles][world]
+  unsigned int* ar_epochs;  // local, [tiles]: number of fused launches this tile has completed
+  unsigned int* status;     // device status block (timeouts)
+  int ar_world, ar_rank;
+  unsigned int ar_spin;     // poll limit of the arrival wait
 };
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
   uint32_t r;
@@ -75,13 +92,19 @@ __device__ __forceinline__ void epilogue_store(const W4Params& p, int tile, int 
     const size_t o = (size_t)m * p.ldo + n;
     if (EPI == EPI_BF16) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(val);
     else if (EPI == EPI_F32) reinterpret_cast<float*>(p.out)[o] = val;
-    else reinterpret_cast<float*>(p.out)[o] += val;
+    else reinterpret_cast<float*>(p.out)[o] += val;   // EPI_ADD_F32 and EPI_AR_ADD
   }
 }
 
 template <int MT, int R, int EPI>
 __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
-  extern __shared__ float red[];  // [kWarps][R*MT*4][32]
+  // dynamic shared memory: [kWarps][kRing][R*512] weight ring | [kWarps][R*MT*4][32] reduce | barriers
+  extern __shared__ __align__(128) uint8_t smem_dyn[];
+  constexpr int kStageBytes = R * 512;
+  constexpr int NVc = R * MT * 4 * 32;
+  uint8_t* ring = smem_dyn + (size_t)(threadIdx.x >> 5) * kRing * kStageBytes;
+  float* red = reinterpret_cast<float*>(smem_dyn + (size_t)kWarps * kRing * kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + (size_t)kWarps * NVc) + (threadIdx.x >> 5) * kRing;
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -105,32 +128,44 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 
   if (gbeg < gend) {
     const int kt0 = gbeg * p.g64, kt1 = gend * p.g64;
-    // weight pointers: row tile nt -> ((nt>>1)*KT + kt)*64 + (nt&1)*32 + lane
-    const uint4* wp[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int nt = tile * R + r;
-      wp[r] = p.w + ((size_t)(nt >> 1) * KT) * 64 + (nt & 1) * 32 + lane;
+    const int nkt = kt1 - kt0;
+    // The weight stream of this warp: k tile kt of its row tile(s) is kStageBytes contiguous bytes.
+    // R == 2: super-tile `tile`, both halves (1 KiB).  R == 1: row tile `tile`, one half (512 B).
+    const uint4* wsrc = (R == 2) ? p.w + ((size_t)tile * KT) * 64
+                                 : p.w + ((size_t)(tile >> 1) * KT) * 64 + (tile & 1) * 32;
+    // Per-warp ring fed by bulk async copies (TMA engine, completion on an mbarrier): kRing stages
+    // stay in flight per warp regardless of register pressure, which is what saturates HBM.
+    if (lane == 0) {
+      for (int i = 0; i < kRing; ++i) mbar_init(&bars[i], 1);
+      mbar_fence_init();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      const int pre = nkt < kRing ? nkt : kRing;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&bars[i], kStageBytes);
+        bulk_load(ring + i * kStageBytes, wsrc + (size_t)(kt0 + i) * 64, kStageBytes, &bars[i]);
+      }
     }
-    uint4 wcur[R], wnxt[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) wcur[r] = ldg_stream_v4(wp[r] + (size_t)kt0 * 64);
-#pragma unroll
-    for (int r = 0; r < R; ++r) wnxt[r] = (kt0 + 1 < kt1) ? ldg_stream_v4(wp[r] + (size_t)(kt0 + 1) * 64) : wcur[r];
+    __syncwarp();
 
     float accg[R][MT][4];
     uint32_t zc[R][2];
     float sc[R][2];
     const uint32_t* xw = reinterpret_cast<const uint32_t*>(p.x);
     const int ldxw = p.ldx >> 1;
+    bool alive = true;
 
-    for (int kt = kt0; kt < kt1; ++kt) {
+    for (int it = 0; it < nkt; ++it) {
+      const int kt = kt0 + it;
+      const int stg = it % kRing;
+      if (alive && !mbar_wait(&bars[stg], (uint32_t)(it / kRing) & 1u, p.status, 0x500u | stg)) alive = false;
       uint4 wuse[R];
 #pragma unroll
-      for (int r = 0; r < R; ++r) { wuse[r] = wcur[r]; wcur[r] = wnxt[r]; }
-      if (kt + 2 < kt1) {
-#pragma unroll
-        for (int r = 0; r < R; ++r) wnxt[r] = ldg_stream_v4(wp[r] + (size_t)(kt + 2) * 64);
+      for (int r = 0; r < R; ++r)
+        wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStageBytes + r * 512 + lane * 16);
+      __syncwarp();   // every lane has its words in registers: the stage may be refilled
+      if (lane == 0 && alive && it + kRing < nkt) {
+        mbar_expect_tx(&bars[stg], kStageBytes);
+        bulk_load(ring + stg * kStageBytes, wsrc + (size_t)(kt + kRing) * 64, kStageBytes, &bars[stg]);
       }
       if ((kt & (p.g64 - 1)) == 0) {
         const int gi = kt / p.g64;
@@ -204,6 +239,52 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       for (int c = 0; c < 4; ++c) red[warp * NV + ((r * MT + mt) * 4 + c) * 32 + lane] = acc[r][mt][c];
   __syncthreads();
 
+  if (EPI == EPI_AR_ADD) {
+    // One-shot all-reduce fused into the epilogue: push this rank's partial tile into every rank's
+    // receive region over NVLink, raise a per-(tile, source) flag with release semantics, wait
+    // (bounded) for the flags of all sources, then sum the W partials in rank order -- every rank
+    // adds the same numbers in the same order, so all ranks hold bit-identical results (the
+    // property the reference keeps with its rank-ordered shared-memory sums, grimoire.cpp:6263-6366).
+    // Receive regions are double-buffered by launch parity: a peer can be at most one fused launch
+    // ahead, because its next launch needs this rank's next push.
+    __shared__ int s_fail;
+    const int W = p.ar_world;
+    const unsigned int e = p.ar_epochs[tile] + 1u;
+    const size_t tiles = gridDim.x;
+    const size_t par = e & 1u;
+    if (tid == 0) s_fail = 0;
+    for (int v = tid; v < NV; v += kThreads) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) s += red[w * NV + v];
+      const size_t off = ((par * W + p.ar_rank) * tiles + tile) * NV + v;
+      for (int r = 0; r < W; ++r) p.ar_recv[r][off] = s;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < W) st_release_sys(p.ar_flags[tid] + (size_t)tile * W + p.ar_rank, e);
+    if (tid < W) {
+      const unsigned int* f = p.ar_flags[p.ar_rank] + (size_t)tile * W + tid;
+      bool ok = false;
+      for (unsigned int i = 0; i < p.ar_spin; ++i) {
+        if ((int)(ld_acquire_sys(f) - e) >= 0) { ok = true; break; }
+        if (i > 16) __nanosleep(20);
+      }
+      if (!ok) { s_fail = 1; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x10000u | (tid << 12) | (tile & 0xfff)); }
+    }
+    __syncthreads();
+    if (!s_fail) {
+      const float* mine = p.ar_recv[p.ar_rank];
+      for (int v = tid; v < NV; v += kThreads) {
+        float s = 0.f;
+        for (int r = 0; r < W; ++r) s += __ldcg(mine + ((par * W + r) * tiles + tile) * NV + v);
+        epilogue_store<MT, R, EPI>(p, tile, v, s, 0.f);
+      }
+    }
+    if (tid == 0) p.ar_epochs[tile] = e;   // advance even after a timeout so later launches stay aligned
+    return;
+  }
+
   if (p.ksplit == 1) {
     if (EPI == EPI_SWIGLU) {
       constexpr int NH = NV / 2;  // r = 0 half holds the gate rows, r = 1 the up rows
@@ -264,10 +345,24 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 template <int MT, int R, int EPI>
 int launch(const W4Params& p, cudaStream_t st) {
   constexpr int NV = R * MT * 4 * 32;
-  const size_t smem = (size_t)kWarps * NV * sizeof(float);
+  const size_t smem = (size_t)kWarps * kRing * R * 512 + (size_t)kWarps * NV * sizeof(float) + (size_t)kWarps * kRing * 8;
   auto kfn = smallm_w4_kernel<MT, R, EPI>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool attr_done = false;
+  if (!attr_done && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
   dim3 grid(p.N / (16 * R), p.ksplit);
+  if (EPI == EPI_AR_ADD) {
+    // CTAs of different ranks wait for one another's pushes: every CTA of this grid must be
+    // resident at once, otherwise resident CTAs could wait for peers whose partner CTA has no SM.
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, kThreads, smem) != cudaSuccess) return -2;
+    if ((long)per_sm * sms < (long)grid.x * grid.y) return -2;
+  }
   kfn<<<grid, kThreads, smem, st>>>(p);
   GRM_LAUNCH_RET();
 }
@@ -278,10 +373,28 @@ int launch_epi(const W4Params& p, int epi, cudaStream_t st) {
     case EPI_BF16: return launch<MT, R, EPI_BF16>(p, st);
     case EPI_F32: return launch<MT, R, EPI_F32>(p, st);
     case EPI_ADD_F32: return launch<MT, R, EPI_ADD_F32>(p, st);
+    case EPI_AR_ADD: return launch<MT, R, EPI_AR_ADD>(p, st);
     default: return -1;
   }
 }
 
+}  // namespace
+
+namespace {
+int dispatch(W4Params& p, int epi, int rows_per_cta, cudaStream_t st) {
+  const int MT = (p.M + 7) / 8;
+  if (epi == EPI_SWIGLU) {
+    if (MT <= 1) return launch<1, 2, EPI_SWIGLU>(p, st);
+    if (MT <= 2) return launch<2, 2, EPI_SWIGLU>(p, st);
+    if (MT <= 4) return launch<4, 2, EPI_SWIGLU>(p, st);
+    return launch<8, 2, EPI_SWIGLU>(p, st);
+  }
+  const bool r2 = rows_per_cta == 32;
+  if (MT <= 1) return r2 ? launch_epi<1, 2>(p, epi, st) : launch_epi<1, 1>(p, epi, st);
+  if (MT <= 2) return r2 ? launch_epi<2, 2>(p, epi, st) : launch_epi<2, 1>(p, epi, st);
+  if (MT <= 4) return launch_epi<4, 1>(p, epi, st);
+  return launch_epi<8, 1>(p, epi, st);
+}
 }  // namespace
 
 // out: EPI 0 bf16 [M][ldo], 1 fp32 [M][ldo], 2 fp32 accumulate (out += y), 3 SwiGLU bf16 [M][ldo]
@@ -299,17 +412,31 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
-  cudaStream_t st = (cudaStream_t)stream;
-  const int MT = (M + 7) / 8;
-  if (epi == EPI_SWIGLU) {
-    if (MT <= 1) return launch<1, 2, EPI_SWIGLU>(p, st);
-    if (MT <= 2) return launch<2, 2, EPI_SWIGLU>(p, st);
-    if (MT <= 4) return launch<4, 2, EPI_SWIGLU>(p, st);
-    return launch<8, 2, EPI_SWIGLU>(p, st);
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  if (epi == EPI_AR_ADD) return -1;   // use grm_smallm_w4_allreduce
+  return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
+}
+
+// Row-parallel projection fused with the tensor-parallel all-reduce: h[M][ldo] (fp32) += sum over
+// ranks of X_r . W_r^T.  recv / flags are arrays of `world` peer-mapped device pointers (see the
+// W4Params comment for their layouts; recv needs 2*world*(N/16)*MT*128 floats per rank, flags
+// (N/16)*world uints, epochs N/16 uints, all zero before first use).  Every rank must issue the same
+// sequence of calls with the same M.  spin = poll limit of the arrival wait (0 = default ~0.1 s).
+GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x, void* h, int M, int N, int K, int ldx,
+                                    int ldo, int group, const void* const* recv, const void* const* flags, void* epochs,
+                                    int world, int rank, unsigned int spin, void* stream) {
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 1)) return -2;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !recv || !flags || !epochs) return -2;
+  W4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = h;
+  p.scratch = nullptr; p.counters = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = 1;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_recv[i] = i < world ? (float*)const_cast<void*>(recv[i]) : nullptr;
+    p.ar_flags[i] = i < world ? (unsigned int*)const_cast<void*>(flags[i]) : nullptr;
   }
-  const bool r2 = rows_per_cta == 32;
-  if (MT <= 1) return r2 ? launch_epi<1, 2>(p, epi, st) : launch_epi<1, 1>(p, epi, st);
-  if (MT <= 2) return r2 ? launch_epi<2, 2>(p, epi, st) : launch_epi<2, 1>(p, epi, st);
-  if (MT <= 4) return launch_epi<4, 1>(p, epi, st);
-  return launch_epi<8, 1>(p, epi, st);
+  p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
+  p.ar_spin = spin ? spin : 2000000u;
+  return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }

@@ -178,10 +178,10 @@ def gather_kv_dense(kv: KvLayer, pages_of_seq: torch.Tensor, T: int, out_k: torc
 
 
 def decode_splits(max_len: int, M: int, Hkv: int) -> int:
-    """Split-KV factor: enough CTAs to fill 148 SMs, at least 2 pages per split."""
+    """Split-KV factor: enough CTAs to fill 148 SMs, at least 8 pages (2 per warp) per split."""
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     want = max(1, (4 * 148) // max(1, M * Hkv))
-    cap = int(max(1, min(want, pages // 2 if pages >= 2 else 1, 64)))
+    cap = int(max(1, min(want, pages // 8 if pages >= 8 else 1, 64)))   # >= 2 pages per warp
     s = 1
     while s * 2 <= cap:     # powers of two only: the decode graphs are keyed by (rows, splits)
         s *= 2
@@ -268,8 +268,13 @@ def argmax_rows(logits: torch.Tensor, out_ids: torch.Tensor) -> torch.Tensor:
         out_ids.copy_(ref.argmax_lowest(logits.float()))
         return out_ids
     M, V = logits.shape
-    code = _native.cuda().grm_argmax(_native.ptr(logits), _native.ptr(out_ids), None, _c(M), _c(V), _c(logits.stride(0)),
-                                     _native.stream_ptr())
+    from .workspace import default_workspace
+    ws = default_workspace(logits.device)
+    pv = ws.get("argmax_val", max(M, 64) * 64, torch.float32)
+    pi = ws.get("argmax_idx", max(M, 64) * 64, torch.int32)
+    cnt = ws.get("argmax_counters", 1024, torch.int32, zero=True)
+    code = _native.cuda().grm_argmax(_native.ptr(logits), _native.ptr(out_ids), None, _native.ptr(pv), _native.ptr(pi),
+                                     _native.ptr(cnt), _c(M), _c(V), _c(logits.stride(0)), _native.stream_ptr())
     _native.check(code, "argmax")
     return out_ids
 

@@ -100,7 +100,9 @@ class W4Linear:
             rows, ksplit, tiles = self._plan_smallm(M)
             scratch = counters = None
             if ksplit > 1:
-                mt = (M + 7) // 8
+                mt = 1
+                while mt * 8 < M:          # the kernel is instantiated for 1, 2, 4 or 8 row tiles
+                    mt *= 2
                 scratch = self.ws.get("smallm_scratch", ksplit * tiles * (rows // 16) * mt * 128, torch.float32)
                 counters = self.ws.get("smallm_counters", 8192, torch.int32, zero=True)
             code = lib.grm_smallm_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out),

@@ -1,0 +1,115 @@
+"""Tensor parallelism ("Megatron" split, one all-reduce per block = two per layer).
+
+Same partitioning as the reference's tp_mega mode (grimoire.cpp:2500-2534, slicing :5256-5368):
+each rank *is* the model with 1/W of the q / kv heads and of the FFN width; q|k|v and gate|up keep
+row blocks, o_proj and down_proj keep K columns, embeddings / norms / lm_head are replicated and
+every rank therefore picks the same token.  What differs is the exchange.  The reference stages
+partial sums through host memory (tp_small_allreduce, ~33 us per [1][H] exchange,
+grimoire.cpp:6499-6679); here the row-parallel projection and the all-reduce are ONE kernel
+(smallm_w4.cu, EPI_AR_ADD): each CTA pushes its partial tile into every peer's receive region over
+NVLink, raises a per-(tile, source) flag, waits (bounded) for the peers' flags and sums the W
+partials in rank order, so all ranks hold bit-identical results.
+
+Peer memory comes from ``torch.distributed._symmetric_memory`` (allocation + handle exchange only;
+all traffic is issued by our kernels).  Rows beyond the small-M kernel's range (prefill chunks) use
+the fused GEMM reduce-scatter / all-gather path when available and an NCCL all-reduce otherwise;
+the NCCL composition is also the measured baseline (``fused=False``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops.linear import SMALLM_MAX, W4Linear
+
+
+class CommTimeout(RuntimeError):
+    """A bounded device-side wait on a peer ran out (the kernel returned; the context is usable)."""
+
+
+class SymmetricBuffer:
+    """A tensor allocated at the same offset on every rank, with the peers' mappings."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, group, device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.local = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, group=group.group_name)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.world = len(self.ptrs)
+
+    def ptr_array(self):
+        return (ctypes.c_void_p * self.world)(*self.ptrs)
+
+
+class TensorParallel:
+    def __init__(self, group, device, fused: Optional[bool] = None):
+        self.group = group
+        self.device = torch.device(device)
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if fused is None:
+            fused = os.environ.get("GRIMOIRE_TP_FUSED", "1") != "0"
+        self.fused = fused and self.device.type == "cuda"
+        self.recv: Optional[SymmetricBuffer] = None
+        self.flags: Optional[SymmetricBuffer] = None
+        self.epochs: Optional[torch.Tensor] = None
+        self.partial: Optional[torch.Tensor] = None
+        self.spin = int(os.environ.get("GRIMOIRE_TP_SPIN", "0"))
+        self.stats = {"fused_allreduce": 0, "nccl_allreduce": 0}
+
+    def attach(self, model, max_rows: int = 64) -> None:
+        """Size the exchange buffers for ``model`` (hidden width) and hook the model's row-parallel ops."""
+        H = model.cfg.hidden_size
+        model.tp = self
+        self.partial = torch.zeros(max_rows, H, dtype=torch.float32, device=self.device)
+        if not self.fused:
+            return
+        tiles = (H + 31) // 32 * 32 // 16
+        nv_max = 8 * 128                                   # MT = 8, R = 1
+        try:
+            self.recv = SymmetricBuffer(2 * self.world * tiles * nv_max, torch.float32, self.group, self.device)
+            self.flags = SymmetricBuffer(tiles * self.world, torch.int32, self.group, self.device)
+        except Exception as e:  # pragma: no cover - depends on the driver / fabric
+            raise RuntimeError(f"symmetric peer memory is unavailable ({e}); set GRIMOIRE_TP_FUSED=0 to run the "
+                               f"NCCL-only baseline") from e
+        self.epochs = torch.zeros(tiles, dtype=torch.int32, device=self.device)
+        dist.barrier(self.group)
+        torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------------------------------
+    def row_parallel_add(self, lin, x: torch.Tensor, h: torch.Tensor) -> None:
+        """h (fp32 [M][H], replicated) += all-reduce over ranks of ``x @ W_rank^T``."""
+        M = x.shape[0]
+        if self.fused and M <= SMALLM_MAX and isinstance(lin, W4Linear) and lin.tiled is not None:
+            t = lin.tiled
+            code = _native.cuda().grm_smallm_w4_allreduce(
+                _native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(h), ctypes.c_int(M), ctypes.c_int(t.N),
+                ctypes.c_int(t.K), ctypes.c_int(x.stride(0)), ctypes.c_int(h.stride(0)), ctypes.c_int(t.group),
+                self.recv.ptr_array(), self.flags.ptr_array(), _native.ptr(self.epochs), ctypes.c_int(self.world),
+                ctypes.c_int(self.rank), ctypes.c_uint(self.spin), _native.stream_ptr())
+            _native.check(code, f"smallm_w4_allreduce {lin.name}")
+            self.stats["fused_allreduce"] += 1
+            return
+        part = self.partial[:M] if self.partial is not None and M <= self.partial.shape[0] else torch.empty(
+            M, h.shape[1], dtype=torch.float32, device=h.device)
+        lin(x, part, "f32")
+        dist.all_reduce(part, group=self.group)
+        h.add_(part)
+        self.stats["nccl_allreduce"] += 1
+
+    def check(self) -> None:
+        """Raise CommTimeout if a fused kernel recorded a peer-wait timeout."""
+        if self.device.type != "cuda":
+            return
+        from ..ops.core import status_read
+
+        code, detail, n = status_read()
+        if code:
+            raise CommTimeout(f"device status code {code} detail {detail:#x} ({n} events) on rank {self.rank}")
