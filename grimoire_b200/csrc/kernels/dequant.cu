@@ -36,11 +36,11 @@ __global__ void __launch_bounds__(256) dequant_w4_kernel(const uint4* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {   // register r: row g + 8*(r&1), k = 16j + 2t + 8*(r>>1) + {0,1}
+      for (int r = 0; r < 4; ++r) {   // register r: row g + 8*(r&1), k = 16t + 4j + 2*(r>>1) + {0,1}
         const int lo = (wj[j] >> (4 * r)) & 0xf, hi = (wj[j] >> (4 * r + 16)) & 0xf;
         const int rr = r & 1;
         const int row = half * 16 + g + 8 * rr;
-        const int col = ktl * 64 + 16 * j + 2 * t + 8 * (r >> 1);
+        const int col = ktl * 64 + 16 * t + 4 * j + 2 * (r >> 1);
         const uint32_t o = pack_bf16x2(((float)lo - zc[rr]) * sc[rr], ((float)hi - zc[rr]) * sc[rr]);
         *reinterpret_cast<uint32_t*>(&tile[row][col]) = o;
       }

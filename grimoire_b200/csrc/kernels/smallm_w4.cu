@@ -20,7 +20,8 @@
 //
 // Tiled layout (built by grimoire_b200/formats/w4_tile_layout.py, checked by tests/test_w4_layout.py):
 //   w   : [N/32][K/64][2][32 lanes] uint4.  Lane L (g=L/4, t=L%4), word j (k16 step j), nibble i:
-//         row = 16*rowtile + g + 8*(i&1), k = 64*kt + 16*j + 2*t + 8*((i>>1)&1) + (i>>2)
+//         row = 16*rowtile + g + 8*(i&1), k = 64*kt + 16*t + 4*j + 2*((i>>1)&1) + (i>>2)
+//         (a lane's 16 columns of a k tile are contiguous, so its activation fragment is two 16-byte reads)
 //   sz  : [N/16][K/group][16] uint32: low 16 bits = fp16 scale, high 16 bits = bf16(128 + zero)
 #include "common.cuh"
 
@@ -28,7 +29,6 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kRing = 8;                // bulk-copy stages in flight per warp
 
 enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_AR_ADD = 4 };
 
@@ -43,6 +43,8 @@ struct W4Params {
   int ldx, ldo;
   int g64;                  // group size / 64 (1, 2 or 4)
   int ksplit;               // grid-level K slices
+  int szg;                  // groups per warp (capacity of the per-warp scale staging area)
+  int stage;                // bytes of one ring stage: R*512 + M*144
   // ---- fused tensor-parallel all-reduce (EPI_AR_ADD): out(fp32) += sum over ranks of the partials ----
   float* ar_recv[8];        // rank p's receive region: [2 parity][world][tiles][NV] floats (peer-mapped)
   unsigned int* ar_flags[8];// rank p's arrival flags:   [tiles][world]
@@ -96,17 +98,29 @@ __device__ __forceinline__ void epilogue_store(const W4Params& p, int tile, int 
   }
 }
 
+// Ring depth (stages of R*512 weight bytes in flight per warp) by batch width.
+template <int MT> struct RingDepth { static constexpr int v = MT <= 2 ? 8 : 4; };
+
+// slow path of the stage wait, kept out of line so the hot loop carries only one try_wait
+__device__ __noinline__ bool stage_wait_slow(uint64_t* bar, uint32_t parity, unsigned int* status, uint32_t tag) {
+  return mbar_wait(bar, parity, status, tag);
+}
+
 template <int MT, int R, int EPI>
 __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
-  // dynamic shared memory: [kWarps][kRing][R*512] weight ring | [kWarps][R*MT*4][32] reduce | barriers
+  // dynamic shared memory: [kWarps][RING][R*512] weight ring | [kWarps][R*MT*4][32] reduce | barriers | scales
   extern __shared__ __align__(128) uint8_t smem_dyn[];
-  constexpr int kStageBytes = R * 512;
+  constexpr int RING = RingDepth<MT>::v;
+  constexpr int kStage = R * 512;
   constexpr int NVc = R * MT * 4 * 32;
-  uint8_t* ring = smem_dyn + (size_t)(threadIdx.x >> 5) * kRing * kStageBytes;
-  float* red = reinterpret_cast<float*>(smem_dyn + (size_t)kWarps * kRing * kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(red + (size_t)kWarps * NVc) + (threadIdx.x >> 5) * kRing;
-  __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* ring = smem_dyn + warp * (RING * kStage);
+  float* red = reinterpret_cast<float*>(smem_dyn + kWarps * RING * kStage);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + kWarps * NVc) + warp * (RING + 1);
+  // scale / zero words of this warp's groups: [R][p.szg][16] uint32, staged once by a bulk copy
+  uint32_t* szs = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(red + kWarps * NVc) + kWarps * (RING + 1) * 8) +
+                  (size_t)warp * R * p.szg * 16;
+  __shared__ int s_last;
   const int g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x;          // super-tile of R row tiles
   const int KT = p.K >> 6;              // k tiles of 64
@@ -128,104 +142,132 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 
   if (gbeg < gend) {
     const int kt0 = gbeg * p.g64, kt1 = gend * p.g64;
-    const int nkt = kt1 - kt0;
-    // The weight stream of this warp: k tile kt of its row tile(s) is kStageBytes contiguous bytes.
-    // R == 2: super-tile `tile`, both halves (1 KiB).  R == 1: row tile `tile`, one half (512 B).
-    const uint4* wsrc = (R == 2) ? p.w + ((size_t)tile * KT) * 64
-                                 : p.w + ((size_t)(tile >> 1) * KT) * 64 + (tile & 1) * 32;
-    // Per-warp ring fed by bulk async copies (TMA engine, completion on an mbarrier): kRing stages
-    // stay in flight per warp regardless of register pressure, which is what saturates HBM.
+    // The weight stream of this warp: k tile kt of its row tile(s) is R*512 contiguous bytes, and
+    // consecutive k tiles are 1 KiB apart.  R == 2: both halves of super-tile `tile`; R == 1: one half.
+    const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(
+        (R == 2) ? p.w + ((size_t)tile * KT) * 64 : p.w + ((size_t)(tile >> 1) * KT) * 64 + (tile & 1) * 32);
+    // Per-warp ring fed by bulk async copies (TMA engine, completion on an mbarrier): RING stages of
+    // weights stay in flight per warp regardless of register pressure.
     if (lane == 0) {
-      for (int i = 0; i < kRing; ++i) mbar_init(&bars[i], 1);
+      for (int i = 0; i <= RING; ++i) mbar_init(&bars[i], 1);
       mbar_fence_init();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      const int pre = nkt < kRing ? nkt : kRing;
+      // scales first: a load at the point of use would expose a DRAM latency per group
+      const uint32_t szbytes = (uint32_t)(gend - gbeg) * 64u;
+      mbar_expect_tx(&bars[RING], szbytes * R);
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        bulk_load(szs + (size_t)r * p.szg * 16, p.sz + ((size_t)(tile * R + r) * G + gbeg) * 16, szbytes, &bars[RING]);
+      const int pre = min(kt1 - kt0, RING);
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&bars[i], kStageBytes);
-        bulk_load(ring + i * kStageBytes, wsrc + (size_t)(kt0 + i) * 64, kStageBytes, &bars[i]);
+        mbar_expect_tx(&bars[i], kStage);
+        bulk_load(ring + i * kStage, wsrc + (size_t)(kt0 + i) * 1024, kStage, &bars[i]);
       }
     }
     __syncwarp();
 
-    float accg[R][MT][4];
-    uint32_t zc[R][2];
-    float sc[R][2];
-    const uint32_t* xw = reinterpret_cast<const uint32_t*>(p.x);
-    const int ldxw = p.ldx >> 1;
-    bool alive = true;
+    // Activation fragments: lane (g, t) owns columns 16t..16t+15 of batch row 8*mt+g in every k tile
+    // (the weight tiles use the same K order), i.e. two 16-byte loads per k tile, fetched one k tile
+    // ahead into registers; the L1 line of a later k tile is requested with a prefetch.
+    const uint4* xp[MT];
+    bool xok[MT];
+    uint4 xa[MT], xb[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int m = mt * 8 + g;
+      xok[mt] = m < p.M;
+      xp[mt] = reinterpret_cast<const uint4*>(p.x + (size_t)(xok[mt] ? m : 0) * p.ldx + (size_t)kt0 * 64 + t * 16);
+      xa[mt] = xb[mt] = make_uint4(0u, 0u, 0u, 0u);
+      if (xok[mt]) { xa[mt] = __ldg(xp[mt]); xb[mt] = __ldg(xp[mt] + 1); }
+    }
+    constexpr int kAhead = 4;   // k tiles of L1 prefetch distance (one 128-byte line per row and k tile)
 
-    for (int it = 0; it < nkt; ++it) {
-      const int kt = kt0 + it;
-      const int stg = it % kRing;
-      if (alive && !mbar_wait(&bars[stg], (uint32_t)(it / kRing) & 1u, p.status, 0x500u | stg)) alive = false;
-      uint4 wuse[R];
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-        wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStageBytes + r * 512 + lane * 16);
-      __syncwarp();   // every lane has its words in registers: the stage may be refilled
-      if (lane == 0 && alive && it + kRing < nkt) {
-        mbar_expect_tx(&bars[stg], kStageBytes);
-        bulk_load(ring + stg * kStageBytes, wsrc + (size_t)(kt + kRing) * 64, kStageBytes, &bars[stg]);
-      }
-      if ((kt & (p.g64 - 1)) == 0) {
-        const int gi = kt / p.g64;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const int nt = tile * R + r;
-          const uint32_t* s = p.sz + ((size_t)nt * G + gi) * 16;
-          const uint32_t s0 = __ldg(s + g), s1 = __ldg(s + g + 8);
-          sc[r][0] = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
-          sc[r][1] = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
-          zc[r][0] = (s0 >> 16) | (s0 & 0xffff0000u);
-          zc[r][1] = (s1 >> 16) | (s1 & 0xffff0000u);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) accg[r][mt][c] = 0.f;
-        }
-      }
-      // activation fragments for the 4 k16 steps of this k tile
-      uint32_t b[4][MT][2];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int m = mt * 8 + g;
-        const bool ok = m < p.M;
-        const uint32_t* xr = xw + (size_t)m * ldxw + (kt << 5) + t;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          b[j][mt][0] = ok ? __ldg(xr + j * 8) : 0u;
-          b[j][mt][1] = ok ? __ldg(xr + j * 8 + 4) : 0u;
-        }
-      }
+    uint32_t stg = 0, phase = 0;
+    bool dead = !mbar_wait(&bars[RING], 0u, p.status, 0x5ffu);
+    const uint32_t* szp = szs + g;
+    const uint32_t ones = 0x3f803f80u;   // bf16 {1, 1}
+    int kt = kt0;
+
+#pragma unroll 1
+    for (int grp = gbeg; grp < gend && !dead; ++grp, szp += 16) {
+      float sc[R][2], zf[R][2];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const uint32_t wj[4] = {wuse[r].x, wuse[r].y, wuse[r].z, wuse[r].w};
+        const uint32_t s0 = szp[r * p.szg * 16], s1 = szp[r * p.szg * 16 + 8];
+        sc[r][0] = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
+        sc[r][1] = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
+        zf[r][0] = bf16hi_to_f(s0);      // 128 + zero
+        zf[r][1] = bf16hi_to_f(s1);
+      }
+      float accg[R][MT][4], xsum[MT][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t u = wj[j];
-          uint32_t a0 = lop3_or_and(u, 0x000f000fu, 0x43004300u);
-          uint32_t a1 = lop3_or_and(u >> 4, 0x000f000fu, 0x43004300u);
-          uint32_t a2 = lop3_or_and(u >> 8, 0x000f000fu, 0x43004300u);
-          uint32_t a3 = lop3_or_and(u >> 12, 0x000f000fu, 0x43004300u);
-          a0 = bf16x2_sub(a0, zc[r][0]);
-          a1 = bf16x2_sub(a1, zc[r][1]);
-          a2 = bf16x2_sub(a2, zc[r][0]);
-          a3 = bf16x2_sub(a3, zc[r][1]);
+      for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(accg[r][mt], a0, a1, a2, a3, b[j][mt][0], b[j][mt][1]);
+        for (int c = 0; c < 4; ++c) {
+          xsum[mt][c] = 0.f;
+#pragma unroll
+          for (int r = 0; r < R; ++r) accg[r][mt][c] = 0.f;
         }
       }
-      if (((kt + 1) & (p.g64 - 1)) == 0) {
+#pragma unroll 1
+      for (int kk = 0; kk < p.g64; ++kk, ++kt) {
+        if (!mbar_try_wait(&bars[stg], phase)) {
+          if (!stage_wait_slow(&bars[stg], phase, p.status, 0x500u | stg)) { dead = true; break; }
+        }
+        uint4 wuse[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r) wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStage + r * 512 + lane * 16);
+        uint32_t b[MT][8];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          b[mt][0] = xa[mt].x; b[mt][1] = xa[mt].y; b[mt][2] = xa[mt].z; b[mt][3] = xa[mt].w;
+          b[mt][4] = xb[mt].x; b[mt][5] = xb[mt].y; b[mt][6] = xb[mt].z; b[mt][7] = xb[mt].w;
+        }
+        __syncwarp();   // every lane has its weight words in registers: the stage may be refilled
+        if (lane == 0 && kt + RING < kt1) {
+          mbar_expect_tx(&bars[stg], kStage);
+          bulk_load(ring + stg * kStage, wsrc + (size_t)(kt + RING) * 1024, kStage, &bars[stg]);
+        }
+        if (kt + 1 < kt1) {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            acc[r][mt][0] = fmaf(sc[r][0], accg[r][mt][0], acc[r][mt][0]);
-            acc[r][mt][1] = fmaf(sc[r][0], accg[r][mt][1], acc[r][mt][1]);
-            acc[r][mt][2] = fmaf(sc[r][1], accg[r][mt][2], acc[r][mt][2]);
-            acc[r][mt][3] = fmaf(sc[r][1], accg[r][mt][3], acc[r][mt][3]);
+            xp[mt] += 8;   // 64 bf16
+            if (xok[mt]) {
+              xa[mt] = __ldg(xp[mt]); xb[mt] = __ldg(xp[mt] + 1);
+              if (t == 0 && kt + kAhead < kt1) asm volatile("prefetch.global.L1 [%0];" ::"l"(xp[mt] + 8 * (kAhead - 1)));
+            }
           }
+        }
+        // Nibbles -> bf16 integers 128+q (one logic op per pair).  The zero point is NOT subtracted
+        // per element: an extra MMA with an all-ones A operand accumulates sum_k x, and
+        // (128 + zero) * sum_k x is removed when the group is flushed.
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(xsum[mt], ones, ones, ones, ones, b[mt][2 * j], b[mt][2 * j + 1]);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
+            const uint32_t a0 = lop3_or_and(u, 0x000f000fu, 0x43004300u);
+            const uint32_t a1 = lop3_or_and(u >> 4, 0x000f000fu, 0x43004300u);
+            const uint32_t a2 = lop3_or_and(u >> 8, 0x000f000fu, 0x43004300u);
+            const uint32_t a3 = lop3_or_and(u >> 12, 0x000f000fu, 0x43004300u);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(accg[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
+          }
+        }
+        stg = (stg + 1) & (RING - 1);
+        phase ^= (stg == 0);
       }
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          acc[r][mt][0] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][0], accg[r][mt][0]), acc[r][mt][0]);
+          acc[r][mt][1] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][1], accg[r][mt][1]), acc[r][mt][1]);
+          acc[r][mt][2] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][2], accg[r][mt][2]), acc[r][mt][2]);
+          acc[r][mt][3] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][3], accg[r][mt][3]), acc[r][mt][3]);
+        }
     }
   }
 
@@ -343,15 +385,19 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 }
 
 template <int MT, int R, int EPI>
-int launch(const W4Params& p, cudaStream_t st) {
+int launch(const W4Params& p_in, cudaStream_t st) {
   constexpr int NV = R * MT * 4 * 32;
-  const size_t smem = (size_t)kWarps * kRing * R * 512 + (size_t)kWarps * NV * sizeof(float) + (size_t)kWarps * kRing * 8;
+  constexpr int RING = RingDepth<MT>::v;
+  const W4Params& p = p_in;
+  const size_t smem = (size_t)kWarps * RING * R * 512 + (size_t)kWarps * NV * sizeof(float) +
+                      (size_t)kWarps * (RING + 1) * 8 + (size_t)kWarps * R * p.szg * 64;
   auto kfn = smallm_w4_kernel<MT, R, EPI>;
-  static bool attr_done = false;
-  if (!attr_done && smem > 48 * 1024) {
+  static size_t attr_max = 48 * 1024;
+  if (smem > 200 * 1024) return -2;
+  if (smem > attr_max) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_done = true;
+    attr_max = smem;
   }
   dim3 grid(p.N / (16 * R), p.ksplit);
   if (EPI == EPI_AR_ADD) {
@@ -383,6 +429,11 @@ int launch_epi(const W4Params& p, int epi, cudaStream_t st) {
 namespace {
 int dispatch(W4Params& p, int epi, int rows_per_cta, cudaStream_t st) {
   const int MT = (p.M + 7) / 8;
+  {
+    const int G = (p.K >> 6) / p.g64;
+    const int cta_groups = G / p.ksplit;
+    p.szg = (cta_groups + kWarps - 1) / kWarps;
+  }
   if (epi == EPI_SWIGLU) {
     if (MT <= 1) return launch<1, 2, EPI_SWIGLU>(p, st);
     if (MT <= 2) return launch<2, 2, EPI_SWIGLU>(p, st);
@@ -404,7 +455,7 @@ int dispatch(W4Params& p, int epi, int rows_per_cta, cudaStream_t st) {
 GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* out, void* scratch, void* counters,
                           int M, int N, int K, int ldx, int ldo, int group, int epi, int rows_per_cta, int ksplit,
                           void* stream) {
-  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 1)) return -2;
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 7) || ((uintptr_t)x & 15)) return -2;
   const int G = K / group;
   if (ksplit < 1 || (G % ksplit)) return -2;
   if (ksplit > 1 && (!scratch || !counters)) return -2;
@@ -426,7 +477,7 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
 GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x, void* h, int M, int N, int K, int ldx,
                                     int ldo, int group, const void* const* recv, const void* const* flags, void* epochs,
                                     int world, int rank, unsigned int spin, void* stream) {
-  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 1)) return -2;
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 7) || ((uintptr_t)x & 15)) return -2;
   if (world < 1 || world > 8 || rank < 0 || rank >= world || !recv || !flags || !epochs) return -2;
   W4Params p;
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = h;

@@ -49,6 +49,8 @@ class Engine:
         pin = self.device.type == "cuda"
         self.h_stage = torch.zeros(3, lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
         self.h_next = torch.zeros(lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
+        self.prefix_cache = None
+        self._reused_head_logits = None
         self.graphs: dict[tuple[int, int], "torch.cuda.CUDAGraph"] = {}
         self.counters = {"prefill_rows": 0, "decode_steps": 0, "decode_rows": 0, "graph_replays": 0, "kernel_launches": 0}
 
@@ -58,8 +60,31 @@ class Engine:
     def open(self, slot: Optional[int] = None) -> SeqSlot:
         return self.kv.open_slot(slot)
 
-    def release(self, seq: SeqSlot) -> None:
+    def release(self, seq: SeqSlot, cache: bool = False, head_logits=None) -> None:
+        """Free the slot; with ``cache`` its KV stays resident in the prefix cache (cache_sequence,
+        grimoire.cpp:12333) until evicted."""
+        if cache and self.prefix_cache is not None:
+            self.prefix_cache.store(seq, head_logits)
         self.kv.release(seq)
+
+    def enable_prefix_cache(self, max_entries: int = 16):
+        from .prefix_cache import PrefixCache
+
+        self.prefix_cache = PrefixCache(self.kv, max_entries)
+        return self.prefix_cache
+
+    def prefix_reuse(self, seq: SeqSlot, prompt) -> int:
+        """Attach the longest cached prefix of ``prompt`` to a fresh slot; returns tokens reused."""
+        if self.prefix_cache is None:
+            return 0
+        n, logits = self.prefix_cache.reuse(seq, list(prompt))
+        self._reused_head_logits = logits
+        return n
+
+    def rollback(self, seq: SeqSlot, length: int) -> None:
+        """Forget cached positions >= length (rows of a verify block past the accepted prefix)."""
+        if seq.length > length or len(seq.pages) * PAGE > length + PAGE:
+            self.kv.truncate(seq, length)
 
     # ------------------------------------------------------------------------------------------
     # prefill (one sequence, chunked)
@@ -77,7 +102,11 @@ class Engine:
         tokens = tokens.to(torch.int32)
         n = int(tokens.shape[0])
         if n == 0:
-            return None
+            # an identical prompt was fully served by the prefix cache (prompt-head snapshot)
+            lg, self._reused_head_logits = self._reused_head_logits, None
+            return lg
+        if self.prefix_cache is not None:
+            self.prefix_cache.make_room((seq.length + n + PAGE - 1) // PAGE - len(seq.pages))
         if seq.length + n > self.limits.max_ctx:
             raise OutOfPages(f"prompt of {seq.length + n} tokens exceeds the context cap {self.limits.max_ctx}")
         self.kv.ensure(seq, seq.length + n)

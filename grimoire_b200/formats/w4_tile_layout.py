@@ -5,7 +5,8 @@ include/b70/b70q4.hpp, src/b70q4.cpp).  This layout is built for the m16n8k16 bf
 
   w  : int32 ``[N/32][K/64][2][32][4]``  -- row tile ``nt = 2*ns + half`` (16 rows), k tile of 64,
        lane ``L`` (g = L//4, t = L%4) owns 4 words; word ``j`` is k16 step ``j``; nibble ``i`` of a
-       word is W[16*nt + g + 8*(i&1)][64*kt + 16*j + 2*t + 8*((i>>1)&1) + (i>>2)].
+       word is W[16*nt + g + 8*(i&1)][64*kt + 16*t + 4*j + 2*((i>>1)&1) + (i>>2)]: the 16 columns a
+       lane needs from a k tile are contiguous, so its activation fragment is two 16-byte reads.
   sz : int32 ``[N/16][K/group][16]``     -- low 16 bits fp16 scale bits, high 16 bits bf16(128+zero).
 
 ``interleave_gate_up`` orders a fused gate|up matrix so that row tile 2s holds gate rows
@@ -62,9 +63,9 @@ def tile_w4(qw: QuantWeight) -> W4Tiled:
         scales = torch.cat([scales, torch.zeros(Np - N, scales.shape[1], dtype=torch.half, device=dev)])
         zeros = torch.cat([zeros, torch.full((Np - N, zeros.shape[1]), 8, dtype=torch.int64, device=dev)])
     NS, KT = Np // 32, K // 64
-    # rows: 32*ns + 16*half + 8*r8 + g ; k: 64*kt + 16*j + 8*k8 + 2*t + h
-    q9 = q.reshape(NS, 2, 2, 8, KT, 4, 2, 4, 2)         # ns half r8 g kt j k8 t h
-    q9 = q9.permute(0, 4, 1, 3, 7, 5, 8, 6, 2)          # ns kt half g t j h k8 r8
+    # rows: 32*ns + 16*half + 8*r8 + g ; k: 64*kt + 16*t + 4*j + 2*k8 + h
+    q9 = q.reshape(NS, 2, 2, 8, KT, 4, 4, 2, 2)         # ns half r8 g kt t j k8 h
+    q9 = q9.permute(0, 4, 1, 3, 5, 6, 8, 7, 2)          # ns kt half g t j h k8 r8
     words = (q9 * _nibble_weights(q.device)).sum(dim=(-1, -2, -3))
     words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
     w = words.reshape(NS, KT, 2, 32, 4).contiguous()
@@ -83,7 +84,7 @@ def untile_w4(t: W4Tiled) -> QuantWeight:
     words = t.w.to(torch.int64) & 0xFFFFFFFF
     shifts = (4 * torch.arange(8, dtype=torch.int64, device=t.w.device)).reshape(2, 2, 2)   # [h][k8][r8]
     q9 = (words.reshape(NS, KT, 2, 8, 4, 4, 1, 1, 1) >> shifts) & 0xF     # ns kt half g t j h k8 r8
-    q = q9.permute(0, 2, 8, 3, 1, 5, 7, 4, 6).reshape(t.N, t.K)          # ns half r8 g kt j k8 t h
+    q = q9.permute(0, 2, 8, 3, 1, 4, 5, 7, 6).reshape(t.N, t.K)          # ns half r8 g kt t j k8 h
     szw = t.sz.to(torch.int64) & 0xFFFFFFFF
     G = t.K // t.group
     szr = szw.permute(0, 2, 1).reshape(t.N, G)

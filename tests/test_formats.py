@@ -101,7 +101,7 @@ def test_w4_tile_roundtrip_and_element_map(N, K, group):
         ns, kt, half, lane, j, i = [int(torch.randint(0, hi, (1,), generator=gen)) for hi in
                                     (t.N // 32, K // 64, 2, 32, 4, 8)]
         row = 16 * (2 * ns + half) + lane // 4 + 8 * (i & 1)
-        k = 64 * kt + 16 * j + 2 * (lane % 4) + 8 * ((i >> 1) & 1) + (i >> 2)
+        k = 64 * kt + 16 * (lane % 4) + 4 * j + 2 * ((i >> 1) & 1) + (i >> 2)
         word = int(t.w[ns, kt, half, lane, j]) & 0xFFFFFFFF
         want = int(q[row, k]) if row < N else 8
         assert (word >> (4 * i)) & 0xF == want
