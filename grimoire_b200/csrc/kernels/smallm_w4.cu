@@ -491,3 +491,75 @@ GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x
   p.ar_spin = spin ? spin : 2000000u;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// grm_smallm_w4_noalloc: the split-K small-M product for callers that must not allocate.
+// Declared and documented in smallm_w4_noalloc.h.
+// ---------------------------------------------------------------------------------------------
+#include "smallm_w4_noalloc.h"
+
+namespace {
+
+// Scratch that the ordinary entry point receives from its caller lives here instead, inside the
+// library image: every GPU that loads the library carries these 4 MiB + 16 KiB until the process exits.
+static __device__ __align__(256) float g_noalloc_partials[GRM_NOALLOC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) unsigned int g_noalloc_counters[GRM_NOALLOC_MAX_TILES];
+
+struct NoAllocDev {
+  float* partials;
+  unsigned int* counters;
+  bool ready;
+};
+NoAllocDev g_noalloc_dev[64];
+
+// In host code the two array names above are only stand-ins; a kernel needs the device addresses,
+// which cudaGetSymbolAddress hands out for the device that is current at the time of the call.
+int noalloc_setup(int dev) {
+  NoAllocDev& d = g_noalloc_dev[dev];
+  if (d.ready) return 0;
+  void* a = nullptr;
+  void* b = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&a, g_noalloc_partials);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaGetSymbolAddress(&b, g_noalloc_counters);
+  if (e != cudaSuccess) return (int)e;
+  d.partials = (float*)a;
+  d.counters = (unsigned int*)b;
+  d.ready = true;
+  return 0;
+}
+
+}  // namespace
+
+GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, void* out, int M, int N, int K, int ldx,
+                                  int ldo, int group, int epi, int rows_per_cta, int ksplit, void* stream) {
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldx & 7) || ((uintptr_t)x & 15)) return -2;
+  if (epi < EPI_BF16 || epi > EPI_SWIGLU) return -1;
+  const int G = K / group;
+  if (ksplit < 1 || (G % ksplit)) return -2;
+  int mt = 1;
+  while (mt * 8 < M) mt *= 2;
+  // which row-tile width the dispatcher will pick (kept in step with dispatch() above)
+  const int R = (epi == EPI_SWIGLU) ? 2 : ((rows_per_cta == 32 && mt <= 2) ? 2 : 1);
+  const long tiles = N / (16 * R);
+  const long need = (long)ksplit * tiles * R * mt * 128;
+  if (tiles > GRM_NOALLOC_MAX_TILES || need > GRM_NOALLOC_MAX_PARTIAL_FLOATS) return GRM_NOALLOC_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -2;
+  int rc = noalloc_setup(dev);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // The counters are shared by every call and must start at zero; a previous call that was cut short
+  // could have left them otherwise, so they are cleared on the caller's stream each time.
+  e = cudaMemsetAsync(g_noalloc_dev[dev].counters, 0, sizeof(unsigned int) * (size_t)tiles, st);
+  if (e != cudaSuccess) return (int)e;
+  W4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
+  p.scratch = g_noalloc_dev[dev].partials; p.counters = g_noalloc_dev[dev].counters;
+  p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  return dispatch(p, epi, rows_per_cta, st);
+}
