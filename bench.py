@@ -112,6 +112,10 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    wd = int(os.environ.get("GRIMOIRE_BENCH_WATCHDOG", "0"))
+    if wd > 0:   # dump every thread's stack and exit if the run is still going after `wd` seconds
+        import faulthandler
+        faulthandler.dump_traceback_later(wd, exit=True)
     if args.warmup < 3:
         args.warmup = 3
 

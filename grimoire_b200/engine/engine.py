@@ -167,6 +167,9 @@ class Engine:
             max_len = max(max_len, p + 1)
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
+        tp = getattr(self.model, "tp", None)
+        if tp is not None and not tp.fused:
+            use_graph = False        # NCCL collectives stay out of captured graphs (baseline path)
         if use_graph and self.device.type == "cuda":
             key = (M, splits)
             g = self.graphs.get(key)

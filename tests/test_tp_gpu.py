@@ -44,7 +44,10 @@ def _worker(rank, world, port, q, fused):
         out = eng.generate(prompt, 16, use_graph=True)
         torch.cuda.synchronize()
         q.put((rank, out, dict(tp.stats), status_read()))
+        eng.graphs.clear()
+        del eng, model
         dist.barrier()
+        torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()
 
@@ -70,10 +73,17 @@ def test_tp2_gpu_tokens_equal_single_gpu(fused):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q, fused)) for r in range(2)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        res = [q.get(timeout=240) for _ in procs]
+        for p in procs:
+            p.join(timeout=60)
+        codes = [p.exitcode for p in procs]
+    finally:
+        for p in procs:            # never leave a rank behind on the GPUs
+            if p.is_alive():
+                p.kill()
+                p.join(timeout=10)
+    assert codes == [0, 0], codes
     outs = {r: o for r, o, _, _ in res}
     assert outs[0] == outs[1]                       # ranks never drift
     agree = sum(int(a == b) for a, b in zip(outs[0], single))
