@@ -173,3 +173,29 @@ def quantize(w: torch.Tensor, fmt: Fmt, *, group: int = C.INT4_GROUP, symmetric:
         payload = C.pack_nibbles(C.f32_to_e2m1(wb / dec[:, :, None]).reshape(N, K))
         return QuantWeight(fmt, N, K, payload, scales=bs.contiguous(), group=C.NVFP4_BLOCK, global_scale=gscale)
     raise ValueError(f"quantize: unsupported target format {fmt!r}")
+
+
+def slice_rows(qw: QuantWeight, a: int, b: int) -> QuantWeight:
+    """Rows [a, b) of a quantized matrix (column-parallel TP shard: tp_take_rows, grimoire.cpp:5256)."""
+    sc = qw.scales[a:b] if qw.scales is not None else None
+    zr = qw.zeros[a:b] if qw.zeros is not None else None
+    return QuantWeight(qw.fmt, b - a, qw.K, qw.payload[a:b].contiguous(), scales=None if sc is None else sc.contiguous(),
+                       zeros=None if zr is None else zr.contiguous(), group=qw.group, global_scale=qw.global_scale)
+
+
+def slice_cols(qw: QuantWeight, a: int, b: int) -> QuantWeight:
+    """K columns [a, b) of a quantized matrix (row-parallel TP shard: tp_take_cols,
+    grimoire.cpp:5300-5346).  The cut must fall on scale-group boundaries."""
+    f = qw.fmt
+    if f == Fmt.BF16:
+        return QuantWeight(f, qw.N, b - a, qw.payload.reshape(qw.N, qw.K, 2)[:, a:b].reshape(qw.N, -1).contiguous())
+    per_row_scale = f in (Fmt.INT8, Fmt.FP8_E4M3, Fmt.FP8_E5M2)
+    bits4 = f in (Fmt.INT4, Fmt.MXFP4, Fmt.NVFP4)
+    g = 1 if per_row_scale else qw.group
+    if a % g or b % g or (bits4 and (a % 2 or b % 2)):
+        raise ValueError(f"column slice [{a},{b}) does not fall on group boundaries of {g}")
+    pay = qw.payload[:, a // 2: b // 2] if bits4 else qw.payload[:, a:b]
+    sc = qw.scales if per_row_scale else qw.scales[:, a // g: b // g]
+    zr = None if qw.zeros is None else qw.zeros[:, a // g: b // g].contiguous()
+    return QuantWeight(f, qw.N, b - a, pay.contiguous(), scales=sc.contiguous(), zeros=zr, group=qw.group,
+                       global_scale=qw.global_scale)

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from ..formats.codecs import Fmt
-from ..formats.quantize import QuantWeight, quantize
+from ..formats.quantize import QuantWeight, quantize, slice_cols, slice_rows
 from ..formats.w4_tile_layout import concat_rows, interleave_gate_up_q
 from ..ops import core as K
 from ..ops import ref
@@ -107,14 +107,25 @@ class DenseModel:
     # ------------------------------------------------------------------------------------------
     # construction
     # ------------------------------------------------------------------------------------------
-    def _quant(self, w: torch.Tensor) -> QuantWeight:
+    def _quant(self, w) -> QuantWeight:
+        """fp32 tensor or stored QuantWeight -> runtime int4 (stored int4 is used as is)."""
         cfg = self.cfg
+        if isinstance(w, QuantWeight):
+            return w if w.fmt == Fmt.INT4 else quantize(w.dequant(), Fmt.INT4, group=cfg.quant_group)
         return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
 
-    def _shard_rows(self, w: torch.Tensor, heads: int, per: int) -> torch.Tensor:
+    @staticmethod
+    def _rows(w, a: int, b: int):
+        return slice_rows(w, a, b) if isinstance(w, QuantWeight) else w[a:b]
+
+    @staticmethod
+    def _cols(w, a: int, b: int):
+        return slice_cols(w, a, b) if isinstance(w, QuantWeight) else w[:, a:b]
+
+    def _shard_rows(self, w, heads: int, per: int):
         """rows of a column-parallel weight owned by this rank (whole heads)."""
         n = heads // self.tp_world * per
-        return w[self.tp_rank * n: (self.tp_rank + 1) * n]
+        return self._rows(w, self.tp_rank * n, (self.tp_rank + 1) * n)
 
     def add_layer_from_dense(self, wq, wk, wv, wo, wg, wu, wd, in_norm, post_norm, q_norm=None, k_norm=None):
         """Quantize + shard + tile one layer from full-precision logical weights (``[out][in]``)."""
@@ -125,10 +136,10 @@ class DenseModel:
         wk_s = self._shard_rows(wk, cfg.num_key_value_heads, D)
         wv_s = self._shard_rows(wv, cfg.num_key_value_heads, D)
         kq = cfg.num_attention_heads * D // W
-        wo_s = wo[:, r * kq: (r + 1) * kq]
+        wo_s = self._cols(wo, r * kq, (r + 1) * kq)
         I = cfg.intermediate_size // W
-        wg_s, wu_s = wg[r * I: (r + 1) * I], wu[r * I: (r + 1) * I]
-        wd_s = wd[:, r * I: (r + 1) * I]
+        wg_s, wu_s = self._rows(wg, r * I, (r + 1) * I), self._rows(wu, r * I, (r + 1) * I)
+        wd_s = self._cols(wd, r * I, (r + 1) * I)
         qkv = concat_rows([self._quant(wq_s), self._quant(wk_s), self._quant(wv_s)])
         gu = interleave_gate_up_q(self._quant(wg_s), self._quant(wu_s))
         f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
@@ -195,6 +206,32 @@ class DenseModel:
                                    g("post_attention_layernorm.weight"), g("self_attn.q_norm.weight"),
                                    g("self_attn.k_norm.weight"))
         m.set_embeddings(sd["model.embed_tokens.weight"], sd["model.norm.weight"], sd.get("lm_head.weight"))
+        return m
+
+    @staticmethod
+    def from_checkpoint(path, device, tp_rank: int = 0, tp_world: int = 1, workspace: Optional[Workspace] = None,
+                        lm_head_bf16: bool = False) -> "DenseModel":
+        """Load a HF directory (safetensors shards; bf16 / GPTQ / compressed-tensors / fp8 / NVFP4
+        projections) and serve it with int4-g128 projections.  Stored int4 is repacked, anything
+        else is dequantized and quantized on the host (Grimoire::build, grimoire.cpp:7133-10637)."""
+        from ..formats.checkpoint import Checkpoint
+
+        ck = Checkpoint(path)
+        cfg = ck.cfg
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
+        for i in range(cfg.num_hidden_layers):
+            p = f"{ck.prefix}layers.{i}."
+            lin = lambda k: ck.linear(p + k)
+            m.add_layer_from_dense(lin("self_attn.q_proj"), lin("self_attn.k_proj"), lin("self_attn.v_proj"),
+                                   lin("self_attn.o_proj"), lin("mlp.gate_proj"), lin("mlp.up_proj"), lin("mlp.down_proj"),
+                                   ck.plain(p + "input_layernorm.weight"), ck.plain(p + "post_attention_layernorm.weight"),
+                                   ck.plain(p + "self_attn.q_norm.weight"), ck.plain(p + "self_attn.k_norm.weight"))
+        head = None if cfg.tie_word_embeddings else ck.linear("lm_head")
+        emb = ck.embedding()
+        m.set_embeddings(emb, ck.plain(ck.prefix + "norm.weight"), head)
+        if lm_head_bf16 and head is not None:
+            hw = head.dequant() if isinstance(head, QuantWeight) else head
+            m.lm_head = BF16Linear(hw, device, "lm_head(bf16)")
         return m
 
     def weight_bytes(self) -> int:
