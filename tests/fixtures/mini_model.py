@@ -1,0 +1,74 @@
+"""Synthetic HF checkpoints for tests: a real ``config.json`` + ``model.safetensors`` (+ optional
+GPTQ triples, + a trained byte-level BPE ``tokenizer.json``) with random, never-zero weights -- the
+role of the reference's tools/mini_model.hpp:18-110."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+from grimoire_b200.formats import gptq
+from grimoire_b200.formats.codecs import Fmt
+from grimoire_b200.formats.quantize import quantize
+from grimoire_b200.formats.safetensors_io import save_file
+from grimoire_b200.models.config import ModelConfig
+from grimoire_b200.models.synthetic import random_state_dict
+
+_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "bf16", tokenizer: bool = False, shards: int = 1):
+    path.mkdir(parents=True, exist_ok=True)
+    sd = random_state_dict(cfg, seed)
+    out = {}
+    for name, w in sd.items():
+        is_proj = any(name.endswith(p + ".weight") for p in _PROJ)
+        if quant == "gptq" and is_proj:
+            qw = quantize(w, Fmt.INT4, group=cfg.quant_group)
+            a, b, c = gptq.gptq_pack(qw)
+            base = name[: -len(".weight")]
+            out[base + ".qweight"], out[base + ".qzeros"], out[base + ".scales"] = a, b, c
+            out[base + ".g_idx"] = (torch.arange(qw.K) // cfg.quant_group).to(torch.int32)
+        else:
+            out[name] = w.bfloat16()
+    hf = {"model_type": "qwen3", "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
+          "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads,
+          "head_dim": cfg.head_dim, "vocab_size": cfg.vocab_size, "intermediate_size": cfg.intermediate_size,
+          "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta, "tie_word_embeddings": cfg.tie_word_embeddings,
+          "qk_norm": cfg.qk_norm}
+    if quant == "gptq":
+        hf["quantization_config"] = {"quant_method": "gptq", "bits": 4, "group_size": cfg.quant_group, "sym": False}
+    (path / "config.json").write_text(json.dumps(hf))
+    if shards == 1:
+        save_file(out, path / "model.safetensors", {"format": "pt"})
+    else:
+        names = list(out)
+        wm = {}
+        for s in range(shards):
+            part = {n: out[n] for n in names[s::shards]}
+            fn = f"model-{s + 1:05d}-of-{shards:05d}.safetensors"
+            save_file(part, path / fn)
+            wm.update({n: fn for n in part})
+        (path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": wm}))
+    if tokenizer:
+        write_tokenizer(path, cfg.vocab_size)
+    return sd
+
+
+def write_tokenizer(path: Path, vocab_size: int):
+    from tokenizers import Regex, Tokenizer, decoders, models, normalizers, pre_tokenizers, trainers
+
+    pat = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+")
+    tok = Tokenizer(models.BPE())
+    tok.normalizer = normalizers.NFC()
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated", invert=False),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    tr = trainers.BpeTrainer(vocab_size=min(vocab_size, 600), show_progress=False, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                             special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>", "<think>", "</think>", "<tool_call>", "</tool_call>"])
+    corpus = ["the quick brown fox jumps over the lazy dog", "hello world, how are you today?", "def f(x):\n    return x + 1\n",
+              "user assistant system tool weather in Paris is sunny"] * 8
+    tok.train_from_iterator(corpus, tr)
+    tok.save(str(path / "tokenizer.json"))
+    (path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
