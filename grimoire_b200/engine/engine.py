@@ -36,7 +36,7 @@ class Engine:
         self.device = model.device
         self.limits = limits or EngineLimits()
         lim = self.limits
-        n_attn = self.cfg.num_attention_layers()
+        n_attn = len(model.layers)          # attention layers of this pipeline stage
         pages = lim.kv_pages or (lim.max_slots * ((lim.max_ctx + PAGE - 1) // PAGE))
         self.kv = KvPool(n_attn, model.geom.Hkv, model.geom.D, pages, lim.max_slots, lim.max_ctx, self.device)
         chunk = min(lim.prefill_chunk, lim.max_ctx)
@@ -126,6 +126,11 @@ class Engine:
             self.counters["prefill_rows"] += m
             logits = out
         seq.tokens.extend(int(t) for t in tokens.tolist())
+        pp = getattr(self.model, "pp", None)
+        if pp is not None:
+            # the last stage owns the logits; every stage needs the same first token
+            row = logits[0] if logits is not None else torch.empty(self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+            logits = pp.broadcast_from_last(row)[None]
         return logits[0] if want_logits else None
 
     # ------------------------------------------------------------------------------------------
@@ -148,7 +153,11 @@ class Engine:
     def _run_rows(self, M: int, splits: int) -> torch.Tensor:
         rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits)
         logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
-        K.argmax_rows(logits, self.decode_buf.next_ids[:M])
+        pp = getattr(self.model, "pp", None)
+        if logits is not None:
+            K.argmax_rows(logits, self.decode_buf.next_ids[:M])
+        if pp is not None:
+            pp.broadcast_from_last(self.decode_buf.next_ids[:M])     # token chosen by the last stage travels back
         return logits
 
     def decode_rows(self, tokens: Sequence[int], seqs: Sequence[SeqSlot], positions: Sequence[int],
@@ -168,8 +177,8 @@ class Engine:
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
         tp = getattr(self.model, "tp", None)
-        if tp is not None and not tp.fused:
-            use_graph = False        # NCCL collectives stay out of captured graphs (baseline path)
+        if (tp is not None and not tp.fused) or getattr(self.model, "pp", None) is not None:
+            use_graph = False        # NCCL collectives / stage hops stay out of captured graphs
         if use_graph and self.device.type == "cuda":
             key = (M, splits)
             g = self.graphs.get(key)

@@ -84,10 +84,16 @@ class Buffers:
 
 class DenseModel:
     def __init__(self, cfg: ModelConfig, device, tp_rank: int = 0, tp_world: int = 1,
-                 workspace: Optional[Workspace] = None):
+                 workspace: Optional[Workspace] = None, pp_rank: int = 0, pp_world: int = 1):
         self.cfg = cfg
         self.device = torch.device(device)
         self.tp_rank, self.tp_world = tp_rank, tp_world
+        # pipeline stage r owns layers [layer_begin, layer_end) (grimoire.cpp:2485-2499)
+        self.pp_rank, self.pp_world = pp_rank, pp_world
+        per, extra = divmod(cfg.num_hidden_layers, pp_world)
+        self.layer_begin = pp_rank * per + min(pp_rank, extra)
+        self.layer_end = self.layer_begin + per + (1 if pp_rank < extra else 0)
+        self.pp = None          # parallel.pp.PipelineParallel when pp_world > 1
         self.ws = workspace or Workspace(device)
         if cfg.num_attention_heads % tp_world or cfg.num_key_value_heads % tp_world or cfg.intermediate_size % tp_world:
             raise ValueError("tensor parallel degree must divide heads, kv heads and the FFN width")
@@ -164,11 +170,11 @@ class DenseModel:
 
     @staticmethod
     def random(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, std: float = 0.02,
-               gen_device=None, workspace: Optional[Workspace] = None) -> "DenseModel":
+               gen_device=None, workspace: Optional[Workspace] = None, pp_rank: int = 0, pp_world: int = 1) -> "DenseModel":
         """Random-init weights N(0, std) of the named architecture, quantized to int4 (the synthetic
         checkpoints of the benchmarks).  Every rank draws the same logical matrices and keeps its
         shard, so TP results can be compared with a single-GPU run token for token."""
-        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace, pp_rank, pp_world)
         gdev = torch.device(gen_device or device)
         g = torch.Generator(device=gdev)
         H, D = cfg.hidden_size, cfg.head_dim
@@ -179,7 +185,7 @@ class DenseModel:
             return torch.randn(n, k, generator=g, device=gdev, dtype=torch.float32) * std
 
         ones = torch.ones(H)
-        for i in range(cfg.num_hidden_layers):
+        for i in range(m.layer_begin, m.layer_end):
             t = i * 16
             m.add_layer_from_dense(rnd(qrows, H, t + 1), rnd(cfg.kv_size, H, t + 2), rnd(cfg.kv_size, H, t + 3),
                                    rnd(H, cfg.num_attention_heads * D, t + 4), rnd(cfg.intermediate_size, H, t + 5),
@@ -194,10 +200,10 @@ class DenseModel:
 
     @staticmethod
     def from_state_dict(cfg: ModelConfig, sd: dict, device, tp_rank: int = 0, tp_world: int = 1,
-                        workspace: Optional[Workspace] = None) -> "DenseModel":
+                        workspace: Optional[Workspace] = None, pp_rank: int = 0, pp_world: int = 1) -> "DenseModel":
         """Build from HF-named full-precision tensors (``[out][in]``), quantizing to int4."""
-        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
-        for i in range(cfg.num_hidden_layers):
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace, pp_rank, pp_world)
+        for i in range(m.layer_begin, m.layer_end):
             p = f"model.layers.{i}."
             g = lambda k: sd.get(p + k)
             m.add_layer_from_dense(g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight"),
@@ -210,7 +216,7 @@ class DenseModel:
 
     @staticmethod
     def from_checkpoint(path, device, tp_rank: int = 0, tp_world: int = 1, workspace: Optional[Workspace] = None,
-                        lm_head_bf16: bool = False) -> "DenseModel":
+                        lm_head_bf16: bool = False, pp_rank: int = 0, pp_world: int = 1) -> "DenseModel":
         """Load a HF directory (safetensors shards; bf16 / GPTQ / compressed-tensors / fp8 / NVFP4
         projections) and serve it with int4-g128 projections.  Stored int4 is repacked, anything
         else is dequantized and quantized on the host (Grimoire::build, grimoire.cpp:7133-10637)."""
@@ -218,8 +224,8 @@ class DenseModel:
 
         ck = Checkpoint(path)
         cfg = ck.cfg
-        m = DenseModel(cfg, device, tp_rank, tp_world, workspace)
-        for i in range(cfg.num_hidden_layers):
+        m = DenseModel(cfg, device, tp_rank, tp_world, workspace, pp_rank, pp_world)
+        for i in range(m.layer_begin, m.layer_end):
             p = f"{ck.prefix}layers.{i}."
             lin = lambda k: ck.linear(p + k)
             m.add_layer_from_dense(lin("self_attn.q_proj"), lin("self_attn.k_proj"), lin("self_attn.v_proj"),
@@ -260,7 +266,11 @@ class DenseModel:
         h, x = buf.h[:M], buf.x[:M]
         qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]
         gate = buf.gate[:M] if buf.gate is not None else None
-        K.embed(rb.tokens, self.embed, h)
+        first_stage, last_stage = self.pp_rank == 0, self.pp_rank == self.pp_world - 1
+        if first_stage:
+            K.embed(rb.tokens, self.embed, h)
+        else:
+            self.pp.recv_hidden(h)          # [rows][H] from the previous stage
         prefill = rb.mode == "prefill"
         T = rb.q_pos0 + M
         for li, L in enumerate(self.layers):
@@ -280,6 +290,9 @@ class DenseModel:
             K.add_rmsnorm(h, L.post_norm, x, eps, off)
             L.gate_up(x, act, "swiglu")
             self._row_parallel(L.down, act, h)
+        if not last_stage:
+            self.pp.send_hidden(h)
+            return None
         # head
         if rb.logits_rows is None:
             hsel, n = h, M
