@@ -1,0 +1,90 @@
+"""GGUF: block decoders against llama.cpp-derived golden vectors (read in place from the reference
+checkout when it is present: b"GGLD", type, n_expected, raw_size, raw blocks, expected fp32), the
+container parser on a file written by the test, and the name adapter."""
+import struct
+from pathlib import Path
+
+import pytest
+import torch
+
+from grimoire_b200.formats import gguf
+
+GOLD = Path("/root/reference/tests/gguf/data")
+DECODED = ["F32", "F16", "BF16", "F64", "I8", "I16", "I32", "I64", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q8_1", "Q2_K", "Q3_K",
+           "Q4_K", "Q5_K", "Q6_K", "Q8_K", "IQ4_NL", "IQ4_XS", "TQ2_0", "MXFP4"]
+
+
+@pytest.mark.skipif(not GOLD.exists(), reason="golden vectors not available on this machine")
+@pytest.mark.parametrize("name", DECODED)
+def test_block_decoders_match_goldens(name):
+    blob = (GOLD / f"{name}.bin").read_bytes()
+    assert blob[:4] == b"GGLD"
+    qtype, n_exp, raw_size = struct.unpack_from("<III", blob, 4)
+    raw = blob[16: 16 + raw_size]
+    want = torch.frombuffer(bytearray(blob[16 + raw_size: 16 + raw_size + 4 * n_exp]), dtype=torch.float32)
+    got = gguf.dequantize(qtype, raw, n_exp)
+    assert torch.equal(got, want), (name, float((got - want).abs().max()))
+
+
+def test_undecoded_types_are_reported():
+    with pytest.raises(NotImplementedError):
+        gguf.dequantize(16, b"\0" * 66, 256)          # IQ2_XXS needs a codebook this build does not carry
+    with pytest.raises(ValueError):
+        gguf.dequantize(2, b"\0" * 17, 32)            # wrong byte count
+
+
+def _write_gguf(path, kv, tensors, version=3, alignment=32):
+    def s(x):
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+    out = b"GGUF" + struct.pack("<IQQ", version, len(tensors), len(kv))
+    for k, (t, v) in kv.items():
+        out += s(k) + struct.pack("<I", t)
+        if t == 4:
+            out += struct.pack("<I", v)
+        elif t == 6:
+            out += struct.pack("<f", v)
+        elif t == 8:
+            out += s(v)
+        elif t == 9:
+            et, items = v
+            out += struct.pack("<IQ", et, len(items))
+            for it in items:
+                out += s(it) if et == 8 else struct.pack("<i", it)
+    data, off = b"", 0
+    for name, (typ, dims, raw) in tensors.items():
+        out += s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, off)
+        pad = (alignment - len(raw) % alignment) % alignment
+        data += raw + b"\0" * pad
+        off += len(raw) + pad
+    out += b"\0" * ((alignment - len(out) % alignment) % alignment)
+    Path(path).write_bytes(out + data)
+
+
+def test_container_parser_and_adapter(tmp_path):
+    torch.manual_seed(0)
+    w = torch.randn(8, 64)
+    q8 = b""
+    for row in w:
+        for blk in row.reshape(-1, 32):
+            d = float(blk.abs().max()) / 127
+            q8 += struct.pack("<e", d) + bytes((torch.round(blk / d).to(torch.int8).view(torch.uint8)).tolist())
+    kv = {"general.architecture": (8, "qwen3"), "qwen3.block_count": (4, 1), "qwen3.embedding_length": (4, 64),
+          "qwen3.attention.head_count": (4, 2), "qwen3.attention.head_count_kv": (4, 1), "qwen3.feed_forward_length": (4, 128),
+          "qwen3.rope.freq_base": (6, 1e6), "tokenizer.ggml.model": (8, "gpt2"), "tokenizer.ggml.tokens": (9, (8, ["a", "b", "ab"])),
+          "tokenizer.ggml.merges": (9, (8, ["a b"])), "tokenizer.ggml.token_type": (9, (5, [1, 1, 1]))}
+    tensors = {"blk.0.attn_q.weight": (8, (64, 8), q8), "output_norm.weight": (0, (64,), torch.ones(64).numpy().tobytes())}
+    _write_gguf(tmp_path / "m.gguf", kv, tensors)
+    g = gguf.GGUFFile(tmp_path / "m.gguf")
+    assert g.version == 3 and g.arch == "qwen3" and g.metadata["qwen3.block_count"] == 1
+    t = g.tensor("blk.0.attn_q.weight")
+    assert t.shape == (8, 64) and float((t - w).abs().max()) < 0.02
+    assert gguf.hf_name("blk.0.attn_q.weight") == "model.layers.0.self_attn.q_proj.weight"
+    assert gguf.hf_name("blk.12.ffn_down.weight") == "model.layers.12.mlp.down_proj.weight"
+    cfg = gguf.config_from_gguf(g)
+    assert cfg.num_hidden_layers == 1 and cfg.hidden_size == 64 and cfg.num_key_value_heads == 1 and cfg.tie_word_embeddings
+    tj = gguf.tokenizer_json_from_gguf(g)
+    assert tj["model"]["vocab"] == {"a": 0, "b": 1, "ab": 2} and tj["model"]["merges"] == ["a b"]
+    with pytest.raises(ValueError):
+        (tmp_path / "bad.gguf").write_bytes(b"GGUX" + b"\0" * 64)
+        gguf.GGUFFile(tmp_path / "bad.gguf")
