@@ -42,7 +42,26 @@ struct GemmParams {
   // peer_out[r] at slot `my_rank`: peer_out[r] + ((my_rank * rows_per_rank + local_row) * ldo + n)
   void* peer_out[8];
   int world, my_rank, rows_per_rank;
+  // tile arrival counters of the reduce-scatter: after a tile is stored into rank r's buffer, the
+  // CTA adds 1 (release, system scope) to peer_cnt[r][(local m tile) * world + my_rank]; the
+  // consumer waits for epoch * (N / BN) arrivals per (m tile, source)
+  unsigned int* peer_cnt[8];
+  // all-gather wait (consumer side of a fused all-gather -> GEMM): before the A rows of m tile t are
+  // loaded, the producer warp waits until ag_cnt[t] >= ag_expect (rows pushed by their owners into
+  // this rank's own copy of A); null disables the wait
+  const unsigned int* ag_cnt;
+  unsigned int ag_expect;
+  unsigned int spin;
 };
+
+__device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 template <int BN>
 struct SmemLayout {
@@ -98,6 +117,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int m_blk = t % num_m, n_blk = t / num_m;
+        if (p.ag_cnt) {
+          // rows of this m tile were written by their owner ranks over NVLink (generic proxy); once
+          // the count is seen with acquire semantics, order the async-proxy (TMA) reads after it
+          bool seen = false;
+          for (unsigned int i = 0; i < p.spin; ++i) {
+            if ((int)(ld_acquire_sys_u32(p.ag_cnt + m_blk) - p.ag_expect) >= 0) { seen = true; break; }
+            __nanosleep(64);
+          }
+          if (!seen) { grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x20000u | (unsigned)m_blk); ok = false; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (*s_abort || !mbar_wait(&empty[stage], phase ^ 1, p.status, 0x100u | stage)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -230,6 +260,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (EPI == G_RS_PUSH) {
+        // the 32 rows this warp stored belong to one owner (rows_per_rank is a multiple of 128):
+        // publish them, then count one arrival per warp quarter (4 per tile)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && m_blk * BM + q * 32 < p.M) {
+          const int r0 = m_blk * BM + q * 32;
+          const int owner = r0 / p.rows_per_rank, ltile = (r0 % p.rows_per_rank) / BM;
+          red_release_sys_add(p.peer_cnt[owner] + (size_t)ltile * p.world + p.my_rank, 1u);
+        }
+      }
     }
     if (!ok) *s_abort = 1;
   }
@@ -322,11 +363,12 @@ int sm_count() {
 // 3 SwiGLU (B rows interleaved 16 gate / 16 up; out bf16 [M][N/2]), 4 reduce-scatter push (peer_out
 // = array of `world` device pointers, rows_per_rank = M / world).  K % 8 == 0; K tails and M/N tails
 // are zero-filled by TMA.  bn: 0 = auto, else 128 or 256.  max_ctas: 0 = one per SM.
-GRM_API int grm_gemm_bf16(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K, int epi,
-                          int bn, int max_ctas, const void* const* peer_out, int world, int my_rank, void* stream) {
+static int gemm_bf16_impl(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K, int epi,
+                          int bn, int max_ctas, const void* const* peer_out, const void* const* peer_cnt, int world, int my_rank,
+                          const void* ag_cnt, unsigned int ag_expect, void* stream) {
   if (M < 1 || N < 1 || K < 8 || (K & 7)) return -2;
   if (epi == G_SWIGLU && (N & 31)) return -2;
-  if (epi == G_RS_PUSH && (!peer_out || world < 1 || world > 8 || (M % world))) return -2;
+  if (epi == G_RS_PUSH && (!peer_out || !peer_cnt || world < 1 || world > 8 || (M % (world * BM)))) return -2;
   if (bn == 0) bn = (N >= 2048 && (N % 256 == 0 || N > 8192)) ? 256 : 128;
   if (bn != 128 && bn != 256) return -2;
   CUtensorMap ta, tb;
@@ -337,9 +379,33 @@ GRM_API int grm_gemm_bf16(const void* A, int lda, const void* B, int ldb, void* 
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.out = out; p.ldo = ldo; p.status = grm_status_ptr();
   p.world = world; p.my_rank = my_rank; p.rows_per_rank = world > 0 ? M / world : M;
-  for (int i = 0; i < 8; ++i) p.peer_out[i] = (peer_out && i < world) ? const_cast<void*>(peer_out[i]) : nullptr;
+  for (int i = 0; i < 8; ++i) {
+    p.peer_out[i] = (peer_out && i < world) ? const_cast<void*>(peer_out[i]) : nullptr;
+    p.peer_cnt[i] = (peer_cnt && i < world) ? (unsigned int*)const_cast<void*>(peer_cnt[i]) : nullptr;
+  }
+  p.ag_cnt = (const unsigned int*)ag_cnt; p.ag_expect = ag_expect; p.spin = 4000000u;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;
   return bn == 256 ? launch_epi<256>(ta, tb, p, epi, sms, st) : launch_epi<128>(ta, tb, p, epi, sms, st);
+}
+
+GRM_API int grm_gemm_bf16(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K, int epi,
+                          int bn, int max_ctas, const void* const* peer_out, int world, int my_rank, void* stream) {
+  if (epi == G_RS_PUSH) return -1;   // use grm_gemm_bf16_tp
+  return gemm_bf16_impl(A, lda, B, ldb, out, ldo, M, N, K, epi, bn, max_ctas, peer_out, nullptr, world, my_rank, nullptr, 0u, stream);
+}
+
+// Tensor-parallel variants.  epi 4 (reduce-scatter push): bf16 partial tiles go to the owner rank's
+// buffer peer_out[r] (slot my_rank; [world][M/world][ldo]) and every stored 32-row slab adds 1 to
+// peer_cnt[r][(local m tile)*world + my_rank], so a complete (m tile, source) pair reads
+// 4 * ceil(N/BN) per launch.  ag_cnt != null (all-gather wait): rows of A are pushed into this rank's
+// copy by their owners; m tile t is loaded once ag_cnt[t] >= ag_expect.  M must be a multiple of
+// world*128 for epi 4.  The block-column count this launch uses is returned through n_tiles_out.
+GRM_API int grm_gemm_bf16_tp(const void* A, int lda, const void* B, int ldb, void* out, int ldo, int M, int N, int K, int epi,
+                             int bn, const void* const* peer_out, const void* const* peer_cnt, int world, int my_rank,
+                             const void* ag_cnt, unsigned int ag_expect, int* n_tiles_out, void* stream) {
+  int use_bn = bn ? bn : ((N >= 2048 && (N % 256 == 0 || N > 8192)) ? 256 : 128);
+  if (n_tiles_out) *n_tiles_out = (N + use_bn - 1) / use_bn;
+  return gemm_bf16_impl(A, lda, B, ldb, out, ldo, M, N, K, epi, use_bn, 0, peer_out, peer_cnt, world, my_rank, ag_cnt, ag_expect, stream);
 }

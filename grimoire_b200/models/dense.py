@@ -258,8 +258,53 @@ class DenseModel:
         else:
             self.tp.row_parallel_add(lin, x, h)
 
+    def forward_prefill_sp(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
+        """Prefill chunk under tensor parallelism with the fused GEMM -> reduce-scatter and
+        all-gather -> GEMM kernels; the residual stream and the norms live on this rank's M/W token
+        shard (sequence parallelism).  Same math as ``forward`` up to bf16 partial sums on the wire."""
+        cfg, geom, tp = self.cfg, self.geom, self.tp
+        M, H = rb.tokens.shape[0], cfg.hidden_size
+        W, r = self.tp_world, self.tp_rank
+        R = M // W
+        eps, off = cfg.rms_norm_eps, cfg.norm_offset
+        tp.sp_setup(M, H)
+        hs = tp.sp_hs[:R]
+        K.embed(rb.tokens[r * R: (r + 1) * R], self.embed, hs)
+        qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]
+        gate = buf.gate[:M] if buf.gate is not None else None
+        T = rb.q_pos0 + M
+        for li, L in enumerate(self.layers):
+            kvl = kv_layers[li]
+            x_full, agc, age = tp.sp_reduce_norm_allgather(hs, L.in_norm, eps, off, reduce=li > 0, M=M)
+            tp.sp_gemm_allgathered(L.qkv, x_full, agc, age, qkv, "bf16")
+            if rb.q_pos0 > 0:
+                K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
+            K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
+                           gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+            K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
+            tp.sp_gemm_reduce_scatter(L.o, attn, M, H)
+            x_full, agc, age = tp.sp_reduce_norm_allgather(hs, L.post_norm, eps, off, reduce=True, M=M)
+            tp.sp_gemm_allgathered(L.gate_up, x_full, agc, age, act, "swiglu")
+            tp.sp_gemm_reduce_scatter(L.down, act, M, H)
+        tp.sp_reduce_norm_allgather(hs, None, eps, off, reduce=True, M=M)
+        # the rows that need logits live on their owners: collect them on every rank
+        rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
+        n = rows.shape[0]
+        sel = torch.zeros(n, H, dtype=torch.float32, device=self.device)
+        mine = (rows >= r * R) & (rows < (r + 1) * R)
+        if bool(mine.any()):
+            sel[mine] = hs.index_select(0, rows[mine] - r * R)
+        torch.distributed.all_reduce(sel, group=tp.group)
+        xf, logits = buf.xf[:n], buf.logits[:n]
+        K.add_rmsnorm(sel, self.final_norm, xf, eps, off)
+        self.lm_head(xf, logits, "f32")
+        return logits
+
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
+        if (rb.mode == "prefill" and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
+                and self.tp.sp_ready(rb.tokens.shape[0]) and self.tp.sp_enabled):
+            return self.forward_prefill_sp(rb, buf, kv_layers, block_table)
         cfg, geom = self.cfg, self.geom
         M = rb.tokens.shape[0]
         eps, off = cfg.rms_norm_eps, cfg.norm_offset

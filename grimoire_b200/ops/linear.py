@@ -168,3 +168,29 @@ class BF16Linear:
         return gemm_bf16(x, self.w, out, epi)
 
     __call__ = forward
+
+
+def gemm_bf16_tp(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], epi: str, *, peer_out=None, peer_cnt=None,
+                 world: int = 1, my_rank: int = 0, ag_cnt: Optional[torch.Tensor] = None, ag_expect: int = 0, ldo: int = 0) -> int:
+    """Tensor-parallel variants of the tcgen05 GEMM (see grm_gemm_bf16_tp): ``epi='rs_push'`` pushes
+    bf16 partial tiles to the owner ranks and counts arrivals; ``ag_cnt`` makes the producer warp
+    wait per m tile for rows pushed by their owners.  Returns the number of block columns used."""
+    M, K = a.shape
+    N = b.shape[0]
+    nt = ctypes.c_int(0)
+    code = _native.cuda().grm_gemm_bf16_tp(
+        _native.ptr(a), _c(a.stride(0)), _native.ptr(b), _c(b.stride(0)), _native.ptr(out), _c(ldo or (out.stride(0) if out is not None else N)),
+        _c(M), _c(N), _c(K), _c(EPI[epi]), _c(0), peer_out, peer_cnt, _c(world), _c(my_rank), _native.ptr(ag_cnt),
+        ctypes.c_uint(ag_expect & 0xFFFFFFFF), ctypes.byref(nt), _native.stream_ptr())
+    _native.check(code, f"gemm_bf16_tp M={M} N={N} K={K} epi={epi}")
+    return nt.value
+
+
+def w4_dequant_into(lin: "W4Linear") -> torch.Tensor:
+    """Dequantize an int4 projection into the shared bf16 scratch and return the [N][K] view."""
+    t = lin.tiled
+    wbuf = lin.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
+    code = _native.cuda().grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
+                                         _c(t.K), _native.stream_ptr())
+    _native.check(code, f"dequant_w4 {lin.name}")
+    return wbuf[: lin.N]

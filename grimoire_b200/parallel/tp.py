@@ -62,6 +62,7 @@ class TensorParallel:
         self.epochs: Optional[torch.Tensor] = None
         self.partial: Optional[torch.Tensor] = None
         self.spin = int(os.environ.get("GRIMOIRE_TP_SPIN", "0"))
+        self.sp_enabled = os.environ.get("GRIMOIRE_TP_SP", "1") != "0"     # fused sequence-parallel prefill
         self.stats = {"fused_allreduce": 0, "nccl_allreduce": 0}
 
     def attach(self, model, max_rows: int = 64) -> None:
@@ -103,6 +104,86 @@ class TensorParallel:
         dist.all_reduce(part, group=self.group)
         h.add_(part)
         self.stats["nccl_allreduce"] += 1
+
+    # ------------------------------------------------------------------------------------------
+    # fused prefill: GEMM -> reduce-scatter, all-gather -> GEMM, norms on the token shard
+    # ------------------------------------------------------------------------------------------
+    def sp_ready(self, M: int) -> bool:
+        """The fused sequence-parallel prefill needs whole 128-row tiles per rank."""
+        return self.fused and self.device.type == "cuda" and M % (self.world * 128) == 0 and M > 0
+
+    def sp_setup(self, M: int, H: int) -> None:
+        if getattr(self, "_sp_M", 0) >= M and getattr(self, "_sp_H", 0) == H:
+            if getattr(self, "_sp_cur_M", M) != M:
+                # a different chunk height touches a different set of tiles: restart the arrival
+                # counters (all ranks, between launches) so the monotonic expectations stay aligned
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+                self.sp_rs_cnt.local.zero_()
+                for c in self.sp_ag_cnt:
+                    c.local.zero_()
+                self._rs_expect, self._ag_expect = 0, [0, 0]
+                torch.cuda.synchronize(self.device)
+                dist.barrier(self.group)
+                self._sp_cur_M = M
+            return
+        self._sp_cur_M = M
+        W = self.world
+        R = M // W
+        self.sp_x = [SymmetricBuffer(M * H, torch.bfloat16, self.group, self.device) for _ in range(2)]          # gathered activations
+        self.sp_recv = [SymmetricBuffer(W * R * H, torch.bfloat16, self.group, self.device) for _ in range(2)]    # partial slots
+        self.sp_rs_cnt = SymmetricBuffer((R // 128) * W + 8, torch.int32, self.group, self.device)
+        self.sp_ag_cnt = [SymmetricBuffer(M // 128 + 8, torch.int32, self.group, self.device) for _ in range(2)]
+        self.sp_hs = torch.zeros(R, H, dtype=torch.float32, device=self.device)
+        self._sp_M, self._sp_H = M, H
+        self._rs_expect = 0
+        self._ag_expect = [0, 0]
+        self._sp_flip = 0
+        self._rs_flip = 0
+        dist.barrier(self.group)
+        torch.cuda.synchronize(self.device)
+
+    def sp_reduce_norm_allgather(self, hs: torch.Tensor, norm_w, eps: float, offset: float, reduce: bool, M: int):
+        """Owner side: hs (+= sum of the W partials of the last row-parallel GEMM); when ``norm_w``
+        is given, push rms(hs)*w into every rank's activation copy.  Returns (x_full view, ag counter
+        tensor, expected count) for the consuming GEMM."""
+        W, R, H = self.world, hs.shape[0], hs.shape[1]
+        recv = cnt = None
+        if reduce:
+            recv = self.sp_recv[self._rs_flip ^ 1].local       # the buffer the last rs_push wrote
+            cnt = self.sp_rs_cnt.local
+        xi = self._sp_flip
+        x_ptrs = ag_ptrs = None
+        if norm_w is not None:
+            x_ptrs, ag_ptrs = self.sp_x[xi].ptr_array(), self.sp_ag_cnt[xi].ptr_array()
+            self._ag_expect[xi] += 128
+        code = _native.cuda().grm_rs_reduce_norm_ag(
+            _native.ptr(hs), ctypes.c_int(hs.stride(0)), _native.ptr(recv), _native.ptr(cnt), ctypes.c_uint(self._rs_expect & 0xFFFFFFFF),
+            _native.ptr(norm_w), ctypes.c_float(eps), ctypes.c_float(offset), x_ptrs, ag_ptrs, ctypes.c_int(R), ctypes.c_int(H),
+            ctypes.c_int(W), ctypes.c_int(self.rank), ctypes.c_uint(self.spin), _native.stream_ptr())
+        _native.check(code, "rs_reduce_norm_ag")
+        if norm_w is None:
+            return None, None, 0
+        self._sp_flip ^= 1
+        return self.sp_x[xi].local[: M * H].view(M, H), self.sp_ag_cnt[xi].local, self._ag_expect[xi]
+
+    def sp_gemm_allgathered(self, lin, x_full, ag_cnt, ag_expect, out, epi: str):
+        """Column-parallel projection whose A rows arrive by all-gather pushes (waits per m tile)."""
+        from ..ops.linear import gemm_bf16_tp, w4_dequant_into
+
+        w = w4_dequant_into(lin)
+        gemm_bf16_tp(x_full, w, out, epi, ag_cnt=ag_cnt, ag_expect=ag_expect)
+
+    def sp_gemm_reduce_scatter(self, lin, x, M: int, H: int):
+        """Row-parallel projection whose epilogue pushes partial tiles to the row owners."""
+        from ..ops.linear import gemm_bf16_tp, w4_dequant_into
+
+        w = w4_dequant_into(lin)
+        buf = self.sp_recv[self._rs_flip]
+        nt = gemm_bf16_tp(x, w, None, "rs_push", peer_out=buf.ptr_array(), peer_cnt=self.sp_rs_cnt.ptr_array(), world=self.world,
+                          my_rank=self.rank, ldo=H)
+        self._rs_expect += 4 * nt
+        self._rs_flip ^= 1
 
     def check(self) -> None:
         """Raise CommTimeout if a fused kernel recorded a peer-wait timeout."""
