@@ -52,6 +52,7 @@ struct GemmParams {
   const unsigned int* ag_cnt;
   unsigned int ag_expect;
   unsigned int spin;
+  int vec_ok;   // output base and row pitch are 16-byte aligned: the epilogue may use 128-bit stores
 };
 
 __device__ __forceinline__ void red_release_sys_add(unsigned int* p, unsigned int v) {
@@ -208,7 +209,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           } else {
             dst = reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldo + col;
           }
-          if (col + 32 <= p.N) {
+          if (col + 32 <= p.N && p.vec_ok) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -225,7 +226,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         } else if (EPI == G_F32 || EPI == G_ADD_F32) {
           float* dst = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col;
-          if (col + 32 <= p.N) {
+          if (col + 32 <= p.N && p.vec_ok) {
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
               float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
@@ -384,6 +385,12 @@ static int gemm_bf16_impl(const void* A, int lda, const void* B, int ldb, void* 
     p.peer_cnt[i] = (peer_cnt && i < world) ? (unsigned int*)const_cast<void*>(peer_cnt[i]) : nullptr;
   }
   p.ag_cnt = (const unsigned int*)ag_cnt; p.ag_expect = ag_expect; p.spin = 4000000u;
+  {
+    const size_t esz = (epi == G_F32 || epi == G_ADD_F32) ? 4 : 2;
+    bool ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (((size_t)ldo * esz) % 16 == 0);
+    for (int i = 0; i < 8 && ok; ++i) if (p.peer_out[i] && reinterpret_cast<uintptr_t>(p.peer_out[i]) % 16) ok = false;
+    p.vec_ok = ok ? 1 : 0;
+  }
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   cudaStream_t st = (cudaStream_t)stream;

@@ -1,0 +1,256 @@
+// Mixture-of-experts kernels: routing (softmax over all experts, top-k, renormalise), the grouped
+// expert GEMM over block-scaled fp8 weights (e4m3 payload, one fp32 scale per 1x128 block along K)
+// and the top-k weighted combine.
+//
+// Reference: launch_router_topk* (src/ops.cpp:1022-1490), moe_gate_up_impl_r / moe_down_impl_r and
+// the grouped expert GEMMs (src/moe_kernels.cpp:83-1170, src/gemm_fast.cpp:1444-2560), dispatch /
+// un-permute helpers (src/prefill.cpp:2644-2905).  One grouped kernel serves decode rows (one tile
+// per (row, selected expert)) and prompt chunks (rows sorted by expert, 16-row tiles): every tile
+// names its expert and its rows, weights are converted fp8 -> f16 in registers and multiplied with
+// warp-level f16 MMAs (fp32 accumulate), the block scale is applied to the fp32 partial sum every
+// 128 columns of K, the gate/up projection applies SwiGLU in the epilogue.
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// routing: one warp per row.  logits fp32 [M][ld] (E experts, optional extra column E = shared gate)
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxExpertsPerLane = 16;   // E <= 512
+
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, int M, int E, int top_k, int renorm,
+                                                        int* __restrict__ ids, int ld_ids, float* __restrict__ weights, int ld_w,
+                                                        int* __restrict__ counts) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float* lg = logits + (size_t)row * ld;
+  float v[kMaxExpertsPerLane];
+  float mx = -INFINITY;
+  const int per = (E + 31) / 32;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (i < per && e < E) ? lg[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxExpertsPerLane; ++i) { v[i] = (v[i] == -INFINITY) ? 0.f : __expf(v[i] - mx); sum += v[i]; }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  float wsum = 0.f, mine_w = 0.f;
+  int mine_id = 0;
+  for (int k = 0; k < top_k; ++k) {
+    float bv = -1.f; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxExpertsPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > bv || (v[i] == bv && e < bi)) { bv = v[i]; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) v[bi >> 5] = -1.f;      // taken (all probabilities are >= 0)
+    if (lane == k) { mine_id = bi; mine_w = bv * inv; }
+    wsum += bv * inv;
+  }
+  if (lane < top_k) {
+    ids[(size_t)row * ld_ids + lane] = mine_id;
+    weights[(size_t)row * ld_w + lane] = renorm ? mine_w / wsum : mine_w;
+    if (counts) atomicAdd(&counts[mine_id], 1);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// grouped GEMM: tile = 16 rows of one expert x 128 output columns.
+// ---------------------------------------------------------------------------------------------
+struct GroupedParams {
+  const bf16* x; int ldx;           // activations [rows][K]
+  const int* row_ids;               // [total_rows] source row of x for each grouped row (null: identity)
+  const int* tile_expert;           // [tiles]
+  const int* tile_row0;             // [tiles] first grouped row
+  const int* tile_rows;             // [tiles] rows in the tile (1..16)
+  const uint8_t* w;                 // [E][N][K] e4m3
+  const float* scale;               // [E][N][K/128]
+  void* out; int ldo;               // mode 0: bf16 [total_rows][N/2] (SwiGLU: rows [0,N/2) gate, [N/2,N) up)
+                                    // mode 1: fp32 [total_rows][N]
+  int N, K, mode;
+};
+
+constexpr int kGThreads = 128;      // 4 warps, each 32 output columns (x2 for gate/up)
+
+__device__ __forceinline__ void cvt_e4m3x4_to_f16x2x2(uint32_t v, uint32_t& lo, uint32_t& hi) {
+  unsigned short a = (unsigned short)(v & 0xffffu), b = (unsigned short)(v >> 16);
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"(a));
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"(b));
+}
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MODE 0: gate|up + SwiGLU (each warp computes 32 gate and the matching 32 up columns); MODE 1: plain.
+template <int MODE>
+__global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedParams p) {
+  __shared__ __align__(16) __half xs[16][128 + 8];     // one 128-wide K block of the tile's rows, f16
+  const int tile = blockIdx.x, nblk = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = p.tile_rows[tile];
+  const int NO = MODE == 0 ? p.N / 2 : p.N;             // output columns
+  const int col0 = nblk * 128 + warp * 32;              // this warp's first output column
+  const int KB = p.K / 128;
+  const uint8_t* we = p.w + (size_t)e * p.N * p.K;
+  const float* se = p.scale + (size_t)e * p.N * KB;
+  constexpr int NB = MODE == 0 ? 2 : 1;                 // weight row groups per output column (gate, up)
+  float acc[NB][4][4];
+#pragma unroll
+  for (int b = 0; b < NB; ++b)
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[b][i][c] = 0.f;
+
+  for (int kb = 0; kb < KB; ++kb) {
+    __syncthreads();
+    // stage x rows [16][128] as f16 (rows beyond the tile are zero)
+    for (int i = tid; i < 16 * 16; i += kGThreads) {
+      const int r = i >> 4, c8 = i & 15;
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);
+      if (r < nr) {
+        const int src = p.row_ids ? p.row_ids[r0 + r] : (r0 + r);
+        const uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx + kb * 128 + c8 * 8);
+        const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+        uint32_t ou[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const __half2 h2 = __floats2half2_rn(bf16lo_to_f(in[q]), bf16hi_to_f(in[q]));
+          ou[q] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        o = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      }
+      *reinterpret_cast<uint4*>(&xs[r][c8 * 8]) = o;
+    }
+    __syncthreads();
+    float part[NB][4][4];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) part[b][i][c] = 0.f;
+    // two 64-wide halves; lane t owns k columns [16t, 16t+16) of a half (A and B use the same K order)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint4 wv[NB][4];
+#pragma unroll
+      for (int b = 0; b < NB; ++b)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int n = col0 + i * 8 + g + b * NO;
+          wv[b][i] = (col0 + i * 8 + g < NO)
+                         ? ldg_stream_v4(we + (size_t)n * p.K + kb * 128 + half * 64 + t * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // A fragment: rows g / g+8, k slots (2t,2t+1) <- columns 16t+4j, +1 ; (2t+8,2t+9) <- 16t+4j+2, +3
+        const uint2 xa = *reinterpret_cast<const uint2*>(&xs[g][half * 64 + t * 16 + j * 4]);
+        const uint2 xb = *reinterpret_cast<const uint2*>(&xs[g + 8][half * 64 + t * 16 + j * 4]);
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t wq = j == 0 ? wv[b][i].x : (j == 1 ? wv[b][i].y : (j == 2 ? wv[b][i].z : wv[b][i].w));
+            uint32_t b0, b1;
+            cvt_e4m3x4_to_f16x2x2(wq, b0, b1);
+            mma_f16_16816(part[b][i], xa.x, xb.x, xa.y, xb.y, b0, b1);
+          }
+      }
+    }
+    // block scale of this 128-wide K block: columns 2t, 2t+1 of each n8 tile
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = col0 + i * 8 + 2 * t;
+        const float s0 = (n < NO) ? se[(size_t)(n + b * NO) * KB + kb] : 0.f;
+        const float s1 = (n + 1 < NO) ? se[(size_t)(n + 1 + b * NO) * KB + kb] : 0.f;
+        acc[b][i][0] = fmaf(s0, part[b][i][0], acc[b][i][0]);
+        acc[b][i][1] = fmaf(s1, part[b][i][1], acc[b][i][1]);
+        acc[b][i][2] = fmaf(s0, part[b][i][2], acc[b][i][2]);
+        acc[b][i][3] = fmaf(s1, part[b][i][3], acc[b][i][3]);
+      }
+  }
+  // epilogue: c0,c1 = (row g, cols 2t, 2t+1); c2,c3 = (row g+8, same cols)
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = g + 8 * (c >> 1), n = col0 + i * 8 + 2 * t + (c & 1);
+      if (r >= nr || n >= NO) continue;
+      const size_t o = (size_t)(r0 + r) * p.ldo + n;
+      if (MODE == 0) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(silu_f(acc[0][i][c]) * acc[NB - 1][i][c]);
+      else if (MODE == 1) reinterpret_cast<float*>(p.out)[o] = acc[0][i][c];
+      else if (MODE == 2) reinterpret_cast<float*>(p.out)[o] += acc[0][i][c];
+      else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc[0][i][c]);
+    }
+}
+
+// h[token] += sum_j w[token][j] * y[pos[token][j]]  (fixed j order -> deterministic)
+__global__ void moe_combine_kernel(float* __restrict__ h, int ldh, const float* __restrict__ y, int ldy, const int* __restrict__ pos,
+                                   const float* __restrict__ wts, int slots, int H) {
+  const int tok = blockIdx.x;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < slots; ++j) {
+      const int ps = pos[(size_t)tok * slots + j];
+      if (ps >= 0) acc = fmaf(wts[(size_t)tok * slots + j], y[(size_t)ps * ldy + c], acc);
+    }
+    h[(size_t)tok * ldh + c] += acc;
+  }
+}
+
+}  // namespace
+
+GRM_API int grm_moe_route(const void* logits, int ld, int M, int E, int top_k, int renorm, void* ids, int ld_ids, void* weights,
+                          int ld_w, void* counts, void* stream) {
+  if (E < 1 || E > 32 * kMaxExpertsPerLane || top_k < 1 || top_k > 32 || top_k > E) return -2;
+  const int threads = 128;
+  const int blocks = (M * 32 + threads - 1) / threads;
+  moe_route_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const float*)logits, ld, M, E, top_k, renorm, (int*)ids, ld_ids,
+                                                                (float*)weights, ld_w, (int*)counts);
+  GRM_LAUNCH_RET();
+}
+
+// mode 0: out bf16 [total_rows][N/2] = silu(x Wg^T) * (x Wu^T) with W = [gate rows | up rows];
+// mode 1: out fp32 [total_rows][N] = x W^T; mode 2: out += ; mode 3: bf16 store.  K % 128 == 0; weights e4m3 with fp32 scales [E][N][K/128].
+GRM_API int grm_moe_grouped_gemm(const void* x, int ldx, const void* row_ids, const void* tile_expert, const void* tile_row0,
+                                 const void* tile_rows, int n_tiles, const void* w, const void* scale, void* out, int ldo, int N,
+                                 int K, int mode, void* stream) {
+  if (n_tiles < 1 || (K % 128) || (ldx & 7) || (mode == 0 && (N & 1))) return -2;
+  GroupedParams p;
+  p.x = (const bf16*)x; p.ldx = ldx; p.row_ids = (const int*)row_ids; p.tile_expert = (const int*)tile_expert;
+  p.tile_row0 = (const int*)tile_row0; p.tile_rows = (const int*)tile_rows; p.w = (const uint8_t*)w; p.scale = (const float*)scale;
+  p.out = out; p.ldo = ldo; p.N = N; p.K = K; p.mode = mode;
+  const int NO = mode == 0 ? N / 2 : N;
+  dim3 grid(n_tiles, (NO + 127) / 128);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (mode) {
+    case 0: moe_grouped_kernel<0><<<grid, kGThreads, 0, st>>>(p); break;
+    case 1: moe_grouped_kernel<1><<<grid, kGThreads, 0, st>>>(p); break;
+    case 2: moe_grouped_kernel<2><<<grid, kGThreads, 0, st>>>(p); break;
+    case 3: moe_grouped_kernel<3><<<grid, kGThreads, 0, st>>>(p); break;
+    default: return -1;
+  }
+  GRM_LAUNCH_RET();
+}
+
+GRM_API int grm_moe_combine(void* h, int ldh, const void* y, int ldy, const void* pos, const void* wts, int M, int slots, int H,
+                            void* stream) {
+  moe_combine_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((float*)h, ldh, (const float*)y, ldy, (const int*)pos, (const float*)wts, slots, H);
+  GRM_LAUNCH_RET();
+}

@@ -36,7 +36,7 @@ class Engine:
         self.device = model.device
         self.limits = limits or EngineLimits()
         lim = self.limits
-        n_attn = len(model.layers)          # attention layers of this pipeline stage
+        n_attn = getattr(model, "kv_layer_count", len(model.layers))   # attention layers of this pipeline stage
         pages = lim.kv_pages or (lim.max_slots * ((lim.max_ctx + PAGE - 1) // PAGE))
         self.kv = KvPool(n_attn, model.geom.Hkv, model.geom.D, pages, lim.max_slots, lim.max_ctx, self.device)
         chunk = min(lim.prefill_chunk, lim.max_ctx)
@@ -58,7 +58,10 @@ class Engine:
     # slots
     # ------------------------------------------------------------------------------------------
     def open(self, slot: Optional[int] = None) -> SeqSlot:
-        return self.kv.open_slot(slot)
+        seq = self.kv.open_slot(slot)
+        if hasattr(self.model, "reset_slot"):
+            self.model.reset_slot(seq.slot)        # recurrent state of hybrid models starts at zero
+        return seq
 
     def release(self, seq: SeqSlot, cache: bool = False, head_logits=None) -> None:
         """Free the slot; with ``cache`` its KV stays resident in the prefix cache (cache_sequence,
@@ -170,6 +173,9 @@ class Engine:
             return []
         if M > self.limits.max_decode_rows:
             raise ValueError("too many rows for one step")
+        if not getattr(self.model, "supports_verify_rows", True) and len({s.slot for s in seqs}) != M:
+            # recurrent layers advance one token per conversation per step: no multi-row verify blocks
+            raise NotImplementedError("this model cannot score several rows of one conversation in one step")
         max_len = 0
         for s, p in zip(seqs, positions):
             self.kv.ensure(s, p + 1)
@@ -205,10 +211,21 @@ class Engine:
                 s.length += 1
                 s.tokens.append(int(t))
 
+    def _save_recurrent(self, M: int):
+        fn = getattr(self.model, "save_recurrent", None)
+        return fn(torch.unique(self.d_row_seq[:M])) if fn is not None else None
+
+    def _restore_recurrent(self, saved) -> None:
+        if saved is not None:
+            self.model.restore_recurrent(saved)
+
     def _capture(self, M: int, splits: int):
-        # warm the allocator / workspace outside capture, then record
+        # warm the allocator / workspace outside capture, then record; a model with recurrent state
+        # must not keep the warm-up run's update
+        saved = self._save_recurrent(M)
         self._run_rows(M, splits)
         torch.cuda.current_stream().synchronize()
+        self._restore_recurrent(saved)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._run_rows(M, splits)
@@ -238,9 +255,11 @@ class Engine:
             self.d_row_pos[:M].add_(1)
 
         saved = (self.d_tokens[:M].clone(), self.d_row_pos[:M].clone())
+        rec = self._save_recurrent(M)
         body()                       # warm-up outside capture (also sizes the workspace)
         torch.cuda.current_stream().synchronize()
         self.d_tokens[:M].copy_(saved[0]); self.d_row_pos[:M].copy_(saved[1])
+        self._restore_recurrent(rec)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             body()

@@ -1,0 +1,293 @@
+"""Hybrid linear-attention MoE decoder (Qwen3-Next / Qwen3.5 family): repeating 3 Gated DeltaNet
+layers + 1 gated full-attention layer, every FFN a top-k MoE with one shared expert.
+
+Layer math and conventions follow the reference engine's forward() for this family
+(grimoire.cpp:15105-15202 DeltaNet mixer, :15207-15351 gated attention, :15364-15453 MoE) and the
+numerics it pins with tests: zero-centred (1+w) norms except the DeltaNet output norm, q|gate split
+of q_proj with ``attn * sigmoid(gate)`` before o_proj, per-head q/k RMSNorm before partial RoPE,
+conv(k=4)+SiLU over packed q|k|v, L2-normalised q/k, ``o = (S q)/sqrt(Dk)``, ``rms_norm(o)*silu(z)``,
+router softmax over all experts -> top-k -> renormalise, shared expert scaled by sigmoid(x.w_gate).
+Weights are block-scaled fp8 (e4m3, 1x128 scales); the tiny a/b gate projections and the router
+stay bf16.  Per-slot recurrent state (DeltaNet ``S`` + conv ring) lives beside the paged KV cache.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..formats.codecs import Fmt
+from ..formats.quantize import quantize
+from ..ops import core as K
+from ..ops import hybrid as Hb
+from ..ops import ref
+from ..ops.linear import BF16Linear
+from ..ops.workspace import Workspace
+from .config import ModelConfig
+from .dense import RowBatch
+
+
+@dataclass
+class MoEBlock:
+    router: BF16Linear            # [E + 1][H]: expert logits, last row = shared-expert gate
+    gate_up: torch.Tensor         # uint8 [E][2I][H]
+    gate_up_scale: torch.Tensor   # fp32  [E][2I][H/128]
+    down: torch.Tensor            # uint8 [E][H][I]
+    down_scale: torch.Tensor      # fp32  [E][H][I/128]
+    shared_gu: Hb.FP8BlockLinear
+    shared_down: Hb.FP8BlockLinear
+
+
+@dataclass
+class HybridLayer:
+    kind: str                     # "gdn" | "attn"
+    in_norm: torch.Tensor
+    post_norm: torch.Tensor
+    moe: MoEBlock
+    # gdn
+    in_qkv: Optional[Hb.FP8BlockLinear] = None
+    in_z: Optional[Hb.FP8BlockLinear] = None
+    in_ab: Optional[BF16Linear] = None
+    conv_w: Optional[torch.Tensor] = None
+    A_log: Optional[torch.Tensor] = None
+    dt_bias: Optional[torch.Tensor] = None
+    gdn_norm: Optional[torch.Tensor] = None
+    out_proj: Optional[Hb.FP8BlockLinear] = None
+    # attention
+    qkv: Optional[Hb.FP8BlockLinear] = None
+    o: Optional[Hb.FP8BlockLinear] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    kv_index: int = -1
+    state_index: int = -1
+
+
+class HybridBuffers:
+    def __init__(self, m: "HybridModel", max_rows: int, max_logit_rows: int, dense_kv_tokens: int = 0):
+        cfg, dev = m.cfg, m.device
+        H, g = cfg.hidden_size, m.geom
+        bf, f32 = torch.bfloat16, torch.float32
+        mk = lambda *s, dt: torch.zeros(*s, dtype=dt, device=dev)
+        k = cfg.num_experts_per_tok
+        self.h, self.x = mk(max_rows, H, dt=f32), mk(max_rows, H, dt=bf)
+        self.qkv = mk(max_rows, g.Hq * g.D * 2 + 2 * g.Hkv * g.D, dt=bf)
+        self.q, self.gate, self.attn = (mk(max_rows, g.Hq * g.D, dt=bf) for _ in range(3))
+        self.gdn_qkv, self.gdn_conv = mk(max_rows, m.gdn_channels, dt=bf), mk(max_rows, m.gdn_channels, dt=bf)
+        self.gdn_z, self.gdn_o = mk(max_rows, m.Hv * m.Dv, dt=bf), mk(max_rows, m.Hv * m.Dv, dt=bf)
+        self.gdn_ab = mk(max_rows, 2 * m.Hv, dt=f32)
+        # row pitch padded to 16 bytes so the GEMM epilogue can use 128-bit stores
+        self.router = mk(max_rows, (cfg.num_experts + 1 + 3) // 4 * 4, dt=f32)
+        self.ids, self.wts = mk(max_rows, k, dt=torch.int32), mk(max_rows, k + 1, dt=f32)
+        self.act = mk(max_rows * k, cfg.moe_intermediate_size, dt=bf)
+        self.y = mk(max_rows * (k + 1), H, dt=f32)
+        self.act_s = mk(max_rows, cfg.shared_expert_intermediate_size, dt=bf)
+        self.pos = mk(max_rows, k + 1, dt=torch.int32)
+        self.xf, self.logits = mk(max_logit_rows, H, dt=bf), mk(max_logit_rows, cfg.vocab_size, dt=f32)
+        self.next_ids = mk(max_logit_rows, dt=torch.int32)
+        self.dense_k = mk(dense_kv_tokens, g.Hkv * g.D, dt=bf) if dense_kv_tokens else None
+        self.dense_v = mk(dense_kv_tokens, g.Hkv * g.D, dt=bf) if dense_kv_tokens else None
+        # static tables of the decode path: one run / one expert tile per row (graph friendly)
+        ar = torch.arange(max_rows * k, dtype=torch.int32, device=dev)
+        self.run_start = torch.arange(max_rows, dtype=torch.int32, device=dev)
+        self.run_len = torch.ones(max_rows, dtype=torch.int32, device=dev)
+        self.tile_row0, self.tile_rows, self.tile_src = ar, torch.ones_like(ar), (ar // k).to(torch.int32)
+        self.max_rows, self.max_logit_rows = max_rows, max_logit_rows
+
+
+class HybridModel:
+    def __init__(self, cfg: ModelConfig, device, workspace: Optional[Workspace] = None, max_slots: int = 8):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.ws = workspace or Workspace(device)
+        self.tp_rank, self.tp_world, self.pp_rank, self.pp_world = 0, 1, 0, 1
+        self.tp = self.pp = None
+        self.supports_verify_rows = False
+        self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        self.Hk, self.Hv, self.Dk, self.Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.gdn_channels = 2 * self.Hk * self.Dk + self.Hv * self.Dv
+        self.geom = K.AttnGeom(self.Hq, self.Hkv, cfg.head_dim, cfg.rot_dim, cfg.softmax_scale or ref.softmax_scale(cfg.head_dim),
+                               True, cfg.sliding_window, cfg.rms_norm_eps, cfg.norm_offset)
+        self.inv_freq = ref.rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
+        self.layers: list[HybridLayer] = []          # all layers, in order
+        self.kv_layer_count = cfg.num_attention_layers()
+        self.max_slots = max_slots
+        n_gdn = cfg.num_hidden_layers - self.kv_layer_count
+        self.state = torch.zeros(n_gdn, max_slots, self.Hv, self.Dv, self.Dk, dtype=torch.float32, device=self.device)
+        self.ring = torch.zeros(n_gdn, max_slots, self.gdn_channels, 3, dtype=torch.float32, device=self.device)
+        self.ring_tmp = torch.zeros(max_slots, self.gdn_channels, 3, dtype=torch.float32, device=self.device)
+        self.embed = self.final_norm = self.lm_head = None
+
+    def reset_slot(self, slot: int) -> None:
+        """A fresh conversation starts from a zero recurrent state (grimoire.cpp:10436-10451)."""
+        self.state[:, slot].zero_()
+        self.ring[:, slot].zero_()
+
+    def save_recurrent(self, slots: torch.Tensor):
+        """Copy of the recurrent state of ``slots`` (conv tails + delta-rule matrices).  Used around
+        executions whose effect must not persist (graph warm-up runs) and for speculative rollback
+        (the reference keeps a per-slot state checkpoint for the same purpose, grimoire.cpp:10452-10500)."""
+        idx = slots.long()
+        return idx, self.state.index_select(1, idx), self.ring.index_select(1, idx)
+
+    def restore_recurrent(self, saved) -> None:
+        idx, st, rg = saved
+        self.state.index_copy_(1, idx, st)
+        self.ring.index_copy_(1, idx, rg)
+
+    # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def random(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02, max_slots: int = 8, gen_device=None) -> "HybridModel":
+        """Random-init weights.  ``gen_device`` picks where the numbers are drawn (draw on "cpu" to get
+        the same model on a GPU and on the CPU path)."""
+        m = HybridModel(cfg, device, max_slots=max_slots)
+        dev = m.device
+        gdev = torch.device(gen_device or dev)
+        g = torch.Generator(device=gdev)
+        H, D = cfg.hidden_size, cfg.head_dim
+        E, I, Is = cfg.num_experts, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+
+        def rnd(*shape, tag, scale=std):
+            g.manual_seed(seed * 1000003 + tag)
+            return (torch.randn(*shape, generator=g, device=gdev, dtype=torch.float32) * scale).to(dev)
+
+        def fp8(w, name):
+            return Hb.FP8BlockLinear(w, dev, name)
+
+        nw = (lambda n: torch.zeros(n, device=dev)) if cfg.norm_zero_centered else (lambda n: torch.ones(n, device=dev))
+        kv_i = st_i = 0
+        for i in range(cfg.num_hidden_layers):
+            t = i * 64
+            gu = rnd(E, 2 * I, H, tag=t + 20)
+            dn = rnd(E, H, I, tag=t + 21)
+            gq = [quantize(gu[e], Fmt.FP8_BLOCK) for e in range(E)] if E <= 64 else None
+            if gq is not None:
+                dq = [quantize(dn[e], Fmt.FP8_BLOCK) for e in range(E)]
+                gu8, gus = torch.stack([q.payload for q in gq]), torch.stack([q.scales for q in gq])
+                dn8, dns = torch.stack([q.payload for q in dq]), torch.stack([q.scales for q in dq])
+            else:   # many experts: quantize as one [E*N][K] matrix (1x128 blocks never cross rows)
+                q1 = quantize(gu.reshape(E * 2 * I, H), Fmt.FP8_BLOCK)
+                q2 = quantize(dn.reshape(E * H, I), Fmt.FP8_BLOCK)
+                gu8, gus = q1.payload.reshape(E, 2 * I, H), q1.scales.reshape(E, 2 * I, H // 128)
+                dn8, dns = q2.payload.reshape(E, H, I), q2.scales.reshape(E, H, I // 128)
+            del gu, dn
+            moe = MoEBlock(BF16Linear(rnd(E + 1, H, tag=t + 22, scale=0.5), dev, f"L{i}.router"), gu8.contiguous(), gus.float().contiguous(),
+                           dn8.contiguous(), dns.float().contiguous(), fp8(rnd(2 * Is, H, tag=t + 23), f"L{i}.shared_gu"),
+                           fp8(rnd(H, Is, tag=t + 24), f"L{i}.shared_down"))
+            if cfg.is_attention_layer(i):
+                L = HybridLayer("attn", nw(H), nw(H), moe, qkv=fp8(rnd(cfg.q_size + 2 * cfg.kv_size, H, tag=t + 1), f"L{i}.qkv"),
+                                o=fp8(rnd(H, m.Hq * D, tag=t + 2), f"L{i}.o"), q_norm=nw(D), k_norm=nw(D), kv_index=kv_i)
+                kv_i += 1
+            else:
+                L = HybridLayer("gdn", nw(H), nw(H), moe, in_qkv=fp8(rnd(m.gdn_channels, H, tag=t + 3), f"L{i}.in_qkv"),
+                                in_z=fp8(rnd(m.Hv * m.Dv, H, tag=t + 4), f"L{i}.in_z"),
+                                in_ab=BF16Linear(rnd(2 * m.Hv, H, tag=t + 5, scale=0.2), dev, f"L{i}.in_ab"),
+                                conv_w=rnd(m.gdn_channels, 4, tag=t + 6, scale=0.4), A_log=rnd(m.Hv, tag=t + 7, scale=0.5),
+                                dt_bias=rnd(m.Hv, tag=t + 8, scale=0.5), gdn_norm=torch.ones(m.Dv, device=dev),
+                                out_proj=fp8(rnd(H, m.Hv * m.Dv, tag=t + 9), f"L{i}.out_proj"), state_index=st_i)
+                st_i += 1
+            m.layers.append(L)
+        m.embed = rnd(cfg.vocab_size, H, tag=900001).bfloat16()
+        m.final_norm = nw(H)
+        m.lm_head = fp8(rnd(cfg.vocab_size, H, tag=900002), "lm_head")
+        return m
+
+    def weight_bytes(self) -> int:
+        n = self.lm_head.nbytes()
+        for L in self.layers:
+            n += L.moe.gate_up.numel() + L.moe.down.numel() + 4 * (L.moe.gate_up_scale.numel() + L.moe.down_scale.numel())
+            for lin in (L.in_qkv, L.in_z, L.out_proj, L.qkv, L.o, L.moe.shared_gu, L.moe.shared_down):
+                if lin is not None:
+                    n += lin.nbytes()
+        return n
+
+    def make_buffers(self, max_rows: int, max_logit_rows: int, dense_kv_tokens: int = 0) -> HybridBuffers:
+        return HybridBuffers(self, max_rows, max_logit_rows, dense_kv_tokens)
+
+    # ------------------------------------------------------------------------------------------
+    def _moe(self, L: HybridLayer, x, h, buf: HybridBuffers, M: int, decode: bool) -> None:
+        cfg, moe = self.cfg, L.moe
+        E, k, H = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size
+        lg = buf.router[:M, : cfg.num_experts + 1]
+        moe.router(x, lg, "f32")
+        ids, wts = buf.ids[:M], buf.wts[:M]
+        Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts[:, :k])
+        wts[:, k] = torch.sigmoid(lg[:, E])
+        act, y, pos = buf.act[: M * k], buf.y[: M * (k + 1)], buf.pos[:M]
+        if decode:
+            te, r0, nr, src = ids.reshape(-1), buf.tile_row0[: M * k], buf.tile_rows[: M * k], buf.tile_src[: M * k]
+            pos[:, :k] = buf.tile_row0[: M * k].reshape(M, k)
+        else:
+            flat = ids.reshape(-1).long()
+            order = torch.sort(flat, stable=True).indices
+            counts = torch.bincount(flat, minlength=E).cpu()
+            src = (order // k).to(torch.int32)
+            inv = torch.empty_like(order)
+            inv[order] = torch.arange(order.numel(), device=order.device)
+            pos[:, :k] = inv.reshape(M, k).to(torch.int32)
+            tiles_per = (counts + 15) // 16
+            starts = torch.cumsum(counts, 0) - counts
+            te = torch.repeat_interleave(torch.arange(E), tiles_per)
+            within = torch.arange(int(tiles_per.sum())) - torch.repeat_interleave(torch.cumsum(tiles_per, 0) - tiles_per, tiles_per)
+            r0c = starts[te] + within * 16
+            nrc = torch.minimum(torch.full_like(r0c, 16), counts[te] - within * 16)
+            te, r0, nr = (t.to(torch.int32).to(x.device) for t in (te, r0c, nrc))
+        Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu")
+        Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32")
+        # shared expert as slot k of the combine
+        moe.shared_gu(x, buf.act_s[:M], "swiglu")
+        moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
+        pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
+        Hb.moe_combine(h, y, pos, wts)
+
+    def forward(self, rb: RowBatch, buf: HybridBuffers, kv_layers, block_table) -> torch.Tensor:
+        cfg, geom = self.cfg, self.geom
+        M = rb.tokens.shape[0]
+        eps, off = cfg.rms_norm_eps, cfg.norm_offset
+        h, x = buf.h[:M], buf.x[:M]
+        K.embed(rb.tokens, self.embed, h)
+        prefill = rb.mode == "prefill"
+        T = rb.q_pos0 + M
+        if prefill:
+            run_slot = torch.tensor([rb.seq_slot], dtype=torch.int32, device=self.device)
+            run_start = torch.zeros(1, dtype=torch.int32, device=self.device)
+            run_len = torch.tensor([M], dtype=torch.int32, device=self.device)
+            touched = torch.tensor([rb.seq_slot], dtype=torch.long, device=self.device)
+        else:
+            run_slot, run_start, run_len = rb.row_seq, buf.run_start[:M], buf.run_len[:M]
+            touched = rb.row_seq.long()
+        for L in self.layers:
+            K.add_rmsnorm(h, L.in_norm, x, eps, off)
+            if L.kind == "gdn":
+                si = L.state_index
+                L.in_qkv(x, buf.gdn_qkv[:M], "bf16")
+                L.in_z(x, buf.gdn_z[:M], "bf16")
+                L.in_ab(x, buf.gdn_ab[:M], "f32")
+                Hb.conv4_silu(buf.gdn_qkv[:M], L.conv_w, self.ring[si], self.ring_tmp, rb.row_seq, rb.row_pos, buf.gdn_conv[:M], touched)
+                Hb.gdn_runs(buf.gdn_conv[:M], buf.gdn_ab[:M], buf.gdn_z[:M], L.A_log, L.dt_bias, L.gdn_norm, eps, self.state[si],
+                            run_slot, run_start, run_len, buf.gdn_o[:M], self.Hk, self.Hv, self.Dk, self.Dv)
+                L.out_proj(buf.gdn_o[:M], h, "add_f32")
+            else:
+                kvl = kv_layers[L.kv_index]
+                qkv, q, gate, attn = buf.qkv[:M], buf.q[:M], buf.gate[:M], buf.attn[:M]
+                L.qkv(x, qkv, "bf16")
+                if prefill:
+                    if rb.q_pos0 > 0:
+                        K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
+                    K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate,
+                                   buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+                    K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
+                else:
+                    K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
+                    K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+                L.o(attn, h, "add_f32")
+            K.add_rmsnorm(h, L.post_norm, x, eps, off)
+            self._moe(L, x, h, buf, M, decode=not prefill)
+        if rb.logits_rows is None:
+            hsel, n = h, M
+        else:
+            n = rb.logits_rows.shape[0]
+            hsel = h.index_select(0, rb.logits_rows) if n != M else h
+        xf, logits = buf.xf[:n], buf.logits[:n]
+        K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
+        self.lm_head(xf, logits, "f32")
+        return logits
