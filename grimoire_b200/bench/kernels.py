@@ -1,0 +1,168 @@
+"""Per-kernel micro-benchmarks on the 27B projection / attention shapes.
+
+    python -m grimoire_b200.bench.kernels smallm  --rows 1        # int4 small-M (decode GEMV family)
+    python -m grimoire_b200.bench.kernels gemm    --rows 4096     # tcgen05 GEMM on the prefill shapes
+    python -m grimoire_b200.bench.kernels attn    --ctx 4096      # paged int8 decode attention
+    python -m grimoire_b200.bench.kernels prefill --rows 4096     # flash prefill attention
+
+Timing: CUDA events on the launching stream after warm-up, synchronised on both sides.  Every case
+cycles through enough operand copies that the bytes touched between two uses of the same copy
+exceed the 126 MB L2, so DRAM figures are cold-cache.  Fractions are quoted against the measured
+copy bandwidth / cuBLAS bf16 throughput in MEASURED_PEAKS.json at the repository root when present,
+else against 6650 GB/s and 1590 TFLOP/s ("of fallback").  The same commands with a small
+``--iters`` are the ones profiled under ncu.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .. import _native
+from ..formats.w4_tile_layout import W4Tiled
+from ..ops import core as K
+from ..ops.linear import W4Linear, gemm_bf16
+from ..ops.workspace import Workspace
+
+L2_BYTES = 126e6
+SHAPES = [("qkv", 7168, 5120, False, "bf16"), ("o", 5120, 5120, False, "add_f32"), ("gate_up", 34816, 5120, True, "swiglu"),
+          ("down", 5120, 17408, False, "add_f32")]
+
+
+def peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "of measured"
+    except Exception:
+        return 6650.0, 1590.0, "of fallback"
+
+
+def timed(fn, iters: int, warmup: int = 5) -> float:
+    """Mean microseconds per call of ``fn(i)``."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / iters
+
+
+def _synthetic_w4(N: int, K_: int, swiglu: bool, dev) -> W4Linear:
+    lin = W4Linear.__new__(W4Linear)
+    lin.name = f"mb{N}x{K_}"
+    lin.N, lin.K, lin.group, lin.swiglu = N, K_, 128, swiglu
+    lin.device, lin.ws, lin.Np, lin.w_ref = torch.device(dev), Workspace(dev), N, None
+    w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N // 32, K_ // 64, 2, 32, 4), dtype=torch.int32, device=dev)
+    sz = torch.full((N // 16, K_ // 128, 16), (0x4308 << 16) | 0x1C00, dtype=torch.int32, device=dev)   # zero 8, scale 2^-8
+    lin.tiled = W4Tiled(w, sz, N, K_, 128)
+    lin.out_features = N // 2 if swiglu else N
+    return lin
+
+
+def bench_smallm(args) -> None:
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        one = _synthetic_w4(N, K_, sw, dev)
+        copies = max(2, int(L2_BYTES * 2 // one.tiled.nbytes()) + 1)
+        lins = [one] + [_synthetic_w4(N, K_, sw, dev) for _ in range(copies - 1)]
+        x = torch.randn(args.rows, K_, device=dev).bfloat16()
+        out = torch.zeros(args.rows, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        us = timed(lambda i: lins[i % copies](x, out, epi), args.iters)
+        gbs = one.tiled.nbytes() / 1e9 / (us * 1e-6)
+        print(f"smallm_w4 {name:8s} M={args.rows:2d} N={N:6d} K={K_:6d} copies={copies:2d}  {us:8.2f} us  {gbs:7.0f} GB/s  "
+              f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
+
+
+def bench_gemm(args) -> None:
+    _, tf, tag = peaks()
+    dev = "cuda"
+    M = args.rows
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        nbytes = (M * K_ + N * K_) * 2
+        copies = max(2, int(L2_BYTES * 2 // nbytes) + 1)
+        A = [torch.randn(M, K_, device=dev).bfloat16() for _ in range(copies)]
+        B = [(torch.randn(N, K_, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+        out = torch.zeros(M, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        us = timed(lambda i: gemm_bf16(A[i % copies], B[i % copies], out, epi), args.iters)
+        tfl = 2.0 * M * N * K_ / (us * 1e-6) / 1e12
+        print(f"gemm_tcgen05 {name:8s} M={M} N={N:6d} K={K_:6d} epi={epi:8s} {us:9.2f} us  {tfl:7.1f} TFLOP/s  "
+              f"{tfl / tf:.3f} {tag} cuBLAS bf16 burst", flush=True)
+
+
+def _paged_kv(ctx: int, slots: int, geom, dev):
+    from ..engine.kv import KvPool
+
+    pool = KvPool(1, geom.Hkv, geom.D, slots * ((ctx + 31) // 16) + 1, slots, ctx + 16, dev)
+    seqs = [pool.open_slot() for _ in range(slots)]
+    for s in seqs:
+        pool.ensure(s, ctx + 1)
+        s.length = ctx
+    lay = pool.layers[0]
+    lay.k.random_(-127, 127)
+    lay.v.random_(-127, 127)
+    lay.ks.fill_(0.01)
+    lay.vs.fill_(0.01)
+    return pool, seqs
+
+
+def bench_attn(args) -> None:
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    geom = K.AttnGeom(Hq=40, Hkv=8, D=128, rot=128, scale=128 ** -0.5)
+    M = args.rows
+    slots = max(M, int(L2_BYTES * 2 // (args.ctx * geom.Hkv * geom.D * 2)) + 1)
+    pool, seqs = _paged_kv(args.ctx, slots, geom, dev)
+    ws = Workspace(dev)
+    q = torch.randn(M, geom.Hq * geom.D, device=dev).bfloat16()
+    out = torch.zeros_like(q)
+    pos = torch.full((M,), args.ctx - 1, dtype=torch.int32, device=dev)
+    row_seq = [torch.tensor([(i * M + r) % slots for r in range(M)], dtype=torch.int32, device=dev) for i in range(slots)]
+    splits = max(1, min(64, (args.ctx // 16) // 8))
+    us = timed(lambda i: K.paged_decode_attn(q, row_seq[i % slots], pos, pool.table, pool.layers[0], geom, out, splits, ws), args.iters)
+    nbytes = M * args.ctx * geom.Hkv * (geom.D + 4) * 2
+    gbs = nbytes / 1e9 / (us * 1e-6)
+    print(f"paged_decode_attn rows={M} ctx={args.ctx} splits={splits}  {us:8.2f} us  {gbs:7.0f} GB/s  {gbs / hbm:.3f} {tag} copy bandwidth",
+          flush=True)
+
+
+def bench_prefill(args) -> None:
+    _, tf, tag = peaks()
+    dev = "cuda"
+    geom = K.AttnGeom(Hq=40, Hkv=8, D=128, rot=128, scale=128 ** -0.5)
+    T = args.rows
+    q = torch.randn(T, geom.Hq * geom.D, device=dev).bfloat16()
+    k = torch.randn(T, geom.Hkv * geom.D, device=dev).bfloat16()
+    v = torch.randn(T, geom.Hkv * geom.D, device=dev).bfloat16()
+    out = torch.zeros_like(q)
+    us = timed(lambda i: K.flash_prefill(q, k, v, geom, out, 0), args.iters)
+    tfl = 4.0 * geom.Hq * geom.D * T * T / 2 / (us * 1e-6) / 1e12        # causal: half the score matrix
+    print(f"flash_prefill T={T} Hq=40 Hkv=8 D=128 causal  {us:9.2f} us  {tfl:7.1f} TFLOP/s  {tfl / tf:.3f} {tag} cuBLAS bf16 burst", flush=True)
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=["smallm", "gemm", "attn", "prefill"])
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
+    args = ap.parse_args(argv)
+    {"smallm": bench_smallm, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
+    print(f"launches={_native.launch_count}", flush=True)
+
+
+if __name__ == "__main__":
+    main()
