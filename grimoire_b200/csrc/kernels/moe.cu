@@ -79,6 +79,12 @@ struct GroupedParams {
   void* out; int ldo;               // mode 0: bf16 [total_rows][N/2] (SwiGLU: rows [0,N/2) gate, [N/2,N) up)
                                     // mode 1: fp32 [total_rows][N]
   int N, K, mode;
+  // expert-parallel extensions (null / unused on the single-GPU path)
+  const int* n_tiles_dev;           // device-side tile count: CTAs of tiles beyond it exit (grid is an upper bound)
+  const int* tile_src;              // [tiles] rank whose tokens the tile's rows belong to            (MODE 4)
+  const int* row_dst;               // [total_rows] row of the source rank's return buffer            (MODE 4)
+  float* peer_y[8];                 // return buffers of all ranks, fp32 [pairs][ldo]                 (MODE 4)
+  unsigned int* peer_done[8];       // arrival counters of all ranks (one count per row and column block)
 };
 
 constexpr int kGThreads = 128;      // 4 warps, each 32 output columns (x2 for gate/up)
@@ -94,10 +100,14 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 }
 
 // MODE 0: gate|up + SwiGLU (each warp computes 32 gate and the matching 32 up columns); MODE 1: plain.
+// MODE 4 (expert parallel combine): the fp32 result rows are stored straight into the return buffer of
+// the rank that owns the token (peer stores over NVLink), then the tile raises that rank's arrival
+// counter with a system-scope release, so the owner's weighted top-k sum can start as rows land.
 template <int MODE>
 __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedParams p) {
   __shared__ __align__(16) __half xs[16][128 + 8];     // one 128-wide K block of the tile's rows, f16
   const int tile = blockIdx.x, nblk = blockIdx.y;
+  if (p.n_tiles_dev && tile >= *p.n_tiles_dev) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = p.tile_rows[tile];
@@ -192,12 +202,23 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedPar
     for (int c = 0; c < 4; ++c) {
       const int r = g + 8 * (c >> 1), n = col0 + i * 8 + 2 * t + (c & 1);
       if (r >= nr || n >= NO) continue;
+      if (MODE == 4) {
+        p.peer_y[p.tile_src[tile]][(size_t)p.row_dst[r0 + r] * p.ldo + n] = acc[0][i][c];
+        continue;
+      }
       const size_t o = (size_t)(r0 + r) * p.ldo + n;
       if (MODE == 0) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(silu_f(acc[0][i][c]) * acc[NB - 1][i][c]);
       else if (MODE == 1) reinterpret_cast<float*>(p.out)[o] = acc[0][i][c];
       else if (MODE == 2) reinterpret_cast<float*>(p.out)[o] += acc[0][i][c];
       else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc[0][i][c]);
     }
+  if (MODE == 4) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_done[p.tile_src[tile]]), "r"((unsigned)nr) : "memory");
+    }
+  }
 }
 
 // h[token] += sum_j w[token][j] * y[pos[token][j]]  (fixed j order -> deterministic)
@@ -236,6 +257,8 @@ GRM_API int grm_moe_grouped_gemm(const void* x, int ldx, const void* row_ids, co
   p.x = (const bf16*)x; p.ldx = ldx; p.row_ids = (const int*)row_ids; p.tile_expert = (const int*)tile_expert;
   p.tile_row0 = (const int*)tile_row0; p.tile_rows = (const int*)tile_rows; p.w = (const uint8_t*)w; p.scale = (const float*)scale;
   p.out = out; p.ldo = ldo; p.N = N; p.K = K; p.mode = mode;
+  p.n_tiles_dev = nullptr; p.tile_src = nullptr; p.row_dst = nullptr;
+  for (int i = 0; i < 8; ++i) { p.peer_y[i] = nullptr; p.peer_done[i] = nullptr; }
   const int NO = mode == 0 ? N / 2 : N;
   dim3 grid(n_tiles, (NO + 127) / 128);
   cudaStream_t st = (cudaStream_t)stream;
@@ -246,6 +269,32 @@ GRM_API int grm_moe_grouped_gemm(const void* x, int ldx, const void* row_ids, co
     case 3: moe_grouped_kernel<3><<<grid, kGThreads, 0, st>>>(p); break;
     default: return -1;
   }
+  GRM_LAUNCH_RET();
+}
+
+// Expert-parallel form: tile descriptors and the tile count live on the device (built by grm_ep_plan),
+// the grid is the upper bound ``max_tiles``.  mode 0: SwiGLU into the local activation buffer;
+// mode 4: rows go back to their source rank (see MODE 4 above).
+GRM_API int grm_moe_grouped_gemm_ep(const void* x, int ldx, const void* tile_expert, const void* tile_row0, const void* tile_rows,
+                                    const void* tile_src, const void* n_tiles_dev, int max_tiles, const void* w, const void* scale,
+                                    void* out, int ldo, int N, int K, int mode, const void* row_dst, void* const* peer_y,
+                                    void* const* peer_done, int world, void* stream) {
+  if (max_tiles < 1 || (K % 128) || (ldx & 7) || (mode == 0 && (N & 1)) || world < 1 || world > 8) return -2;
+  GroupedParams p;
+  p.x = (const bf16*)x; p.ldx = ldx; p.row_ids = nullptr; p.tile_expert = (const int*)tile_expert;
+  p.tile_row0 = (const int*)tile_row0; p.tile_rows = (const int*)tile_rows; p.w = (const uint8_t*)w; p.scale = (const float*)scale;
+  p.out = out; p.ldo = ldo; p.N = N; p.K = K; p.mode = mode;
+  p.n_tiles_dev = (const int*)n_tiles_dev; p.tile_src = (const int*)tile_src; p.row_dst = (const int*)row_dst;
+  for (int i = 0; i < 8; ++i) {
+    p.peer_y[i] = (mode == 4 && i < world) ? (float*)peer_y[i] : nullptr;
+    p.peer_done[i] = (mode == 4 && i < world) ? (unsigned int*)peer_done[i] : nullptr;
+  }
+  const int NO = mode == 0 ? N / 2 : N;
+  dim3 grid(max_tiles, (NO + 127) / 128);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode == 0) moe_grouped_kernel<0><<<grid, kGThreads, 0, st>>>(p);
+  else if (mode == 4) moe_grouped_kernel<4><<<grid, kGThreads, 0, st>>>(p);
+  else return -1;
   GRM_LAUNCH_RET();
 }
 

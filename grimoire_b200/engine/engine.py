@@ -183,7 +183,8 @@ class Engine:
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
         tp = getattr(self.model, "tp", None)
-        if (tp is not None and not tp.fused) or getattr(self.model, "pp", None) is not None:
+        ep = getattr(self.model, "ep", None)
+        if (tp is not None and not tp.fused) or (ep is not None and not ep.fused) or getattr(self.model, "pp", None) is not None:
             use_graph = False        # NCCL collectives / stage hops stay out of captured graphs
         if use_graph and self.device.type == "cuda":
             key = (M, splits)

@@ -101,6 +101,8 @@ class HybridModel:
         self.ws = workspace or Workspace(device)
         self.tp_rank, self.tp_world, self.pp_rank, self.pp_world = 0, 1, 0, 1
         self.tp = self.pp = None
+        self.ep = None                   # parallel.ep.ExpertParallel when the experts are sharded over ranks
+        self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = False
         self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         self.Hk, self.Hv, self.Dk, self.Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
@@ -122,6 +124,18 @@ class HybridModel:
         self.state[:, slot].zero_()
         self.ring[:, slot].zero_()
 
+    def attach_ep(self, group, max_rows: int, fused=None):
+        """Shard the MoE layers over ``group`` (the model must have been built with the matching
+        ep_rank / ep_world expert slice)."""
+        from ..parallel.ep import ExpertParallel
+
+        cfg = self.cfg
+        self.ep = ExpertParallel(group, self.device, cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size,
+                                 cfg.moe_intermediate_size, max_rows, fused=fused)
+        if (self.ep.rank, self.ep.world) != (self.ep_rank, self.ep_world):
+            raise ValueError("expert slice of the model does not match the expert-parallel group")
+        return self.ep
+
     def save_recurrent(self, slots: torch.Tensor):
         """Copy of the recurrent state of ``slots`` (conv tails + delta-rule matrices).  Used around
         executions whose effect must not persist (graph warm-up runs) and for speculative rollback
@@ -136,10 +150,16 @@ class HybridModel:
 
     # ------------------------------------------------------------------------------------------
     @staticmethod
-    def random(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02, max_slots: int = 8, gen_device=None) -> "HybridModel":
+    def random(cfg: ModelConfig, device, seed: int = 0, std: float = 0.02, max_slots: int = 8, gen_device=None,
+               ep_rank: int = 0, ep_world: int = 1) -> "HybridModel":
         """Random-init weights.  ``gen_device`` picks where the numbers are drawn (draw on "cpu" to get
-        the same model on a GPU and on the CPU path)."""
+        the same model on a GPU and on the CPU path).  With ``ep_world`` > 1 the rank keeps experts
+        [ep_rank * E/W, (ep_rank + 1) * E/W) of every layer (same values as the unsharded model)."""
         m = HybridModel(cfg, device, max_slots=max_slots)
+        m.ep_rank, m.ep_world = ep_rank, ep_world
+        if cfg.num_experts % ep_world:
+            raise ValueError("experts do not split evenly over the expert-parallel ranks")
+        e0, e1 = ep_rank * (cfg.num_experts // ep_world), (ep_rank + 1) * (cfg.num_experts // ep_world)
         dev = m.device
         gdev = torch.device(gen_device or dev)
         g = torch.Generator(device=gdev)
@@ -170,6 +190,7 @@ class HybridModel:
                 gu8, gus = q1.payload.reshape(E, 2 * I, H), q1.scales.reshape(E, 2 * I, H // 128)
                 dn8, dns = q2.payload.reshape(E, H, I), q2.scales.reshape(E, H, I // 128)
             del gu, dn
+            gu8, gus, dn8, dns = gu8[e0:e1], gus[e0:e1], dn8[e0:e1], dns[e0:e1]
             moe = MoEBlock(BF16Linear(rnd(E + 1, H, tag=t + 22, scale=0.5), dev, f"L{i}.router"), gu8.contiguous(), gus.float().contiguous(),
                            dn8.contiguous(), dns.float().contiguous(), fp8(rnd(2 * Is, H, tag=t + 23), f"L{i}.shared_gu"),
                            fp8(rnd(H, Is, tag=t + 24), f"L{i}.shared_down"))
@@ -209,6 +230,12 @@ class HybridModel:
         E, k, H = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size
         lg = buf.router[:M, : cfg.num_experts + 1]
         moe.router(x, lg, "f32")
+        if self.ep is not None:
+            if self.ep.fused:
+                self.ep.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
+            else:
+                self.ep.moe_allreduce(moe, x, h, lg, M, cfg.norm_topk_prob)
+            return
         ids, wts = buf.ids[:M], buf.wts[:M]
         Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts[:, :k])
         wts[:, k] = torch.sigmoid(lg[:, E])
