@@ -25,6 +25,7 @@ from ..ops import core as K
 from ..ops import ref
 from ..ops.linear import BF16Linear, W4Linear
 from ..ops.workspace import Workspace
+from ..utils import trace
 from .config import ModelConfig
 
 
@@ -318,10 +319,13 @@ class DenseModel:
             self.pp.recv_hidden(h)          # [rows][H] from the previous stage
         prefill = rb.mode == "prefill"
         T = rb.q_pos0 + M
+        tl = trace.timeline.on
         for li, L in enumerate(self.layers):
             kvl = kv_layers[li]
+            if tl: trace.mark("norm+qkv")
             K.add_rmsnorm(h, L.in_norm, x, eps, off)
             L.qkv(x, qkv, "bf16")
+            if tl: trace.mark("rope+attn")
             if prefill:
                 if rb.q_pos0 > 0:
                     K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
@@ -331,10 +335,14 @@ class DenseModel:
             else:
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
                 K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+            if tl: trace.mark("o_proj")
             self._row_parallel(L.o, attn, h)
+            if tl: trace.mark("norm+gate_up")
             K.add_rmsnorm(h, L.post_norm, x, eps, off)
             L.gate_up(x, act, "swiglu")
+            if tl: trace.mark("down")
             self._row_parallel(L.down, act, h)
+        if tl: trace.mark("head")
         if not last_stage:
             self.pp.send_hidden(h)
             return None
@@ -347,4 +355,5 @@ class DenseModel:
         xf, logits = buf.xf[:n], buf.logits[:n]
         K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
         self.lm_head(xf, logits, "f32")
+        if tl: trace.mark("end")
         return logits

@@ -38,9 +38,13 @@ class ControlChannel:
         if n > MAX_PAYLOAD:
             raise ValueError("control payload too large")
         head = torch.tensor([kind, a, b, n], dtype=torch.int64)
-        dist.broadcast(head, src=self.src, group=self.group)
-        if n:
-            dist.broadcast(torch.tensor(list(payload), dtype=torch.int64), src=self.src, group=self.group)
+        try:
+            dist.broadcast(head, src=self.src, group=self.group)
+            if n:
+                dist.broadcast(torch.tensor(list(payload), dtype=torch.int64), src=self.src, group=self.group)
+        except RuntimeError as e:
+            # a worker that left its loop (exception, exit) or stopped answering within the group timeout
+            raise WorkerLost(f"control channel broken while sending kind={kind}: {e}") from None
 
     def recv(self):
         head = torch.zeros(HEADER, dtype=torch.int64)

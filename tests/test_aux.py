@@ -1,0 +1,127 @@
+"""Auxiliary subsystems: timeline / probe tracing, expert heat + placement, DFlash config resolution."""
+import json
+
+import torch
+
+from grimoire_b200.models.dflash import resolve_dflash_config
+from grimoire_b200.models.expert_placement import ExpertHeat, HeatParams, balanced_placement, rank_loads
+from grimoire_b200.utils import trace
+
+
+def test_timeline_regions_and_probe(capsys, monkeypatch):
+    tl = trace.Timeline()
+    tl.enable(True)
+    for tag in ("a", "b", "a", "end"):
+        tl.mark(tag)
+    d = tl.dump()
+    assert list(d) == ["a", "b"] and all(v >= 0 for v in d.values())
+    assert len(tl.dump(per_mark=True)) == 3
+    assert "a" in tl.format()
+    tl.enable(False)
+    tl.mark("x")
+    assert tl.dump() == {}
+    t = torch.tensor([3.0, -4.0, float("nan"), float("inf")])
+    st = trace.probe_stats(t, exact=True)
+    assert st["nan"] == 1 and st["inf"] == 1 and st["max"] == 4.0 and len(st["fnv1a"]) == 16
+    assert trace.probe_stats(t, exact=True)["fnv1a"] == st["fnv1a"]
+    assert trace.fnv1a(b"") == 0xCBF29CE484222325 and trace.fnv1a(b"a") == 0xAF63DC4C8601EC8C
+    assert trace.probe("off", t) is None
+    monkeypatch.setenv("GRIMOIRE_DEBUG", "1")
+    assert trace.probe("h", t)["n"] == 4 and "[probe] h:" in capsys.readouterr().out
+    store = {}
+    with trace.FencedTimer(store, "verify"):
+        pass
+    assert store["verify"] >= 0.0
+
+
+def test_dense_forward_marks_regions():
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+    from grimoire_b200.models.config import tiny_dense
+    from grimoire_b200.models.dense import DenseModel
+    from grimoire_b200.models.synthetic import random_state_dict
+
+    cfg = tiny_dense()
+    eng = Engine(DenseModel.from_state_dict(cfg, random_state_dict(cfg, seed=0), "cpu"), EngineLimits(max_slots=1, max_ctx=64, prefill_chunk=32,
+                                                                                                 max_decode_rows=2))
+    trace.timeline.enable(True)
+    try:
+        eng.generate([1, 2, 3, 4], 2)
+        d = trace.timeline.dump()
+    finally:
+        trace.timeline.enable(False)
+    assert {"norm+qkv", "rope+attn", "o_proj", "norm+gate_up", "down", "head"} <= set(d)
+
+
+def test_expert_heat_credit_cap_decay_and_swaps(tmp_path):
+    h = ExpertHeat(2, 8, HeatParams(decay=0.5, credit_cap=4, moves_per_step=2, hysteresis=1.25, min_gain=1.5))
+    h.credit(0, [1, 1, 1, -1])                # out-of-range ids are skipped
+    assert h.h[0, 1] == 3.0 and h.h[0].sum() == 3.0
+    h.credit(0, [2] * 16)                      # 16 selections capped to 4 credits in total; older heat halves
+    assert abs(h.h[0, 2] - 4.0) < 1e-6 and abs(h.h[0, 1] - 1.5) < 1e-6
+    resident = lambda l, e: e in (0, 1)        # experts 0,1 resident; 2 is hot and not resident
+    swaps = h.propose_swaps(resident, lambda l, e: l == 0)
+    assert len(swaps) == 1 and (swaps[0].promote_expert, swaps[0].demote_expert) == (2, 0)   # coldest victim first
+    # hysteresis: a marginally hotter expert does not displace a resident one
+    g = ExpertHeat(1, 4, HeatParams(decay=1.0, min_gain=1.5))
+    g.credit(0, [0, 0, 1, 1, 1])
+    assert g.propose_swaps(lambda l, e: e == 0, lambda l, e: True) == []
+    p = str(tmp_path / "hits.json")
+    h.save(p)
+    h2 = ExpertHeat(2, 8)
+    assert h2.load(p) and (h2.hits == h.hits).all()
+    assert not ExpertHeat(3, 8).load(p)
+
+
+def test_balanced_placement_evens_rank_loads():
+    heat = [100, 90, 80, 70, 1, 1, 1, 1]
+    naive = rank_loads(heat, list(range(8)), 2)
+    perm = balanced_placement(heat, 2)
+    bal = rank_loads(heat, perm, 2)
+    assert sorted(perm) == list(range(8))
+    assert max(bal) - min(bal) < max(naive) - min(naive)
+    assert max(bal) - min(bal) <= 20
+    assert balanced_placement(heat, 2) == perm            # deterministic
+
+
+STANDARD = {
+    "hidden_size": 4096, "intermediate_size": 12288, "num_hidden_layers": 6, "num_attention_heads": 32, "num_key_value_heads": 4,
+    "head_dim": 128, "rms_norm_eps": 1e-06, "vocab_size": 262144, "draft_vocab_size": 32768, "sliding_window": None,
+    "rope_parameters": {"rope_type": "default", "rope_theta": 5000000.0},
+    "dflash_config": {"mask_token_id": 248077, "block_size": 16}, "target_layer_ids": [1, 6, 11, 16, 22, 27, 32, 37]}
+
+
+def test_dflash_config_standard_and_precedence():
+    s = resolve_dflash_config(json.dumps(STANDARD))
+    assert not s.error and s.n_layers == 6 and s.head_dim == 128 and s.rope_theta == 5e6 and s.mask_token == 248077
+    assert s.draft_vocab == 32768 and s.target_layers == [1, 6, 11, 16, 22, 27, 32, 37] and s.tap_key == "target_layer_ids"
+    assert not s.attn_from_config and all(l.window == 0 and not l.causal for l in s.layers) and len(s.layers) == 6
+    # dflash_config wins over eagle_config wins over the top level
+    c = dict(STANDARD, eagle_config={"num_hidden_layers": 5, "rms_norm_eps": 1e-5}, dflash_config={"num_hidden_layers": 4, "mask_token_id": 7})
+    s = resolve_dflash_config(json.dumps(c))
+    assert s.n_layers == 4 and abs(s.rms_eps - 1e-5) < 1e-12 and s.mask_token == 7
+    # defaults that are not checkpoint facts are reported
+    s = resolve_dflash_config(json.dumps({"num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4}))
+    assert s.rope_theta == 1e6 and s.head_dim == 64 and s.mask_token == -1 and len(s.notes) >= 3
+
+
+def test_dflash_config_attention_shape_rules():
+    base = {"num_hidden_layers": 4, "hidden_size": 256, "num_attention_heads": 4}
+    # use_swa with no layer_types: every layer slides with the dflash window
+    s = resolve_dflash_config(json.dumps(dict(base, dflash_config={"use_swa": 1, "swa_window_size": 512})))
+    assert s.attn_from_config and [l.window for l in s.layers] == [512] * 4 and not any(l.causal for l in s.layers)
+    # layer_types decide per layer; sliding layers are causal unless overridden
+    lt = ["sliding_attention", "full_attention", "sliding_attention", "full_attention"]
+    s = resolve_dflash_config(json.dumps(dict(base, layer_types=lt, sliding_window=1024)))
+    assert [l.window for l in s.layers] == [1024, 0, 1024, 0] and [l.causal for l in s.layers] == [True, False, True, False]
+    s = resolve_dflash_config(json.dumps(dict(base, layer_types=lt, sliding_window=1024, is_causal=False)))
+    assert not any(l.causal for l in s.layers)
+    s = resolve_dflash_config(json.dumps(dict(base, layer_types=lt, sliding_window=1024, dflash_config={"causal": True})))
+    assert all(l.causal for l in s.layers)
+    # use_swa with layer_types that name no sliding layer: the flag wins for all layers
+    s = resolve_dflash_config(json.dumps(dict(base, layer_types=["full_attention"] * 4, dflash_config={"use_swa": True, "swa_window_size": 64})))
+    assert [l.window for l in s.layers] == [64] * 4
+    # errors: sliding without a window, short layer_types, bad JSON
+    assert "no window" in resolve_dflash_config(json.dumps(dict(base, dflash_config={"use_swa": True}))).error
+    assert "only 2 entries" in resolve_dflash_config(json.dumps(dict(base, layer_types=lt[:2]))).error
+    assert resolve_dflash_config("{nope").error and resolve_dflash_config("[1]").error
+    assert resolve_dflash_config(json.dumps({"hidden_size": 8})).error
