@@ -130,7 +130,7 @@ def bench_attn(args) -> None:
     out = torch.zeros_like(q)
     pos = torch.full((M,), args.ctx - 1, dtype=torch.int32, device=dev)
     row_seq = [torch.tensor([(i * M + r) % slots for r in range(M)], dtype=torch.int32, device=dev) for i in range(slots)]
-    splits = max(1, min(64, (args.ctx // 16) // 8))
+    splits = args.splits or K.decode_splits(args.ctx, M, geom.Hkv)
     us = timed(lambda i: K.paged_decode_attn(q, row_seq[i % slots], pos, pool.table, pool.layers[0], geom, out, splits, ws), args.iters)
     nbytes = M * args.ctx * geom.Hkv * (geom.D + 4) * 2
     gbs = nbytes / 1e9 / (us * 1e-6)
@@ -158,6 +158,7 @@ def main(argv=None) -> None:
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--splits", type=int, default=0, help="attn: split-KV factor (0 = the engine's heuristic)")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
     {"smallm": bench_smallm, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)

@@ -6,9 +6,8 @@
 //
 // Design (bandwidth-bound, int8 K and V with one fp32 scale per token and kv head):
 //   grid = (splits, kv heads, rows); the G = Hq/Hkv query heads of a group share every K/V byte;
-//   a warp owns whole 16-token pages: QK with 2 lanes per token (D/2 dims each, 16-byte loads),
-//   online softmax per warp, PV with lanes over D (coalesced 128-byte rows), probabilities passed
-//   through warp-private shared memory with the V scale folded in;
+//   a warp owns whole 16-token pages and runs both products on the tensor cores (int8 QK^T straight
+//   from the cached bytes, f16 PV), with the online softmax on the accumulator fragments;
 //   the 4 warps merge in shared memory, split partials go to a scratch buffer and the last CTA to
 //   arrive for a (row, kv head) merges the splits in split order (deterministic) and applies the
 //   optional sigmoid output gate of gated attention.
@@ -35,12 +34,44 @@ struct DecParams {
   float scale;
 };
 
+// int8 x int8 -> int32 tensor-core MMA (K rows are int8 already; q is split in two int8 levels)
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Tensor-core formulation.  Per 16-token page and warp:
+//   S[head][token] = Q K^T with the G query heads of the group as MMA rows (8 of 16 rows used), the page's
+//     tokens as two n8 tiles and int8 operands: K bytes go from global memory straight into the B
+//     fragments (lane t of a quad owns 16 contiguous dims of a 64-dim half; A and B use the same
+//     dim -> k-slot mapping, so no shuffling is needed), q is quantised once per CTA to 15 bits as
+//     128*hi + lo with int8 hi / lo and both levels are accumulated in int32;
+//   online softmax on the C fragments (a head's 16 scores live in one quad: 2 shuffles per reduction);
+//   O[head][dim] += P V with P (f16, the token's V scale folded in) reused from the C fragments as the A
+//     operand and V bytes expanded to f16 by byte permutes as 1152 + v; the constant is removed at
+//     the end with the running sum of the rounded P values (exact in fp32).
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p) {
-  constexpr int HD = D / 2;        // dims per lane in the QK phase
-  constexpr int DPL = D / 32;      // dims per lane in the PV phase
-  __shared__ float qs[G][D];
-  __shared__ float ps[kWarps][G][kPage];
+  static_assert(G <= 8 && (D == 64 || D == 128 || D == 256), "unsupported geometry");
+  constexpr int NH = D / 64;       // 64-dim halves of the QK contraction
+  constexpr int DT = D / 8;        // dims per row group g in the PV product = number of n8 tiles
+  constexpr int VW = DT / 4;       // 32-bit words of V per token row and lane
+  __shared__ __align__(16) int8_t q_hi[8][D];
+  __shared__ __align__(16) int8_t q_lo[8][D];
+  __shared__ float q_delta[8];
   __shared__ float sm_ml[kWarps][G][2];
   __shared__ float sm_o[kWarps][G][D];
   __shared__ int s_last;
@@ -48,6 +79,7 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int nsplit = gridDim.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
   const int seq = p.row_seq[row];
   const int len = p.row_pos[row] + 1;
   const int first = (p.window > 0 && len > p.window) ? (len - p.window) : 0;
@@ -58,121 +90,194 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   const int pbeg = page_lo + split * pps;
   const int pend = min(pbeg + pps, page_hi);
 
-  for (int i = tid; i < G * D; i += kThreads) {
-    const int g = i / D, d = i % D;
-    qs[g][d] = __bfloat162float(p.q[(size_t)row * p.ld_q + (size_t)(kvh * G + g) * D + d]) * p.scale;
+  // ---- q -> two int8 levels per head (warp w quantises heads w, w + 4) ----
+  for (int h = warp; h < 8; h += kWarps) {
+    float v[D / 32];
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      v[i] = h < G ? __bfloat162float(p.q[(size_t)row * p.ld_q + (size_t)(kvh * G + h) * D + lane + 32 * i]) * p.scale : 0.f;
+      mx = fmaxf(mx, fabsf(v[i]));
+    }
+    mx = warp_max(mx);
+    const float delta = mx > 0.f ? mx / 16256.f : 1.f;
+    const float inv = 1.f / delta;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const int qi = __float2int_rn(v[i] * inv);
+      const int hi = (qi + 64) >> 7;
+      q_hi[h][lane + 32 * i] = (int8_t)hi;
+      q_lo[h][lane + 32 * i] = (int8_t)(qi - 128 * hi);
+    }
+    if (lane == 0) q_delta[h] = h < G ? delta : 0.f;
   }
   __syncthreads();
-
-  float m[G], l[G], o[G][DPL];
+  uint32_t qa_hi[NH][4], qa_lo[NH][4];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) o[g][d] = 0.f;
+  for (int h = 0; h < NH; ++h) {
+    const uint4 a = *reinterpret_cast<const uint4*>(&q_hi[g][64 * h + 16 * t]);
+    const uint4 b = *reinterpret_cast<const uint4*>(&q_lo[g][64 * h + 16 * t]);
+    qa_hi[h][0] = a.x; qa_hi[h][1] = a.y; qa_hi[h][2] = a.z; qa_hi[h][3] = a.w;
+    qa_lo[h][0] = b.x; qa_lo[h][1] = b.y; qa_lo[h][2] = b.z; qa_lo[h][3] = b.w;
   }
-  const int tok_in_page = lane >> 1, half = lane & 1;
+  const float qd = q_delta[g];
+
+  float m_run = -INFINITY, l_part = 0.f, lv_part = 0.f;   // head g: running max, this lane's share of sum p and of sum f16(p*vs)
+  float o[DT][4];
+#pragma unroll
+  for (int j = 0; j < DT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
 
-  // K of the first page is fetched before the loop; inside, the V rows of the current page and the K
-  // rows of the next page are requested before the QK math so the loads overlap the arithmetic.
-  uint4 kreg[HD / 16];
-  float ksc = 0.f, vsc = 0.f;
+  // ---- per-warp ring of whole pages in shared memory, filled by cp.async STAGES-1 pages ahead ----
+  // stage = K page [16][D] | V page [16][D] | K scales [16] | V scales [16]; 16-byte chunks are XOR-swizzled
+  // so the fragment reads below are bank-conflict free.
+  constexpr int STAGES = (D == 256) ? 3 : 4;
+  constexpr int STAGE_BYTES = 2 * kPage * D + 128;
+  constexpr int CPR = D / 16;                           // 16-byte chunks per token row
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  uint8_t* ring = ring_raw + (size_t)warp * STAGES * STAGE_BYTES;
+  auto k_off = [](int r, int c) { return r * D + 16 * (D >= 128 ? (c ^ (4 * (r & 1))) : c); };
+  auto v_off = [](int r, int c) {
+    const int x = (r >> 1) & 3;
+    const int sw = D == 128 ? 2 * x : (D == 256 ? ((x & 1) | ((x & 2) << 1)) : 0);
+    return kPage * D + r * D + 16 * (c ^ sw);
+  };
+  auto issue = [&](int page, int st) {
+    if (page < pend) {
+      const size_t pb = ((size_t)bt[page] * p.Hkv + kvh) * kPage;
+      const uint32_t sb = smem_u32(ring + st * STAGE_BYTES);
+      const int8_t* ksrc = p.k_pages + pb * D;
+      const int8_t* vsrc = p.v_pages + pb * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) {
+        const int idx = lane + 32 * i, r = idx / CPR, c = idx % CPR;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + k_off(r, c)), "l"(ksrc + 16 * idx) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + v_off(r, c)), "l"(vsrc + 16 * idx) : "memory");
+      }
+      if (lane < 8) {
+        const float* ssrc = (lane < 4 ? p.k_scale : p.v_scale) + pb + 4 * (lane & 3);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + 2 * kPage * D + 16 * lane), "l"(ssrc) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
   int pg = pbeg + warp;
-  if (pg < pend) {
-    const size_t pb = ((size_t)bt[pg] * p.Hkv + kvh) * kPage;
-    const int8_t* kp = p.k_pages + (pb + tok_in_page) * D + half * HD;
 #pragma unroll
-    for (int c = 0; c < HD / 16; ++c) kreg[c] = *reinterpret_cast<const uint4*>(kp + c * 16);
-    ksc = p.k_scale[pb + tok_in_page];
-    vsc = p.v_scale[pb + tok_in_page];
-  }
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) issue(pg + s0 * kWarps, s0);
+  int st = 0;
   for (; pg < pend; pg += kWarps) {
-    const size_t pbase = ((size_t)bt[pg] * p.Hkv + kvh) * kPage;
-    const int tok = pg * kPage + tok_in_page;
-    const bool valid = tok < len && tok >= first;
-    // V rows of this page (lane = 4 dims of every token row)
-    const int8_t* vp = p.v_pages + pbase * D + lane * DPL;
-    uint32_t vraw[kPage][(DPL + 3) / 4];
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncwarp();
+    issue(pg + (STAGES - 1) * kWarps, (st + STAGES - 1) % STAGES);
+    const uint8_t* sb = ring + st * STAGE_BYTES;
+    st = (st + 1 == STAGES) ? 0 : st + 1;
+    uint4 kreg[2][NH];                 // K rows of tokens g and g + 8, this lane's 16 dims per 64-dim half
 #pragma unroll
-    for (int j = 0; j < kPage; ++j) {
-      if (DPL == 4) vraw[j][0] = *reinterpret_cast<const uint32_t*>(vp + j * D);
-      else if (DPL == 8) { const uint2 w8 = *reinterpret_cast<const uint2*>(vp + j * D); vraw[j][0] = w8.x; vraw[j][(DPL + 3) / 4 - 1] = w8.y; }
-      else vraw[j][0] = *reinterpret_cast<const unsigned short*>(vp + j * D);
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int h = 0; h < NH; ++h) kreg[nt][h] = *reinterpret_cast<const uint4*>(sb + k_off(8 * nt + g, 4 * h + t));
+    float2 ksc[2], vsc[2];             // scales of tokens (2t, 2t+1) and (2t+8, 2t+9)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      ksc[nt] = *reinterpret_cast<const float2*>(sb + 2 * kPage * D + 4 * (8 * nt + 2 * t));
+      vsc[nt] = *reinterpret_cast<const float2*>(sb + 2 * kPage * D + 64 + 4 * (8 * nt + 2 * t));
     }
-    uint4 kcur[HD / 16];
+    // V rows 2t, 2t+1, 2t+8, 2t+9: this lane's DT contiguous dims [DT*g, DT*g + DT)
+    uint32_t vraw[4][VW];
 #pragma unroll
-    for (int c = 0; c < HD / 16; ++c) kcur[c] = kreg[c];
-    const float ksc_c = ksc, vsc_c = vsc;
-    if (pg + kWarps < pend) {
-      const size_t pb = ((size_t)bt[pg + kWarps] * p.Hkv + kvh) * kPage;
-      const int8_t* kp = p.k_pages + (pb + tok_in_page) * D + half * HD;
+    for (int r = 0; r < 4; ++r) {
+      const int vr = 2 * t + (r & 1) + 8 * (r >> 1);
+      if (VW == 2) {
+        const uint2 w = *reinterpret_cast<const uint2*>(sb + v_off(vr, g >> 1) + 8 * (g & 1));
+        vraw[r][0] = w.x; vraw[r][VW - 1] = w.y;
+      } else {
 #pragma unroll
-      for (int c = 0; c < HD / 16; ++c) kreg[c] = *reinterpret_cast<const uint4*>(kp + c * 16);
-      ksc = p.k_scale[pb + tok_in_page];
-      vsc = p.v_scale[pb + tok_in_page];
-    }
-    // ---- QK ----
-    float s[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) s[g] = 0.f;
-#pragma unroll
-    for (int c = 0; c < HD / 16; ++c) {
-      const uint32_t wds[4] = {kcur[c].x, kcur[c].y, kcur[c].z, kcur[c].w};
-#pragma unroll
-      for (int wv = 0; wv < 4; ++wv) {
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const float kf = (float)(int8_t)((wds[wv] >> (8 * b)) & 0xff);
-          const int d = half * HD + c * 16 + wv * 4 + b;
-#pragma unroll
-          for (int g = 0; g < G; ++g) s[g] = fmaf(kf, qs[g][d], s[g]);
+        for (int q4 = 0; q4 < VW / 4; ++q4) {
+          const uint4 w = *reinterpret_cast<const uint4*>(sb + v_off(vr, (VW / 4) * g + q4));
+          vraw[r][4 * q4] = w.x; vraw[r][4 * q4 + 1] = w.y; vraw[r][4 * q4 + 2] = w.z; vraw[r][4 * q4 + 3] = w.w;
         }
       }
     }
-    float alpha[G];
+    // ---- S = Q K^T (int8, two levels) ----
+    int s_hi[2][4], s_lo[2][4];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float sg = s[g] + __shfl_xor_sync(0xffffffffu, s[g], 1);
-      sg = valid ? sg * ksc_c : -INFINITY;
-      float mx = sg;
+    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int off = 2; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-      const float mnew = fmaxf(m[g], mx);
-      alpha[g] = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - mnew);
-      const float pr = (sg == -INFINITY) ? 0.f : __expf(sg - mnew);
-      m[g] = mnew;
-      l[g] = l[g] * alpha[g] + (half == 0 ? pr : 0.f);
-      if (half == 0) ps[warp][g][tok_in_page] = valid ? pr * vsc_c : 0.f;
+      for (int c = 0; c < 4; ++c) { s_hi[nt][c] = 0; s_lo[nt][c] = 0; }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int h = 0; h < NH; ++h) {
+        const uint32_t kw[4] = {kreg[nt][h].x, kreg[nt][h].y, kreg[nt][h].z, kreg[nt][h].w};
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          mma_s8_16832(s_hi[nt], qa_hi[h][2 * s], 0u, qa_hi[h][2 * s + 1], 0u, kw[2 * s], kw[2 * s + 1]);
+          mma_s8_16832(s_lo[nt], qa_lo[h][2 * s], 0u, qa_lo[h][2 * s + 1], 0u, kw[2 * s], kw[2 * s + 1]);
+        }
+      }
+    const float2 ksc_c[2] = {ksc[0], ksc[1]}, vsc_c[2] = {vsc[0], vsc[1]};
+    // ---- online softmax for head g over this lane's 4 tokens, quad reductions ----
+    float sc[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int nt = i >> 1, c = i & 1;
+      const int tok = pg * kPage + 8 * nt + 2 * t + c;
+      const float ks = c ? ksc_c[nt].y : ksc_c[nt].x;
+      const float sv = (float)(128 * s_hi[nt][c] + s_lo[nt][c]) * qd * ks;
+      sc[i] = (tok < len && tok >= first) ? sv : -INFINITY;
+      mx = fmaxf(mx, sc[i]);
     }
-    __syncwarp();
-    // ---- PV ----
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mnew = fmaxf(m_run, mx);
+    const float alpha = (m_run == -INFINITY) ? 0.f : __expf(m_run - mnew);
+    m_run = mnew;
+    float pv[4];
+    float psum = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int i = 0; i < 4; ++i) {
+      const float pr = (sc[i] == -INFINITY) ? 0.f : __expf(sc[i] - mnew);
+      psum += pr;
+      pv[i] = pr * ((i & 1) ? vsc_c[i >> 1].y : vsc_c[i >> 1].x) * 1024.f;   // lifted out of the f16 subnormal range
+    }
+    const uint32_t pa0 = pack_f16x2(pv[0], pv[1]), pa2 = pack_f16x2(pv[2], pv[3]);
+    const float2 r0 = __half22float2(*reinterpret_cast<const __half2*>(&pa0));
+    const float2 r2 = __half22float2(*reinterpret_cast<const __half2*>(&pa2));
+    l_part = l_part * alpha + psum;
+    lv_part = lv_part * alpha + (r0.x + r0.y + r2.x + r2.y);
+    // ---- O = alpha O + P V ----
 #pragma unroll
-      for (int d = 0; d < DPL; ++d) o[g][d] *= alpha[g];
+    for (int w = 0; w < VW; ++w) {
+      // bytes of rows (2t, 2t+1) and (2t+8, 2t+9), interleaved per dim, biased to unsigned
+      const uint32_t lo01 = prmt(vraw[0][w], vraw[1][w], 0x5140u) ^ 0x80808080u, hi01 = prmt(vraw[0][w], vraw[1][w], 0x7362u) ^ 0x80808080u;
+      const uint32_t lo89 = prmt(vraw[2][w], vraw[3][w], 0x5140u) ^ 0x80808080u, hi89 = prmt(vraw[2][w], vraw[3][w], 0x7362u) ^ 0x80808080u;
 #pragma unroll
-    for (int j = 0; j < kPage; ++j) {
-      float vf[DPL];
-#pragma unroll
-      for (int d = 0; d < DPL; ++d) vf[d] = (float)(int8_t)((vraw[j][d >> 2] >> (8 * (d & 3))) & 0xff);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pj = ps[warp][g][j];
-#pragma unroll
-        for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(pj, vf[d], o[g][d]);
+      for (int e = 0; e < 4; ++e) {
+        const int j = 4 * w + e;
+        const uint32_t src01 = e < 2 ? lo01 : hi01, src89 = e < 2 ? lo89 : hi89;
+        const uint32_t sel = (e & 1) ? 0x4342u : 0x4140u;
+        const uint32_t b0 = prmt(src01, 0x64646464u, sel), b1 = prmt(src89, 0x64646464u, sel);
+        o[j][0] *= alpha; o[j][1] *= alpha;
+        mma_f16_16816(o[j], pa0, 0u, pa2, 0u, b0, b1);
       }
     }
-    __syncwarp();
   }
 
-  // ---- merge the 4 warps ----
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // ---- this warp's result for head g: quad-reduce the sums, remove the 1152 bias, stage for the CTA merge ----
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
+  l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
+  lv_part += __shfl_xor_sync(0xffffffffu, lv_part, 1);
+  lv_part += __shfl_xor_sync(0xffffffffu, lv_part, 2);
+  if (g < G) {
+    if (t == 0) { sm_ml[warp][g][0] = m_run; sm_ml[warp][g][1] = l_part; }
+    const float bias = 1152.f * lv_part;
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const float lg = warp_sum(l[g]);
-    if (lane == 0) { sm_ml[warp][g][0] = m[g]; sm_ml[warp][g][1] = lg; }
-#pragma unroll
-    for (int d = 0; d < DPL; ++d) sm_o[warp][g][lane * DPL + d] = o[g][d];
+    for (int j = 0; j < DT; ++j) {
+      sm_o[warp][g][DT * (2 * t) + j] = (o[j][0] - bias) * (1.f / 1024.f);
+      sm_o[warp][g][DT * (2 * t + 1) + j] = (o[j][1] - bias) * (1.f / 1024.f);
+    }
   }
   __syncthreads();
 
@@ -234,23 +339,40 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     sm_ml[0][tid][0] = L;
   }
   __syncthreads();
-  for (int i = tid; i < G * D; i += kThreads) {
-    const int g = i / D, d = i % D;
-    float O = 0.f;
-#pragma unroll 8
-    for (int sp = 0; sp < nsplit; ++sp) O = fmaf(__ldcg(&p.part_o[((base + sp) * G + g) * D + d]), wts[g * kMaxSplits + sp], O);
+  for (int i = tid; i < G * D / 4; i += kThreads) {
+    const int g = i / (D / 4), d = 4 * (i % (D / 4));
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 16
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(&p.part_o[((base + sp) * G + g) * D + d]));
+      const float w = wts[g * kMaxSplits + sp];
+      O.x = fmaf(v.x, w, O.x); O.y = fmaf(v.y, w, O.y); O.z = fmaf(v.z, w, O.z); O.w = fmaf(v.w, w, O.w);
+    }
     const float L = sm_ml[0][g][0];
-    float r = L > 0.f ? O / L : 0.f;
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float r[4] = {O.x * inv, O.y * inv, O.z * inv, O.w * inv};
     const size_t oi = (size_t)row * p.ld_o + (size_t)(kvh * G + g) * D + d;
-    if (p.gate) r *= sigmoid_f(__bfloat162float(p.gate[oi]));
-    p.out[oi] = __float2bfloat16(r);
+    if (p.gate) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) r[c] *= sigmoid_f(__bfloat162float(p.gate[oi + c]));
+    }
+    uint2 o2;
+    o2.x = pack_bf16x2(r[0], r[1]); o2.y = pack_bf16x2(r[2], r[3]);
+    *reinterpret_cast<uint2*>(p.out + oi) = o2;
   }
 }
 
 template <int D, int G>
 int launch(const DecParams& p, int splits, cudaStream_t st) {
   dim3 grid(splits, p.Hkv, p.M);
-  decode_attn_kernel<D, G><<<grid, kThreads, 0, st>>>(p);
+  constexpr int kRing = kWarps * ((D == 256) ? 3 : 4) * (2 * kPage * D + 128);
+  static bool configured = false;      // per template instance; setting the attribute twice is harmless
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  decode_attn_kernel<D, G><<<grid, kThreads, kRing, st>>>(p);
   GRM_LAUNCH_RET();
 }
 
@@ -276,7 +398,7 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
                                   const void* v_scale, const void* gate, void* out, int ld_o, void* part_o, void* part_ml,
                                   void* counters, int M, int Hq, int Hkv, int D, int splits, int window, float scale,
                                   void* stream) {
-  if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1 || splits > kMaxSplits) return -2;
+  if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1 || splits > kMaxSplits || (ld_o & 3)) return -2;
   if (splits > 1 && (!part_o || !part_ml || !counters)) return -2;
   DecParams p;
   p.q = (const bf16*)q; p.ld_q = ld_q; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos;
