@@ -1,6 +1,7 @@
 """Per-kernel micro-benchmarks on the 27B projection / attention shapes.
 
     python -m grimoire_b200.bench.kernels smallm  --rows 1        # int4 small-M (decode GEMV family)
+    python -m grimoire_b200.bench.kernels mx      --rows 1        # MXFP4 small-M
     python -m grimoire_b200.bench.kernels gemm    --rows 4096     # tcgen05 GEMM on the prefill shapes
     python -m grimoire_b200.bench.kernels attn    --ctx 4096      # paged int8 decode attention
     python -m grimoire_b200.bench.kernels prefill --rows 4096     # flash prefill attention
@@ -84,6 +85,32 @@ def bench_smallm(args) -> None:
               f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
 
 
+def bench_mx(args) -> None:
+    """MXFP4 small-M kernel on the same shapes (bytes = packed e2m1 + e8m0 scales)."""
+    from ..formats.codecs import Fmt
+    from ..formats.quantize import QuantWeight
+    from ..ops.linear import MXLinear
+
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        nbytes = N * K_ // 2 + N * K_ // 32
+        copies = max(2, int(L2_BYTES * 2 // nbytes) + 1)
+        lins = []
+        for _ in range(copies):
+            qw = QuantWeight(Fmt.MXFP4, N, K_, torch.randint(0, 256, (N, K_ // 2), dtype=torch.uint8),
+                             scales=torch.full((N, K_ // 32), 120, dtype=torch.uint8), group=32)
+            lins.append(MXLinear(qw, dev, name, swiglu=sw))
+        x = torch.randn(args.rows, K_, device=dev).bfloat16()
+        out = torch.zeros(args.rows, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        us = timed(lambda i: lins[i % copies](x, out, epi), args.iters)
+        gbs = nbytes / 1e9 / (us * 1e-6)
+        print(f"smallm_mx {name:8s} M={args.rows:2d} N={N:6d} K={K_:6d} copies={copies:2d}  {us:8.2f} us  {gbs:7.0f} GB/s  "
+              f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
+
+
 def bench_gemm(args) -> None:
     _, tf, tag = peaks()
     dev = "cuda"
@@ -154,14 +181,14 @@ def bench_prefill(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["smallm", "gemm", "attn", "prefill"])
+    ap.add_argument("what", choices=["smallm", "mx", "gemm", "attn", "prefill"])
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--splits", type=int, default=0, help="attn: split-KV factor (0 = the engine's heuristic)")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
-    {"smallm": bench_smallm, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
+    {"smallm": bench_smallm, "mx": bench_mx, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
     print(f"launches={_native.launch_count}", flush=True)
 
 

@@ -27,6 +27,7 @@ class EngineLimits:
     prefill_chunk: int = 4096        # GRIMOIRE_PREFILL_CHUNK
     max_decode_rows: int = 64        # rows of one batched decode / verify step
     kv_pages: int = 0                # 0 = max_slots * max_ctx / 16
+    extra_kv_layers: int = 0         # KV layers beyond the model's own (1 for an MTP draft head)
 
 
 class Engine:
@@ -36,7 +37,8 @@ class Engine:
         self.device = model.device
         self.limits = limits or EngineLimits()
         lim = self.limits
-        n_attn = getattr(model, "kv_layer_count", len(model.layers))   # attention layers of this pipeline stage
+        n_attn = getattr(model, "kv_layer_count", len(model.layers)) + lim.extra_kv_layers   # attention layers of this stage
+        self.mtp = None                  # models.mtp.MtpDrafter attaches itself here
         pages = lim.kv_pages or (lim.max_slots * ((lim.max_ctx + PAGE - 1) // PAGE))
         self.kv = KvPool(n_attn, model.geom.Hkv, model.geom.D, pages, lim.max_slots, lim.max_ctx, self.device)
         chunk = min(lim.prefill_chunk, lim.max_ctx)
@@ -124,6 +126,8 @@ class Engine:
                           mode="prefill", q_pos0=pos0, seq_slot=seq.slot,
                           logits_rows=torch.tensor([m - 1], device=self.device))
             out = self.model.forward(rb, self.prefill_buf, self.kv.layers, self.kv.table)
+            if self.mtp is not None:
+                self.mtp.warm_chunk(seq, tok_dev, done, m, pos0, self.prefill_buf, last=(done + m == n))
             seq.length += m
             done += m
             self.counters["prefill_rows"] += m

@@ -153,6 +153,8 @@ def generate_tokens(engine: EngineLike, prompt: Sequence[int], opts: GenerationO
             if not drafts:
                 nxt = engine.decode_rows([tok], [seq], [pos], use_graph=opts.use_graph)
                 engine.commit_rows([seq], [tok], [pos])
+                if opts.drafter is not None:
+                    opts.drafter.observe(engine, seq, [tok])      # a model drafter tracks the newest hidden state
                 tok = int(nxt[0])
                 continue
             # ---- verify: block [tok, d1..dK] as K+1 rows of this conversation ----

@@ -120,4 +120,4 @@ def interleave_gate_up_q(gate: QuantWeight, up: QuantWeight) -> QuantWeight:
     """Quantized version of ``interleave_gate_up`` (rows permuted, codes untouched)."""
     return QuantWeight(gate.fmt, gate.N * 2, gate.K, interleave_gate_up(gate.payload, up.payload),
                        scales=interleave_gate_up(gate.scales, up.scales),
-                       zeros=interleave_gate_up(gate.zeros, up.zeros), group=gate.group)
+                       zeros=None if gate.zeros is None else interleave_gate_up(gate.zeros, up.zeros), group=gate.group)

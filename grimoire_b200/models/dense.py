@@ -23,7 +23,7 @@ from ..formats.quantize import QuantWeight, quantize, slice_cols, slice_rows
 from ..formats.w4_tile_layout import concat_rows, interleave_gate_up_q
 from ..ops import core as K
 from ..ops import ref
-from ..ops.linear import BF16Linear, W4Linear
+from ..ops.linear import BF16Linear, MXLinear, W4Linear
 from ..ops.workspace import Workspace
 from ..utils import trace
 from .config import ModelConfig
@@ -117,9 +117,18 @@ class DenseModel:
     def _quant(self, w) -> QuantWeight:
         """fp32 tensor or stored QuantWeight -> runtime int4 (stored int4 is used as is)."""
         cfg = self.cfg
+        if cfg.quant == "mxfp4":
+            if isinstance(w, QuantWeight):
+                return w if w.fmt == Fmt.MXFP4 else quantize(w.dequant(), Fmt.MXFP4)
+            return quantize(w, Fmt.MXFP4)
         if isinstance(w, QuantWeight):
             return w if w.fmt == Fmt.INT4 else quantize(w.dequant(), Fmt.INT4, group=cfg.quant_group)
         return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
+
+    def _linear(self, qw: QuantWeight, name: str, swiglu: bool = False):
+        """Runtime projection for a quantized weight: int4 -> W4Linear, MXFP4 -> MXLinear."""
+        cls = MXLinear if qw.fmt == Fmt.MXFP4 else W4Linear
+        return cls(qw, self.device, name, swiglu=swiglu, workspace=self.ws)
 
     @staticmethod
     def _rows(w, a: int, b: int):
@@ -153,10 +162,10 @@ class DenseModel:
         i = len(self.layers)
         self.layers.append(DenseLayer(
             f32(in_norm), f32(post_norm),
-            W4Linear(qkv, dev, f"L{i}.qkv", workspace=self.ws),
-            W4Linear(self._quant(wo_s), dev, f"L{i}.o", workspace=self.ws),
-            W4Linear(gu, dev, f"L{i}.gate_up", swiglu=True, workspace=self.ws),
-            W4Linear(self._quant(wd_s), dev, f"L{i}.down", workspace=self.ws),
+            self._linear(qkv, f"L{i}.qkv"),
+            self._linear(self._quant(wo_s), f"L{i}.o"),
+            self._linear(gu, f"L{i}.gate_up", swiglu=True),
+            self._linear(self._quant(wd_s), f"L{i}.down"),
             f32(q_norm), f32(k_norm)))
 
     def set_embeddings(self, embed: torch.Tensor, final_norm: torch.Tensor, lm_head: Optional[torch.Tensor]):
@@ -167,7 +176,7 @@ class DenseModel:
             # tied: the head aliases the embedding table and is never quantized (grimoire.cpp:3492-3495)
             self.lm_head = BF16Linear(self.embed, dev, "lm_head(tied)")
         else:
-            self.lm_head = W4Linear(self._quant(lm_head), dev, "lm_head", workspace=self.ws)
+            self.lm_head = self._linear(self._quant(lm_head), "lm_head")
 
     @staticmethod
     def random(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, std: float = 0.02,

@@ -15,6 +15,7 @@ from typing import Optional
 import torch
 
 from .. import _native
+from ..formats.codecs import Fmt
 from ..formats.quantize import QuantWeight
 from ..formats.w4_tile_layout import W4Tiled, tile_w4
 from .workspace import Workspace, default_workspace
@@ -194,3 +195,56 @@ def w4_dequant_into(lin: "W4Linear") -> torch.Tensor:
                                          _c(t.K), _native.stream_ptr())
     _native.check(code, f"dequant_w4 {lin.name}")
     return wbuf[: lin.N]
+
+
+class MXLinear:
+    """MXFP4 ``[N][K]`` projection (e2m1 in blocks of 32 with an e8m0 scale), weights in the
+    checkpoint's natural layout.  1..64 rows run the hand-written small-M kernel in passes of 8 rows
+    (smallm_mx.cu); taller inputs dequantise once into a bf16 scratch and use the tcgen05 GEMM --
+    the reference's policy for its MXFP4 path as well (gemv_mxfp4 for decode, dequant + oneDNN for
+    prefill, src/kernels.hpp:163-169, src/gemm_fast.cpp:26-31).  ``swiglu`` weights are gate/up
+    interleaved per 16 rows like the int4 ones."""
+
+    def __init__(self, qw: QuantWeight, device, name: str = "", swiglu: bool = False, workspace: Optional[Workspace] = None):
+        if qw.fmt != Fmt.MXFP4:
+            raise ValueError("MXLinear needs an MXFP4 weight")
+        self.name, self.N, self.K, self.swiglu = name, qw.N, qw.K, swiglu
+        self.device = torch.device(device)
+        self.ws = workspace or default_workspace(device)
+        self.tiled = None
+        self.out_features = self.N // 2 if swiglu else self.N
+        if self.device.type == "cuda":
+            self.w = qw.payload.to(self.device).contiguous()
+            self.s = qw.scales.to(self.device).contiguous()
+            self.w_ref = None
+        else:
+            self.w = self.s = None
+            self.w_ref = qw.dequant()
+
+    def nbytes(self) -> int:
+        return (self.w.numel() + self.s.numel()) if self.w is not None else self.w_ref.numel() * 4
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
+        M = x.shape[0]
+        if self.swiglu and epi != "swiglu":
+            raise ValueError("a gate|up interleaved weight must run with the swiglu epilogue")
+        if self.device.type != "cuda":
+            return W4Linear._forward_ref(self, x, out, epi)
+        lib = _native.cuda()
+        if M <= SMALLM_MAX:
+            ld16 = (self.K + 7) // 8 * 8
+            x16 = self.ws.get("mx_x16", 8 * ld16, torch.float16)
+            code_epi = {"bf16": 0, "f32": 1, "add_f32": 2, "swiglu": 3}[epi]
+            for m0 in range(0, M, 8):
+                m = min(8, M - m0)
+                code = lib.grm_smallm_mx(_native.ptr(self.w), _native.ptr(self.s), _native.ptr(x[m0: m0 + m]), _c(x.stride(0)),
+                                         _native.ptr(x16), _c(ld16), _native.ptr(out[m0: m0 + m]), _c(out.stride(0)), _c(m), _c(self.N),
+                                         _c(self.K), _c(code_epi), _native.stream_ptr())
+                _native.check(code, f"smallm_mx {self.name} M={m} N={self.N} K={self.K}")
+            return out
+        wbuf = self.ws.get("dequant_bf16", self.N * self.K, torch.bfloat16).view(-1)[: self.N * self.K].view(self.N, self.K)
+        _native.check(lib.grm_dequant_mxfp4(_native.ptr(self.w), _native.ptr(self.s), _native.ptr(wbuf), _c(self.N), _c(self.K),
+                                            _native.stream_ptr()), f"dequant_mxfp4 {self.name}")
+        return gemm_bf16(x, wbuf, out, epi)
+
+    __call__ = forward
