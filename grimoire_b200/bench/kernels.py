@@ -6,7 +6,7 @@
     python -m grimoire_b200.bench.kernels attn    --ctx 4096      # paged int8 decode attention
     python -m grimoire_b200.bench.kernels prefill --rows 4096     # flash prefill attention
 
-Timing: CUDA events on the launching stream after warm-up, synchronised on both sides.  Every case
+Timing: CUDA events around a CUDA-graph replay of the iterations, after warm-up, synchronised on both sides.  Every case
 cycles through enough operand copies that the bytes touched between two uses of the same copy
 exceed the 126 MB L2, so DRAM figures are cold-cache.  Fractions are quoted against the measured
 copy bandwidth / cuBLAS bf16 throughput in MEASURED_PEAKS.json at the repository root when present,
@@ -43,14 +43,25 @@ def peaks():
 
 
 def timed(fn, iters: int, warmup: int = 5) -> float:
-    """Mean microseconds per call of ``fn(i)``."""
+    """Mean microseconds per call of ``fn(i)``.  The ``iters`` calls are captured into one CUDA graph and
+    the replay is timed, so the figure is device time back to back without host launch gaps (the way
+    the engine runs these kernels in its decode graph)."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(iters):
+                fn(i)
+    torch.cuda.synchronize()
+    g.replay()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(iters):
-        fn(i)
+    g.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1000.0 / iters

@@ -24,6 +24,8 @@
 //         (a lane's 16 columns of a k tile are contiguous, so its activation fragment is two 16-byte reads)
 //   sz  : [N/16][K/group][16] uint32: low 16 bits = fp16 scale, high 16 bits = bf16(128 + zero)
 #include "common.cuh"
+#include <type_traits>
+#include <cstdlib>
 
 namespace {
 
@@ -52,6 +54,14 @@ struct W4Params {
   unsigned int* status;     // device status block (timeouts)
   int ar_world, ar_rank;
   unsigned int ar_spin;     // poll limit of the arrival wait
+  // ---- integer activation path (I8 kernels): x carried as two int8 levels per quantisation group ----
+  const int8_t* xq_hi;      // [M][ldq] high level  (x ~ delta * (128*hi + lo)), columns permuted (0,2,1,3) within 4
+  const int8_t* xq_lo;      // [M][ldq] low level
+  const float2* xtab;       // [M][ldtab] per (row, group): {delta, delta * sum_k(128*hi + lo)}
+  int ldq, ldtab;
+  // ---- warp layout inside a CTA: rt row super-tiles x ks K slices, rt * ks == kWarps ----
+  int rt, ks, ntiles;
+  int min_ctas;             // smallest grid the row-tile grouping may produce (GRIMOIRE_SMALLM_MIN_CTAS, default 222 = 1.5 per SM)
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
@@ -67,6 +77,10 @@ __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint3
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
   return r;
+}
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -99,19 +113,40 @@ __device__ __forceinline__ void epilogue_store(const W4Params& p, int tile, int 
 }
 
 // Ring depth (stages of R*512 weight bytes in flight per warp) by batch width.
-template <int MT> struct RingDepth { static constexpr int v = MT <= 2 ? 8 : 4; };
+// A ring stage holds kSK consecutive k tiles (one bulk copy of kSK KiB when R == 2: requests of a few KiB
+// keep the copy engine's request rate off the critical path); two stages per warp are in flight.
+template <int MT> struct RingDepth { static constexpr int v = 2; };
+constexpr int kSK = 4;
 
 // slow path of the stage wait, kept out of line so the hot loop carries only one try_wait
 __device__ __noinline__ bool stage_wait_slow(uint64_t* bar, uint32_t parity, unsigned int* status, uint32_t tag) {
   return mbar_wait(bar, parity, status, tag);
 }
 
-template <int MT, int R, int EPI>
+// One ring stage <- k tiles [kt, min(kt + kSK, kt1)) of the warp's weight stream (issued by one lane).
+template <int R>
+__device__ __forceinline__ void fill_stage(uint8_t* dst, const uint8_t* wsrc, int kt, int kt1, uint64_t* bar) {
+  const int n = min(kSK, kt1 - kt);
+  if (n <= 0) return;
+  mbar_expect_tx(bar, (uint32_t)n * R * 512u);
+  if (R == 2) {
+    bulk_load(dst, wsrc + (size_t)kt * 1024, (uint32_t)n * 1024u, bar);
+  } else {
+    for (int i = 0; i < n; ++i) bulk_load(dst + i * 512, wsrc + (size_t)(kt + i) * 1024, 512u, bar);
+  }
+}
+
+// I8 = true: the products run on the int8 tensor-core path.  The activations arrive quantised per weight
+// group to 15 bits as two int8 levels (grm_quant_x_i8), a weight word splits into the int8 A fragments of
+// rows g and g+8 with three logic ops (even nibbles / odd nibbles), group sums are exact int32 and the
+// zero point is removed with the group's pre-computed activation sum -- about a third of the ALU work
+// of the bf16 path, with a smaller activation rounding error than bf16 inputs have.
+template <int MT, int R, int EPI, bool I8>
 __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
   // dynamic shared memory: [kWarps][RING][R*512] weight ring | [kWarps][R*MT*4][32] reduce | barriers | scales
   extern __shared__ __align__(128) uint8_t smem_dyn[];
   constexpr int RING = RingDepth<MT>::v;
-  constexpr int kStage = R * 512;
+  constexpr int kStage = kSK * R * 512;
   constexpr int NVc = R * MT * 4 * 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* ring = smem_dyn + warp * (RING * kStage);
@@ -122,14 +157,20 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
                   (size_t)warp * R * p.szg * 16;
   __shared__ int s_last;
   const int g = lane >> 2, t = lane & 3;
-  const int tile = blockIdx.x;          // super-tile of R row tiles
+  // The CTA's 8 warps cover rt row super-tiles (of R row tiles each) x ks K slices.  Few, long-lived
+  // CTAs with long per-warp weight streams keep HBM busy: the fixed start-up (scale staging, first
+  // ring fill) and the reduction tail are paid once per 8 * (K / ks) tiles of work instead of once per
+  // (K / 8) tiles.
+  const int wr = warp / p.ks, wk = warp - wr * p.ks;
+  const int tile = blockIdx.x * p.rt + wr;   // super-tile of R row tiles owned by this warp
+  const bool live = tile < p.ntiles;
   const int KT = p.K >> 6;              // k tiles of 64
   const int G = KT / p.g64;             // groups per row
   // K range of this CTA, then of this warp; both aligned to group boundaries
   const int cta_groups = G / p.ksplit;
   const int gbeg_cta = blockIdx.y * cta_groups;
-  const int per_warp = (cta_groups + kWarps - 1) / kWarps;
-  const int gbeg = gbeg_cta + warp * per_warp;
+  const int per_warp = (cta_groups + p.ks - 1) / p.ks;
+  const int gbeg = gbeg_cta + wk * per_warp;
   const int gend = min(gbeg + per_warp, gbeg_cta + cta_groups);
 
   float acc[R][MT][4];
@@ -140,7 +181,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[r][mt][c] = 0.f;
 
-  if (gbeg < gend) {
+  if (live && gbeg < gend) {
     const int kt0 = gbeg * p.g64, kt1 = gend * p.g64;
     // The weight stream of this warp: k tile kt of its row tile(s) is R*512 contiguous bytes, and
     // consecutive k tiles are 1 KiB apart.  R == 2: both halves of super-tile `tile`; R == 1: one half.
@@ -158,14 +199,137 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 #pragma unroll
       for (int r = 0; r < R; ++r)
         bulk_load(szs + (size_t)r * p.szg * 16, p.sz + ((size_t)(tile * R + r) * G + gbeg) * 16, szbytes, &bars[RING]);
-      const int pre = min(kt1 - kt0, RING);
-      for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&bars[i], kStage);
-        bulk_load(ring + i * kStage, wsrc + (size_t)(kt0 + i) * 1024, kStage, &bars[i]);
-      }
+      for (int i = 0; i < RING; ++i) fill_stage<R>(ring + i * kStage, wsrc, kt0 + i * kSK, kt1, &bars[i]);
     }
     __syncwarp();
 
+    if constexpr (I8) {
+      // int8 activation fragments: lane (g, t) reads the 16 bytes [64 kt + 16 t, +16) of row 8*mt+g per level
+      const uint4* xh[MT];
+      const uint4* xl[MT];
+      bool xok[MT];
+      uint4 xhv[MT], xlv[MT];
+      const float2* tab0[MT];
+      const float2* tab1[MT];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int m = mt * 8 + g;
+        xok[mt] = m < p.M;
+        const size_t ro = (size_t)(xok[mt] ? m : 0) * p.ldq + (size_t)kt0 * 64 + t * 16;
+        xh[mt] = reinterpret_cast<const uint4*>(p.xq_hi + ro);
+        xl[mt] = reinterpret_cast<const uint4*>(p.xq_lo + ro);
+        xhv[mt] = xlv[mt] = make_uint4(0u, 0u, 0u, 0u);
+        if (xok[mt]) { xhv[mt] = __ldg(xh[mt]); xlv[mt] = __ldg(xl[mt]); }
+        tab0[mt] = p.xtab + (size_t)min(mt * 8 + 2 * t, p.M - 1) * p.ldtab;
+        tab1[mt] = p.xtab + (size_t)min(mt * 8 + 2 * t + 1, p.M - 1) * p.ldtab;
+      }
+      // Main loop, one ring stage (kSK k tiles) per iteration, fully unrolled inside: constant shared-memory
+      // offsets, no per-tile loop control, one barrier wait and one refill per stage.
+      static_assert(RING == 2, "the stage toggle below assumes two ring stages");
+      auto run = [&](auto g64c) {
+        constexpr int G64 = decltype(g64c)::value;       // k tiles per quantisation group (1, 2 or 4)
+        constexpr int GPS = kSK / G64;                   // groups per full stage
+        uint32_t stg = 0, phase = 0;
+        bool dead = !mbar_wait(&bars[RING], 0u, p.status, 0x5ffu);
+        const uint32_t* szp = szs + g;
+        int grp = gbeg;
+#pragma unroll 1
+        for (int kt = kt0; kt < kt1 && !dead; kt += kSK, grp += GPS, szp += 16 * GPS) {
+          const int nt = min(kSK, kt1 - kt);
+          if (!mbar_try_wait(&bars[stg], phase)) {
+            if (!stage_wait_slow(&bars[stg], phase, p.status, 0x500u | stg)) { dead = true; break; }
+          }
+          const uint8_t* sbase = ring + stg * kStage + lane * 16;
+          float2 ta[GPS][MT], tb[GPS][MT];
+#pragma unroll
+          for (int gi = 0; gi < GPS; ++gi)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const int gq = min(grp + gi, gend - 1);
+              ta[gi][mt] = __ldg(tab0[mt] + gq); tb[gi][mt] = __ldg(tab1[mt] + gq);
+            }
+          int sh[R][MT][4], sl[R][MT][4];
+#pragma unroll
+          for (int s = 0; s < kSK; ++s) {
+            if (s < nt) {
+              if (s % G64 == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) { sh[r][mt][c] = 0; sl[r][mt][c] = 0; }
+              }
+              uint4 wuse[R];
+#pragma unroll
+              for (int r = 0; r < R; ++r) wuse[r] = *reinterpret_cast<const uint4*>(sbase + s * (R * 512) + r * 512);
+              uint32_t bh[MT][4], bl[MT][4];
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                bh[mt][0] = xhv[mt].x; bh[mt][1] = xhv[mt].y; bh[mt][2] = xhv[mt].z; bh[mt][3] = xhv[mt].w;
+                bl[mt][0] = xlv[mt].x; bl[mt][1] = xlv[mt].y; bl[mt][2] = xlv[mt].z; bl[mt][3] = xlv[mt].w;
+              }
+              if (s == nt - 1) {
+                __syncwarp();   // every lane has read the stage: it may be refilled
+                if (lane == 0) fill_stage<R>(ring + stg * kStage, wsrc, kt + RING * kSK, kt1, &bars[stg]);
+              }
+              if (kt + s + 1 < kt1) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                  if (xok[mt]) { xhv[mt] = __ldg(xh[mt] + 4 * (s + 1)); xlv[mt] = __ldg(xl[mt] + 4 * (s + 1)); }
+              }
+#pragma unroll
+              for (int s2 = 0; s2 < 2; ++s2) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                  const uint32_t u0 = s2 == 0 ? wuse[r].x : wuse[r].z, u1 = s2 == 0 ? wuse[r].y : wuse[r].w;
+                  const uint32_t a0 = u0 & 0x0f0f0f0fu, a1 = (u0 >> 4) & 0x0f0f0f0fu;
+                  const uint32_t a2 = u1 & 0x0f0f0f0fu, a3 = (u1 >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt) {
+                    mma_s8_16832(sh[r][mt], a0, a1, a2, a3, bh[mt][2 * s2], bh[mt][2 * s2 + 1]);
+                    mma_s8_16832(sl[r][mt], a0, a1, a2, a3, bl[mt][2 * s2], bl[mt][2 * s2 + 1]);
+                  }
+                }
+              }
+              if ((s + 1) % G64 == 0) {
+                // group flush: sum_k (q - z) x = delta * S - z * (delta * X), then the fp16 weight scale
+                const int gi = s / G64;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                  const uint32_t s0 = szp[gi * 16 + r * p.szg * 16], s1 = szp[gi * 16 + r * p.szg * 16 + 8];
+                  const float sc0 = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
+                  const float sc1 = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
+                  const float z0 = bf16hi_to_f(s0) - 128.f, z1 = bf16hi_to_f(s1) - 128.f;
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt) {
+                    const float v0 = (float)(128 * sh[r][mt][0] + sl[r][mt][0]), v1 = (float)(128 * sh[r][mt][1] + sl[r][mt][1]);
+                    const float v2 = (float)(128 * sh[r][mt][2] + sl[r][mt][2]), v3 = (float)(128 * sh[r][mt][3] + sl[r][mt][3]);
+                    acc[r][mt][0] = fmaf(sc0, fmaf(v0, ta[gi][mt].x, -z0 * ta[gi][mt].y), acc[r][mt][0]);
+                    acc[r][mt][1] = fmaf(sc0, fmaf(v1, tb[gi][mt].x, -z0 * tb[gi][mt].y), acc[r][mt][1]);
+                    acc[r][mt][2] = fmaf(sc1, fmaf(v2, ta[gi][mt].x, -z1 * ta[gi][mt].y), acc[r][mt][2]);
+                    acc[r][mt][3] = fmaf(sc1, fmaf(v3, tb[gi][mt].x, -z1 * tb[gi][mt].y), acc[r][mt][3]);
+                  }
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            xh[mt] += 4 * kSK; xl[mt] += 4 * kSK;
+            if (xok[mt] && t == 0 && kt + 3 * kSK < kt1) {
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(xh[mt] + 4 * kSK)); asm volatile("prefetch.global.L1 [%0];" ::"l"(xh[mt] + 4 * kSK + 8));
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(xl[mt] + 4 * kSK)); asm volatile("prefetch.global.L1 [%0];" ::"l"(xl[mt] + 4 * kSK + 8));
+            }
+          }
+          stg ^= 1u;
+          phase ^= (stg == 0u);
+        }
+      };
+      if (p.g64 == 1) run(std::integral_constant<int, 1>{});
+      else if (p.g64 == 2) run(std::integral_constant<int, 2>{});
+      else run(std::integral_constant<int, 4>{});
+    } else {
     // Activation fragments: lane (g, t) owns columns 16t..16t+15 of batch row 8*mt+g in every k tile
     // (the weight tiles use the same K order), i.e. two 16-byte loads per k tile, fetched one k tile
     // ahead into registers; the L1 line of a later k tile is requested with a prefetch.
@@ -183,6 +347,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
     constexpr int kAhead = 4;   // k tiles of L1 prefetch distance (one 128-byte line per row and k tile)
 
     uint32_t stg = 0, phase = 0;
+    int sub = 0;
     bool dead = !mbar_wait(&bars[RING], 0u, p.status, 0x5ffu);
     const uint32_t* szp = szs + g;
     const uint32_t ones = 0x3f803f80u;   // bf16 {1, 1}
@@ -211,12 +376,13 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       }
 #pragma unroll 1
       for (int kk = 0; kk < p.g64; ++kk, ++kt) {
-        if (!mbar_try_wait(&bars[stg], phase)) {
+        if (sub == 0 && !mbar_try_wait(&bars[stg], phase)) {
           if (!stage_wait_slow(&bars[stg], phase, p.status, 0x500u | stg)) { dead = true; break; }
         }
         uint4 wuse[R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStage + r * 512 + lane * 16);
+        for (int r = 0; r < R; ++r)
+          wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStage + sub * (R * 512) + r * 512 + lane * 16);
         uint32_t b[MT][8];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -224,10 +390,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
           b[mt][4] = xb[mt].x; b[mt][5] = xb[mt].y; b[mt][6] = xb[mt].z; b[mt][7] = xb[mt].w;
         }
         __syncwarp();   // every lane has its weight words in registers: the stage may be refilled
-        if (lane == 0 && kt + RING < kt1) {
-          mbar_expect_tx(&bars[stg], kStage);
-          bulk_load(ring + stg * kStage, wsrc + (size_t)(kt + RING) * 1024, kStage, &bars[stg]);
-        }
+        if (lane == 0 && (sub == kSK - 1 || kt + 1 == kt1)) fill_stage<R>(ring + stg * kStage, wsrc, kt - sub + RING * kSK, kt1, &bars[stg]);
         if (kt + 1 < kt1) {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
@@ -256,8 +419,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
             for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(accg[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
           }
         }
-        stg = (stg + 1) & (RING - 1);
-        phase ^= (stg == 0);
+        if (++sub == kSK) { sub = 0; stg = (stg + 1) & (RING - 1); phase ^= (stg == 0); }
       }
 #pragma unroll
       for (int r = 0; r < R; ++r)
@@ -269,6 +431,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
           acc[r][mt][3] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][3], accg[r][mt][3]), acc[r][mt][3]);
         }
     }
+    }   // bf16 path
   }
 
   // ---- reduce the K slices of the 8 warps (fixed order) -----------------------------------------
@@ -330,18 +493,20 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
   if (p.ksplit == 1) {
     if (EPI == EPI_SWIGLU) {
       constexpr int NH = NV / 2;  // r = 0 half holds the gate rows, r = 1 the up rows
-      for (int v = tid; v < NH; v += kThreads) {
+      for (int i = tid; i < p.rt * NH; i += kThreads) {
+        const int w0 = i / NH, v = i - w0 * NH, tl = blockIdx.x * p.rt + w0;
+        if (tl >= p.ntiles) continue;
         float sg = 0.f, su = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) { sg += red[w * NV + v]; su += red[w * NV + NH + v]; }
-        epilogue_store<MT, R, EPI>(p, tile, v, sg, su);
+        for (int k = 0; k < p.ks; ++k) { sg += red[(w0 * p.ks + k) * NV + v]; su += red[(w0 * p.ks + k) * NV + NH + v]; }
+        epilogue_store<MT, R, EPI>(p, tl, v, sg, su);
       }
     } else {
-      for (int v = tid; v < NV; v += kThreads) {
+      for (int i = tid; i < p.rt * NV; i += kThreads) {
+        const int w0 = i / NV, v = i - w0 * NV, tl = blockIdx.x * p.rt + w0;
+        if (tl >= p.ntiles) continue;
         float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) s += red[w * NV + v];
-        epilogue_store<MT, R, EPI>(p, tile, v, s, 0.f);
+        for (int k = 0; k < p.ks; ++k) s += red[(w0 * p.ks + k) * NV + v];
+        epilogue_store<MT, R, EPI>(p, tl, v, s, 0.f);
       }
     }
     return;
@@ -384,14 +549,33 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
   }
 }
 
-template <int MT, int R, int EPI>
-int launch(const W4Params& p_in, cudaStream_t st) {
+static int grm_smallm_min_ctas() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("GRIMOIRE_SMALLM_MIN_CTAS"); v = e ? atoi(e) : 222; if (v < 1) v = 222; }
+  return v;
+}
+
+template <int MT, int R, int EPI, bool I8>
+int launch_i(const W4Params& p_in, cudaStream_t st) {
   constexpr int NV = R * MT * 4 * 32;
   constexpr int RING = RingDepth<MT>::v;
   const W4Params& p = p_in;
-  const size_t smem = (size_t)kWarps * RING * R * 512 + (size_t)kWarps * NV * sizeof(float) +
-                      (size_t)kWarps * (RING + 1) * 8 + (size_t)kWarps * R * p.szg * 64;
-  auto kfn = smallm_w4_kernel<MT, R, EPI>;
+  W4Params q = p;
+  q.ntiles = p.N / (16 * R);
+  q.rt = 1;
+  if (EPI != EPI_AR_ADD && p.ksplit == 1) {
+    // as many row super-tiles per CTA as still leave one full wave of CTAs on 148 SMs
+    while (q.rt < kWarps && q.ntiles / (q.rt * 2) >= p.min_ctas) q.rt *= 2;
+  }
+  q.ks = kWarps / q.rt;
+  {
+    const int G = (p.K >> 6) / p.g64;
+    const int cta_groups = G / p.ksplit;
+    q.szg = (cta_groups + q.ks - 1) / q.ks;
+  }
+  const size_t smem = (size_t)kWarps * RING * kSK * R * 512 + (size_t)kWarps * NV * sizeof(float) +
+                      (size_t)kWarps * (RING + 1) * 8 + (size_t)kWarps * R * q.szg * 64;
+  auto kfn = smallm_w4_kernel<MT, R, EPI, I8>;
   static size_t attr_max = 48 * 1024;
   if (smem > 200 * 1024) return -2;
   if (smem > attr_max) {
@@ -399,7 +583,7 @@ int launch(const W4Params& p_in, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     attr_max = smem;
   }
-  dim3 grid(p.N / (16 * R), p.ksplit);
+  dim3 grid((q.ntiles + q.rt - 1) / q.rt, p.ksplit);
   if (EPI == EPI_AR_ADD) {
     // CTAs of different ranks wait for one another's pushes: every CTA of this grid must be
     // resident at once, otherwise resident CTAs could wait for peers whose partner CTA has no SM.
@@ -409,8 +593,13 @@ int launch(const W4Params& p_in, cudaStream_t st) {
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, kThreads, smem) != cudaSuccess) return -2;
     if ((long)per_sm * sms < (long)grid.x * grid.y) return -2;
   }
-  kfn<<<grid, kThreads, smem, st>>>(p);
+  kfn<<<grid, kThreads, smem, st>>>(q);
   GRM_LAUNCH_RET();
+}
+
+template <int MT, int R, int EPI>
+int launch(const W4Params& p, cudaStream_t st) {
+  return p.xq_hi ? launch_i<MT, R, EPI, true>(p, st) : launch_i<MT, R, EPI, false>(p, st);
 }
 
 template <int MT, int R>
@@ -465,6 +654,7 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
   p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
   if (epi == EPI_AR_ADD) return -1;   // use grm_smallm_w4_allreduce
   return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
 }
@@ -489,6 +679,105 @@ GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
+  return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Integer activation path: grm_quant_x_i8 turns bf16 rows into two int8 levels per quantisation group,
+// grm_smallm_w4_i8 / grm_smallm_w4_allreduce_i8 are the products over them (same contracts as above).
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// One CTA per row; a warp quantises one group at a time: delta = max|x| / 16256, Q = round(x / delta)
+// = 128 * hi + lo with hi in [-127, 127], lo in [-64, 63].  Bytes are stored with columns (1, 2) of every
+// 4 swapped, the order in which a weight word's even / odd nibbles enumerate k.
+__global__ void __launch_bounds__(256) quant_x_i8_kernel(const bf16* __restrict__ x, int ldx, int K, int group, int8_t* __restrict__ qh,
+                                                         int8_t* __restrict__ ql, int ldq, float2* __restrict__ tab, int ldtab) {
+  const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = K / group;
+  const int per = group / 32;              // elements per lane: 2, 4 or 8 (contiguous)
+  for (int gi = warp; gi < G; gi += 8) {
+    const bf16* src = x + (size_t)m * ldx + (size_t)gi * group + lane * per;
+    float v[8];
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] = i < per ? __bfloat162float(src[i]) : 0.f;
+      mx = fmaxf(mx, fabsf(v[i]));
+    }
+    mx = warp_max(mx);
+    const float delta = mx > 0.f ? mx / 16256.f : 1.f;
+    const float inv = 1.f / delta;
+    int sum = 0;
+    const size_t base = (size_t)m * ldq + (size_t)gi * group + lane * per;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i < per) {
+        const int q = __float2int_rn(v[i] * inv);
+        const int hi = (q + 64) >> 7;
+        sum += q;
+        const int k = lane * per + i;                                  // column inside the group (group % 4 == 0)
+        const int pos = (k & ~3) | ((k & 1) << 1) | ((k >> 1) & 1);    // swap bits 0 and 1
+        qh[base - (size_t)(lane * per) + pos] = (int8_t)hi;
+        ql[base - (size_t)(lane * per) + pos] = (int8_t)(q - 128 * hi);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) tab[(size_t)m * ldtab + gi] = make_float2(delta, delta * (float)sum);
+  }
+}
+
+}  // namespace
+
+// x bf16 [M][ldx] -> xq_hi / xq_lo int8 [M][ldq] (ldq % 16 == 0) and xtab float2 [M][ldtab] (ldtab >= K / group).
+GRM_API int grm_quant_x_i8(const void* x, int ldx, int M, int K, int group, void* xq_hi, void* xq_lo, int ldq, void* xtab, int ldtab,
+                           void* stream) {
+  if (M < 1 || (group != 64 && group != 128 && group != 256) || (K % group) || (ldq & 15) || ldq < K || ldtab < K / group) return -2;
+  quant_x_i8_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ldx, K, group, (int8_t*)xq_hi, (int8_t*)xq_lo, ldq,
+                                                        (float2*)xtab, ldtab);
+  GRM_LAUNCH_RET();
+}
+
+GRM_API int grm_smallm_w4_i8(const void* w, const void* sz, const void* xq_hi, const void* xq_lo, int ldq, const void* xtab, int ldtab,
+                             void* out, void* scratch, void* counters, int M, int N, int K, int ldo, int group, int epi,
+                             int rows_per_cta, int ksplit, void* stream) {
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldq & 15) ||
+      ((uintptr_t)xq_hi & 15) || ((uintptr_t)xq_lo & 15) || !xtab)
+    return -2;
+  const int G = K / group;
+  if (ksplit < 1 || (G % ksplit)) return -2;
+  if (ksplit > 1 && (!scratch || !counters)) return -2;
+  W4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = nullptr; p.out = out;
+  p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
+  p.M = M; p.N = N; p.K = K; p.ldx = 0; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas();
+  if (epi == EPI_AR_ADD) return -1;
+  return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
+}
+
+GRM_API int grm_smallm_w4_allreduce_i8(const void* w, const void* sz, const void* xq_hi, const void* xq_lo, int ldq, const void* xtab,
+                                       int ldtab, void* h, int M, int N, int K, int ldo, int group, const void* const* recv,
+                                       const void* const* flags, void* epochs, int world, int rank, unsigned int spin, void* stream) {
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || (ldq & 15) ||
+      ((uintptr_t)xq_hi & 15) || ((uintptr_t)xq_lo & 15) || !xtab)
+    return -2;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !recv || !flags || !epochs) return -2;
+  W4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = nullptr; p.out = h;
+  p.scratch = nullptr; p.counters = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldx = 0; p.ldo = ldo; p.g64 = group / 64; p.ksplit = 1;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_recv[i] = i < world ? (float*)const_cast<void*>(recv[i]) : nullptr;
+    p.ar_flags[i] = i < world ? (unsigned int*)const_cast<void*>(flags[i]) : nullptr;
+  }
+  p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
+  p.ar_spin = spin ? spin : 2000000u;
+  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas();
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
 
@@ -561,5 +850,6 @@ GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, 
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
   p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
   return dispatch(p, epi, rows_per_cta, st);
 }

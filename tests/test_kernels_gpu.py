@@ -280,3 +280,31 @@ def test_kv_gather_dequant():
     cv = torch.zeros(T, Hkv * D, dtype=torch.bfloat16)
     K.gather_kv_dense(kvc, table[1].cpu(), T, ck, cv)
     assert torch.equal(ok.cpu(), ck) and torch.equal(ov.cpu(), cv)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 17, 32])
+@pytest.mark.parametrize("N,Kd,group", [(256, 512, 128), (96, 1024, 64), (2048, 2048, 128), (64, 1280, 256)])
+def test_smallm_w4_int8_path_matches_fp32(M, N, Kd, group, monkeypatch):
+    """The integer activation path (two int8 levels per weight group, exact int32 group sums) against the
+    fp32 product of the same bf16 inputs: its activation rounding (15 bits per group) must not cost
+    more than the bf16 path's own tolerance."""
+    from grimoire_b200.ops import linear as L
+    monkeypatch.setattr(L, "W4_I8", True)
+    torch.manual_seed(M * 17 + N)
+    w = torch.randn(N, Kd) * 0.02
+    qw = quantize(w, Fmt.INT4, group=group)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    x = (torch.randn(M, Kd) * 0.5).to(DEV).bfloat16()
+    x[0, 7] = 40.0                      # an outlier inside one group
+    want = ref.linear_dequant(x.cpu(), qw.dequant())
+    out32 = torch.empty(M, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, out32, "f32")
+    got = out32[:, :N].cpu()
+    assert torch.allclose(got, want, atol=2e-3, rtol=1e-3), float((got - want).abs().max())
+    h = torch.ones(M, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, h, "add_f32")
+    assert torch.allclose(h[:, :N].cpu(), want + 1.0, atol=2e-3, rtol=1e-3)
+    one = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x[M - 1: M], one, "f32")
+    assert torch.equal(one[0], out32[M - 1])            # batch invariant
+    _assert_clean()
