@@ -221,18 +221,154 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedPar
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Small-row form of the grouped product (decode: every tile has at most 8 rows): a weight-streaming
+// GEMV.  CTA = (tile, block of `opc` output columns); the tile's activation rows are staged once in
+// shared memory as f16; each warp owns output columns and streams their weight rows with 16-byte loads
+// (four in flight per lane), expands e4m3 pairs with the hardware conversion, accumulates a lane's 16
+// products of one 128-block in packed f16 and folds them into fp32 with the block scale, then
+// reduces across the warp.  Same tile descriptors, modes and expert-parallel push as the MMA kernel.
+// ---------------------------------------------------------------------------------------------
+constexpr int kVThreads = 256;
+constexpr int kVRows = 8;
+
+template <int MODE>
+__global__ void __launch_bounds__(kVThreads) moe_gemv_kernel(const GroupedParams p, int opc) {
+  extern __shared__ __align__(16) __half xs16[];        // [kVRows][K]
+  const int tile = blockIdx.x;
+  if (p.n_tiles_dev && tile >= *p.n_tiles_dev) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = min(p.tile_rows[tile], kVRows);
+  const int NO = MODE == 0 ? p.N / 2 : p.N;
+  const int KB = p.K / 128;
+  const uint8_t* we = p.w + (size_t)e * p.N * p.K;
+  const float* se = p.scale + (size_t)e * p.N * KB;
+  for (int i = tid; i < nr * (p.K / 8); i += kVThreads) {
+    const int r = i / (p.K / 8), c8 = i - r * (p.K / 8);
+    const int src = p.row_ids ? p.row_ids[r0 + r] : (r0 + r);
+    const uint4 v = *reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx + c8 * 8);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t ou[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const __half2 h2 = __floats2half2_rn(bf16lo_to_f(in[q]), bf16hi_to_f(in[q]));
+      ou[q] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    *reinterpret_cast<uint4*>(xs16 + (size_t)r * p.K + c8 * 8) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+  __syncthreads();
+  constexpr int NB = MODE == 0 ? 2 : 1;
+  const int n_lo = blockIdx.y * opc, n_hi = min(n_lo + opc, NO);
+  for (int n = n_lo + warp; n < n_hi; n += kVThreads / 32) {
+    float acc[NB][kVRows];
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+      for (int r = 0; r < kVRows; ++r) acc[b][r] = 0.f;
+    // lane l covers bytes [512 i + 16 l, +16) of the row: one 128-block per 8 lanes and iteration
+    for (int k0 = lane * 16; k0 < p.K; k0 += 512 * 4) {
+      uint4 wv[NB][4];
+      float sc[NB][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + u * 512;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          if (k < p.K) {
+            wv[b][u] = ldg_stream_v4(we + (size_t)(n + b * NO) * p.K + k);
+            sc[b][u] = se[(size_t)(n + b * NO) * KB + (k >> 7)];
+          } else {
+            wv[b][u] = make_uint4(0u, 0u, 0u, 0u); sc[b][u] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + u * 512;
+        if (k >= p.K) break;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          uint32_t wh[8];
+          cvt_e4m3x4_to_f16x2x2(wv[b][u].x, wh[0], wh[1]); cvt_e4m3x4_to_f16x2x2(wv[b][u].y, wh[2], wh[3]);
+          cvt_e4m3x4_to_f16x2x2(wv[b][u].z, wh[4], wh[5]); cvt_e4m3x4_to_f16x2x2(wv[b][u].w, wh[6], wh[7]);
+#pragma unroll
+          for (int r = 0; r < kVRows; ++r) {
+            if (r < nr) {
+              const uint4 xa = *reinterpret_cast<const uint4*>(xs16 + (size_t)r * p.K + k);
+              const uint4 xb = *reinterpret_cast<const uint4*>(xs16 + (size_t)r * p.K + k + 8);
+              const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+              __half2 s2 = __float2half2_rn(0.f);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                s2 = __hfma2(*reinterpret_cast<const __half2*>(&wh[q]), *reinterpret_cast<const __half2*>(&xw[q]), s2);
+              const float2 f = __half22float2(s2);
+              acc[b][r] = fmaf(sc[b][u], f.x + f.y, acc[b][r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; ++b)
+#pragma unroll
+      for (int r = 0; r < kVRows; ++r) acc[b][r] = warp_sum(acc[b][r]);
+    if (lane == 0) {
+      for (int r = 0; r < nr; ++r) {
+        const float v0 = acc[0][r];
+        if (MODE == 4) { p.peer_y[p.tile_src[tile]][(size_t)p.row_dst[r0 + r] * p.ldo + n] = v0; continue; }
+        const size_t o = (size_t)(r0 + r) * p.ldo + n;
+        if (MODE == 0) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(silu_f(v0) * acc[NB - 1][r]);
+        else if (MODE == 1) reinterpret_cast<float*>(p.out)[o] = v0;
+        else if (MODE == 2) reinterpret_cast<float*>(p.out)[o] += v0;
+        else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(v0);
+      }
+    }
+  }
+  if (MODE == 4) {
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_done[p.tile_src[tile]]), "r"((unsigned)nr) : "memory");
+    }
+  }
+}
+
+template <int MODE>
+int launch_gemv(const GroupedParams& p, int n_tiles, int opc, cudaStream_t st) {
+  const int NO = MODE == 0 ? p.N / 2 : p.N;
+  const size_t smem = (size_t)kVRows * p.K * sizeof(__half);
+  static size_t attr_max = 48 * 1024;
+  if (smem > 160 * 1024) return -2;
+  if (smem > attr_max) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemv_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_max = smem;
+  }
+  dim3 grid(n_tiles, (NO + opc - 1) / opc);
+  moe_gemv_kernel<MODE><<<grid, kVThreads, smem, st>>>(p, opc);
+  GRM_LAUNCH_RET();
+}
+
+// output columns per CTA: enough CTAs (>= ~2 per SM) without dropping below one column per warp
+int gemv_opc(int n_tiles, int NO) {
+  int opc = 128;
+  while (opc > 8 && (long)n_tiles * ((NO + opc - 1) / opc) < 296) opc >>= 1;
+  return opc;
+}
+
 // h[token] += sum_j w[token][j] * y[pos[token][j]]  (fixed j order -> deterministic)
 __global__ void moe_combine_kernel(float* __restrict__ h, int ldh, const float* __restrict__ y, int ldy, const int* __restrict__ pos,
                                    const float* __restrict__ wts, int slots, int H) {
   const int tok = blockIdx.x;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < slots; ++j) {
-      const int ps = pos[(size_t)tok * slots + j];
-      if (ps >= 0) acc = fmaf(wts[(size_t)tok * slots + j], y[(size_t)ps * ldy + c], acc);
-    }
-    h[(size_t)tok * ldh + c] += acc;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float acc = 0.f;
+#pragma unroll 4
+  for (int j = 0; j < slots; ++j) {
+    const int ps = pos[(size_t)tok * slots + j];
+    if (ps >= 0) acc = fmaf(wts[(size_t)tok * slots + j], y[(size_t)ps * ldy + c], acc);
   }
+  h[(size_t)tok * ldh + c] += acc;
 }
 
 }  // namespace
@@ -272,13 +408,35 @@ GRM_API int grm_moe_grouped_gemm(const void* x, int ldx, const void* row_ids, co
   GRM_LAUNCH_RET();
 }
 
+// Small-row entry point (every tile has at most 8 rows): the weight-streaming GEMV above.
+GRM_API int grm_moe_grouped_gemv(const void* x, int ldx, const void* row_ids, const void* tile_expert, const void* tile_row0,
+                                 const void* tile_rows, int n_tiles, const void* w, const void* scale, void* out, int ldo, int N,
+                                 int K, int mode, void* stream) {
+  if (n_tiles < 1 || (K % 128) || (ldx & 7) || (mode == 0 && (N & 1))) return -2;
+  GroupedParams p;
+  p.x = (const bf16*)x; p.ldx = ldx; p.row_ids = (const int*)row_ids; p.tile_expert = (const int*)tile_expert;
+  p.tile_row0 = (const int*)tile_row0; p.tile_rows = (const int*)tile_rows; p.w = (const uint8_t*)w; p.scale = (const float*)scale;
+  p.out = out; p.ldo = ldo; p.N = N; p.K = K; p.mode = mode;
+  p.n_tiles_dev = nullptr; p.tile_src = nullptr; p.row_dst = nullptr;
+  for (int i = 0; i < 8; ++i) { p.peer_y[i] = nullptr; p.peer_done[i] = nullptr; }
+  const int opc = gemv_opc(n_tiles, mode == 0 ? N / 2 : N);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (mode) {
+    case 0: return launch_gemv<0>(p, n_tiles, opc, st);
+    case 1: return launch_gemv<1>(p, n_tiles, opc, st);
+    case 2: return launch_gemv<2>(p, n_tiles, opc, st);
+    case 3: return launch_gemv<3>(p, n_tiles, opc, st);
+    default: return -1;
+  }
+}
+
 // Expert-parallel form: tile descriptors and the tile count live on the device (built by grm_ep_plan),
 // the grid is the upper bound ``max_tiles``.  mode 0: SwiGLU into the local activation buffer;
 // mode 4: rows go back to their source rank (see MODE 4 above).
 GRM_API int grm_moe_grouped_gemm_ep(const void* x, int ldx, const void* tile_expert, const void* tile_row0, const void* tile_rows,
                                     const void* tile_src, const void* n_tiles_dev, int max_tiles, const void* w, const void* scale,
                                     void* out, int ldo, int N, int K, int mode, const void* row_dst, void* const* peer_y,
-                                    void* const* peer_done, int world, void* stream) {
+                                    void* const* peer_done, int world, int small_rows, void* stream) {
   if (max_tiles < 1 || (K % 128) || (ldx & 7) || (mode == 0 && (N & 1)) || world < 1 || world > 8) return -2;
   GroupedParams p;
   p.x = (const bf16*)x; p.ldx = ldx; p.row_ids = nullptr; p.tile_expert = (const int*)tile_expert;
@@ -292,6 +450,11 @@ GRM_API int grm_moe_grouped_gemm_ep(const void* x, int ldx, const void* tile_exp
   const int NO = mode == 0 ? N / 2 : N;
   dim3 grid(max_tiles, (NO + 127) / 128);
   cudaStream_t st = (cudaStream_t)stream;
+  if (small_rows) {     // every tile has <= 8 rows: GEMV form, 128 columns per CTA so the arrival counts match
+    if (mode == 0) return launch_gemv<0>(p, max_tiles, 128, st);
+    if (mode == 4) return launch_gemv<4>(p, max_tiles, 128, st);
+    return -1;
+  }
   if (mode == 0) moe_grouped_kernel<0><<<grid, kGThreads, 0, st>>>(p);
   else if (mode == 4) moe_grouped_kernel<4><<<grid, kGThreads, 0, st>>>(p);
   else return -1;
@@ -300,6 +463,6 @@ GRM_API int grm_moe_grouped_gemm_ep(const void* x, int ldx, const void* tile_exp
 
 GRM_API int grm_moe_combine(void* h, int ldh, const void* y, int ldy, const void* pos, const void* wts, int M, int slots, int H,
                             void* stream) {
-  moe_combine_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((float*)h, ldh, (const float*)y, ldy, (const int*)pos, (const float*)wts, slots, H);
+  moe_combine_kernel<<<dim3(M, (H + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)h, ldh, (const float*)y, ldy, (const int*)pos, (const float*)wts, slots, H);
   GRM_LAUNCH_RET();
 }

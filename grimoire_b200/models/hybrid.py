@@ -258,8 +258,8 @@ class HybridModel:
             r0c = starts[te] + within * 16
             nrc = torch.minimum(torch.full_like(r0c, 16), counts[te] - within * 16)
             te, r0, nr = (t.to(torch.int32).to(x.device) for t in (te, r0c, nrc))
-        Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu")
-        Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32")
+        Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu", small=decode)
+        Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32", small=decode)
         # shared expert as slot k of the combine
         moe.shared_gu(x, buf.act_s[:M], "swiglu")
         moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")

@@ -26,8 +26,10 @@ MODE = {"swiglu": 0, "f32": 1, "add_f32": 2, "bf16": 3}
 
 
 def grouped_gemm_fp8(x: torch.Tensor, row_ids: Optional[torch.Tensor], tile_expert: torch.Tensor, tile_row0: torch.Tensor,
-                     tile_rows: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, mode: str) -> torch.Tensor:
-    """out[grouped rows] = x[row_ids] @ W[expert]^T.  w uint8 [E][N][K] (e4m3), scale fp32 [E][N][K/128]."""
+                     tile_rows: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out: torch.Tensor, mode: str,
+                     small: bool = False) -> torch.Tensor:
+    """out[grouped rows] = x[row_ids] @ W[expert]^T.  w uint8 [E][N][K] (e4m3), scale fp32 [E][N][K/128].
+    ``small``: every tile has at most 8 rows (decode) -> the weight-streaming GEMV form of the kernel."""
     E, N, K = w.shape
     nt = tile_expert.shape[0]
     if not x.is_cuda:
@@ -45,9 +47,10 @@ def grouped_gemm_fp8(x: torch.Tensor, row_ids: Optional[torch.Tensor], tile_expe
             else:
                 out[rows] = y.to(out.dtype)
         return out
-    code = _native.cuda().grm_moe_grouped_gemm(_native.ptr(x), _c(x.stride(0)), _native.ptr(row_ids), _native.ptr(tile_expert),
-                                               _native.ptr(tile_row0), _native.ptr(tile_rows), _c(nt), _native.ptr(w), _native.ptr(scale),
-                                               _native.ptr(out), _c(out.stride(0)), _c(N), _c(K), _c(MODE[mode]), _native.stream_ptr())
+    fn = _native.cuda().grm_moe_grouped_gemv if small else _native.cuda().grm_moe_grouped_gemm
+    code = fn(_native.ptr(x), _c(x.stride(0)), _native.ptr(row_ids), _native.ptr(tile_expert),
+              _native.ptr(tile_row0), _native.ptr(tile_rows), _c(nt), _native.ptr(w), _native.ptr(scale),
+              _native.ptr(out), _c(out.stride(0)), _c(N), _c(K), _c(MODE[mode]), _native.stream_ptr())
     _native.check(code, f"moe_grouped_gemm N={N} K={K} tiles={nt} mode={mode}")
     return out
 
@@ -78,8 +81,20 @@ class FP8BlockLinear:
             self._tiles[M] = t
         return t
 
+    def tiles8(self, M: int):
+        t = self._tiles.get(-M)
+        if t is None:
+            t = (torch.zeros(1, dtype=torch.int32, device=self.device), torch.zeros(1, dtype=torch.int32, device=self.device),
+                 torch.full((1,), M, dtype=torch.int32, device=self.device))
+            self._tiles[-M] = t
+        return t
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
-        te, r0, nr = self.tiles(x.shape[0])
+        M = x.shape[0]
+        if M <= 8:
+            te, r0, nr = self.tiles8(M)
+            return grouped_gemm_fp8(x, None, te, r0, nr, self.w, self.scale, out, epi, small=True)
+        te, r0, nr = self.tiles(M)
         return grouped_gemm_fp8(x, None, te, r0, nr, self.w, self.scale, out, epi)
 
     __call__ = forward

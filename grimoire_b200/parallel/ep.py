@@ -111,11 +111,12 @@ class ExpertParallel:
         _native.check(lib.grm_moe_grouped_gemm_ep(
             _native.ptr(self.xrecv.local), _c(H), _native.ptr(self.tile_expert), _native.ptr(self.tile_row0), _native.ptr(self.tile_rows),
             _native.ptr(self.tile_src), _native.ptr(self.n_tiles), _c(bound), _native.ptr(moe.gate_up), _native.ptr(moe.gate_up_scale),
-            _native.ptr(self.act), _c(I), _c(N1), _c(H), _c(0), None, None, None, _c(W), st), "ep gate_up")
+            _native.ptr(self.act), _c(I), _c(N1), _c(H), _c(0), None, None, None, _c(W), _c(1 if M <= 8 else 0), st), "ep gate_up")
         _native.check(lib.grm_moe_grouped_gemm_ep(
             _native.ptr(self.act), _c(I), _native.ptr(self.tile_expert), _native.ptr(self.tile_row0), _native.ptr(self.tile_rows),
             _native.ptr(self.tile_src), _native.ptr(self.n_tiles), _c(bound), _native.ptr(moe.down), _native.ptr(moe.down_scale),
-            None, _c(H), _c(H), _c(I), _c(4), _native.ptr(self.rowdst.local), self.y.ptr_array(), self.done.ptr_array(), _c(W), st),
+            None, _c(H), _c(H), _c(I), _c(4), _native.ptr(self.rowdst.local), self.y.ptr_array(), self.done.ptr_array(), _c(W),
+            _c(1 if M <= 8 else 0), st),
             "ep down+combine push")
         yl = self.y.local.view(-1, H)
         has_shared = 0

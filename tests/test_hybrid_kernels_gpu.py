@@ -126,3 +126,35 @@ def test_moe_combine_is_slot_ordered():
     Hb.moe_combine(h_ref, y, pos, w)
     Hb.moe_combine(h, y.to(DEV), pos.to(DEV), w.to(DEV))
     assert torch.allclose(h.cpu(), h_ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("H,I", [(256, 128), (640, 256), (2048, 512)])
+def test_grouped_gemv_fp8_small_rows(M, H, I):
+    """The weight-streaming GEMV form (tiles of at most 8 rows) against the CPU oracle: one tile per
+    (row, expert) pair as in a decode step, and one dense tile of M rows."""
+    torch.manual_seed(M * 11 + H)
+    E = 4
+    wgu = torch.randn(E, 2 * I, H) * 0.05
+    q = [quantize(wgu[e], Fmt.FP8_BLOCK) for e in range(E)]
+    w8, sc = torch.stack([t.payload for t in q]), torch.stack([t.scales for t in q])
+    x = (torch.randn(M, H) * 0.5).bfloat16()
+    k = 2
+    pairs = M * k
+    te = torch.tensor([(r * 3 + j) % E for r in range(M) for j in range(k)], dtype=torch.int32)
+    t0 = torch.arange(pairs, dtype=torch.int32)
+    tn = torch.ones(pairs, dtype=torch.int32)
+    src = (t0 // k).to(torch.int32)
+    for mode, shape, dt in (("swiglu", (pairs, I), torch.bfloat16), ("f32", (pairs, 2 * I), torch.float32), ("bf16", (pairs, 2 * I), torch.bfloat16)):
+        ref = torch.zeros(shape, dtype=dt)
+        Hb.grouped_gemm_fp8(x, src, te, t0, tn, w8, sc, ref, mode)
+        out = torch.zeros(shape, dtype=dt, device=DEV)
+        Hb.grouped_gemm_fp8(x.to(DEV), src.to(DEV), te.to(DEV), t0.to(DEV), tn.to(DEV), w8.to(DEV), sc.to(DEV), out, mode, small=True)
+        err = float((out.float().cpu() - ref.float()).abs().max())
+        assert err < 2e-2 * max(1.0, float(ref.float().abs().max())), (mode, err)
+    lin, cpu = Hb.FP8BlockLinear(wgu[1], DEV), Hb.FP8BlockLinear(wgu[1], "cpu")
+    out = torch.ones(M, 2 * I, dtype=torch.float32, device=DEV)
+    lin(x.to(DEV), out, "add_f32")
+    ref = torch.ones(M, 2 * I)
+    cpu(x, ref, "add_f32")
+    assert torch.allclose(out.cpu(), ref, atol=2e-2, rtol=2e-2)
