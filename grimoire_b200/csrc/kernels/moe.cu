@@ -461,6 +461,42 @@ GRM_API int grm_moe_grouped_gemm_ep(const void* x, int ldx, const void* tile_exp
   GRM_LAUNCH_RET();
 }
 
+namespace {
+// block-scaled e4m3 [N][K] -> bf16 [N][K]; one thread per 16 values
+__global__ void __launch_bounds__(256) dequant_fp8_block_kernel(const uint8_t* __restrict__ w, const float* __restrict__ s, bf16* __restrict__ out,
+                                                                long n16, int K) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n16) return;
+  const long e0 = i * 16;
+  const long row = e0 / K;
+  const int k = (int)(e0 - row * K);
+  const float sc = s[row * (K / 128) + (k >> 7)];
+  const uint4 v = *reinterpret_cast<const uint4*>(w + e0);
+  const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+  uint32_t r[8];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t lo, hi;
+    cvt_e4m3x4_to_f16x2x2(words[q], lo, hi);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo)), b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    r[2 * q] = pack_bf16x2(a.x * sc, a.y * sc);
+    r[2 * q + 1] = pack_bf16x2(b.x * sc, b.y * sc);
+  }
+  uint4* o = reinterpret_cast<uint4*>(out + e0);
+  o[0] = make_uint4(r[0], r[1], r[2], r[3]);
+  o[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+}  // namespace
+
+// Dequantise a block-scaled fp8 matrix once into bf16 (tall prefill inputs then use the tcgen05 GEMM).
+GRM_API int grm_dequant_fp8_block(const void* w, const void* scale, void* out, int N, int K, void* stream) {
+  if (K % 128) return -2;
+  const long n16 = (long)N * K / 16;
+  dequant_fp8_block_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)w, (const float*)scale, (bf16*)out,
+                                                                                            n16, K);
+  GRM_LAUNCH_RET();
+}
+
 GRM_API int grm_moe_combine(void* h, int ldh, const void* y, int ldy, const void* pos, const void* wts, int M, int slots, int H,
                             void* stream) {
   moe_combine_kernel<<<dim3(M, (H + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)h, ldh, (const float*)y, ldy, (const int*)pos, (const float*)wts, slots, H);

@@ -94,6 +94,26 @@ class FP8BlockLinear:
         if M <= 8:
             te, r0, nr = self.tiles8(M)
             return grouped_gemm_fp8(x, None, te, r0, nr, self.w, self.scale, out, epi, small=True)
+        if M > 64 and x.is_cuda:
+            # tall inputs: dequantise once into the shared bf16 scratch and run the tcgen05 GEMM (the policy of the
+            # int4 projections as well); SwiGLU weights are [gate | up] here, so the two halves are separate GEMMs
+            from .linear import gemm_bf16
+            from .workspace import default_workspace
+
+            ws = default_workspace(self.device)
+            wb = ws.get("dequant_bf16", self.N * self.K, torch.bfloat16).view(-1)[: self.N * self.K].view(self.N, self.K)
+            _native.check(_native.cuda().grm_dequant_fp8_block(_native.ptr(self.w), _native.ptr(self.scale), _native.ptr(wb), _c(self.N),
+                                                               _c(self.K), _native.stream_ptr()), f"dequant_fp8_block {self.name}")
+            if epi == "swiglu":
+                I = self.N // 2
+                g = ws.get("fp8_gate_f32", M * I, torch.float32).view(-1)[: M * I].view(M, I)
+                u = ws.get("fp8_up_f32", M * I, torch.float32).view(-1)[: M * I].view(M, I)
+                gemm_bf16(x, wb[:I], g, "f32")
+                gemm_bf16(x, wb[I:], u, "f32")
+                torch.mul(torch.nn.functional.silu(g), u, out=g)
+                out.copy_(g)
+                return out
+            return gemm_bf16(x, wb, out, epi)
         te, r0, nr = self.tiles(M)
         return grouped_gemm_fp8(x, None, te, r0, nr, self.w, self.scale, out, epi)
 

@@ -158,3 +158,25 @@ def test_grouped_gemv_fp8_small_rows(M, H, I):
     ref = torch.ones(M, 2 * I)
     cpu(x, ref, "add_f32")
     assert torch.allclose(out.cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [65, 200])
+def test_fp8_block_linear_tall_inputs_use_dequant_gemm(M):
+    """More than 64 rows: dequantise once + tcgen05 GEMM (bf16 rounding of the dequantised weights)."""
+    torch.manual_seed(M)
+    N, H = 512, 384
+    w = torch.randn(N, H) * 0.05
+    x = (torch.randn(M, H) * 0.5).bfloat16()
+    lin, cpu = Hb.FP8BlockLinear(w, DEV), Hb.FP8BlockLinear(w, "cpu")
+    for epi, shape, dt in (("bf16", (M, N), torch.bfloat16), ("f32", (M, N), torch.float32), ("swiglu", (M, N // 2), torch.bfloat16)):
+        ref = torch.zeros(shape, dtype=dt)
+        cpu(x, ref, epi)
+        out = torch.zeros(shape, dtype=dt, device=DEV)
+        lin(x.to(DEV), out, epi)
+        err = float((out.float().cpu() - ref.float()).abs().max())
+        assert err < 3e-2 * max(1.0, float(ref.float().abs().max())), (epi, err)
+    out = torch.ones(M, N, dtype=torch.float32, device=DEV)
+    lin(x.to(DEV), out, "add_f32")
+    ref = torch.ones(M, N)
+    cpu(x, ref, "add_f32")
+    assert torch.allclose(out.cpu(), ref, atol=3e-2, rtol=3e-2)
