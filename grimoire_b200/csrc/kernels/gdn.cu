@@ -168,6 +168,209 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_runs_kernel(const GdnParams p
     reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Chunked form of the same recurrence for prompt chunks (64 tokens per chunk).
+//
+// With u_t = beta_t (v_t - a_t S_{t-1} k_t) the step is S_t = a_t S_{t-1} + u_t k_t^T, so inside a chunk
+// (gamma_t = prod_{j<=t} a_j, S_0 the state at the chunk start)
+//     (I + L) U = diag(beta) (V - diag(gamma) K S_0^T),   L_tj = beta_t (gamma_t/gamma_j) (k_t.k_j), j < t
+//     O = (diag(gamma) Q S_0^T + M U) / sqrt(Dk),          M_tj = (gamma_t/gamma_j) (q_t.k_j),       j <= t
+//     S_C = gamma_C S_0 + U^T diag(gamma_C/gamma) K
+// (the WY / UT-transform form of the gated delta rule; every ratio gamma_t/gamma_j is <= 1).  All
+// products are fp32.  A CTA owns (run, v head, a quarter of Dv): thread = (dv, quarter of Dk) keeps its 32
+// state values in registers across the whole run, the chunk's K / Q rows and the two C x C matrices sit
+// in shared memory, the triangular system is solved by forward substitution with the 64 unknowns of a
+// dv column spread over the 4 threads of its quad.  The output norm needs all of Dv, so the raw outputs
+// go to an fp32 scratch and gdn_gated_norm_kernel finishes them.
+// ---------------------------------------------------------------------------------------------
+constexpr int CH = 64;             // chunk length
+constexpr int DVL = 32;            // Dv rows per CTA
+constexpr int kChThreads = 128;
+constexpr int LDK = D + 4;         // padded row pitch of the K / Q tiles
+
+struct GdnChunkParams {
+  const bf16* qkv; int ld_qkv;
+  const float* ab; int ld_ab;
+  const float* A_log; const float* dt_bias;
+  float* state;
+  const int* run_slot; const int* run_start; const int* run_len;
+  float* o_raw; int ld_o;          // fp32 [M][Hv*Dv], un-normalised outputs
+  int Hk, Hv;
+};
+
+__global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkParams p) {
+  extern __shared__ __align__(16) float smc[];
+  float* Ks = smc;                          // [CH][LDK]
+  float* Qs = Ks + CH * LDK;                // [CH][LDK]
+  float* Vs = Qs + CH * LDK;                // [CH][DVL]
+  float* Lm = Vs + CH * DVL;                // [CH][CH + 1]
+  float* Mm = Lm + CH * (CH + 1);           // [CH][CH + 1]
+  float* Us = Mm + CH * (CH + 1);           // [CH][DVL + 1]
+  float* Gs = Us + CH * (DVL + 1);          // [CH] cumulative log decay
+  float* Bs = Gs + CH;                      // [CH] beta
+  const int run = blockIdx.x, vh = blockIdx.y, dvs = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dvl = tid >> 2, part = tid & 3;             // thread = (dv row, quarter of Dk)
+  const int slot = p.run_slot[run], r0 = p.run_start[run], n = p.run_len[run];
+  const int kh = vh / (p.Hv / p.Hk);
+  const int dv = dvs * DVL + dvl;
+  float S[32];
+  float* sp = p.state + (((size_t)slot * p.Hv + vh) * D + dv) * D + part * 32;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 t4 = reinterpret_cast<const float4*>(sp)[i];
+    S[4 * i] = t4.x; S[4 * i + 1] = t4.y; S[4 * i + 2] = t4.z; S[4 * i + 3] = t4.w;
+  }
+  const float neg_expA = -__expf(p.A_log[vh]);
+  const float dtb = p.dt_bias[vh];
+  const float inv_sqrt_d = rsqrtf((float)D);
+  const int qoff = kh * D, koff = p.Hk * D + kh * D, voff = 2 * p.Hk * D + vh * D + dvs * DVL;
+
+  for (int c0 = 0; c0 < n; c0 += CH) {
+    const int nc = min(CH, n - c0);
+    __syncthreads();
+    // ---- stage the chunk: L2-normalised q / k rows (a warp per token), the v slice, gates ----
+    for (int t = warp; t < CH; t += kChThreads / 32) {
+      float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
+      if (t < nc) {
+        const bf16* xr = p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv;
+        const uint2 qa = *reinterpret_cast<const uint2*>(xr + qoff + lane * 4), ka = *reinterpret_cast<const uint2*>(xr + koff + lane * 4);
+        qv = make_float4(bf16lo_to_f(qa.x), bf16hi_to_f(qa.x), bf16lo_to_f(qa.y), bf16hi_to_f(qa.y));
+        kv = make_float4(bf16lo_to_f(ka.x), bf16hi_to_f(ka.x), bf16lo_to_f(ka.y), bf16hi_to_f(ka.y));
+      }
+      const float qs = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+      const float ks = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+      const float qr = t < nc ? rsqrtf(qs + 1e-6f) : 0.f, kr = t < nc ? rsqrtf(ks + 1e-6f) : 0.f;
+      *reinterpret_cast<float4*>(Qs + t * LDK + lane * 4) = make_float4(qv.x * qr, qv.y * qr, qv.z * qr, qv.w * qr);
+      *reinterpret_cast<float4*>(Ks + t * LDK + lane * 4) = make_float4(kv.x * kr, kv.y * kr, kv.z * kr, kv.w * kr);
+    }
+    for (int i = tid; i < CH * DVL; i += kChThreads) {
+      const int t = i / DVL, d = i - t * DVL;
+      Vs[i] = t < nc ? __bfloat162float(p.qkv[(size_t)(r0 + c0 + t) * p.ld_qkv + voff + d]) : 0.f;
+    }
+    if (tid < CH) {
+      float la = 0.f, be = 0.f;
+      if (tid < nc) {
+        const size_t row = (size_t)(r0 + c0 + tid);
+        const float xs = p.ab[row * p.ld_ab + vh] + dtb;
+        const float spl = xs > 20.f ? xs : log1pf(__expf(xs));
+        la = neg_expA * spl;                              // log a_t  (<= 0)
+        be = sigmoid_f(p.ab[row * p.ld_ab + p.Hv + vh]);
+      }
+      Gs[tid] = la; Bs[tid] = be;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float acc = 0.f;
+      for (int t = 0; t < CH; ++t) { acc += Gs[t]; Gs[t] = acc; }
+    }
+    // ---- k_t.k_j and q_t.k_j: thread = (row t, half of the j range) ----
+    {
+      const int t = tid >> 1, jh = (tid & 1) * 32;
+      float akk[32], aqk[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { akk[j] = 0.f; aqk[j] = 0.f; }
+      for (int kb = 0; kb < D / 4; ++kb) {
+        const float4 kt = *reinterpret_cast<const float4*>(Ks + t * LDK + kb * 4);
+        const float4 qt = *reinterpret_cast<const float4*>(Qs + t * LDK + kb * 4);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float4 kj = *reinterpret_cast<const float4*>(Ks + (jh + j) * LDK + kb * 4);
+          akk[j] = fmaf(kt.x, kj.x, fmaf(kt.y, kj.y, fmaf(kt.z, kj.z, fmaf(kt.w, kj.w, akk[j]))));
+          aqk[j] = fmaf(qt.x, kj.x, fmaf(qt.y, kj.y, fmaf(qt.z, kj.z, fmaf(qt.w, kj.w, aqk[j]))));
+        }
+      }
+      __syncthreads();                                     // Gs is complete
+      const float gt = Gs[t], bt = Bs[t];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int jj = jh + j;
+        const float ratio = jj <= t ? __expf(gt - Gs[jj]) : 0.f;
+        Lm[t * (CH + 1) + jj] = jj < t ? bt * ratio * akk[j] : 0.f;
+        Mm[t * (CH + 1) + jj] = ratio * aqk[j];
+      }
+    }
+    // ---- p_t = (K S_0^T)[t][dv], r_t = (Q S_0^T)[t][dv]: partial over this thread's 32 k, quad-reduced; thread
+    //      `part` keeps the values of its 16 tokens ----
+    float pk[16], rq[16];
+#pragma unroll
+    for (int t = 0; t < CH; ++t) {
+      float a1 = 0.f, a2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 kx = *reinterpret_cast<const float4*>(Ks + t * LDK + part * 32 + i * 4);
+        const float4 qx = *reinterpret_cast<const float4*>(Qs + t * LDK + part * 32 + i * 4);
+        a1 = fmaf(S[4 * i], kx.x, fmaf(S[4 * i + 1], kx.y, fmaf(S[4 * i + 2], kx.z, fmaf(S[4 * i + 3], kx.w, a1))));
+        a2 = fmaf(S[4 * i], qx.x, fmaf(S[4 * i + 1], qx.y, fmaf(S[4 * i + 2], qx.z, fmaf(S[4 * i + 3], qx.w, a2))));
+      }
+      a1 += __shfl_xor_sync(0xffffffffu, a1, 1); a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, 1); a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
+      if ((t >> 4) == part) { pk[t & 15] = a1; rq[t & 15] = a2; }
+    }
+    __syncthreads();                                       // Lm / Mm are complete
+    // ---- forward substitution for this dv column of U; u_t lives in thread (t >> 4) of the quad ----
+    float u[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) u[i] = 0.f;
+#pragma unroll
+    for (int t = 0; t < CH; ++t) {
+      float sacc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) sacc = fmaf(Lm[t * (CH + 1) + part * 16 + i], u[i], sacc);   // rows j >= t are zero
+      sacc += __shfl_xor_sync(0xffffffffu, sacc, 1); sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
+      if ((t >> 4) == part) {
+        const float gam = __expf(Gs[t]);
+        u[t & 15] = Bs[t] * (Vs[t * DVL + dvl] - gam * pk[t & 15]) - sacc;
+      }
+    }
+    // ---- outputs ----
+#pragma unroll
+    for (int t = 0; t < CH; ++t) {
+      float oacc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) oacc = fmaf(Mm[t * (CH + 1) + part * 16 + i], u[i], oacc);
+      oacc += __shfl_xor_sync(0xffffffffu, oacc, 1); oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
+      if ((t >> 4) == part && t < nc)
+        p.o_raw[(size_t)(r0 + c0 + t) * p.ld_o + vh * D + dv] = (__expf(Gs[t]) * rq[t & 15] + oacc) * inv_sqrt_d;
+    }
+    // ---- state: S = gamma_C S + sum_j (gamma_C / gamma_j) u_j k_j^T over this thread's 32 k ----
+#pragma unroll
+    for (int i = 0; i < 16; ++i) Us[(part * 16 + i) * (DVL + 1) + dvl] = u[i];
+    __syncwarp();                                           // a quad's four threads share a warp
+    const float gC = Gs[CH - 1];
+    const float gamC = __expf(gC);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[i] *= gamC;
+    for (int j = 0; j < CH; ++j) {
+      const float cu = __expf(gC - Gs[j]) * Us[j * (DVL + 1) + dvl];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 kx = *reinterpret_cast<const float4*>(Ks + j * LDK + part * 32 + i * 4);
+        S[4 * i] = fmaf(cu, kx.x, S[4 * i]); S[4 * i + 1] = fmaf(cu, kx.y, S[4 * i + 1]);
+        S[4 * i + 2] = fmaf(cu, kx.z, S[4 * i + 2]); S[4 * i + 3] = fmaf(cu, kx.w, S[4 * i + 3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+}
+
+// out = rms_norm(o_raw) * w * silu(z) per (row, v head)
+__global__ void __launch_bounds__(128) gdn_gated_norm_kernel(const float* __restrict__ o_raw, int ld_o, const bf16* __restrict__ z, int ld_z,
+                                                             const float* __restrict__ w, float eps, bf16* __restrict__ out, int ld_out) {
+  __shared__ float red[4];
+  const int row = blockIdx.x, vh = blockIdx.y, tid = threadIdx.x;
+  const float o = o_raw[(size_t)row * ld_o + vh * D + tid];
+  const float ss = warp_sum(o * o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  const float r = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)D + eps);
+  const float zz = __bfloat162float(z[(size_t)row * ld_z + vh * D + tid]);
+  out[(size_t)row * ld_out + vh * D + tid] = __float2bfloat16(o * r * w[tid] * silu_f(zz));
+}
+
 }  // namespace
 
 GRM_API int grm_conv4_silu(const void* x, const void* w, const void* ring_in, void* ring_out, const void* row_seq,
@@ -192,5 +395,32 @@ GRM_API int grm_gdn_runs(const void* qkv, int ld_qkv, const void* ab, int ld_ab,
   p.out = (bf16*)out; p.ld_out = ld_out; p.Hk = Hk; p.Hv = Hv;
   dim3 grid(n_runs, Hv);
   gdn_runs_kernel<<<grid, kGdnThreads, 0, (cudaStream_t)stream>>>(p);
+  GRM_LAUNCH_RET();
+}
+
+// Chunked (prompt) form: same contract as grm_gdn_runs plus an fp32 scratch o_raw [M][Hv*Dv]; M = total rows.
+GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_ab, const void* z, int ld_z, const void* A_log,
+                            const void* dt_bias, const void* norm_w, float norm_eps, void* state, const void* run_slot,
+                            const void* run_start, const void* run_len, int n_runs, void* o_raw, void* out, int ld_out, int M,
+                            int Hk, int Hv, int Dk, int Dv, void* stream) {
+  if (Dk != D || Dv != D || n_runs < 1 || Hv % Hk || M < 1 || (ld_qkv & 3)) return -2;
+  GdnChunkParams p;
+  p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.ab = (const float*)ab; p.ld_ab = ld_ab;
+  p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias; p.state = (float*)state;
+  p.run_slot = (const int*)run_slot; p.run_start = (const int*)run_start; p.run_len = (const int*)run_len;
+  p.o_raw = (float*)o_raw; p.ld_o = Hv * D; p.Hk = Hk; p.Hv = Hv;
+  const size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 2 * CH * (CH + 1) + CH * (DVL + 1) + 2 * CH);
+  static bool configured = false;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdn_chunked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  gdn_chunked_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  gdn_gated_norm_kernel<<<dim3(M, Hv), 128, 0, st>>>((const float*)o_raw, Hv * D, (const bf16*)z, ld_z, (const float*)norm_w, norm_eps,
+                                                     (bf16*)out, ld_out);
   GRM_LAUNCH_RET();
 }

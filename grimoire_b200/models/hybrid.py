@@ -102,6 +102,7 @@ class HybridModel:
         self.tp_rank, self.tp_world, self.pp_rank, self.pp_world = 0, 1, 0, 1
         self.tp = self.pp = None
         self.ep = None                   # parallel.ep.ExpertParallel when the experts are sharded over ranks
+        self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = False
         self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
@@ -230,6 +231,15 @@ class HybridModel:
         E, k, H = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size
         lg = buf.router[:M, : cfg.num_experts + 1]
         moe.router(x, lg, "f32")
+        if self.ep is None and not decode and x.is_cuda and M > 64:
+            # a prompt chunk on one GPU: group the rows by expert on the device (the expert-parallel chain with
+            # this GPU as its only rank) instead of sorting on the host, which would stall the stream every layer
+            if self._local_moe is None or self._local_moe.max_rows < buf.max_rows:
+                from ..parallel.ep import ExpertParallel
+
+                self._local_moe = ExpertParallel(None, self.device, E, k, H, cfg.moe_intermediate_size, buf.max_rows, fused=True)
+            self._local_moe.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
+            return
         if self.ep is not None:
             if self.ep.fused:
                 self.ep.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
@@ -291,7 +301,7 @@ class HybridModel:
                 L.in_ab(x, buf.gdn_ab[:M], "f32")
                 Hb.conv4_silu(buf.gdn_qkv[:M], L.conv_w, self.ring[si], self.ring_tmp, rb.row_seq, rb.row_pos, buf.gdn_conv[:M], touched)
                 Hb.gdn_runs(buf.gdn_conv[:M], buf.gdn_ab[:M], buf.gdn_z[:M], L.A_log, L.dt_bias, L.gdn_norm, eps, self.state[si],
-                            run_slot, run_start, run_len, buf.gdn_o[:M], self.Hk, self.Hv, self.Dk, self.Dv)
+                            run_slot, run_start, run_len, buf.gdn_o[:M], self.Hk, self.Hv, self.Dk, self.Dv, chunked=prefill and M >= 32)
                 L.out_proj(buf.gdn_o[:M], h, "add_f32")
             else:
                 kvl = kv_layers[L.kv_index]

@@ -182,8 +182,10 @@ def conv4_silu(x: torch.Tensor, w: torch.Tensor, ring: torch.Tensor, ring_tmp: t
 
 
 def gdn_runs(qkv: torch.Tensor, ab: torch.Tensor, z: torch.Tensor, A_log, dt_bias, norm_w, eps: float, state: torch.Tensor,
-             run_slot: torch.Tensor, run_start: torch.Tensor, run_len: torch.Tensor, out: torch.Tensor, Hk: int, Hv: int, Dk: int, Dv: int):
-    """Gated delta rule over runs of rows (see gdn.cu); state [slots][Hv][Dv][Dk] fp32 is updated."""
+             run_slot: torch.Tensor, run_start: torch.Tensor, run_len: torch.Tensor, out: torch.Tensor, Hk: int, Hv: int, Dk: int, Dv: int,
+             chunked: bool = False):
+    """Gated delta rule over runs of rows (see gdn.cu); state [slots][Hv][Dv][Dk] fp32 is updated.
+    ``chunked``: the runs are long (prompt chunks) -> the 64-token chunked form instead of the per-token scan."""
     if not qkv.is_cuda:
         for s, r0, n in zip(run_slot.tolist(), run_start.tolist(), run_len.tolist()):
             x = qkv[r0: r0 + n].float()
@@ -193,6 +195,18 @@ def gdn_runs(qkv: torch.Tensor, ab: torch.Tensor, z: torch.Tensor, A_log, dt_bia
             a, b = gdn_ref.gates(ab[r0: r0 + n, :Hv], ab[r0: r0 + n, Hv:], A_log, dt_bias)
             o = gdn_ref.gdn_sequence(state[s], q, k, v, a, b)
             out[r0: r0 + n] = gdn_ref.gated_rmsnorm(o, z[r0: r0 + n].float().reshape(n, Hv, Dv), norm_w, eps).reshape(n, Hv * Dv).to(out.dtype)
+        return out
+    if chunked:
+        from .workspace import default_workspace
+
+        M = qkv.shape[0]
+        o_raw = default_workspace(qkv.device).get("gdn_o_raw", M * Hv * Dv, torch.float32)
+        code = _native.cuda().grm_gdn_chunked(_native.ptr(qkv), _c(qkv.stride(0)), _native.ptr(ab), _c(ab.stride(0)), _native.ptr(z),
+                                              _c(z.stride(0)), _native.ptr(A_log), _native.ptr(dt_bias), _native.ptr(norm_w),
+                                              ctypes.c_float(eps), _native.ptr(state), _native.ptr(run_slot), _native.ptr(run_start),
+                                              _native.ptr(run_len), _c(run_slot.shape[0]), _native.ptr(o_raw), _native.ptr(out),
+                                              _c(out.stride(0)), _c(M), _c(Hk), _c(Hv), _c(Dk), _c(Dv), _native.stream_ptr())
+        _native.check(code, "gdn_chunked")
         return out
     code = _native.cuda().grm_gdn_runs(_native.ptr(qkv), _c(qkv.stride(0)), _native.ptr(ab), _c(ab.stride(0)), _native.ptr(z), _c(z.stride(0)),
                                        _native.ptr(A_log), _native.ptr(dt_bias), _native.ptr(norm_w), ctypes.c_float(eps), _native.ptr(state),

@@ -33,11 +33,25 @@ def _c(v):
     return ctypes.c_int(int(v))
 
 
+class _LocalBuffer:
+    """Stand-in for ``SymmetricBuffer`` when the "group" is this GPU alone."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device):
+        self.local = torch.zeros(numel, dtype=dtype, device=device)
+        self.ptrs, self.world = [self.local.data_ptr()], 1
+
+    def ptr_array(self):
+        return (ctypes.c_void_p * 1)(*self.ptrs)
+
+
 class ExpertParallel:
     def __init__(self, group, device, num_experts: int, top_k: int, hidden: int, inter: int, max_rows: int,
                  fused: Optional[bool] = None):
+        """``group`` None: a single-GPU instance -- the same device-side dispatch / plan / grouped GEMM /
+        combine chain with local buffers, used for prompt chunks so that grouping tokens by expert needs no
+        host round trip."""
         self.group, self.device = group, torch.device(device)
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.rank, self.world = (dist.get_rank(group), dist.get_world_size(group)) if group is not None else (0, 1)
         if num_experts % self.world:
             raise ValueError(f"{num_experts} experts do not split over {self.world} ranks")
         self.E, self.E_loc, self.k, self.H, self.I = num_experts, num_experts // self.world, top_k, hidden, inter
@@ -65,14 +79,15 @@ class ExpertParallel:
         Mq_max = (self.max_rows + W - 1) // W
         self.cap = Mq_max * k                              # rows one source can send to one owner
         i32, f32, bf = torch.int32, torch.float32, torch.bfloat16
-        self.xrecv = SymmetricBuffer(W * self.cap * H, bf, g, dev)
-        self.rowdst = SymmetricBuffer(W * self.cap, i32, g, dev)
-        self.groups = SymmetricBuffer(W * self.E_loc * 2, i32, g, dev)
-        self.flags = SymmetricBuffer(8, i32, g, dev)
-        self.y = SymmetricBuffer(Mq_max * (k + 1) * H, f32, g, dev)
-        self.done = SymmetricBuffer(8, i32, g, dev)
-        self.gather = SymmetricBuffer(2 * self.max_rows * H, f32, g, dev)
-        self.hflags = SymmetricBuffer(8, i32, g, dev)
+        mkbuf = (lambda n, dt: SymmetricBuffer(n, dt, g, dev)) if g is not None else (lambda n, dt: _LocalBuffer(n, dt, dev))
+        self.xrecv = mkbuf(W * self.cap * H, bf)
+        self.rowdst = mkbuf(W * self.cap, i32)
+        self.groups = mkbuf(W * self.E_loc * 2, i32)
+        self.flags = mkbuf(8, i32)
+        self.y = mkbuf(Mq_max * (k + 1) * H, f32)
+        self.done = mkbuf(8, i32)
+        self.gather = mkbuf(2 * self.max_rows * H if W > 1 else 8, f32)
+        self.hflags = mkbuf(8, i32)
         z = lambda *s, dt=i32: torch.zeros(*s, dtype=dt, device=dev)
         self.state = z(16)
         self.counts, self.ebase, self.cursors = z(self.E), z(self.E), z(self.E)
@@ -80,7 +95,8 @@ class ExpertParallel:
         self.tile_expert, self.tile_row0, self.tile_rows, self.tile_src = (z(self.max_tiles) for _ in range(4))
         self.n_tiles = z(1)
         self.act = z(W * self.cap, self.I, dt=bf)
-        dist.barrier(g)
+        if g is not None:
+            dist.barrier(g)
         torch.cuda.synchronize(dev)
 
     # ------------------------------------------------------------------------------------------

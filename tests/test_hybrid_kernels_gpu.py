@@ -180,3 +180,29 @@ def test_fp8_block_linear_tall_inputs_use_dequant_gemm(M):
     ref = torch.ones(M, N)
     cpu(x, ref, "add_f32")
     assert torch.allclose(out.cpu(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("lens", [[64], [200], [37, 130], [1, 64, 65]])
+def test_gdn_chunked_matches_sequential_oracle(lens):
+    """The 64-token chunked form (UT-transform of the gated delta rule) against the token-by-token fp32
+    oracle: outputs, final state, partial last chunks, several runs with different slots."""
+    torch.manual_seed(sum(lens))
+    Hk, Hv, D = 2, 4, 128
+    M = sum(lens)
+    run_slot = torch.tensor([(2 * i + 1) % 3 for i in range(len(lens))], dtype=torch.int32)
+    run_len = torch.tensor(lens, dtype=torch.int32)
+    run_start = (torch.cumsum(run_len, 0) - run_len).to(torch.int32)
+    qkv = (torch.randn(M, 2 * Hk * D + Hv * D) * 0.5).bfloat16()
+    ab = torch.randn(M, 2 * Hv)
+    z = torch.randn(M, Hv * D).bfloat16()
+    A_log, dt_bias, nw = torch.randn(Hv) * 0.5, torch.randn(Hv) * 0.5, 1 + 0.1 * torch.randn(D)
+    state = torch.randn(3, Hv, D, D) * 0.1
+    out_ref = torch.zeros(M, Hv * D, dtype=torch.bfloat16)
+    st_ref = state.clone()
+    Hb.gdn_runs(qkv, ab, z, A_log, dt_bias, nw, 1e-6, st_ref, run_slot, run_start, run_len, out_ref, Hk, Hv, D, D)
+    out = torch.zeros(M, Hv * D, dtype=torch.bfloat16, device=DEV)
+    st = state.clone().to(DEV)
+    Hb.gdn_runs(qkv.to(DEV), ab.to(DEV), z.to(DEV), A_log.to(DEV), dt_bias.to(DEV), nw.to(DEV), 1e-6, st, run_slot.to(DEV),
+                run_start.to(DEV), run_len.to(DEV), out, Hk, Hv, D, D, chunked=True)
+    assert torch.allclose(out.float().cpu(), out_ref.float(), atol=3e-2, rtol=3e-2), float((out.float().cpu() - out_ref.float()).abs().max())
+    assert torch.allclose(st.cpu(), st_ref, atol=2e-3, rtol=2e-3), float((st.cpu() - st_ref).abs().max())
