@@ -188,6 +188,7 @@ constexpr int CH = 64;             // chunk length
 constexpr int DVL = 32;            // Dv rows per CTA
 constexpr int kChThreads = 128;
 constexpr int LDK = D + 4;         // padded row pitch of the K / Q tiles
+constexpr int UP = DVL + 8;        // row pitch of the [token][dv] tiles: the four j-phases of a quad hit different banks
 
 struct GdnChunkParams {
   const bf16* qkv; int ld_qkv;
@@ -207,7 +208,9 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
   float* Lm = Vs + CH * DVL;                // [CH][CH + 1]
   float* Mm = Lm + CH * (CH + 1);           // [CH][CH + 1]
   float* Us = Mm + CH * (CH + 1);           // [CH][DVL + 1]
-  float* Gs = Us + CH * (DVL + 1);          // [CH] cumulative log decay
+  float* Ps = Us + CH * UP;          // [CH][DVL + 1]  (K S_0^T) for this CTA's dv rows
+  float* Rs = Ps + CH * UP;          // [CH][DVL + 1]  (Q S_0^T)
+  float* Gs = Rs + CH * UP;          // [CH] cumulative log decay
   float* Bs = Gs + CH;                      // [CH] beta
   const int run = blockIdx.x, vh = blockIdx.y, dvs = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -216,10 +219,12 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
   const int kh = vh / (p.Hv / p.Hk);
   const int dv = dvs * DVL + dvl;
   float S[32];
-  float* sp = p.state + (((size_t)slot * p.Hv + vh) * D + dv) * D + part * 32;
+  // thread `part` owns the k columns 16 i + 4 part + (0..3), i = 0..7: the four threads of a quad read four
+  // consecutive 16-byte words of a K / Q row, which keeps the shared-memory reads free of bank conflicts
+  float* sp = p.state + (((size_t)slot * p.Hv + vh) * D + dv) * D + part * 4;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float4 t4 = reinterpret_cast<const float4*>(sp)[i];
+    const float4 t4 = reinterpret_cast<const float4*>(sp)[4 * i];
     S[4 * i] = t4.x; S[4 * i + 1] = t4.y; S[4 * i + 2] = t4.z; S[4 * i + 3] = t4.w;
   }
   const float neg_expA = -__expf(p.A_log[vh]);
@@ -231,19 +236,31 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
     const int nc = min(CH, n - c0);
     __syncthreads();
     // ---- stage the chunk: L2-normalised q / k rows (a warp per token), the v slice, gates ----
-    for (int t = warp; t < CH; t += kChThreads / 32) {
-      float4 qv = make_float4(0.f, 0.f, 0.f, 0.f), kv = qv;
-      if (t < nc) {
-        const bf16* xr = p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv;
-        const uint2 qa = *reinterpret_cast<const uint2*>(xr + qoff + lane * 4), ka = *reinterpret_cast<const uint2*>(xr + koff + lane * 4);
-        qv = make_float4(bf16lo_to_f(qa.x), bf16hi_to_f(qa.x), bf16lo_to_f(qa.y), bf16hi_to_f(qa.y));
-        kv = make_float4(bf16lo_to_f(ka.x), bf16hi_to_f(ka.x), bf16lo_to_f(ka.y), bf16hi_to_f(ka.y));
+    // a warp owns 16 tokens (t = warp + 4 i); the global loads of 8 tokens are issued before any reduction
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint2 qa[8], ka[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = warp + 4 * (half * 8 + i);
+        qa[i] = ka[i] = make_uint2(0u, 0u);
+        if (t < nc) {
+          const bf16* xr = p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv;
+          qa[i] = *reinterpret_cast<const uint2*>(xr + qoff + lane * 4);
+          ka[i] = *reinterpret_cast<const uint2*>(xr + koff + lane * 4);
+        }
       }
-      const float qs = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
-      const float ks = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
-      const float qr = t < nc ? rsqrtf(qs + 1e-6f) : 0.f, kr = t < nc ? rsqrtf(ks + 1e-6f) : 0.f;
-      *reinterpret_cast<float4*>(Qs + t * LDK + lane * 4) = make_float4(qv.x * qr, qv.y * qr, qv.z * qr, qv.w * qr);
-      *reinterpret_cast<float4*>(Ks + t * LDK + lane * 4) = make_float4(kv.x * kr, kv.y * kr, kv.z * kr, kv.w * kr);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = warp + 4 * (half * 8 + i);
+        const float4 qv = make_float4(bf16lo_to_f(qa[i].x), bf16hi_to_f(qa[i].x), bf16lo_to_f(qa[i].y), bf16hi_to_f(qa[i].y));
+        const float4 kv = make_float4(bf16lo_to_f(ka[i].x), bf16hi_to_f(ka[i].x), bf16lo_to_f(ka[i].y), bf16hi_to_f(ka[i].y));
+        const float qs = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+        const float ks = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+        const float qr = t < nc ? rsqrtf(qs + 1e-6f) : 0.f, kr = t < nc ? rsqrtf(ks + 1e-6f) : 0.f;
+        *reinterpret_cast<float4*>(Qs + t * LDK + lane * 4) = make_float4(qv.x * qr, qv.y * qr, qv.z * qr, qv.w * qr);
+        *reinterpret_cast<float4*>(Ks + t * LDK + lane * 4) = make_float4(kv.x * kr, kv.y * kr, kv.z * kr, kv.w * kr);
+      }
     }
     for (int i = tid; i < CH * DVL; i += kChThreads) {
       const int t = i / DVL, d = i - t * DVL;
@@ -293,60 +310,50 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
     }
     // ---- p_t = (K S_0^T)[t][dv], r_t = (Q S_0^T)[t][dv]: partial over this thread's 32 k, quad-reduced; thread
     //      `part` keeps the values of its 16 tokens ----
-    float pk[16], rq[16];
-#pragma unroll
+    // (results go to shared memory so the token loops below stay rolled: the code of a chunk fits the
+    //  instruction cache)
+#pragma unroll 2
     for (int t = 0; t < CH; ++t) {
       float a1 = 0.f, a2 = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float4 kx = *reinterpret_cast<const float4*>(Ks + t * LDK + part * 32 + i * 4);
-        const float4 qx = *reinterpret_cast<const float4*>(Qs + t * LDK + part * 32 + i * 4);
+        const float4 kx = *reinterpret_cast<const float4*>(Ks + t * LDK + i * 16 + part * 4);
+        const float4 qx = *reinterpret_cast<const float4*>(Qs + t * LDK + i * 16 + part * 4);
         a1 = fmaf(S[4 * i], kx.x, fmaf(S[4 * i + 1], kx.y, fmaf(S[4 * i + 2], kx.z, fmaf(S[4 * i + 3], kx.w, a1))));
         a2 = fmaf(S[4 * i], qx.x, fmaf(S[4 * i + 1], qx.y, fmaf(S[4 * i + 2], qx.z, fmaf(S[4 * i + 3], qx.w, a2))));
       }
       a1 += __shfl_xor_sync(0xffffffffu, a1, 1); a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
       a2 += __shfl_xor_sync(0xffffffffu, a2, 1); a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
-      if ((t >> 4) == part) { pk[t & 15] = a1; rq[t & 15] = a2; }
+      if (part == 0) { Ps[t * UP + dvl] = a1; Rs[t * UP + dvl] = a2; }
     }
-    __syncthreads();                                       // Lm / Mm are complete
-    // ---- forward substitution for this dv column of U; u_t lives in thread (t >> 4) of the quad ----
-    float u[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) u[i] = 0.f;
-#pragma unroll
+    __syncthreads();                                       // Lm / Mm / Ps / Rs are complete
+    // ---- forward substitution for this dv column of U (in Us); the four threads of a quad split the sum over j ----
+#pragma unroll 1
     for (int t = 0; t < CH; ++t) {
       float sacc = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) sacc = fmaf(Lm[t * (CH + 1) + part * 16 + i], u[i], sacc);   // rows j >= t are zero
+      for (int j = part; j < t; j += 4) sacc = fmaf(Lm[t * (CH + 1) + j], Us[j * UP + dvl], sacc);
       sacc += __shfl_xor_sync(0xffffffffu, sacc, 1); sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
-      if ((t >> 4) == part) {
-        const float gam = __expf(Gs[t]);
-        u[t & 15] = Bs[t] * (Vs[t * DVL + dvl] - gam * pk[t & 15]) - sacc;
-      }
+      if (part == 0) Us[t * UP + dvl] = Bs[t] * (Vs[t * DVL + dvl] - __expf(Gs[t]) * Ps[t * UP + dvl]) - sacc;
+      __syncwarp();
     }
     // ---- outputs ----
-#pragma unroll
-    for (int t = 0; t < CH; ++t) {
+#pragma unroll 1
+    for (int t = 0; t < nc; ++t) {
       float oacc = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) oacc = fmaf(Mm[t * (CH + 1) + part * 16 + i], u[i], oacc);
+      for (int j = part; j <= t; j += 4) oacc = fmaf(Mm[t * (CH + 1) + j], Us[j * UP + dvl], oacc);
       oacc += __shfl_xor_sync(0xffffffffu, oacc, 1); oacc += __shfl_xor_sync(0xffffffffu, oacc, 2);
-      if ((t >> 4) == part && t < nc)
-        p.o_raw[(size_t)(r0 + c0 + t) * p.ld_o + vh * D + dv] = (__expf(Gs[t]) * rq[t & 15] + oacc) * inv_sqrt_d;
+      if (part == 0) p.o_raw[(size_t)(r0 + c0 + t) * p.ld_o + vh * D + dv] = (__expf(Gs[t]) * Rs[t * UP + dvl] + oacc) * inv_sqrt_d;
     }
     // ---- state: S = gamma_C S + sum_j (gamma_C / gamma_j) u_j k_j^T over this thread's 32 k ----
-#pragma unroll
-    for (int i = 0; i < 16; ++i) Us[(part * 16 + i) * (DVL + 1) + dvl] = u[i];
-    __syncwarp();                                           // a quad's four threads share a warp
     const float gC = Gs[CH - 1];
     const float gamC = __expf(gC);
 #pragma unroll
     for (int i = 0; i < 32; ++i) S[i] *= gamC;
     for (int j = 0; j < CH; ++j) {
-      const float cu = __expf(gC - Gs[j]) * Us[j * (DVL + 1) + dvl];
+      const float cu = __expf(gC - Gs[j]) * Us[j * UP + dvl];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float4 kx = *reinterpret_cast<const float4*>(Ks + j * LDK + part * 32 + i * 4);
+        const float4 kx = *reinterpret_cast<const float4*>(Ks + j * LDK + i * 16 + part * 4);
         S[4 * i] = fmaf(cu, kx.x, S[4 * i]); S[4 * i + 1] = fmaf(cu, kx.y, S[4 * i + 1]);
         S[4 * i + 2] = fmaf(cu, kx.z, S[4 * i + 2]); S[4 * i + 3] = fmaf(cu, kx.w, S[4 * i + 3]);
       }
@@ -354,7 +361,7 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i)
-    reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+    reinterpret_cast<float4*>(sp)[4 * i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
 }
 
 // out = rms_norm(o_raw) * w * silu(z) per (row, v head)
@@ -409,7 +416,7 @@ GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_
   p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias; p.state = (float*)state;
   p.run_slot = (const int*)run_slot; p.run_start = (const int*)run_start; p.run_len = (const int*)run_len;
   p.o_raw = (float*)o_raw; p.ld_o = Hv * D; p.Hk = Hk; p.Hv = Hv;
-  const size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 2 * CH * (CH + 1) + CH * (DVL + 1) + 2 * CH);
+  const size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 2 * CH * (CH + 1) + 3 * CH * UP + 2 * CH);
   static bool configured = false;
   cudaStream_t st = (cudaStream_t)stream;
   if (!configured) {
