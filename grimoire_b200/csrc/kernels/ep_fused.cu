@@ -9,7 +9,7 @@
 //                receive region and records where the result has to come back; the last CTA raises a
 //                per-source flag on every owner (release at system scope)
 //   ep_plan      owner: waits (bounded) for the W source flags, turns the W x E_local group descriptors
-//                into 16-row tiles (expert-major, so an expert's weights stay hot in L2)
+//                into 32-row tiles (expert-major, so an expert's weights stay hot in L2)
 //   grouped GEMM gate|up + SwiGLU on the received rows, then the down projection whose epilogue stores
 //                each fp32 result row into the SOURCE rank's return buffer and bumps its arrival counter
 //   ep_combine   source: waits (bounded) for all its rows, h += sum_j w_j * y_j in fixed slot order
@@ -132,6 +132,8 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const DispatchParams p
 }
 
 // ---------------------------------------------------------------------------------------------
+constexpr int kPlanRows = 32;      // rows per tile: the grouped kernel's tile height (moe.cu: kTileRows)
+
 struct PlanParams {
   const unsigned int* flags;  // [W] (local)
   const int* groups;          // [W * E_loc][2] (local)
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(512) ep_plan_kernel(const PlanParams p) {
       const int2 g = reinterpret_cast<const int2*>(p.groups)[(size_t)s * p.E_loc + el];
       row0 = g.x; cnt = g.y;
     }
-    const int nt = (cnt + 15) >> 4;
+    const int nt = (cnt + kPlanRows - 1) / kPlanRows;
     int v = nt;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -176,7 +178,8 @@ __global__ void __launch_bounds__(512) ep_plan_kernel(const PlanParams p) {
     int off = before + v - nt;
     for (int t = 0; t < nt; ++t, ++off) {
       if (off >= p.max_tiles) break;
-      p.tile_expert[off] = el; p.tile_row0[off] = row0 + 16 * t; p.tile_rows[off] = min(16, cnt - 16 * t); p.tile_src[off] = s;
+      p.tile_expert[off] = el; p.tile_row0[off] = row0 + kPlanRows * t; p.tile_rows[off] = min(kPlanRows, cnt - kPlanRows * t);
+      p.tile_src[off] = s;
     }
     __syncthreads();
     if (tid == 511) s_base = before + v;

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
-// grouped GEMM: tile = 16 rows of one expert x 128 output columns.
+// grouped GEMM: tile = up to 32 rows of one expert x 128 output columns.
 // ---------------------------------------------------------------------------------------------
 struct GroupedParams {
   const bf16* x; int ldx;           // activations [rows][K]
@@ -103,32 +103,40 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 // MODE 4 (expert parallel combine): the fp32 result rows are stored straight into the return buffer of
 // the rank that owns the token (peer stores over NVLink), then the tile raises that rank's arrival
 // counter with a system-scope release, so the owner's weighted top-k sum can start as rows land.
+constexpr int kTileRows = 32;       // rows of one tile: two m16 tiles share every converted weight fragment
+constexpr float kScaleLift = 4096.f; // block scales are lifted by 2^12 before their f16 conversion (small scales would be
+                                     // f16 subnormals) and the accumulators are lowered by 2^-12 in the epilogue (exact)
+
 template <int MODE>
 __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedParams p) {
-  __shared__ __align__(16) __half xs[16][128 + 8];     // one 128-wide K block of the tile's rows, f16
+  __shared__ __align__(16) __half xs[kTileRows][128 + 8];     // one 128-wide K block of the tile's rows, f16
   const int tile = blockIdx.x, nblk = blockIdx.y;
   if (p.n_tiles_dev && tile >= *p.n_tiles_dev) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = p.tile_rows[tile];
+  const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = min(p.tile_rows[tile], kTileRows);
   const int NO = MODE == 0 ? p.N / 2 : p.N;             // output columns
   const int col0 = nblk * 128 + warp * 32;              // this warp's first output column
   const int KB = p.K / 128;
   const uint8_t* we = p.w + (size_t)e * p.N * p.K;
   const float* se = p.scale + (size_t)e * p.N * KB;
   constexpr int NB = MODE == 0 ? 2 : 1;                 // weight row groups per output column (gate, up)
-  float acc[NB][4][4];
+  constexpr int MTL = kTileRows / 16;
+  const bool two = nr > 16;                             // second m tile in use
+  float acc[MTL][NB][4][4];
 #pragma unroll
-  for (int b = 0; b < NB; ++b)
+  for (int m = 0; m < MTL; ++m)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int b = 0; b < NB; ++b)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) acc[b][i][c] = 0.f;
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[m][b][i][c] = 0.f;
 
   for (int kb = 0; kb < KB; ++kb) {
     __syncthreads();
-    // stage x rows [16][128] as f16 (rows beyond the tile are zero)
-    for (int i = tid; i < 16 * 16; i += kGThreads) {
+    // stage x rows [32][128] as f16 (rows beyond the tile are zero)
+    for (int i = tid; i < kTileRows * 16; i += kGThreads) {
       const int r = i >> 4, c8 = i & 15;
       uint4 o = make_uint4(0u, 0u, 0u, 0u);
       if (r < nr) {
@@ -145,14 +153,18 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedPar
       }
       *reinterpret_cast<uint4*>(&xs[r][c8 * 8]) = o;
     }
-    __syncthreads();
-    float part[NB][4][4];
+    // block scale of this 128-wide K block for the weight row (= B column) this lane converts: n = col0 + 8 i + g.
+    // The scale is folded into the f16 weights before the MMA (e4m3 * scale is the weight itself, well inside
+    // f16 range), so the products accumulate straight into fp32.
+    __half2 sc2[NB][4];
 #pragma unroll
     for (int b = 0; b < NB; ++b)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) part[b][i][c] = 0.f;
+      for (int i = 0; i < 4; ++i) {
+        const int n = col0 + i * 8 + g;
+        sc2[b][i] = __float2half2_rn(n < NO ? se[(size_t)(n + b * NO) * KB + kb] * kScaleLift : 0.f);
+      }
+    __syncthreads();
     // two 64-wide halves; lane t owns k columns [16t, 16t+16) of a half (A and B use the same K order)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -170,6 +182,11 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedPar
         // A fragment: rows g / g+8, k slots (2t,2t+1) <- columns 16t+4j, +1 ; (2t+8,2t+9) <- 16t+4j+2, +3
         const uint2 xa = *reinterpret_cast<const uint2*>(&xs[g][half * 64 + t * 16 + j * 4]);
         const uint2 xb = *reinterpret_cast<const uint2*>(&xs[g + 8][half * 64 + t * 16 + j * 4]);
+        uint2 xc = make_uint2(0u, 0u), xd = xc;
+        if (two) {
+          xc = *reinterpret_cast<const uint2*>(&xs[g + 16][half * 64 + t * 16 + j * 4]);
+          xd = *reinterpret_cast<const uint2*>(&xs[g + 24][half * 64 + t * 16 + j * 4]);
+        }
 #pragma unroll
         for (int b = 0; b < NB; ++b)
 #pragma unroll
@@ -177,41 +194,35 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const GroupedPar
             const uint32_t wq = j == 0 ? wv[b][i].x : (j == 1 ? wv[b][i].y : (j == 2 ? wv[b][i].z : wv[b][i].w));
             uint32_t b0, b1;
             cvt_e4m3x4_to_f16x2x2(wq, b0, b1);
-            mma_f16_16816(part[b][i], xa.x, xb.x, xa.y, xb.y, b0, b1);
+            const __half2 h0 = __hmul2(*reinterpret_cast<const __half2*>(&b0), sc2[b][i]);
+            const __half2 h1 = __hmul2(*reinterpret_cast<const __half2*>(&b1), sc2[b][i]);
+            b0 = *reinterpret_cast<const uint32_t*>(&h0); b1 = *reinterpret_cast<const uint32_t*>(&h1);
+            mma_f16_16816(acc[0][b][i], xa.x, xb.x, xa.y, xb.y, b0, b1);
+            if (two) mma_f16_16816(acc[1][b][i], xc.x, xd.x, xc.y, xd.y, b0, b1);
           }
       }
     }
-    // block scale of this 128-wide K block: columns 2t, 2t+1 of each n8 tile
-#pragma unroll
-    for (int b = 0; b < NB; ++b)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int n = col0 + i * 8 + 2 * t;
-        const float s0 = (n < NO) ? se[(size_t)(n + b * NO) * KB + kb] : 0.f;
-        const float s1 = (n + 1 < NO) ? se[(size_t)(n + 1 + b * NO) * KB + kb] : 0.f;
-        acc[b][i][0] = fmaf(s0, part[b][i][0], acc[b][i][0]);
-        acc[b][i][1] = fmaf(s1, part[b][i][1], acc[b][i][1]);
-        acc[b][i][2] = fmaf(s0, part[b][i][2], acc[b][i][2]);
-        acc[b][i][3] = fmaf(s1, part[b][i][3], acc[b][i][3]);
-      }
   }
+  constexpr float kInvLift = 1.f / kScaleLift;
   // epilogue: c0,c1 = (row g, cols 2t, 2t+1); c2,c3 = (row g+8, same cols)
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int m = 0; m < MTL; ++m)
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int r = g + 8 * (c >> 1), n = col0 + i * 8 + 2 * t + (c & 1);
-      if (r >= nr || n >= NO) continue;
-      if (MODE == 4) {
-        p.peer_y[p.tile_src[tile]][(size_t)p.row_dst[r0 + r] * p.ldo + n] = acc[0][i][c];
-        continue;
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = 16 * m + g + 8 * (c >> 1), n = col0 + i * 8 + 2 * t + (c & 1);
+        if (r >= nr || n >= NO) continue;
+        if (MODE == 4) {
+          p.peer_y[p.tile_src[tile]][(size_t)p.row_dst[r0 + r] * p.ldo + n] = (acc[m][0][i][c] * kInvLift);
+          continue;
+        }
+        const size_t o = (size_t)(r0 + r) * p.ldo + n;
+        if (MODE == 0) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(silu_f((acc[m][0][i][c] * kInvLift)) * (acc[m][NB - 1][i][c] * kInvLift));
+        else if (MODE == 1) reinterpret_cast<float*>(p.out)[o] = (acc[m][0][i][c] * kInvLift);
+        else if (MODE == 2) reinterpret_cast<float*>(p.out)[o] += (acc[m][0][i][c] * kInvLift);
+        else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16((acc[m][0][i][c] * kInvLift));
       }
-      const size_t o = (size_t)(r0 + r) * p.ldo + n;
-      if (MODE == 0) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(silu_f(acc[0][i][c]) * acc[NB - 1][i][c]);
-      else if (MODE == 1) reinterpret_cast<float*>(p.out)[o] = acc[0][i][c];
-      else if (MODE == 2) reinterpret_cast<float*>(p.out)[o] += acc[0][i][c];
-      else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16(acc[0][i][c]);
-    }
   if (MODE == 4) {
     __syncthreads();
     if (tid == 0) {

@@ -91,7 +91,7 @@ class ExpertParallel:
         z = lambda *s, dt=i32: torch.zeros(*s, dtype=dt, device=dev)
         self.state = z(16)
         self.counts, self.ebase, self.cursors = z(self.E), z(self.E), z(self.E)
-        self.max_tiles = (W * self.cap + 15) // 16 + W * self.E_loc
+        self.max_tiles = (W * self.cap + 31) // 32 + W * self.E_loc
         self.tile_expert, self.tile_row0, self.tile_rows, self.tile_src = (z(self.max_tiles) for _ in range(4))
         self.n_tiles = z(1)
         self.act = z(W * self.cap, self.I, dt=bf)
@@ -122,7 +122,7 @@ class ExpertParallel:
                                       _native.ptr(self.tile_row0), _native.ptr(self.tile_rows), _native.ptr(self.tile_src),
                                       _native.ptr(self.n_tiles), _native.ptr(self.state), _c(self.E_loc), _c(W), _c(self.max_tiles),
                                       ctypes.c_uint(self.spin), st), "ep_plan")
-        bound = min(self.max_tiles, (W * Mq * k + 15) // 16 + min(W * self.E_loc, W * Mq * k))
+        bound = min(self.max_tiles, (W * Mq * k + 31) // 32 + min(W * self.E_loc, W * Mq * k))
         N1, I = moe.gate_up.shape[1], self.I
         _native.check(lib.grm_moe_grouped_gemm_ep(
             _native.ptr(self.xrecv.local), _c(H), _native.ptr(self.tile_expert), _native.ptr(self.tile_row0), _native.ptr(self.tile_rows),
