@@ -1,0 +1,304 @@
+// flash_prefill_tc: causal attention of a prompt chunk on the 5th-generation tensor cores (head_dim 128).
+// Same contract as flash_prefill (attn_prefill.cu): M query rows of ONE sequence at positions q_pos0.. over
+// T = q_pos0 + M keys, GQA, optional sliding window; K dense bf16 [T][Hkv*128]; V is consumed TRANSPOSED
+// (vt [Hkv*128][ldt], key index contiguous) so both products take K-major operands.
+//
+// Role in the reference: flash prefill on the matrix unit (flash_fast_impl, src/gemm_fast.cpp:832-1375,
+// 17.9 TFLOP/s quoted there).  Design for sm_100a:
+//   CTA = 128 query rows of one head, 128 threads (thread = row = TMEM lane), 64-key blocks.
+//   S = Q K^T : tcgen05.mma 128x64x128, operands brought by TMA into 128-byte-swizzled shared memory,
+//               accumulator in TMEM; each thread reads its row with tcgen05.ld, so the online softmax
+//               needs no cross-thread reduction;
+//   P (bf16) is written back to shared memory in the same swizzled K-major layout and
+//   O_blk = P V : tcgen05.mma 128x128x64 into a second TMEM region, read back and folded into per-thread
+//               fp32 accumulators with the softmax rescale.
+//   The next K / V tiles are requested as soon as the MMA that read the current ones has committed.
+// Two CTAs per SM (80 KB shared memory, 256 TMEM columns each) overlap one CTA's softmax with the other's
+// MMAs.  Every mbarrier wait is bounded; on a timeout the CTA records the error, frees its TMEM and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace {
+
+constexpr int D = 128, BQ = 128, BKV = 64, kThreads = 128;
+constexpr int kQBytes = BQ * D * 2, kKBytes = BKV * D * 2, kVBytes = D * BKV * 2, kPBytes = BQ * BKV * 2;
+constexpr int kSmem = kQBytes + kKBytes + kVBytes + kPBytes + 256 + 1024;
+constexpr uint32_t kTmemCols = 256;       // S: columns [0, 64), O_blk: columns [64, 192)
+
+struct TcParams {
+  bf16* out; int ld_o;
+  int M, T, Hq, Hkv, q_pos0, window;
+  float scale_log2;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                         // 2 boxes of [128 rows][64 dims]
+  uint8_t* sK = sQ + kQBytes;                 // 2 boxes of [64 keys][64 dims]
+  uint8_t* sV = sK + kKBytes;                 // [128 dims][64 keys]
+  uint8_t* sP = sV + kVBytes;                 // [128 rows][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);     // 0 Q, 1 K, 2 V, 3 S done, 4 O done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qb = blockIdx.x, h = blockIdx.y;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int row = qb * BQ + tid;              // query row of this thread inside the chunk
+  const bool row_ok = row < p.M;
+  const int q_pos = p.q_pos0 + row;
+  const int last_q = p.q_pos0 + min(p.M, (qb + 1) * BQ) - 1;
+  const int first_q = p.q_pos0 + qb * BQ;
+  const int kb_lo = p.window > 0 ? max(0, first_q - p.window + 1) / BKV : 0;
+  const int kb_hi = last_q / BKV;             // inclusive
+
+  if (tid == 0) {
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+  auto load_k = [&](int kb) {
+    mbar_expect_tx(&bars[1], kKBytes);
+    tma_load_2d(sK, &tmK, &bars[1], kvh * D, kb * BKV);
+    tma_load_2d(sK + kKBytes / 2, &tmK, &bars[1], kvh * D + 64, kb * BKV);
+  };
+  auto load_v = [&](int kb) {
+    mbar_expect_tx(&bars[2], kVBytes);
+    tma_load_2d(sV, &tmV, &bars[2], kb * BKV, kvh * D);
+  };
+  if (tid == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    mbar_expect_tx(&bars[0], kQBytes);
+    tma_load_2d(sQ, &tmQ, &bars[0], h * D, qb * BQ);
+    tma_load_2d(sQ + kQBytes / 2, &tmQ, &bars[0], h * D + 64, qb * BQ);
+    load_k(kb_lo);
+    load_v(kb_lo);
+  }
+
+  float o[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  constexpr uint32_t idesc_s = make_idesc(BQ, BKV, 1, 1);
+  constexpr uint32_t idesc_o = make_idesc(BQ, D, 1, 1);
+  bool ok = true;
+
+  for (int kb = kb_lo; kb <= kb_hi && ok; ++kb) {
+    const uint32_t par = (uint32_t)(kb - kb_lo) & 1u;
+    // ---- S = Q K^T ----
+    if (tid == 0) {
+      bool good = true;
+      if (kb == kb_lo) good = mbar_wait(&bars[0], 0u, p.status, 0x800u);
+      good = good && mbar_wait(&bars[1], par, p.status, 0x801u);
+      if (good) {
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * (kQBytes / 2)) + (uint64_t)((k & 3) * 2);
+          const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * (kKBytes / 2)) + (uint64_t)((k & 3) * 2);
+          tc_mma_f16(tmem_base, da, db, idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[3]);
+      } else {
+        *s_abort = 1;
+      }
+    }
+    if (!mbar_wait(&bars[3], par, p.status, 0x803u)) { ok = false; break; }
+    tc_fence_after();
+    if (tid == 0 && kb < kb_hi) load_k(kb + 1);            // the S MMAs have read K
+    // ---- softmax of this thread's row ----
+    float sv[BKV];
+    {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
+      tmem_ld_32x32b_x32(t_row + 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sv[32 + i] = __uint_as_float(r[i]);
+    }
+    float mx = -INFINITY;
+    const int key0 = kb * BKV;
+    const bool need_mask = (key0 + BKV - 1 > first_q) || (p.window > 0) || !row_ok;
+#pragma unroll
+    for (int i = 0; i < BKV; ++i) {
+      float s = sv[i] * p.scale_log2;
+      if (need_mask) {
+        const int kp = key0 + i;
+        const bool vis = row_ok && kp <= q_pos && (p.window <= 0 || kp > q_pos - p.window);
+        s = vis ? s : -INFINITY;
+      }
+      sv[i] = s;
+      mx = fmaxf(mx, s);
+    }
+    const float m_new = fmaxf(m_run, mx);
+    const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    float psum = 0.f;
+    uint32_t pk[BKV / 2];
+#pragma unroll
+    for (int i = 0; i < BKV; i += 2) {
+      const float p0 = ex2(sv[i] - m_use), p1 = ex2(sv[i + 1] - m_use);
+      psum += p0 + p1;
+      pk[i >> 1] = pack_bf16x2(p0, p1);
+    }
+    m_run = m_new;
+    l_run = l_run * alpha + psum;
+    // P -> shared memory, K-major rows of 128 bytes with the 16-byte chunks XOR-swizzled by (row & 7)
+    {
+      uint8_t* prow = sP + tid * 128;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(prow + ((j ^ (tid & 7)) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    // ---- O_blk = P V ----
+    if (tid == 0) {
+      if (!*s_abort && mbar_wait(&bars[2], par, p.status, 0x802u)) {
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_f16(tmem_base + 64, make_sw128_kmajor_desc(pa) + (uint64_t)(k * 2), make_sw128_kmajor_desc(va) + (uint64_t)(k * 2), idesc_o,
+                     k != 0 ? 1u : 0u);
+        tc_commit(&bars[4]);
+      } else {
+        *s_abort = 1;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] *= alpha;
+    if (!mbar_wait(&bars[4], par, p.status, 0x804u)) { ok = false; break; }
+    tc_fence_after();
+    if (tid == 0 && kb < kb_hi) load_v(kb + 1);            // the O MMAs have read V (and P)
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+    }
+    tc_fence_before();
+    __syncthreads();                                       // S / O_blk / P may be overwritten by the next block
+    tc_fence_after();
+  }
+
+  if (ok && row_ok) {
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    bf16* dst = p.out + (size_t)row * p.ld_o + (size_t)h * D;
+#pragma unroll
+    for (int i = 0; i < D; i += 8) {
+      uint4 v;
+      v.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv); v.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+      v.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv); v.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + i) = v;
+    }
+  }
+  if (!ok && tid == 0) {
+    // let copies in flight land before the shared memory is handed to another CTA (bounded)
+    for (int b = 1; b <= 2; ++b)
+      for (int i = 0; i < 200000 && !mbar_try_wait(&bars[b], 0u) && !mbar_try_wait(&bars[b], 1u); ++i) __nanosleep(64);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// v [T][ld] (this kv head block of 128 columns at col0) -> vt [128][ldt]: 32x32 tiles through shared memory
+__global__ void __launch_bounds__(256) kv_transpose_kernel(const bf16* __restrict__ v, int ld, bf16* __restrict__ vt, int ldt, int T, int cols) {
+  __shared__ bf16 tile[32][33];
+  const int t0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const int t = t0 + r, c = c0 + tx;
+    tile[r][tx] = (t < T && c < cols) ? v[(size_t)t * ld + c] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int c = c0 + r, t = t0 + tx;
+    if (c < cols && t < ldt) vt[(size_t)c * ldt + t] = tile[tx][r];
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+// 2-D bf16 row-major [rows][cols], box = box_rows x 64 columns, 128-byte swizzle, zero fill outside
+int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -3;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * 2) & 15)) return -2;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld * 2};
+  const cuuint32_t box[2] = {64u, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+}  // namespace
+
+// vt: scratch bf16 [Hkv*128][ldt] with ldt >= T rounded up to 64 (filled here from v).  head_dim must be 128.
+GRM_API int grm_flash_prefill_tc(const void* q, int ld_q, const void* k, const void* v, int ld_kv, void* vt, int ldt, void* out, int ld_o,
+                                 int M, int T, int Hq, int Hkv, int Dh, int q_pos0, int window, float scale, void* stream) {
+  if (Dh != D || M < 1 || T < M || Hq % Hkv || (ld_o & 7) || (ldt & 63) || ldt < ((T + 63) / 64) * 64) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  kv_transpose_kernel<<<dim3((ldt + 31) / 32, (Hkv * D + 31) / 32), 256, 0, st>>>((const bf16*)v, ld_kv, (bf16*)vt, ldt, T, Hkv * D);
+  CUtensorMap tq, tk, tv;
+  int e = make_map(&tq, q, (uint64_t)M, (uint64_t)Hq * D, (uint64_t)ld_q, BQ);
+  if (e) return e;
+  e = make_map(&tk, k, (uint64_t)T, (uint64_t)Hkv * D, (uint64_t)ld_kv, BKV);
+  if (e) return e;
+  e = make_map(&tv, vt, (uint64_t)Hkv * D, (uint64_t)ldt, (uint64_t)ldt, D);
+  if (e) return e;
+  TcParams p;
+  p.out = (bf16*)out; p.ld_o = ld_o; p.M = M; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.q_pos0 = q_pos0; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f; p.status = grm_status_ptr();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t ce = cudaFuncSetAttribute(flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (ce != cudaSuccess) return (int)ce;
+    configured = true;
+  }
+  flash_prefill_tc_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreads, kSmem, st>>>(tq, tk, tv, p);
+  GRM_LAUNCH_RET();
+}

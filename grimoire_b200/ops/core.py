@@ -6,6 +6,7 @@ missing native library raises instead of falling back.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -16,6 +17,8 @@ from . import ref
 from .workspace import Workspace
 
 PAGE = 16
+# tcgen05 flash prefill for head_dim 128 (GRIMOIRE_FLASH_TC=0 selects the warp-MMA kernel)
+FLASH_TC = os.environ.get("GRIMOIRE_FLASH_TC", "1") != "0"
 
 
 def _c(v):
@@ -239,6 +242,17 @@ def flash_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, geom: AttnG
         if gate is not None:
             o = o * torch.sigmoid(gate.float())
         out.copy_(o.to(out.dtype))
+        return out
+    if D == 128 and gate is None and FLASH_TC and M >= 64:
+        # tcgen05 / TMEM kernel; it consumes V transposed, built per call in a workspace buffer
+        from .workspace import default_workspace
+
+        ldt = (T + 63) // 64 * 64
+        vt = default_workspace(q.device).get("flash_vt", Hkv * D * ldt, torch.bfloat16)
+        code = _native.cuda().grm_flash_prefill_tc(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
+                                                   _native.ptr(vt), _c(ldt), _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq),
+                                                   _c(Hkv), _c(D), _c(q_pos0), _c(geom.window), _f(geom.scale), _native.stream_ptr())
+        _native.check(code, "flash_prefill_tc")
         return out
     code = _native.cuda().grm_flash_prefill(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
                                             _native.ptr(gate), _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq),
