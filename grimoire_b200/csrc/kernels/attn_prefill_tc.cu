@@ -10,8 +10,9 @@
 //               accumulator in TMEM; each thread reads its row with tcgen05.ld, so the online softmax
 //               needs no cross-thread reduction;
 //   P (bf16) is written back to shared memory in the same swizzled K-major layout and
-//   O_blk = P V : tcgen05.mma 128x128x64 into a second TMEM region, read back and folded into per-thread
-//               fp32 accumulators with the softmax rescale.
+//   O += P V    : tcgen05.mma 128x128x64 accumulating in a second TMEM region across all key blocks; a row
+//               whose running maximum moved is rescaled in place (tcgen05.ld / st), which is rare after the first
+//               few blocks; the accumulator is read once at the end.
 //   The next K / V tiles are requested as soon as the MMA that read the current ones has committed.
 // Two CTAs per SM (80 KB shared memory, 256 TMEM columns each) overlap one CTA's softmax with the other's
 // MMAs.  Every mbarrier wait is bounded; on a timeout the CTA records the error, frees its TMEM and returns.
@@ -31,6 +32,20 @@ struct TcParams {
   float scale_log2;
   unsigned int* status;
 };
+
+// registers -> TMEM: 32 lanes x 32 columns of 32-bit (the mirror of tmem_ld_32x32b_x32)
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x) {
   float r;
@@ -95,9 +110,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     load_v(kb_lo);
   }
 
-  float o[D];
-#pragma unroll
-  for (int i = 0; i < D; ++i) o[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   constexpr uint32_t idesc_s = make_idesc(BQ, BKV, 1, 1);
   constexpr uint32_t idesc_o = make_idesc(BQ, D, 1, 1);
@@ -167,6 +179,20 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     m_run = m_new;
     l_run = l_run * alpha + psum;
+    // O stays in TMEM across blocks; a row whose running maximum moved is rescaled in place.  After the first few
+    // blocks of a row this is rare, so the branch is taken per warp only when one of its rows needs it.
+    if (kb > kb_lo && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st_32x32b_x32(t_row + 64 + c * 32, r);
+      }
+      tmem_st_wait();
+    }
     // P -> shared memory, K-major rows of 128 bytes with the 16-byte chunks XOR-swizzled by (row & 7)
     {
       uint8_t* prow = sP + tid * 128;
@@ -185,39 +211,36 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
           tc_mma_f16(tmem_base + 64, make_sw128_kmajor_desc(pa) + (uint64_t)(k * 2), make_sw128_kmajor_desc(va) + (uint64_t)(k * 2), idesc_o,
-                     k != 0 ? 1u : 0u);
+                     (k != 0 || kb != kb_lo) ? 1u : 0u);
         tc_commit(&bars[4]);
       } else {
         *s_abort = 1;
       }
     }
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] *= alpha;
     if (!mbar_wait(&bars[4], par, p.status, 0x804u)) { ok = false; break; }
     tc_fence_after();
     if (tid == 0 && kb < kb_hi) load_v(kb + 1);            // the O MMAs have read V (and P)
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
-    }
-    tc_fence_before();
-    __syncthreads();                                       // S / O_blk / P may be overwritten by the next block
-    tc_fence_after();
   }
 
-  if (ok && row_ok) {
+  if (ok) {
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     bf16* dst = p.out + (size_t)row * p.ld_o + (size_t)h * D;
 #pragma unroll
-    for (int i = 0; i < D; i += 8) {
-      uint4 v;
-      v.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv); v.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
-      v.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv); v.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + i) = v;
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);          // warp-wide: every lane takes part, rows beyond M skip the store
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+        }
+      }
     }
   }
   if (!ok && tid == 0) {
