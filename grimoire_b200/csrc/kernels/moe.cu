@@ -20,7 +20,7 @@ constexpr int kMaxExpertsPerLane = 16;   // E <= 512
 
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int ld, int M, int E, int top_k, int renorm,
                                                         int* __restrict__ ids, int ld_ids, float* __restrict__ weights, int ld_w,
-                                                        int* __restrict__ counts) {
+                                                        int* __restrict__ counts, int shared_gate) {
   const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (row >= M) return;
   const float* lg = logits + (size_t)row * ld;
@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
     weights[(size_t)row * ld_w + lane] = renorm ? mine_w / wsum : mine_w;
     if (counts) atomicAdd(&counts[mine_id], 1);
   }
+  // shared expert: its weight sigmoid(logits[E]) goes to slot top_k of the row (the caller's rows have top_k + 1 slots)
+  if (shared_gate && lane == 0) weights[(size_t)row * ld_w + top_k] = sigmoid_f(lg[E]);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -385,12 +387,12 @@ __global__ void moe_combine_kernel(float* __restrict__ h, int ldh, const float* 
 }  // namespace
 
 GRM_API int grm_moe_route(const void* logits, int ld, int M, int E, int top_k, int renorm, void* ids, int ld_ids, void* weights,
-                          int ld_w, void* counts, void* stream) {
+                          int ld_w, void* counts, int shared_gate, void* stream) {
   if (E < 1 || E > 32 * kMaxExpertsPerLane || top_k < 1 || top_k > 32 || top_k > E) return -2;
   const int threads = 128;
   const int blocks = (M * 32 + threads - 1) / threads;
   moe_route_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const float*)logits, ld, M, E, top_k, renorm, (int*)ids, ld_ids,
-                                                                (float*)weights, ld_w, (int*)counts);
+                                                                (float*)weights, ld_w, (int*)counts, shared_gate);
   GRM_LAUNCH_RET();
 }
 

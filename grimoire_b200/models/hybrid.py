@@ -93,6 +93,18 @@ class HybridBuffers:
         self.run_len = torch.ones(max_rows, dtype=torch.int32, device=dev)
         self.tile_row0, self.tile_rows, self.tile_src = ar, torch.ones_like(ar), (ar // k).to(torch.int32)
         self.max_rows, self.max_logit_rows = max_rows, max_logit_rows
+        self._k = k
+        self._decode_pos: dict[int, torch.Tensor] = {}
+
+    def decode_pos(self, M: int) -> torch.Tensor:
+        t = self._decode_pos.get(M)
+        if t is None:
+            k, dev = self._k, self.pos.device
+            t = torch.empty(M, k + 1, dtype=torch.int32, device=dev)
+            t[:, :k] = torch.arange(M * k, dtype=torch.int32, device=dev).reshape(M, k)
+            t[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=dev)
+            self._decode_pos[M] = t
+        return t
 
 
 class HybridModel:
@@ -247,12 +259,11 @@ class HybridModel:
                 self.ep.moe_allreduce(moe, x, h, lg, M, cfg.norm_topk_prob)
             return
         ids, wts = buf.ids[:M], buf.wts[:M]
-        Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts[:, :k])
-        wts[:, k] = torch.sigmoid(lg[:, E])
+        Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts, shared_gate=True)
         act, y, pos = buf.act[: M * k], buf.y[: M * (k + 1)], buf.pos[:M]
         if decode:
             te, r0, nr, src = ids.reshape(-1), buf.tile_row0[: M * k], buf.tile_rows[: M * k], buf.tile_src[: M * k]
-            pos[:, :k] = buf.tile_row0[: M * k].reshape(M, k)
+            pos = buf.decode_pos(M)          # static for a row count: slot j of row m is grouped row m*k + j, shared at M*k + m
         else:
             flat = ids.reshape(-1).long()
             order = torch.sort(flat, stable=True).indices
@@ -273,7 +284,8 @@ class HybridModel:
         # shared expert as slot k of the combine
         moe.shared_gu(x, buf.act_s[:M], "swiglu")
         moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
-        pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
+        if not decode:
+            pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
         Hb.moe_combine(h, y, pos, wts)
 
     def forward(self, rb: RowBatch, buf: HybridBuffers, kv_layers, block_table) -> torch.Tensor:

@@ -124,18 +124,22 @@ class FP8BlockLinear:
 # routing / combine
 # ---------------------------------------------------------------------------------------------
 def moe_route(logits: torch.Tensor, E: int, top_k: int, renorm: bool, ids: torch.Tensor, wts: torch.Tensor,
-              counts: Optional[torch.Tensor] = None):
+              counts: Optional[torch.Tensor] = None, shared_gate: bool = False):
+    """Softmax top-k routing.  ``shared_gate``: wts has top_k + 1 columns and column top_k receives
+    sigmoid(logits[:, E]), the shared expert's weight."""
     M = logits.shape[0]
     if not logits.is_cuda:
         i, w = moe_ref.route(logits[:, :E], top_k, renorm)
         ids.copy_(i.to(ids.dtype))
-        wts.copy_(w)
+        wts[:, :top_k].copy_(w)
+        if shared_gate:
+            wts[:, top_k] = torch.sigmoid(logits[:, E].float())
         if counts is not None:
             counts += torch.bincount(i.flatten(), minlength=counts.shape[0]).to(counts.dtype)
         return ids, wts
     code = _native.cuda().grm_moe_route(_native.ptr(logits), _c(logits.stride(0)), _c(M), _c(E), _c(top_k), _c(1 if renorm else 0),
                                         _native.ptr(ids), _c(ids.stride(0)), _native.ptr(wts), _c(wts.stride(0)), _native.ptr(counts),
-                                        _native.stream_ptr())
+                                        _c(1 if shared_gate else 0), _native.stream_ptr())
     _native.check(code, "moe_route")
     return ids, wts
 

@@ -108,6 +108,9 @@ class W4Linear:
             while want > 1 and G % want:
                 want -= 1
             ksplit = max(1, want)
+        force = int(os.environ.get("GRIMOIRE_SMALLM_KSPLIT", "0"))      # tuning override
+        if force > 0 and G % force == 0 and not self.swiglu:
+            ksplit = force
         return rows, ksplit, tiles
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:

@@ -110,8 +110,7 @@ class ExpertParallel:
         xs, hs, lgs, idl, wl = x[lo: lo + n], h[lo: lo + n], lg[lo: lo + n], ids[:n], wts[:n]
         self.counts.zero_()
         if n:
-            Hb.moe_route(lgs, E, k, renorm, idl, wl[:, :k], self.counts)
-            wl[:, k] = torch.sigmoid(lgs[:, E])
+            Hb.moe_route(lgs, E, k, renorm, idl, wl, self.counts, shared_gate=True)
         _native.check(lib.grm_ep_prefix(_native.ptr(self.counts), _native.ptr(self.ebase), _native.ptr(self.cursors),
                                         self.groups.ptr_array(), _c(E), _c(self.E_loc), _c(W), _c(self.rank), _c(self.cap), st), "ep_prefix")
         _native.check(lib.grm_ep_dispatch(_native.ptr(xs) if n else None, _c(x.stride(0)), _native.ptr(idl), _c(ids.stride(0)),
