@@ -62,15 +62,40 @@ class Grimoire:
         else:
             from .tokenizer import Tokenizer
 
-            cfg = ModelConfig.from_dir(ec.model)
-            why = unsupported_reason(cfg, ec)
-            if why:
-                raise UnsupportedModel(why)
-            if ec.proj not in ("int4", "native"):
-                raise UnsupportedModel(f"--proj {ec.proj}: this build serves int4 projections (bf16 lm_head optional)")
-            model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16))
-            if os.path.exists(os.path.join(ec.model, "tokenizer.json")):
-                tok = Tokenizer(ec.model)
+            if ec.proj not in ("int4", "mxfp4", "native"):
+                raise UnsupportedModel(f"--proj {ec.proj}: this build serves int4 (g128) and mxfp4 projections (bf16 lm_head optional)")
+            if ec.model.endswith(".gguf"):
+                # GGUF: config and tokenizer from the metadata, tensors dequantised block by block and re-quantised
+                # to the serving format (the reference's native GGUF path keeps the file's blocks; this one does not)
+                import dataclasses
+                import json as _json
+                import tempfile
+                from .formats import gguf as G
+
+                gf = G.GGUFFile(ec.model)
+                cfg = G.config_from_gguf(gf)
+                if ec.proj == "mxfp4":
+                    cfg = dataclasses.replace(cfg, quant="mxfp4")
+                why = unsupported_reason(cfg, ec)
+                if why:
+                    raise UnsupportedModel(why)
+                model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world)
+                tj = G.tokenizer_json_from_gguf(gf)
+                if tj is not None:
+                    tdir = tempfile.mkdtemp(prefix="grimoire_tok_")
+                    with open(os.path.join(tdir, "tokenizer.json"), "w") as f:
+                        _json.dump(tj, f)
+                    tok = Tokenizer(tdir)
+                gf.close()
+            else:
+                cfg = ModelConfig.from_dir(ec.model)
+                why = unsupported_reason(cfg, ec)
+                if why:
+                    raise UnsupportedModel(why)
+                model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
+                                                   proj=ec.proj)
+                if os.path.exists(os.path.join(ec.model, "tokenizer.json")):
+                    tok = Tokenizer(ec.model)
         if tp is not None:
             tp.attach(model, max_rows=max(ec.prefill_chunk, 64))
         lim = EngineLimits(max_slots=ec.seq_slots, max_ctx=ec.ctx, prefill_chunk=ec.prefill_chunk, max_decode_rows=64,

@@ -226,7 +226,7 @@ class DenseModel:
 
     @staticmethod
     def from_checkpoint(path, device, tp_rank: int = 0, tp_world: int = 1, workspace: Optional[Workspace] = None,
-                        lm_head_bf16: bool = False, pp_rank: int = 0, pp_world: int = 1) -> "DenseModel":
+                        lm_head_bf16: bool = False, pp_rank: int = 0, pp_world: int = 1, proj: str = "int4") -> "DenseModel":
         """Load a HF directory (safetensors shards; bf16 / GPTQ / compressed-tensors / fp8 / NVFP4
         projections) and serve it with int4-g128 projections.  Stored int4 is repacked, anything
         else is dequantized and quantized on the host (Grimoire::build, grimoire.cpp:7133-10637)."""
@@ -234,6 +234,10 @@ class DenseModel:
 
         ck = Checkpoint(path)
         cfg = ck.cfg
+        if proj == "mxfp4":
+            import dataclasses
+
+            cfg = dataclasses.replace(cfg, quant="mxfp4")
         m = DenseModel(cfg, device, tp_rank, tp_world, workspace, pp_rank, pp_world)
         for i in range(m.layer_begin, m.layer_end):
             p = f"{ck.prefix}layers.{i}."

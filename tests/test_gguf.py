@@ -88,3 +88,46 @@ def test_container_parser_and_adapter(tmp_path):
     with pytest.raises(ValueError):
         (tmp_path / "bad.gguf").write_bytes(b"GGUX" + b"\0" * 64)
         gguf.GGUFFile(tmp_path / "bad.gguf")
+
+
+def test_gguf_file_loads_into_the_engine(tmp_path):
+    """A whole (tiny, F32) GGUF model through the public API: config + tensors + tokenizer from the file, and the
+    tokens must equal those of the same weights loaded as a state dict."""
+    from grimoire_b200.api import Grimoire
+    from grimoire_b200.config import EngineConfig
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+    from grimoire_b200.models.config import ModelConfig
+    from grimoire_b200.models.dense import DenseModel
+
+    H, I, L, V, Hq, Hkv, D = 128, 256, 2, 64, 2, 1, 64
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05
+    sd, tensors = {}, {}
+
+    def put(gname, hname, t):
+        sd[hname] = t
+        tensors[gname] = (0, tuple(reversed(t.shape)), t.contiguous().numpy().tobytes())      # type 0 = F32, ggml dims are reversed
+    put("token_embd.weight", "model.embed_tokens.weight", rnd(V, H))
+    put("output_norm.weight", "model.norm.weight", torch.ones(H))
+    for i in range(L):
+        for gn, hn, shape in (("attn_q", "self_attn.q_proj", (Hq * D, H)), ("attn_k", "self_attn.k_proj", (Hkv * D, H)),
+                              ("attn_v", "self_attn.v_proj", (Hkv * D, H)), ("attn_output", "self_attn.o_proj", (H, Hq * D)),
+                              ("ffn_gate", "mlp.gate_proj", (I, H)), ("ffn_up", "mlp.up_proj", (I, H)), ("ffn_down", "mlp.down_proj", (H, I))):
+            put(f"blk.{i}.{gn}.weight", f"model.layers.{i}.{hn}.weight", rnd(*shape))
+        put(f"blk.{i}.attn_norm.weight", f"model.layers.{i}.input_layernorm.weight", torch.ones(H))
+        put(f"blk.{i}.ffn_norm.weight", f"model.layers.{i}.post_attention_layernorm.weight", torch.ones(H))
+    toks = [chr(0x100 + i) for i in range(V)]
+    kv = {"general.architecture": (8, "qwen3"), "qwen3.block_count": (4, L), "qwen3.embedding_length": (4, H),
+          "qwen3.attention.head_count": (4, Hq), "qwen3.attention.head_count_kv": (4, Hkv), "qwen3.attention.key_length": (4, D),
+          "qwen3.feed_forward_length": (4, I), "qwen3.rope.freq_base": (6, 1e6), "tokenizer.ggml.model": (8, "gpt2"),
+          "tokenizer.ggml.tokens": (9, (8, toks)), "tokenizer.ggml.merges": (9, (8, [])), "tokenizer.ggml.token_type": (9, (5, [1] * V))}
+    _write_gguf(tmp_path / "tiny.gguf", kv, tensors)
+    llm = Grimoire.load(EngineConfig(model=str(tmp_path / "tiny.gguf"), ctx=64, seq_slots=2, prefill_chunk=32), device="cpu")
+    assert llm.model.cfg.num_hidden_layers == L and llm.model.cfg.head_dim == D and llm.tokenizer is not None
+    prompt = [3, 9, 27, 11, 5]
+    got, _ = llm.generate(prompt, 6)
+    cfg = ModelConfig(model_type="qwen3", hidden_size=H, num_hidden_layers=L, num_attention_heads=Hq, num_key_value_heads=Hkv, head_dim=D,
+                      vocab_size=V, intermediate_size=I, tie_word_embeddings=True, rope_theta=1e6)
+    want = Engine(DenseModel.from_state_dict(cfg, sd, "cpu"), EngineLimits(max_slots=2, max_ctx=64, prefill_chunk=32, max_decode_rows=4)).generate(prompt, 6)
+    assert list(got) == list(want)
+    llm.close()
