@@ -13,8 +13,9 @@
 //   O += P V    : tcgen05.mma 128x128x64 accumulating in a second TMEM region across all key blocks; a row
 //               whose running maximum moved is rescaled in place (tcgen05.ld / st), which is rare after the first
 //               few blocks; the accumulator is read once at the end.
-//   The next K / V tiles are requested as soon as the MMA that read the current ones has committed.
-// Two CTAs per SM (80 KB shared memory, 256 TMEM columns each) overlap one CTA's softmax with the other's
+//   Software pipeline: S has two TMEM buffers and V two shared-memory buffers, so S(j+1) and PV(j) run on the
+//   tensor cores while the CTA computes the softmax of block j+1; K / V tiles are requested a block ahead.
+// Two CTAs per SM (96 KB shared memory, 256 TMEM columns each) overlap one CTA's softmax with the other's
 // MMAs.  Every mbarrier wait is bounded; on a timeout the CTA records the error, frees its TMEM and returns.
 #include "common.cuh"
 #include <cuda.h>
@@ -23,8 +24,8 @@ namespace {
 
 constexpr int D = 128, BQ = 128, BKV = 64, kThreads = 128;
 constexpr int kQBytes = BQ * D * 2, kKBytes = BKV * D * 2, kVBytes = D * BKV * 2, kPBytes = BQ * BKV * 2;
-constexpr int kSmem = kQBytes + kKBytes + kVBytes + kPBytes + 256 + 1024;
-constexpr uint32_t kTmemCols = 256;       // S: columns [0, 64), O_blk: columns [64, 192)
+constexpr int kSmem = kQBytes + kKBytes + 2 * kVBytes + kPBytes + 256 + 1024;
+constexpr uint32_t kTmemCols = 256;       // S buffer 0: columns [0, 64), O: [64, 192), S buffer 1: [192, 256)
 
 struct TcParams {
   bf16* out; int ld_o;
@@ -60,14 +61,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                         // 2 boxes of [128 rows][64 dims]
   uint8_t* sK = sQ + kQBytes;                 // 2 boxes of [64 keys][64 dims]
-  uint8_t* sV = sK + kKBytes;                 // [128 dims][64 keys]
-  uint8_t* sP = sV + kVBytes;                 // [128 rows][64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);     // 0 Q, 1 K, 2 V, 3 S done, 4 O done
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 5);
+  uint8_t* sV = sK + kKBytes;                 // 2 buffers of [128 dims][64 keys]
+  uint8_t* sP = sV + 2 * kVBytes;             // [128 rows][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);     // 0 Q, 1 K, 2/3 V[0/1], 4/5 S[0/1] done, 6 O done
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 7);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qb = blockIdx.x, h = blockIdx.y;
+  // causal: later query blocks have more key blocks; they are launched first so the short ones fill the tail
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
   const int kvh = h / (p.Hq / p.Hkv);
   const int row = qb * BQ + tid;              // query row of this thread inside the chunk
   const bool row_ok = row < p.M;
@@ -78,7 +80,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const int kb_hi = last_q / BKV;             // inclusive
 
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
     *s_abort = 0;
     mbar_fence_init();
   }
@@ -97,9 +99,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     tma_load_2d(sK, &tmK, &bars[1], kvh * D, kb * BKV);
     tma_load_2d(sK + kKBytes / 2, &tmK, &bars[1], kvh * D + 64, kb * BKV);
   };
-  auto load_v = [&](int kb) {
-    mbar_expect_tx(&bars[2], kVBytes);
-    tma_load_2d(sV, &tmV, &bars[2], kb * BKV, kvh * D);
+  auto load_v = [&](int kb, int buf) {
+    mbar_expect_tx(&bars[2 + buf], kVBytes);
+    tma_load_2d(sV + buf * kVBytes, &tmV, &bars[2 + buf], kb * BKV, kvh * D);
   };
   if (tid == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -107,47 +109,53 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     tma_load_2d(sQ, &tmQ, &bars[0], h * D, qb * BQ);
     tma_load_2d(sQ + kQBytes / 2, &tmQ, &bars[0], h * D + 64, qb * BQ);
     load_k(kb_lo);
-    load_v(kb_lo);
+    load_v(kb_lo, 0);
   }
 
   float m_run = -INFINITY, l_run = 0.f;
   constexpr uint32_t idesc_s = make_idesc(BQ, BKV, 1, 1);
   constexpr uint32_t idesc_o = make_idesc(BQ, D, 1, 1);
   bool ok = true;
+  const int nblk = kb_hi - kb_lo + 1;
 
-  for (int kb = kb_lo; kb <= kb_hi && ok; ++kb) {
-    const uint32_t par = (uint32_t)(kb - kb_lo) & 1u;
-    // ---- S = Q K^T ----
-    if (tid == 0) {
-      bool good = true;
-      if (kb == kb_lo) good = mbar_wait(&bars[0], 0u, p.status, 0x800u);
-      good = good && mbar_wait(&bars[1], par, p.status, 0x801u);
-      if (good) {
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * (kQBytes / 2)) + (uint64_t)((k & 3) * 2);
-          const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * (kKBytes / 2)) + (uint64_t)((k & 3) * 2);
-          tc_mma_f16(tmem_base, da, db, idesc_s, k != 0 ? 1u : 0u);
-        }
-        tc_commit(&bars[3]);
-      } else {
-        *s_abort = 1;
-      }
-    }
-    if (!mbar_wait(&bars[3], par, p.status, 0x803u)) { ok = false; break; }
+  // S(j) = Q K(j)^T into S buffer (j & 1); issued by thread 0 once K(j) has landed
+  auto issue_s = [&](int j) -> bool {
+    if (!mbar_wait(&bars[1], (uint32_t)j & 1u, p.status, 0x801u)) return false;
     tc_fence_after();
-    if (tid == 0 && kb < kb_hi) load_k(kb + 1);            // the S MMAs have read K
+    const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
+    const uint32_t td = tmem_base + ((j & 1) ? 192u : 0u);
+#pragma unroll
+    for (int k = 0; k < D / 16; ++k) {
+      const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * (kQBytes / 2)) + (uint64_t)((k & 3) * 2);
+      const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * (kKBytes / 2)) + (uint64_t)((k & 3) * 2);
+      tc_mma_f16(td, da, db, idesc_s, k != 0 ? 1u : 0u);
+    }
+    tc_commit(&bars[4 + (j & 1)]);
+    return true;
+  };
+  if (tid == 0) {
+    if (!mbar_wait(&bars[0], 0u, p.status, 0x800u) || !issue_s(0)) *s_abort = 1;
+  }
+
+  // Software pipeline over the key blocks j = 0 .. nblk-1 (kb = kb_lo + j):
+  //   top     : S(j) is ready; K(j+1) is requested (the K buffer is free)
+  //   softmax : this thread's row of S(j); then PV(j-1) is awaited, V(j+1) requested, O rescaled if needed, P(j) stored
+  //   barrier : thread 0 issues S(j+1) and PV(j); both run while the CTA does the softmax of the next block
+  for (int j = 0; j < nblk && ok; ++j) {
+    const int kb = kb_lo + j, b = j & 1;
+    if (!mbar_wait(&bars[4 + b], (uint32_t)(j >> 1) & 1u, p.status, 0x803u)) { ok = false; break; }
+    tc_fence_after();
+    if (tid == 0 && j + 1 < nblk) load_k(kb + 1);            // the S(j) MMAs have read K
     // ---- softmax of this thread's row ----
     float sv[BKV];
     {
+      const uint32_t ts = t_row + (b ? 192u : 0u);
       uint32_t r[32];
-      tmem_ld_32x32b_x32(t_row, r);
+      tmem_ld_32x32b_x32(ts, r);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
-      tmem_ld_32x32b_x32(t_row + 32, r);
+      tmem_ld_32x32b_x32(ts + 32, r);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) sv[32 + i] = __uint_as_float(r[i]);
@@ -157,14 +165,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const bool need_mask = (key0 + BKV - 1 > first_q) || (p.window > 0) || !row_ok;
 #pragma unroll
     for (int i = 0; i < BKV; ++i) {
-      float s = sv[i] * p.scale_log2;
+      float sc = sv[i] * p.scale_log2;
       if (need_mask) {
         const int kp = key0 + i;
         const bool vis = row_ok && kp <= q_pos && (p.window <= 0 || kp > q_pos - p.window);
-        s = vis ? s : -INFINITY;
+        sc = vis ? sc : -INFINITY;
       }
-      sv[i] = s;
-      mx = fmaxf(mx, s);
+      sv[i] = sc;
+      mx = fmaxf(mx, sc);
     }
     const float m_new = fmaxf(m_run, mx);
     const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
@@ -179,9 +187,15 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     m_run = m_new;
     l_run = l_run * alpha + psum;
+    // PV(j-1) must have finished before O is rescaled, P is overwritten and its V buffer is refilled
+    if (j > 0) {
+      if (!mbar_wait(&bars[6], (uint32_t)(j - 1) & 1u, p.status, 0x804u)) { ok = false; break; }
+      tc_fence_after();
+    }
+    if (tid == 0 && j + 1 < nblk) load_v(kb + 1, b ^ 1);
     // O stays in TMEM across blocks; a row whose running maximum moved is rescaled in place.  After the first few
     // blocks of a row this is rare, so the branch is taken per warp only when one of its rows needs it.
-    if (kb > kb_lo && __any_sync(0xffffffffu, alpha != 1.f)) {
+    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -197,29 +211,33 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     {
       uint8_t* prow = sP + tid * 128;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(prow + ((j ^ (tid & 7)) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     tc_fence_before();
     __syncthreads();
-    // ---- O_blk = P V ----
     if (tid == 0) {
-      if (!*s_abort && mbar_wait(&bars[2], par, p.status, 0x802u)) {
+      bool good = !*s_abort;
+      // S(j+1) first: the next block's softmax waits for it; its TMEM buffer was last read before this barrier
+      if (good && j + 1 < nblk) good = issue_s(j + 1);
+      if (good) good = mbar_wait(&bars[2 + b], (uint32_t)(j >> 1) & 1u, p.status, 0x802u);
+      if (good) {
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + b * kVBytes);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
           tc_mma_f16(tmem_base + 64, make_sw128_kmajor_desc(pa) + (uint64_t)(k * 2), make_sw128_kmajor_desc(va) + (uint64_t)(k * 2), idesc_o,
-                     (k != 0 || kb != kb_lo) ? 1u : 0u);
-        tc_commit(&bars[4]);
+                     (k != 0 || j != 0) ? 1u : 0u);
+        tc_commit(&bars[6]);
       } else {
         *s_abort = 1;
       }
     }
-    if (!mbar_wait(&bars[4], par, p.status, 0x804u)) { ok = false; break; }
+  }
+  if (ok) {
+    if (!mbar_wait(&bars[6], (uint32_t)(nblk - 1) & 1u, p.status, 0x805u)) ok = false;
     tc_fence_after();
-    if (tid == 0 && kb < kb_hi) load_v(kb + 1);            // the O MMAs have read V (and P)
   }
 
   if (ok) {
@@ -245,7 +263,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
   if (!ok && tid == 0) {
     // let copies in flight land before the shared memory is handed to another CTA (bounded)
-    for (int b = 1; b <= 2; ++b)
+    for (int b = 1; b <= 3; ++b)
       for (int i = 0; i < 200000 && !mbar_try_wait(&bars[b], 0u) && !mbar_try_wait(&bars[b], 1u); ++i) __nanosleep(64);
   }
   tc_fence_before();
