@@ -62,8 +62,9 @@ class Grimoire:
         else:
             from .tokenizer import Tokenizer
 
-            if ec.proj not in ("int4", "mxfp4", "native"):
-                raise UnsupportedModel(f"--proj {ec.proj}: this build serves int4 (g128) and mxfp4 projections (bf16 lm_head optional)")
+            if ec.proj not in ("int4", "mxfp4", "fp8", "native"):
+                raise UnsupportedModel(f"--proj {ec.proj}: this build serves int4 (g128), mxfp4 and block-scaled fp8 projections "
+                                       f"(bf16 lm_head optional)")
             if ec.model.endswith(".gguf"):
                 # GGUF: config and tokenizer from the metadata, tensors dequantised block by block and re-quantised
                 # to the serving format (the reference's native GGUF path keeps the file's blocks; this one does not)
@@ -74,8 +75,8 @@ class Grimoire:
 
                 gf = G.GGUFFile(ec.model)
                 cfg = G.config_from_gguf(gf)
-                if ec.proj == "mxfp4":
-                    cfg = dataclasses.replace(cfg, quant="mxfp4")
+                if ec.proj in ("mxfp4", "fp8"):
+                    cfg = dataclasses.replace(cfg, quant=ec.proj)
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)

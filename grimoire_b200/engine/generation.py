@@ -77,7 +77,7 @@ class EngineLike(Protocol):
 
 class Drafter(Protocol):
     def propose(self, engine, seq, last_token: int, depth: int) -> list[int]: ...
-    def observe(self, engine, seq, accepted_tokens: Sequence[int]) -> None: ...
+    def observe(self, engine, seq, accepted_tokens: Sequence[int], row0: int = 0) -> None: ...
 
 
 class CopyDrafter:
@@ -103,7 +103,7 @@ class CopyDrafter:
                     break
         return []
 
-    def observe(self, engine, seq, accepted_tokens) -> None:
+    def observe(self, engine, seq, accepted_tokens, row0: int = 0) -> None:
         pass
 
 

@@ -117,6 +117,10 @@ class DenseModel:
     def _quant(self, w) -> QuantWeight:
         """fp32 tensor or stored QuantWeight -> runtime int4 (stored int4 is used as is)."""
         cfg = self.cfg
+        if cfg.quant == "fp8":
+            if isinstance(w, QuantWeight):
+                return w if w.fmt == Fmt.FP8_BLOCK else quantize(w.dequant(), Fmt.FP8_BLOCK)
+            return quantize(w, Fmt.FP8_BLOCK)
         if cfg.quant == "mxfp4":
             if isinstance(w, QuantWeight):
                 return w if w.fmt == Fmt.MXFP4 else quantize(w.dequant(), Fmt.MXFP4)
@@ -126,7 +130,12 @@ class DenseModel:
         return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
 
     def _linear(self, qw: QuantWeight, name: str, swiglu: bool = False):
-        """Runtime projection for a quantized weight: int4 -> W4Linear, MXFP4 -> MXLinear."""
+        """Runtime projection for a quantized weight: int4 -> W4Linear, MXFP4 -> MXLinear, block-scaled fp8 ->
+        FP8BlockLinear (its SwiGLU form takes [gate rows | up rows], not the per-16 interleave)."""
+        if qw.fmt == Fmt.FP8_BLOCK:
+            from ..ops.hybrid import FP8BlockLinear
+
+            return FP8BlockLinear(qw, self.device, name)
         cls = MXLinear if qw.fmt == Fmt.MXFP4 else W4Linear
         return cls(qw, self.device, name, swiglu=swiglu, workspace=self.ws)
 
@@ -157,7 +166,8 @@ class DenseModel:
         wg_s, wu_s = self._rows(wg, r * I, (r + 1) * I), self._rows(wu, r * I, (r + 1) * I)
         wd_s = self._cols(wd, r * I, (r + 1) * I)
         qkv = concat_rows([self._quant(wq_s), self._quant(wk_s), self._quant(wv_s)])
-        gu = interleave_gate_up_q(self._quant(wg_s), self._quant(wu_s))
+        qg, qu = self._quant(wg_s), self._quant(wu_s)
+        gu = concat_rows([qg, qu]) if qg.fmt == Fmt.FP8_BLOCK else interleave_gate_up_q(qg, qu)
         f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
         i = len(self.layers)
         self.layers.append(DenseLayer(
@@ -234,10 +244,10 @@ class DenseModel:
 
         ck = Checkpoint(path)
         cfg = ck.cfg
-        if proj == "mxfp4":
+        if proj in ("mxfp4", "fp8"):
             import dataclasses
 
-            cfg = dataclasses.replace(cfg, quant="mxfp4")
+            cfg = dataclasses.replace(cfg, quant=proj)
         m = DenseModel(cfg, device, tp_rank, tp_world, workspace, pp_rank, pp_world)
         for i in range(m.layer_begin, m.layer_end):
             p = f"{ck.prefix}layers.{i}."

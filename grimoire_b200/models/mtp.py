@@ -163,6 +163,15 @@ class MtpDrafter:
     # ---- prefill: fill the head's KV from the target's hidden states of the chunk ----
     def warm_chunk(self, seq, tokens_dev: torch.Tensor, done: int, m: int, pos0: int, buf, last: bool) -> None:
         eng = self.engine
+        prev = self.pending.get(seq.slot)
+        if done == 0 and prev is not None and prev[0] == pos0 - 1:
+            # the prompt arrives in several prefill calls: the position the previous call left pending gets its
+            # entry now that its next token (the first of this call) is known
+            one = torch.full((1,), seq.slot, dtype=torch.int32, device=eng.device)
+            rb1 = RowBatch(tokens_dev[:1], one, torch.full((1,), pos0 - 1, dtype=torch.int32, device=eng.device), mode="decode",
+                           splits=K.decode_splits(pos0, 1, self.head.inner.geom.Hkv))
+            self.head.forward(rb1, prev[1].unsqueeze(0), eng.decode_buf, self.kvl, eng.kv.table)
+            self.stats["warm_rows"] += 1
         rows = m - 1 if last else m                      # the last prompt position has no next token yet
         hid = buf.h[:m]
         if last:
@@ -199,12 +208,13 @@ class MtpDrafter:
         return [int(v) for v in self._drafts[:depth].tolist()]
 
     # ---- after a committed block: provisional entries are replaced by ones made from target hiddens ----
-    def observe(self, engine, seq, accepted_tokens) -> None:
+    def observe(self, engine, seq, accepted_tokens, row0: int = 0) -> None:
+        """``row0``: first row of this conversation's block inside the step that was just verified."""
         eng, dev = self.engine, self.engine.device
         keep = list(accepted_tokens)
         a = len(keep) - 1
         pos0 = seq.length - len(keep)
-        hid = eng.decode_buf.h
+        hid = eng.decode_buf.h[row0:]
         if a > 0:
             toks = torch.tensor(keep[1:], dtype=torch.int32, device=dev)
             pos = torch.arange(pos0, pos0 + a, dtype=torch.int32, device=dev)

@@ -58,7 +58,7 @@ class SchedJob:
 class Scheduler:
     def __init__(self, engine, width: int = 8, interleave_chunk: int = 1024, prefill_chunk: int = 4096,
                  hold_ms: float = 8.0, hold_long_ms: float = 100.0, depths: Sequence[int] = (0,), spec_rows: int = 32,
-                 copy_drafts: bool = False, use_graph: bool = True, clock: Callable[[], float] = time.monotonic):
+                 copy_drafts: bool = False, use_graph: bool = True, clock: Callable[[], float] = time.monotonic, drafter=None):
         self.engine = engine
         self.lib = _native.host()
         self.lib.grm_sched_new.restype = ctypes.c_void_p
@@ -71,7 +71,8 @@ class Scheduler:
         self.width = width
         self.use_graph = use_graph
         self.clock = clock
-        self.drafter = CopyDrafter() if copy_drafts else None
+        # any object with the Drafter protocol (engine/generation.py): the MTP head's drafter, or prompt-lookup copy drafts
+        self.drafter = drafter if drafter is not None else (CopyDrafter() if copy_drafts else None)
         self.jobs: dict[int, SchedJob] = {}
         self._ids = itertools.count(1)
         self._lock = threading.Lock()
@@ -294,6 +295,8 @@ class Scheduler:
             eng.commit_rows([job.seq] * len(keep), keep, list(range(pos0, pos0 + len(keep))))
             if n > 1 and hasattr(eng, "rollback"):
                 eng.rollback(job.seq, pos0 + len(keep))
+            if self.drafter is not None:
+                self.drafter.observe(eng, job.seq, keep, row0=o)       # model drafters track the newest hidden state
             alive = True
             for d in block[1: accepted + 1]:
                 alive = self._emit(job, d)

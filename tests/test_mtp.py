@@ -47,3 +47,34 @@ def test_mtp_speculation_reproduces_greedy_gpu(quant):
     assert toks == plain
     assert stats.rounds > 0 and drafter.stats["warm_rows"] == 36
     assert K.status_read()[0] == 0
+
+
+def test_mtp_drafter_in_the_scheduler_reproduces_greedy_cpu():
+    """Two concurrent conversations through the continuous-batching scheduler with the MTP drafter: tokens equal
+    plain greedy decoding, the head's KV is warmed across partial prefill calls."""
+    from grimoire_b200.sched.scheduler import Scheduler
+
+    cfg = dataclasses.replace(tiny_dense(), tie_word_embeddings=False)
+    lim = EngineLimits(max_slots=3, max_ctx=160, prefill_chunk=16, max_decode_rows=16, extra_kv_layers=1)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (29, 41)]
+    plain = [Engine(DenseModel.random(cfg, "cpu", seed=1), lim).generate(p, 12, use_graph=False) for p in prompts]
+    model = DenseModel.random(cfg, "cpu", seed=1)
+    eng = Engine(model, lim)
+    drafter = MtpDrafter(eng, MtpHead.random_from_target(model, seed=1, noise=0.01))
+    sched = Scheduler(eng, width=4, prefill_chunk=16, interleave_chunk=16, depths=(3, 3, 3, 3), drafter=drafter, use_graph=False)
+    try:
+        import threading
+        out = [None, None]
+
+        def run(i):
+            out[i] = sched.generate(prompts[i], 12)[0]
+        ts = [threading.Thread(target=run, args=(i,)) for i in range(2)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(timeout=120)
+    finally:
+        sched.shutdown()
+    assert out[0] == plain[0] and out[1] == plain[1]
+    assert drafter.stats["draft_steps"] > 0

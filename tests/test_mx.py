@@ -104,3 +104,46 @@ def test_dense_model_mxfp4_gpu_matches_cpu():
     _, l2c = cpu.decode_rows([tok], [sc], [sc.length], return_logits=True)
     _, l2g = gpu.decode_rows([tok], [sg], [sg.length], use_graph=False, return_logits=True)
     assert float((l2c[0] - l2g[0].float().cpu()).abs().max()) < 0.05 * max(1.0, float(l2c.abs().max()))
+
+
+def test_dense_model_fp8_block_cpu_and_api_proj(tmp_path):
+    """--proj fp8: block-scaled e4m3 projections ([gate | up] SwiGLU halves) through the dense model."""
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+    from grimoire_b200.models.config import tiny_dense
+    from grimoire_b200.models.dense import DenseModel
+    from grimoire_b200.models.synthetic import random_state_dict
+    from grimoire_b200.ops.hybrid import FP8BlockLinear
+
+    cfg = dataclasses.replace(tiny_dense(), quant="fp8")
+    sd = random_state_dict(cfg, seed=0)
+    m = DenseModel.from_state_dict(cfg, sd, "cpu")
+    assert isinstance(m.layers[0].qkv, FP8BlockLinear) and isinstance(m.layers[0].gate_up, FP8BlockLinear)
+    lim = EngineLimits(max_slots=1, max_ctx=64, prefill_chunk=32, max_decode_rows=4)
+    prompt = list(range(1, 17))
+    out = Engine(m, lim).generate(prompt, 8)
+    ref = Engine(DenseModel.from_state_dict(dataclasses.replace(cfg, quant="int4"), sd, "cpu"), lim)
+    s1, s2 = Engine(m, lim).open(), ref.open()
+    # fp8 (3 mantissa bits) and int4-g128 logits of the same weights agree to quantisation noise
+    l8, l4 = Engine(m, lim).prefill(s1, prompt).float(), ref.prefill(s2, prompt).float()
+    assert len(out) == 8 and float((l8 - l4).abs().max()) < 0.25 * max(1.0, float(l4.abs().max()))
+
+
+@pytest.mark.gpu
+def test_dense_model_fp8_gpu_matches_cpu():
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+    from grimoire_b200.models.config import tiny_dense
+    from grimoire_b200.models.dense import DenseModel
+    from grimoire_b200.models.synthetic import random_state_dict
+
+    cfg = dataclasses.replace(tiny_dense(), quant="fp8")
+    sd = random_state_dict(cfg, seed=0)
+    lim = EngineLimits(max_slots=1, max_ctx=256, prefill_chunk=128, max_decode_rows=4)
+    prompt = torch.randint(0, 4096, (100,), generator=torch.Generator().manual_seed(1)).tolist()
+    cpu, gpu = Engine(DenseModel.from_state_dict(cfg, sd, "cpu"), lim), Engine(DenseModel.from_state_dict(cfg, sd, "cuda"), lim)
+    sc, sg = cpu.open(), gpu.open()
+    lc, lg = cpu.prefill(sc, prompt).float(), gpu.prefill(sg, prompt).float().cpu()
+    assert float((lc - lg).abs().max()) < 0.05 * max(1.0, float(lc.abs().max()))
+    tok = int(lc.argmax())
+    _, l2c = cpu.decode_rows([tok], [sc], [sc.length], return_logits=True)
+    _, l2g = gpu.decode_rows([tok], [sg], [sg.length], use_graph=False, return_logits=True)
+    assert float((l2c[0] - l2g[0].float().cpu()).abs().max()) < 0.05 * max(1.0, float(l2c.abs().max()))
