@@ -147,6 +147,19 @@ __global__ void bf16_to_f16_kernel(const bf16* __restrict__ x, int ldx, __half* 
   *reinterpret_cast<__half2*>(y + (size_t)m * ldy + c) = __floats2half2_rn(bf16lo_to_f(v), bf16hi_to_f(v));
 }
 
+// bf16 rows -> f16 rows in the lane order of the tiled MXFP4 kernel: inside every 64-column k tile, position
+// 16 t + 4 j + c holds column 16 j + (2t, 2t+1, 2t+8, 2t+9)[c], so lane t of a quad reads its B fragments of the
+// four k16 steps as 32 contiguous bytes.
+__global__ void x16_lane_order_kernel(const bf16* __restrict__ x, int ldx, __half* __restrict__ y, int ldy, int M, int K) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * K) return;
+  const int m = i / K, pos = i - m * K;
+  const int kt = pos >> 6, r = pos & 63;
+  const int t = r >> 4, j = (r >> 2) & 3, c = r & 3;
+  const int col = (kt << 6) + 16 * j + 2 * t + (c & 1) + ((c >> 1) << 3);
+  y[(size_t)m * ldy + pos] = __float2half_rn(__bfloat162float(x[(size_t)m * ldx + col]));
+}
+
 // dequantise a whole MXFP4 matrix to bf16 [N][K] (prefill: dequantise once, then the tcgen05 GEMM)
 __global__ void __launch_bounds__(256) dequant_mx_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ s, bf16* __restrict__ out,
                                                          long nblocks) {
@@ -201,5 +214,12 @@ GRM_API int grm_dequant_mxfp4(const void* w, const void* scales, void* out, int 
   const long nblocks = (long)N * (K / 32);
   dequant_mx_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)w, (const uint8_t*)scales, (bf16*)out,
                                                                                           nblocks);
+  GRM_LAUNCH_RET();
+}
+
+GRM_API int grm_x16_lane_order(const void* x, int ldx, void* y, int ldy, int M, int K, void* stream) {
+  if (M < 1 || (K % 64) || (ldy & 7)) return -2;
+  const int n = M * K;
+  x16_lane_order_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const bf16*)x, ldx, (__half*)y, ldy, M, K);
   GRM_LAUNCH_RET();
 }

@@ -61,6 +61,8 @@ struct W4Params {
   int ldq, ldtab;
   // ---- warp layout inside a CTA: rt row super-tiles x ks K slices, rt * ks == kWarps ----
   int rt, ks, ntiles;
+  int mx;                   // MATH == 2: weights are MXFP4 tiles (see tile_mx), sz holds e8m0 bytes, x is f16 in lane order
+  int szw;                  // 32-bit words of scale data per (16-row tile, group): 16 for int4, 8 for MXFP4 (group = one k tile)
   int min_ctas;             // smallest grid the row-tile grouping may produce (GRIMOIRE_SMALLM_MIN_CTAS, default 222 = 1.5 per SM)
 };
 
@@ -81,6 +83,15 @@ __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint3
 __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t cvt_e2m1x2_f16(uint32_t byte) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b0;\n\t}" : "=r"(r) : "r"(byte));
+  return r;
+}
+__device__ __forceinline__ void mma_f16_16816_w4(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
   uint32_t r;
@@ -141,8 +152,10 @@ __device__ __forceinline__ void fill_stage(uint8_t* dst, const uint8_t* wsrc, in
 // rows g and g+8 with three logic ops (even nibbles / odd nibbles), group sums are exact int32 and the
 // zero point is removed with the group's pre-computed activation sum -- about a third of the ALU work
 // of the bf16 path, with a smaller activation rounding error than bf16 inputs have.
-template <int MT, int R, int EPI, bool I8>
+template <int MT, int R, int EPI, int MATH>
 __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
+  constexpr bool I8 = MATH == 1;
+  constexpr bool MX = MATH == 2;
   // dynamic shared memory: [kWarps][RING][R*512] weight ring | [kWarps][R*MT*4][32] reduce | barriers | scales
   extern __shared__ __align__(128) uint8_t smem_dyn[];
   constexpr int RING = RingDepth<MT>::v;
@@ -154,7 +167,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(red + kWarps * NVc) + warp * (RING + 1);
   // scale / zero words of this warp's groups: [R][p.szg][16] uint32, staged once by a bulk copy
   uint32_t* szs = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(red + kWarps * NVc) + kWarps * (RING + 1) * 8) +
-                  (size_t)warp * R * p.szg * 16;
+                  (size_t)warp * R * p.szg * p.szw;
   __shared__ int s_last;
   const int g = lane >> 2, t = lane & 3;
   // The CTA's 8 warps cover rt row super-tiles (of R row tiles each) x ks K slices.  Few, long-lived
@@ -194,11 +207,11 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       mbar_fence_init();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       // scales first: a load at the point of use would expose a DRAM latency per group
-      const uint32_t szbytes = (uint32_t)(gend - gbeg) * 64u;
+      const uint32_t szbytes = (uint32_t)(gend - gbeg) * 4u * (uint32_t)p.szw;
       mbar_expect_tx(&bars[RING], szbytes * R);
 #pragma unroll
       for (int r = 0; r < R; ++r)
-        bulk_load(szs + (size_t)r * p.szg * 16, p.sz + ((size_t)(tile * R + r) * G + gbeg) * 16, szbytes, &bars[RING]);
+        bulk_load(szs + (size_t)r * p.szg * p.szw, p.sz + ((size_t)(tile * R + r) * G + gbeg) * p.szw, szbytes, &bars[RING]);
       for (int i = 0; i < RING; ++i) fill_stage<R>(ring + i * kStage, wsrc, kt0 + i * kSK, kt1, &bars[i]);
     }
     __syncwarp();
@@ -354,24 +367,35 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
     int kt = kt0;
 
 #pragma unroll 1
-    for (int grp = gbeg; grp < gend && !dead; ++grp, szp += 16) {
+    for (int grp = gbeg; grp < gend && !dead; ++grp, szp += p.szw) {
       float sc[R][2], zf[R][2];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const uint32_t s0 = szp[r * p.szg * 16], s1 = szp[r * p.szg * 16 + 8];
-        sc[r][0] = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
-        sc[r][1] = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
-        zf[r][0] = bf16hi_to_f(s0);      // 128 + zero
-        zf[r][1] = bf16hi_to_f(s1);
+        if constexpr (MX) {
+          // e8m0 bytes of the two 32-wide blocks of this k tile: [block][16 rows]; rows g and g + 8 of each
+          const uint8_t* sb = reinterpret_cast<const uint8_t*>(szp - g + (size_t)r * p.szg * p.szw);
+          sc[r][0] = __uint_as_float((uint32_t)sb[g] << 23); sc[r][1] = __uint_as_float((uint32_t)sb[g + 8] << 23);         // block 0
+          zf[r][0] = __uint_as_float((uint32_t)sb[16 + g] << 23); zf[r][1] = __uint_as_float((uint32_t)sb[24 + g] << 23);   // block 1
+        } else {
+          const uint32_t s0 = szp[r * p.szg * 16], s1 = szp[r * p.szg * 16 + 8];
+          sc[r][0] = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
+          sc[r][1] = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
+          zf[r][0] = bf16hi_to_f(s0);      // 128 + zero
+          zf[r][1] = bf16hi_to_f(s1);
+        }
       }
       float accg[R][MT][4], xsum[MT][4];
+      float accg2[MX ? R : 1][MX ? MT : 1][4];      // MXFP4: the k tile's second 32-wide block
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           xsum[mt][c] = 0.f;
 #pragma unroll
-          for (int r = 0; r < R; ++r) accg[r][mt][c] = 0.f;
+          for (int r = 0; r < R; ++r) {
+            accg[r][mt][c] = 0.f;
+            if constexpr (MX) accg2[r][mt][c] = 0.f;
+          }
         }
       }
 #pragma unroll 1
@@ -406,6 +430,19 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
         // (128 + zero) * sum_k x is removed when the group is flushed.
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+          if constexpr (MX) {
+            // MXFP4: a word holds the four A-fragment bytes of k16 step j (two e2m1 per byte); the hardware e2m1x2 -> f16x2
+            // conversion yields each fragment register; steps 0,1 belong to block 0 (accg), steps 2,3 to block 1 (xsum reused
+            // per r is not possible, so block 1 accumulates in accg2)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
+              const uint32_t a0 = cvt_e2m1x2_f16(u), a1 = cvt_e2m1x2_f16(u >> 8), a2 = cvt_e2m1x2_f16(u >> 16), a3 = cvt_e2m1x2_f16(u >> 24);
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) mma_f16_16816_w4(j < 2 ? accg[r][mt] : accg2[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
+            }
+            continue;
+          }
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(xsum[mt], ones, ones, ones, ones, b[mt][2 * j], b[mt][2 * j + 1]);
 #pragma unroll
@@ -425,6 +462,14 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       for (int r = 0; r < R; ++r)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
+          if constexpr (MX) {
+            // rows g (c0, c1) and g + 8 (c2, c3): block 0 scales in sc, block 1 scales in zf
+            acc[r][mt][0] = fmaf(sc[r][0], accg[r][mt][0], fmaf(zf[r][0], accg2[r][mt][0], acc[r][mt][0]));
+            acc[r][mt][1] = fmaf(sc[r][0], accg[r][mt][1], fmaf(zf[r][0], accg2[r][mt][1], acc[r][mt][1]));
+            acc[r][mt][2] = fmaf(sc[r][1], accg[r][mt][2], fmaf(zf[r][1], accg2[r][mt][2], acc[r][mt][2]));
+            acc[r][mt][3] = fmaf(sc[r][1], accg[r][mt][3], fmaf(zf[r][1], accg2[r][mt][3], acc[r][mt][3]));
+            continue;
+          }
           acc[r][mt][0] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][0], accg[r][mt][0]), acc[r][mt][0]);
           acc[r][mt][1] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][1], accg[r][mt][1]), acc[r][mt][1]);
           acc[r][mt][2] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][2], accg[r][mt][2]), acc[r][mt][2]);
@@ -555,7 +600,7 @@ static int grm_smallm_min_ctas() {
   return v;
 }
 
-template <int MT, int R, int EPI, bool I8>
+template <int MT, int R, int EPI, int MATH>
 int launch_i(const W4Params& p_in, cudaStream_t st) {
   constexpr int NV = R * MT * 4 * 32;
   constexpr int RING = RingDepth<MT>::v;
@@ -574,8 +619,8 @@ int launch_i(const W4Params& p_in, cudaStream_t st) {
     q.szg = (cta_groups + q.ks - 1) / q.ks;
   }
   const size_t smem = (size_t)kWarps * RING * kSK * R * 512 + (size_t)kWarps * NV * sizeof(float) +
-                      (size_t)kWarps * (RING + 1) * 8 + (size_t)kWarps * R * q.szg * 64;
-  auto kfn = smallm_w4_kernel<MT, R, EPI, I8>;
+                      (size_t)kWarps * (RING + 1) * 8 + (size_t)kWarps * R * q.szg * 4 * q.szw;
+  auto kfn = smallm_w4_kernel<MT, R, EPI, MATH>;
   static size_t attr_max = 48 * 1024;
   if (smem > 200 * 1024) return -2;
   if (smem > attr_max) {
@@ -599,7 +644,8 @@ int launch_i(const W4Params& p_in, cudaStream_t st) {
 
 template <int MT, int R, int EPI>
 int launch(const W4Params& p, cudaStream_t st) {
-  return p.xq_hi ? launch_i<MT, R, EPI, true>(p, st) : launch_i<MT, R, EPI, false>(p, st);
+  if (p.mx) return launch_i<MT, R, EPI, 2>(p, st);
+  return p.xq_hi ? launch_i<MT, R, EPI, 1>(p, st) : launch_i<MT, R, EPI, 0>(p, st);
 }
 
 template <int MT, int R>
@@ -654,7 +700,7 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
   p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
-  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   if (epi == EPI_AR_ADD) return -1;   // use grm_smallm_w4_allreduce
   return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
 }
@@ -679,7 +725,7 @@ GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
-  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
 
@@ -755,7 +801,7 @@ GRM_API int grm_smallm_w4_i8(const void* w, const void* sz, const void* xq_hi, c
   p.M = M; p.N = N; p.K = K; p.ldx = 0; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
   p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
-  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas();
+  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   if (epi == EPI_AR_ADD) return -1;
   return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
 }
@@ -777,8 +823,28 @@ GRM_API int grm_smallm_w4_allreduce_i8(const void* w, const void* sz, const void
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
-  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas();
+  p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
+}
+
+// MXFP4 weights in the tiled layout of tile_mx (formats/w4_tile_layout.py); x16p: f16 activations in lane order
+// (grm_x16_lane_order in smallm_mx.cu).  Same epilogues and split-K contract as grm_smallm_w4.
+GRM_API int grm_smallm_mx_tiled(const void* w, const void* sz, const void* x16p, void* out, void* scratch, void* counters, int M, int N,
+                                int K, int ldx, int ldo, int epi, int rows_per_cta, int ksplit, void* stream) {
+  if (M < 1 || M > 64 || (N % 32) || (K % 64) || (ldx & 7) || ((uintptr_t)x16p & 15)) return -2;
+  const int G = K / 64;
+  if (ksplit < 1 || (G % ksplit)) return -2;
+  if (ksplit > 1 && (!scratch || !counters)) return -2;
+  W4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x16p; p.out = out;
+  p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
+  p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = 1; p.ksplit = ksplit;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
+  p.mx = 1; p.szw = 8;
+  if (epi == EPI_AR_ADD) return -1;
+  return dispatch(p, epi, rows_per_cta, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -850,6 +916,6 @@ GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, 
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
   p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
-  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
+  p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, epi, rows_per_cta, st);
 }

@@ -121,3 +121,20 @@ def interleave_gate_up_q(gate: QuantWeight, up: QuantWeight) -> QuantWeight:
     return QuantWeight(gate.fmt, gate.N * 2, gate.K, interleave_gate_up(gate.payload, up.payload),
                        scales=interleave_gate_up(gate.scales, up.scales),
                        zeros=None if gate.zeros is None else interleave_gate_up(gate.zeros, up.zeros), group=gate.group)
+
+
+def tile_mx(qw: QuantWeight):
+    """MXFP4 ``[N][K]`` (payload [N][K/2] bytes, even k in the low nibble; e8m0 scales [N][K/32]) -> the execution
+    layout of the tiled small-M kernel.  Returns (w int32 [N/32][K/64][2][32][4], sz uint8 [N/16][K/32][16]).
+
+    A lane's 32-bit word j of a k tile holds the four A-fragment bytes of k16 step j: byte b = 2*hi + r8 is row
+    ``16*half + g + 8*r8`` and the column pair ``16 j + 2 t + 8 hi`` (+1) of the tile, so one hardware e2m1x2 -> f16x2
+    conversion per byte yields the fragment registers (a0, a1, a2, a3) in order."""
+    if qw.fmt != Fmt.MXFP4 or qw.N % 32 or qw.K % 64:
+        raise ValueError("tile_mx needs an MXFP4 weight with N % 32 == 0 and K % 64 == 0")
+    N, K = qw.N, qw.K
+    P = qw.payload.reshape(N // 32, 2, 2, 8, K // 64, 4, 2, 4)          # (rt, half, r8, g, kt, j, hi, t)
+    w = P.permute(0, 4, 1, 3, 7, 5, 6, 2).contiguous()                  # (rt, kt, half, g, t, j, hi, r8)
+    w = w.reshape(N // 32, K // 64, 2, 32, 16).view(torch.int32).reshape(N // 32, K // 64, 2, 32, 4)
+    sz = qw.scales.reshape(N // 16, 16, K // 32).permute(0, 2, 1).contiguous()
+    return w, sz

@@ -35,6 +35,8 @@ def _c(v):
 # exact integers.  Measured on B200 it executes 38 % fewer instructions but is not faster end to end (the
 # activation quantisation pass costs what the leaner loop saves), so the bf16 MMA path is the default.
 W4_I8 = os.environ.get("GRIMOIRE_W4_I8", "0") != "0"
+# MXFP4 small-M products through the tiled kernel (GRIMOIRE_MX_TILED=0: the natural-layout kernel of smallm_mx.cu)
+MX_TILED = os.environ.get("GRIMOIRE_MX_TILED", "1") != "0"
 
 
 def quant_x_i8(x: torch.Tensor, K: int, group: int, ws: Workspace):
@@ -246,10 +248,16 @@ class MXLinear:
         self.ws = workspace or default_workspace(device)
         self.tiled = None
         self.out_features = self.N // 2 if swiglu else self.N
+        self.tw = self.tsz = None
         if self.device.type == "cuda":
             self.w = qw.payload.to(self.device).contiguous()
             self.s = qw.scales.to(self.device).contiguous()
             self.w_ref = None
+            if qw.N % 32 == 0 and qw.K % 64 == 0 and MX_TILED:
+                from ..formats.w4_tile_layout import tile_mx
+
+                tw, tsz = tile_mx(qw)
+                self.tw, self.tsz = tw.to(self.device), tsz.to(self.device)
         else:
             self.w = self.s = None
             self.w_ref = qw.dequant()
@@ -264,6 +272,18 @@ class MXLinear:
         if self.device.type != "cuda":
             return W4Linear._forward_ref(self, x, out, epi)
         lib = _native.cuda()
+        if M <= SMALLM_MAX and self.tw is not None:
+            # tiled path: the int4 kernel's ring / warp layout / epilogues with the MXFP4 math
+            ld16 = self.K
+            x16 = self.ws.get("mx_x16p", SMALLM_MAX * ld16, torch.float16).view(-1)[: M * ld16].view(M, ld16)
+            _native.check(lib.grm_x16_lane_order(_native.ptr(x), _c(x.stride(0)), _native.ptr(x16), _c(ld16), _c(M), _c(self.K),
+                                                 _native.stream_ptr()), "x16_lane_order")
+            rows = 32 if (self.swiglu or self.N // 32 >= 2 * _SMS) and M <= 16 else 16
+            code = lib.grm_smallm_mx_tiled(_native.ptr(self.tw), _native.ptr(self.tsz), _native.ptr(x16), _native.ptr(out), None, None,
+                                           _c(M), _c(self.N), _c(self.K), _c(ld16), _c(out.stride(0)), _c(EPI[epi]), _c(rows), _c(1),
+                                           _native.stream_ptr())
+            _native.check(code, f"smallm_mx_tiled {self.name} M={M} N={self.N} K={self.K}")
+            return out
         if M <= SMALLM_MAX:
             ld16 = (self.K + 7) // 8 * 8
             x16 = self.ws.get("mx_x16", 8 * ld16, torch.float16)
