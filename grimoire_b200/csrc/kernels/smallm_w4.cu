@@ -357,125 +357,141 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       xa[mt] = xb[mt] = make_uint4(0u, 0u, 0u, 0u);
       if (xok[mt]) { xa[mt] = __ldg(xp[mt]); xb[mt] = __ldg(xp[mt] + 1); }
     }
-    constexpr int kAhead = 4;   // k tiles of L1 prefetch distance (one 128-byte line per row and k tile)
-
-    uint32_t stg = 0, phase = 0;
-    int sub = 0;
-    bool dead = !mbar_wait(&bars[RING], 0u, p.status, 0x5ffu);
-    const uint32_t* szp = szs + g;
-    const uint32_t ones = 0x3f803f80u;   // bf16 {1, 1}
-    int kt = kt0;
-
+    // Main loop, one ring stage (kSK k tiles) per iteration, fully unrolled inside (constant shared-memory offsets, one
+    // barrier wait and one refill per stage, the instruction streams of neighbouring k tiles interleave).
+    static_assert(RING == 2, "the stage toggle below assumes two ring stages");
+    auto run16 = [&](auto g64c) {
+      constexpr int G64 = decltype(g64c)::value;       // k tiles per quantisation group (MXFP4: 1, two blocks per k tile)
+      constexpr int GPS = kSK / G64;                   // groups per full stage
+      uint32_t stg = 0, phase = 0;
+      bool dead = !mbar_wait(&bars[RING], 0u, p.status, 0x5ffu);
+      const uint32_t* szp = szs + g;
+      const uint32_t ones = 0x3f803f80u;   // bf16 {1, 1}
 #pragma unroll 1
-    for (int grp = gbeg; grp < gend && !dead; ++grp, szp += p.szw) {
-      float sc[R][2], zf[R][2];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        if constexpr (MX) {
-          // e8m0 bytes of the two 32-wide blocks of this k tile: [block][16 rows]; rows g and g + 8 of each
-          const uint8_t* sb = reinterpret_cast<const uint8_t*>(szp - g + (size_t)r * p.szg * p.szw);
-          sc[r][0] = __uint_as_float((uint32_t)sb[g] << 23); sc[r][1] = __uint_as_float((uint32_t)sb[g + 8] << 23);         // block 0
-          zf[r][0] = __uint_as_float((uint32_t)sb[16 + g] << 23); zf[r][1] = __uint_as_float((uint32_t)sb[24 + g] << 23);   // block 1
-        } else {
-          const uint32_t s0 = szp[r * p.szg * 16], s1 = szp[r * p.szg * 16 + 8];
-          sc[r][0] = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
-          sc[r][1] = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
-          zf[r][0] = bf16hi_to_f(s0);      // 128 + zero
-          zf[r][1] = bf16hi_to_f(s1);
-        }
-      }
-      float accg[R][MT][4], xsum[MT][4];
-      float accg2[MX ? R : 1][MX ? MT : 1][4];      // MXFP4: the k tile's second 32-wide block
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          xsum[mt][c] = 0.f;
-#pragma unroll
-          for (int r = 0; r < R; ++r) {
-            accg[r][mt][c] = 0.f;
-            if constexpr (MX) accg2[r][mt][c] = 0.f;
-          }
-        }
-      }
-#pragma unroll 1
-      for (int kk = 0; kk < p.g64; ++kk, ++kt) {
-        if (sub == 0 && !mbar_try_wait(&bars[stg], phase)) {
+      for (int kt = kt0; kt < kt1 && !dead; kt += kSK, szp += GPS * p.szw) {
+        const int nt = min(kSK, kt1 - kt);
+        if (!mbar_try_wait(&bars[stg], phase)) {
           if (!stage_wait_slow(&bars[stg], phase, p.status, 0x500u | stg)) { dead = true; break; }
         }
-        uint4 wuse[R];
+        const uint8_t* sbase = ring + stg * kStage + lane * 16;
+        float accg[R][MT][4], xsum[MT][4];
+        float accg2[MX ? R : 1][MX ? MT : 1][4];      // MXFP4: the k tile's second 32-wide block
 #pragma unroll
-        for (int r = 0; r < R; ++r)
-          wuse[r] = *reinterpret_cast<const uint4*>(ring + stg * kStage + sub * (R * 512) + r * 512 + lane * 16);
-        uint32_t b[MT][8];
+        for (int s = 0; s < kSK; ++s) {
+          if (s < nt) {
+            if (s % G64 == 0) {
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                  xsum[mt][c] = 0.f;
+#pragma unroll
+                  for (int r = 0; r < R; ++r) {
+                    accg[r][mt][c] = 0.f;
+                    if constexpr (MX) accg2[r][mt][c] = 0.f;
+                  }
+                }
+            }
+            uint4 wuse[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) wuse[r] = *reinterpret_cast<const uint4*>(sbase + s * (R * 512) + r * 512);
+            uint32_t b[MT][8];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              b[mt][0] = xa[mt].x; b[mt][1] = xa[mt].y; b[mt][2] = xa[mt].z; b[mt][3] = xa[mt].w;
+              b[mt][4] = xb[mt].x; b[mt][5] = xb[mt].y; b[mt][6] = xb[mt].z; b[mt][7] = xb[mt].w;
+            }
+            if (s == nt - 1) {
+              __syncwarp();   // every lane has read the stage: it may be refilled
+              if (lane == 0) fill_stage<R>(ring + stg * kStage, wsrc, kt + RING * kSK, kt1, &bars[stg]);
+            }
+            if (kt + s + 1 < kt1) {
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+                if (xok[mt]) { xa[mt] = __ldg(xp[mt] + 8 * (s + 1)); xb[mt] = __ldg(xp[mt] + 8 * (s + 1) + 1); }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if constexpr (MX) {
+                // MXFP4: a word holds the four A-fragment bytes of k16 step j (two e2m1 per byte), expanded by the hardware
+                // e2m1x2 -> f16x2 conversion; steps 0,1 belong to block 0 of the k tile, steps 2,3 to block 1
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                  const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
+                  const uint32_t a0 = cvt_e2m1x2_f16(u), a1 = cvt_e2m1x2_f16(u >> 8), a2 = cvt_e2m1x2_f16(u >> 16), a3 = cvt_e2m1x2_f16(u >> 24);
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt)
+                    mma_f16_16816_w4(j < 2 ? accg[r][mt] : accg2[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
+                }
+              } else {
+                // int4: nibbles -> bf16 integers 128+q (one logic op per pair).  The zero point is NOT subtracted per
+                // element: an extra MMA with an all-ones A operand accumulates sum_k x, and (128 + zero) * sum_k x is
+                // removed when the group is flushed.
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(xsum[mt], ones, ones, ones, ones, b[mt][2 * j], b[mt][2 * j + 1]);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                  const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
+                  const uint32_t a0 = lop3_or_and(u, 0x000f000fu, 0x43004300u);
+                  const uint32_t a1 = lop3_or_and(u >> 4, 0x000f000fu, 0x43004300u);
+                  const uint32_t a2 = lop3_or_and(u >> 8, 0x000f000fu, 0x43004300u);
+                  const uint32_t a3 = lop3_or_and(u >> 12, 0x000f000fu, 0x43004300u);
+#pragma unroll
+                  for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(accg[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
+                }
+              }
+            }
+            if ((s + 1) % G64 == 0) {
+              const int gi = s / G64;
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                float sc0, sc1, zf0, zf1;
+                if constexpr (MX) {
+                  // e8m0 bytes of the two 32-wide blocks of this k tile: [block][16 rows]; rows g and g + 8 of each
+                  const uint8_t* sb = reinterpret_cast<const uint8_t*>(szp - g + (size_t)gi * p.szw + (size_t)r * p.szg * p.szw);
+                  sc0 = __uint_as_float((uint32_t)sb[g] << 23); sc1 = __uint_as_float((uint32_t)sb[g + 8] << 23);
+                  zf0 = __uint_as_float((uint32_t)sb[16 + g] << 23); zf1 = __uint_as_float((uint32_t)sb[24 + g] << 23);
+                } else {
+                  const uint32_t s0 = szp[gi * 16 + r * p.szg * 16], s1 = szp[gi * 16 + r * p.szg * 16 + 8];
+                  sc0 = __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu)));
+                  sc1 = __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu)));
+                  zf0 = bf16hi_to_f(s0);      // 128 + zero
+                  zf1 = bf16hi_to_f(s1);
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                  if constexpr (MX) {
+                    acc[r][mt][0] = fmaf(sc0, accg[r][mt][0], fmaf(zf0, accg2[r][mt][0], acc[r][mt][0]));
+                    acc[r][mt][1] = fmaf(sc0, accg[r][mt][1], fmaf(zf0, accg2[r][mt][1], acc[r][mt][1]));
+                    acc[r][mt][2] = fmaf(sc1, accg[r][mt][2], fmaf(zf1, accg2[r][mt][2], acc[r][mt][2]));
+                    acc[r][mt][3] = fmaf(sc1, accg[r][mt][3], fmaf(zf1, accg2[r][mt][3], acc[r][mt][3]));
+                  } else {
+                    acc[r][mt][0] = fmaf(sc0, fmaf(-zf0, xsum[mt][0], accg[r][mt][0]), acc[r][mt][0]);
+                    acc[r][mt][1] = fmaf(sc0, fmaf(-zf0, xsum[mt][1], accg[r][mt][1]), acc[r][mt][1]);
+                    acc[r][mt][2] = fmaf(sc1, fmaf(-zf1, xsum[mt][2], accg[r][mt][2]), acc[r][mt][2]);
+                    acc[r][mt][3] = fmaf(sc1, fmaf(-zf1, xsum[mt][3], accg[r][mt][3]), acc[r][mt][3]);
+                  }
+                }
+              }
+            }
+          }
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          b[mt][0] = xa[mt].x; b[mt][1] = xa[mt].y; b[mt][2] = xa[mt].z; b[mt][3] = xa[mt].w;
-          b[mt][4] = xb[mt].x; b[mt][5] = xb[mt].y; b[mt][6] = xb[mt].z; b[mt][7] = xb[mt].w;
-        }
-        __syncwarp();   // every lane has its weight words in registers: the stage may be refilled
-        if (lane == 0 && (sub == kSK - 1 || kt + 1 == kt1)) fill_stage<R>(ring + stg * kStage, wsrc, kt - sub + RING * kSK, kt1, &bars[stg]);
-        if (kt + 1 < kt1) {
+          xp[mt] += 8 * kSK;
+          if (xok[mt] && t == 0 && kt + 3 * kSK < kt1) {
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            xp[mt] += 8;   // 64 bf16
-            if (xok[mt]) {
-              xa[mt] = __ldg(xp[mt]); xb[mt] = __ldg(xp[mt] + 1);
-              if (t == 0 && kt + kAhead < kt1) asm volatile("prefetch.global.L1 [%0];" ::"l"(xp[mt] + 8 * (kAhead - 1)));
-            }
+            for (int l = 0; l < kSK; ++l) asm volatile("prefetch.global.L1 [%0];" ::"l"(xp[mt] + 8 * kSK + 8 * l));
           }
         }
-        // Nibbles -> bf16 integers 128+q (one logic op per pair).  The zero point is NOT subtracted
-        // per element: an extra MMA with an all-ones A operand accumulates sum_k x, and
-        // (128 + zero) * sum_k x is removed when the group is flushed.
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if constexpr (MX) {
-            // MXFP4: a word holds the four A-fragment bytes of k16 step j (two e2m1 per byte); the hardware e2m1x2 -> f16x2
-            // conversion yields each fragment register; steps 0,1 belong to block 0 (accg), steps 2,3 to block 1 (xsum reused
-            // per r is not possible, so block 1 accumulates in accg2)
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-              const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
-              const uint32_t a0 = cvt_e2m1x2_f16(u), a1 = cvt_e2m1x2_f16(u >> 8), a2 = cvt_e2m1x2_f16(u >> 16), a3 = cvt_e2m1x2_f16(u >> 24);
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) mma_f16_16816_w4(j < 2 ? accg[r][mt] : accg2[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
-            }
-            continue;
-          }
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(xsum[mt], ones, ones, ones, ones, b[mt][2 * j], b[mt][2 * j + 1]);
-#pragma unroll
-          for (int r = 0; r < R; ++r) {
-            const uint32_t u = j == 0 ? wuse[r].x : (j == 1 ? wuse[r].y : (j == 2 ? wuse[r].z : wuse[r].w));
-            const uint32_t a0 = lop3_or_and(u, 0x000f000fu, 0x43004300u);
-            const uint32_t a1 = lop3_or_and(u >> 4, 0x000f000fu, 0x43004300u);
-            const uint32_t a2 = lop3_or_and(u >> 8, 0x000f000fu, 0x43004300u);
-            const uint32_t a3 = lop3_or_and(u >> 12, 0x000f000fu, 0x43004300u);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(accg[r][mt], a0, a1, a2, a3, b[mt][2 * j], b[mt][2 * j + 1]);
-          }
-        }
-        if (++sub == kSK) { sub = 0; stg = (stg + 1) & (RING - 1); phase ^= (stg == 0); }
+        stg ^= 1u;
+        phase ^= (stg == 0u);
       }
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          if constexpr (MX) {
-            // rows g (c0, c1) and g + 8 (c2, c3): block 0 scales in sc, block 1 scales in zf
-            acc[r][mt][0] = fmaf(sc[r][0], accg[r][mt][0], fmaf(zf[r][0], accg2[r][mt][0], acc[r][mt][0]));
-            acc[r][mt][1] = fmaf(sc[r][0], accg[r][mt][1], fmaf(zf[r][0], accg2[r][mt][1], acc[r][mt][1]));
-            acc[r][mt][2] = fmaf(sc[r][1], accg[r][mt][2], fmaf(zf[r][1], accg2[r][mt][2], acc[r][mt][2]));
-            acc[r][mt][3] = fmaf(sc[r][1], accg[r][mt][3], fmaf(zf[r][1], accg2[r][mt][3], acc[r][mt][3]));
-            continue;
-          }
-          acc[r][mt][0] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][0], accg[r][mt][0]), acc[r][mt][0]);
-          acc[r][mt][1] = fmaf(sc[r][0], fmaf(-zf[r][0], xsum[mt][1], accg[r][mt][1]), acc[r][mt][1]);
-          acc[r][mt][2] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][2], accg[r][mt][2]), acc[r][mt][2]);
-          acc[r][mt][3] = fmaf(sc[r][1], fmaf(-zf[r][1], xsum[mt][3], accg[r][mt][3]), acc[r][mt][3]);
-        }
-    }
+    };
+    if constexpr (MX) run16(std::integral_constant<int, 1>{});
+    else if (p.g64 == 1) run16(std::integral_constant<int, 1>{});
+    else if (p.g64 == 2) run16(std::integral_constant<int, 2>{});
+    else run16(std::integral_constant<int, 4>{});
     }   // bf16 path
   }
 
