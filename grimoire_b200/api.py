@@ -26,6 +26,11 @@ class UnsupportedModel(ValueError):
     pass
 
 
+# --proj values with a runtime projection: int4 g128 (default; 'native' keeps a stored int4 / MXFP4 / fp8 checkpoint's own
+# format), MXFP4, block-scaled fp8 ('fp8'), and the byte-per-weight formats with per-row or per-32 scales
+_SERVED_PROJ = ("int4", "native", "mxfp4", "fp8", "int8", "bf16", "mxfp8", "fp8_e4m3", "fp8_e5m2")
+
+
 def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     """Refusal by name before any weight is read (unsupported_reason, grimoire.cpp:6969)."""
     if ec.tp_world > 1:
@@ -62,9 +67,10 @@ class Grimoire:
         else:
             from .tokenizer import Tokenizer
 
-            if ec.proj not in ("int4", "mxfp4", "fp8", "native"):
-                raise UnsupportedModel(f"--proj {ec.proj}: this build serves int4 (g128), mxfp4 and block-scaled fp8 projections "
-                                       f"(bf16 lm_head optional)")
+            if ec.proj == "fp8-e5m2" or ec.proj == "fp8-e4m3":
+                ec.proj = ec.proj.replace("-", "_")
+            if ec.proj not in _SERVED_PROJ:
+                raise UnsupportedModel(f"--proj {ec.proj}: this build serves {sorted(_SERVED_PROJ)}")
             if ec.model.endswith(".gguf"):
                 # GGUF: config and tokenizer from the metadata, tensors dequantised block by block and re-quantised
                 # to the serving format (the reference's native GGUF path keeps the file's blocks; this one does not)
@@ -75,7 +81,7 @@ class Grimoire:
 
                 gf = G.GGUFFile(ec.model)
                 cfg = G.config_from_gguf(gf)
-                if ec.proj in ("mxfp4", "fp8"):
+                if ec.proj not in ("int4", "native"):
                     cfg = dataclasses.replace(cfg, quant=ec.proj)
                 why = unsupported_reason(cfg, ec)
                 if why:

@@ -122,6 +122,35 @@ def bench_mx(args) -> None:
               f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
 
 
+def bench_rowq(args) -> None:
+    """Byte-per-weight small-M kernel (int8 with a scale per row unless --fmt names another format)."""
+    from ..formats.codecs import PROJ_NAMES, Fmt
+    from ..formats.quantize import QuantWeight
+    from ..ops.linear import RowQLinear
+
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    fmt = PROJ_NAMES[args.fmt]
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        width = 2 if fmt == Fmt.BF16 else 1
+        nbytes = N * K_ * width + (N * K_ // 32 if fmt == Fmt.MXFP8 else 4 * N)
+        copies = max(2, int(L2_BYTES * 2 // nbytes) + 1)
+        lins = []
+        for _ in range(copies):
+            pay = torch.randint(0, 120, (N, K_ * width), dtype=torch.uint8)
+            sc = None if fmt == Fmt.BF16 else (torch.full((N, K_ // 32), 120, dtype=torch.uint8) if fmt == Fmt.MXFP8
+                                              else torch.full((N,), 1e-3))
+            lins.append(RowQLinear(QuantWeight(fmt, N, K_, pay, scales=sc, group=32), dev, name, swiglu=sw))
+        x = torch.randn(args.rows, K_, device=dev).bfloat16()
+        out = torch.zeros(args.rows, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        us = timed(lambda i: lins[i % copies](x, out, epi), args.iters)
+        gbs = nbytes / 1e9 / (us * 1e-6)
+        print(f"smallm_rowq {args.fmt:8s} {name:8s} M={args.rows:2d} N={N:6d} K={K_:6d} copies={copies:2d}  {us:8.2f} us  {gbs:7.0f} GB/s  "
+              f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
+
+
 def bench_gemm(args) -> None:
     _, tf, tag = peaks()
     dev = "cuda"
@@ -192,14 +221,15 @@ def bench_prefill(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["smallm", "mx", "gemm", "attn", "prefill"])
+    ap.add_argument("what", choices=["smallm", "mx", "rowq", "gemm", "attn", "prefill"])
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--splits", type=int, default=0, help="attn: split-KV factor (0 = the engine's heuristic)")
+    ap.add_argument("--fmt", default="int8", help="rowq: int8 / bf16 / fp8_e4m3 / fp8_e5m2 / mxfp8")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
-    {"smallm": bench_smallm, "mx": bench_mx, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
+    {"smallm": bench_smallm, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
     print(f"launches={_native.launch_count}", flush=True)
 
 

@@ -112,14 +112,14 @@ def concat_rows(parts: list[QuantWeight]) -> QuantWeight:
         if p.fmt != f.fmt or p.K != f.K or p.group != f.group:
             raise ValueError("concat_rows: mismatched weights")
     return QuantWeight(f.fmt, sum(p.N for p in parts), f.K, torch.cat([p.payload for p in parts]),
-                       scales=torch.cat([p.scales for p in parts]),
+                       scales=None if f.scales is None else torch.cat([p.scales for p in parts]),
                        zeros=None if f.zeros is None else torch.cat([p.zeros for p in parts]), group=f.group)
 
 
 def interleave_gate_up_q(gate: QuantWeight, up: QuantWeight) -> QuantWeight:
     """Quantized version of ``interleave_gate_up`` (rows permuted, codes untouched)."""
     return QuantWeight(gate.fmt, gate.N * 2, gate.K, interleave_gate_up(gate.payload, up.payload),
-                       scales=interleave_gate_up(gate.scales, up.scales),
+                       scales=None if gate.scales is None else interleave_gate_up(gate.scales, up.scales),
                        zeros=None if gate.zeros is None else interleave_gate_up(gate.zeros, up.zeros), group=gate.group)
 
 

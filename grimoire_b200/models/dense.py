@@ -23,10 +23,13 @@ from ..formats.quantize import QuantWeight, quantize, slice_cols, slice_rows
 from ..formats.w4_tile_layout import concat_rows, interleave_gate_up_q
 from ..ops import core as K
 from ..ops import ref
-from ..ops.linear import BF16Linear, MXLinear, W4Linear
+from ..ops.linear import BF16Linear, MXLinear, ROWQ_KIND, RowQLinear, W4Linear
 from ..ops.workspace import Workspace
 from ..utils import trace
 from .config import ModelConfig
+
+# --proj names served by the byte-per-weight kernel (per-row scale, or e8m0 per 32 for mxfp8)
+_ROWQ_PROJ = {"int8": Fmt.INT8, "bf16": Fmt.BF16, "mxfp8": Fmt.MXFP8, "fp8_e4m3": Fmt.FP8_E4M3, "fp8_e5m2": Fmt.FP8_E5M2}
 
 
 @dataclass
@@ -125,6 +128,11 @@ class DenseModel:
             if isinstance(w, QuantWeight):
                 return w if w.fmt == Fmt.MXFP4 else quantize(w.dequant(), Fmt.MXFP4)
             return quantize(w, Fmt.MXFP4)
+        if cfg.quant in _ROWQ_PROJ:
+            fmt = _ROWQ_PROJ[cfg.quant]
+            if isinstance(w, QuantWeight):
+                return w if w.fmt == fmt else quantize(w.dequant(), fmt)
+            return quantize(w, fmt)
         if isinstance(w, QuantWeight):
             return w if w.fmt == Fmt.INT4 else quantize(w.dequant(), Fmt.INT4, group=cfg.quant_group)
         return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
@@ -136,6 +144,8 @@ class DenseModel:
             from ..ops.hybrid import FP8BlockLinear
 
             return FP8BlockLinear(qw, self.device, name)
+        if qw.fmt in ROWQ_KIND:
+            return RowQLinear(qw, self.device, name, swiglu=swiglu, workspace=self.ws)
         cls = MXLinear if qw.fmt == Fmt.MXFP4 else W4Linear
         return cls(qw, self.device, name, swiglu=swiglu, workspace=self.ws)
 
@@ -244,7 +254,7 @@ class DenseModel:
 
         ck = Checkpoint(path)
         cfg = ck.cfg
-        if proj in ("mxfp4", "fp8"):
+        if proj in ("mxfp4", "fp8") or proj in _ROWQ_PROJ:
             import dataclasses
 
             cfg = dataclasses.replace(cfg, quant=proj)
@@ -327,7 +337,7 @@ class DenseModel:
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
         if (rb.mode == "prefill" and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
-                and self.tp.sp_ready(rb.tokens.shape[0]) and self.tp.sp_enabled):
+                and isinstance(self.layers[0].qkv, (W4Linear, RowQLinear)) and self.tp.sp_ready(rb.tokens.shape[0]) and self.tp.sp_enabled):
             return self.forward_prefill_sp(rb, buf, kv_layers, block_table)
         cfg, geom = self.cfg, self.geom
         M = rb.tokens.shape[0]

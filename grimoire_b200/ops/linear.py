@@ -206,6 +206,64 @@ class BF16Linear:
     __call__ = forward
 
 
+ROWQ_KIND = {Fmt.BF16: 0, Fmt.INT8: 1, Fmt.FP8_E4M3: 2, Fmt.FP8_E5M2: 3, Fmt.MXFP8: 4}
+
+
+class RowQLinear:
+    """Projection in one of the byte-per-weight formats of ``--proj`` (bf16, int8, fp8 e4m3 / e5m2 with a scale per
+    output row, MXFP8 with an e8m0 scale per 32 weights): the reference's int8 / fp8 / mxfp8 / bf16 GEMV and small-M
+    rows (src/gemv_decode.cpp:77-347, src/gemm_fast.cpp).  Up to 8 rows stream the weight through smallm_rowq.cu (wider
+    small batches in chunks of 8); tall inputs dequantise into the shared bf16 scratch and run the tcgen05 GEMM.
+    ``swiglu`` weights are gate/up interleaved per 16 rows, as for the int4 path."""
+
+    def __init__(self, qw: QuantWeight, device, name: str = "", swiglu: bool = False, workspace: Optional[Workspace] = None):
+        if qw.fmt not in ROWQ_KIND or qw.K % 32:
+            raise ValueError(f"RowQLinear: unsupported weight {qw.fmt!r} K={qw.K}")
+        self.name, self.N, self.K, self.swiglu, self.fmt = name, qw.N, qw.K, swiglu, qw.fmt
+        self.kind = ROWQ_KIND[qw.fmt]
+        self.device = torch.device(device)
+        self.ws = workspace or default_workspace(self.device)
+        self.out_features = self.N // 2 if swiglu else self.N
+        self.w = qw.payload.to(self.device).contiguous()
+        self.scale = self.e8 = None
+        if qw.fmt == Fmt.MXFP8:
+            self.e8 = qw.scales.to(self.device).contiguous()
+        elif qw.scales is not None:
+            self.scale = qw.scales.float().to(self.device).contiguous()
+        self.w_ref = qw.dequant() if self.device.type != "cuda" else None
+
+    def nbytes(self) -> int:
+        return self.w.numel() + (0 if self.scale is None else self.scale.numel() * 4) + (0 if self.e8 is None else self.e8.numel())
+
+    def dequant_into_scratch(self) -> torch.Tensor:
+        wb = self.ws.get("dequant_bf16", self.N * self.K, torch.bfloat16).view(-1)[: self.N * self.K].view(self.N, self.K)
+        code = _native.cuda().grm_dequant_rowq(_native.ptr(self.w), _native.ptr(self.scale), _native.ptr(self.e8), _native.ptr(wb),
+                                               _c(self.kind), _c(self.N), _c(self.K), ctypes.c_long(self.w.stride(0)), _c(self.K),
+                                               _native.stream_ptr())
+        _native.check(code, f"dequant_rowq {self.name}")
+        return wb
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
+        M = x.shape[0]
+        if self.swiglu and epi != "swiglu":
+            raise ValueError("a gate|up interleaved weight must run with the swiglu epilogue")
+        if self.device.type != "cuda":
+            return W4Linear._forward_ref(self, x, out, epi)
+        if M > SMALLM_MAX:
+            return gemm_bf16(x, self.dequant_into_scratch(), out, epi)
+        lib = _native.cuda()
+        for m0 in range(0, M, 8):
+            m = min(8, M - m0)
+            code = lib.grm_smallm_rowq(_native.ptr(self.w), _native.ptr(self.scale), _native.ptr(self.e8), _native.ptr(x[m0: m0 + m]),
+                                       _native.ptr(out[m0: m0 + m]), _c(self.kind), _c(m), _c(self.N), _c(self.K),
+                                       ctypes.c_long(self.w.stride(0)), _c(x.stride(0)), _c(out.stride(0)), _c(EPI[epi]),
+                                       _native.stream_ptr())
+            _native.check(code, f"smallm_rowq {self.name} M={m} N={self.N} K={self.K}")
+        return out
+
+    __call__ = forward
+
+
 def gemm_bf16_tp(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], epi: str, *, peer_out=None, peer_cnt=None,
                  world: int = 1, my_rank: int = 0, ag_cnt: Optional[torch.Tensor] = None, ag_expect: int = 0, ldo: int = 0) -> int:
     """Tensor-parallel variants of the tcgen05 GEMM (see grm_gemm_bf16_tp): ``epi='rs_push'`` pushes
@@ -223,7 +281,9 @@ def gemm_bf16_tp(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], 
 
 
 def w4_dequant_into(lin: "W4Linear") -> torch.Tensor:
-    """Dequantize an int4 projection into the shared bf16 scratch and return the [N][K] view."""
+    """Dequantize an int4 (or byte-per-weight) projection into the shared bf16 scratch and return the [N][K] view."""
+    if isinstance(lin, RowQLinear):
+        return lin.dequant_into_scratch()
     t = lin.tiled
     wbuf = lin.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
     code = _native.cuda().grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
