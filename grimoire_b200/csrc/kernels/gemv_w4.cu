@@ -1,0 +1,165 @@
+// gemv_w4: Y[1][N] = X[1][K] . W[N][K]^T for int4 (group 64/128/256, fp16 scale, integer zero) weights in the tiled
+// execution layout of formats/w4_tile_layout.py -- the single-row decode step, the reference's gemv_impl int4 row
+// (src/gemv_decode.cpp:77-347).
+//
+// One batch row leaves 7/8 of an m16n8k16 MMA empty and the fragment dequantisation of the tensor-core kernel
+// (smallm_w4.cu) costs ~5 instructions per weight, so a single row runs on the CUDA cores instead, at ~2 instructions
+// per weight: a lane's 16-byte word group holds rows g and g + 8 of a 16-row tile for 16 consecutive k; one
+// logic op per nibble pair builds the fp16 pair {1024 + q, 1024 + q'} (or {1024 + 16 q, ...} for the odd nibbles),
+// one fp16x2 subtract / fma removes the bias and the zero point exactly, and one fp16x2 fma multiplies with the
+// activations (converted to fp16 once per CTA into shared memory).  The fp16 partial sums of one quantisation group
+// (16 or 32 products per accumulator half) are scaled and added into fp32.  A CTA owns one 16-row tile (SwiGLU: the
+// gate tile and its up tile); its 8 warps split K and reduce through shared memory in a fixed order, so there is no
+// cross-CTA reduction, no scratch and no atomics, and results are bit-reproducible.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kGvWarps = 8;
+
+struct GemvW4Params {
+  const uint4* w;         // tiles [N/32][K/64][2][32] x 16 bytes
+  const uint32_t* sz;     // [N/16][G][16]: fp16 scale | bf16(128 + zero) << 16
+  const bf16* x;          // [K]
+  void* out;              // bf16 or fp32 [N] (SwiGLU: bf16 [N/2])
+  int N, K, g64;
+};
+
+__device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));   // (a & mask) | orv
+  return r;
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// 8 weights of one 32-bit word (rows g and g + 8, four consecutive k) times their activations
+__device__ __forceinline__ void word_fma(uint32_t w, __half2 x01, __half2 x23, __half2 c_lo, __half2 c_hi, __half2& a0, __half2& a1) {
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  const uint32_t w2 = w >> 8;
+  const __half2 l0 = as_h2(lop3_or_and(w, 0x000f000fu, 0x64006400u)), h0 = as_h2(lop3_or_and(w, 0x00f000f0u, 0x64006400u));
+  const __half2 l1 = as_h2(lop3_or_and(w2, 0x000f000fu, 0x64006400u)), h1 = as_h2(lop3_or_and(w2, 0x00f000f0u, 0x64006400u));
+  a0 = __hfma2(__hsub2(l0, c_lo), x01, a0);                    // row g,     k = 4j, 4j + 1
+  a1 = __hfma2(__hfma2(h0, sixteenth, c_hi), x01, a1);         // row g + 8
+  a0 = __hfma2(__hsub2(l1, c_lo), x23, a0);                    // row g,     k = 4j + 2, 4j + 3
+  a1 = __hfma2(__hfma2(h1, sixteenth, c_hi), x23, a1);
+}
+
+// EPI: 0 bf16, 1 f32, 2 add_f32, 3 swiglu.  G64: k tiles per quantisation group.
+template <int EPI, int G64>
+__global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Params p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  __half* xs = reinterpret_cast<__half*>(gv_smem);                       // [K] fp16 activations
+  __shared__ float red[kGvWarps][16];
+  constexpr bool SW = EPI == 3;
+  constexpr int TILES = SW ? 2 : 1;               // 16-row tiles per CTA
+  constexpr int SLICES = kGvWarps / TILES;        // K slices per tile
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int KT = p.K >> 6, G = KT / G64;
+  const int tile = blockIdx.x * TILES + (SW ? warp / SLICES : 0);   // 16-row tile of this warp
+  const int slice = SW ? warp % SLICES : warp;
+  const int per = (G + SLICES - 1) / SLICES;
+  const int gbeg = slice * per, gend = min(gbeg + per, G);
+  const uint4* wp = p.w + ((size_t)(tile >> 1) * KT * 2 + (tile & 1)) * 32 + lane;   // + kt * 64
+  const uint32_t* szp = p.sz + (size_t)tile * G * 16 + g;
+
+  // first weights in flight before the activations are staged
+  uint4 cur[G64];
+  if (gbeg < gend) {
+#pragma unroll
+    for (int u = 0; u < G64; ++u) cur[u] = ldg_stream_v4(wp + (size_t)(gbeg * G64 + u) * 64);
+  }
+  for (int i = tid * 8; i < p.K; i += kGvWarps * 32 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p.x + i);
+    const uint32_t s[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 h = __floats2half2_rn(bf16lo_to_f(s[j]), bf16hi_to_f(s[j]));
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(xs + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  __syncthreads();
+
+  float f0 = 0.f, f1 = 0.f;
+  for (int grp = gbeg; grp < gend; ++grp) {
+    uint4 nxt[G64];
+    if (grp + 1 < gend) {
+#pragma unroll
+      for (int u = 0; u < G64; ++u) nxt[u] = ldg_stream_v4(wp + (size_t)((grp + 1) * G64 + u) * 64);
+    }
+    const uint32_t s0 = __ldg(szp + (size_t)grp * 16), s1 = __ldg(szp + (size_t)grp * 16 + 8);
+    const float z0 = bf16hi_to_f(s0) - 128.f, z1 = bf16hi_to_f(s1) - 128.f;
+    const __half2 c_lo = __float2half2_rn(1024.f + z0), c_hi = __float2half2_rn(-(64.f + z1));
+    __half2 a0 = __float2half2_rn(0.f), a1 = a0, b0 = a0, b1 = a0;
+#pragma unroll
+    for (int u = 0; u < G64; ++u) {
+      const uint4* xp = reinterpret_cast<const uint4*>(xs + ((size_t)(grp * G64 + u) * 64 + t * 16));
+      const uint4 xa = xp[0], xb = xp[1];
+      word_fma(cur[u].x, as_h2(xa.x), as_h2(xa.y), c_lo, c_hi, a0, a1);
+      word_fma(cur[u].y, as_h2(xa.z), as_h2(xa.w), c_lo, c_hi, b0, b1);
+      word_fma(cur[u].z, as_h2(xb.x), as_h2(xb.y), c_lo, c_hi, a0, a1);
+      word_fma(cur[u].w, as_h2(xb.z), as_h2(xb.w), c_lo, c_hi, b0, b1);
+    }
+    const float2 r0 = __half22float2(__hadd2(a0, b0)), r1 = __half22float2(__hadd2(a1, b1));
+    f0 += __half2float(__ushort_as_half((unsigned short)(s0 & 0xffffu))) * (r0.x + r0.y);
+    f1 += __half2float(__ushort_as_half((unsigned short)(s1 & 0xffffu))) * (r1.x + r1.y);
+#pragma unroll
+    for (int u = 0; u < G64; ++u) cur[u] = nxt[u];
+  }
+  // the four lanes of a row group hold disjoint k subsets
+  f0 += __shfl_xor_sync(0xffffffffu, f0, 1); f0 += __shfl_xor_sync(0xffffffffu, f0, 2);
+  f1 += __shfl_xor_sync(0xffffffffu, f1, 1); f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
+  if (t == 0) { red[warp][g] = f0; red[warp][g + 8] = f1; }
+  __syncthreads();
+  if (tid < 16) {
+    float s = 0.f, u = 0.f;
+#pragma unroll
+    for (int k = 0; k < SLICES; ++k) s += red[k][tid];
+    if (SW) {
+#pragma unroll
+      for (int k = 0; k < SLICES; ++k) u += red[SLICES + k][tid];
+    }
+    const size_t col = (size_t)blockIdx.x * 16 + tid;
+    if (EPI == 0) reinterpret_cast<bf16*>(p.out)[col] = __float2bfloat16(s);
+    else if (EPI == 1) reinterpret_cast<float*>(p.out)[col] = s;
+    else if (EPI == 2) reinterpret_cast<float*>(p.out)[col] += s;
+    else reinterpret_cast<bf16*>(p.out)[col] = __float2bfloat16(silu_f(s) * u);
+  }
+}
+
+template <int EPI>
+int launch_epi(const GemvW4Params& p, cudaStream_t st) {
+  const int tiles = p.N / 16;
+  const unsigned grid = (unsigned)(EPI == 3 ? tiles / 2 : tiles);
+  const size_t smem = (size_t)p.K * 2;
+  switch (p.g64) {
+    case 1: gemv_w4_kernel<EPI, 1><<<grid, kGvWarps * 32, smem, st>>>(p); break;
+    case 2: gemv_w4_kernel<EPI, 2><<<grid, kGvWarps * 32, smem, st>>>(p); break;
+    case 4: gemv_w4_kernel<EPI, 4><<<grid, kGvWarps * 32, smem, st>>>(p); break;
+    default: return -2;
+  }
+  GRM_LAUNCH_RET();
+}
+
+}  // namespace
+
+// One activation row.  w / sz: the tiled int4 layout (N % 32 == 0, K % 64 == 0, K % group == 0, K <= 20480 so that the
+// fp16 activations fit the default shared-memory window).  epi: 0 bf16, 1 f32, 2 add_f32, 3 swiglu (gate / up row tiles
+// interleaved, out has N / 2 columns).  Returns -2 on an unsupported shape.
+GRM_API int grm_gemv_w4(const void* w, const void* sz, const void* x, void* out, int N, int K, int group, int epi, void* stream) {
+  if ((N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || K > 20480 || epi < 0 || epi > 3 ||
+      ((uintptr_t)x & 15))
+    return -2;
+  GemvW4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
+  p.N = N; p.K = K; p.g64 = group / 64;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (epi) {
+    case 0: return launch_epi<0>(p, st);
+    case 1: return launch_epi<1>(p, st);
+    case 2: return launch_epi<2>(p, st);
+    default: return launch_epi<3>(p, st);
+  }
+}

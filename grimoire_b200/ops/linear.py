@@ -39,6 +39,9 @@ W4_I8 = os.environ.get("GRIMOIRE_W4_I8", "0") != "0"
 MX_TILED = os.environ.get("GRIMOIRE_MX_TILED", "1") != "0"
 
 
+GEMV_W4 = os.environ.get("GRIMOIRE_GEMV_W4", "1") != "0"   # single-row int4 projections on the CUDA-core GEMV
+
+
 def quant_x_i8(x: torch.Tensor, K: int, group: int, ws: Workspace):
     """bf16 rows -> (hi int8 [M][ldq], lo int8 [M][ldq], table float2 [M][K/group]) in workspace buffers."""
     M = x.shape[0]
@@ -124,6 +127,12 @@ class W4Linear:
             return self._forward_ref(x, out, epi)
         t = self.tiled
         lib = _native.cuda()
+        if M == 1 and GEMV_W4 and t.K <= 20480:
+            # one row: CUDA-core weight stream (gemv_w4.cu); the tensor-core kernel below serves 2..64 rows
+            code = lib.grm_gemv_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _c(t.N), _c(t.K), _c(t.group),
+                                   _c(EPI[epi]), _native.stream_ptr())
+            _native.check(code, f"gemv_w4 {self.name} N={t.N} K={t.K}")
+            return out
         if M <= SMALLM_MAX:
             rows, ksplit, tiles = self._plan_smallm(M)
             scratch = counters = None

@@ -49,18 +49,28 @@ def test_graph_replay_equals_eager(setup):
     assert gpu.counters["graph_replays"] > 0
 
 
-def test_batched_decode_is_bit_identical_to_solo(setup):
+def test_batched_decode_is_bit_identical_to_solo(setup, monkeypatch):
+    """With every batch width on the tensor-core small-M kernel (GRIMOIRE_GEMV_W4=0) a conversation's logits do not
+    depend on who shares its step; with the single-row CUDA-core GEMV (the default) they agree to rounding and pick
+    the same token."""
+    from grimoire_b200.ops import linear
+
     cfg, gpu, cpu, prompt = setup
-    sa, sb = gpu.open(), gpu.open()
-    la, lb = gpu.prefill(sa, prompt), gpu.prefill(sb, prompt[:61])
-    ta, tb = int(la.argmax()), int(lb.argmax())
-    both, lg = gpu.decode_rows([ta, tb], [sa, sb], [sa.length, sb.length], use_graph=False, return_logits=True)
-    lg = lg.clone()
-    solo, l1 = gpu.decode_rows([tb], [sb], [sb.length], use_graph=False, return_logits=True)
-    assert both[1] == solo[0]
-    assert torch.equal(lg[1], l1[0])
-    gpu.release(sa), gpu.release(sb)
-    assert gpu.kv.pages_used() == 0
+    for gemv in (False, True):
+        monkeypatch.setattr(linear, "GEMV_W4", gemv)
+        sa, sb = gpu.open(), gpu.open()
+        la, lb = gpu.prefill(sa, prompt), gpu.prefill(sb, prompt[:61])
+        ta, tb = int(la.argmax()), int(lb.argmax())
+        both, lg = gpu.decode_rows([ta, tb], [sa, sb], [sa.length, sb.length], use_graph=False, return_logits=True)
+        lg = lg.clone()
+        solo, l1 = gpu.decode_rows([tb], [sb], [sb.length], use_graph=False, return_logits=True)
+        assert both[1] == solo[0]
+        if gemv:
+            assert float((lg[1] - l1[0]).abs().max()) < 0.02 * max(1.0, float(l1[0].abs().max()))
+        else:
+            assert torch.equal(lg[1], l1[0])
+        gpu.release(sa), gpu.release(sb)
+        assert gpu.kv.pages_used() == 0
 
 
 def test_tiny_model_on_gpu_matches_cpu(setup):
