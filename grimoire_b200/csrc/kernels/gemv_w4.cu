@@ -69,7 +69,12 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
 #pragma unroll
     for (int u = 0; u < G64; ++u) cur[u] = ldg_stream_v4(wp + (size_t)(gbeg * G64 + u) * 64);
   }
-  for (int i = tid * 8; i < p.K; i += kGvWarps * 32 * 8) {
+  // activations -> fp16 in shared memory.  Without SwiGLU every K slice belongs to one warp, which stages just its
+  // own columns and needs no CTA barrier; the gate and up warps of a SwiGLU CTA share slices and stage together.
+  const int xbeg = SW ? tid * 8 : gbeg * G64 * 64 + lane * 8;
+  const int xend = SW ? p.K : min(gend * G64 * 64, p.K);
+  const int xstep = SW ? kGvWarps * 32 * 8 : 256;
+  for (int i = xbeg; i < xend; i += xstep) {
     const uint4 v = *reinterpret_cast<const uint4*>(p.x + i);
     const uint32_t s[4] = {v.x, v.y, v.z, v.w};
     uint32_t o[4];
@@ -80,7 +85,8 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
     }
     *reinterpret_cast<uint4*>(xs + i) = make_uint4(o[0], o[1], o[2], o[3]);
   }
-  __syncthreads();
+  if (SW) __syncthreads();
+  else __syncwarp();
 
   float f0 = 0.f, f1 = 0.f;
   for (int grp = gbeg; grp < gend; ++grp) {
