@@ -23,6 +23,11 @@ struct GemvW4Params {
   const bf16* x;          // [K]
   void* out;              // bf16 or fp32 [N] (SwiGLU: bf16 [N/2])
   int N, K, g64;
+  // fused RMSNorm prologue (h != null): x = bf16(h * rsqrt(mean(h^2) + eps) * (offset + nw)) is computed by every CTA
+  // from the fp32 residual row instead of being read
+  const float* h;         // [K]
+  const float* nw;        // [K]
+  float eps, offset;
 };
 
 __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
@@ -71,12 +76,38 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
   }
   // activations -> fp16 in shared memory.  Without SwiGLU every K slice belongs to one warp, which stages just its
   // own columns and needs no CTA barrier; the gate and up warps of a SwiGLU CTA share slices and stage together.
+  float rnorm = 0.f;
+  if (p.h != nullptr) {
+    float ss = 0.f;
+    for (int i = tid * 4; i < p.K; i += kGvWarps * 32 * 4) {
+      const float4 a = *reinterpret_cast<const float4*>(p.h + i);
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp][0] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kGvWarps; ++k) ss += red[k][0];
+    rnorm = rsqrtf(ss / (float)p.K + p.eps);
+    __syncthreads();                       // red is reused by the K-slice reduction below
+  }
   const int xbeg = SW ? tid * 8 : gbeg * G64 * 64 + lane * 8;
   const int xend = SW ? p.K : min(gend * G64 * 64, p.K);
   const int xstep = SW ? kGvWarps * 32 * 8 : 256;
   for (int i = xbeg; i < xend; i += xstep) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p.x + i);
-    const uint32_t s[4] = {v.x, v.y, v.z, v.w};
+    uint32_t s[4];
+    if (p.h != nullptr) {
+      const float4 a = *reinterpret_cast<const float4*>(p.h + i), b = *reinterpret_cast<const float4*>(p.h + i + 4);
+      const float4 wa = *reinterpret_cast<const float4*>(p.nw + i), wb = *reinterpret_cast<const float4*>(p.nw + i + 4);
+      s[0] = pack_bf16x2(a.x * rnorm * (p.offset + wa.x), a.y * rnorm * (p.offset + wa.y));
+      s[1] = pack_bf16x2(a.z * rnorm * (p.offset + wa.z), a.w * rnorm * (p.offset + wa.w));
+      s[2] = pack_bf16x2(b.x * rnorm * (p.offset + wb.x), b.y * rnorm * (p.offset + wb.y));
+      s[3] = pack_bf16x2(b.z * rnorm * (p.offset + wb.z), b.w * rnorm * (p.offset + wb.w));
+    } else {
+      const uint4 v = *reinterpret_cast<const uint4*>(p.x + i);
+      s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+    }
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -153,14 +184,17 @@ int launch_epi(const GemvW4Params& p, cudaStream_t st) {
 
 // One activation row.  w / sz: the tiled int4 layout (N % 32 == 0, K % 64 == 0, K % group == 0, K <= 20480 so that the
 // fp16 activations fit the default shared-memory window).  epi: 0 bf16, 1 f32, 2 add_f32, 3 swiglu (gate / up row tiles
-// interleaved, out has N / 2 columns).  Returns -2 on an unsupported shape.
-GRM_API int grm_gemv_w4(const void* w, const void* sz, const void* x, void* out, int N, int K, int group, int epi, void* stream) {
+// interleaved, out has N / 2 columns).  h != null: x is ignored and the activations are RMSNorm(h) with weight nw
+// (fp32 [K] both), computed in the prologue.  Returns -2 on an unsupported shape.
+GRM_API int grm_gemv_w4_norm(const void* w, const void* sz, const void* x, const void* h, const void* nw, float eps, float offset,
+                             void* out, int N, int K, int group, int epi, void* stream) {
   if ((N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || K > 20480 || epi < 0 || epi > 3 ||
-      ((uintptr_t)x & 15))
+      (!h && ((uintptr_t)x & 15)) || (h && (!nw || ((uintptr_t)h & 15) || ((uintptr_t)nw & 15))))
     return -2;
   GemvW4Params p;
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.N = N; p.K = K; p.g64 = group / 64;
+  p.h = (const float*)h; p.nw = (const float*)nw; p.eps = eps; p.offset = offset;
   cudaStream_t st = (cudaStream_t)stream;
   switch (epi) {
     case 0: return launch_epi<0>(p, st);
@@ -168,4 +202,8 @@ GRM_API int grm_gemv_w4(const void* w, const void* sz, const void* x, void* out,
     case 2: return launch_epi<2>(p, st);
     default: return launch_epi<3>(p, st);
   }
+}
+
+GRM_API int grm_gemv_w4(const void* w, const void* sz, const void* x, void* out, int N, int K, int group, int epi, void* stream) {
+  return grm_gemv_w4_norm(w, sz, x, nullptr, nullptr, 0.f, 0.f, out, N, K, group, epi, stream);
 }

@@ -150,6 +150,16 @@ class DenseModel:
         return cls(qw, self.device, name, swiglu=swiglu, workspace=self.ws)
 
     @staticmethod
+    def _norm_linear(lin, h, norm_w, x, out, epi: str, eps: float, off: float) -> None:
+        """out = epi(lin(RMSNorm(h))): one launch when the projection can take the norm into its prologue (single-row
+        int4 GEMV), otherwise the norm kernel writes x and the projection reads it."""
+        fused = getattr(lin, "fused_norm", None)
+        if fused is not None and h.shape[0] == 1 and fused(h, norm_w, out, epi, eps, off):
+            return
+        K.add_rmsnorm(h, norm_w, x, eps, off)
+        lin(x, out, epi)
+
+    @staticmethod
     def _rows(w, a: int, b: int):
         return slice_rows(w, a, b) if isinstance(w, QuantWeight) else w[a:b]
 
@@ -356,8 +366,7 @@ class DenseModel:
         for li, L in enumerate(self.layers):
             kvl = kv_layers[li]
             if tl: trace.mark("norm+qkv")
-            K.add_rmsnorm(h, L.in_norm, x, eps, off)
-            L.qkv(x, qkv, "bf16")
+            self._norm_linear(L.qkv, h, L.in_norm, x, qkv, "bf16", eps, off)
             if tl: trace.mark("rope+attn")
             if prefill:
                 if rb.q_pos0 > 0:
@@ -371,8 +380,7 @@ class DenseModel:
             if tl: trace.mark("o_proj")
             self._row_parallel(L.o, attn, h)
             if tl: trace.mark("norm+gate_up")
-            K.add_rmsnorm(h, L.post_norm, x, eps, off)
-            L.gate_up(x, act, "swiglu")
+            self._norm_linear(L.gate_up, h, L.post_norm, x, act, "swiglu", eps, off)
             if tl: trace.mark("down")
             self._row_parallel(L.down, act, h)
         if tl: trace.mark("head")
@@ -386,7 +394,6 @@ class DenseModel:
             n = rb.logits_rows.shape[0]
             hsel = h.index_select(0, rb.logits_rows) if n != M else h
         xf, logits = buf.xf[:n], buf.logits[:n]
-        K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
-        self.lm_head(xf, logits, "f32")
+        self._norm_linear(self.lm_head, hsel, self.final_norm, xf, logits, "f32", eps, off)
         if tl: trace.mark("end")
         return logits

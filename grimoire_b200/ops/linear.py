@@ -42,6 +42,9 @@ MX_TILED = os.environ.get("GRIMOIRE_MX_TILED", "1") != "0"
 GEMV_W4 = os.environ.get("GRIMOIRE_GEMV_W4", "1") != "0"   # single-row int4 projections on the CUDA-core GEMV
 
 
+FUSED_NORM = os.environ.get("GRIMOIRE_FUSED_NORM", "1") != "0"   # RMSNorm inside the single-row GEMV prologue
+
+
 def quant_x_i8(x: torch.Tensor, K: int, group: int, ws: Workspace):
     """bf16 rows -> (hi int8 [M][ldq], lo int8 [M][ldq], table float2 [M][K/group]) in workspace buffers."""
     M = x.shape[0]
@@ -163,6 +166,19 @@ class W4Linear:
         return gemm_bf16(x, wbuf[: self.N], out, epi)
 
     __call__ = forward
+
+    def fused_norm(self, h: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, epi: str, eps: float, offset: float) -> bool:
+        """``out = epi(RMSNorm(h) @ W^T)`` for one fp32 residual row with the norm inside the GEMV prologue (one launch
+        instead of two).  Returns False when the shape or device is not served; the caller then runs norm + forward."""
+        t = self.tiled
+        if (not GEMV_W4 or not FUSED_NORM or self.device.type != "cuda" or t is None or h.shape[0] != 1 or t.K > 20480
+                or h.dtype != torch.float32 or h.shape[1] != t.K):
+            return False
+        code = _native.cuda().grm_gemv_w4_norm(_native.ptr(t.w), _native.ptr(t.sz), None, _native.ptr(h), _native.ptr(norm_w),
+                                               ctypes.c_float(eps), ctypes.c_float(offset), _native.ptr(out), _c(t.N), _c(t.K),
+                                               _c(t.group), _c(EPI[epi]), _native.stream_ptr())
+        _native.check(code, f"gemv_w4_norm {self.name} N={t.N} K={t.K}")
+        return True
 
     def _forward_ref(self, x, out, epi):
         y = x.bfloat16().float() @ self.w_ref.t()

@@ -83,6 +83,25 @@ def test_gemv_w4_single_row_matches_dequant(N, K, group, epi):
     _assert_clean()
 
 
+@pytest.mark.parametrize("offset", [0.0, 1.0])
+def test_gemv_w4_fused_norm_equals_norm_then_gemv(offset):
+    """RMSNorm in the GEMV prologue gives the unfused pair's result (same bf16 rounding of the normalised row)."""
+    torch.manual_seed(5)
+    H, N = 2048, 1024
+    qw = quantize(torch.randn(N, H) * 0.02, Fmt.INT4)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    h = (torch.randn(1, H, device=DEV) * 3.0).contiguous()
+    nw = (torch.rand(H, device=DEV) + 0.5).contiguous()
+    x = torch.empty(1, H, dtype=torch.bfloat16, device=DEV)
+    K.add_rmsnorm(h, nw, x, 1e-6, offset)
+    want = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, want, "f32")
+    got = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
+    assert lin.fused_norm(h, nw, got, "f32", 1e-6, offset)
+    assert torch.allclose(got, want, atol=2e-3 * max(1.0, float(want.abs().max())), rtol=1e-3)
+    _assert_clean()
+
+
 def test_gemv_w4_single_row_swiglu():
     from grimoire_b200.formats.w4_tile_layout import interleave_gate_up_q
     torch.manual_seed(3)
