@@ -56,6 +56,37 @@ def _timed(fn, iters: int, dev, warmup: int = 3) -> float:
     return float(t)
 
 
+def _timed_graph(fn, iters: int, dev) -> float:
+    """ms per call of ``fn`` replayed from a CUDA graph of ``iters`` calls (no host launch cost between the calls; every
+    rank replays the same graph at the same time), max over ranks."""
+    fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(iters):
+                fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    for _ in range(2):
+        g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
 class _Cfg:
     hidden_size = 5120
 
@@ -125,7 +156,8 @@ def bench_tp_decode(dev, W: int, rank: int, iters: int) -> list:
         tp.attach(_Model(), max_rows=64)
         x = torch.randn(M, Il, device=dev).bfloat16()
         h = torch.zeros(M, H, device=dev)
-        ms_fused = _timed(lambda: tp.row_parallel_add(down, x, h), iters, dev)
+        ms_fused = _timed_graph(lambda: tp.row_parallel_add(down, x, h), max(iters, 20), dev)
+        ms_local = _timed_graph(lambda: down(x, h, "add_f32"), max(iters, 20), dev)     # the product alone, no exchange
         tp.check()
         tpn = TensorParallel(dist.group.WORLD, dev, fused=False)
         tpn.attach(_Model(), max_rows=64)
@@ -133,8 +165,8 @@ def bench_tp_decode(dev, W: int, rank: int, iters: int) -> list:
         t_mem = down.tiled.nbytes() / (hbm * 1e9) * 1e3
         t_wire = (W - 1) * M * H * 4 / (NVLINK_GBS * 1e9) * 1e3
         roof = max(t_mem, t_wire)
-        out.append({"path": "tp_decode_down_allreduce", "rows": M, "us_fused": round(ms_fused * 1e3, 2), "us_nccl": round(ms_nccl * 1e3, 2),
-                    "roofline_us": round(roof * 1e3, 2), "roofline_bound": "hbm" if t_mem >= t_wire else "nvlink",
+        out.append({"path": "tp_decode_down_allreduce", "rows": M, "us_fused": round(ms_fused * 1e3, 2), "us_product_only": round(ms_local * 1e3, 2),
+                    "us_nccl": round(ms_nccl * 1e3, 2), "roofline_us": round(roof * 1e3, 2), "roofline_bound": "hbm" if t_mem >= t_wire else "nvlink",
                     "fraction_of_roofline": round(roof / ms_fused, 3), "speedup_vs_nccl": round(ms_nccl / ms_fused, 3)})
     return out
 

@@ -28,7 +28,24 @@ struct GemvW4Params {
   const float* h;         // [K]
   const float* nw;        // [K]
   float eps, offset;
+  // fused tensor-parallel all-reduce (EPI 4): out (fp32) += sum over ranks of the partial products.  Receive region
+  // of a rank: {value, epoch} pairs [2 parity][world][tiles][16]; one epoch counter per tile (shared with smallm_w4.cu).
+  float* ar_recv[8];
+  unsigned int* ar_flags[8];
+  unsigned int* ar_epochs;
+  unsigned int* status;
+  int ar_world, ar_rank;
+  unsigned int ar_spin;
 };
+
+__device__ __forceinline__ void gv_st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int gv_ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
   uint32_t r;
@@ -49,7 +66,7 @@ __device__ __forceinline__ void word_fma(uint32_t w, __half2 x01, __half2 x23, _
   a1 = __hfma2(__hfma2(h1, sixteenth, c_hi), x23, a1);
 }
 
-// EPI: 0 bf16, 1 f32, 2 add_f32, 3 swiglu.  G64: k tiles per quantisation group.
+// EPI: 0 bf16, 1 f32, 2 add_f32, 3 swiglu, 4 add_f32 after an all-reduce over ranks.  G64: k tiles per quantisation group.
 template <int EPI, int G64>
 __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Params p) {
   extern __shared__ __align__(16) uint8_t gv_smem[];
@@ -150,6 +167,49 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
   f1 += __shfl_xor_sync(0xffffffffu, f1, 1); f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
   if (t == 0) { red[warp][g] = f0; red[warp][g + 8] = f1; }
   __syncthreads();
+  if (EPI == 4) {
+    // One-shot all-reduce by warp 0 without fences: every partial sum travels as one 8-byte {value, epoch} store into
+    // the slot (parity, source rank, tile, row) of each peer's receive region; an aligned 8-byte store lands as a
+    // whole, so the receiver polls the slot itself until its epoch word is this launch's and then holds the value
+    // (the low-latency protocol of collective libraries).  The cost is one one-way NVLink latency instead of two
+    // system-scope fences plus a flag.  Partials are added in rank order, so every rank holds the same bits.  A peer
+    // can be at most one launch ahead (its next launch needs this rank's next push), hence the two parities.
+    if (warp != 0) return;
+    const int W = p.ar_world;
+    const unsigned int e = p.ar_epochs[tile] + 1u;
+    const size_t tiles = gridDim.x, par = e & 1u;
+    bool ok = true;
+    if (lane < 16) {
+      float mine = 0.f;
+#pragma unroll
+      for (int k = 0; k < SLICES; ++k) mine += red[k][lane];
+      const size_t slot = ((par * W + p.ar_rank) * tiles + tile) * 16 + lane;
+      for (int r = 0; r < W; ++r) {
+        if (r == p.ar_rank) continue;
+        uint2* dst = reinterpret_cast<uint2*>(p.ar_recv[r]) + slot;
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(mine)), "r"(e) : "memory");
+      }
+      float s = 0.f;
+      const uint2* base = reinterpret_cast<const uint2*>(p.ar_recv[p.ar_rank]);
+      for (int r = 0; r < W; ++r) {
+        if (r == p.ar_rank) { s += mine; continue; }
+        const uint2* src = base + ((par * W + r) * tiles + tile) * 16 + lane;
+        uint32_t vx = 0u, vy = 0u;
+        bool got = false;
+        for (unsigned int i = 0; i < p.ar_spin; ++i) {
+          asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+          if (vy == e) { got = true; break; }
+          if (i > 64) __nanosleep(20);
+        }
+        if (!got) { ok = false; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x20000u | (r << 12) | (tile & 0xfff)); break; }
+        s += __uint_as_float(vx);
+      }
+      if (ok) reinterpret_cast<float*>(p.out)[(size_t)tile * 16 + lane] += s;
+    }
+    __syncwarp();
+    if (lane == 0) p.ar_epochs[tile] = e;   // advance even after a timeout so later launches stay aligned
+    return;
+  }
   if (tid < 16) {
     float s = 0.f, u = 0.f;
 #pragma unroll
@@ -171,6 +231,17 @@ int launch_epi(const GemvW4Params& p, cudaStream_t st) {
   const int tiles = p.N / 16;
   const unsigned grid = (unsigned)(EPI == 3 ? tiles / 2 : tiles);
   const size_t smem = (size_t)p.K * 2;
+  if (EPI == 4) {
+    // CTAs of different ranks wait for one another's pushes: the whole grid must be resident at once
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t oe = cudaErrorInvalidValue;
+    if (p.g64 == 1) oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_w4_kernel<EPI, 1>, kGvWarps * 32, smem);
+    else if (p.g64 == 2) oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_w4_kernel<EPI, 2>, kGvWarps * 32, smem);
+    else if (p.g64 == 4) oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_w4_kernel<EPI, 4>, kGvWarps * 32, smem);
+    if (oe != cudaSuccess || (long)per_sm * sms < (long)grid) return -2;
+  }
   switch (p.g64) {
     case 1: gemv_w4_kernel<EPI, 1><<<grid, kGvWarps * 32, smem, st>>>(p); break;
     case 2: gemv_w4_kernel<EPI, 2><<<grid, kGvWarps * 32, smem, st>>>(p); break;
@@ -195,6 +266,8 @@ GRM_API int grm_gemv_w4_norm(const void* w, const void* sz, const void* x, const
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.N = N; p.K = K; p.g64 = group / 64;
   p.h = (const float*)h; p.nw = (const float*)nw; p.eps = eps; p.offset = offset;
+  for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.ar_epochs = nullptr; p.status = nullptr; p.ar_world = 1; p.ar_rank = 0; p.ar_spin = 0;
   cudaStream_t st = (cudaStream_t)stream;
   switch (epi) {
     case 0: return launch_epi<0>(p, st);
@@ -206,4 +279,31 @@ GRM_API int grm_gemv_w4_norm(const void* w, const void* sz, const void* x, const
 
 GRM_API int grm_gemv_w4(const void* w, const void* sz, const void* x, void* out, int N, int K, int group, int epi, void* stream) {
   return grm_gemv_w4_norm(w, sz, x, nullptr, nullptr, 0.f, 0.f, out, N, K, group, epi, stream);
+}
+
+// Row-parallel projection of one activation row fused with the tensor-parallel all-reduce: h[N] (fp32) += sum over
+// ranks of x_r . W_r^T.  recv / epochs: the exchange buffers of grm_smallm_w4_allreduce; this kernel uses the
+// 2 * world * (N / 16) * 16 {value, epoch} pairs (8 bytes each) that start recv_off floats (a multiple of 2) into each
+// rank's receive region, zero before first use -- a range the small-M kernel never touches, because a peer that is one
+// launch ahead may already be writing the next launch's region while this rank still reads its own (epochs: N / 16
+// uints, shared; flags are not used by this kernel).  Every rank issues the
+// same sequence of fused calls.  spin = poll limit of the arrival wait (0 = default, ~0.1 s).  Returns -2 when the
+// shape is unsupported or the grid could not be resident at once.
+GRM_API int grm_gemv_w4_allreduce(const void* w, const void* sz, const void* x, void* h, int N, int K, int group,
+                                  const void* const* recv, long recv_off, const void* const* flags, void* epochs, int world,
+                                  int rank, unsigned int spin, void* stream) {
+  if ((N % 32) || (K % 64) || (group != 64 && group != 128 && group != 256) || (K % group) || K > 20480 || ((uintptr_t)x & 15))
+    return -2;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !recv || !epochs || (recv_off & 1)) return -2;
+  GemvW4Params p;
+  p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = h;
+  p.N = N; p.K = K; p.g64 = group / 64;
+  p.h = nullptr; p.nw = nullptr; p.eps = 0.f; p.offset = 0.f;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_recv[i] = i < world ? (float*)const_cast<void*>(recv[i]) + recv_off : nullptr;
+    p.ar_flags[i] = (i < world && flags) ? (unsigned int*)const_cast<void*>(flags[i]) : nullptr;
+  }
+  p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
+  p.ar_spin = spin ? spin : 2000000u;
+  return launch_epi<4>(p, (cudaStream_t)stream);
 }

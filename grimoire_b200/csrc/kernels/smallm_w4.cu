@@ -48,12 +48,14 @@ struct W4Params {
   int szg;                  // groups per warp (capacity of the per-warp scale staging area)
   int stage;                // bytes of one ring stage: R*512 + M*144
   // ---- fused tensor-parallel all-reduce (EPI_AR_ADD): out(fp32) += sum over ranks of the partials ----
-  float* ar_recv[8];        // rank p's receive region: [2 parity][world][tiles][NV] floats (peer-mapped)
+  float* ar_recv[8];        // rank p's receive region: [2 parity halves of ar_half floats][world][tiles][NV] (peer-mapped)
   unsigned int* ar_flags[8];// rank p's arrival flags:   [tiles][world]
   unsigned int* ar_epochs;  // local, [tiles]: number of fused launches this tile has completed
   unsigned int* status;     // device status block (timeouts)
   int ar_world, ar_rank;
   unsigned int ar_spin;     // poll limit of the arrival wait
+  size_t ar_half;           // floats between the two parity halves of a receive region: fixed for the buffer, so that launches
+                            // with different row counts (different values per tile) never share bytes across parities
   // ---- integer activation path (I8 kernels): x carried as two int8 levels per quantisation group ----
   const int8_t* xq_hi;      // [M][ldq] high level  (x ~ delta * (128*hi + lo)), columns permuted (0,2,1,3) within 4
   const int8_t* xq_lo;      // [M][ldq] low level
@@ -523,7 +525,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) s += red[w * NV + v];
-      const size_t off = ((par * W + p.ar_rank) * tiles + tile) * NV + v;
+      const size_t off = par * p.ar_half + ((size_t)p.ar_rank * tiles + tile) * NV + v;
       for (int r = 0; r < W; ++r) p.ar_recv[r][off] = s;
     }
     __threadfence_system();
@@ -543,7 +545,7 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
       const float* mine = p.ar_recv[p.ar_rank];
       for (int v = tid; v < NV; v += kThreads) {
         float s = 0.f;
-        for (int r = 0; r < W; ++r) s += __ldcg(mine + ((par * W + r) * tiles + tile) * NV + v);
+        for (int r = 0; r < W; ++r) s += __ldcg(mine + par * p.ar_half + ((size_t)r * tiles + tile) * NV + v);
         epilogue_store<MT, R, EPI>(p, tile, v, s, 0.f);
       }
     }
@@ -714,7 +716,7 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
-  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0; p.ar_half = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
   p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   if (epi == EPI_AR_ADD) return -1;   // use grm_smallm_w4_allreduce
@@ -723,7 +725,8 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
 
 // Row-parallel projection fused with the tensor-parallel all-reduce: h[M][ldo] (fp32) += sum over
 // ranks of X_r . W_r^T.  recv / flags are arrays of `world` peer-mapped device pointers (see the
-// W4Params comment for their layouts; recv needs 2*world*(N/16)*MT*128 floats per rank, flags
+// W4Params comment for their layouts; recv needs 2*world*(N/16)*1024 floats per rank (two parity halves sized for the
+// widest launch), flags
 // (N/16)*world uints, epochs N/16 uints, all zero before first use).  Every rank must issue the same
 // sequence of calls with the same M.  spin = poll limit of the arrival wait (0 = default ~0.1 s).
 GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x, void* h, int M, int N, int K, int ldx,
@@ -741,6 +744,7 @@ GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
+  p.ar_half = (size_t)world * (size_t)(N / 16) * 1024;   // the widest launch: 8 row tiles x 128 values per 16-row tile
   p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
@@ -815,7 +819,7 @@ GRM_API int grm_smallm_w4_i8(const void* w, const void* sz, const void* xq_hi, c
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = nullptr; p.out = out;
   p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
   p.M = M; p.N = N; p.K = K; p.ldx = 0; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
-  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0; p.ar_half = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
   p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   if (epi == EPI_AR_ADD) return -1;
@@ -839,6 +843,7 @@ GRM_API int grm_smallm_w4_allreduce_i8(const void* w, const void* sz, const void
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
+  p.ar_half = (size_t)world * (size_t)(N / 16) * 1024;   // the widest launch: 8 row tiles x 128 values per 16-row tile
   p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
@@ -855,7 +860,7 @@ GRM_API int grm_smallm_mx_tiled(const void* w, const void* sz, const void* x16p,
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x16p; p.out = out;
   p.scratch = (float*)scratch; p.counters = (unsigned int*)counters;
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = 1; p.ksplit = ksplit;
-  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0; p.ar_half = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
   p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas();
   p.mx = 1; p.szw = 8;
@@ -930,7 +935,7 @@ GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, 
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.scratch = g_noalloc_dev[dev].partials; p.counters = g_noalloc_dev[dev].counters;
   p.M = M; p.N = N; p.K = K; p.ldx = ldx; p.ldo = ldo; p.g64 = group / 64; p.ksplit = ksplit;
-  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0;
+  p.status = grm_status_ptr(); p.ar_world = 1; p.ar_rank = 0; p.ar_epochs = nullptr; p.ar_spin = 0; p.ar_half = 0;
   for (int i = 0; i < 8; ++i) { p.ar_recv[i] = nullptr; p.ar_flags[i] = nullptr; }
   p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, epi, rows_per_cta, st);

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _native
+from ..ops import linear as L
 from ..ops.linear import SMALLM_MAX, W4Linear
 
 
@@ -75,7 +76,9 @@ class TensorParallel:
         tiles = (H + 31) // 32 * 32 // 16
         nv_max = 8 * 128                                   # MT = 8, R = 1
         try:
-            self.recv = SymmetricBuffer(2 * self.world * tiles * nv_max, torch.float32, self.group, self.device)
+            # + a separate range for the single-row GEMV's partials (16 {value, epoch} pairs per tile), see grm_gemv_w4_allreduce
+            self.gemv_off = 2 * self.world * tiles * nv_max
+            self.recv = SymmetricBuffer(self.gemv_off + 2 * self.world * tiles * 32, torch.float32, self.group, self.device)
             self.flags = SymmetricBuffer(tiles * self.world, torch.int32, self.group, self.device)
         except Exception as e:  # pragma: no cover - depends on the driver / fabric
             raise RuntimeError(f"symmetric peer memory is unavailable ({e}); set GRIMOIRE_TP_FUSED=0 to run the "
@@ -88,6 +91,18 @@ class TensorParallel:
     def row_parallel_add(self, lin, x: torch.Tensor, h: torch.Tensor) -> None:
         """h (fp32 [M][H], replicated) += all-reduce over ranks of ``x @ W_rank^T``."""
         M = x.shape[0]
+        if self.fused and M == 1 and L.GEMV_W4 and isinstance(lin, W4Linear) and lin.tiled is not None and lin.tiled.K <= 20480:
+            # one row: the CUDA-core GEMV with the same one-shot all-reduce in its epilogue
+            t = lin.tiled
+            code = _native.cuda().grm_gemv_w4_allreduce(
+                _native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(h), ctypes.c_int(t.N), ctypes.c_int(t.K),
+                ctypes.c_int(t.group), self.recv.ptr_array(), ctypes.c_long(self.gemv_off), self.flags.ptr_array(),
+                _native.ptr(self.epochs), ctypes.c_int(self.world), ctypes.c_int(self.rank), ctypes.c_uint(self.spin),
+                _native.stream_ptr())
+            if code != -2:
+                _native.check(code, f"gemv_w4_allreduce {lin.name}")
+                self.stats["fused_allreduce"] += 1
+                return
         if self.fused and M <= SMALLM_MAX and isinstance(lin, W4Linear) and lin.tiled is not None:
             t = lin.tiled
             code = _native.cuda().grm_smallm_w4_allreduce(
