@@ -48,7 +48,7 @@ struct W4Params {
   int szg;                  // groups per warp (capacity of the per-warp scale staging area)
   int stage;                // bytes of one ring stage: R*512 + M*144
   // ---- fused tensor-parallel all-reduce (EPI_AR_ADD): out(fp32) += sum over ranks of the partials ----
-  float* ar_recv[8];        // rank p's receive region: [2 parity halves of ar_half floats][world][tiles][NV] (peer-mapped)
+  float* ar_recv[8];        // rank p's receive region: [2 parity halves of ar_half floats][world][tiles][NV] {value, epoch} pairs (peer-mapped)
   unsigned int* ar_flags[8];// rank p's arrival flags:   [tiles][world]
   unsigned int* ar_epochs;  // local, [tiles]: number of fused launches this tile has completed
   unsigned int* status;     // device status block (timeouts)
@@ -509,46 +509,47 @@ __global__ void __launch_bounds__(kThreads) smallm_w4_kernel(const W4Params p) {
 
   if (EPI == EPI_AR_ADD) {
     // One-shot all-reduce fused into the epilogue: push this rank's partial tile into every rank's
-    // receive region over NVLink, raise a per-(tile, source) flag with release semantics, wait
-    // (bounded) for the flags of all sources, then sum the W partials in rank order -- every rank
+    // receive region over NVLink, wait (bounded) for the partials of all sources, then sum the W
+    // partials in rank order -- every rank
     // adds the same numbers in the same order, so all ranks hold bit-identical results (the
     // property the reference keeps with its rank-ordered shared-memory sums, grimoire.cpp:6263-6366).
     // Receive regions are double-buffered by launch parity: a peer can be at most one fused launch
     // ahead, because its next launch needs this rank's next push.
-    __shared__ int s_fail;
     const int W = p.ar_world;
     const unsigned int e = p.ar_epochs[tile] + 1u;
     const size_t tiles = gridDim.x;
     const size_t par = e & 1u;
-    if (tid == 0) s_fail = 0;
+    // Every partial travels as one 8-byte {value, epoch} store (an aligned 8-byte store lands as a whole), so the
+    // receiver polls the data slot itself: no system-scope fences and no separate flag, one one-way NVLink latency.
     for (int v = tid; v < NV; v += kThreads) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) s += red[w * NV + v];
-      const size_t off = par * p.ar_half + ((size_t)p.ar_rank * tiles + tile) * NV + v;
-      for (int r = 0; r < W; ++r) p.ar_recv[r][off] = s;
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < W) st_release_sys(p.ar_flags[tid] + (size_t)tile * W + p.ar_rank, e);
-    if (tid < W) {
-      const unsigned int* f = p.ar_flags[p.ar_rank] + (size_t)tile * W + tid;
-      bool ok = false;
-      for (unsigned int i = 0; i < p.ar_spin; ++i) {
-        if ((int)(ld_acquire_sys(f) - e) >= 0) { ok = true; break; }
-        if (i > 16) __nanosleep(20);
-      }
-      if (!ok) { s_fail = 1; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x10000u | (tid << 12) | (tile & 0xfff)); }
-    }
-    __syncthreads();
-    if (!s_fail) {
-      const float* mine = p.ar_recv[p.ar_rank];
-      for (int v = tid; v < NV; v += kThreads) {
-        float s = 0.f;
-        for (int r = 0; r < W; ++r) s += __ldcg(mine + par * p.ar_half + ((size_t)r * tiles + tile) * NV + v);
-        epilogue_store<MT, R, EPI>(p, tile, v, s, 0.f);
+      const size_t slot = par * (p.ar_half >> 1) + ((size_t)p.ar_rank * tiles + tile) * NV + v;
+      for (int r = 0; r < W; ++r) {
+        uint2* dst = reinterpret_cast<uint2*>(p.ar_recv[r]) + slot;
+        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(s)), "r"(e) : "memory");
       }
     }
+    const uint2* mine = reinterpret_cast<const uint2*>(p.ar_recv[p.ar_rank]);
+    for (int v = tid; v < NV; v += kThreads) {
+      float s = 0.f;
+      bool ok = true;
+      for (int r = 0; r < W && ok; ++r) {
+        const uint2* src = mine + par * (p.ar_half >> 1) + ((size_t)r * tiles + tile) * NV + v;
+        uint32_t vx = 0u, vy = 0u;
+        ok = false;
+        for (unsigned int i = 0; i < p.ar_spin; ++i) {
+          asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+          if (vy == e) { ok = true; break; }
+          if (i > 64) __nanosleep(20);
+        }
+        if (!ok) grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x10000u | (r << 12) | (tile & 0xfff));
+        s += __uint_as_float(vx);
+      }
+      if (ok) epilogue_store<MT, R, EPI>(p, tile, v, s, 0.f);
+    }
+    __syncthreads();
     if (tid == 0) p.ar_epochs[tile] = e;   // advance even after a timeout so later launches stay aligned
     return;
   }
@@ -725,8 +726,8 @@ GRM_API int grm_smallm_w4(const void* w, const void* sz, const void* x, void* ou
 
 // Row-parallel projection fused with the tensor-parallel all-reduce: h[M][ldo] (fp32) += sum over
 // ranks of X_r . W_r^T.  recv / flags are arrays of `world` peer-mapped device pointers (see the
-// W4Params comment for their layouts; recv needs 2*world*(N/16)*1024 floats per rank (two parity halves sized for the
-// widest launch), flags
+// W4Params comment for their layouts; recv needs 2*world*(N/16)*2048 floats per rank (two parity halves of {value, epoch}
+// pairs sized for the widest launch, zero before first use), flags (unused since the pairs carry the epoch)
 // (N/16)*world uints, epochs N/16 uints, all zero before first use).  Every rank must issue the same
 // sequence of calls with the same M.  spin = poll limit of the arrival wait (0 = default ~0.1 s).
 GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x, void* h, int M, int N, int K, int ldx,
@@ -744,7 +745,7 @@ GRM_API int grm_smallm_w4_allreduce(const void* w, const void* sz, const void* x
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
-  p.ar_half = (size_t)world * (size_t)(N / 16) * 1024;   // the widest launch: 8 row tiles x 128 values per 16-row tile
+  p.ar_half = (size_t)world * (size_t)(N / 16) * 2048;   // floats per parity half: the widest launch has 8 x 128 {value, epoch} pairs per 16-row tile
   p.xq_hi = p.xq_lo = nullptr; p.xtab = nullptr; p.ldq = p.ldtab = 0; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }
@@ -843,7 +844,7 @@ GRM_API int grm_smallm_w4_allreduce_i8(const void* w, const void* sz, const void
   }
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
-  p.ar_half = (size_t)world * (size_t)(N / 16) * 1024;   // the widest launch: 8 row tiles x 128 values per 16-row tile
+  p.ar_half = (size_t)world * (size_t)(N / 16) * 2048;   // floats per parity half: the widest launch has 8 x 128 {value, epoch} pairs per 16-row tile
   p.xq_hi = (const int8_t*)xq_hi; p.xq_lo = (const int8_t*)xq_lo; p.xtab = (const float2*)xtab; p.ldq = ldq; p.ldtab = ldtab; p.min_ctas = grm_smallm_min_ctas(); p.mx = 0; p.szw = 16;
   return dispatch(p, EPI_AR_ADD, 16, (cudaStream_t)stream);
 }

@@ -74,7 +74,7 @@ class TensorParallel:
         if not self.fused:
             return
         tiles = (H + 31) // 32 * 32 // 16
-        nv_max = 8 * 128                                   # MT = 8, R = 1
+        nv_max = 8 * 128 * 2                               # MT = 8, R = 1, {value, epoch} pairs
         try:
             # + a separate range for the single-row GEMV's partials (16 {value, epoch} pairs per tile), see grm_gemv_w4_allreduce
             self.gemv_off = 2 * self.world * tiles * nv_max
