@@ -23,6 +23,7 @@ import torch
 import torch.distributed as dist
 
 from ..engine.engine import Engine, EngineLimits
+from ..ops import linear as _linear
 from ..engine.generation import GenerationOptions, generate_tokens
 from ..models.config import dense_27b
 from ..models.dense import DenseModel
@@ -81,6 +82,9 @@ def main(argv=None) -> int:
                           "spec_tok_s": round(world * len(spec) * 1000.0 / spec_ms, 1), "accepted_length": round(st.accept_length, 3),
                           "rounds": st.rounds, "drafted": st.drafted, "accepted": st.accepted,
                           "plain_tok_s": round(world * len(plain) * 1000.0 / plain_ms, 1), "tokens_equal_plain": spec == plain,
+                          # one row runs the CUDA-core GEMV, verify rows the tensor-core kernel: equal to rounding only
+                          # (GRIMOIRE_GEMV_W4=0 puts every width on the batch-invariant kernel and the streams are equal)
+                          "batch_invariant_kernels": not _linear.GEMV_W4,
                           "includes_prefill": True, "mtp_bytes": drafter.head.nbytes(), "build_s": round(build_s, 1),
                           "device_status": list(K.status_read()), "data": "synthetic"}), flush=True)
     if world > 1:

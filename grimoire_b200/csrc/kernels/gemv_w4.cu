@@ -38,15 +38,6 @@ struct GemvW4Params {
   unsigned int ar_spin;
 };
 
-__device__ __forceinline__ void gv_st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int gv_ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));   // (a & mask) | orv
@@ -226,6 +217,137 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
   }
 }
 
+// ---- MXFP4 (tile_mx layout: byte b = 2 hi + r8 of a lane's word j holds row g + 8 r8, columns 16 j + 2 t + 8 hi, +1;
+// e8m0 scale bytes [N/16][K/32][16]) -------------------------------------------------------------------------------
+__device__ __forceinline__ __half2 gv_e2m1x2(uint32_t byte) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b0;\n\t}" : "=r"(r) : "r"(byte));
+  return as_h2(r);
+}
+
+struct GemvMxParams {
+  const uint4* w;
+  const uint8_t* sz;
+  const bf16* x;
+  void* out;
+  int N, K;
+  const float* h;
+  const float* nw;
+  float eps, offset;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(256) gemv_mx_kernel(const GemvMxParams p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  __half* xs = reinterpret_cast<__half*>(gv_smem);
+  __shared__ float red[8][16];
+  constexpr bool SW = EPI == 3;
+  constexpr int TILES = SW ? 2 : 1;
+  constexpr int SLICES = 8 / TILES;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int KT = p.K >> 6;
+  const int tile = blockIdx.x * TILES + (SW ? warp / SLICES : 0);
+  const int slice = SW ? warp % SLICES : warp;
+  const int per = (KT + SLICES - 1) / SLICES;
+  const int kbeg = slice * per, kend = min(kbeg + per, KT);
+  const uint4* wp = p.w + ((size_t)(tile >> 1) * KT * 2 + (tile & 1)) * 32 + lane;   // + kt * 64
+  const uint8_t* szp = p.sz + (size_t)tile * (KT * 2) * 16 + g;                        // + block * 16 (+ 8)
+
+  uint4 cur = make_uint4(0u, 0u, 0u, 0u), nxt = cur;
+  if (kbeg < kend) cur = ldg_stream_v4(wp + (size_t)kbeg * 64);
+  if (kbeg + 1 < kend) nxt = ldg_stream_v4(wp + (size_t)(kbeg + 1) * 64);
+
+  float rnorm = 0.f;
+  if (p.h != nullptr) {
+    float ss = 0.f;
+    for (int i = tid * 4; i < p.K; i += 256 * 4) {
+      const float4 a = *reinterpret_cast<const float4*>(p.h + i);
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp][0] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += red[k][0];
+    rnorm = rsqrtf(ss / (float)p.K + p.eps);
+    __syncthreads();
+  }
+  const int xbeg = SW ? tid * 8 : kbeg * 64 + lane * 8;
+  const int xend = SW ? p.K : min(kend * 64, p.K);
+  const int xstep = SW ? 256 * 8 : 256;
+  for (int i = xbeg; i < xend; i += xstep) {
+    uint32_t s[4];
+    if (p.h != nullptr) {
+      const float4 a = *reinterpret_cast<const float4*>(p.h + i), b = *reinterpret_cast<const float4*>(p.h + i + 4);
+      const float4 wa = *reinterpret_cast<const float4*>(p.nw + i), wb = *reinterpret_cast<const float4*>(p.nw + i + 4);
+      s[0] = pack_bf16x2(a.x * rnorm * (p.offset + wa.x), a.y * rnorm * (p.offset + wa.y));
+      s[1] = pack_bf16x2(a.z * rnorm * (p.offset + wa.z), a.w * rnorm * (p.offset + wa.w));
+      s[2] = pack_bf16x2(b.x * rnorm * (p.offset + wb.x), b.y * rnorm * (p.offset + wb.y));
+      s[3] = pack_bf16x2(b.z * rnorm * (p.offset + wb.z), b.w * rnorm * (p.offset + wb.w));
+    } else {
+      const uint4 v = *reinterpret_cast<const uint4*>(p.x + i);
+      s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2 hh = __floats2half2_rn(bf16lo_to_f(s[j]), bf16hi_to_f(s[j]));
+      o[j] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+    *reinterpret_cast<uint4*>(xs + i) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (SW) __syncthreads();
+  else __syncwarp();
+
+  float f0 = 0.f, f1 = 0.f;
+  for (int kt = kbeg; kt < kend; ++kt) {
+    uint4 nx2 = make_uint4(0u, 0u, 0u, 0u);
+    if (kt + 2 < kend) nx2 = ldg_stream_v4(wp + (size_t)(kt + 2) * 64);
+    const uint32_t wv[4] = {cur.x, cur.y, cur.z, cur.w};
+    const __half2* xk = reinterpret_cast<const __half2*>(xs + (size_t)kt * 64) + t;    // half2 index: (16 j + 2 t) / 2 = 8 j + t
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = blk * 2 + jj;
+        const uint32_t u = wv[j];
+        const __half2 xlo = xk[8 * j], xhi = xk[8 * j + 4];
+        a0 = __hfma2(gv_e2m1x2(u), xlo, a0);
+        a1 = __hfma2(gv_e2m1x2(u >> 8), xlo, a1);
+        a0 = __hfma2(gv_e2m1x2(u >> 16), xhi, a0);
+        a1 = __hfma2(gv_e2m1x2(u >> 24), xhi, a1);
+      }
+      const uint8_t* sb = szp + (size_t)(kt * 2 + blk) * 16;
+      const float s0 = __uint_as_float((uint32_t)__ldg(sb) << 23), s1 = __uint_as_float((uint32_t)__ldg(sb + 8) << 23);
+      const float2 r0 = __half22float2(a0), r1 = __half22float2(a1);
+      f0 += s0 * (r0.x + r0.y);
+      f1 += s1 * (r1.x + r1.y);
+    }
+    cur = nxt; nxt = nx2;
+  }
+  f0 += __shfl_xor_sync(0xffffffffu, f0, 1); f0 += __shfl_xor_sync(0xffffffffu, f0, 2);
+  f1 += __shfl_xor_sync(0xffffffffu, f1, 1); f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
+  if (t == 0) { red[warp][g] = f0; red[warp][g + 8] = f1; }
+  __syncthreads();
+  if (tid < 16) {
+    float s = 0.f, u = 0.f;
+#pragma unroll
+    for (int k = 0; k < SLICES; ++k) s += red[k][tid];
+    if (SW) {
+#pragma unroll
+      for (int k = 0; k < SLICES; ++k) u += red[SLICES + k][tid];
+    }
+    const size_t col = (size_t)blockIdx.x * 16 + tid;
+    if (EPI == 0) reinterpret_cast<bf16*>(p.out)[col] = __float2bfloat16(s);
+    else if (EPI == 1) reinterpret_cast<float*>(p.out)[col] = s;
+    else if (EPI == 2) reinterpret_cast<float*>(p.out)[col] += s;
+    else reinterpret_cast<bf16*>(p.out)[col] = __float2bfloat16(silu_f(s) * u);
+  }
+}
+
 template <int EPI>
 int launch_epi(const GemvW4Params& p, cudaStream_t st) {
   const int tiles = p.N / 16;
@@ -306,4 +428,26 @@ GRM_API int grm_gemv_w4_allreduce(const void* w, const void* sz, const void* x, 
   p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
   p.ar_spin = spin ? spin : 2000000u;
   return launch_epi<4>(p, (cudaStream_t)stream);
+}
+
+// MXFP4 weights in the tile_mx layout (formats/w4_tile_layout.py), one activation row; same epilogues and optional
+// RMSNorm prologue as grm_gemv_w4_norm.  N % 32 == 0, K % 64 == 0, K <= 20480.
+GRM_API int grm_gemv_mx(const void* w, const void* sz, const void* x, const void* h, const void* nw, float eps, float offset, void* out,
+                        int N, int K, int epi, void* stream) {
+  if ((N % 32) || (K % 64) || K > 20480 || epi < 0 || epi > 3 || (!h && ((uintptr_t)x & 15)) ||
+      (h && (!nw || ((uintptr_t)h & 15) || ((uintptr_t)nw & 15))))
+    return -2;
+  GemvMxParams p;
+  p.w = (const uint4*)w; p.sz = (const uint8_t*)sz; p.x = (const bf16*)x; p.out = out; p.N = N; p.K = K;
+  p.h = (const float*)h; p.nw = (const float*)nw; p.eps = eps; p.offset = offset;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int tiles = N / 16;
+  const size_t smem = (size_t)K * 2;
+  switch (epi) {
+    case 0: gemv_mx_kernel<0><<<tiles, 256, smem, st>>>(p); break;
+    case 1: gemv_mx_kernel<1><<<tiles, 256, smem, st>>>(p); break;
+    case 2: gemv_mx_kernel<2><<<tiles, 256, smem, st>>>(p); break;
+    default: gemv_mx_kernel<3><<<tiles / 2, 256, smem, st>>>(p); break;
+  }
+  GRM_LAUNCH_RET();
 }

@@ -357,6 +357,12 @@ class MXLinear:
         if self.device.type != "cuda":
             return W4Linear._forward_ref(self, x, out, epi)
         lib = _native.cuda()
+        if M == 1 and GEMV_W4 and self.tw is not None and self.K <= 20480:
+            # one row: CUDA-core weight stream over the same tiles (gemv_w4.cu), bf16 activations read directly
+            code = lib.grm_gemv_mx(_native.ptr(self.tw), _native.ptr(self.tsz), _native.ptr(x), None, None, ctypes.c_float(0.0),
+                                   ctypes.c_float(0.0), _native.ptr(out), _c(self.N), _c(self.K), _c(EPI[epi]), _native.stream_ptr())
+            _native.check(code, f"gemv_mx {self.name} N={self.N} K={self.K}")
+            return out
         if M <= SMALLM_MAX and self.tw is not None:
             # tiled path: the int4 kernel's ring / warp layout / epilogues with the MXFP4 math
             ld16 = self.K
@@ -384,5 +390,16 @@ class MXLinear:
         _native.check(lib.grm_dequant_mxfp4(_native.ptr(self.w), _native.ptr(self.s), _native.ptr(wbuf), _c(self.N), _c(self.K),
                                             _native.stream_ptr()), f"dequant_mxfp4 {self.name}")
         return gemm_bf16(x, wbuf, out, epi)
+
+    def fused_norm(self, h: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, epi: str, eps: float, offset: float) -> bool:
+        """RMSNorm of one fp32 residual row inside the single-row GEMV prologue (see W4Linear.fused_norm)."""
+        if (not GEMV_W4 or not FUSED_NORM or self.device.type != "cuda" or self.tw is None or h.shape[0] != 1 or self.K > 20480
+                or h.dtype != torch.float32 or h.shape[1] != self.K):
+            return False
+        code = _native.cuda().grm_gemv_mx(_native.ptr(self.tw), _native.ptr(self.tsz), None, _native.ptr(h), _native.ptr(norm_w),
+                                          ctypes.c_float(eps), ctypes.c_float(offset), _native.ptr(out), _c(self.N), _c(self.K),
+                                          _c(EPI[epi]), _native.stream_ptr())
+        _native.check(code, f"gemv_mx_norm {self.name} N={self.N} K={self.K}")
+        return True
 
     __call__ = forward
