@@ -348,3 +348,112 @@ GRM_API int grm_ep_apply(void* h, int ldh, const void* gather, const void* hflag
   ep_apply_kernel<<<M_total, 256, 0, (cudaStream_t)stream>>>(p);
   GRM_LAUNCH_RET();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel decode (a handful of rows): activations and routing are replicated, every rank runs the chosen
+// experts it owns as one-row tiles, and the weighted sum over choices is all-reduced in the combine kernel itself.
+// The exchange is the fence-free one of the tensor-parallel decode path: every partial value travels as one 8-byte
+// {value, epoch} store into each peer's receive region and the receiver polls the data slot; partials are added in
+// rank order, so all ranks hold the same bits.  (The reference's expert parallelism is this scheme with a host
+// all-reduce: grimoire.cpp:6263-6366.)
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void ep_decode_prep_kernel(const int* __restrict__ ids, int ld_ids, int M, int k, int e0, int e1, int owns_shared,
+                                      int* __restrict__ te, int* __restrict__ nr, int* __restrict__ pos) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < M * k) {
+    const int m = idx / k, j = idx - m * k;
+    const int id = ids[(size_t)m * ld_ids + j];
+    const bool local = id >= e0 && id < e1;
+    te[idx] = local ? id - e0 : 0;
+    nr[idx] = local ? 1 : 0;
+    pos[(size_t)m * (k + 1) + j] = local ? idx : -1;
+  }
+  if (idx < M) pos[(size_t)idx * (k + 1) + k] = owns_shared ? M * k + idx : -1;
+}
+
+struct CombineArParams {
+  float* h; int ldh;
+  const float* y; int ldy;
+  const int* pos; const float* wts;
+  int M, slots, H;
+  float* recv[8];            // per rank: {value, epoch} pairs [2 parity][world][cap]
+  unsigned int* epochs;      // [blocks], local
+  unsigned int* status;
+  size_t cap;                // pairs per (parity, source): fixed for the buffer
+  int W, rank;
+  unsigned int spin;
+};
+
+__global__ void __launch_bounds__(256) ep_combine_allreduce_kernel(const CombineArParams p) {
+  const int idx = blockIdx.x * 256 + threadIdx.x;
+  const unsigned int e = p.epochs[blockIdx.x] + 1u;
+  const size_t par = e & 1u;
+  if (idx < p.M * p.H) {
+    const int row = idx / p.H, c = idx - row * p.H;
+    float acc = 0.f;
+    for (int j = 0; j < p.slots; ++j) {
+      const int ps = p.pos[(size_t)row * p.slots + j];
+      if (ps >= 0) acc = fmaf(p.wts[(size_t)row * p.slots + j], p.y[(size_t)ps * p.ldy + c], acc);
+    }
+    const size_t slot = (par * p.W + p.rank) * p.cap + idx;
+    for (int r = 0; r < p.W; ++r) {
+      if (r == p.rank) continue;
+      uint2* dst = reinterpret_cast<uint2*>(p.recv[r]) + slot;
+      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(acc)), "r"(e) : "memory");
+    }
+    const uint2* mine = reinterpret_cast<const uint2*>(p.recv[p.rank]);
+    float s = 0.f;
+    bool ok = true;
+    for (int r = 0; r < p.W && ok; ++r) {
+      if (r == p.rank) { s += acc; continue; }
+      const uint2* src = mine + (par * p.W + r) * p.cap + idx;
+      uint32_t vx = 0u, vy = 0u;
+      ok = false;
+      for (unsigned int i = 0; i < p.spin; ++i) {
+        asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+        if (vy == e) { ok = true; break; }
+        if (i > 64) __nanosleep(20);
+      }
+      if (!ok) grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x30000u | (r << 12) | (blockIdx.x & 0xfff));
+      s += __uint_as_float(vx);
+    }
+    if (ok) p.h[(size_t)row * p.ldh + c] += s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) p.epochs[blockIdx.x] = e;   // advance even after a timeout so later launches stay aligned
+}
+
+}  // namespace
+
+// ids [M][ld_ids] global expert choices -> one-row tiles over this rank's experts [e0, e1): te (local expert or 0), nr (1 if
+// the choice is local else 0), pos [M][k + 1] (grouped row m * k + j of a local choice, -1 otherwise; column k = the shared
+// expert's row M * k + m on the rank that owns it).
+GRM_API int grm_ep_decode_prep(const void* ids, int ld_ids, int M, int k, int e0, int e1, int owns_shared, void* te, void* nr,
+                               void* pos, void* stream) {
+  if (M < 1 || k < 1) return -2;
+  const int n = M * k;
+  ep_decode_prep_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>((const int*)ids, ld_ids, M, k, e0, e1, owns_shared, (int*)te,
+                                                                          (int*)nr, (int*)pos);
+  GRM_LAUNCH_RET();
+}
+
+// h[M][ldh] += sum over ranks of (sum_j wts[m][j] * y[pos[m][j]]).  recv: `world` peer-mapped receive regions of
+// 2 * world * cap {value, epoch} pairs (zero before first use), cap >= M * H; epochs: ceil(cap / 256) local counters (zero
+// before first use).  Every rank issues the same sequence of calls with the same M.  The grid (M * H / 256 CTAs) must be
+// resident at once, which holds for the few rows this path is used for (-2 otherwise).
+GRM_API int grm_ep_combine_allreduce(void* h, int ldh, const void* y, int ldy, const void* pos, const void* wts, int M, int slots, int H,
+                                     void* const* recv, long cap, void* epochs, int world, int rank, unsigned int spin, void* stream) {
+  if (M < 1 || world < 1 || world > 8 || rank < 0 || rank >= world || (long)M * H > cap) return -2;
+  const int blocks = (M * H + 255) / 256;
+  if (blocks > 148 * 4) return -2;
+  CombineArParams p;
+  p.h = (float*)h; p.ldh = ldh; p.y = (const float*)y; p.ldy = ldy; p.pos = (const int*)pos; p.wts = (const float*)wts;
+  p.M = M; p.slots = slots; p.H = H;
+  for (int i = 0; i < 8; ++i) p.recv[i] = i < world ? (float*)recv[i] : nullptr;
+  p.epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.cap = (size_t)cap; p.W = world; p.rank = rank;
+  p.spin = spin ? spin : 2000000u;
+  ep_combine_allreduce_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+  GRM_LAUNCH_RET();
+}

@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(kVThreads) moe_gemv_kernel(const GroupedParams
   if (p.n_tiles_dev && tile >= *p.n_tiles_dev) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int e = p.tile_expert[tile], r0 = p.tile_row0[tile], nr = min(p.tile_rows[tile], kVRows);
+  if (nr <= 0) return;   // an empty tile (expert-parallel decode: the choice belongs to another rank) streams no weights
   const int NO = MODE == 0 ? p.N / 2 : p.N;
   const int KB = p.K / 128;
   const uint8_t* we = p.w + (size_t)e * p.N * p.K;

@@ -12,6 +12,7 @@ stay bf16.  Per-slot recurrent state (DeltaNet ``S`` + conv ring) lives beside t
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -26,6 +27,9 @@ from ..ops.linear import BF16Linear
 from ..ops.workspace import Workspace
 from .config import ModelConfig
 from .dense import RowBatch
+
+# expert-parallel decode of <= 8 rows through replicated routing + the all-reducing combine kernel (0: dispatch chain)
+EP_DECODE_LL = os.environ.get("GRIMOIRE_EP_DECODE_LL", "1") != "0"
 
 
 @dataclass
@@ -251,6 +255,22 @@ class HybridModel:
 
                 self._local_moe = ExpertParallel(None, self.device, E, k, H, cfg.moe_intermediate_size, buf.max_rows, fused=True)
             self._local_moe.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
+            return
+        if self.ep is not None and self.ep.fused and decode and M <= self.ep.ll_rows and EP_DECODE_LL:
+            # a few decode rows: every rank runs the chosen experts it owns on the replicated rows and the combine
+            # kernel all-reduces the weighted sums (no dispatch / return traffic, one exchange per layer)
+            ep = self.ep
+            ids, wts = buf.ids[:M], buf.wts[:M]
+            Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts, shared_gate=True)
+            te, nr, pos = ep.decode_tiles(ids, M)
+            act, y = buf.act[: M * k], buf.y[: M * (k + 1)]
+            r0, src = buf.tile_row0[: M * k], buf.tile_src[: M * k]
+            Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu", small=True)
+            Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32", small=True)
+            if ep.rank == 0:
+                moe.shared_gu(x, buf.act_s[:M], "swiglu")
+                moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
+            ep.combine_allreduce(h, y, pos, wts, M)
             return
         if self.ep is not None:
             if self.ep.fused:

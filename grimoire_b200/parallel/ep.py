@@ -95,6 +95,13 @@ class ExpertParallel:
         self.tile_expert, self.tile_row0, self.tile_rows, self.tile_src = (z(self.max_tiles) for _ in range(4))
         self.n_tiles = z(1)
         self.act = z(W * self.cap, self.I, dt=bf)
+        # decode (<= ll_rows rows): replicated routing, local experts only, all-reduce inside the combine kernel
+        self.ll_rows = 8
+        self.ll_cap = self.ll_rows * H
+        self.ll_recv = mkbuf(2 * W * self.ll_cap * 2, f32)                 # {value, epoch} pairs [2 parity][W][cap]
+        self.ll_epochs = z((self.ll_cap + 255) // 256)
+        self.ll_te, self.ll_nr = z(self.ll_rows * k), z(self.ll_rows * k)
+        self.ll_pos = z(self.ll_rows * (k + 1))
         if g is not None:
             dist.barrier(g)
         torch.cuda.synchronize(dev)
@@ -152,6 +159,26 @@ class ExpertParallel:
         self.stats["fused_layers"] += 1
 
     # ------------------------------------------------------------------------------------------
+    def decode_tiles(self, ids: torch.Tensor, M: int):
+        """Replicated choices ``ids`` [M][k] -> (tile_expert, tile_rows, pos [M][k+1]) over this rank's experts: a choice
+        owned elsewhere becomes an empty tile and a skipped combine slot; rank 0 owns the (replicated) shared expert."""
+        e0, e1 = self.expert_range()
+        te, nr, pos = self.ll_te[: M * self.k], self.ll_nr[: M * self.k], self.ll_pos[: M * (self.k + 1)].view(M, self.k + 1)
+        code = _native.cuda().grm_ep_decode_prep(_native.ptr(ids), _c(ids.stride(0)), _c(M), _c(self.k), _c(e0), _c(e1),
+                                                 _c(1 if self.rank == 0 else 0), _native.ptr(te), _native.ptr(nr), _native.ptr(pos),
+                                                 _native.stream_ptr())
+        _native.check(code, "ep_decode_prep")
+        return te, nr, pos
+
+    def combine_allreduce(self, h: torch.Tensor, y: torch.Tensor, pos: torch.Tensor, wts: torch.Tensor, M: int) -> None:
+        """h += sum over ranks of the weighted sum of this rank's expert outputs (one kernel, see ep_fused.cu)."""
+        code = _native.cuda().grm_ep_combine_allreduce(
+            _native.ptr(h), _c(h.stride(0)), _native.ptr(y), _c(y.stride(0)), _native.ptr(pos), _native.ptr(wts), _c(M), _c(self.k + 1),
+            _c(self.H), self.ll_recv.ptr_array(), ctypes.c_long(self.ll_cap), _native.ptr(self.ll_epochs), _c(self.world), _c(self.rank),
+            ctypes.c_uint(self.spin), _native.stream_ptr())
+        _native.check(code, "ep_combine_allreduce")
+        self.stats["fused_layers"] += 1
+
     def moe_allreduce(self, moe, x: torch.Tensor, h: torch.Tensor, lg: torch.Tensor, M: int, renorm: bool) -> None:
         """Local experts for all rows, partial sums all-reduced (CPU ranks, and the NCCL baseline)."""
         E, k, H = self.E, self.k, self.H
