@@ -32,7 +32,44 @@ struct DecParams {
   unsigned int* counters;     // [M*Hkv]
   int M, Hq, Hkv, window;
   float scale;
+  // fused q/k norm + RoPE + KV append (qkv != null; one row per sequence in the launch): q is read from the raw fused
+  // projection output and the CTA whose split holds the row's last page appends this token's K / V before it reads it
+  const bf16* qkv; int ld_qkv;     // [M][(Hq + 2 Hkv) * D]
+  const float* inv_freq;           // [rot / 2]
+  const float* q_norm_w;           // [D] or null
+  const float* k_norm_w;           // [D] or null
+  float norm_eps, norm_offset;
+  int rot;
 };
+
+// Per-head RMSNorm (optional) and rotary embedding of one head held as v[i] = x[lane + 32 i] -- the arithmetic of
+// rope_kv.cu, so the fused and the two-kernel paths produce the same bits.
+template <int D>
+__device__ __forceinline__ void head_norm_rope(float (&v)[D / 32], const float* nw, float eps, float offset, const float* inv_freq,
+                                               int rot, float pos, int lane) {
+  constexpr int per = D / 32;
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < per; ++i) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < per; ++i) v[i] = v[i] * r * (offset + nw[lane + 32 * i]);
+  }
+  const int hreg = rot >> 6;   // registers per rotary half
+#pragma unroll
+  for (int i = 0; i < per / 2; ++i) {
+    if (i < hreg) {
+      const float ang = pos * inv_freq[lane + 32 * i];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      const float a = v[i], b = v[i + hreg];
+      v[i] = a * cs - b * sn;
+      v[i + hreg] = b * cs + a * sn;
+    }
+  }
+}
 
 // int8 x int8 -> int32 tensor-core MMA (K rows are int8 already; q is split in two int8 levels)
 __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -63,6 +100,10 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 //   O[head][dim] += P V with P (f16, the token's V scale folded in) reused from the C fragments as the A
 //     operand and V bytes expanded to f16 by byte permutes as 1152 + v; the constant is removed at
 //     the end with the running sum of the rounded P values (exact in fp32).
+__device__ __forceinline__ int bt_page(const DecParams& p, int seq, int page_index) {
+  return p.block_table[(size_t)seq * p.max_pages + page_index];
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p) {
   static_assert(G <= 8 && (D == 64 || D == 128 || D == 256), "unsupported geometry");
@@ -90,13 +131,45 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   const int pbeg = page_lo + split * pps;
   const int pend = min(pbeg + pps, page_hi);
 
+  const bool fused = p.qkv != nullptr;
+  if (fused && pbeg < pend && pend == page_hi && warp < 2) {
+    // This CTA's split holds the last page: append the row's K (warp 0: norm, RoPE) and V (warp 1) to it -- int8 with a
+    // scale per (token, head) -- before the barrier below; the page loads start after it.
+    const int pos = len - 1;
+    const int page = bt_page(p, seq, pos / kPage);
+    if (page >= 0) {
+      const bf16* src = p.qkv + (size_t)row * p.ld_qkv + (size_t)p.Hq * D + (size_t)((warp == 0 ? 0 : p.Hkv) + kvh) * D;
+      float v[D / 32];
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
+      if (warp == 0) head_norm_rope<D>(v, p.k_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)pos, lane);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = warp_max(amax);
+      const float sc = amax > 0.f ? amax / 127.f : 1.f;
+      const float inv = 1.f / sc;
+      const size_t base = ((size_t)page * p.Hkv + kvh) * kPage + (pos % kPage);
+      int8_t* dst = const_cast<int8_t*>(warp == 0 ? p.k_pages : p.v_pages) + base * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) dst[lane + 32 * i] = (int8_t)max(-127, min(127, __float2int_rn(v[i] * inv)));
+      if (lane == 0) const_cast<float*>(warp == 0 ? p.k_scale : p.v_scale)[base] = sc;
+    }
+  }
   // ---- q -> two int8 levels per head (warp w quantises heads w, w + 4) ----
   for (int h = warp; h < 8; h += kWarps) {
     float v[D / 32];
     float mx = 0.f;
+    if (fused && h < G) {
+      const bf16* src = p.qkv + (size_t)row * p.ld_qkv + (size_t)(kvh * G + h) * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
+      head_norm_rope<D>(v, p.q_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)(len - 1), lane);
+    }
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) {
-      v[i] = h < G ? __bfloat162float(p.q[(size_t)row * p.ld_q + (size_t)(kvh * G + h) * D + lane + 32 * i]) * p.scale : 0.f;
+      if (fused) v[i] = h < G ? __bfloat162float(__float2bfloat16(v[i])) * p.scale : 0.f;   // the two-kernel path rounds q to bf16
+      else v[i] = h < G ? __bfloat162float(p.q[(size_t)row * p.ld_q + (size_t)(kvh * G + h) * D + lane + 32 * i]) * p.scale : 0.f;
       mx = fmaxf(mx, fabsf(v[i]));
     }
     mx = warp_max(mx);
@@ -406,6 +479,37 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
   p.k_pages = (const int8_t*)k_pages; p.v_pages = (const int8_t*)v_pages; p.k_scale = (const float*)k_scale; p.v_scale = (const float*)v_scale;
   p.gate = (const bf16*)gate; p.out = (bf16*)out; p.ld_o = ld_o; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
   p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
+  p.qkv = nullptr; p.ld_qkv = 0; p.inv_freq = nullptr; p.q_norm_w = p.k_norm_w = nullptr; p.norm_eps = p.norm_offset = 0.f; p.rot = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int G = Hq / Hkv;
+  switch (D) {
+    case 64: return launch_g<64>(p, G, splits, st);
+    case 128: return launch_g<128>(p, G, splits, st);
+    case 256: return launch_g<256>(p, G, splits, st);
+    default: return -2;
+  }
+}
+
+// The same attention with the q/k norm, RoPE and the KV append of the rows' own tokens folded in (the work of
+// grm_rope_kvwrite): qkv is the raw fused projection output [M][(Hq + 2 Hkv) * D] (ungated q).  Valid when no row
+// attends to a token that another row of the same launch appends, i.e. every row is a different sequence.
+GRM_API int grm_paged_decode_attn_fused(const void* qkv, int ld_qkv, const void* inv_freq, const void* q_norm_w, const void* k_norm_w,
+                                        float norm_eps, float norm_offset, int rot, const void* row_seq, const void* row_pos,
+                                        const void* block_table, int max_pages, void* k_pages, void* v_pages, void* k_scale,
+                                        void* v_scale, void* out, int ld_o, void* part_o, void* part_ml, void* counters, int M,
+                                        int Hq, int Hkv, int D, int splits, int window, float scale, void* stream) {
+  if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1 || splits > kMaxSplits || (ld_o & 3) || !qkv || !inv_freq || (rot & 63) || rot > D ||
+      rot < 64)
+    return -2;
+  if (splits > 1 && (!part_o || !part_ml || !counters)) return -2;
+  DecParams p;
+  p.q = nullptr; p.ld_q = 0; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos;
+  p.block_table = (const int*)block_table; p.max_pages = max_pages;
+  p.k_pages = (const int8_t*)k_pages; p.v_pages = (const int8_t*)v_pages; p.k_scale = (const float*)k_scale; p.v_scale = (const float*)v_scale;
+  p.gate = nullptr; p.out = (bf16*)out; p.ld_o = ld_o; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
+  p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
+  p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.inv_freq = (const float*)inv_freq; p.q_norm_w = (const float*)q_norm_w;
+  p.k_norm_w = (const float*)k_norm_w; p.norm_eps = norm_eps; p.norm_offset = norm_offset; p.rot = rot;
   cudaStream_t st = (cudaStream_t)stream;
   const int G = Hq / Hkv;
   switch (D) {

@@ -229,6 +229,38 @@ def paged_decode_attn(q: torch.Tensor, row_seq: torch.Tensor, row_pos: torch.Ten
     return out
 
 
+FUSED_ROPE_ATTN = os.environ.get("GRIMOIRE_FUSED_ROPE_ATTN", "1") != "0"
+
+
+def paged_decode_attn_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, q_norm_w, k_norm_w, row_seq: torch.Tensor,
+                            row_pos: torch.Tensor, block_table: torch.Tensor, kv: KvLayer, geom: AttnGeom, out: torch.Tensor,
+                            splits: int, ws: Optional[Workspace]) -> bool:
+    """``rope_kvwrite`` + ``paged_decode_attn`` in one launch for rows of different sequences (ungated q): the kernel
+    norms / rotates q itself and the CTA that reads a row's last page appends the row's K / V first.  Returns False
+    when the case is not served (CPU tensors, gated q, switch off); the caller then runs the two kernels."""
+    if not (qkv.is_cuda and FUSED_ROPE_ATTN) or geom.q_gated or geom.rot < 64:
+        return False
+    M = qkv.shape[0]
+    Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
+    part_o = part_ml = counters = None
+    if splits > 1:
+        part_o = ws.get("attn_part_o", M * Hq * splits * D, torch.float32)
+        part_ml = ws.get("attn_part_ml", M * Hq * splits * 2, torch.float32)
+        counters = ws.get("attn_counters", 4096, torch.int32, zero=True)
+        if M * Hkv > 4096:
+            return False
+    code = _native.cuda().grm_paged_decode_attn_fused(
+        _native.ptr(qkv), _c(qkv.stride(0)), _native.ptr(inv_freq), _native.ptr(q_norm_w), _native.ptr(k_norm_w), _f(geom.norm_eps),
+        _f(geom.norm_offset), _c(geom.rot), _native.ptr(row_seq), _native.ptr(row_pos), _native.ptr(block_table),
+        _c(block_table.stride(0)), _native.ptr(kv.k), _native.ptr(kv.v), _native.ptr(kv.ks), _native.ptr(kv.vs), _native.ptr(out),
+        _c(out.stride(0)), _native.ptr(part_o), _native.ptr(part_ml), _native.ptr(counters), _c(M), _c(Hq), _c(Hkv), _c(D), _c(splits),
+        _c(geom.window), _f(geom.scale), _native.stream_ptr())
+    if code == -2:
+        return False
+    _native.check(code, "paged_decode_attn_fused")
+    return True
+
+
 def flash_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, geom: AttnGeom, out: torch.Tensor, q_pos0: int,
                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of one sequence's M new rows over its T = q_pos0 + M dense bf16 keys."""

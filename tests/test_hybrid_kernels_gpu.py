@@ -206,3 +206,34 @@ def test_gdn_chunked_matches_sequential_oracle(lens):
                 run_start.to(DEV), run_len.to(DEV), out, Hk, Hv, D, D, chunked=True)
     assert torch.allclose(out.float().cpu(), out_ref.float(), atol=3e-2, rtol=3e-2), float((out.float().cpu() - out_ref.float()).abs().max())
     assert torch.allclose(st.cpu(), st_ref, atol=2e-3, rtol=2e-3), float((st.cpu() - st_ref).abs().max())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_ep_decode_tiles_and_allreducing_combine_single_rank(M):
+    """The expert-parallel decode route with one rank owning experts [0, E): tiles from replicated choices (a choice
+    outside the range becomes an empty tile and a skipped slot), then the combine kernel whose all-reduce over one
+    rank is the plain slot-ordered combine.  Run twice: the epoch counters carry over between launches."""
+    from grimoire_b200.parallel.ep import ExpertParallel
+
+    torch.manual_seed(M)
+    E, k, H, I = 16, 4, 512, 128
+    ep = ExpertParallel(None, DEV, E, k, H, I, max_rows=8, fused=True)
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(M)]).to(torch.int32)
+    ep.E_loc = 12                                   # pretend experts 12..15 live elsewhere
+    te, nr, pos = ep.decode_tiles(ids.to(DEV), M)
+    local = ids < 12
+    flat = torch.arange(M * k, dtype=torch.int32).reshape(M, k)
+    assert torch.equal(te.cpu().reshape(M, k), torch.where(local, ids, torch.zeros_like(ids)))
+    assert torch.equal(nr.cpu().reshape(M, k), local.to(torch.int32))
+    assert torch.equal(pos.cpu()[:, :k], torch.where(local, flat, torch.full_like(flat, -1)))
+    assert torch.equal(pos.cpu()[:, k], torch.arange(M * k, M * (k + 1), dtype=torch.int32))
+    y = torch.randn(M * (k + 1), H)
+    w = torch.rand(M, k + 1)
+    h_ref = torch.randn(M, H)
+    h = h_ref.clone().to(DEV)
+    for _ in range(2):
+        Hb.moe_combine(h_ref, y, pos.cpu(), w)
+        ep.combine_allreduce(h, y.to(DEV), pos, w.to(DEV), M)
+    assert torch.allclose(h.cpu(), h_ref, atol=1e-5)
+    from grimoire_b200.ops import core as K
+    assert K.status_read()[0] == 0

@@ -366,3 +366,86 @@ def test_smallm_w4_int8_path_matches_fp32(M, N, Kd, group, monkeypatch):
     lin(x[M - 1: M], one, "f32")
     assert torch.equal(one[0], out32[M - 1])            # batch invariant
     _assert_clean()
+
+
+@pytest.mark.parametrize("M", [1, 5, 24])
+def test_fused_allreduce_epilogues_with_one_rank(M):
+    """The all-reducing epilogues (gemv_w4 for one row, smallm_w4 for more) with a world of one rank: the exchange
+    degenerates to this rank's own {value, epoch} slots, the result is the plain accumulate.  Three launches in a row
+    exercise both parities and the epoch counters; the multi-rank form runs in the 2-GPU tests."""
+    import ctypes
+    from grimoire_b200 import _native
+
+    torch.manual_seed(M)
+    N, Kd = 1024, 2048
+    qw = quantize(torch.randn(N, Kd) * 0.02, Fmt.INT4)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    t = lin.tiled
+    tiles = N // 16
+    half = tiles * 2048                                   # floats per parity half of the small-M exchange (world 1)
+    recv = torch.zeros(2 * half + 2 * tiles * 32, dtype=torch.float32, device=DEV)
+    flags = torch.zeros(tiles, dtype=torch.int32, device=DEV)
+    epochs = torch.zeros(tiles, dtype=torch.int32, device=DEV)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    want = torch.ones(M, N, dtype=torch.float32, device=DEV)
+    h = torch.ones(M, N, dtype=torch.float32, device=DEV)
+    rp = (ctypes.c_void_p * 1)(recv.data_ptr())
+    fp = (ctypes.c_void_p * 1)(flags.data_ptr())
+    c = ctypes.c_int
+    lib = _native.cuda()
+    for _ in range(3):
+        lin(x, want, "add_f32")
+        if M == 1:
+            code = lib.grm_gemv_w4_allreduce(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(h), c(t.N), c(t.K),
+                                             c(t.group), rp, ctypes.c_long(2 * half), fp, _native.ptr(epochs), c(1), c(0),
+                                             ctypes.c_uint(0), _native.stream_ptr())
+        else:
+            code = lib.grm_smallm_w4_allreduce(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(h), c(M), c(t.N),
+                                               c(t.K), c(x.stride(0)), c(h.stride(0)), c(t.group), rp, fp, _native.ptr(epochs), c(1),
+                                               c(0), ctypes.c_uint(0), _native.stream_ptr())
+        _native.check(code, "fused allreduce, one rank")
+    assert torch.allclose(h, want, atol=2e-3, rtol=1e-3)
+    assert int(epochs.min()) == 3 and int(epochs.max()) == 3
+    _assert_clean()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,rot,qk_norm", [(10, 2, 128, 128, True), (8, 2, 128, 64, False), (4, 2, 64, 64, True), (4, 1, 256, 64, True)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_decode_attn_with_fused_rope_kv_append_equals_two_kernels(Hq, Hkv, D, rot, qk_norm, splits):
+    """q/k norm + RoPE + KV append inside the decode attention kernel against rope_kvwrite followed by the attention
+    kernel: same arithmetic, so the appended cache bytes and the outputs are equal bit for bit.  Positions include a
+    page boundary (first slot of a new page) and the last slot of a page."""
+    torch.manual_seed(D + Hq)
+    S, pages_per = 3, 12
+    geom = K.AttnGeom(Hq, Hkv, D, rot, 1.0 / math.sqrt(D), False, 0, 1e-6, 0.0)
+    inv = ref.rope_inv_freq(rot, 10000.0).to(DEV)
+    qn = (torch.rand(D) + 0.5).to(DEV) if qk_norm else None
+    kn = (torch.rand(D) + 0.5).to(DEV) if qk_norm else None
+    table = torch.arange(S * pages_per, dtype=torch.int32).reshape(S, pages_per).to(DEV)
+    ws = Workspace(DEV)
+
+    def filled():
+        kv = K.KvLayer.alloc(S * pages_per, Hkv, D, DEV)
+        g = torch.Generator().manual_seed(1)
+        for s, n in enumerate((150, 96, 47)):
+            qkv = (torch.randn(n, (Hq + 2 * Hkv) * D, generator=g) * 0.7).bfloat16().to(DEV)
+            rs = torch.full((n,), s, dtype=torch.int32, device=DEV)
+            rp = torch.arange(n, dtype=torch.int32, device=DEV)
+            K.rope_kvwrite(qkv, rp, rs, table, inv, geom, torch.empty(n, Hq * D, dtype=torch.bfloat16, device=DEV), kv, qn, kn, None)
+        return kv
+
+    kv_a, kv_b = filled(), filled()
+    for s, pos in ((0, 150), (1, 96), (2, 47), (0, 151)):      # 96 opens a new page, 47 is a page's last slot
+        qkv = (torch.randn(1, (Hq + 2 * Hkv) * D) * 0.7).bfloat16().to(DEV)
+        rs = torch.tensor([s], dtype=torch.int32, device=DEV)
+        rp = torch.tensor([pos], dtype=torch.int32, device=DEV)
+        q = torch.empty(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+        want = torch.zeros(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+        K.rope_kvwrite(qkv, rp, rs, table, inv, geom, q, kv_a, qn, kn, None)
+        K.paged_decode_attn(q, rs, rp, table, kv_a, geom, want, splits, ws, None)
+        got = torch.zeros(1, Hq * D, dtype=torch.bfloat16, device=DEV)
+        assert K.paged_decode_attn_fused(qkv, inv, qn, kn, rs, rp, table, kv_b, geom, got, splits, ws)
+        assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    for a, b in ((kv_a.k, kv_b.k), (kv_a.v, kv_b.v), (kv_a.ks, kv_b.ks), (kv_a.vs, kv_b.vs)):
+        assert torch.equal(a, b)
+    _assert_clean()
