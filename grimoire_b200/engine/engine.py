@@ -53,7 +53,7 @@ class Engine:
         self.h_next = torch.zeros(lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
         self.prefix_cache = None
         self._reused_head_logits = None
-        self.graphs: dict[tuple[int, int], "torch.cuda.CUDAGraph"] = {}
+        self.graphs: dict[tuple, "torch.cuda.CUDAGraph"] = {}      # (rows, splits, distinct sequences)
         self.counters = {"prefill_rows": 0, "decode_steps": 0, "decode_rows": 0, "graph_replays": 0, "kernel_launches": 0}
 
     # ------------------------------------------------------------------------------------------
@@ -157,8 +157,8 @@ class Engine:
     def _splits_for(self, M: int, max_len: int) -> int:
         return K.decode_splits(max_len, M, self.model.geom.Hkv)
 
-    def _run_rows(self, M: int, splits: int) -> torch.Tensor:
-        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits)
+    def _run_rows(self, M: int, splits: int, distinct: bool = False) -> torch.Tensor:
+        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct)
         logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
         pp = getattr(self.model, "pp", None)
         if logits is not None:
@@ -186,19 +186,20 @@ class Engine:
             max_len = max(max_len, p + 1)
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
+        distinct = len({s.slot for s in seqs}) == M      # no verify block: the attention kernel may append K / V itself
         tp = getattr(self.model, "tp", None)
         ep = getattr(self.model, "ep", None)
         if (tp is not None and not tp.fused) or (ep is not None and not ep.fused) or getattr(self.model, "pp", None) is not None:
             use_graph = False        # NCCL collectives / stage hops stay out of captured graphs
         if use_graph and self.device.type == "cuda":
-            key = (M, splits)
+            key = (M, splits, distinct)
             g = self.graphs.get(key)
             if g is None:
-                g = self._capture(M, splits)
+                g = self._capture(M, splits, distinct)
             g.replay()
             self.counters["graph_replays"] += 1
         else:
-            self._run_rows(M, splits)
+            self._run_rows(M, splits, distinct)
         self.h_next[:M].copy_(self.decode_buf.next_ids[:M], non_blocking=True)
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
@@ -224,17 +225,17 @@ class Engine:
         if saved is not None:
             self.model.restore_recurrent(saved)
 
-    def _capture(self, M: int, splits: int):
+    def _capture(self, M: int, splits: int, distinct: bool = False):
         # warm the allocator / workspace outside capture, then record; a model with recurrent state
         # must not keep the warm-up run's update
         saved = self._save_recurrent(M)
-        self._run_rows(M, splits)
+        self._run_rows(M, splits, distinct)
         torch.cuda.current_stream().synchronize()
         self._restore_recurrent(saved)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._run_rows(M, splits)
-        self.graphs[(M, splits)] = g
+            self._run_rows(M, splits, distinct)
+        self.graphs[(M, splits, distinct)] = g
         return g
 
     # ------------------------------------------------------------------------------------------
@@ -253,9 +254,10 @@ class Engine:
             max_len = max(max_len, s.length + steps_ahead + 1)
         self._stage_rows(first_tokens, [s.slot for s in seqs], [s.length for s in seqs])
         splits = self._splits_for(M, max_len)
+        distinct = len({s.slot for s in seqs}) == M
 
         def body():
-            self._run_rows(M, splits)
+            self._run_rows(M, splits, distinct)
             self.d_tokens[:M].copy_(self.decode_buf.next_ids[:M])
             self.d_row_pos[:M].add_(1)
 

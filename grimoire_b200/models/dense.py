@@ -58,6 +58,7 @@ class RowBatch:
     seq_slot: int = 0
     splits: int = 1
     logits_rows: Optional[torch.Tensor] = None   # int64 indices of rows that need logits (None = all)
+    distinct: bool = False               # decode: every row is a different sequence (no verify block in the step)
 
 
 class Buffers:
@@ -374,7 +375,7 @@ class DenseModel:
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
                                gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
                 K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
-            elif not (M == 1 and gate is None and K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos,
+            elif not ((M == 1 or rb.distinct) and gate is None and K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos,
                                                                           block_table, kvl, geom, attn, rb.splits, self.ws)):
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
                 K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)

@@ -446,6 +446,17 @@ def test_decode_attn_with_fused_rope_kv_append_equals_two_kernels(Hq, Hkv, D, ro
         got = torch.zeros(1, Hq * D, dtype=torch.bfloat16, device=DEV)
         assert K.paged_decode_attn_fused(qkv, inv, qn, kn, rs, rp, table, kv_b, geom, got, splits, ws)
         assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    # three rows of three different sequences in one launch
+    qkv = (torch.randn(3, (Hq + 2 * Hkv) * D) * 0.7).bfloat16().to(DEV)
+    rs = torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV)
+    rp = torch.tensor([152, 97, 48], dtype=torch.int32, device=DEV)
+    q = torch.empty(3, Hq * D, dtype=torch.bfloat16, device=DEV)
+    want = torch.zeros(3, Hq * D, dtype=torch.bfloat16, device=DEV)
+    K.rope_kvwrite(qkv, rp, rs, table, inv, geom, q, kv_a, qn, kn, None)
+    K.paged_decode_attn(q, rs, rp, table, kv_a, geom, want, splits, ws, None)
+    got = torch.zeros(3, Hq * D, dtype=torch.bfloat16, device=DEV)
+    assert K.paged_decode_attn_fused(qkv, inv, qn, kn, rs, rp, table, kv_b, geom, got, splits, ws)
+    assert torch.equal(got, want)
     for a, b in ((kv_a.k, kv_b.k), (kv_a.v, kv_b.v), (kv_a.ks, kv_b.ks), (kv_a.vs, kv_b.vs)):
         assert torch.equal(a, b)
     _assert_clean()
