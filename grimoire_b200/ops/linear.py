@@ -43,6 +43,9 @@ GEMV_W4 = os.environ.get("GRIMOIRE_GEMV_W4", "1") != "0"   # single-row int4 pro
 
 
 FUSED_NORM = os.environ.get("GRIMOIRE_FUSED_NORM", "1") != "0"   # RMSNorm inside the single-row GEMV prologue
+# every CTA of the fused form re-reads the residual row and the norm weights (60 KB at H = 5120): worth it for a layer's
+# projections (a few hundred CTAs), not for a vocabulary-sized head (~9,500 CTAs)
+FUSED_NORM_MAX_N = int(os.environ.get("GRIMOIRE_FUSED_NORM_MAX_N", "40960"))
 
 
 def quant_x_i8(x: torch.Tensor, K: int, group: int, ws: Workspace):
@@ -172,7 +175,7 @@ class W4Linear:
         instead of two).  Returns False when the shape or device is not served; the caller then runs norm + forward."""
         t = self.tiled
         if (not GEMV_W4 or not FUSED_NORM or self.device.type != "cuda" or t is None or h.shape[0] != 1 or t.K > 20480
-                or h.dtype != torch.float32 or h.shape[1] != t.K):
+                or h.dtype != torch.float32 or h.shape[1] != t.K or t.N > FUSED_NORM_MAX_N):
             return False
         code = _native.cuda().grm_gemv_w4_norm(_native.ptr(t.w), _native.ptr(t.sz), None, _native.ptr(h), _native.ptr(norm_w),
                                                ctypes.c_float(eps), ctypes.c_float(offset), _native.ptr(out), _c(t.N), _c(t.K),
