@@ -128,7 +128,7 @@ class EngineConfig:
 
 def add_engine_flags(ap: argparse.ArgumentParser) -> None:
     ap.add_argument("--model", "-m", default="", help="HF directory, .gguf file or pre-quantized artifact")
-    ap.add_argument("--proj", default="int4", help="projection format: int4 int8 mxfp4 mxfp8 fp8 fp8_e5m2 bf16 native")
+    ap.add_argument("--proj", default="int4", help="projection format: int4 int8 mxfp4 mxfp8 fp8 (block-scaled) fp8_e4m3 fp8_e5m2 bf16 native")
     ap.add_argument("--ctx", type=int, default=8192, help="context cap per request")
     ap.add_argument("--dflash-model", default="", help="optional block drafter checkpoint")
     ap.add_argument("--defer-moe-gather", action="store_true")
