@@ -31,16 +31,45 @@ class UnsupportedModel(ValueError):
 _SERVED_PROJ = ("int4", "native", "mxfp4", "fp8", "int8", "bf16", "mxfp8", "fp8_e4m3", "fp8_e5m2")
 
 
+def is_hybrid(cfg: ModelConfig) -> bool:
+    """Configurations served by ``HybridModel``: any linear-attention (Gated DeltaNet) layer or an MoE FFN."""
+    from .models.config import LINEAR_ATTN
+
+    return cfg.is_moe or any(t == LINEAR_ATTN for t in cfg.layer_types)
+
+
 def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     """Refusal by name before any weight is read (unsupported_reason, grimoire.cpp:6969)."""
+    if cfg.head_dim not in (64, 128, 256):
+        return f"head_dim {cfg.head_dim} is not supported (64, 128, 256)"
+    if is_hybrid(cfg):
+        if not cfg.is_moe or not cfg.shared_expert_intermediate_size:
+            return "linear-attention layers are served with the MoE FFN (+ shared expert) of the hybrid family only"
+        if ec.tp_world > 1 or ec.pp_world > 1:
+            return "the hybrid (DeltaNet + MoE) family scales by expert parallelism (multi EP); tensor / pipeline stages are not built for it"
+        if cfg.num_experts % max(1, ec.ep_world):
+            return f"expert parallel {ec.ep_world} does not divide {cfg.num_experts} experts"
+        if cfg.hidden_size % 128 or cfg.moe_intermediate_size % 128:
+            return "block-scaled fp8 projections need widths that are multiples of 128"
+        return None
+    if ec.ep_world > 1:
+        return "expert parallelism needs an MoE model"
     if ec.tp_world > 1:
         if cfg.num_attention_heads % ec.tp_world or cfg.num_key_value_heads % ec.tp_world:
             return f"tensor parallel {ec.tp_world} does not divide {cfg.num_attention_heads} q / {cfg.num_key_value_heads} kv heads"
         if cfg.intermediate_size and (cfg.intermediate_size // ec.tp_world) % cfg.quant_group:
             return "FFN slice per rank is not a multiple of the quantisation group"
-    if cfg.head_dim not in (64, 128, 256):
-        return f"head_dim {cfg.head_dim} is not supported (64, 128, 256)"
+    if ec.pp_world > cfg.num_hidden_layers:
+        return f"pipeline parallel {ec.pp_world} exceeds {cfg.num_hidden_layers} layers"
     return None
+
+
+def _find_artifact(path: str) -> Optional[str]:
+    """``model-v3.grm`` itself, or a bundle directory that holds one."""
+    if path.endswith(".grm") and os.path.isfile(path):
+        return path
+    cand = os.path.join(path, "model-v3.grm")
+    return cand if os.path.isfile(cand) else None
 
 
 class Grimoire:
@@ -48,13 +77,23 @@ class Grimoire:
         self.model, self.engine, self.tokenizer = model, engine, tokenizer
         self.config = config or EngineConfig()
         self.name = name or self.config.model
+        self.drafter = None            # models.mtp.MtpDrafter when the checkpoint carries a draft head and GRIMOIRE_MTP=1
         self._sched = None
 
     # ---- construction ----
     @classmethod
-    def load(cls, ec: EngineConfig, device: Optional[str] = None, tp=None) -> "Grimoire":
+    def load(cls, ec: EngineConfig, device: Optional[str] = None, tp=None, pp=None, ep_group=None) -> "Grimoire":
+        """Build model + engine for ``ec.model``: ``synthetic:<preset>``, a HF directory (dense or hybrid family), a
+        ``.gguf`` file, or a pre-quantised artifact (``model-v3.grm`` / its bundle directory).  ``tp`` / ``pp`` are this
+        rank's TensorParallel / PipelineParallel objects, ``ep_group`` the expert-parallel process group."""
+        from .models.hybrid import HybridModel
+
         dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
         tok = None
+        mtp_src = None                    # (state-dict-like getter, config) for the draft head
+        ck_dir = None
+        if ec.proj == "fp8-e5m2" or ec.proj == "fp8-e4m3":
+            ec.proj = ec.proj.replace("-", "_")
         if ec.model.startswith("synthetic:"):
             preset = ec.model.split(":", 1)[1]
             if preset not in PRESETS:
@@ -63,15 +102,27 @@ class Grimoire:
             why = unsupported_reason(cfg, ec)
             if why:
                 raise UnsupportedModel(why)
-            model = DenseModel.random(cfg, dev, seed=0, tp_rank=ec.tp_rank, tp_world=ec.tp_world)
+            if is_hybrid(cfg):
+                model = HybridModel.random(cfg, dev, seed=0, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
+            else:
+                model = DenseModel.random(cfg, dev, seed=0, tp_rank=ec.tp_rank, tp_world=ec.tp_world, pp_rank=ec.pp_rank,
+                                          pp_world=ec.pp_world)
         else:
             from .tokenizer import Tokenizer
 
-            if ec.proj == "fp8-e5m2" or ec.proj == "fp8-e4m3":
-                ec.proj = ec.proj.replace("-", "_")
             if ec.proj not in _SERVED_PROJ:
                 raise UnsupportedModel(f"--proj {ec.proj}: this build serves {sorted(_SERVED_PROJ)}")
-            if ec.model.endswith(".gguf"):
+            art = _find_artifact(ec.model)
+            if art is not None:
+                from .formats.artifact import load_artifact_model
+
+                ck_dir = os.path.dirname(art)
+                cfg = ModelConfig.from_dir(ck_dir)
+                why = unsupported_reason(cfg, ec)
+                if why:
+                    raise UnsupportedModel(why)
+                model, mtp_src = load_artifact_model(art, cfg, dev, ec)
+            elif ec.model.endswith(".gguf"):
                 # GGUF: config and tokenizer from the metadata, tensors dequantised block by block and re-quantised
                 # to the serving format (the reference's native GGUF path keeps the file's blocks; this one does not)
                 import dataclasses
@@ -86,7 +137,8 @@ class Grimoire:
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world)
+                model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world, pp_rank=ec.pp_rank,
+                                                   pp_world=ec.pp_world)
                 tj = G.tokenizer_json_from_gguf(gf)
                 if tj is not None:
                     tdir = tempfile.mkdtemp(prefix="grimoire_tok_")
@@ -95,22 +147,43 @@ class Grimoire:
                     tok = Tokenizer(tdir)
                 gf.close()
             else:
+                ck_dir = ec.model
                 cfg = ModelConfig.from_dir(ec.model)
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
-                                                   proj=ec.proj)
-                if os.path.exists(os.path.join(ec.model, "tokenizer.json")):
-                    tok = Tokenizer(ec.model)
+                if is_hybrid(cfg):
+                    model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
+                else:
+                    model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
+                                                       proj=ec.proj, pp_rank=ec.pp_rank, pp_world=ec.pp_world)
+                    if ec.mtp and cfg.mtp_num_hidden_layers > 0:
+                        from .formats.checkpoint import Checkpoint
+
+                        ck = Checkpoint(ec.model)
+                        if ck.has("mtp.fc.weight"):
+                            mtp_src = ck
+            if ck_dir and tok is None and os.path.exists(os.path.join(ck_dir, "tokenizer.json")):
+                tok = Tokenizer(ck_dir)
+        hybrid = isinstance(model, HybridModel)
         if tp is not None:
             tp.attach(model, max_rows=max(ec.prefill_chunk, 64))
+        if pp is not None:
+            pp.attach(model)
+        if hybrid and ep_group is not None and ec.ep_world > 1:
+            model.attach_ep(ep_group, max_rows=max(ec.prefill_chunk, 64))
+        # draft head: only on a single-stage, single-rank dense model (the reference drafts on the last stage)
+        want_mtp = mtp_src is not None and ec.tp_world == 1 and ec.pp_world == 1
         lim = EngineLimits(max_slots=ec.seq_slots, max_ctx=ec.ctx, prefill_chunk=ec.prefill_chunk, max_decode_rows=64,
-                           kv_pages=ec.kv_pages)
+                           kv_pages=ec.kv_pages, extra_kv_layers=1 if want_mtp else 0)
         eng = Engine(model, lim)
         if ec.prefix_cache:
             eng.enable_prefix_cache()
         g = cls(model, eng, tok, ec)
+        if want_mtp:
+            from .models.mtp import MtpDrafter, MtpHead
+
+            g.drafter = MtpDrafter(eng, MtpHead.from_checkpoint(model, mtp_src, draft_vocab=ec.mtp_draft_vocab))
         g.banner()
         return g
 
@@ -120,8 +193,10 @@ class Grimoire:
         lines = [
             f"[grimoire-b200] model={self.name or 'synthetic'} layers={m.cfg.num_hidden_layers} hidden={m.cfg.hidden_size} "
             f"heads={m.cfg.num_attention_heads}/{m.cfg.num_key_value_heads}x{m.cfg.head_dim} vocab={m.cfg.vocab_size}",
-            f"  parallel   : tp={m.tp_world} (fused all-reduce={'on' if getattr(m, 'tp', None) and m.tp.fused else 'off'}) pp={ec.pp_world} dp={ec.dp_world}",
-            f"  weights    : int4 g{m.cfg.quant_group} ({m.weight_bytes() / 1e9:.2f} GB on this rank), lm_head={'tied bf16' if m.cfg.tie_word_embeddings else 'int4'}",
+            f"  parallel   : tp={m.tp_world} (fused all-reduce={'on' if getattr(m, 'tp', None) and m.tp.fused else 'off'}) pp={ec.pp_world} "
+            f"ep={getattr(m, 'ep_world', 1)} dp={ec.dp_world}",
+            f"  weights    : {'block-scaled fp8 (e4m3, 1x128)' if getattr(m, 'kv_layer_count', None) is not None else ec.proj + ' g' + str(m.cfg.quant_group)} "
+            f"({m.weight_bytes() / 1e9:.2f} GB on this rank), draft head={'mtp' if self.drafter is not None else 'none'}",
             f"  kv cache   : int8 paged, {self.engine.kv.num_pages} pages x 16 tokens, {self.engine.kv.bytes_per_token()} B/token",
             f"  batching   : width {ec.width()}, prefill chunk {ec.prefill_chunk}, interleave chunk {ec.interleave_chunk}",
             f"  speculation: copy drafts={'on' if ec.copy_drafts else 'off'} depth table {ec.spec_depth_table()}",
@@ -135,8 +210,11 @@ class Grimoire:
     # ---- single request path (CLI, workers) ----
     def generate(self, prompt_ids: Sequence[int], max_new: int, eos: Optional[int] = None, eos2: Optional[int] = None,
                  on_token: Optional[Callable[[int], bool]] = None, draft_depth: int = 0, stats: Optional[SpecStats] = None):
-        opts = GenerationOptions(max_new=max_new, eos=eos, eos2=eos2, draft_depth=draft_depth,
-                                 drafter=CopyDrafter() if draft_depth else None, stats=stats or SpecStats())
+        drafter = None
+        if draft_depth:
+            drafter = self.drafter if self.drafter is not None else CopyDrafter()
+        opts = GenerationOptions(max_new=max_new, eos=eos, eos2=eos2, draft_depth=draft_depth, drafter=drafter,
+                                 stats=stats or SpecStats())
         return generate_tokens(self.engine, list(prompt_ids), opts, on_token)
 
     def generate_batch(self, prompts: Sequence[Sequence[int]], max_new: int, eos: Optional[int] = None):
@@ -160,10 +238,11 @@ class Grimoire:
             from .sched.scheduler import Scheduler
 
             ec = self.config
+            spec = self.drafter is not None or (ec.copy_drafts and getattr(self.model, "supports_verify_rows", True))
             self._sched = Scheduler(self.engine, width=ec.width(), interleave_chunk=ec.interleave_chunk,
                                     prefill_chunk=ec.prefill_chunk, hold_ms=ec.admit_hold_ms, hold_long_ms=ec.admit_hold_long_ms,
-                                    depths=ec.spec_depth_table() if ec.copy_drafts else (0,), spec_rows=ec.spec_rows,
-                                    copy_drafts=bool(ec.copy_drafts))
+                                    depths=ec.spec_depth_table() if spec else (0,), spec_rows=ec.spec_rows,
+                                    copy_drafts=bool(ec.copy_drafts) and spec, drafter=self.drafter)
         return self._sched
 
     def prefix_slots_used(self) -> int:

@@ -34,6 +34,7 @@ _ENV = {
     "GRIMOIRE_PP_WORLD_SIZE": ("pp_world", int),
     "GRIMOIRE_DP_WORLD_SIZE": ("dp_world", int),
     "GRIMOIRE_EP_WORLD_SIZE": ("ep_world", int),
+    "GRIMOIRE_EP_RANK": ("ep_rank", int),
     "GRIMOIRE_CP_WORLD_SIZE": ("cp_world", int),
     "GRIMOIRE_SPEC_ROWS": ("spec_rows", int),
     "GRIMOIRE_SPEC_DEPTHS": ("spec_depths", str),
@@ -90,6 +91,7 @@ class EngineConfig:
     pp_world: int = 1
     dp_world: int = 1
     ep_world: int = 1
+    ep_rank: int = 0
     cp_world: int = 1
     tp_fused: int = 1
     # diagnostics
@@ -110,7 +112,7 @@ class EngineConfig:
         for name in ("seq_slots", "max_batch", "prefill_chunk", "tp_world", "pp_world", "dp_world", "ep_world", "cp_world"):
             if getattr(self, name) < 1:
                 raise ValueError(f"{name} must be >= 1")
-        if not (0 <= self.tp_rank < self.tp_world) or not (0 <= self.pp_rank < self.pp_world):
+        if not (0 <= self.tp_rank < self.tp_world) or not (0 <= self.pp_rank < self.pp_world) or not (0 <= self.ep_rank < self.ep_world):
             raise ValueError("rank outside its world size")
         if self.mtp_k < 0 or self.mtp_k > 16:
             raise ValueError("GRIMOIRE_MTP_K must be in 0..16")

@@ -69,7 +69,16 @@ class Engine:
         """Free the slot; with ``cache`` its KV stays resident in the prefix cache (cache_sequence,
         grimoire.cpp:12333) until evicted."""
         if cache and self.prefix_cache is not None:
-            self.prefix_cache.store(seq, head_logits)
+            extra = None
+            snap = getattr(self.model, "snapshot_slot", None)
+            if snap is not None:
+                # recurrent layers: the state after the last cached token travels with the entry; an entry whose token
+                # record and cache length disagree cannot be resumed and is not kept
+                if seq.length != len(seq.tokens):
+                    self.kv.release(seq)
+                    return
+                extra = {"recurrent": snap(seq.slot)}
+            self.prefix_cache.store(seq, head_logits, extra)
         self.kv.release(seq)
 
     def enable_prefix_cache(self, max_entries: int = 16):
@@ -84,6 +93,9 @@ class Engine:
             return 0
         n, logits = self.prefix_cache.reuse(seq, list(prompt))
         self._reused_head_logits = logits
+        rec = self.prefix_cache.last_extra.get("recurrent") if n else None
+        if rec is not None:
+            self.model.load_slot(seq.slot, rec)
         return n
 
     def rollback(self, seq: SeqSlot, length: int) -> None:

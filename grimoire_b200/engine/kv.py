@@ -45,6 +45,8 @@ class KvPool:
             self.table_host = self.table_host.pin_memory()
         self.table = self.table_host.to(self.device)
         self.slots: dict[int, SeqSlot] = {}
+        # called with the number of pages still missing when the free list runs dry (the prefix cache evicts entries)
+        self.reclaim = None
 
     # ---- accounting ----
     def pages_free(self) -> int:
@@ -76,9 +78,12 @@ class KvPool:
         if need > self.max_pages_per_seq:
             raise OutOfPages(f"context {new_length} exceeds the per-request cap")
         grew = False
+        if need - len(seq.pages) > len(self.free) and self.reclaim is not None:
+            self.reclaim(need - len(seq.pages))
+        if need - len(seq.pages) > len(self.free):
+            # nothing is mapped for a request that cannot be served in full: the caller parks or fails this one only
+            raise OutOfPages(f"KV page pool exhausted ({need - len(seq.pages)} pages wanted, {len(self.free)} free)")
         while len(seq.pages) < need:
-            if not self.free:
-                raise OutOfPages("KV page pool exhausted")
             pg = self.free.pop()
             self.refcount[pg] = 1
             self.table_host[seq.slot, len(seq.pages)] = pg

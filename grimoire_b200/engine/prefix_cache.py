@@ -39,6 +39,8 @@ class PrefixCache:
         self._clock = itertools.count(1)
         self.hits = 0
         self.tokens_reused = 0
+        self.last_extra: dict = {}          # ``extra`` of the entry the last successful ``reuse`` attached
+        kv.reclaim = self.make_room         # a live decode that needs a page evicts cached entries before it fails
 
     # ---- store ----
     def store(self, seq: SeqSlot, head_logits: Optional[torch.Tensor] = None, extra: Optional[dict] = None) -> None:
@@ -94,41 +96,50 @@ class PrefixCache:
         """Attach cached pages to a fresh slot.  Returns (tokens reused, head logits or None).
         At least one prompt token is always left to prefill unless the entry carries the logits of
         exactly this prompt."""
+        self.last_extra = {}
         if seq.length or seq.pages:
             return 0, None
         ent, n = self.match(prompt)
         if ent is None:
             return 0, None
         exact = n == len(prompt) == len(ent.tokens) and ent.head_logits is not None
+        # the whole entry is a prefix of the prompt: its partial tail page can be copied and appended to
+        whole = n == len(ent.tokens) and (exact or len(prompt) > n)
+        recurrent = ent.extra.get("recurrent") is not None
+        if recurrent and not whole:
+            # a recurrent state exists only for the entry's last position: a shorter match cannot resume from it
+            return 0, None
         if not exact:
             n = min(n, len(prompt) - 1)
         n_full = n // PAGE
-        if n_full == 0 and not exact:
+        if n_full == 0 and not whole:
             return 0, None
         kv = self.kv
+        if whole and n > n_full * PAGE and not kv.free:
+            self.make_room(1)
+        if recurrent and n > n_full * PAGE and not kv.free:
+            return 0, None                 # the tail page cannot be copied: KV and state would disagree
         for i in range(n_full):
             pg = ent.pages[i]
             kv.refcount[pg] += 1
             kv.table_host[seq.slot, i] = pg
             seq.pages.append(pg)
         reused = n_full * PAGE
-        if exact and n > reused:
-            # the whole entry is reused: copy its partial tail page so this conversation can append to it
-            if not kv.free:
-                self.make_room(1)
-            if kv.free:
-                new = kv.free.pop()
-                kv.refcount[new] = 1
-                src = ent.pages[n_full]
-                for L in kv.layers:
-                    L.k[new].copy_(L.k[src]); L.v[new].copy_(L.v[src]); L.ks[new].copy_(L.ks[src]); L.vs[new].copy_(L.vs[src])
-                kv.table_host[seq.slot, n_full] = new
-                seq.pages.append(new)
-                reused = n
+        if whole and n > reused and kv.free:
+            # copy-on-write of the entry's partial tail page so this conversation can append to it
+            new = kv.free.pop()
+            kv.refcount[new] = 1
+            src = ent.pages[n_full]
+            for L in kv.layers:
+                L.k[new].copy_(L.k[src]); L.v[new].copy_(L.v[src]); L.ks[new].copy_(L.ks[src]); L.vs[new].copy_(L.vs[src])
+            kv.table_host[seq.slot, n_full] = new
+            seq.pages.append(new)
+            reused = n
         kv._sync_row(seq.slot)
         seq.length = reused
         seq.tokens = list(prompt[:reused])
         ent.stamp = next(self._clock)
+        self.last_extra = ent.extra
         self.hits += 1
         self.tokens_reused += reused
         return reused, (ent.head_logits if (exact and reused == len(prompt)) else None)

@@ -148,6 +148,69 @@ class Artifact:
         self._f.close()
 
 
+class ArtifactSource:
+    """Tensor resolver over an artifact with the interface the model loaders use (``cfg``, ``prefix``, ``has``,
+    ``tensor``, ``plain``, ``linear``, ``embedding``): the counterpart of NativeModel::view feeding Grimoire::build
+    (src/native_model.cpp:157-260).  Quantised entries come back as QuantWeights and are served in their stored format
+    when it matches the projection format, raw entries as tensors."""
+
+    def __init__(self, art: "Artifact", cfg):
+        self.art, self.cfg = art, cfg
+        keys = set(art.keys())
+        self._keys = keys
+        self.prefix = "model.language_model." if any(k.startswith("model.language_model.") for k in keys) else "model."
+
+    def has(self, name: str) -> bool:
+        return name in self._keys
+
+    def tensor(self, name: str):
+        if name not in self._keys:
+            return None
+        e = self.art.get(name)
+        return e.dequant() if isinstance(e, QuantWeight) else e
+
+    def plain(self, name: str):
+        t = self.tensor(name)
+        return None if t is None else t.float()
+
+    def linear(self, base: str):
+        name = base + ".weight"
+        if name not in self._keys:
+            return None
+        e = self.art.get(name)
+        return e if isinstance(e, QuantWeight) else e.float()
+
+    def embedding(self):
+        t = self.plain(self.prefix + "embed_tokens.weight")
+        if t is None:
+            raise KeyError(self.prefix + "embed_tokens.weight")
+        return t
+
+
+def load_artifact_model(path: str | Path, cfg, device, ec):
+    """Build the model of a pre-quantised artifact (``model-v3.grm`` next to its ``config.json``).  Returns (model,
+    resolver for the draft head or None)."""
+    from ..models.dense import DenseModel
+    from ..models.hybrid import HybridModel
+    from ..models.config import LINEAR_ATTN
+
+    src = ArtifactSource(Artifact(path), cfg)
+    if cfg.is_moe or any(t == LINEAR_ATTN for t in cfg.layer_types):
+        model = HybridModel.from_checkpoint(src, device, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
+        return model, None
+    # the artifact's own format wins unless --proj names another one
+    stored = {Fmt(r[2]) for r in src.art.records.values() if r[1] != ENC_RAW}
+    proj = ec.proj
+    if proj in ("int4", "native") and len(stored) == 1:
+        only = next(iter(stored))
+        proj = {Fmt.INT4: "int4", Fmt.MXFP4: "mxfp4", Fmt.FP8_BLOCK: "fp8", Fmt.INT8: "int8", Fmt.BF16: "bf16", Fmt.MXFP8: "mxfp8",
+                Fmt.FP8_E4M3: "fp8_e4m3", Fmt.FP8_E5M2: "fp8_e5m2"}.get(only, proj)
+    model = DenseModel.from_checkpoint(src, device, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16), proj=proj,
+                                       pp_rank=ec.pp_rank, pp_world=ec.pp_world)
+    mtp = src if (ec.mtp and cfg.mtp_num_hidden_layers > 0 and src.has("mtp.fc.weight")) else None
+    return model, mtp
+
+
 _FORMATS = {"int4": Fmt.INT4, "bf16": Fmt.BF16, "fp8": Fmt.FP8_E4M3, "fp8-e4m3": Fmt.FP8_E4M3, "fp8-e5m2": Fmt.FP8_E5M2,
             "int8": Fmt.INT8, "mxfp4": Fmt.MXFP4, "mxfp8": Fmt.MXFP8, "fp8-block": Fmt.FP8_BLOCK, "nvfp4": Fmt.NVFP4}
 _LINEAR = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj", "in_proj_qkv", "in_proj_z", "out_proj")

@@ -263,7 +263,7 @@ class DenseModel:
         else is dequantized and quantized on the host (Grimoire::build, grimoire.cpp:7133-10637)."""
         from ..formats.checkpoint import Checkpoint
 
-        ck = Checkpoint(path)
+        ck = Checkpoint(path) if isinstance(path, (str, bytes)) or hasattr(path, "__fspath__") else path    # or any tensor resolver
         cfg = ck.cfg
         if proj in ("mxfp4", "fp8") or proj in _ROWQ_PROJ:
             import dataclasses
@@ -345,6 +345,38 @@ class DenseModel:
         self.lm_head(xf, logits, "f32")
         return logits
 
+    def _mega_ready(self) -> bool:
+        ok = getattr(self, "_mega_ok", None)
+        if ok is None:
+            from ..ops import mega
+
+            ok = self._mega_ok = mega.dense_supported(self)
+        return ok
+
+    def forward_mega(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
+        """One decode token through the persistent phase kernel (ops/mega.py): two launches per layer -- attention, then
+        o_proj | gate_up | down | the next layer's q|k|v inside one kernel -- with the same rounding points as ``forward``."""
+        from ..ops import mega
+
+        cfg, geom = self.cfg, self.geom
+        tab = mega.table_for(self, buf)
+        h, qkv, q, attn = buf.h[:1], buf.qkv[:1], buf.q[:1], buf.attn[:1]
+        K.embed(rb.tokens, self.embed, h)
+        tab.run(0, 1)
+        n = tab.n_layers
+        for li, L in enumerate(self.layers):
+            kvl = kv_layers[li]
+            if not K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos, block_table, kvl, geom,
+                                             attn, rb.splits, self.ws):
+                K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, None)
+                K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, None)
+            last = li == n - 1
+            tab.run(1 + 4 * li, 4 if (not last or tab.head_in_table) else 3)
+        logits = buf.logits[:1]
+        if not tab.head_in_table:
+            self._norm_linear(self.lm_head, h, self.final_norm, buf.xf[:1], logits, "f32", cfg.rms_norm_eps, cfg.norm_offset)
+        return logits
+
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
         if (rb.mode == "prefill" and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
@@ -352,6 +384,8 @@ class DenseModel:
             return self.forward_prefill_sp(rb, buf, kv_layers, block_table)
         cfg, geom = self.cfg, self.geom
         M = rb.tokens.shape[0]
+        if M == 1 and rb.mode == "decode" and not trace.timeline.on and self._mega_ready():
+            return self.forward_mega(rb, buf, kv_layers, block_table)
         eps, off = cfg.rms_norm_eps, cfg.norm_offset
         h, x = buf.h[:M], buf.x[:M]
         qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]

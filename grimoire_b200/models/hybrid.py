@@ -141,6 +141,15 @@ class HybridModel:
         self.state[:, slot].zero_()
         self.ring[:, slot].zero_()
 
+    def snapshot_slot(self, slot: int):
+        """Recurrent state of one conversation (prefix-cache entries of this family carry it: the reference snapshots
+        conv tails + DeltaNet matrices with the KV, snapshot_recurrent grimoire.cpp:12364-12406)."""
+        return self.state[:, slot].clone(), self.ring[:, slot].clone()
+
+    def load_slot(self, slot: int, snap) -> None:
+        self.state[:, slot].copy_(snap[0])
+        self.ring[:, slot].copy_(snap[1])
+
     def attach_ep(self, group, max_rows: int, fused=None):
         """Shard the MoE layers over ``group`` (the model must have been built with the matching
         ep_rank / ep_world expert slice)."""
@@ -227,6 +236,105 @@ class HybridModel:
         m.embed = rnd(cfg.vocab_size, H, tag=900001).bfloat16()
         m.final_norm = nw(H)
         m.lm_head = fp8(rnd(cfg.vocab_size, H, tag=900002), "lm_head")
+        return m
+
+    # ------------------------------------------------------------------------------------------
+    # checkpoints
+    # ------------------------------------------------------------------------------------------
+    def _add_layer(self, i: int, w: dict) -> None:
+        """One layer from logical fp32 tensors (``[out][in]``; stored block-fp8 QuantWeights are used as they are).
+        Keys: in_norm, post_norm, router [E][H], shared_gate [1][H], gate_up [E][2I][H], down [E][H][I], shared_gate_proj,
+        shared_up_proj, shared_down_proj, then either q, k, v, o, q_norm, k_norm or in_qkv, in_z, in_a, in_b, conv [C][4],
+        A_log, dt_bias, gdn_norm, out_proj."""
+        cfg, dev = self.cfg, self.device
+        E = cfg.num_experts
+        e0, e1 = self.ep_rank * (E // self.ep_world), (self.ep_rank + 1) * (E // self.ep_world)
+        f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
+        dense = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
+        fp8 = lambda t, name: Hb.FP8BlockLinear(t, dev, name)
+
+        def experts(t3):
+            n, k = t3.shape[1], t3.shape[2]
+            q = quantize(t3[e0:e1].reshape((e1 - e0) * n, k).float(), Fmt.FP8_BLOCK)
+            return q.payload.reshape(e1 - e0, n, k).to(dev).contiguous(), q.scales.reshape(e1 - e0, n, k // 128).float().to(dev).contiguous()
+
+        gu8, gus = experts(w["gate_up"])
+        dn8, dns = experts(w["down"])
+        sg = w.get("shared_gate")
+        router = torch.cat([dense(w["router"]), dense(sg) if sg is not None else torch.zeros(1, cfg.hidden_size)], dim=0)
+        shared_gu = torch.cat([dense(w["shared_gate_proj"]), dense(w["shared_up_proj"])], dim=0)
+        moe = MoEBlock(BF16Linear(router, dev, f"L{i}.router"), gu8, gus, dn8, dns, fp8(shared_gu, f"L{i}.shared_gu"),
+                       fp8(w["shared_down_proj"], f"L{i}.shared_down"))
+        if cfg.is_attention_layer(i):
+            qkv = torch.cat([dense(w["q"]), dense(w["k"]), dense(w["v"])], dim=0)
+            L = HybridLayer("attn", f32(w["in_norm"]), f32(w["post_norm"]), moe, qkv=fp8(qkv, f"L{i}.qkv"), o=fp8(w["o"], f"L{i}.o"),
+                            q_norm=f32(w.get("q_norm")), k_norm=f32(w.get("k_norm")),
+                            kv_index=sum(1 for l in self.layers if l.kind == "attn"))
+        else:
+            ab = torch.cat([dense(w["in_a"]), dense(w["in_b"])], dim=0)
+            L = HybridLayer("gdn", f32(w["in_norm"]), f32(w["post_norm"]), moe, in_qkv=fp8(w["in_qkv"], f"L{i}.in_qkv"),
+                            in_z=fp8(w["in_z"], f"L{i}.in_z"), in_ab=BF16Linear(ab, dev, f"L{i}.in_ab"),
+                            conv_w=f32(w["conv"].reshape(self.gdn_channels, -1)), A_log=f32(w["A_log"]), dt_bias=f32(w["dt_bias"]),
+                            gdn_norm=f32(w["gdn_norm"]), out_proj=fp8(w["out_proj"], f"L{i}.out_proj"),
+                            state_index=sum(1 for l in self.layers if l.kind == "gdn"))
+        self.layers.append(L)
+
+    @staticmethod
+    def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1) -> "HybridModel":
+        """Load a HF directory of the hybrid family.  Tensor names follow the reference's resolver
+        (src/qwen35_loader.cpp:1149-1169 ``linear_attn.{in_proj_qkv,in_proj_z,in_proj_a,in_proj_b,conv1d,A_log,dt_bias,norm,
+        out_proj}``, :1320-1380 ``mlp.gate``, ``mlp.shared_expert*``, per-expert ``mlp.experts.N.*`` or the fused
+        ``mlp.experts.gate_up_proj`` [E][2I][H] / ``mlp.experts.down_proj`` [E][H][I]); projections are served as
+        block-scaled fp8, the a / b gates and the router stay bf16 (keep_qwen_bf16, :129-159)."""
+        from ..formats.checkpoint import Checkpoint
+
+        ck = Checkpoint(path) if isinstance(path, (str, bytes)) or hasattr(path, "__fspath__") else path    # or any tensor resolver
+        cfg = ck.cfg
+        if not cfg.is_moe or cfg.num_experts % ep_world:
+            raise ValueError("from_checkpoint: not a hybrid MoE configuration or experts do not split over the ranks")
+        m = HybridModel(cfg, device, max_slots=max_slots)
+        m.ep_rank, m.ep_world = ep_rank, ep_world
+        E = cfg.num_experts
+
+        def need(v, name):
+            if v is None:
+                raise KeyError(f"checkpoint has no tensor for {name}")
+            return v
+
+        for i in range(cfg.num_hidden_layers):
+            p = f"{ck.prefix}layers.{i}."
+            lin = lambda k: need(ck.linear(p + k), p + k)
+            w = {"in_norm": need(ck.plain(p + "input_layernorm.weight"), p + "input_layernorm"),
+                 "post_norm": need(ck.plain(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm"),
+                 "router": lin("mlp.gate"), "shared_gate": ck.linear(p + "mlp.shared_expert_gate"),
+                 "shared_gate_proj": lin("mlp.shared_expert.gate_proj"), "shared_up_proj": lin("mlp.shared_expert.up_proj"),
+                 "shared_down_proj": lin("mlp.shared_expert.down_proj")}
+            fused_gu, fused_dn = ck.tensor(p + "mlp.experts.gate_up_proj"), ck.tensor(p + "mlp.experts.down_proj")
+            dq = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
+            if fused_gu is not None and fused_dn is not None:
+                w["gate_up"], w["down"] = fused_gu.float(), fused_dn.float()
+            else:
+                gu, dn = [], []
+                for e in range(E):
+                    x = f"mlp.experts.{e}."
+                    gu.append(torch.cat([dq(lin(x + "gate_proj")), dq(lin(x + "up_proj"))], dim=0))
+                    dn.append(dq(lin(x + "down_proj")))
+                w["gate_up"], w["down"] = torch.stack(gu), torch.stack(dn)
+            if cfg.is_attention_layer(i):
+                a = "self_attn."
+                w.update(q=lin(a + "q_proj"), k=lin(a + "k_proj"), v=lin(a + "v_proj"), o=lin(a + "o_proj"),
+                         q_norm=ck.plain(p + a + "q_norm.weight"), k_norm=ck.plain(p + a + "k_norm.weight"))
+            else:
+                a = "linear_attn."
+                w.update(in_qkv=lin(a + "in_proj_qkv"), in_z=lin(a + "in_proj_z"), in_a=lin(a + "in_proj_a"), in_b=lin(a + "in_proj_b"),
+                         conv=need(ck.plain(p + a + "conv1d.weight"), p + a + "conv1d"), A_log=need(ck.plain(p + a + "A_log"), "A_log"),
+                         dt_bias=need(ck.plain(p + a + "dt_bias"), "dt_bias"), gdn_norm=need(ck.plain(p + a + "norm.weight"), "norm"),
+                         out_proj=lin(a + "out_proj"))
+            m._add_layer(i, w)
+        m.embed = ck.embedding().to(device=m.device, dtype=torch.bfloat16).contiguous()
+        m.final_norm = need(ck.plain(ck.prefix + "norm.weight"), "norm.weight").to(m.device)
+        head = ck.linear("lm_head")
+        m.lm_head = Hb.FP8BlockLinear(head if head is not None else ck.embedding(), m.device, "lm_head")
         return m
 
     def weight_bytes(self) -> int:

@@ -55,6 +55,38 @@ class MtpHead:
         return self
 
     @staticmethod
+    def from_checkpoint(target: DenseModel, ck, draft_vocab: int = 0) -> "MtpHead":
+        """The checkpoint's own draft head: ``mtp.fc.weight`` [H][2H], ``mtp.pre_fc_norm_embedding`` / ``_hidden`` /
+        ``mtp.norm`` and the decoder layer ``mtp.layers.0.*`` (src/grimoire.cpp:8603-8618).  ``ck`` resolves tensors
+        (formats.checkpoint.Checkpoint or the artifact adapter).  ``draft_vocab`` > 0 drafts over the first rows of the
+        target's lm_head only (GRIMOIRE_MTP_DRAFT_VOCAB, :15920-15960)."""
+        head = MtpHead(target, draft_vocab)
+        p = "mtp.layers.0."
+
+        def need(v, name):
+            if v is None:
+                raise KeyError(f"checkpoint has no {name}")
+            return v
+
+        lin = lambda k: need(ck.linear(p + k), p + k)
+        lw = dict(wq=lin("self_attn.q_proj"), wk=lin("self_attn.k_proj"), wv=lin("self_attn.v_proj"), wo=lin("self_attn.o_proj"),
+                  wg=lin("mlp.gate_proj"), wu=lin("mlp.up_proj"), wd=lin("mlp.down_proj"),
+                  in_norm=need(ck.plain(p + "input_layernorm.weight"), p + "input_layernorm"),
+                  post_norm=need(ck.plain(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm"),
+                  q_norm=ck.plain(p + "self_attn.q_norm.weight"), k_norm=ck.plain(p + "self_attn.k_norm.weight"))
+        fc = need(ck.linear("mtp.fc"), "mtp.fc.weight")
+        fc = fc.dequant() if hasattr(fc, "dequant") else fc
+        head_w = None
+        cfg = target.cfg
+        if draft_vocab and 0 < draft_vocab < cfg.vocab_size:
+            hw = ck.linear("lm_head") if not cfg.tie_word_embeddings else None
+            hw = ck.embedding() if hw is None else (hw.dequant() if hasattr(hw, "dequant") else hw)
+            head_w = hw[:draft_vocab].contiguous()
+        return head.load(fc, need(ck.plain("mtp.pre_fc_norm_embedding.weight"), "mtp.pre_fc_norm_embedding"),
+                         need(ck.plain("mtp.pre_fc_norm_hidden.weight"), "mtp.pre_fc_norm_hidden"),
+                         need(ck.plain("mtp.norm.weight"), "mtp.norm"), lw, head_w)
+
+    @staticmethod
     def random_from_target(target: DenseModel, seed: int = 0, noise: float = 0.01, draft_vocab: int = 0, std: float = 0.02,
                            gen_device=None) -> "MtpHead":
         """Synthetic head: the layer is the target's final layer (re-drawn from the same seeds as

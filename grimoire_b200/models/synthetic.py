@@ -37,3 +37,76 @@ def random_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02, device
         sd[p + "mlp.up_proj.weight"] = rnd(cfg.intermediate_size, H)
         sd[p + "mlp.down_proj.weight"] = rnd(H, cfg.intermediate_size)
     return sd
+
+
+def random_hybrid_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02, fused_experts: bool = False,
+                             mtp: bool = False) -> dict[str, torch.Tensor]:
+    """fp32 logical weights of a hybrid (Gated DeltaNet + gated attention, MoE FFN) decoder under the tensor names the
+    reference's loader resolves (src/qwen35_loader.cpp:1149-1169, :1320-1380): ``linear_attn.*`` with ``conv1d.weight``
+    as [C][1][K], ``mlp.gate`` (router), ``mlp.shared_expert*`` and either per-expert ``mlp.experts.N.*_proj`` or the fused
+    ``mlp.experts.gate_up_proj`` / ``down_proj``."""
+    g = torch.Generator().manual_seed(seed)
+    H, D = cfg.hidden_size, cfg.head_dim
+    E, I, Is = cfg.num_experts, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    C = 2 * Hk * Dk + Hv * Dv
+
+    def rnd(*shape, scale=std):
+        return torch.randn(*shape, generator=g, dtype=torch.float32) * scale
+
+    nw = (lambda n: rnd(n, scale=0.05)) if cfg.norm_zero_centered else (lambda n: 1.0 + rnd(n, scale=0.05))
+    sd = {"model.embed_tokens.weight": rnd(cfg.vocab_size, H), "model.norm.weight": nw(H)}
+    if not cfg.tie_word_embeddings:
+        sd["lm_head.weight"] = rnd(cfg.vocab_size, H)
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        sd[p + "input_layernorm.weight"], sd[p + "post_attention_layernorm.weight"] = nw(H), nw(H)
+        if cfg.is_attention_layer(i):
+            a = p + "self_attn."
+            sd[a + "q_proj.weight"] = rnd(cfg.q_size, H)
+            sd[a + "k_proj.weight"], sd[a + "v_proj.weight"] = rnd(cfg.kv_size, H), rnd(cfg.kv_size, H)
+            sd[a + "o_proj.weight"] = rnd(H, cfg.num_attention_heads * D)
+            if cfg.qk_norm:
+                sd[a + "q_norm.weight"], sd[a + "k_norm.weight"] = nw(D), nw(D)
+        else:
+            a = p + "linear_attn."
+            sd[a + "in_proj_qkv.weight"], sd[a + "in_proj_z.weight"] = rnd(C, H), rnd(Hv * Dv, H)
+            sd[a + "in_proj_a.weight"], sd[a + "in_proj_b.weight"] = rnd(Hv, H, scale=0.2), rnd(Hv, H, scale=0.2)
+            sd[a + "conv1d.weight"] = rnd(C, 1, cfg.linear_conv_kernel_dim, scale=0.4)
+            sd[a + "A_log"], sd[a + "dt_bias"] = rnd(Hv, scale=0.5), rnd(Hv, scale=0.5)
+            sd[a + "norm.weight"] = 1.0 + rnd(Dv, scale=0.05)
+            sd[a + "out_proj.weight"] = rnd(H, Hv * Dv)
+        m = p + "mlp."
+        sd[m + "gate.weight"] = rnd(E, H, scale=0.5)
+        sd[m + "shared_expert_gate.weight"] = rnd(1, H, scale=0.5)
+        sd[m + "shared_expert.gate_proj.weight"], sd[m + "shared_expert.up_proj.weight"] = rnd(Is, H), rnd(Is, H)
+        sd[m + "shared_expert.down_proj.weight"] = rnd(H, Is)
+        gu, dn = rnd(E, 2 * I, H), rnd(E, H, I)
+        if fused_experts:
+            sd[m + "experts.gate_up_proj"], sd[m + "experts.down_proj"] = gu, dn
+        else:
+            for e in range(E):
+                x = m + f"experts.{e}."
+                sd[x + "gate_proj.weight"], sd[x + "up_proj.weight"], sd[x + "down_proj.weight"] = gu[e, :I], gu[e, I:], dn[e]
+    return sd
+
+
+def random_mtp_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """The dense family's one-layer multi-token-prediction head under its checkpoint names (``mtp.fc`` [H][2H], the three
+    norms, ``mtp.layers.0.*``; src/grimoire.cpp:8603-8618)."""
+    g = torch.Generator().manual_seed(seed + 4242)
+    H, D = cfg.hidden_size, cfg.head_dim
+    rnd = lambda *shape: torch.randn(*shape, generator=g, dtype=torch.float32) * std
+    nw = (lambda n: torch.zeros(n)) if cfg.norm_zero_centered else (lambda n: torch.ones(n))
+    sd = {"mtp.fc.weight": rnd(H, 2 * H) + torch.cat([torch.eye(H), torch.eye(H)], dim=1) * 0.5,
+          "mtp.pre_fc_norm_hidden.weight": nw(H), "mtp.pre_fc_norm_embedding.weight": nw(H), "mtp.norm.weight": nw(H)}
+    p = "mtp.layers.0."
+    sd[p + "input_layernorm.weight"], sd[p + "post_attention_layernorm.weight"] = nw(H), nw(H)
+    sd[p + "self_attn.q_proj.weight"] = rnd(cfg.q_size, H)
+    sd[p + "self_attn.k_proj.weight"], sd[p + "self_attn.v_proj.weight"] = rnd(cfg.kv_size, H), rnd(cfg.kv_size, H)
+    sd[p + "self_attn.o_proj.weight"] = rnd(H, cfg.num_attention_heads * D)
+    if cfg.qk_norm:
+        sd[p + "self_attn.q_norm.weight"], sd[p + "self_attn.k_norm.weight"] = nw(D), nw(D)
+    sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = rnd(cfg.intermediate_size, H), rnd(cfg.intermediate_size, H)
+    sd[p + "mlp.down_proj.weight"] = rnd(H, cfg.intermediate_size)
+    return sd

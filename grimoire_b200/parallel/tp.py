@@ -80,6 +80,9 @@ class TensorParallel:
             self.gemv_off = 2 * self.world * tiles * nv_max
             self.recv = SymmetricBuffer(self.gemv_off + 2 * self.world * tiles * 32, torch.float32, self.group, self.device)
             self.flags = SymmetricBuffer(tiles * self.world, torch.int32, self.group, self.device)
+            # exchange regions of the persistent decode kernel (ops/mega.py): [2][world][rows] {value, epoch} pairs
+            self.mega_rows = (H + 31) // 32 * 32
+            self.mega_recv = SymmetricBuffer(2 * self.world * self.mega_rows * 2, torch.float32, self.group, self.device)
         except Exception as e:  # pragma: no cover - depends on the driver / fabric
             raise RuntimeError(f"symmetric peer memory is unavailable ({e}); set GRIMOIRE_TP_FUSED=0 to run the "
                                f"NCCL-only baseline") from e

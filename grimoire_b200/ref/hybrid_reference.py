@@ -1,0 +1,79 @@
+"""fp32 whole-model oracle of the hybrid (Gated DeltaNet + gated attention, MoE FFN) decoder, written against the HF
+tensor names: one sequence, all positions at once for attention, token by token for the recurrence.  It is the
+host-side counterpart of the reference engine's model-matrix gate (tools/test_model_matrix.cpp) and of its per-family
+forward (src/grimoire.cpp:15105-15453); ``HybridModel`` must agree with it up to its weight / KV quantisation."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from ..models.config import ModelConfig
+from . import gdn_ref, moe_ref
+from ..ops import ref
+
+
+def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.Tensor:
+    """Logits [T][V] for ``tokens`` from the state dict ``sd`` (names as in models/synthetic.py).  ``weight_fn`` maps every
+    projection matrix before use (pass a quantise-dequantise round trip to compare like with like)."""
+    wf = weight_fn or (lambda w: w.float())
+    pfx = "model.language_model." if any(k.startswith("model.language_model.") for k in sd) else "model."
+    eps, off = cfg.rms_norm_eps, cfg.norm_offset
+    H, D, Hq, Hkv = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    T = len(tokens)
+    pos = torch.arange(T)
+    inv_freq = ref.rope_inv_freq(cfg.rot_dim, cfg.rope_theta)
+    scale = cfg.softmax_scale or ref.softmax_scale(D)
+    h = sd[pfx + "embed_tokens.weight"].bfloat16().float()[torch.tensor(tokens, dtype=torch.long)]
+    bf = lambda t: t.bfloat16().float()
+    for i in range(cfg.num_hidden_layers):
+        p = f"{pfx}layers.{i}."
+        x = bf(ref.rmsnorm(h, sd[p + "input_layernorm.weight"].float(), eps, off))
+        if cfg.is_attention_layer(i):
+            a = p + "self_attn."
+            qg = (x @ wf(sd[a + "q_proj.weight"]).t()).reshape(T, Hq, 2 * D)
+            q, gate = qg[..., :D], qg[..., D:].reshape(T, Hq * D)
+            k = (x @ wf(sd[a + "k_proj.weight"]).t()).reshape(T, Hkv, D)
+            v = (x @ wf(sd[a + "v_proj.weight"]).t()).reshape(T, Hkv, D)
+            qn, kn = sd.get(a + "q_norm.weight"), sd.get(a + "k_norm.weight")
+            q = ref.apply_rope(ref.head_rmsnorm(bf(q), None if qn is None else qn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
+            k = ref.apply_rope(ref.head_rmsnorm(bf(k), None if kn is None else kn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
+            o = ref.attention_rows(q, k, bf(v), pos, scale, cfg.sliding_window).reshape(T, Hq * D)
+            o = o * torch.sigmoid(bf(gate))
+            h = h + bf(o) @ wf(sd[a + "o_proj.weight"]).t()
+        else:
+            a = p + "linear_attn."
+            qkv = bf(x @ wf(sd[a + "in_proj_qkv.weight"]).t())
+            z = bf(x @ wf(sd[a + "in_proj_z.weight"]).t()).reshape(T, Hv, Dv)
+            ar = x @ bf(sd[a + "in_proj_a.weight"]).t()
+            br = x @ bf(sd[a + "in_proj_b.weight"]).t()
+            conv, _ = gdn_ref.conv4_silu(qkv, sd[a + "conv1d.weight"].float().reshape(qkv.shape[1], -1), torch.zeros(qkv.shape[1], 3))
+            conv = bf(conv)
+            qk, kk = Hk * Dk, 2 * Hk * Dk
+            q = gdn_ref.l2norm(conv[:, :qk].reshape(T, Hk, Dk))
+            k = gdn_ref.l2norm(conv[:, qk:kk].reshape(T, Hk, Dk))
+            v = conv[:, kk:].reshape(T, Hv, Dv)
+            al, be = gdn_ref.gates(ar, br, sd[a + "A_log"], sd[a + "dt_bias"])
+            S = torch.zeros(Hv, Dv, Dk)
+            o = gdn_ref.gdn_sequence(S, q, k, v, al, be)
+            o = bf(gdn_ref.gated_rmsnorm(o, z, sd[a + "norm.weight"], eps)).reshape(T, Hv * Dv)
+            h = h + o @ wf(sd[a + "out_proj.weight"]).t()
+        x = bf(ref.rmsnorm(h, sd[p + "post_attention_layernorm.weight"].float(), eps, off))
+        m = p + "mlp."
+        E, I = cfg.num_experts, cfg.moe_intermediate_size
+        if m + "experts.gate_up_proj" in sd:
+            gu, dn = sd[m + "experts.gate_up_proj"], sd[m + "experts.down_proj"]
+            experts = [(wf(gu[e, :I]), wf(gu[e, I:]), wf(dn[e])) for e in range(E)]
+        else:
+            experts = [(wf(sd[f"{m}experts.{e}.gate_proj.weight"]), wf(sd[f"{m}experts.{e}.up_proj.weight"]),
+                        wf(sd[f"{m}experts.{e}.down_proj.weight"])) for e in range(E)]
+        shared = (wf(sd[m + "shared_expert.gate_proj.weight"]), wf(sd[m + "shared_expert.up_proj.weight"]),
+                  wf(sd[m + "shared_expert.down_proj.weight"]))
+        y, _, _ = moe_ref.moe_forward(x, bf(sd[m + "gate.weight"]), experts, cfg.num_experts_per_tok, shared,
+                                      bf(sd[m + "shared_expert_gate.weight"]), cfg.norm_topk_prob)
+        h = h + y
+    xf = bf(ref.rmsnorm(h, sd[pfx + "norm.weight"].float(), eps, off))
+    head = sd.get("lm_head.weight", sd[pfx + "embed_tokens.weight"])
+    return xf @ wf(head).t()

@@ -23,6 +23,7 @@ import torch
 
 from .. import _native
 from ..engine.generation import CopyDrafter, FinishReason, SpecStats, first_token_of
+from ..engine.kv import OutOfPages
 from ..engine.sampling import SamplingOptions, sample_ref
 
 PLAN_ADMIT, PLAN_STEP, PLAN_WAIT = 1, 2, 4
@@ -166,6 +167,13 @@ class Scheduler:
             return False
         return True
 
+    def _fail(self, job: SchedJob, err: Exception) -> None:
+        """End one request with an error; the scheduler core retires it on the next plan."""
+        self.metrics["errors"] += 1
+        job.finish = FinishReason.ERROR
+        self.lib.grm_sched_on_tokens(self.h, ctypes.c_int64(job.id), 0, 1)
+        job.q.put(err)
+
     def _pick(self, job: SchedJob, logits: torch.Tensor, position: int) -> int:
         if job.sampling.greedy:
             return first_token_of(logits)
@@ -260,7 +268,7 @@ class Scheduler:
         if not live:
             return
         depth = plan.draft_depth if self.drafter is not None else 0
-        tokens, seqs, positions, spans = [], [], [], []
+        tokens, seqs, positions, spans, stepped = [], [], [], [], []
         for job in live:
             drafts = []
             if depth > 0 and job.sampling.greedy:
@@ -270,10 +278,23 @@ class Scheduler:
                     drafts = list(self.drafter.propose(eng, job.seq, job.next_token, d))[:d]
             block = [job.next_token] + drafts
             pos0 = job.seq.length
+            kv = getattr(eng, "kv", None)
+            if kv is not None:
+                # map the pages of this job's rows now: a pool that stays short after evicting cached prefixes fails
+                # this request only, the others keep decoding
+                try:
+                    kv.ensure(job.seq, pos0 + len(block))
+                except OutOfPages as e:
+                    self._fail(job, e)
+                    continue
             spans.append((len(tokens), len(block)))
+            stepped.append(job)
             tokens += block
             seqs += [job.seq] * len(block)
             positions += list(range(pos0, pos0 + len(block)))
+        live = stepped
+        if not live:
+            return
         need_logits = any(not j.sampling.greedy for j in live)
         res = eng.decode_rows(tokens, seqs, positions, use_graph=self.use_graph, return_logits=need_logits)
         chosen, logits = (res if need_logits else (res, None))

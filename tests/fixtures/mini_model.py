@@ -13,14 +13,17 @@ from grimoire_b200.formats.codecs import Fmt
 from grimoire_b200.formats.quantize import quantize
 from grimoire_b200.formats.safetensors_io import save_file
 from grimoire_b200.models.config import ModelConfig
-from grimoire_b200.models.synthetic import random_state_dict
+from grimoire_b200.models.synthetic import random_hybrid_state_dict, random_mtp_state_dict, random_state_dict
 
 _PROJ = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
 
 
-def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "bf16", tokenizer: bool = False, shards: int = 1):
+def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "bf16", tokenizer: bool = False, shards: int = 1,
+                     mtp: bool = False):
     path.mkdir(parents=True, exist_ok=True)
     sd = random_state_dict(cfg, seed)
+    if mtp:
+        sd.update(random_mtp_state_dict(cfg, seed))
     out = {}
     for name, w in sd.items():
         is_proj = any(name.endswith(p + ".weight") for p in _PROJ)
@@ -36,7 +39,7 @@ def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "
           "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads,
           "head_dim": cfg.head_dim, "vocab_size": cfg.vocab_size, "intermediate_size": cfg.intermediate_size,
           "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta, "tie_word_embeddings": cfg.tie_word_embeddings,
-          "qk_norm": cfg.qk_norm}
+          "qk_norm": cfg.qk_norm, "mtp_num_hidden_layers": 1 if mtp else 0}
     if quant == "gptq":
         hf["quantization_config"] = {"quant_method": "gptq", "bits": 4, "group_size": cfg.quant_group, "sym": False}
     (path / "config.json").write_text(json.dumps(hf))
@@ -53,6 +56,25 @@ def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "
         (path / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": wm}))
     if tokenizer:
         write_tokenizer(path, cfg.vocab_size)
+    return sd
+
+
+def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_experts: bool = False):
+    """A hybrid (Gated DeltaNet + gated attention + MoE) checkpoint under the HF names of that family."""
+    path.mkdir(parents=True, exist_ok=True)
+    sd = random_hybrid_state_dict(cfg, seed, fused_experts=fused_experts)
+    hf = {"model_type": cfg.model_type, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
+          "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+          "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
+          "partial_rotary_factor": cfg.partial_rotary_factor, "tie_word_embeddings": cfg.tie_word_embeddings,
+          "layer_types": ["linear_attention" if t != "full_attention" else "full_attention" for t in cfg.layer_types],
+          "linear_num_key_heads": cfg.linear_num_key_heads, "linear_num_value_heads": cfg.linear_num_value_heads,
+          "linear_key_head_dim": cfg.linear_key_head_dim, "linear_value_head_dim": cfg.linear_value_head_dim,
+          "linear_conv_kernel_dim": cfg.linear_conv_kernel_dim, "num_experts": cfg.num_experts,
+          "num_experts_per_tok": cfg.num_experts_per_tok, "moe_intermediate_size": cfg.moe_intermediate_size,
+          "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob}
+    (path / "config.json").write_text(json.dumps(hf))
+    save_file({k: v.bfloat16() for k, v in sd.items()}, path / "model.safetensors", {"format": "pt"})
     return sd
 
 

@@ -1,0 +1,145 @@
+"""Every way a model reaches the engine through ``Grimoire.load``: synthetic presets of both families, HF checkpoints of
+the hybrid family (per-expert and fused expert tensors) checked against the fp32 whole-model oracle, the checkpoint's
+MTP draft head, and the pre-quantised artifact round trip (CPU path; the reference's counterpart is the model-matrix
+gate, tools/test_model_matrix.cpp, over tools/mini_model.hpp fixtures)."""
+import dataclasses
+
+import pytest
+import torch
+
+from grimoire_b200.api import Grimoire, UnsupportedModel
+from grimoire_b200.config import EngineConfig
+from grimoire_b200.formats.codecs import Fmt
+from grimoire_b200.formats.quantize import quantize
+from grimoire_b200.models.config import tiny_dense, tiny_hybrid_moe
+from grimoire_b200.models.hybrid import HybridModel
+from grimoire_b200.ref import hybrid_reference
+
+from .fixtures.mini_model import write_checkpoint, write_hybrid_checkpoint
+
+
+def _ec(model, **kw):
+    base = dict(model=str(model), ctx=192, seq_slots=4, prefill_chunk=64, prefix_cache=0, mtp=0, copy_drafts=0)
+    base.update(kw)
+    return EngineConfig(**base)
+
+
+def _prompt(n, seed=3, vocab=4096):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def test_synthetic_presets_dispatch_by_family():
+    g = Grimoire.load(_ec("synthetic:tiny_hybrid_moe"), device="cpu")
+    assert isinstance(g.model, HybridModel)
+    out, why = g.generate(_prompt(12), 5)
+    assert len(out) == 5
+    g.close()
+    g = Grimoire.load(_ec("synthetic:tiny_dense"), device="cpu")
+    assert not isinstance(g.model, HybridModel)
+    g.close()
+    with pytest.raises(UnsupportedModel):
+        Grimoire.load(_ec("synthetic:tiny_hybrid_moe", tp_world=2, tp_rank=0), device="cpu")
+
+
+@pytest.fixture(scope="module")
+def hybrid_dirs(tmp_path_factory):
+    cfg = tiny_hybrid_moe(4)
+    a, b = tmp_path_factory.mktemp("hyb_split"), tmp_path_factory.mktemp("hyb_fused")
+    sd = write_hybrid_checkpoint(a, cfg, seed=5, fused_experts=False)
+    write_hybrid_checkpoint(b, cfg, seed=5, fused_experts=True)
+    return cfg, sd, a, b
+
+
+def test_hybrid_checkpoint_matches_fp32_oracle(hybrid_dirs):
+    cfg, sd, split_dir, fused_dir = hybrid_dirs
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    assert isinstance(g.model, HybridModel) and len(g.model.layers) == 4
+    ids = _prompt(21, 9)
+    got = g.score_ids(ids)
+    # like with like: the oracle sees the same bf16 storage and block-fp8 round trip of every projection
+    q = lambda w: quantize(w.bfloat16().float(), Fmt.FP8_BLOCK).dequant().float()
+    want = hybrid_reference.forward_logits(cfg, {k: v.bfloat16().float() for k, v in sd.items()}, ids, weight_fn=q)
+    err = float((got - want).abs().max())
+    assert err < 0.06 * float(want.abs().max()), (err, float(want.abs().max()))
+    agree = (got.argmax(-1) == want.argmax(-1)).float().mean()
+    assert float(agree) >= 0.9
+    g2 = Grimoire.load(_ec(fused_dir), device="cpu")
+    got2 = g2.score_ids(ids)
+    assert torch.allclose(got, got2, atol=1e-5), float((got - got2).abs().max())
+    g.close(), g2.close()
+
+
+def test_hybrid_prefix_cache_restores_recurrent_state(hybrid_dirs):
+    _, _, split_dir, _ = hybrid_dirs
+    g = Grimoire.load(_ec(split_dir, prefix_cache=1), device="cpu")
+    eng = g.engine
+    p1 = _prompt(37, 21)
+    s = eng.open()
+    lg = eng.prefill(s, p1)
+    first = int(lg.argmax())
+    eng.release(s, cache=True)
+    # a prompt that extends the cached conversation resumes from its KV pages AND its DeltaNet / conv state
+    p2 = p1 + [first] + _prompt(9, 22)
+    s2 = eng.open()
+    n = eng.prefix_reuse(s2, p2)
+    assert n == len(p1)
+    a = eng.prefill(s2, p2[n:]).clone()
+    eng.release(s2)
+    eng.prefix_cache.entries.clear()
+    s3 = eng.open()
+    assert eng.prefix_reuse(s3, p2) == 0
+    b = eng.prefill(s3, p2).clone()
+    eng.release(s3)
+    assert int(a.argmax()) == int(b.argmax()) and float((a - b).abs().max()) < 0.05 * max(1.0, float(b.abs().max()))
+    # a prompt that diverges inside the cached entry cannot use its end-of-sequence state
+    s4 = eng.open()
+    s5 = eng.open()
+    eng.prefill(s4, p1)
+    eng.release(s4, cache=True)
+    assert eng.prefix_reuse(s5, p1[:20] + _prompt(10, 23)) == 0
+    eng.release(s5)
+    g.close()
+
+
+def test_mtp_head_from_checkpoint_drafts_and_keeps_greedy(tmp_path):
+    cfg = dataclasses.replace(tiny_dense(), tie_word_embeddings=False)
+    write_checkpoint(tmp_path, cfg, seed=2, mtp=True)
+    plain = Grimoire.load(_ec(tmp_path), device="cpu")
+    assert plain.drafter is None
+    ids = _prompt(30, 4)
+    want, _ = plain.generate(ids, 16)
+    plain.close()
+    g = Grimoire.load(_ec(tmp_path, mtp=1), device="cpu")
+    assert g.drafter is not None and len(g.engine.kv.layers) == cfg.num_hidden_layers + 1
+    from grimoire_b200.engine.generation import SpecStats
+
+    st = SpecStats()
+    got, _ = g.generate(ids, 16, draft_depth=3, stats=st)
+    assert got == want and st.rounds > 0 and st.drafted > 0
+    out, why, job = g.scheduler().generate(ids, 16)
+    assert out == want
+    g.close()
+
+
+def test_artifact_round_trip_serves_same_logits(tmp_path):
+    from grimoire_b200.formats.artifact import quantize_checkpoint
+
+    cfg = dataclasses.replace(tiny_dense(), tie_word_embeddings=False)
+    src = tmp_path / "src"
+    write_checkpoint(src, cfg, seed=7, tokenizer=False, mtp=True)
+    out = tmp_path / "bundle"
+    stats = quantize_checkpoint(src, out, Fmt.INT4, policy="linear", bundle=True)
+    assert stats["quantized"] > 0 and (out / "model-v3.grm").exists() and (out / "config.json").exists()
+    ids = _prompt(17, 8)
+    a = Grimoire.load(_ec(src), device="cpu")
+    la = a.score_ids(ids)
+    a.close()
+    b = Grimoire.load(_ec(out), device="cpu")                       # the bundle directory
+    lb = b.score_ids(ids)
+    b.close()
+    c = Grimoire.load(_ec(out / "model-v3.grm", mtp=1), device="cpu")   # the file itself, with its draft head
+    assert c.drafter is not None
+    lc = c.score_ids(ids)
+    c.close()
+    assert torch.allclose(la, lb, atol=1e-4), float((la - lb).abs().max())
+    assert torch.allclose(lb, lc, atol=1e-6)
