@@ -299,7 +299,12 @@ void* grm_gguf_open(const char* path, char* err, int cap) {
     f->meta_json += "\"" + grm::json_escape(key) + "\":";
     const uint8_t* before = r.p;
     if (!value_json(r, vt, f->meta_json)) return fail("bad metadata value for " + key);
-    if (key == "general.alignment" && vt == 4) { uint32_t a; std::memcpy(&a, before, 4); if (a) alignment = a; }
+    if (key == "general.alignment" && vt == 4) {
+      uint32_t a; std::memcpy(&a, before, 4);
+      // a power of two no larger than a page: anything else is a damaged or hostile header
+      if (a == 0 || a > 4096 || (a & (a - 1))) return fail("general.alignment must be a power of two <= 4096");
+      alignment = a;
+    }
   }
   f->meta_json += "}";
   for (uint64_t i = 0; i < n_tensors; ++i) {
@@ -308,18 +313,25 @@ void* grm_gguf_open(const char* path, char* err, int cap) {
     const uint32_t nd = r.get<uint32_t>();
     if (!r.ok || nd > 8) return fail("bad tensor record");
     uint64_t ne = 1;
-    for (uint32_t d = 0; d < nd; ++d) { t.dims.push_back(r.get<uint64_t>()); ne *= t.dims.back(); }
+    bool overflow = false;
+    for (uint32_t d = 0; d < nd; ++d) {
+      t.dims.push_back(r.get<uint64_t>());
+      overflow = overflow || __builtin_mul_overflow(ne, t.dims.back(), &ne);
+    }
+    if (overflow) return fail("tensor element count overflows: " + t.name);
     t.type = (int)r.get<uint32_t>();
     t.offset = r.get<uint64_t>();
     const TypeInfo* ti = type_info(t.type);
     if (!r.ok || !ti || ne % ti->elems) return fail("bad tensor type/shape for " + t.name);
-    t.nbytes = ne / ti->elems * ti->size;
+    if (__builtin_mul_overflow(ne / ti->elems, (uint64_t)ti->size, &t.nbytes)) return fail("tensor size overflows: " + t.name);
     f->tensors.push_back(std::move(t));
   }
   const uint64_t pos = (uint64_t)(r.p - f->map);
   f->data_start = (pos + alignment - 1) / alignment * alignment;
-  for (auto& t : f->tensors)
-    if (f->data_start + t.offset + t.nbytes > f->size) return fail("tensor data out of range: " + t.name);
+  if (f->data_start > f->size) return fail("tensor data section starts past the end of the file");
+  const uint64_t room = f->size - f->data_start;
+  for (auto& t : f->tensors)      // subtraction form: neither side can wrap
+    if (t.offset > room || t.nbytes > room - t.offset) return fail("tensor data out of range: " + t.name);
   return f;
 }
 

@@ -120,6 +120,21 @@ bool parse_header(StFile& f) {
     if (!ps.eat('}')) { f.error = "unterminated entry " + key; return false; }
     const int64_t data_len = (int64_t)f.size - 8 - (int64_t)f.header_len;
     if (t.begin < 0 || t.end < t.begin || t.end > data_len) { f.error = "data offsets out of range: " + key; return false; }
+    // the byte range must be exactly shape x element size (a mismatch would otherwise surface as a reshape error, or as a
+    // read past the tensor when a caller trusts the shape)
+    {
+      static const struct { const char* n; int64_t b; } kDt[] = {{"F64", 8}, {"F32", 4}, {"F16", 2}, {"BF16", 2}, {"I64", 8}, {"I32", 4},
+                                                               {"I16", 2}, {"I8", 1}, {"U8", 1}, {"BOOL", 1}, {"F8_E4M3", 1}, {"F8_E5M2", 1},
+                                                               {"U16", 2}, {"U32", 4}, {"U64", 8}, {"F8_E8M0", 1}};
+      int64_t esz = 0;
+      for (const auto& d : kDt) if (t.dtype == d.n) esz = d.b;
+      if (esz) {
+        int64_t n = esz;
+        bool bad = false;
+        for (int64_t d : t.shape) bad = bad || d < 0 || __builtin_mul_overflow(n, d, &n);
+        if (bad || n != t.end - t.begin) { f.error = "byte length does not match shape x dtype: " + key; return false; }
+      }
+    }
     f.tensors.push_back(std::move(t));
   } while (ps.eat(','));
   if (!ps.eat('}')) { f.error = "unterminated header"; return false; }

@@ -72,6 +72,7 @@ struct MegaParams {
   // optional timeline (null = off): [phase][CTA][5] SM clock values of thread 0 -- phase entered, grid barrier passed,
   // activations staged, last ring stage consumed, row pairs finalised
   long long* timeline;
+  int tune;                       // measurement switches (results become meaningless): 1 = skip the MMAs, 2 = skip the shared-memory reads too
 };
 
 struct Ctx {
@@ -490,7 +491,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
           uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0, xa = w0, xb = w0;
           uint32_t s00 = 0u, s01 = 0u, s10 = 0u, s11 = 0u;
           float xu = 0.f;
-          if (act) {
+          if (act && !(p.tune & 2)) {
             const uint8_t* sl = ring + (size_t)slot * kSlotBytes;
             w0 = *reinterpret_cast<const uint4*>(sl + u * 1024 + lane * 16);
             w1 = *reinterpret_cast<const uint4*>(sl + u * 1024 + 512 + lane * 16);
@@ -505,13 +506,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
           __syncwarp();
           if (lane == 0) mbar_arrive(empty + slot);     // the unit is in registers: the producer may refill the slot
           if (++slot == (uint32_t)S) { slot = 0; par ^= 1u; }
-          if (act) {
-            // two independent chains (tile 0, tile 1) of four MMAs each
+          if (act && !(p.tune & 1)) {
+            // eight independent MMAs (a legacy mma.sync result takes a few hundred cycles to come back on this part: a
+            // chain through one accumulator would serialise those latencies), summed per tile afterwards
+            float e0[4][4], e1[4][4];
+            mma_word<true>(e0[0], w0.x, xa.x, xa.y); mma_word<true>(e1[0], w1.x, xa.x, xa.y);
+            mma_word<true>(e0[1], w0.y, xa.z, xa.w); mma_word<true>(e1[1], w1.y, xa.z, xa.w);
+            mma_word<true>(e0[2], w0.z, xb.x, xb.y); mma_word<true>(e1[2], w1.z, xb.x, xb.y);
+            mma_word<true>(e0[3], w0.w, xb.z, xb.w); mma_word<true>(e1[3], w1.w, xb.z, xb.w);
             float d0[4], d1[4];
-            mma_word<true>(d0, w0.x, xa.x, xa.y); mma_word<true>(d1, w1.x, xa.x, xa.y);
-            mma_word<false>(d0, w0.y, xa.z, xa.w); mma_word<false>(d1, w1.y, xa.z, xa.w);
-            mma_word<false>(d0, w0.z, xb.x, xb.y); mma_word<false>(d1, w1.z, xb.x, xb.y);
-            mma_word<false>(d0, w0.w, xb.z, xb.w); mma_word<false>(d1, w1.w, xb.z, xb.w);
+            d0[0] = (e0[0][0] + e0[1][0]) + (e0[2][0] + e0[3][0]); d0[2] = (e0[0][2] + e0[1][2]) + (e0[2][2] + e0[3][2]);
+            d1[0] = (e1[0][0] + e1[1][0]) + (e1[2][0] + e1[3][0]); d1[2] = (e1[0][2] + e1[1][2]) + (e1[2][2] + e1[3][2]);
             fold_unit(d0, s00, s01, xu, f00, f01);
             fold_unit(d1, s10, s11, xu, f10, f11);
           }
@@ -532,6 +537,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
 }
 
 int g_mega_sms = 0;
+int g_mega_tune = 0;
 int g_mega_slot_cap = 0;       // tuning: fewer ring slots than fit (0 = all that fit)
 bool g_mega_configured = false;
 
@@ -551,6 +557,10 @@ GRM_API int grm_mega_phase_bytes() { return (int)sizeof(MegaPhase); }
 
 // Tuning knob: cap the number of ring slots per CTA (0 = as many as shared memory holds).
 GRM_API void grm_mega_set_slot_cap(int slots) { g_mega_slot_cap = slots; }
+
+// Measurement switches for profiling the pipeline (outputs are then meaningless): bit 0 skips the tensor-core math of
+// every stage, bit 1 also skips the shared-memory reads, leaving only the copy ring and its barriers.
+GRM_API void grm_mega_set_tune(int flags) { g_mega_tune = flags; }
 
 // CTAs of a launch (one per SM); 0 when no device is current.
 GRM_API int grm_mega_grid() { return mega_sms(); }
@@ -601,6 +611,7 @@ GRM_API int grm_decode_mega(const void* phases, int first, int count, const void
   for (int i = 0; i < 8; ++i) p.ar_recv[i] = (world > 1 && i < world) ? (float*)const_cast<void*>(recv[i]) : nullptr;
   p.ar_world = world > 1 ? world : 1; p.ar_rank = world > 1 ? rank : 0; p.ar_rows = ar_rows;
   p.timeline = (long long*)timeline;
+  p.tune = g_mega_tune;
   const size_t smem = (size_t)fixed + (size_t)p.nslots * kSlotBytes;
   if (!g_mega_configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);

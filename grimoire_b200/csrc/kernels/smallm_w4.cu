@@ -681,8 +681,20 @@ int launch_epi(const W4Params& p, int epi, cudaStream_t st) {
 }  // namespace
 
 namespace {
+// The instantiation the dispatcher picks for (M, epilogue, rows_per_cta): MT = 8-row batch tiles the kernel is built for
+// (1, 2, 4 or 8), R = 16-row weight tiles per CTA.  The scratch of a split-K launch is ksplit * (N / (16 R)) * R * MT * 128
+// floats and N / (16 R) counters; every entry point sizes it from this one function.
+struct SmallMShape { int MT, R; };
+inline SmallMShape smallm_shape(int M, int epi, int rows_per_cta) {
+  const int mt8 = (M + 7) / 8;
+  const int MT = mt8 <= 1 ? 1 : (mt8 <= 2 ? 2 : (mt8 <= 4 ? 4 : 8));
+  const int R = (epi == EPI_SWIGLU) ? 2 : ((rows_per_cta == 32 && MT <= 2) ? 2 : 1);
+  return {MT, R};
+}
+
 int dispatch(W4Params& p, int epi, int rows_per_cta, cudaStream_t st) {
-  const int MT = (p.M + 7) / 8;
+  const SmallMShape shp = smallm_shape(p.M, epi, rows_per_cta);
+  const int MT = shp.MT;
   {
     const int G = (p.K >> 6) / p.g64;
     const int cta_groups = G / p.ksplit;
@@ -694,7 +706,7 @@ int dispatch(W4Params& p, int epi, int rows_per_cta, cudaStream_t st) {
     if (MT <= 4) return launch<4, 2, EPI_SWIGLU>(p, st);
     return launch<8, 2, EPI_SWIGLU>(p, st);
   }
-  const bool r2 = rows_per_cta == 32;
+  const bool r2 = shp.R == 2;
   if (MT <= 1) return r2 ? launch_epi<1, 2>(p, epi, st) : launch_epi<1, 1>(p, epi, st);
   if (MT <= 2) return r2 ? launch_epi<2, 2>(p, epi, st) : launch_epi<2, 1>(p, epi, st);
   if (MT <= 4) return launch_epi<4, 1>(p, epi, st);
@@ -873,6 +885,8 @@ GRM_API int grm_smallm_mx_tiled(const void* w, const void* sz, const void* x16p,
 // grm_smallm_w4_noalloc: the split-K small-M product for callers that must not allocate.
 // Declared and documented in smallm_w4_noalloc.h.
 // ---------------------------------------------------------------------------------------------
+#include <mutex>
+
 #include "smallm_w4_noalloc.h"
 
 namespace {
@@ -883,27 +897,28 @@ static __device__ __align__(256) float g_noalloc_partials[GRM_NOALLOC_MAX_PARTIA
 static __device__ __align__(256) unsigned int g_noalloc_counters[GRM_NOALLOC_MAX_TILES];
 
 struct NoAllocDev {
-  float* partials;
-  unsigned int* counters;
-  bool ready;
+  float* partials = nullptr;
+  unsigned int* counters = nullptr;
+  int rc = 0;
+  std::once_flag once;
 };
 NoAllocDev g_noalloc_dev[64];
 
 // In host code the two array names above are only stand-ins; a kernel needs the device addresses,
 // which cudaGetSymbolAddress hands out for the device that is current at the time of the call.
+// Runs once per device ordinal, also when several host threads make their first call together.
 int noalloc_setup(int dev) {
   NoAllocDev& d = g_noalloc_dev[dev];
-  if (d.ready) return 0;
-  void* a = nullptr;
-  void* b = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(&a, g_noalloc_partials);
-  if (e != cudaSuccess) return (int)e;
-  e = cudaGetSymbolAddress(&b, g_noalloc_counters);
-  if (e != cudaSuccess) return (int)e;
-  d.partials = (float*)a;
-  d.counters = (unsigned int*)b;
-  d.ready = true;
-  return 0;
+  std::call_once(d.once, [&d]() {
+    void* a = nullptr;
+    void* b = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&a, g_noalloc_partials);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&b, g_noalloc_counters);
+    d.partials = (float*)a;
+    d.counters = (unsigned int*)b;
+    d.rc = (int)e;
+  });
+  return d.rc;
 }
 
 }  // namespace
@@ -914,13 +929,11 @@ GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, 
   if (epi < EPI_BF16 || epi > EPI_SWIGLU) return -1;
   const int G = K / group;
   if (ksplit < 1 || (G % ksplit)) return -2;
-  int mt = 1;
-  while (mt * 8 < M) mt *= 2;
-  // which row-tile width the dispatcher will pick (kept in step with dispatch() above)
-  const int R = (epi == EPI_SWIGLU) ? 2 : ((rows_per_cta == 32 && mt <= 2) ? 2 : 1);
-  const long tiles = N / (16 * R);
-  const long need = (long)ksplit * tiles * R * mt * 128;
-  if (tiles > GRM_NOALLOC_MAX_TILES || need > GRM_NOALLOC_MAX_PARTIAL_FLOATS) return GRM_NOALLOC_TOO_LARGE;
+  const SmallMShape shp = smallm_shape(M, epi, rows_per_cta);
+  const long tiles = N / (16 * shp.R);
+  const long need = (long)ksplit * tiles * shp.R * shp.MT * 128;
+  // a single K slice touches neither the partial sums nor the counters: no limit applies and nothing is cleared
+  if (ksplit > 1 && (tiles > GRM_NOALLOC_MAX_TILES || need > GRM_NOALLOC_MAX_PARTIAL_FLOATS)) return GRM_NOALLOC_TOO_LARGE;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -928,10 +941,12 @@ GRM_API int grm_smallm_w4_noalloc(const void* w, const void* sz, const void* x, 
   int rc = noalloc_setup(dev);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  // The counters are shared by every call and must start at zero; a previous call that was cut short
-  // could have left them otherwise, so they are cleared on the caller's stream each time.
-  e = cudaMemsetAsync(g_noalloc_dev[dev].counters, 0, sizeof(unsigned int) * (size_t)tiles, st);
-  if (e != cudaSuccess) return (int)e;
+  if (ksplit > 1) {
+    // The counters are shared by every call and must start at zero; a previous call that was cut short
+    // could have left them otherwise, so they are cleared on the caller's stream each time.
+    e = cudaMemsetAsync(g_noalloc_dev[dev].counters, 0, sizeof(unsigned int) * (size_t)tiles, st);
+    if (e != cudaSuccess) return (int)e;
+  }
   W4Params p;
   p.w = (const uint4*)w; p.sz = (const uint32_t*)sz; p.x = (const bf16*)x; p.out = out;
   p.scratch = g_noalloc_dev[dev].partials; p.counters = g_noalloc_dev[dev].counters;

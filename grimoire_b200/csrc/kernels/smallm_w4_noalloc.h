@@ -17,12 +17,15 @@
 // Contract.
 //  * Same arguments and results as grm_smallm_w4 minus the scratch / counters pointers; epi 0..3
 //    (bf16 store, fp32 store, fp32 accumulate, SwiGLU).  The caller still owns w, sz, x and out.
-//  * Problems whose scratch would not fit -- ksplit * (N / rows_per_cta) * rows_per_cta/16 *
-//    roundup_pow2(ceil(M/8)) * 128 floats, or more than GRM_NOALLOC_MAX_TILES row tiles -- are
-//    refused with GRM_NOALLOC_TOO_LARGE and nothing is launched.
+//  * Split-K problems (ksplit > 1) whose scratch would not fit -- ksplit * (N / rows_per_cta) *
+//    rows_per_cta/16 * roundup_pow2(ceil(M/8)) * 128 floats, or more than GRM_NOALLOC_MAX_TILES row
+//    tiles -- are refused with GRM_NOALLOC_TOO_LARGE and nothing is launched.  With ksplit == 1 the
+//    scratch is not touched and no size limit applies.
 //  * It calls no cudaMalloc, cudaFree or allocating library routine.  The first call on a device
 //    resolves the device addresses of the arrays (cudaGetSymbolAddress, with that device current);
-//    make that first call before starting any stream capture.
+//    make that first call before starting any stream capture.  That set-up is guarded (once per
+//    device ordinal), so host threads may make their first calls concurrently; the calls themselves
+//    still share the scratch, see the last point.
 //  * Every call on a device uses the same arrays.  The counters are cleared at the start of each
 //    call (on the caller's stream); the partial sums keep whatever the previous call left and are
 //    fully rewritten before they are read.  Two calls that overlap on the GPU (different streams

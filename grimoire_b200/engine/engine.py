@@ -44,6 +44,7 @@ class Engine:
         chunk = min(lim.prefill_chunk, lim.max_ctx)
         self.prefill_buf: Optional[Buffers] = None
         self._prefill_rows = chunk
+        self._prefill_logit_rows = max(1, min(lim.max_slots, 64))
         self.decode_buf = model.make_buffers(lim.max_decode_rows, lim.max_decode_rows)
         # device-resident step inputs (graph replay reads these)
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=self.device)
@@ -108,7 +109,8 @@ class Engine:
     # ------------------------------------------------------------------------------------------
     def _ensure_prefill_buf(self):
         if self.prefill_buf is None:
-            self.prefill_buf = self.model.make_buffers(self._prefill_rows, 1, dense_kv_tokens=self.limits.max_ctx)
+            self.prefill_buf = self.model.make_buffers(self._prefill_rows, self._prefill_logit_rows,
+                                                       dense_kv_tokens=max(self.limits.max_ctx, self._prefill_rows))
 
     def prefill(self, seq: SeqSlot, tokens: Sequence[int] | torch.Tensor, want_logits: bool = True) -> Optional[torch.Tensor]:
         """Append ``tokens`` to the sequence in chunks of ``prefill_chunk`` rows; returns the fp32
@@ -151,6 +153,40 @@ class Engine:
             row = logits[0] if logits is not None else torch.empty(self.cfg.vocab_size, dtype=torch.float32, device=self.device)
             logits = pp.broadcast_from_last(row)[None]
         return logits[0] if want_logits else None
+
+    def can_prefill_batch(self) -> bool:
+        """Several fresh prompts in one M-row pass: dense models without a draft head or pipeline stages."""
+        return isinstance(self.model, DenseModel) and self.mtp is None and getattr(self.model, "pp", None) is None
+
+    def prefill_batch(self, seqs: Sequence[SeqSlot], prompts: Sequence[Sequence[int]]) -> list[torch.Tensor]:
+        """Read several whole prompts into fresh slots with ONE forward pass (admit_batch, grimoire.cpp:12071-12146): the
+        projections run over the sum of the prompt lengths, attention per prompt.  Every sequence must be empty and the
+        rows must fit one prefill chunk.  Returns the last-token logits of each prompt."""
+        total = sum(len(p) for p in prompts)
+        if not self.can_prefill_batch() or total > self._prefill_rows or any(s.length or s.pages for s in seqs) or \
+                any(len(p) == 0 or len(p) > self.limits.max_ctx for p in prompts):
+            raise ValueError("prefill_batch needs fresh slots, non-empty prompts and at most one chunk of rows in total")
+        self._ensure_prefill_buf()
+        if self.prefix_cache is not None:
+            self.prefix_cache.make_room(sum((len(p) + PAGE - 1) // PAGE for p in prompts))
+        toks, rs, rp, segs, last = [], [], [], [], []
+        for s, p in zip(seqs, prompts):
+            self.kv.ensure(s, len(p))
+            segs.append((len(toks), len(p)))
+            toks += [int(t) for t in p]
+            rs += [s.slot] * len(p)
+            rp += list(range(len(p)))
+            last.append(len(toks) - 1)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32).to(self.device, non_blocking=True)
+        rb = RowBatch(i32(toks), i32(rs), i32(rp), mode="prefill", q_pos0=0, seq_slot=seqs[0].slot, segments=segs,
+                      logits_rows=torch.tensor(last, device=self.device))
+        logits = self.model.forward(rb, self.prefill_buf, self.kv.layers, self.kv.table)
+        for s, p in zip(seqs, prompts):
+            s.length = len(p)
+            s.tokens.extend(int(t) for t in p)
+        self.counters["prefill_rows"] += total
+        self.counters["prefill_batches"] = self.counters.get("prefill_batches", 0) + 1
+        return [logits[i] for i in range(len(prompts))]
 
     # ------------------------------------------------------------------------------------------
     # batched decode / verify rows
@@ -221,6 +257,26 @@ class Engine:
         if return_logits:
             return out, self.decode_buf.logits[:M]
         return out
+
+    def sample_rows(self, logits: torch.Tensor, opts: Sequence, positions: Sequence[int]) -> list[int]:
+        """Draw one token per logits row with per-row options (temperature / top-k / top-p / seed, the draw is a pure
+        function of (seed, position): launch_sample_logits, src/sample_logits.hpp:41-134).  On a GPU the rows never leave
+        the device: the options go up (a few bytes per row), the chosen ids come back (4 bytes per row)."""
+        from .sampling import DeviceSampler, sample_ref
+
+        n = logits.shape[0]
+        if self.device.type != "cuda":
+            self.counters["logits_d2h_bytes"] = self.counters.get("logits_d2h_bytes", 0)
+            return [sample_ref(logits[i], opts[i], int(positions[i])) for i in range(n)]
+        if getattr(self, "_sampler", None) is None:
+            self._sampler = DeviceSampler(self.limits.max_decode_rows, self.device)
+            self._sample_pos = torch.zeros(self.limits.max_decode_rows, dtype=torch.int32, device=self.device)
+            self._sample_out = torch.zeros(self.limits.max_decode_rows, dtype=torch.int32, device=self.device)
+        self._sampler.set_rows(list(opts))
+        self._sample_pos[:n] = torch.tensor([int(p) for p in positions], dtype=torch.int32)
+        self._sampler.sample(logits, self._sample_pos[:n], self._sample_out[:n])
+        self.counters["sample_d2h_bytes"] = self.counters.get("sample_d2h_bytes", 0) + 4 * n
+        return [int(v) for v in self._sample_out[:n].tolist()]
 
     def commit_rows(self, seqs: Sequence[SeqSlot], tokens: Sequence[int], positions: Sequence[int]) -> None:
         """Record that rows were appended (host bookkeeping after an accepted step)."""

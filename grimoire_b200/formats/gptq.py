@@ -66,9 +66,9 @@ def gptq_unpack(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
         if not torch.equal(g_idx.cpu(), trivial):
             raise ValueError("GPTQ act-order (non-trivial g_idx) checkpoints are not supported")
     q = _unpack_i32_nibbles(qweight.cpu(), 0).t().contiguous()          # [N][K]
-    z = (_unpack_i32_nibbles(qzeros.cpu(), 1) + 1) & 0xF                # [K/g][N]
-    # a stored 15 wraps to 0 in 4 bits but means 16 in AutoGPTQ arithmetic; keep the 0..15 domain
-    # the reference uses (include/b70/gptq.hpp:36-42)
+    # zero = stored code + 1 in 1..16 with no wrap: a stored 15 means 16 (src/gptq.cpp:44 dequantises with
+    # znib + 1, :73 repacks uint8(z + 1)); zeros travel as bytes, so 16 needs no special case downstream
+    z = _unpack_i32_nibbles(qzeros.cpu(), 1) + 1                        # [K/g][N]
     zeros = z[:, :N].t().contiguous().to(torch.uint8)                   # [N][K/g]
     sc = scales.cpu().t().contiguous().half()                           # [N][K/g]
     return QuantWeight(Fmt.INT4, N, K, C.pack_nibbles(q.to(torch.uint8)), scales=sc, zeros=zeros, group=group)
@@ -80,7 +80,9 @@ def gptq_pack(qw: QuantWeight):
         raise ValueError("gptq_pack needs an INT4 weight")
     q = C.unpack_nibbles(qw.payload)                                    # [N][K]
     qweight = _pack_i32_nibbles(q.t().contiguous(), 0)                  # [K/8][N]
-    zc = ((qw.zeros.to(torch.int64) - 1) & 0xF).t().contiguous()        # [K/g][N]
+    if int(qw.zeros.min()) < 1 or int(qw.zeros.max()) > 16:
+        raise ValueError("GPTQ stores zero - 1 in 4 bits: only zero points 1..16 can be written")
+    zc = (qw.zeros.to(torch.int64) - 1).t().contiguous()                # [K/g][N]
     if zc.shape[1] % 8:
         raise ValueError("out features must be a multiple of 8 for GPTQ qzeros packing")
     qzeros = _pack_i32_nibbles(zc, 1)                                   # [K/g][N/8]

@@ -116,6 +116,9 @@ class CheckpointDir:
         if idx.exists():
             wm = json.loads(idx.read_text())["weight_map"]
             for name, shard in wm.items():
+                # a shard is a plain file name inside this directory: no separators, no parent references
+                if not isinstance(shard, str) or shard in ("", ".", "..") or "/" in shard or "\\" in shard or Path(shard).name != shard:
+                    raise ValueError(f"index names a shard outside the checkpoint directory: {shard!r}")
                 self.where[name] = shard
         else:
             shards = sorted(p.name for p in self.path.glob("*.safetensors"))

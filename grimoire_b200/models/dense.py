@@ -59,6 +59,9 @@ class RowBatch:
     splits: int = 1
     logits_rows: Optional[torch.Tensor] = None   # int64 indices of rows that need logits (None = all)
     distinct: bool = False               # decode: every row is a different sequence (no verify block in the step)
+    # prefill of several fresh prompts in one pass: (first row, rows) per prompt, rows of a prompt contiguous and at
+    # positions 0..rows-1 of its own sequence (admit_batch, grimoire.cpp:12071-12146); None = one sequence
+    segments: Optional[list] = None
 
 
 class Buffers:
@@ -379,7 +382,7 @@ class DenseModel:
 
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
-        if (rb.mode == "prefill" and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
+        if (rb.mode == "prefill" and rb.segments is None and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
                 and isinstance(self.layers[0].qkv, (W4Linear, RowQLinear)) and self.tp.sp_ready(rb.tokens.shape[0]) and self.tp.sp_enabled):
             return self.forward_prefill_sp(rb, buf, kv_layers, block_table)
         cfg, geom = self.cfg, self.geom
@@ -403,7 +406,15 @@ class DenseModel:
             if tl: trace.mark("norm+qkv")
             self._norm_linear(L.qkv, h, L.in_norm, x, qkv, "bf16", eps, off)
             if tl: trace.mark("rope+attn")
-            if prefill:
+            if prefill and rb.segments is not None:
+                # several fresh prompts in one pass: the projections see all M rows at once, attention runs per prompt
+                # over that prompt's slice of the dense K / V rows
+                K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
+                               gate, buf.dense_k[:M], buf.dense_v[:M])
+                for r0, n in rb.segments:
+                    K.flash_prefill(q[r0: r0 + n], buf.dense_k[r0: r0 + n], buf.dense_v[r0: r0 + n], geom, attn[r0: r0 + n], 0,
+                                    None if gate is None else gate[r0: r0 + n])
+            elif prefill:
                 if rb.q_pos0 > 0:
                     K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,

@@ -72,6 +72,8 @@ class MegaTable:
         self.cnt = torch.zeros(max_rp, dtype=torch.int32, device=self.device)
         self.tp = tp
         self.spin = int(os.environ.get("GRIMOIRE_MEGA_SPIN", "0"))
+        if os.environ.get("GRIMOIRE_MEGA_TUNE"):
+            lib.grm_mega_set_tune(int(os.environ["GRIMOIRE_MEGA_TUNE"]))
         if os.environ.get("GRIMOIRE_MEGA_SLOTS"):
             lib.grm_mega_set_slot_cap(int(os.environ["GRIMOIRE_MEGA_SLOTS"]))
         self.grid = grid

@@ -105,6 +105,12 @@ class ControlledEngine:
         self.ch.send(ROLLBACK, seq.slot, length)
         self.engine.rollback(seq, length)
 
+    def sample_rows(self, logits, opts, positions):
+        return self.engine.sample_rows(logits, opts, positions)      # every rank holds the same logits: the front end draws
+
+    def can_prefill_batch(self) -> bool:
+        return False                                                 # the control protocol announces one prompt per call
+
     def shutdown(self) -> None:
         self.ch.send(SHUTDOWN)
 

@@ -177,6 +177,10 @@ class Scheduler:
     def _pick(self, job: SchedJob, logits: torch.Tensor, position: int) -> int:
         if job.sampling.greedy:
             return first_token_of(logits)
+        dev = getattr(self.engine, "sample_rows", None)
+        if dev is not None and torch.is_tensor(logits):
+            # the device sampler: no logits row travels to the host (the options of the row go up, 4 bytes come back)
+            return dev(logits.reshape(1, -1), [job.sampling], [position])[0]
         return sample_ref(logits, job.sampling, position)
 
     def _run(self) -> None:
@@ -237,7 +241,42 @@ class Scheduler:
     def _admit(self, plan: _Plan) -> None:
         eng = self.engine
         firsts = []
+        # whole prompts that start from an empty slot share ONE M-row pass (admit_batch, grimoire.cpp:12071-12146)
+        batched = set()
+        can = getattr(eng, "can_prefill_batch", None)
+        if plan.n_admit > 1 and can is not None and can():
+            cand = []
+            for i in range(plan.n_admit):
+                job = self.jobs.get(plan.admit_job[i])
+                if job is not None and job.seq is None and plan.admit_from[i] == 0 and plan.admit_to[i] == len(job.prompt):
+                    cand.append((i, job))
+            room = eng._prefill_rows
+            chosen = []
+            for i, job in cand:
+                if len(job.prompt) <= room and len(chosen) < eng._prefill_logit_rows:
+                    chosen.append((i, job))
+                    room -= len(job.prompt)
+            if len(chosen) > 1:
+                seqs, taken = [], []
+                for i, job in chosen:
+                    seq = eng.open()
+                    reused = eng.prefix_reuse(seq, job.prompt) if hasattr(eng, "prefix_reuse") else 0
+                    job.seq = seq
+                    if reused == 0:
+                        seqs.append(seq)
+                        taken.append((i, job))       # prompts with a cached prefix take the single path below
+                if len(taken) > 1:
+                    logits = eng.prefill_batch(seqs, [job.prompt for _, job in taken])
+                    for (i, job), lg in zip(taken, logits):
+                        batched.add(i)
+                        self.metrics["admit_rows"] += len(job.prompt)
+                        state = self.lib.grm_sched_on_prefilled(self.h, ctypes.c_int64(job.id), len(job.prompt))
+                        if state == 2:
+                            firsts.append((job, self._pick(job, lg, job.seq.length)))
+                    self.metrics["admit_batches"] = self.metrics.get("admit_batches", 0) + 1
         for i in range(plan.n_admit):
+            if i in batched:
+                continue
             job = self.jobs.get(plan.admit_job[i])
             if job is None:
                 continue
@@ -245,11 +284,11 @@ class Scheduler:
             if job.seq is None:
                 job.seq = eng.open()
                 if lo == 0 and hasattr(eng, "prefix_reuse"):
-                    reused = eng.prefix_reuse(job.seq, job.prompt)
-                    if reused:
-                        lo = max(lo, min(reused, len(job.prompt)))
-                        if lo >= hi:
-                            hi = min(len(job.prompt), max(hi, lo))
+                    eng.prefix_reuse(job.seq, job.prompt)
+            if lo == 0 and job.seq.length:
+                lo = min(job.seq.length, len(job.prompt))          # tokens served by the prefix cache
+                if lo >= hi:
+                    hi = min(len(job.prompt), max(hi, lo))
             lo = max(lo, job.seq.length)
             logits = eng.prefill(job.seq, job.prompt[lo:hi]) if hi > lo or lo >= len(job.prompt) else None
             self.metrics["admit_rows"] += max(0, hi - lo)

@@ -113,3 +113,42 @@ def test_gate_up_interleave():
     f = interleave_gate_up(g, u)
     assert f[:16, 0].tolist() == list(range(16)) and f[16:32, 0].tolist() == [100 + i for i in range(16)]
     assert f[32:48, 0].tolist() == list(range(16, 32))
+
+
+def test_gptq_stored_zero_15_means_16():
+    """AutoGPTQ stores zero - 1; a stored nibble of 15 is the zero point 16, not 0 (the reference dequantises with
+    znib + 1 without wrapping, src/gptq.cpp:44)."""
+    import torch
+    from grimoire_b200.formats import gptq
+
+    K, N, g = 128, 8, 128
+    codes = torch.randint(0, 16, (K, N))
+    qweight = gptq._pack_i32_nibbles(codes, 0)                       # [K/8][N]
+    zc = torch.tensor([[15, 0, 7, 15, 3, 14, 15, 8]])                # stored zero - 1 per output column
+    qzeros = gptq._pack_i32_nibbles(zc, 1)                           # [1][N/8]
+    scales = (torch.rand(1, N) * 0.01 + 0.001).half()
+    qw = gptq.gptq_unpack(qweight, qzeros, scales)
+    assert qw.zeros[:, 0].tolist() == [16, 1, 8, 16, 4, 15, 16, 9]
+    want = (codes.t().float() - (zc[0].float() + 1)[:, None]) * scales[0].float()[:, None]
+    assert torch.allclose(qw.dequant(), want, atol=1e-7)
+    a, b, c = gptq.gptq_pack(qw)
+    assert torch.equal(b, qzeros) and torch.equal(a, qweight)
+
+
+def test_safetensors_rejects_length_mismatch_and_escaping_shards(tmp_path):
+    import json
+    import struct
+
+    import pytest
+    import torch
+    from grimoire_b200.formats.safetensors_io import CheckpointDir, SafeTensorsFile
+
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [4, 4], "data_offsets": [0, 32]}}).encode()     # 16 floats need 64 bytes
+    (tmp_path / "bad.safetensors").write_bytes(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 32)
+    with pytest.raises(Exception):
+        SafeTensorsFile(tmp_path / "bad.safetensors")
+    d = tmp_path / "ck"
+    d.mkdir()
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"w": "../bad.safetensors"}}))
+    with pytest.raises(ValueError):
+        CheckpointDir(d)

@@ -75,6 +75,10 @@ def engine():
     return Engine(DenseModel.from_state_dict(cfg, sd, "cpu"), EngineLimits(max_slots=4, max_ctx=256, prefill_chunk=64, max_decode_rows=16))
 
 
+def _prompt(n, seed):
+    return torch.randint(0, 4096, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
 def _prompts():
     g = torch.Generator().manual_seed(7)
     return [torch.randint(0, 4096, (n,), generator=g).tolist() for n in (5, 23, 70)]
@@ -119,3 +123,43 @@ def test_overlong_prompt_is_a_value_error(engine):
     with pytest.raises(ValueError):
         s.generate(list(range(300)), 4)
     s.shutdown()
+
+
+def test_short_prompts_admitted_together_run_one_pass(engine):
+    """Prompts that arrive together share ONE M-row prefill (admit_batch, grimoire.cpp:12071) and still produce the
+    tokens they produce alone."""
+    import threading
+
+    prompts = [_prompt(n, seed) for n, seed in ((9, 31), (17, 32), (5, 33))]
+    alone = [engine.generate(p, 6) for p in prompts]
+    sched = Scheduler(engine, width=4, hold_ms=200.0, hold_long_ms=400.0, use_graph=False)
+    res = [None] * len(prompts)
+
+    def run(i):
+        res[i] = sched.generate(prompts[i], 6)[0]
+
+    ts = [threading.Thread(target=run, args=(i,)) for i in range(len(prompts))]
+    [t.start() for t in ts]
+    [t.join(120) for t in ts]
+    batches = sched.metrics.get("admit_batches", 0)
+    sched.shutdown()
+    assert res == alone
+    assert batches >= 1 and engine.counters.get("prefill_batches", 0) >= 1
+
+
+def test_prefill_batch_logits_equal_single_prefill(engine):
+    import torch
+
+    prompts = [_prompt(12, 41), _prompt(7, 42)]
+    single = []
+    for p in prompts:
+        s = engine.open()
+        single.append(engine.prefill(s, p).clone())
+        engine.release(s)
+    seqs = [engine.open(), engine.open()]
+    got = engine.prefill_batch(seqs, prompts)
+    for a, b in zip(single, got):
+        assert int(a.argmax()) == int(b.argmax()) and torch.allclose(a, b, atol=5e-3)
+    nxt = engine.decode_rows([int(g.argmax()) for g in got], seqs, [s.length for s in seqs], use_graph=False)
+    assert len(nxt) == 2
+    [engine.release(s) for s in seqs]

@@ -25,25 +25,30 @@ def _c(v):
     return ctypes.c_int(int(v))
 
 
-def _call_plain(lib, t, x, out, ksplit, rows):
-    M = x.shape[0]
-    tiles = t.N // rows
+def _scratch_floats(M, N, rows, ksplit, epi):
     mt = 1
     while mt * 8 < M:
         mt *= 2
-    scratch = torch.empty(ksplit * tiles * (rows // 16) * mt * 128, dtype=torch.float32, device="cuda")
+    r = 2 if epi == 3 else (2 if rows == 32 and mt <= 2 else 1)
+    return ksplit * (N // (16 * r)) * r * mt * 128, N // (16 * r)
+
+
+def _call_plain(lib, t, x, out, ksplit, rows, epi=1):
+    M = x.shape[0]
+    nf, tiles = _scratch_floats(M, t.N, rows, ksplit, epi)
+    scratch = torch.empty(nf, dtype=torch.float32, device="cuda")
     counters = torch.zeros(tiles, dtype=torch.int32, device="cuda")
     rc = lib.grm_smallm_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _native.ptr(scratch),
                            _native.ptr(counters), _c(M), _c(t.N), _c(t.K), _c(x.stride(0)), _c(out.stride(0)), _c(t.group),
-                           _c(1), _c(rows), _c(ksplit), _native.stream_ptr())
+                           _c(epi), _c(rows), _c(ksplit), _native.stream_ptr())
     assert rc == 0
 
 
-def _call_noalloc(lib, t, x, out, ksplit, rows):
+def _call_noalloc(lib, t, x, out, ksplit, rows, epi=1):
     M = x.shape[0]
     fn = lib.grm_smallm_w4_noalloc           # resolved by name from the shared library
     return fn(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _c(M), _c(t.N), _c(t.K),
-              _c(x.stride(0)), _c(out.stride(0)), _c(t.group), _c(1), _c(rows), _c(ksplit), _native.stream_ptr())
+              _c(x.stride(0)), _c(out.stride(0)), _c(t.group), _c(epi), _c(rows), _c(ksplit), _native.stream_ptr())
 
 
 def test_noalloc_entry_point_matches_ordinary_entry_point_twice():
@@ -67,14 +72,37 @@ def test_noalloc_entry_point_matches_ordinary_entry_point_twice():
         assert torch.allclose(got[:, :N].cpu(), ref, atol=2e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("M,N,K,ksplit,rows,epi", [(5, 256, 2048, 2, 32, 3),     # SwiGLU tiles (two 16-row tiles per CTA), split K
+                                                   (9, 128, 4096, 4, 32, 1),     # 32-row CTAs with two batch tiles
+                                                   (64, 64, 2048, 2, 16, 1),     # the widest batch the kernel is built for
+                                                   (2, 96, 1024, 1, 16, 2)])     # one K slice: scratch untouched, accumulate epilogue
+def test_noalloc_entry_point_covers_every_scratch_sizing(M, N, K, ksplit, rows, epi):
+    """Each (batch tile count, rows per CTA, epilogue) combination sizes the shared scratch differently; all of them must
+    agree with the ordinary entry point."""
+    lib = _native.cuda()
+    torch.manual_seed(M + N)
+    qw = quantize(torch.randn(N, K) * 0.02, Fmt.INT4)
+    t = tile_w4(qw).to("cuda")
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    if epi == 3:
+        mk = lambda: torch.zeros(M, t.N // 2, dtype=torch.bfloat16, device="cuda")
+    else:
+        mk = lambda: torch.ones(M, t.N, dtype=torch.float32, device="cuda")
+    want, got = mk(), mk()
+    _call_plain(lib, t, x, want, ksplit, rows, epi)
+    assert _call_noalloc(lib, t, x, got, ksplit, rows, epi) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+
+
 def test_noalloc_entry_point_rejects_oversized_problems():
     lib = _native.cuda()
-    qw = quantize(torch.randn(32, 128) * 0.02, Fmt.INT4)
+    qw = quantize(torch.randn(32, 512) * 0.02, Fmt.INT4)
     t = tile_w4(qw).to("cuda")
-    x = torch.randn(1, 128, device="cuda").bfloat16()
+    x = torch.randn(1, 512, device="cuda").bfloat16()
     out = torch.zeros(1, 32, dtype=torch.float32, device="cuda")
-    # a made-up N far beyond the tile limit: refused before anything is read or launched
+    # a made-up N far beyond the tile limit of a split-K call: refused before anything is read or launched
     fn = lib.grm_smallm_w4_noalloc
-    rc = fn(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _c(1), _c(32 * 8192), _c(128), _c(128),
-            _c(32), _c(128), _c(1), _c(16), _c(1), _native.stream_ptr())
+    rc = fn(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _c(1), _c(32 * 8192), _c(512), _c(512),
+            _c(32), _c(128), _c(1), _c(16), _c(2), _native.stream_ptr())
     assert rc == -5
