@@ -38,7 +38,7 @@ BASELINE_PP4096 = 2698.0          # tok/s, 1xB70 (README.md:183); TP2: 3498
 
 def reference_arm(args) -> int:
     # The reference is a SYCL / Level Zero engine for Intel Arc with no Python package and no CUDA
-    # path: `pip install /root/reference` fails ("neither setup.py nor pyproject.toml") and its
+    # path: pip cannot install its source tree ("neither setup.py nor pyproject.toml") and its
     # kernels cannot target sm_100a.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a SYCL/Level Zero (Intel Arc) C++ engine: not pip-installable "

@@ -39,9 +39,14 @@ def cuda() -> ctypes.CDLL:
 
 
 def host() -> ctypes.CDLL:
+    """The host runtime.  GRIMOIRE_HOST_LIB names another build of it (the sanitizer build of ``build_host(sanitize=True)``)."""
     global _host
     if _host is None:
-        _host = _load("libgrimoire_host.so", "build_host")
+        alt = os.environ.get("GRIMOIRE_HOST_LIB")
+        if alt:
+            _host = ctypes.CDLL(alt, mode=ctypes.RTLD_GLOBAL)
+        else:
+            _host = _load("libgrimoire_host.so", "build_host")
     return _host
 
 

@@ -107,16 +107,56 @@ def build_cuda(verbose: bool = False, ptxas_info: bool = False) -> Path:
     return out
 
 
-def build_host(verbose: bool = False) -> Path:
-    """Compile the host-side C++ runtime (no CUDA needed) and link libgrimoire_host.so."""
+SANITIZE_FLAGS = ["-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined", "-g", "-O1"]
+
+
+def sanitizer_toolchain():
+    """(g++ path, libasan.so path) of a compiler that ships the AddressSanitizer runtime, or None."""
+    for cxx in dict.fromkeys([CXX, "/usr/bin/g++", shutil.which("g++") or "g++"]):
+        try:
+            out = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+        except OSError:
+            continue
+        if out and os.path.sep in out and os.path.exists(out):
+            return cxx, os.path.realpath(out)
+    return None
+
+
+def build_host(verbose: bool = False, sanitize: bool = False) -> Path:
+    """Compile the host-side C++ runtime (no CUDA needed) and link libgrimoire_host.so.  ``sanitize`` builds
+    libgrimoire_host_asan.so with AddressSanitizer + UndefinedBehaviorSanitizer instead (the parsers of untrusted files
+    run under it in the tests; load it with GRIMOIRE_HOST_LIB and the ASan runtime preloaded)."""
     srcs = sorted((CSRC / "host").glob("*.cpp"))
     if not srcs:
         raise RuntimeError("no host sources under csrc/host")
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + SANITIZE_FLAGS if sanitize else CXX_FLAGS
+    objdir_tag = "asan." if sanitize else ""
+    cxx = CXX
+    if sanitize:
+        tc = sanitizer_toolchain()
+        if tc is None:
+            raise RuntimeError("no compiler with the AddressSanitizer runtime on this machine")
+        cxx = tc[0]
+
+    def comp(src: Path) -> Path:
+        if not sanitize:
+            return _compile(src, CXX, flags, verbose)
+        OBJDIR.mkdir(exist_ok=True)
+        obj = OBJDIR / f"{src.stem}.{objdir_tag}{_hash_inputs(src, flags)}.o"
+        if not obj.exists():
+            for old in OBJDIR.glob(f"{src.stem}.{objdir_tag}*.o"):
+                old.unlink()
+            res = subprocess.run([cxx, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+            if res.returncode != 0:
+                sys.stderr.write(res.stdout + res.stderr)
+                raise RuntimeError(f"compile failed: {src}")
+        return obj
+
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
-        objs = list(ex.map(lambda s: _compile(s, CXX, CXX_FLAGS, verbose), srcs))
-    out = LIBDIR / "libgrimoire_host.so"
+        objs = list(ex.map(comp, srcs))
+    out = LIBDIR / ("libgrimoire_host_asan.so" if sanitize else "libgrimoire_host.so")
     if _stale(out, objs):
-        _link(objs, out, CXX, ["-pthread"])
+        _link(objs, out, cxx, ["-pthread"] + (["-fsanitize=address,undefined"] if sanitize else []))
     return out
 
 

@@ -60,8 +60,7 @@ struct MegaParams {
   int first, count;
   const float* h;                 // fp32 residual row (PRO_NORM input)
   unsigned int* sync;             // [0] barrier arrivals (monotonic), [1] unused, [2] abort
-  float* parts;                   // [row pair][pstride][32] partial sums of non-owner CTAs
-  unsigned int* cnt;              // [row pair] published partials
+  uint2* parts;                   // [row pair][pstride][32] {partial sum, epoch} of the CTAs that do not own the row pair
   int pstride;
   unsigned int* status;
   unsigned int spin;
@@ -108,6 +107,27 @@ __device__ __forceinline__ bool aborted(const Ctx& c, unsigned int i) {
   if (*c.s_abort) return true;
   if ((i & 255u) == 255u && ld_relaxed_gpu(c.sync + 2) != 0u) { *c.s_abort = 1; return true; }
   return false;
+}
+
+// shared-memory accessors on 32-bit addresses (no generic-pointer arithmetic in the hot loop)
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive_s(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, const Ctx& c, uint32_t tag) {
@@ -318,34 +338,38 @@ __device__ void finalize_pair(const MegaParams& p, const MegaPhase& ph, const Ge
     nparts = geo.SPR;
     my_part = si0;
   }
+  // Partial sums travel as aligned 8-byte {value, epoch} pairs: the store lands as a whole, so the owner polls the
+  // slot itself until its epoch word is this phase's -- no fence, no counter, one L2 round trip.
   if (!owner) {
-    p.parts[((size_t)rp * p.pstride + (my_part - 1)) * 32 + lane] = sum;
-    __threadfence();
-    __syncwarp();
-    if (lane == 0) atomicAdd(p.cnt + rp, 1u);
+    uint2* dst = p.parts + ((size_t)rp * p.pstride + (my_part - 1)) * 32 + lane;
+    asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(sum)), "r"(epoch) : "memory");
     return;
   }
+  const int row = rp * 32 + lane;
+  // the accumulate epilogue's old value is fetched while the partial sums are awaited
+  float hold = 0.f;
+  const bool add_local = ph.epi == EPI_ADD && row < ph.N;
+  if (add_local) hold = __ldcg(reinterpret_cast<const float*>(ph.out) + row);
   if (nparts > 1) {
     bool ok = true;
-    if (lane == 0) {
-      ok = false;
+    for (int j = 0; j < nparts - 1 && ok; ++j) {
+      const uint2* src = p.parts + ((size_t)rp * p.pstride + j) * 32 + lane;
+      uint32_t vx = 0u, vy = 0u;
+      bool got = false;
       if (!*c.s_abort) {
         for (unsigned int i = 0; i < c.spin; ++i) {
-          if (ld_acquire_gpu(p.cnt + rp) == (unsigned int)(nparts - 1)) { ok = true; break; }
+          asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+          if (vy == epoch) { got = true; break; }
           if (aborted(c, i)) break;
-          if (i > 16) __nanosleep(40);
+          if (i > 64) __nanosleep(20);
         }
-        if (!ok && !*c.s_abort) raise_abort(c, GRM_ERR_FLAG_TIMEOUT, 0x40000u | (unsigned int)(rp & 0xffff));
+        if (!got && !*c.s_abort) raise_abort(c, GRM_ERR_FLAG_TIMEOUT, 0x40000u | (unsigned int)(rp & 0xffff));
       }
-      p.cnt[rp] = 0u;
+      ok = __all_sync(0xffffffffu, got);
+      sum += __uint_as_float(vx);
     }
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-    __threadfence();
-    if (ok) {
-      for (int j = 0; j < nparts - 1; ++j) sum += __ldcg(p.parts + ((size_t)rp * p.pstride + j) * 32 + lane);
-    }
+    if (!ok) return;
   }
-  const int row = rp * 32 + lane;
   if (ph.epi == EPI_SWIGLU) {
     const float up = __shfl_down_sync(0xffffffffu, sum, 16);
     const int col = rp * 16 + r;
@@ -387,10 +411,7 @@ __device__ void finalize_pair(const MegaParams& p, const MegaPhase& ph, const Ge
   if (row < ph.N) {
     if (ph.epi == EPI_BF16) reinterpret_cast<bf16*>(ph.out)[row] = __float2bfloat16(sum);
     else if (ph.epi == EPI_F32) reinterpret_cast<float*>(ph.out)[row] = sum;
-    else {
-      float* o = reinterpret_cast<float*>(ph.out) + row;
-      *o = __ldcg(o) + sum;
-    }
+    else reinterpret_cast<float*>(ph.out)[row] = hold + sum;
   }
 }
 
@@ -420,7 +441,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
 
   if (warp == kCW) {
     // ================= producer: this CTA's byte range of every phase, through the ring =================
-    if (lane == 0) {
+    // Three lanes issue the three copies of a stage with ONE instruction each step (lane 0: the weights, lanes 1 / 2:
+    // the scale words of the two 16-row tiles): the producer is a single warp competing with sixteen busy ones for
+    // issue slots, so its per-stage instruction chain is kept as short as possible.
+    if (lane < 3) {
+      const uint32_t ring_s = smem_u32(ring), full_s = smem_u32(full), empty_s = smem_u32(empty);
+      const uint32_t dst_off = lane == 0 ? 0u : (uint32_t)(kUnits * 1024 + (lane - 1) * kSzSeg);
       uint32_t slot = 0, par = 0, issued = 0;
       bool live = true;
       for (int pi = 0; pi < p.count && live; ++pi) {
@@ -429,23 +455,30 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
         if (geo.sb >= geo.se) continue;
         int rp = (int)(geo.sb / geo.SPR), si = (int)(geo.sb - (long long)rp * geo.SPR);
         const int G = geo.KT >> geo.g64s;
+        // lane 0 walks one contiguous byte range of the weight array; the scale lanes recompute their short offsets
+        const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(ph.w) + ((size_t)rp * geo.KT + (size_t)kUnits * si) * 1024;
         const uint8_t* szb = reinterpret_cast<const uint8_t*>(ph.sz);
         for (long long s = geo.sb; s < geo.se; ++s) {
           // slot reuse: wait until the consumers released its previous contents (parity of the previous round)
-          if (issued >= (uint32_t)S && !ring_wait(empty + slot, par ^ 1u, c, 0x100u | slot)) { live = false; break; }
+          if (issued >= (uint32_t)S && !mbar_test(empty_s + slot * 8u, par ^ 1u) && !ring_wait(empty + slot, par ^ 1u, c, 0x100u | slot)) live = false;
+          live = __all_sync(0x7u, live);
+          if (!live) break;
           const int nu = min(kUnits, geo.KT - kUnits * si);
           const int ng = nu >> geo.g64s, g0 = (kUnits * si) >> geo.g64s;
-          uint8_t* dst = ring + (size_t)slot * kSlotBytes;
-          mbar_expect_tx(full + slot, (uint32_t)(nu * 1024 + 2 * ng * 64));
-          bulk_load(dst, reinterpret_cast<const uint8_t*>(ph.w) + ((size_t)rp * geo.KT + (size_t)kUnits * si) * 1024, (uint32_t)nu * 1024u, full + slot);
-          bulk_load(dst + kUnits * 1024, szb + ((size_t)(2 * rp) * G + g0) * 64, (uint32_t)ng * 64u, full + slot);
-          bulk_load(dst + kUnits * 1024 + kSzSeg, szb + ((size_t)(2 * rp + 1) * G + g0) * 64, (uint32_t)ng * 64u, full + slot);
+          const uint32_t fb = full_s + slot * 8u;
+          if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fb), "r"((uint32_t)(nu * 1024 + 2 * ng * 64)) : "memory");
+          const uint8_t* src = lane == 0 ? wsrc : szb + ((size_t)((2 * rp + lane - 1) * G + g0) << 6);
+          const uint32_t bytes = lane == 0 ? (uint32_t)nu << 10 : (uint32_t)ng << 6;
+          __syncwarp(0x7u);
+          asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(ring_s + slot * (uint32_t)kSlotBytes + dst_off), "l"(src), "r"(bytes), "r"(fb) : "memory");
+          wsrc += (size_t)nu << 10;
           ++issued;
           if (++slot == (uint32_t)S) { slot = 0; par ^= 1u; }
           if (++si == geo.SPR) { si = 0; ++rp; }
         }
       }
-      if (!live) {
+      if (!live && lane == 0) {
         // a wait gave up: make sure none of this CTA's copies is still in flight before shared memory goes away
         uint32_t sl = slot, pr = par;
         const uint32_t back = issued < (uint32_t)S ? issued : (uint32_t)S;
@@ -460,6 +493,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
     // ================= consumers =================
     const int g = lane >> 2, t = lane & 3;
     const int u = warp;                                // this warp's unit of every stage (both 16-row tiles)
+    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(xs), xsum_s = smem_u32(xsum);
+    const uint32_t full_s = smem_u32(full), empty_s = smem_u32(empty);
+    const uint32_t w_off = (uint32_t)(u * 1024 + lane * 16);
     uint32_t slot = 0, par = 0, flushes = 0;
     const unsigned int gen0 = ld_acquire_gpu(p.sync) / (unsigned int)nC;      // barrier rounds completed before this launch
     for (int pi = 0; pi < p.count; ++pi) {
@@ -477,49 +513,56 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
       float inv_scale = 1.f;
       stage_x(ph, p.h, xs, xsum, red_a, red_b, tid, inv_scale);
       if (tl) tl[2] = clock64();
+      if (pi + 1 < p.count) {
+        // the next phase's norm weights are cold in L2 (read once per token): start fetching them now so that its
+        // staging step, which sits on the critical path right after the grid barrier, finds them there
+        const MegaPhase* nx = p.phases + p.first + pi + 1;
+        if (nx->pro == PRO_NORM) {
+          const char* nwp = reinterpret_cast<const char*>(nx->nw);
+          for (int i = tid * 128; i < nx->K * 4; i += kCW * 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(nwp + i));
+        }
+      }
       const unsigned int epoch = gen0 + (unsigned int)pi + 1u;
-      const int szo = (u >> geo.g64s) * 64 + 4 * g;   // this lane's scale word inside a tile's segment
+      const uint32_t sz_off = (uint32_t)(kUnits * 1024 + (u >> geo.g64s) * 64 + 4 * g);   // this lane's scale word of tile 0 in a slot
       long long s = geo.sb;
       while (s < geo.se) {
         const int rp = (int)(s / geo.SPR);
         const int si0 = (int)(s - (long long)rp * geo.SPR);
         const int si1 = (int)min((long long)geo.SPR, si0 + (geo.se - s));
         float f00 = 0.f, f01 = 0.f, f10 = 0.f, f11 = 0.f;      // tile 0 rows g, g + 8; tile 1 rows g, g + 8
-        for (int si = si0; si < si1; ++si) {
-          const bool ok = ring_wait(full + slot, par, c, 0x200u | slot);
-          const bool act = ok && u < geo.KT - kUnits * si;
-          uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0, xa = w0, xb = w0;
-          uint32_t s00 = 0u, s01 = 0u, s10 = 0u, s11 = 0u;
-          float xu = 0.f;
-          if (act && !(p.tune & 2)) {
-            const uint8_t* sl = ring + (size_t)slot * kSlotBytes;
-            w0 = *reinterpret_cast<const uint4*>(sl + u * 1024 + lane * 16);
-            w1 = *reinterpret_cast<const uint4*>(sl + u * 1024 + 512 + lane * 16);
-            const int kt = kUnits * si + u;
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + kt * 64 + t * 16);
-            xa = xp[0]; xb = xp[1];
-            const uint8_t* szs = sl + kUnits * 1024 + szo;
-            s00 = *reinterpret_cast<const uint32_t*>(szs); s01 = *reinterpret_cast<const uint32_t*>(szs + 32);
-            s10 = *reinterpret_cast<const uint32_t*>(szs + kSzSeg); s11 = *reinterpret_cast<const uint32_t*>(szs + kSzSeg + 32);
-            xu = xsum[kt];
+        // Hot loop.  Everything is addressed by 32-bit shared-memory offsets computed once per row pair; a stage costs a
+        // warp one barrier test, nine shared loads, one arrive, eight (shift + 4 logic + MMA) groups and two folds.
+        uint32_t x_addr = xs_s + (uint32_t)(kUnits * si0 + u) * 128u + (uint32_t)t * 32u;     // this lane's 16 activations
+        uint32_t xsum_addr = xsum_s + (uint32_t)(kUnits * si0 + u) * 4u;
+        int left = geo.KT - kUnits * si0 - u;              // > 0 while this warp's unit exists in the stage
+        for (int si = si0; si < si1; ++si, x_addr += kUnits * 128u, xsum_addr += kUnits * 4u, left -= kUnits) {
+          const uint32_t fbar = full_s + slot * 8u;
+          bool ok = mbar_test(fbar, par);
+          if (!ok) ok = ring_wait(full + slot, par, c, 0x200u | slot);
+          const uint32_t sl = ring_s + slot * (uint32_t)kSlotBytes;
+          if (ok && left > 0 && !(p.tune & 2)) {
+            const uint4 w0 = lds128(sl + w_off), w1 = lds128(sl + w_off + 512u);
+            const uint4 xa = lds128(x_addr), xb = lds128(x_addr + 16u);
+            const uint32_t s00 = lds32(sl + sz_off), s01 = lds32(sl + sz_off + 32u);
+            const uint32_t s10 = lds32(sl + sz_off + kSzSeg), s11 = lds32(sl + sz_off + kSzSeg + 32u);
+            const float xu = __uint_as_float(lds32(xsum_addr));
+            __syncwarp();
+            if (lane == 0) mbar_arrive_s(empty_s + slot * 8u);   // the unit is in registers: the producer may refill the slot
+            if (!(p.tune & 1)) {
+              // two chains (tile 0, tile 1) of four MMAs
+              float d0[4], d1[4];
+              mma_word<true>(d0, w0.x, xa.x, xa.y); mma_word<true>(d1, w1.x, xa.x, xa.y);
+              mma_word<false>(d0, w0.y, xa.z, xa.w); mma_word<false>(d1, w1.y, xa.z, xa.w);
+              mma_word<false>(d0, w0.z, xb.x, xb.y); mma_word<false>(d1, w1.z, xb.x, xb.y);
+              mma_word<false>(d0, w0.w, xb.z, xb.w); mma_word<false>(d1, w1.w, xb.z, xb.w);
+              fold_unit(d0, s00, s01, xu, f00, f01);
+              fold_unit(d1, s10, s11, xu, f10, f11);
+            }
+          } else {
+            __syncwarp();
+            if (lane == 0) mbar_arrive_s(empty_s + slot * 8u);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(empty + slot);     // the unit is in registers: the producer may refill the slot
           if (++slot == (uint32_t)S) { slot = 0; par ^= 1u; }
-          if (act && !(p.tune & 1)) {
-            // eight independent MMAs (a legacy mma.sync result takes a few hundred cycles to come back on this part: a
-            // chain through one accumulator would serialise those latencies), summed per tile afterwards
-            float e0[4][4], e1[4][4];
-            mma_word<true>(e0[0], w0.x, xa.x, xa.y); mma_word<true>(e1[0], w1.x, xa.x, xa.y);
-            mma_word<true>(e0[1], w0.y, xa.z, xa.w); mma_word<true>(e1[1], w1.y, xa.z, xa.w);
-            mma_word<true>(e0[2], w0.z, xb.x, xb.y); mma_word<true>(e1[2], w1.z, xb.x, xb.y);
-            mma_word<true>(e0[3], w0.w, xb.z, xb.w); mma_word<true>(e1[3], w1.w, xb.z, xb.w);
-            float d0[4], d1[4];
-            d0[0] = (e0[0][0] + e0[1][0]) + (e0[2][0] + e0[3][0]); d0[2] = (e0[0][2] + e0[1][2]) + (e0[2][2] + e0[3][2]);
-            d1[0] = (e1[0][0] + e1[1][0]) + (e1[2][0] + e1[3][0]); d1[2] = (e1[0][2] + e1[1][2]) + (e1[2][2] + e1[3][2]);
-            fold_unit(d0, s00, s01, xu, f00, f01);
-            fold_unit(d1, s10, s11, xu, f10, f11);
-          }
         }
         // ---- this CTA's share of row pair rp is complete ----
         if (tl) tl[3] = clock64();
@@ -532,6 +575,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
       }
       if (tl) tl[4] = clock64();
     }
+    // Every launch advances the arrival count by one more round (nobody waits for it): the epochs derived from the
+    // count stay unique per phase also across launches that contain no barrier.
+    if (tid == 0 && !*s_abort) asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
   }
   __syncthreads();
 }
@@ -582,24 +628,25 @@ GRM_API int grm_mega_max_parts(int rp, int K, int grid) {
 
 // Runs phases [first, first + count) of the device-resident table `phases` (MegaPhase records, see ops/mega.py) for one
 // activation row.  h: the fp32 residual row read by the PRO_NORM phases.  sync: 4 zeroed uints that live as long as
-// the table (barrier arrivals, generation, abort word; zero them again after a reported timeout).  parts / cnt: partial
-// sum scratch [max row pairs][pstride][32] floats and zeroed per-row-pair counters.  max_k: largest K of the table.
+// the table ([0] barrier arrivals, which only grow: every launch adds count * grid; [2] abort word; zero both again after
+// a reported timeout).  parts: partial sum scratch, [max row pairs][pstride][32] {value, epoch} pairs (8 bytes each),
+// zero before first use.  max_k: largest K of the table.
 // recv / world / rank / ar_rows: tensor-parallel exchange regions ([2][world][ar_rows] {value, epoch} pairs per rank,
 // zero before first use) for phases with ar_region >= 0; world <= 1 disables.  Every rank must run the same launch
 // sequence.  cooperative = 0 launches without the co-residency guarantee (one CTA per SM fits when nothing else runs on
 // the device).  timeline: optional device buffer of count * grid * 5 int64 that receives per-phase SM clock stamps of
 // every CTA (see MegaParams), null in normal operation.  Returns -2 on an unsupported shape.
-GRM_API int grm_decode_mega(const void* phases, int first, int count, const void* h, void* sync, void* parts, void* cnt, int pstride,
+GRM_API int grm_decode_mega(const void* phases, int first, int count, const void* h, void* sync, void* parts, int pstride,
                             int max_k, const void* const* recv, int world, int rank, int ar_rows, unsigned int spin, int cooperative,
                             void* timeline, void* stream) {
-  if (!phases || count < 1 || !sync || !parts || !cnt || pstride < 1 || max_k < 64 || (max_k & 63) || max_k > kMaxK)
+  if (!phases || count < 1 || !sync || !parts || pstride < 1 || max_k < 64 || (max_k & 63) || max_k > kMaxK)
     return -2;
   if (world > 8 || (world > 1 && (!recv || rank < 0 || rank >= world || ar_rows < 32))) return -2;
   const int sms = mega_sms();
   if (sms < 1) return (int)cudaErrorInvalidDevice;
   MegaParams p;
   p.phases = (const MegaPhase*)phases; p.first = first; p.count = count; p.h = (const float*)h;
-  p.sync = (unsigned int*)sync; p.parts = (float*)parts; p.cnt = (unsigned int*)cnt; p.pstride = pstride;
+  p.sync = (unsigned int*)sync; p.parts = (uint2*)parts; p.pstride = pstride;
   p.status = grm_status_ptr(); p.spin = spin ? spin : 2000000u;
   p.xs_bytes = (max_k * 2 + 127) & ~127;
   p.xsum_bytes = ((max_k / 64) * 4 + 127) & ~127;

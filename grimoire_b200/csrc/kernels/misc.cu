@@ -7,12 +7,14 @@
 
 namespace {
 
-// table bf16 [V][H] -> h fp32 [M][H]; ids < 0 or >= V give a zero row.
+// table bf16 [V][H] -> h fp32 [M][H]; ids < 0 or >= V give a zero row and record GRM_ERR_BOUNDS (detail = row) in the
+// status block: the access is skipped, never made.
 __global__ void embed_kernel(const int* __restrict__ ids, const bf16* __restrict__ table, float* __restrict__ h, int H, int V,
-                             int ldh, float scale) {
+                             int ldh, float scale, unsigned int* status) {
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool ok = id >= 0 && id < V;
+  if (!ok && threadIdx.x == 0) grm_set_error(status, GRM_ERR_BOUNDS, 0x10000u | (unsigned int)(row & 0xffff));
   const uint2* src = reinterpret_cast<const uint2*>(table + (size_t)(ok ? id : 0) * H);
   float4* dst = reinterpret_cast<float4*>(h + (size_t)row * ldh);
   for (int c = threadIdx.x; c < (H >> 2); c += blockDim.x) {
@@ -106,7 +108,7 @@ __global__ void incr_pos_kernel(int* __restrict__ pos, int n, int by) {
 
 GRM_API int grm_embed(const void* ids, const void* table, void* h, int M, int H, int V, int ldh, float scale, void* stream) {
   if (H & 3) return -2;
-  embed_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const int*)ids, (const bf16*)table, (float*)h, H, V, ldh, scale);
+  embed_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const int*)ids, (const bf16*)table, (float*)h, H, V, ldh, scale, grm_status_ptr());
   GRM_LAUNCH_RET();
 }
 

@@ -53,6 +53,7 @@ class Engine:
         self.h_stage = torch.zeros(3, lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
         self.h_next = torch.zeros(lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
         self.prefix_cache = None
+        self._verify: dict = {}           # slot -> (handle, first row, rows, first position) of its last verify block
         self._reused_head_logits = None
         self.graphs: dict[tuple, "torch.cuda.CUDAGraph"] = {}      # (rows, splits, distinct sequences)
         self.counters = {"prefill_rows": 0, "decode_steps": 0, "decode_rows": 0, "graph_replays": 0, "kernel_launches": 0}
@@ -100,7 +101,12 @@ class Engine:
         return n
 
     def rollback(self, seq: SeqSlot, length: int) -> None:
-        """Forget cached positions >= length (rows of a verify block past the accepted prefix)."""
+        """Forget cached positions >= length (rows of a verify block past the accepted prefix); recurrent layers get
+        their state of position ``length`` back (commit_spec_prefix, grimoire.cpp:12407-12482)."""
+        v = self._verify.pop(seq.slot, None) if self._verify else None
+        if v is not None:
+            handle, row0, rows, pos0 = v
+            self.model.commit_verify(handle, seq.slot, row0, length - pos0, rows, pos0, self.decode_buf)
         if seq.length > length or len(seq.pages) * PAGE > length + PAGE:
             self.kv.truncate(seq, length)
 
@@ -205,8 +211,8 @@ class Engine:
     def _splits_for(self, M: int, max_len: int) -> int:
         return K.decode_splits(max_len, M, self.model.geom.Hkv)
 
-    def _run_rows(self, M: int, splits: int, distinct: bool = False) -> torch.Tensor:
-        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct)
+    def _run_rows(self, M: int, splits: int, distinct: bool = False, runs=None) -> torch.Tensor:
+        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct, runs=runs)
         logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
         pp = getattr(self.model, "pp", None)
         if logits is not None:
@@ -228,6 +234,25 @@ class Engine:
         if not getattr(self.model, "supports_verify_rows", True) and len({s.slot for s in seqs}) != M:
             # recurrent layers advance one token per conversation per step: no multi-row verify blocks
             raise NotImplementedError("this model cannot score several rows of one conversation in one step")
+        runs = None
+        self._verify = {}
+        if hasattr(self.model, "begin_verify") and len({s.slot for s in seqs}) != M:
+            # verify blocks over recurrent layers: group the rows into runs and record what a rollback needs
+            groups, i = [], 0
+            while i < M:
+                n = 1
+                while i + n < M and seqs[i + n].slot == seqs[i].slot and positions[i + n] == positions[i] + n:
+                    n += 1
+                groups.append((seqs[i].slot, i, n, positions[i]))
+                i += n
+            if len({g[0] for g in groups}) != len(groups):
+                raise ValueError("rows of one conversation must be consecutive positions in one block")
+            i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=self.device)
+            runs = (i32([g[0] for g in groups]), i32([g[1] for g in groups]), i32([g[2] for g in groups]))
+            blocks = [g for g in groups if g[2] > 1]
+            handle = self.model.begin_verify(i32([g[0] for g in blocks]), M)
+            self._verify = {g[0]: (handle, g[1], g[2], g[3]) for g in blocks}
+            use_graph = False
         max_len = 0
         for s, p in zip(seqs, positions):
             self.kv.ensure(s, p + 1)
@@ -247,7 +272,9 @@ class Engine:
             g.replay()
             self.counters["graph_replays"] += 1
         else:
-            self._run_rows(M, splits, distinct)
+            self._run_rows(M, splits, distinct, runs)
+        if runs is not None:
+            self.model.end_verify()
         self.h_next[:M].copy_(self.decode_buf.next_ids[:M], non_blocking=True)
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()

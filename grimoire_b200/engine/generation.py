@@ -107,6 +107,38 @@ class CopyDrafter:
         pass
 
 
+class OracleDrafter:
+    """Drafts with a dialled acceptance rate, for measuring the verify path on models whose real draft head predicts
+    nothing useful (random weights): it knows the continuation plain greedy decoding produces (``truth`` = prompt +
+    greedy output) and proposes it, replacing a draft by a wrong token with probability ``1 - accept`` per position
+    (a deterministic hash of the position, so runs repeat).  The verified output is still the target's own."""
+
+    def __init__(self, truth: Sequence[int], accept: float = 0.7, vocab: int = 1 << 30, seed: int = 0):
+        self.truth, self.accept, self.vocab, self.seed = list(truth), float(accept), vocab, seed
+
+    def _u(self, pos: int) -> float:
+        x = (pos * 0x9E3779B97F4A7C15 + self.seed * 0xBF58476D1CE4E5B9 + 0x94D049BB133111EB) & ((1 << 64) - 1)
+        x ^= x >> 31
+        x = (x * 0xD6E8FEB86659FD93) & ((1 << 64) - 1)
+        x ^= x >> 29
+        return (x >> 11) / float(1 << 53)
+
+    def propose(self, engine, seq, last_token: int, depth: int) -> list[int]:
+        pos = seq.length + 1                      # index in ``truth`` of the token that follows ``last_token``
+        out = []
+        for j in range(depth):
+            if pos + j >= len(self.truth):
+                break
+            t = self.truth[pos + j]
+            if self._u(pos + j) >= self.accept:
+                t = (t + 1) % self.vocab          # a wrong draft: everything after it is rejected too
+            out.append(t)
+        return out
+
+    def observe(self, engine, seq, accepted_tokens, row0: int = 0) -> None:
+        pass
+
+
 def first_token_of(logits) -> int:
     """Greedy choice from a 1-D logits tensor, ties to the lowest index."""
     import torch

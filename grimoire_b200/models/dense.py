@@ -62,6 +62,9 @@ class RowBatch:
     # prefill of several fresh prompts in one pass: (first row, rows) per prompt, rows of a prompt contiguous and at
     # positions 0..rows-1 of its own sequence (admit_batch, grimoire.cpp:12071-12146); None = one sequence
     segments: Optional[list] = None
+    # decode with verify blocks on a model with recurrent layers: (run_slot, run_start, run_len) int32 device tensors,
+    # one run per maximal group of rows that are consecutive positions of one sequence; None = every row is its own run
+    runs: Optional[tuple] = None
 
 
 class Buffers:

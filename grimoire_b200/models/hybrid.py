@@ -120,7 +120,8 @@ class HybridModel:
         self.ep = None                   # parallel.ep.ExpertParallel when the experts are sharded over ranks
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self.ep_rank, self.ep_world = 0, 1
-        self.supports_verify_rows = False
+        self.supports_verify_rows = True       # verify blocks: rows run as one recurrent run, rejected rows are undone by replay
+        self._vtrace = None                    # per-layer conv inputs / gate inputs of the verify step in flight
         self.Hq, self.Hkv = cfg.num_attention_heads, cfg.num_key_value_heads
         self.Hk, self.Hv, self.Dk, self.Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.gdn_channels = 2 * self.Hk * self.Dk + self.Hv * self.Dv
@@ -149,6 +150,57 @@ class HybridModel:
     def load_slot(self, slot: int, snap) -> None:
         self.state[:, slot].copy_(snap[0])
         self.ring[:, slot].copy_(snap[1])
+
+    # ------------------------------------------------------------------------------------------
+    # speculative verify blocks over recurrent layers
+    # ------------------------------------------------------------------------------------------
+    def begin_verify(self, slots: torch.Tensor, rows: int):
+        """Call before a decode step that contains verify blocks (several consecutive rows of one conversation).  The
+        recurrent layers run a block as one run, so after the step their state has consumed every row, including drafts
+        that will be rejected.  This records what is needed to undo that: a snapshot of the state of ``slots`` and, per
+        DeltaNet layer, the conv inputs and gate inputs of every row (the reference's verify kernels leave the state
+        untouched and save k / v / a / beta per row instead, src/deltanet.cpp:368-460; its replay is :461-628)."""
+        n_gdn = self.state.shape[0]
+        tr = self._vtrace_buf if getattr(self, "_vtrace_buf", None) is not None and self._vtrace_buf["pre"].shape[1] >= rows else None
+        if tr is None:
+            tr = {"pre": torch.zeros(n_gdn, rows, self.gdn_channels, dtype=torch.bfloat16, device=self.device),
+                  "ab": torch.zeros(n_gdn, rows, 2 * self.Hv, dtype=torch.float32, device=self.device)}
+            self._vtrace_buf = tr
+        self._vtrace = tr
+        return {"snap": self.save_recurrent(slots), "slots": [int(v) for v in slots.tolist()], "trace": tr}
+
+    def end_verify(self) -> None:
+        self._vtrace = None
+
+    def commit_verify(self, handle, slot: int, row0: int, keep: int, rows: int, pos0: int, buf: "HybridBuffers") -> None:
+        """Make the recurrent state of ``slot`` the state after the first ``keep`` of the ``rows`` rows of its verify block
+        (rows row0.. of the step, first position pos0): nothing to do when every row was accepted; otherwise the
+        snapshot comes back and the kept rows are replayed through conv + delta rule from the recorded inputs."""
+        if keep >= rows:
+            return
+        idx, st, rg = handle["snap"]
+        j = handle["slots"].index(slot)
+        self.state[:, slot].copy_(st[:, j])
+        self.ring[:, slot].copy_(rg[:, j])
+        if keep <= 0:
+            return
+        dev = self.device
+        tr = handle["trace"]
+        row_seq = torch.full((keep,), slot, dtype=torch.int32, device=dev)
+        row_pos = torch.arange(pos0, pos0 + keep, dtype=torch.int32, device=dev)
+        run_slot = torch.tensor([slot], dtype=torch.int32, device=dev)
+        run_start = torch.zeros(1, dtype=torch.int32, device=dev)
+        run_len = torch.tensor([keep], dtype=torch.int32, device=dev)
+        touched = torch.tensor([slot], dtype=torch.long, device=dev)
+        conv, z, o = buf.gdn_conv[:keep], buf.gdn_z[:keep], buf.gdn_o[:keep]
+        for L in self.layers:
+            if L.kind != "gdn":
+                continue
+            si = L.state_index
+            pre = tr["pre"][si, row0: row0 + keep]
+            Hb.conv4_silu(pre, L.conv_w, self.ring[si], self.ring_tmp, row_seq, row_pos, conv, touched)
+            Hb.gdn_runs(conv, tr["ab"][si, row0: row0 + keep], z, L.A_log, L.dt_bias, L.gdn_norm, self.cfg.rms_norm_eps, self.state[si],
+                        run_slot, run_start, run_len, o, self.Hk, self.Hv, self.Dk, self.Dv)
 
     def attach_ep(self, group, max_rows: int, fused=None):
         """Shard the MoE layers over ``group`` (the model must have been built with the matching
@@ -429,9 +481,13 @@ class HybridModel:
             run_start = torch.zeros(1, dtype=torch.int32, device=self.device)
             run_len = torch.tensor([M], dtype=torch.int32, device=self.device)
             touched = torch.tensor([rb.seq_slot], dtype=torch.long, device=self.device)
+        elif rb.runs is not None:
+            run_slot, run_start, run_len = rb.runs
+            touched = run_slot.long()
         else:
             run_slot, run_start, run_len = rb.row_seq, buf.run_start[:M], buf.run_len[:M]
             touched = rb.row_seq.long()
+        tr = self._vtrace
         for L in self.layers:
             K.add_rmsnorm(h, L.in_norm, x, eps, off)
             if L.kind == "gdn":
@@ -439,6 +495,9 @@ class HybridModel:
                 L.in_qkv(x, buf.gdn_qkv[:M], "bf16")
                 L.in_z(x, buf.gdn_z[:M], "bf16")
                 L.in_ab(x, buf.gdn_ab[:M], "f32")
+                if tr is not None:
+                    tr["pre"][si, :M].copy_(buf.gdn_qkv[:M])
+                    tr["ab"][si, :M].copy_(buf.gdn_ab[:M])
                 Hb.conv4_silu(buf.gdn_qkv[:M], L.conv_w, self.ring[si], self.ring_tmp, rb.row_seq, rb.row_pos, buf.gdn_conv[:M], touched)
                 Hb.gdn_runs(buf.gdn_conv[:M], buf.gdn_ab[:M], buf.gdn_z[:M], L.A_log, L.dt_bias, L.gdn_norm, eps, self.state[si],
                             run_slot, run_start, run_len, buf.gdn_o[:M], self.Hk, self.Hv, self.Dk, self.Dv, chunked=prefill and M >= 32)

@@ -68,8 +68,7 @@ class MegaTable:
         self.max_k = max(p.K for p in phases)
         self.pstride = max(1, max(lib.grm_mega_max_parts(p.rp, p.K, grid) for p in phases) - 1)
         max_rp = max(p.rp for p in phases)
-        self.parts = torch.zeros(max_rp * self.pstride * 32, dtype=torch.float32, device=self.device)
-        self.cnt = torch.zeros(max_rp, dtype=torch.int32, device=self.device)
+        self.parts = torch.zeros(max_rp * self.pstride * 32 * 2, dtype=torch.float32, device=self.device)    # {value, epoch} pairs
         self.tp = tp
         self.spin = int(os.environ.get("GRIMOIRE_MEGA_SPIN", "0"))
         if os.environ.get("GRIMOIRE_MEGA_TUNE"):
@@ -88,14 +87,14 @@ class MegaTable:
             recv, world, rank, rows = tp.mega_recv.ptr_array(), tp.world, tp.rank, tp.mega_rows
         code = _native.cuda().grm_decode_mega(
             _native.ptr(self.table), ctypes.c_int(first), ctypes.c_int(count), _native.ptr(self.h), _native.ptr(self.sync),
-            _native.ptr(self.parts), _native.ptr(self.cnt), ctypes.c_int(self.pstride), ctypes.c_int(self.max_k), recv,
+            _native.ptr(self.parts), ctypes.c_int(self.pstride), ctypes.c_int(self.max_k), recv,
             ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int(rows), ctypes.c_uint(self.spin), ctypes.c_int(COOP), _native.ptr(timeline), _native.stream_ptr())
         _native.check(code, f"decode_mega phases {first}..{first + count - 1}")
 
     def reset(self) -> None:
         """Clear the barrier words after a reported timeout (the arrival count may be left mid-way)."""
         self.sync.zero_()
-        self.cnt.zero_()
+        self.parts.zero_()
 
 
 def dense_supported(model) -> bool:

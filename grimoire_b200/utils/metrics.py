@@ -1,6 +1,6 @@
 """Serving metrics in the Prometheus text format (``GET /metrics``) and an optional JSONL step log.
 
-The reference only prints to stdout (capability banner, SPEC_STATS lines; SURVEY: no Prometheus, no
+The reference only prints to stdout (capability banner, SPEC_STATS lines; it has no Prometheus endpoint and no
 structured logs); this adds tok/s counters, a TTFT histogram, queue depth, KV pages in use,
 speculative accept length and per-collective byte counters."""
 from __future__ import annotations

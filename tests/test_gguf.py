@@ -1,6 +1,7 @@
-"""GGUF: block decoders against llama.cpp-derived golden vectors (read in place from the reference
-checkout when it is present: b"GGLD", type, n_expected, raw_size, raw blocks, expected fp32), the
-container parser on a file written by the test, and the name adapter."""
+"""GGUF: block decoders against llama.cpp-derived golden vectors (``GRIMOIRE_GGUF_GOLDEN_DIR`` names a directory of
+``<TYPE>.bin`` files: b"GGLD", type, n_expected, raw_size, raw blocks, expected fp32; the reference project ships them
+under tests/gguf/data), the container parser on a file written by the test, and the name adapter."""
+import os
 import struct
 from pathlib import Path
 
@@ -9,7 +10,15 @@ import torch
 
 from grimoire_b200.formats import gguf
 
-GOLD = Path("/root/reference/tests/gguf/data")
+def _golden_dir() -> Path:
+    env = os.environ.get("GRIMOIRE_GGUF_GOLDEN_DIR")
+    if env:
+        return Path(env)
+    # a reference checkout beside this repository, when there is one
+    return Path(__file__).resolve().parents[2] / "reference" / "tests" / "gguf" / "data"
+
+
+GOLD = _golden_dir()
 DECODED = ["F32", "F16", "BF16", "F64", "I8", "I16", "I32", "I64", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q8_1", "Q2_K", "Q3_K",
            "Q4_K", "Q5_K", "Q6_K", "Q8_K", "IQ4_NL", "IQ4_XS", "TQ2_0", "MXFP4"]
 

@@ -41,7 +41,7 @@ def test_chunked_prefill_carries_recurrent_state(eng):
     assert float((a - b).abs().max()) < 0.05 * max(1.0, float(b.abs().max())) and int(a.argmax()) == int(b.argmax())
 
 
-def test_batched_decode_equals_solo_and_verify_rows_are_declined(eng):
+def test_batched_decode_equals_solo(eng):
     sa, sb = eng.open(), eng.open()
     la, lb = eng.prefill(sa, _prompt(11, 5)), eng.prefill(sb, _prompt(37, 6))
     ta, tb = int(la.argmax()), int(lb.argmax())
@@ -51,9 +51,56 @@ def test_batched_decode_equals_solo_and_verify_rows_are_declined(eng):
     eng.model.state.copy_(st[0]); eng.model.ring.copy_(st[1])      # undo the step, then decode b alone
     solo, l1 = eng.decode_rows([tb], [sb], [sb.length], return_logits=True)
     assert both[1] == solo[0] and torch.allclose(lg[1], l1[0], atol=5e-3)      # CPU BLAS blocks differ per M
-    with pytest.raises(NotImplementedError):
-        eng.decode_rows([1, 2], [sa, sa], [sa.length, sa.length + 1])
     eng.release(sa), eng.release(sb)
+
+
+@pytest.mark.parametrize("keep", [1, 2, 3])
+def test_verify_block_then_rollback_equals_sequential_decode(eng, keep):
+    """A block of three rows of one conversation runs through the recurrent layers as one run; rolling back to ``keep``
+    rows must leave KV, conv tails and DeltaNet state exactly where ``keep`` single steps leave them."""
+    p = _prompt(29, 8)
+    # sequential path: three single-row steps, logits of each
+    s = eng.open()
+    tok = int(eng.prefill(s, p).argmax())
+    seq_tokens, seq_logits = [tok], []
+    for _ in range(4):
+        nxt, lg = eng.decode_rows([seq_tokens[-1]], [s], [s.length], use_graph=False, return_logits=True)
+        seq_logits.append(lg[0].clone())
+        eng.commit_rows([s], [seq_tokens[-1]], [s.length])
+        seq_tokens.append(int(nxt[0]))
+    eng.release(s)
+    # block path: the same three tokens as one verify block, then keep only the first ``keep``
+    s = eng.open()
+    assert int(eng.prefill(s, p).argmax()) == tok
+    pos0 = s.length
+    block = seq_tokens[:3]
+    if keep < 3:
+        block = block[:keep] + [(seq_tokens[keep] + 1) % 4096] + block[keep + 1:]        # a wrong draft right after the kept rows
+    nxt, lg = eng.decode_rows(block, [s] * 3, [pos0, pos0 + 1, pos0 + 2], use_graph=False, return_logits=True)
+    for i in range(keep):
+        assert int(nxt[i]) == seq_tokens[i + 1]
+        assert float((lg[i] - seq_logits[i]).abs().max()) < 5e-3
+    eng.commit_rows([s] * keep, block[:keep], list(range(pos0, pos0 + keep)))
+    eng.rollback(s, pos0 + keep)
+    assert s.length == pos0 + keep
+    nxt2, lg2 = eng.decode_rows([seq_tokens[keep]], [s], [s.length], use_graph=False, return_logits=True)
+    assert int(nxt2[0]) == seq_tokens[keep + 1]
+    assert float((lg2[0] - seq_logits[keep]).abs().max()) < 5e-3
+    eng.release(s)
+
+
+def test_speculation_on_the_hybrid_model_keeps_greedy_tokens(eng):
+    """Drafts with a mix of right and wrong tokens through verify blocks: the emitted stream equals plain greedy and
+    some drafts are accepted (the reference's hybrid + MTP path, tools/test_spec_e2e.cpp: spec == plain)."""
+    from grimoire_b200.engine.generation import GenerationOptions, OracleDrafter, SpecStats, generate_tokens
+
+    prompt = _prompt(23, 9)
+    plain, _ = generate_tokens(eng, prompt, GenerationOptions(max_new=18, use_graph=False))
+    st = SpecStats()
+    drafter = OracleDrafter(prompt + plain, accept=0.6, vocab=4096, seed=3)
+    spec, _ = generate_tokens(eng, prompt, GenerationOptions(max_new=18, draft_depth=3, drafter=drafter, stats=st, use_graph=False))
+    assert spec == plain
+    assert st.rounds > 0 and 0 < st.accepted < st.drafted
 
 
 def test_gdn_oracle_properties():

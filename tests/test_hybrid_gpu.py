@@ -45,3 +45,37 @@ def test_hybrid_gpu_matches_cpu_path_and_graph_replay():
     b = gpu.generate(prompt, 10, use_graph=True)
     assert a == b
     assert K.status_read()[0] == 0
+
+
+@pytest.mark.parametrize("keep", [1, 2, 4])
+def test_hybrid_verify_block_rollback_equals_sequential_gpu(keep):
+    """A four-row verify block through the DeltaNet layers, rolled back to ``keep`` rows: the next single step must see the
+    state that ``keep`` single steps leave (conv tail, delta-rule state and KV)."""
+    cfg = _cfg()
+    eng = Engine(HybridModel.random(cfg, "cuda", seed=4, max_slots=3), EngineLimits(**LIM))
+    p = torch.randint(0, 4096, (41,), generator=torch.Generator().manual_seed(8)).tolist()
+    s = eng.open()
+    tok = int(eng.prefill(s, p).argmax())
+    toks, logits = [tok], []
+    for _ in range(5):
+        nxt, lg = eng.decode_rows([toks[-1]], [s], [s.length], use_graph=False, return_logits=True)
+        logits.append(lg[0].float().clone())
+        eng.commit_rows([s], [toks[-1]], [s.length])
+        toks.append(int(nxt[0]))
+    eng.release(s)
+    s = eng.open()
+    assert int(eng.prefill(s, p).argmax()) == tok
+    pos0 = s.length
+    block = toks[:4]
+    if keep < 4:
+        block = block[:keep] + [(toks[keep] + 1) % 4096] + block[keep + 1:]
+    nxt, lg = eng.decode_rows(block, [s] * 4, list(range(pos0, pos0 + 4)), use_graph=False, return_logits=True)
+    scale = float(logits[0].abs().max())
+    for i in range(keep):
+        assert float((lg[i].float() - logits[i]).abs().max()) < 0.03 * scale
+    eng.commit_rows([s] * keep, block[:keep], list(range(pos0, pos0 + keep)))
+    eng.rollback(s, pos0 + keep)
+    nxt2, lg2 = eng.decode_rows([toks[keep]], [s], [s.length], use_graph=False, return_logits=True)
+    assert float((lg2[0].float() - logits[keep]).abs().max()) < 0.03 * scale
+    eng.release(s)
+    assert K.status_read()[0] == 0

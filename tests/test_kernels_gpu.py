@@ -460,3 +460,17 @@ def test_decode_attn_with_fused_rope_kv_append_equals_two_kernels(Hq, Hkv, D, ro
     for a, b in ((kv_a.k, kv_b.k), (kv_a.v, kv_b.v), (kv_a.ks, kv_b.ks), (kv_a.vs, kv_b.vs)):
         assert torch.equal(a, b)
     _assert_clean()
+
+
+def test_out_of_range_token_id_is_reported_not_read():
+    """A token id outside the vocabulary gives a zero row and GRM_ERR_BOUNDS in the status block; nothing is read."""
+    table = torch.randn(100, 64, device=DEV).bfloat16()
+    ids = torch.tensor([3, 100, -1, 99], dtype=torch.int32, device=DEV)
+    h = torch.full((4, 64), 7.0, device=DEV)
+    K.embed(ids, table, h)
+    torch.cuda.synchronize()
+    code, detail, n = K.status_read()
+    assert code == 3 and n == 2 and (detail & 0xffff) in (1, 2)
+    assert torch.equal(h[0], table[3].float()) and torch.equal(h[3], table[99].float())
+    assert float(h[1].abs().max()) == 0.0 and float(h[2].abs().max()) == 0.0
+    _assert_clean()

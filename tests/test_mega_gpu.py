@@ -77,7 +77,7 @@ def test_layer_chain_matches_fp32(H, I, Q, group, xmag):
     torch.cuda.synchronize()
     _clean()
     assert torch.allclose(d_h.cpu(), h2, atol=2 * tol["atol"], rtol=2 * tol["rtol"]), float((d_h.cpu() - h2).abs().max())
-    assert int(tab.cnt.abs().sum()) == 0 and int(tab.sync[0]) % tab.grid == 0 and int(tab.sync[2]) == 0
+    assert int(tab.sync[0]) == 2 * 4 * tab.grid and int(tab.sync[2]) == 0       # every launch adds one round per phase
 
 
 def test_phase_runs_are_deterministic_and_graph_replayable():
