@@ -11,15 +11,14 @@
 //     range through a shared-memory ring with cp.async.bulk and simply keeps going into the NEXT phase's range while
 //     the consumers sit in the grid barrier -- weight addresses do not depend on activations, so HBM never drains at
 //     a phase boundary;
-//   * the product runs on the tensor cores with one logic op per nibble pair and no zero-point arithmetic per weight:
-//     a 32-bit word of the layout is exactly the A fragment of an m16n8k16 MMA once each nibble is OR-ed into the
-//     mantissa of fp16 1024 (low nibbles: 1024 + q, high nibbles: 1024 + 16 q); the MMA accumulates
-//     sum (1024 + q) x in fp32 and the epilogue of a 64-column unit subtracts (1024 + zero) * sum(x) and rescales;
+//   * the product runs on the half2 multiply-add pipe at 13 instructions per eight weights (one logic op per nibble
+//     pair builds fp16 {1024 + q}, one subtract / fma removes bias and zero point exactly, one fma multiplies); for a
+//     single activation row that beats the legacy tensor-core path on this part (see word_fma);
 //   * a row pair whose K range straddles two CTAs is finished by the CTA that owns its first stage: the others publish
 //     their partial sums (they meet that row pair first in their range, the owner meets it last), the owner adds them
 //     in CTA order, so results do not depend on timing;
-//   * activations are staged once per phase and CTA as fp16 scaled by a power of two so that |x| <= 1024: no fp16
-//     overflow for outlier activations, the scale is undone in fp32.
+//   * activations are staged once per phase and CTA as fp16 scaled by a power of two so that |x| <= 256: the fp16
+//     partial sums of a 64-column unit cannot overflow whatever the activations are, the scale is undone in fp32.
 // The row-parallel phases can all-reduce their result over tensor-parallel ranks in the same epilogue ({value, epoch}
 // pushes into the peers' receive regions, as in gemv_w4.cu).
 //
@@ -71,7 +70,6 @@ struct MegaParams {
   // optional timeline (null = off): [phase][CTA][5] SM clock values of thread 0 -- phase entered, grid barrier passed,
   // activations staged, last ring stage consumed, row pairs finalised
   long long* timeline;
-  int tune;                       // measurement switches (results become meaningless): 1 = skip the MMAs, 2 = skip the shared-memory reads too
 };
 
 struct Ctx {
@@ -168,30 +166,38 @@ __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint3
   asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));   // (a & mask) | orv
   return r;
 }
-// d (+)= A(w) . B: the word's eight nibbles as fp16 {1024 + q} (rows g) / {1024 + 16 q} (rows g + 8) against four
-// activations (b0: columns 4j, 4j + 1 of the lane's 16, b1: 4j + 2, 4j + 3), every MMA column holding the same row.
-template <bool FIRST>
-__device__ __forceinline__ void mma_word(float (&d)[4], uint32_t w, uint32_t b0, uint32_t b1) {
-  const uint32_t w2 = w >> 8;
-  const uint32_t a0 = lop3_or_and(w, 0x000f000fu, 0x64006400u), a1 = lop3_or_and(w, 0x00f000f0u, 0x64006400u);
-  const uint32_t a2 = lop3_or_and(w2, 0x000f000fu, 0x64006400u), a3 = lop3_or_and(w2, 0x00f000f0u, 0x64006400u);
-  if (FIRST)
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
-  else
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// Eight weights of one 32-bit word (rows g and g + 8, four consecutive columns) times their activations on the half2
+// multiply-add pipe: one logic op per nibble pair builds {1024 + q, 1024 + q'} (odd nibbles: {1024 + 16 q, ...}), one
+// half2 subtract / fma removes the bias together with the zero point exactly, one half2 fma multiplies.  (A legacy
+// mma.sync would do the eight products in one instruction, but on this part it occupies its sub-partition for about nine
+// cycles and does not overlap with the logic ops feeding it: measured, the tensor-core form of this loop runs at half
+// the rate of this one for a single activation row.)
+__device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+__device__ __forceinline__ void word_fma(uint32_t w, __half2 x01, __half2 x23, __half2 c_lo, __half2 c_hi, __half2& a0, __half2& a1) {
+  const __half2 sixteenth = __float2half2_rn(0.0625f);
+  const uint32_t w2 = __umulhi(w, 1u << 24);          // w >> 8 on the multiply pipe (the logic pipe is the busy one)
+  const __half2 l0 = as_h2(lop3_or_and(w, 0x000f000fu, 0x64006400u)), h0 = as_h2(lop3_or_and(w, 0x00f000f0u, 0x64006400u));
+  const __half2 l1 = as_h2(lop3_or_and(w2, 0x000f000fu, 0x64006400u)), h1 = as_h2(lop3_or_and(w2, 0x00f000f0u, 0x64006400u));
+  a0 = __hfma2(__hsub2(l0, c_lo), x01, a0);                    // row g,     columns 4j, 4j + 1
+  a1 = __hfma2(__hfma2(h0, sixteenth, c_hi), x01, a1);         // row g + 8
+  a0 = __hfma2(__hsub2(l1, c_lo), x23, a0);                    // row g,     columns 4j + 2, 4j + 3
+  a1 = __hfma2(__hfma2(h1, sixteenth, c_hi), x23, a1);
 }
 
-// One unit of one 16-row tile folded into the running row sums.  sz word: fp16 scale | bf16(128 + zero) = bf.
-//   rows g:     sum (q - z) x = d0 - (1024 + z) * xu       = d0 - (bf + 896) * xu
-//   rows g + 8: sum (q - z) x = (d2 - (1024 + 16 z) * xu) / 16 = (d2 - (16 bf - 1024) * xu) / 16   (the 1/16 is applied
-//   once, when the row pair is finished)
-__device__ __forceinline__ void fold_unit(const float (&d)[4], uint32_t s_lo, uint32_t s_hi, float xu, float& f_lo, float& f_hi) {
-  const float sc_lo = __half2float(__ushort_as_half((unsigned short)(s_lo & 0xffffu)));
-  const float sc_hi = __half2float(__ushort_as_half((unsigned short)(s_hi & 0xffffu)));
-  f_lo = fmaf(sc_lo, fmaf(-(bf16hi_to_f(s_lo) + 896.f), xu, d[0]), f_lo);
-  f_hi = fmaf(sc_hi, fmaf(-fmaf(bf16hi_to_f(s_hi), 16.f, -1024.f), xu, d[2]), f_hi);
+// One 64-column unit of one 16-row tile: 16 products per row and lane in fp16 (|x| <= 256 after the staging scale and
+// |q - zero| <= 16, so a half accumulates at most 8 * 16 * 256 < 65504), folded into the fp32 row sums with the scale.
+// sz word: fp16 scale | bf16(128 + zero).
+__device__ __forceinline__ void unit_fma(const uint4& w, const uint4& xa, const uint4& xb, uint32_t s_lo, uint32_t s_hi, float& f_lo, float& f_hi) {
+  const __half2 c_lo = __float2half2_rn(bf16hi_to_f(s_lo) + 896.f);        // 1024 + zero
+  const __half2 c_hi = __float2half2_rn(64.f - bf16hi_to_f(s_hi));         // -(64 + zero) = 64 - (128 + zero)
+  __half2 a0 = __float2half2_rn(0.f), a1 = a0, b0 = a0, b1 = a0;
+  word_fma(w.x, as_h2(xa.x), as_h2(xa.y), c_lo, c_hi, a0, a1);
+  word_fma(w.y, as_h2(xa.z), as_h2(xa.w), c_lo, c_hi, b0, b1);
+  word_fma(w.z, as_h2(xb.x), as_h2(xb.y), c_lo, c_hi, a0, a1);
+  word_fma(w.w, as_h2(xb.z), as_h2(xb.w), c_lo, c_hi, b0, b1);
+  const float2 r0 = __half22float2(__hadd2(a0, b0)), r1 = __half22float2(__hadd2(a1, b1));
+  f_lo = fmaf(__low2float(as_h2(s_lo)), r0.x + r0.y, f_lo);
+  f_hi = fmaf(__low2float(as_h2(s_hi)), r1.x + r1.y, f_hi);
 }
 
 // Stage geometry of a phase
@@ -272,7 +278,7 @@ __device__ void stage_x(const MegaPhase& ph, const float* h, __half* xs, float* 
     amax *= rnorm * 1.01f;                                           // bound of |x| after the bf16 rounding below
   }
   int e = 0;
-  if (amax > 1024.f && amax < 3.0e38f) e = ilogbf(amax) - 9;        // amax * 2^-e < 1024
+  if (amax > 256.f && amax < 3.0e38f) e = ilogbf(amax) - 7;         // amax * 2^-e < 256
   const float scale = __int_as_float((127 - e) << 23);
   inv_scale = __int_as_float((127 + e) << 23);
 #pragma unroll
@@ -297,22 +303,12 @@ __device__ void stage_x(const MegaPhase& ph, const float* h, __half* xs, float* 
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
     }
     uint32_t o[4];
-    float s8 = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const __half2 hh = __floats2half2_rn(v[2 * j] * scale, v[2 * j + 1] * scale);
       o[j] = *reinterpret_cast<const uint32_t*>(&hh);
-      const float2 f = __half22float2(hh);
-      s8 += f.x + f.y;
     }
-    // the unit's sum as the tensor cores will see it (fp16-rounded values); lanes 8k..8k+7 hold one unit
-    s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
-    s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
-    s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
-    if (idx < nv) {
-      *reinterpret_cast<uint4*>(xs + 8 * idx) = make_uint4(o[0], o[1], o[2], o[3]);
-      if ((lane & 7) == 0) xsum[idx >> 3] = s8;
-    }
+    if (idx < nv) *reinterpret_cast<uint4*>(xs + 8 * idx) = make_uint4(o[0], o[1], o[2], o[3]);
   }
   cons_bar();
 }
@@ -415,7 +411,10 @@ __device__ void finalize_pair(const MegaParams& p, const MegaPhase& ph, const Ge
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaParams p) {
+// BPS = CTAs per SM.  Two CTAs of 16 consumer warps each double the warps that hide the latency of the dependent
+// half2 chains (at 56 registers a thread and half the ring each); one CTA keeps the deeper ring.
+template <int BPS>
+__global__ void __launch_bounds__(kThreads, BPS) decode_mega_kernel(const MegaParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __half* xs = reinterpret_cast<__half*>(smem);
   float* xsum = reinterpret_cast<float*>(smem + p.xs_bytes);
@@ -447,7 +446,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
     if (lane < 3) {
       const uint32_t ring_s = smem_u32(ring), full_s = smem_u32(full), empty_s = smem_u32(empty);
       const uint32_t dst_off = lane == 0 ? 0u : (uint32_t)(kUnits * 1024 + (lane - 1) * kSzSeg);
-      uint32_t slot = 0, par = 0, issued = 0;
+      uint32_t issued = 0;
+      const uint32_t smask = (uint32_t)S - 1u, sshift = (uint32_t)__ffs(S) - 1u;
       bool live = true;
       for (int pi = 0; pi < p.count && live; ++pi) {
         const MegaPhase ph = p.phases[p.first + pi];
@@ -459,6 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
         const uint8_t* wsrc = reinterpret_cast<const uint8_t*>(ph.w) + ((size_t)rp * geo.KT + (size_t)kUnits * si) * 1024;
         const uint8_t* szb = reinterpret_cast<const uint8_t*>(ph.sz);
         for (long long s = geo.sb; s < geo.se; ++s) {
+          const uint32_t slot = issued & smask, par = (issued >> sshift) & 1u;
           // slot reuse: wait until the consumers released its previous contents (parity of the previous round)
           if (issued >= (uint32_t)S && !mbar_test(empty_s + slot * 8u, par ^ 1u) && !ring_wait(empty + slot, par ^ 1u, c, 0x100u | slot)) live = false;
           live = __all_sync(0x7u, live);
@@ -474,17 +475,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
                        ::"r"(ring_s + slot * (uint32_t)kSlotBytes + dst_off), "l"(src), "r"(bytes), "r"(fb) : "memory");
           wsrc += (size_t)nu << 10;
           ++issued;
-          if (++slot == (uint32_t)S) { slot = 0; par ^= 1u; }
           if (++si == geo.SPR) { si = 0; ++rp; }
         }
       }
       if (!live && lane == 0) {
         // a wait gave up: make sure none of this CTA's copies is still in flight before shared memory goes away
-        uint32_t sl = slot, pr = par;
         const uint32_t back = issued < (uint32_t)S ? issued : (uint32_t)S;
-        for (uint32_t k = 0; k < back; ++k) {
-          if (sl == 0) { sl = (uint32_t)S; pr ^= 1u; }
-          --sl;
+        for (uint32_t k = issued - back; k < issued; ++k) {
+          const uint32_t sl = k & smask, pr = (k >> sshift) & 1u;
           for (unsigned int i = 0; i < c.spin && !mbar_try_wait(full + sl, pr); ++i) __nanosleep(64);
         }
       }
@@ -493,10 +491,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
     // ================= consumers =================
     const int g = lane >> 2, t = lane & 3;
     const int u = warp;                                // this warp's unit of every stage (both 16-row tiles)
-    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(xs), xsum_s = smem_u32(xsum);
+    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(xs);
     const uint32_t full_s = smem_u32(full), empty_s = smem_u32(empty);
     const uint32_t w_off = (uint32_t)(u * 1024 + lane * 16);
-    uint32_t slot = 0, par = 0, flushes = 0;
+    uint32_t it = 0, flushes = 0;
+    const uint32_t smask = (uint32_t)S - 1u, sshift = (uint32_t)__ffs(S) - 1u;      // S is a power of two
     const unsigned int gen0 = ld_acquire_gpu(p.sync) / (unsigned int)nC;      // barrier rounds completed before this launch
     for (int pi = 0; pi < p.count; ++pi) {
       const MegaPhase ph = p.phases[p.first + pi];
@@ -533,41 +532,37 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
         // Hot loop.  Everything is addressed by 32-bit shared-memory offsets computed once per row pair; a stage costs a
         // warp one barrier test, nine shared loads, one arrive, eight (shift + 4 logic + MMA) groups and two folds.
         uint32_t x_addr = xs_s + (uint32_t)(kUnits * si0 + u) * 128u + (uint32_t)t * 32u;     // this lane's 16 activations
-        uint32_t xsum_addr = xsum_s + (uint32_t)(kUnits * si0 + u) * 4u;
         int left = geo.KT - kUnits * si0 - u;              // > 0 while this warp's unit exists in the stage
-        for (int si = si0; si < si1; ++si, x_addr += kUnits * 128u, xsum_addr += kUnits * 4u, left -= kUnits) {
+        for (int si = si0; si < si1; ++si, ++it, x_addr += kUnits * 128u, left -= kUnits) {
+          // the ring has a power-of-two number of slots: slot and parity are bit fields of the running stage counter
+          const uint32_t slot = it & smask, par = (it >> sshift) & 1u;
           const uint32_t fbar = full_s + slot * 8u;
           bool ok = mbar_test(fbar, par);
           if (!ok) ok = ring_wait(full + slot, par, c, 0x200u | slot);
           const uint32_t sl = ring_s + slot * (uint32_t)kSlotBytes;
-          if (ok && left > 0 && !(p.tune & 2)) {
+          if (ok && left > 0) {
             const uint4 w0 = lds128(sl + w_off), w1 = lds128(sl + w_off + 512u);
             const uint4 xa = lds128(x_addr), xb = lds128(x_addr + 16u);
             const uint32_t s00 = lds32(sl + sz_off), s01 = lds32(sl + sz_off + 32u);
             const uint32_t s10 = lds32(sl + sz_off + kSzSeg), s11 = lds32(sl + sz_off + kSzSeg + 32u);
-            const float xu = __uint_as_float(lds32(xsum_addr));
             __syncwarp();
             if (lane == 0) mbar_arrive_s(empty_s + slot * 8u);   // the unit is in registers: the producer may refill the slot
-            if (!(p.tune & 1)) {
-              // two chains (tile 0, tile 1) of four MMAs
-              float d0[4], d1[4];
-              mma_word<true>(d0, w0.x, xa.x, xa.y); mma_word<true>(d1, w1.x, xa.x, xa.y);
-              mma_word<false>(d0, w0.y, xa.z, xa.w); mma_word<false>(d1, w1.y, xa.z, xa.w);
-              mma_word<false>(d0, w0.z, xb.x, xb.y); mma_word<false>(d1, w1.z, xb.x, xb.y);
-              mma_word<false>(d0, w0.w, xb.z, xb.w); mma_word<false>(d1, w1.w, xb.z, xb.w);
-              fold_unit(d0, s00, s01, xu, f00, f01);
-              fold_unit(d1, s10, s11, xu, f10, f11);
-            }
+            unit_fma(w0, xa, xb, s00, s01, f00, f01);
+            unit_fma(w1, xa, xb, s10, s11, f10, f11);
           } else {
             __syncwarp();
             if (lane == 0) mbar_arrive_s(empty_s + slot * 8u);
           }
-          if (++slot == (uint32_t)S) { slot = 0; par ^= 1u; }
         }
         // ---- this CTA's share of row pair rp is complete ----
         if (tl) tl[3] = clock64();
         float (*rb)[32] = reinterpret_cast<float (*)[32]>(red + (flushes & 1u) * kCW * 32);
-        if (t == 0) { rb[warp][g] = f00; rb[warp][g + 8] = f01 * 0.0625f; rb[warp][16 + g] = f10; rb[warp][24 + g] = f11 * 0.0625f; }
+        // the four lanes of a row group hold disjoint column quarters
+        f00 += __shfl_xor_sync(0xffffffffu, f00, 1); f00 += __shfl_xor_sync(0xffffffffu, f00, 2);
+        f01 += __shfl_xor_sync(0xffffffffu, f01, 1); f01 += __shfl_xor_sync(0xffffffffu, f01, 2);
+        f10 += __shfl_xor_sync(0xffffffffu, f10, 1); f10 += __shfl_xor_sync(0xffffffffu, f10, 2);
+        f11 += __shfl_xor_sync(0xffffffffu, f11, 1); f11 += __shfl_xor_sync(0xffffffffu, f11, 2);
+        if (t == 0) { rb[warp][g] = f00; rb[warp][g + 8] = f01; rb[warp][16 + g] = f10; rb[warp][24 + g] = f11; }
         cons_bar();
         if (warp == (int)(flushes % kCW)) finalize_pair(p, ph, geo, c, rb, rp, si0, cta, nC, lane, inv_scale, epoch);
         ++flushes;
@@ -583,8 +578,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaPara
 }
 
 int g_mega_sms = 0;
-int g_mega_tune = 0;
-int g_mega_slot_cap = 0;       // tuning: fewer ring slots than fit (0 = all that fit)
+int g_mega_slot_cap = 0;
+int g_mega_bps = 1;            // CTAs per SM (1 or 2)       // tuning: fewer ring slots than fit (0 = all that fit)
 bool g_mega_configured = false;
 
 int mega_sms() {
@@ -604,12 +599,11 @@ GRM_API int grm_mega_phase_bytes() { return (int)sizeof(MegaPhase); }
 // Tuning knob: cap the number of ring slots per CTA (0 = as many as shared memory holds).
 GRM_API void grm_mega_set_slot_cap(int slots) { g_mega_slot_cap = slots; }
 
-// Measurement switches for profiling the pipeline (outputs are then meaningless): bit 0 skips the tensor-core math of
-// every stage, bit 1 also skips the shared-memory reads, leaving only the copy ring and its barriers.
-GRM_API void grm_mega_set_tune(int flags) { g_mega_tune = flags; }
+// CTAs per SM of the launches that follow (1 or 2); tables sized for one value must not be run with the other.
+GRM_API void grm_mega_set_ctas_per_sm(int n) { g_mega_bps = n == 2 ? 2 : 1; }
 
-// CTAs of a launch (one per SM); 0 when no device is current.
-GRM_API int grm_mega_grid() { return mega_sms(); }
+// CTAs of a launch; 0 when no device is current.
+GRM_API int grm_mega_grid() { return mega_sms() * (g_mega_bps == 2 ? 2 : 1); }
 
 // Largest number of CTAs that share one 32-row pair of an [rp * 32][K] weight when `grid` CTAs split it evenly: the
 // partial-sum scratch needs (that - 1) slots of 32 floats per row pair.
@@ -651,27 +645,30 @@ GRM_API int grm_decode_mega(const void* phases, int first, int count, const void
   p.xs_bytes = (max_k * 2 + 127) & ~127;
   p.xsum_bytes = ((max_k / 64) * 4 + 127) & ~127;
   const int fixed = (p.xs_bytes + p.xsum_bytes + (2 * kCW * 32 + 2 * kCW) * 4 + 2 * kMaxSlots * 8 + 64 + 1023) & ~1023;
-  const int avail = 227 * 1024 - fixed;
+  const int bps = g_mega_bps == 2 ? 2 : 1;
+  // shared memory of an SM is 228 KB in total, 1 KB of it reserved per resident CTA; one CTA may take 227 KB
+  const int avail = (bps == 2 ? (228 * 1024 / 2 - 1024) : 227 * 1024) - fixed;
   p.nslots = avail / kSlotBytes < kMaxSlots ? avail / kSlotBytes : kMaxSlots;
   if (g_mega_slot_cap > 0 && p.nslots > g_mega_slot_cap) p.nslots = g_mega_slot_cap;
   if (p.nslots < 2) return -2;
+  while (p.nslots & (p.nslots - 1)) p.nslots &= p.nslots - 1;          // a power of two: slot and parity are bit fields of a counter
   for (int i = 0; i < 8; ++i) p.ar_recv[i] = (world > 1 && i < world) ? (float*)const_cast<void*>(recv[i]) : nullptr;
   p.ar_world = world > 1 ? world : 1; p.ar_rank = world > 1 ? rank : 0; p.ar_rows = ar_rows;
   p.timeline = (long long*)timeline;
-  p.tune = g_mega_tune;
   const size_t smem = (size_t)fixed + (size_t)p.nslots * kSlotBytes;
   if (!g_mega_configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_mega_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 228 * 1024 / 2 - 1024);
     if (e != cudaSuccess) return (int)e;
     g_mega_configured = true;
   }
   // the CTAs wait for one another (grid barrier, partial sums): a cooperative launch guarantees co-residency
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
+  cfg.gridDim = dim3((unsigned)(sms * bps)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeCooperative; at[0].val.cooperative = 1;
   cfg.attrs = at; cfg.numAttrs = cooperative ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_mega_kernel, p);
+  cudaError_t e = bps == 2 ? cudaLaunchKernelEx(&cfg, decode_mega_kernel<2>, p) : cudaLaunchKernelEx(&cfg, decode_mega_kernel<1>, p);
   if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }

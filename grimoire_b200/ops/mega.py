@@ -64,6 +64,8 @@ class MegaTable:
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self.device)
         self.h = h
         self.sync = torch.zeros(4, dtype=torch.int32, device=self.device)
+        if os.environ.get("GRIMOIRE_MEGA_BPS"):
+            lib.grm_mega_set_ctas_per_sm(int(os.environ["GRIMOIRE_MEGA_BPS"]))
         grid = lib.grm_mega_grid()
         self.max_k = max(p.K for p in phases)
         self.pstride = max(1, max(lib.grm_mega_max_parts(p.rp, p.K, grid) for p in phases) - 1)
@@ -71,8 +73,6 @@ class MegaTable:
         self.parts = torch.zeros(max_rp * self.pstride * 32 * 2, dtype=torch.float32, device=self.device)    # {value, epoch} pairs
         self.tp = tp
         self.spin = int(os.environ.get("GRIMOIRE_MEGA_SPIN", "0"))
-        if os.environ.get("GRIMOIRE_MEGA_TUNE"):
-            lib.grm_mega_set_tune(int(os.environ["GRIMOIRE_MEGA_TUNE"]))
         if os.environ.get("GRIMOIRE_MEGA_SLOTS"):
             lib.grm_mega_set_slot_cap(int(os.environ["GRIMOIRE_MEGA_SLOTS"]))
         self.grid = grid

@@ -474,3 +474,50 @@ def test_out_of_range_token_id_is_reported_not_read():
     assert torch.equal(h[0], table[3].float()) and torch.equal(h[3], table[99].float())
     assert float(h[1].abs().max()) == 0.0 and float(h[2].abs().max()) == 0.0
     _assert_clean()
+
+
+@pytest.mark.parametrize("N,K,group", [(256, 5120, 128), (5120, 17408, 128), (512, 2048, 64)])
+@pytest.mark.parametrize("xmax", [1.0e3, 3.0e3, 2.0e-2])
+def test_gemv_w4_single_row_survives_outlier_activations(N, K, group, xmax):
+    """A few columns of |x| ~ 1e3 .. 1e4 (routine for down_proj inputs of real checkpoints), or tiny activations overall: the
+    fp16 partial sums must neither overflow nor lose the small columns (the reference accumulates its GEMV in fp32,
+    src/gemv_decode.cpp:77-347).  Beyond |x| = 3840 the staged value saturates: the result stays finite."""
+    torch.manual_seed(N + K)
+    qw = quantize(torch.randn(N, K) * 0.02 + 0.004, Fmt.INT4, group=group)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    x = torch.randn(1, K) * (xmax / 30 if xmax < 1 else 1.0)
+    if xmax >= 1:
+        x[0, 5] = xmax
+        x[0, K // 2 + 3] = -0.8 * xmax
+        x[0, K - 9] = 0.5 * xmax
+    x = x.to(DEV).bfloat16()
+    want = x.float().cpu() @ qw.dequant().float().t()
+    out = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x, out, "f32")
+    got = out[:, :N].cpu()
+    assert torch.isfinite(got).all()
+    tol = 2e-3 * float(want.abs().max()) + 1e-6
+    assert float((got - want).abs().max()) < tol, (float((got - want).abs().max()), tol)
+    # the fused-norm prologue takes the same path with its own scale
+    h = (torch.randn(1, K) * (1.0 if xmax >= 1 else xmax)).to(DEV)
+    if xmax >= 1:
+        h[0, 7] = xmax
+    nw = torch.ones(K, device=DEV)
+    if lin.fused_norm(h, nw, out, "f32", 1e-6, 0.0):
+        xn = (h * torch.rsqrt((h * h).mean() + 1e-6)).bfloat16().float().cpu()
+        want = xn @ qw.dequant().float().t()
+        got = out[:, :N].cpu()
+        assert float((got - want).abs().max()) < 2e-3 * float(want.abs().max()) + 1e-6
+    _assert_clean()
+
+
+def test_gemv_w4_single_row_saturates_instead_of_overflowing():
+    torch.manual_seed(1)
+    qw = quantize(torch.randn(256, 2048) * 0.02, Fmt.INT4)
+    lin = W4Linear(qw, DEV, "t", workspace=Workspace(DEV))
+    x = torch.randn(1, 2048)
+    x[0, 11] = 3.0e5
+    x[0, 400] = -2.0e5
+    out = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
+    lin(x.to(DEV).bfloat16(), out, "f32")
+    assert torch.isfinite(out).all()
