@@ -162,6 +162,7 @@ def main() -> int:
     model = DenseModel.random(cfg, dev, seed=0, tp_rank=rank, tp_world=world)
     if tp is not None:
         tp.attach(model, max_rows=max(args.prompt, 64))
+        tp.split_head(model)
     torch.cuda.synchronize()
     build_s = time.time() - t0
     n_users = max(args.batch, 8)

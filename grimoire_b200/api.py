@@ -168,6 +168,8 @@ class Grimoire:
         hybrid = isinstance(model, HybridModel)
         if tp is not None:
             tp.attach(model, max_rows=max(ec.prefill_chunk, 64))
+            if not hybrid and pp is None:
+                tp.split_head(model)             # 1/W of the lm_head per rank; tokens by (value, index) exchange
         if pp is not None:
             pp.attach(model)
         if hybrid and ep_group is not None and ec.ep_world > 1:

@@ -40,7 +40,49 @@ struct DecParams {
   const float* k_norm_w;           // [D] or null
   float norm_eps, norm_offset;
   int rot;
+  unsigned int* status;            // device status block (bounded waits report here)
+  int cluster;                     // 1: the splits of a (row, kv head) are one thread-block cluster and merge through DSMEM
+  unsigned long long* tl;          // optional per-CTA timeline (8 words per CTA, thread 0: clock64 at the marks below)
 };
+
+constexpr int kMaxCluster = 16;   // splits merged through distributed shared memory (8 is the portable cluster size)
+
+// Distributed shared memory helpers (thread-block cluster).  Addresses are 32-bit shared-window addresses of the LOCAL
+// copy of a variable; mapa turns them into the address of the same variable in CTA ``cta`` of the cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, int cta) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(cta));
+  return ra;
+}
+__device__ __forceinline__ void st_dsmem_f1(uint32_t remote_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_dsmem_f2(uint32_t remote_addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote_addr), "f"(a), "f"(b) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0u;
+}
+
+unsigned long long* g_attn_timeline = nullptr;   // host-side: copied into DecParams::tl of every launch while set
+
+__device__ __forceinline__ void tl_mark(const DecParams& p, int slot) {
+  if (p.tl && threadIdx.x == 0) {
+    const size_t cta = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    unsigned long long v;
+    if (slot == 0 || slot == 7) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
+    else v = (unsigned long long)clock64();
+    p.tl[cta * 8 + slot] = v;
+  }
+}
 
 // Per-head RMSNorm (optional) and rotary embedding of one head held as v[i] = x[lane + 32 i] -- the arithmetic of
 // rope_kv.cu, so the fused and the two-kernel paths produce the same bits.
@@ -104,6 +146,20 @@ __device__ __forceinline__ int bt_page(const DecParams& p, int seq, int page_ind
   return p.block_table[(size_t)seq * p.max_pages + page_index];
 }
 
+// Rotation of the float4 chunks of lane (g, t)'s window in the per-warp output staging (see the store in the kernel).
+template <int D>
+__device__ __forceinline__ int so_rot(int g, int t) {
+  return D == 64 ? ((t >> 1) + 2 * g) : (2 * t + g);
+}
+// Position of dim d of head g inside sm_o[warp][g][]: the inverse of that rotation.
+template <int D>
+__device__ __forceinline__ int so_index(int g, int d) {
+  constexpr int W = D / 4;                       // dims per lane window
+  const int t = d / W, m = d % W;
+  const int chunk = ((m >> 2) + so_rot<D>(g, t)) & (D / 16 - 1);
+  return t * W + 4 * chunk + (m & 3);
+}
+
 template <int D, int G>
 __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p) {
   static_assert(G <= 8 && (D == 64 || D == 128 || D == 256), "unsupported geometry");
@@ -114,11 +170,28 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   __shared__ __align__(16) int8_t q_lo[8][D];
   __shared__ float q_delta[8];
   __shared__ float sm_ml[kWarps][G][2];
-  __shared__ float sm_o[kWarps][G][D];
+  __shared__ __align__(16) float sm_o[kWarps][G][D];
   __shared__ int s_last;
+  // cluster merge: CTA r owns outputs [r * per, (r + 1) * per) of the G x D block and receives every split's partial values
+  // of that slice (cl_recv[source][j]) and (max, sum) pairs (cl_rml[source][head]) by remote shared-memory stores
+  __shared__ __align__(16) float cl_recv[G * D + kMaxCluster];
+  __shared__ __align__(16) float cl_rml[kMaxCluster][G][2];
+  __shared__ __align__(16) float cl_ml[G][2];
+  __shared__ __align__(8) uint64_t cl_bar;
 
   const int split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int nsplit = gridDim.x;
+  tl_mark(p, 0);
+  tl_mark(p, 1);
+  if (p.cluster) {
+    // arrival barrier of the merge: one arrival per split.  Its initialisation is published to the cluster by the
+    // arrive half of a cluster barrier here; the wait half sits right before the first remote store.
+    if (threadIdx.x == 0) {
+      mbar_init(&cl_bar, (uint32_t)gridDim.x);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    cluster_arrive();
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int seq = p.row_seq[row];
@@ -132,73 +205,6 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   const int pend = min(pbeg + pps, page_hi);
 
   const bool fused = p.qkv != nullptr;
-  if (fused && pbeg < pend && pend == page_hi && warp < 2) {
-    // This CTA's split holds the last page: append the row's K (warp 0: norm, RoPE) and V (warp 1) to it -- int8 with a
-    // scale per (token, head) -- before the barrier below; the page loads start after it.
-    const int pos = len - 1;
-    const int page = bt_page(p, seq, pos / kPage);
-    if (page >= 0) {
-      const bf16* src = p.qkv + (size_t)row * p.ld_qkv + (size_t)p.Hq * D + (size_t)((warp == 0 ? 0 : p.Hkv) + kvh) * D;
-      float v[D / 32];
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
-      if (warp == 0) head_norm_rope<D>(v, p.k_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)pos, lane);
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
-      amax = warp_max(amax);
-      const float sc = amax > 0.f ? amax / 127.f : 1.f;
-      const float inv = 1.f / sc;
-      const size_t base = ((size_t)page * p.Hkv + kvh) * kPage + (pos % kPage);
-      int8_t* dst = const_cast<int8_t*>(warp == 0 ? p.k_pages : p.v_pages) + base * D;
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) dst[lane + 32 * i] = (int8_t)max(-127, min(127, __float2int_rn(v[i] * inv)));
-      if (lane == 0) const_cast<float*>(warp == 0 ? p.k_scale : p.v_scale)[base] = sc;
-    }
-  }
-  // ---- q -> two int8 levels per head (warp w quantises heads w, w + 4) ----
-  for (int h = warp; h < 8; h += kWarps) {
-    float v[D / 32];
-    float mx = 0.f;
-    if (fused && h < G) {
-      const bf16* src = p.qkv + (size_t)row * p.ld_qkv + (size_t)(kvh * G + h) * D;
-#pragma unroll
-      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
-      head_norm_rope<D>(v, p.q_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)(len - 1), lane);
-    }
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      if (fused) v[i] = h < G ? __bfloat162float(__float2bfloat16(v[i])) * p.scale : 0.f;   // the two-kernel path rounds q to bf16
-      else v[i] = h < G ? __bfloat162float(p.q[(size_t)row * p.ld_q + (size_t)(kvh * G + h) * D + lane + 32 * i]) * p.scale : 0.f;
-      mx = fmaxf(mx, fabsf(v[i]));
-    }
-    mx = warp_max(mx);
-    const float delta = mx > 0.f ? mx / 16256.f : 1.f;
-    const float inv = 1.f / delta;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      const int qi = __float2int_rn(v[i] * inv);
-      const int hi = (qi + 64) >> 7;
-      q_hi[h][lane + 32 * i] = (int8_t)hi;
-      q_lo[h][lane + 32 * i] = (int8_t)(qi - 128 * hi);
-    }
-    if (lane == 0) q_delta[h] = h < G ? delta : 0.f;
-  }
-  __syncthreads();
-  uint32_t qa_hi[NH][4], qa_lo[NH][4];
-#pragma unroll
-  for (int h = 0; h < NH; ++h) {
-    const uint4 a = *reinterpret_cast<const uint4*>(&q_hi[g][64 * h + 16 * t]);
-    const uint4 b = *reinterpret_cast<const uint4*>(&q_lo[g][64 * h + 16 * t]);
-    qa_hi[h][0] = a.x; qa_hi[h][1] = a.y; qa_hi[h][2] = a.z; qa_hi[h][3] = a.w;
-    qa_lo[h][0] = b.x; qa_lo[h][1] = b.y; qa_lo[h][2] = b.z; qa_lo[h][3] = b.w;
-  }
-  const float qd = q_delta[g];
-
-  float m_run = -INFINITY, l_part = 0.f, lv_part = 0.f;   // head g: running max, this lane's share of sum p and of sum f16(p*vs)
-  float o[DT][4];
-#pragma unroll
-  for (int j = 0; j < DT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
   const int* bt = p.block_table + (size_t)seq * p.max_pages;
 
   // ---- per-warp ring of whole pages in shared memory, filled by cp.async STAGES-1 pages ahead ----
@@ -234,6 +240,90 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  // The page loads start after the q prologue.  Requesting the first pages before it was measured and does not pay: the
+  // prologue's own global loads then return behind the page traffic, and prologue + page phase take as long as before.
+  if (fused && pbeg < pend && pend == page_hi && warp < 2) {
+    // This CTA's split holds the last page: append the row's K (warp 0: norm, RoPE) and V (warp 1) to it -- int8 with a
+    // scale per (token, head) -- before the barrier below; the page loads start after it.
+    const int pos = len - 1;
+    const int page = bt_page(p, seq, pos / kPage);
+    if (page >= 0) {
+      const bf16* src = p.qkv + (size_t)row * p.ld_qkv + (size_t)p.Hq * D + (size_t)((warp == 0 ? 0 : p.Hkv) + kvh) * D;
+      float v[D / 32];
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(src[lane + 32 * i]);
+      if (warp == 0) head_norm_rope<D>(v, p.k_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)pos, lane);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      amax = warp_max(amax);
+      const float sc = amax > 0.f ? amax / 127.f : 1.f;
+      const float inv = 1.f / sc;
+      const size_t base = ((size_t)page * p.Hkv + kvh) * kPage + (pos % kPage);
+      int8_t* dst = const_cast<int8_t*>(warp == 0 ? p.k_pages : p.v_pages) + base * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) dst[lane + 32 * i] = (int8_t)max(-127, min(127, __float2int_rn(v[i] * inv)));
+      if (lane == 0) const_cast<float*>(warp == 0 ? p.k_scale : p.v_scale)[base] = sc;
+    }
+  }
+  // ---- q -> two int8 levels per head (warp w quantises heads w, w + 4; both heads' loads are in flight together) ----
+  float qv[8 / kWarps][D / 32];
+#pragma unroll
+  for (int it = 0; it < 8 / kWarps; ++it) {
+    const int h = warp + kWarps * it;
+    if (h < G) {
+      const bf16* src = fused ? p.qkv + (size_t)row * p.ld_qkv + (size_t)(kvh * G + h) * D
+                              : p.q + (size_t)row * p.ld_q + (size_t)(kvh * G + h) * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) qv[it][i] = __bfloat162float(src[lane + 32 * i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) qv[it][i] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < 8 / kWarps; ++it) {
+    const int h = warp + kWarps * it;
+    float (&v)[D / 32] = qv[it];
+    float mx = 0.f;
+    if (fused && h < G) {
+      head_norm_rope<D>(v, p.q_norm_w, p.norm_eps, p.norm_offset, p.inv_freq, p.rot, (float)(len - 1), lane);
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) v[i] = __bfloat162float(__float2bfloat16(v[i]));     // the two-kernel path rounds q to bf16
+    }
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      v[i] *= p.scale;
+      mx = fmaxf(mx, fabsf(v[i]));
+    }
+    mx = warp_max(mx);
+    const float delta = mx > 0.f ? mx / 16256.f : 1.f;
+    const float inv = 1.f / delta;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const int qi = __float2int_rn(v[i] * inv);
+      const int hi = (qi + 64) >> 7;
+      q_hi[h][lane + 32 * i] = (int8_t)hi;
+      q_lo[h][lane + 32 * i] = (int8_t)(qi - 128 * hi);
+    }
+    if (lane == 0) q_delta[h] = h < G ? delta : 0.f;
+  }
+  __syncthreads();
+  tl_mark(p, 2);
+  uint32_t qa_hi[NH][4], qa_lo[NH][4];
+#pragma unroll
+  for (int h = 0; h < NH; ++h) {
+    const uint4 a = *reinterpret_cast<const uint4*>(&q_hi[g][64 * h + 16 * t]);
+    const uint4 b = *reinterpret_cast<const uint4*>(&q_lo[g][64 * h + 16 * t]);
+    qa_hi[h][0] = a.x; qa_hi[h][1] = a.y; qa_hi[h][2] = a.z; qa_hi[h][3] = a.w;
+    qa_lo[h][0] = b.x; qa_lo[h][1] = b.y; qa_lo[h][2] = b.z; qa_lo[h][3] = b.w;
+  }
+  const float qd = q_delta[g];
+
+  float m_run = -INFINITY, l_part = 0.f, lv_part = 0.f;   // head g: running max, this lane's share of sum p and of sum f16(p*vs)
+  float o[DT][4];
+#pragma unroll
+  for (int j = 0; j < DT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
   int pg = pbeg + warp;
 #pragma unroll
   for (int s0 = 0; s0 < STAGES - 1; ++s0) issue(pg + s0 * kWarps, s0);
@@ -338,6 +428,7 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   }
 
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  tl_mark(p, 3);
   // ---- this warp's result for head g: quad-reduce the sums, remove the 1152 bias, stage for the CTA merge ----
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 1);
   l_part += __shfl_xor_sync(0xffffffffu, l_part, 2);
@@ -346,14 +437,24 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   if (g < G) {
     if (t == 0) { sm_ml[warp][g][0] = m_run; sm_ml[warp][g][1] = l_part; }
     const float bias = 1152.f * lv_part;
+    // lane (g, t) owns the D/4 contiguous dims [t * D/4, (t + 1) * D/4) of head g: o[j][0] is dim 2t*DT + j and o[j][1]
+    // dim (2t+1)*DT + j.  They are stored as float4 chunks whose position inside the lane's window is rotated by
+    // so_rot(g, t), so that the eight lanes of a store phase hit eight different groups of four banks (unrotated, every
+    // lane of the warp would start at bank 0).  so_index() is the matching read mapping.
+    float* dst = &sm_o[warp][g][t * (D / 4)];
+    const int rot = so_rot<D>(g, t);
 #pragma unroll
-    for (int j = 0; j < DT; ++j) {
-      sm_o[warp][g][DT * (2 * t) + j] = (o[j][0] - bias) * (1.f / 1024.f);
-      sm_o[warp][g][DT * (2 * t + 1) + j] = (o[j][1] - bias) * (1.f / 1024.f);
+    for (int i = 0; i < D / 16; ++i) {
+      const int c = i / (DT / 4), j0 = 4 * (i % (DT / 4));       // chunk i = dims 4i..4i+3 of the window
+      float4 v4;
+      v4.x = (o[j0][c] - bias) * (1.f / 1024.f); v4.y = (o[j0 + 1][c] - bias) * (1.f / 1024.f);
+      v4.z = (o[j0 + 2][c] - bias) * (1.f / 1024.f); v4.w = (o[j0 + 3][c] - bias) * (1.f / 1024.f);
+      *reinterpret_cast<float4*>(dst + 4 * ((i + rot) & (D / 16 - 1))) = v4;
     }
   }
   __syncthreads();
 
+  if (p.cluster) cluster_wait();        // every CTA of the cluster has initialised its arrival barrier
   const size_t pidx = ((size_t)row * p.Hkv + kvh) * nsplit + split;
   for (int i = tid; i < G * D; i += kThreads) {
     const int g = i / D, d = i % D;
@@ -366,19 +467,81 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
       const float mw = sm_ml[w][g][0];
       const float f = (mw == -INFINITY) ? 0.f : __expf(mw - M_);
       L += sm_ml[w][g][1] * f;
-      O += sm_o[w][g][d] * f;
+      O += sm_o[w][g][so_index<D>(g, d)] * f;
     }
     if (nsplit == 1) {
       float r = L > 0.f ? O / L : 0.f;
       const size_t oi = (size_t)row * p.ld_o + (size_t)(kvh * G + g) * D + d;
       if (p.gate) r *= sigmoid_f(__bfloat162float(p.gate[oi]));
       p.out[oi] = __float2bfloat16(r);
+    } else if (p.cluster) {
+      const int per = (G * D + nsplit - 1) / nsplit;
+      const int r = i / per, j = i - r * per;
+      st_dsmem_f1(dsmem_addr(smem_u32(&cl_recv[split * per + j]), r), O);
+      if (d == 0) { cl_ml[g][0] = M_; cl_ml[g][1] = L; }
     } else {
       p.part_o[(pidx * G + g) * D + d] = O;
       if (d == 0) { p.part_ml[(pidx * G + g) * 2] = M_; p.part_ml[(pidx * G + g) * 2 + 1] = L; }
     }
   }
   if (nsplit == 1) return;
+  tl_mark(p, 4);
+  if (p.cluster) {
+    // The splits of this (row, kv head) are the CTAs of one cluster.  Every CTA has pushed slice r of its un-normalised
+    // output into CTA r's shared memory (above); it now pushes its (max, sum) pairs to every CTA, makes the stores
+    // visible and arrives on every CTA's barrier.  CTA r waits (bounded) for the nsplit arrivals on its own barrier and
+    // combines its slice in split order with the arithmetic of the last-CTA merge below.  Nobody reads another CTA's
+    // memory, so a CTA may exit as soon as its own slice is written.
+    __syncthreads();
+    for (int idx = tid; idx < nsplit * G; idx += kThreads) {
+      const int r = idx / G, g = idx - r * G;
+      st_dsmem_f2(dsmem_addr(smem_u32(&cl_rml[split][g][0]), r), cl_ml[g][0], cl_ml[g][1]);
+    }
+    __syncthreads();
+    if (tid < nsplit) {
+      asm volatile("fence.acq_rel.cluster;" ::: "memory");
+      mbar_arrive_remote(dsmem_addr(smem_u32(&cl_bar), tid));
+    }
+    tl_mark(p, 5);
+    {
+      const uint32_t bar = smem_u32(&cl_bar);
+      bool ok = mbar_try_wait_cluster(bar, 0u);
+      for (unsigned int it = 0; !ok && it < 4000000u; ++it) {
+        __nanosleep(32);
+        ok = mbar_try_wait_cluster(bar, 0u);
+      }
+      if (!ok) {
+        if (tid == 0) grm_set_error(p.status, GRM_ERR_MBAR_TIMEOUT, 0x70000u | (unsigned int)split);
+        return;
+      }
+    }
+    const int per = (G * D + nsplit - 1) / nsplit;
+    for (int j = tid; j < per; j += kThreads) {
+      const int e = split * per + j;
+      if (e >= G * D) break;
+      const int g = e / D, d = e % D;
+      float M_ = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < kMaxCluster; ++sp) if (sp < nsplit) M_ = fmaxf(M_, cl_rml[sp][g][0]);
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < kMaxCluster; ++sp) {
+        if (sp < nsplit) {
+          const float ms = cl_rml[sp][g][0];
+          const float f = (ms == -INFINITY) ? 0.f : __expf(ms - M_);
+          L += cl_rml[sp][g][1] * f;
+          O = fmaf(cl_recv[sp * per + j], f, O);
+        }
+      }
+      float r = O * (L > 0.f ? 1.f / L : 0.f);
+      const size_t oi = (size_t)row * p.ld_o + (size_t)(kvh * G + g) * D + d;
+      if (p.gate) r *= sigmoid_f(__bfloat162float(p.gate[oi]));
+      p.out[oi] = __float2bfloat16(r);
+    }
+    tl_mark(p, 6);
+    tl_mark(p, 7);
+    return;
+  }
 
   __threadfence();
   __syncthreads();
@@ -388,7 +551,8 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     if (s_last) p.counters[row * p.Hkv + kvh] = 0u;
   }
   __syncthreads();
-  if (!s_last) return;
+  tl_mark(p, 5);
+  if (!s_last) { tl_mark(p, 7); return; }
   __threadfence();
   // Last CTA of this (row, kv head): merge the splits in split order.  The per-split (max, sum) pairs
   // are staged in shared memory first so the long loop only carries independent loads.
@@ -433,17 +597,52 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     o2.x = pack_bf16x2(r[0], r[1]); o2.y = pack_bf16x2(r[2], r[3]);
     *reinterpret_cast<uint2*>(p.out + oi) = o2;
   }
+  tl_mark(p, 6);
+  tl_mark(p, 7);
 }
 
+int g_attn_cluster = 1;     // 0: always merge the splits through global scratch and the last-arriving CTA
+
 template <int D, int G>
-int launch(const DecParams& p, int splits, cudaStream_t st) {
-  dim3 grid(splits, p.Hkv, p.M);
+int launch(const DecParams& p_in, int splits, cudaStream_t st) {
+  dim3 grid(splits, p_in.Hkv, p_in.M);
   constexpr int kRing = kWarps * ((D == 256) ? 3 : 4) * (2 * kPage * D + 128);
-  static bool configured = false;      // per template instance; setting the attribute twice is harmless
-  if (!configured) {
+  // per template instance: 0 = not configured, 1 = clusters of up to 8, 2 = clusters of up to 16, -1 = no clusters
+  static int configured = 0;
+  if (configured == 0) {
     cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = 1;
+    if (cudaFuncSetAttribute(decode_attn_kernel<D, G>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+      // a cluster of 16 must fit one GPC with this kernel's shared memory: ask the occupancy calculator
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(16, 1, 1); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kRing;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 16; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int nclusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&nclusters, decode_attn_kernel<D, G>, &cfg) == cudaSuccess && nclusters >= 1) configured = 2;
+    }
+    (void)cudaGetLastError();
+  }
+  DecParams p = p_in;
+  p.status = grm_status_ptr();
+  const int max_cl = configured == 2 ? 16 : 8;
+  // clusters of 16 only while the whole grid is co-resident: with more CTAs than SMs the wait for a GPC with 16 free SMs
+  // delays the launch of the later clusters by more than the merge saves (measured: 8 rows x 8 kv heads x 16 splits)
+  const long ctas = (long)splits * p.Hkv * p.M;
+  p.cluster = (g_attn_cluster && splits >= 2 && splits <= max_cl && (splits <= 8 || ctas <= 148)) ? 1 : 0;
+  if (p.cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kRing; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D, G>, p);
+    if (e != cudaSuccess) return (int)e;
+    GRM_LAUNCH_RET();
   }
   decode_attn_kernel<D, G><<<grid, kThreads, kRing, st>>>(p);
   GRM_LAUNCH_RET();
@@ -464,6 +663,14 @@ int launch_g(const DecParams& p, int G, int splits, cudaStream_t st) {
 
 }  // namespace
 
+// Debug aid: while set, every decode-attention launch writes 8 words per CTA (marks 0 and 7: %globaltimer at entry and
+// exit; 1..6: clock64 at entry, after the q prologue, after the page loop, after the CTA merge, after the arrival
+// counter, after the split merge of the last CTA).  The buffer must hold 8 * grid words; null switches it off.
+GRM_API void grm_attn_set_timeline(void* buf) { g_attn_timeline = (unsigned long long*)buf; }
+
+// 1 (default): splits of up to 16 CTAs merge through cluster shared memory; 0: through global scratch.
+GRM_API void grm_attn_set_cluster(int on) { g_attn_cluster = on; }
+
 // part_o: fp32 M*Hq*splits*D, part_ml: fp32 M*Hq*splits*2, counters: M*Hkv zeroed uints (only read
 // when splits > 1).  window <= 0 disables the sliding window.
 GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, const void* row_pos, const void* block_table,
@@ -480,6 +687,7 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
   p.gate = (const bf16*)gate; p.out = (bf16*)out; p.ld_o = ld_o; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
   p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
   p.qkv = nullptr; p.ld_qkv = 0; p.inv_freq = nullptr; p.q_norm_w = p.k_norm_w = nullptr; p.norm_eps = p.norm_offset = 0.f; p.rot = 0;
+  p.tl = g_attn_timeline;
   cudaStream_t st = (cudaStream_t)stream;
   const int G = Hq / Hkv;
   switch (D) {
@@ -510,6 +718,7 @@ GRM_API int grm_paged_decode_attn_fused(const void* qkv, int ld_qkv, const void*
   p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
   p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.inv_freq = (const float*)inv_freq; p.q_norm_w = (const float*)q_norm_w;
   p.k_norm_w = (const float*)k_norm_w; p.norm_eps = norm_eps; p.norm_offset = norm_offset; p.rot = rot;
+  p.tl = g_attn_timeline;
   cudaStream_t st = (cudaStream_t)stream;
   const int G = Hq / Hkv;
   switch (D) {

@@ -211,11 +211,16 @@ class Engine:
     def _splits_for(self, M: int, max_len: int) -> int:
         return K.decode_splits(max_len, M, self.model.geom.Hkv)
 
-    def _run_rows(self, M: int, splits: int, distinct: bool = False, runs=None) -> torch.Tensor:
-        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct, runs=runs)
+    def _run_rows(self, M: int, splits: int, distinct: bool = False, runs=None, full_logits: bool = True) -> torch.Tensor:
+        hs = getattr(self.model, "head_split", None)
+        rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct, runs=runs,
+                      full_logits=full_logits or hs is None)
         logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
         pp = getattr(self.model, "pp", None)
-        if logits is not None:
+        if logits is not None and hs is not None and not rb.full_logits:
+            # vocabulary-split head: the ranks exchange (value, index) candidates instead of logits rows
+            self.model.tp.head_pick(logits, hs[0], hs[1], self.decode_buf.next_ids[:M])
+        elif logits is not None:
             K.argmax_rows(logits, self.decode_buf.next_ids[:M])
         if pp is not None:
             pp.broadcast_from_last(self.decode_buf.next_ids[:M])     # token chosen by the last stage travels back
@@ -264,6 +269,9 @@ class Engine:
         ep = getattr(self.model, "ep", None)
         if (tp is not None and not tp.fused) or (ep is not None and not ep.fused) or getattr(self.model, "pp", None) is not None:
             use_graph = False        # NCCL collectives / stage hops stay out of captured graphs
+        full = return_logits or getattr(self.model, "head_split", None) is None
+        if full and getattr(self.model, "head_split", None) is not None:
+            use_graph = False        # whole logits rows of a split head are gathered by a library collective
         if use_graph and self.device.type == "cuda":
             key = (M, splits, distinct)
             g = self.graphs.get(key)
@@ -272,7 +280,7 @@ class Engine:
             g.replay()
             self.counters["graph_replays"] += 1
         else:
-            self._run_rows(M, splits, distinct, runs)
+            self._run_rows(M, splits, distinct, runs, full_logits=full)
         if runs is not None:
             self.model.end_verify()
         self.h_next[:M].copy_(self.decode_buf.next_ids[:M], non_blocking=True)
@@ -324,12 +332,13 @@ class Engine:
         # warm the allocator / workspace outside capture, then record; a model with recurrent state
         # must not keep the warm-up run's update
         saved = self._save_recurrent(M)
-        self._run_rows(M, splits, distinct)
+        full = getattr(self.model, "head_split", None) is None     # a split head is captured with its (value, index) pick
+        self._run_rows(M, splits, distinct, full_logits=full)
         torch.cuda.current_stream().synchronize()
         self._restore_recurrent(saved)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._run_rows(M, splits, distinct)
+            self._run_rows(M, splits, distinct, full_logits=full)
         self.graphs[(M, splits, distinct)] = g
         return g
 
@@ -352,7 +361,7 @@ class Engine:
         distinct = len({s.slot for s in seqs}) == M
 
         def body():
-            self._run_rows(M, splits, distinct)
+            self._run_rows(M, splits, distinct, full_logits=getattr(self.model, "head_split", None) is None)
             self.d_tokens[:M].copy_(self.decode_buf.next_ids[:M])
             self.d_row_pos[:M].add_(1)
 

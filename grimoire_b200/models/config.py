@@ -175,8 +175,12 @@ def dense_27b(layers: int = 64) -> ModelConfig:
                        head_dim=128, vocab_size=151936, intermediate_size=17408, rope_theta=1e6)
 
 
-def small_dense(layers: int = 4) -> ModelConfig:
-    """A small GPU test model with 27B-like ratios (hidden 1024, 8q/2kv x 128, FFN 2816)."""
+def small_dense(layers: int = 4, wide: bool = False) -> ModelConfig:
+    """A small GPU test model with 27B-like ratios (hidden 1024, 8q/2kv x 128, FFN 2816).  ``wide`` has 16q/8kv heads and
+    FFN 4096, so that it still divides over 4 and 8 tensor-parallel ranks."""
+    if wide:
+        return ModelConfig(hidden_size=1024, num_hidden_layers=layers, num_attention_heads=16, num_key_value_heads=8,
+                           head_dim=128, vocab_size=8192, intermediate_size=4096, rope_theta=1e6)
     return ModelConfig(hidden_size=1024, num_hidden_layers=layers, num_attention_heads=8, num_key_value_heads=2,
                        head_dim=128, vocab_size=8192, intermediate_size=2816, rope_theta=1e6)
 

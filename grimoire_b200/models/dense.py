@@ -65,6 +65,9 @@ class RowBatch:
     # decode with verify blocks on a model with recurrent layers: (run_slot, run_start, run_len) int32 device tensors,
     # one run per maximal group of rows that are consecutive positions of one sequence; None = every row is its own run
     runs: Optional[tuple] = None
+    # vocabulary-split lm_head (tensor parallel): True = the returned logits rows are gathered over the ranks; False = only
+    # this rank's column slice is valid and the caller picks the token with the (value, index) exchange
+    full_logits: bool = True
 
 
 class Buffers:
@@ -105,6 +108,7 @@ class DenseModel:
         self.layer_begin = pp_rank * per + min(pp_rank, extra)
         self.layer_end = self.layer_begin + per + (1 if pp_rank < extra else 0)
         self.pp = None          # parallel.pp.PipelineParallel when pp_world > 1
+        self.head_split = None  # (first vocabulary row, rows) of this rank's lm_head shard (TensorParallel.split_head)
         self.ws = workspace or Workspace(device)
         if cfg.num_attention_heads % tp_world or cfg.num_key_value_heads % tp_world or cfg.intermediate_size % tp_world:
             raise ValueError("tensor parallel degree must divide heads, kv heads and the FFN width")
@@ -165,6 +169,20 @@ class DenseModel:
             return
         K.add_rmsnorm(h, norm_w, x, eps, off)
         lin(x, out, epi)
+
+    def _head(self, hsel: torch.Tensor, buf: "Buffers", n: int, rb: RowBatch) -> torch.Tensor:
+        """Final norm + lm_head over ``n`` rows.  With a vocabulary-split head this rank writes its column slice of the
+        logits rows; they are gathered unless the caller asked for the slice only (``rb.full_logits`` False)."""
+        cfg = self.cfg
+        xf, logits = buf.xf[:n], buf.logits[:n]
+        if self.head_split is None:
+            self._norm_linear(self.lm_head, hsel, self.final_norm, xf, logits, "f32", cfg.rms_norm_eps, cfg.norm_offset)
+            return logits
+        v0, vn = self.head_split
+        self._norm_linear(self.lm_head, hsel, self.final_norm, xf, logits[:, v0:v0 + vn], "f32", cfg.rms_norm_eps, cfg.norm_offset)
+        if rb.mode == "prefill" or rb.full_logits:
+            self.tp.gather_head(logits)
+        return logits
 
     @staticmethod
     def _rows(w, a: int, b: int):
@@ -346,10 +364,7 @@ class DenseModel:
         if bool(mine.any()):
             sel[mine] = hs.index_select(0, rows[mine] - r * R)
         torch.distributed.all_reduce(sel, group=tp.group)
-        xf, logits = buf.xf[:n], buf.logits[:n]
-        K.add_rmsnorm(sel, self.final_norm, xf, eps, off)
-        self.lm_head(xf, logits, "f32")
-        return logits
+        return self._head(sel, buf, n, rb)
 
     def _mega_ready(self) -> bool:
         ok = getattr(self, "_mega_ok", None)
@@ -378,9 +393,11 @@ class DenseModel:
                 K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, None)
             last = li == n - 1
             tab.run(1 + 4 * li, 4 if (not last or tab.head_in_table) else 3)
-        logits = buf.logits[:1]
         if not tab.head_in_table:
-            self._norm_linear(self.lm_head, h, self.final_norm, buf.xf[:1], logits, "f32", cfg.rms_norm_eps, cfg.norm_offset)
+            return self._head(h, buf, 1, rb)
+        logits = buf.logits[:1]
+        if self.head_split is not None and rb.full_logits:
+            self.tp.gather_head(logits)
         return logits
 
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
@@ -443,7 +460,6 @@ class DenseModel:
         else:
             n = rb.logits_rows.shape[0]
             hsel = h.index_select(0, rb.logits_rows) if n != M else h
-        xf, logits = buf.xf[:n], buf.logits[:n]
-        self._norm_linear(self.lm_head, hsel, self.final_norm, xf, logits, "f32", eps, off)
+        logits = self._head(hsel, buf, n, rb)
         if tl: trace.mark("end")
         return logits

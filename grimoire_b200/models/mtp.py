@@ -50,6 +50,9 @@ class MtpHead:
             self.head = self.inner._linear(self.inner._quant(head_w), "mtp.lm_head")
             self.draft_vocab = head_w.shape[0]
         else:
+            if getattr(self.target, "head_split", None) is not None:
+                raise ValueError("the draft head shares the target's lm_head, which is split over the tensor-parallel ranks; "
+                                 "attach the draft head before TensorParallel.split_head or set GRIMOIRE_TP_HEAD_SPLIT=0")
             self.head = self.target.lm_head
             self.draft_vocab = self.cfg.vocab_size
         return self

@@ -181,14 +181,18 @@ def gather_kv_dense(kv: KvLayer, pages_of_seq: torch.Tensor, T: int, out_k: torc
 
 
 def decode_splits(max_len: int, M: int, Hkv: int) -> int:
-    """Split-KV factor: about 256 CTAs in total (measured optimum on 148 SMs: more CTAs pay the per-CTA
-    prologue and merge again, fewer leave SMs idle), at least 8 pages (2 per warp) per split."""
+    """Split-KV factor.  Measured on 148 SMs (one row, 8 kv heads, us per launch at 16 / 32 splits: context 4096 11.6 / 14.2,
+    8192 15.3 / 16.9, 16384 21.7 / 20.5, 32768 34.4 / 27.0): up to 16 splits merge through cluster shared memory and
+    want at least 8 pages (2 per warp) each; more than 16 fall back to the scratch merge, which only pays from 32 pages
+    per split; about 256 CTAs in total at most."""
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     want = max(1, 256 // max(1, M * Hkv))
-    cap = int(max(1, min(want, pages // 8 if pages >= 8 else 1, 64)))   # >= 2 pages per warp
+    cap = int(max(1, min(want, pages // 8 if pages >= 8 else 1, 64)))
     s = 1
     while s * 2 <= cap:     # powers of two only: the decode graphs are keyed by (rows, splits)
         s *= 2
+    if s > 16 and pages // s < 32:
+        s = 16
     return s
 
 

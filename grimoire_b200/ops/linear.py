@@ -105,6 +105,23 @@ class W4Linear:
     def nbytes(self) -> int:
         return self.tiled.nbytes() if self.tiled is not None else self.w_ref.numel() * 4
 
+    def slice_rows(self, r0: int, n: int) -> "W4Linear":
+        """Rows [r0, r0 + n) as a projection of their own (r0 a multiple of 32: whole 32-row tiles are contiguous in the
+        tiled layout, so the slice is a copy of a byte range).  Used for the vocabulary-split lm_head."""
+        if self.swiglu or r0 % 32 or r0 < 0 or n <= 0 or r0 + n > self.N:
+            raise ValueError("slice_rows needs a 32-row aligned start inside a plain projection")
+        o = object.__new__(W4Linear)
+        o.name, o.K, o.group, o.swiglu, o.device, o.ws = f"{self.name}[{r0}:{r0 + n}]", self.K, self.group, False, self.device, self.ws
+        o.N = o.out_features = n
+        if self.tiled is not None:
+            t = self.tiled
+            npad = (n + 31) // 32 * 32
+            o.tiled = W4Tiled(t.w[r0 // 32:(r0 + npad) // 32].clone(), t.sz[r0 // 16:(r0 + npad) // 16].clone(), npad, t.K, t.group)
+            o.Np, o.w_ref = npad, None
+        else:
+            o.tiled, o.Np, o.w_ref = None, n, self.w_ref[r0:r0 + n].clone()
+        return o
+
     # -- kernel selection ---------------------------------------------------------------------
     def _plan_smallm(self, M: int):
         tiles32 = self.Np // 32
@@ -212,6 +229,14 @@ class BF16Linear:
 
     def nbytes(self) -> int:
         return self.w.numel() * 2
+
+    def slice_rows(self, r0: int, n: int) -> "BF16Linear":
+        """Rows [r0, r0 + n) as a projection of their own (a view: a tied lm_head keeps sharing the embedding table)."""
+        o = object.__new__(BF16Linear)
+        o.name, o.w, o.device, o.swiglu = f"{self.name}[{r0}:{r0 + n}]", self.w[r0:r0 + n], self.device, False
+        o.N, o.K = o.w.shape
+        o.out_features = o.N
+        return o
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
         M = x.shape[0]

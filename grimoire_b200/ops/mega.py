@@ -128,7 +128,8 @@ def build_dense_table(model, buf) -> MegaTable:
             phases.append(_phase(layers[i + 1].qkv, PRO_NORM, EPI_BF16, None, layers[i + 1].in_norm, qkv, eps, off))
     head_in_table = linear_ok(model.lm_head) and not model.lm_head.swiglu
     if head_in_table:
-        phases.append(_phase(model.lm_head, PRO_NORM, EPI_F32, None, model.final_norm, buf.logits[0], eps, off))
+        v0 = model.head_split[0] if getattr(model, "head_split", None) else 0      # a vocabulary shard writes its columns
+        phases.append(_phase(model.lm_head, PRO_NORM, EPI_F32, None, model.final_norm, buf.logits[0, v0:], eps, off))
     t = MegaTable(phases, model.device, h, tp)
     t.head_in_table = head_in_table
     t.n_layers = len(layers)

@@ -49,6 +49,19 @@ class SymmetricBuffer:
         return (ctypes.c_void_p * self.world)(*self.ptrs)
 
 
+def pick_candidates(vals: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """The split head's decision per row over the ranks' candidates ``vals`` / ``idx`` [M][W]: the highest value, on a
+    tie the lowest vocabulary index; an index of INT_MAX (a rank without a finite logit) only wins when every rank has
+    none (tp_head_pick_at, src/grimoire.cpp:5421-5449)."""
+    bv, bi = vals[:, 0], idx[:, 0]
+    for r in range(1, vals.shape[1]):
+        cv, ci = vals[:, r], idx[:, r]
+        better = (cv > bv) | ((cv == bv) & (ci < bi))
+        bv = torch.where(better, cv, bv)
+        bi = torch.where(better, ci, bi)
+    return bi
+
+
 class TensorParallel:
     def __init__(self, group, device, fused: Optional[bool] = None):
         self.group = group
@@ -89,6 +102,78 @@ class TensorParallel:
         self.epochs = torch.zeros(tiles, dtype=torch.int32, device=self.device)
         dist.barrier(self.group)
         torch.cuda.synchronize(self.device)
+
+    # ------------------------------------------------------------------------------------------
+    # vocabulary-split lm_head (tp_head_split / tp_head_pick, src/grimoire.cpp:5381-5449)
+    # ------------------------------------------------------------------------------------------
+    def split_head(self, model, max_rows: int = 64) -> bool:
+        """Keep only this rank's block of lm_head rows (blocks of ceil(V / W) rounded up to 32 rows, the last one shorter).
+        A decode step then streams 1/W of the head and picks the token with ``head_pick``; whole logits rows are
+        gathered on demand.  Returns False (head stays replicated) when the projection type cannot be sliced, the
+        model shares its head with a draft head, or GRIMOIRE_TP_HEAD_SPLIT=0."""
+        head = getattr(model, "lm_head", None)
+        if (self.world < 2 or os.environ.get("GRIMOIRE_TP_HEAD_SPLIT", "1") == "0" or head is None or not hasattr(head, "slice_rows")
+                or getattr(head, "swiglu", False) or getattr(model, "pp_world", 1) != 1 or getattr(model, "head_split", None) is not None):
+            return False
+        V = model.cfg.vocab_size
+        vs = (V + self.world - 1) // self.world
+        vs = (vs + 31) // 32 * 32
+        if vs * (self.world - 1) >= V:
+            return False                      # a rank would be left without rows
+        v0 = self.rank * vs
+        vn = min(V, v0 + vs) - v0
+        model.lm_head = head.slice_rows(v0, vn)
+        model.head_split = (v0, vn)
+        self.head_vs, self.head_rows = vs, max_rows
+        if self.fused:
+            self.head_recv = SymmetricBuffer(2 * self.world * max_rows * 2 * 2, torch.int32, self.group, self.device)
+            self.head_epochs = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+            dist.barrier(self.group)
+            torch.cuda.synchronize(self.device)
+        self.stats["head_pick"] = 0
+        return True
+
+    def head_pick(self, logits: torch.Tensor, v0: int, vn: int, out_ids: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row from the ranks' logits slices: every rank offers its best (value, index), the highest
+        value wins and ties go to the lowest index.  ``logits`` is the full-width [M][V] buffer whose columns
+        [v0, v0 + vn) this rank has filled."""
+        M = logits.shape[0]
+        local = logits[:, v0:v0 + vn]
+        self.stats["head_pick"] += 1
+        if self.fused and M <= self.head_rows:
+            code = _native.cuda().grm_tp_head_pick(
+                _native.ptr(local), ctypes.c_int(logits.stride(0)), ctypes.c_int(M), ctypes.c_int(vn), ctypes.c_int(v0),
+                self.head_recv.ptr_array(), _native.ptr(self.head_epochs), _native.ptr(out_ids), None, ctypes.c_int(self.world),
+                ctypes.c_int(self.rank), ctypes.c_int(self.head_rows), ctypes.c_uint(self.spin), _native.stream_ptr())
+            _native.check(code, "tp_head_pick")
+            return out_ids
+        # composition of library calls (CPU ranks, NCCL baseline): same rule
+        lf = local.float()
+        lf = torch.where(torch.isnan(lf), torch.full_like(lf, float("-inf")), lf)
+        val, idx = lf.max(dim=1)
+        first = (lf == val[:, None]).int().argmax(dim=1)              # lowest index among equal values
+        cand = torch.stack([val.double(), torch.where(torch.isinf(val) & (val < 0), torch.full_like(first, 0x7fffffff), first + v0).double()], dim=1)
+        allc = [torch.empty_like(cand) for _ in range(self.world)]
+        dist.all_gather(allc, cand.contiguous(), group=self.group)
+        allc = torch.stack(allc, dim=1)                               # [M][W][2]
+        out_ids.copy_(pick_candidates(allc[..., 0], allc[..., 1].long()).to(out_ids.dtype))
+        return out_ids
+
+    def gather_head(self, logits: torch.Tensor) -> torch.Tensor:
+        """Fill the other ranks' column blocks of the [n][V] logits rows (all-gather of the slices)."""
+        n, V = logits.shape
+        vs, W = self.head_vs, self.world
+        v0 = self.rank * vs
+        mine = torch.zeros(n, vs, dtype=logits.dtype, device=logits.device)
+        mine[:, : min(V, v0 + vs) - v0] = logits[:, v0:v0 + vs]
+        parts = torch.empty(W, n, vs, dtype=logits.dtype, device=logits.device)
+        dist.all_gather(list(parts.unbind(0)), mine, group=self.group)
+        for r in range(W):
+            if r != self.rank:
+                a = r * vs
+                b = min(V, a + vs)
+                logits[:, a:b] = parts[r][:, : b - a]
+        return logits
 
     # ------------------------------------------------------------------------------------------
     def row_parallel_add(self, lin, x: torch.Tensor, h: torch.Tensor) -> None:

@@ -75,10 +75,10 @@ def _worker(rank, world, port, q, fused):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [True, False])
-def test_ep2_gpu_matches_single_gpu(fused):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("fused,world", [(True, 2), (False, 2), (True, 4), (True, 8)])
+def test_ep_gpu_matches_single_gpu(fused, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from grimoire_b200.engine.engine import Engine, EngineLimits
     from grimoire_b200.models.hybrid import HybridModel
 
@@ -86,7 +86,7 @@ def test_ep2_gpu_matches_single_gpu(fused):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, fused)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, fused)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -104,4 +104,4 @@ def test_ep2_gpu_matches_single_gpu(fused):
         assert float((torch.from_numpy(lg) - lg0).abs().max()) < 0.02 * scale
         assert te == tg                      # graph replay == eager
         assert te == te0 and both == both0
-    assert (res[0][1] == res[1][1]).all()    # ranks agree bit for bit
+    assert all((res[0][1] == r[1]).all() for r in res[1:])    # ranks agree bit for bit

@@ -19,9 +19,11 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q, fused):
+def _worker(rank, world, port, q, fused, split=False, mega=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    if mega:
+        os.environ["GRIMOIRE_MEGA"] = "1"       # read when ops.mega is first imported (below, in this child)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -33,11 +35,13 @@ def _worker(rank, world, port, q, fused):
         from grimoire_b200.ops.core import status_read
         from grimoire_b200.parallel.tp import TensorParallel
 
-        cfg = small_dense(layers=3)
+        cfg = small_dense(layers=3, wide=world > 2)
         sd = random_state_dict(cfg, seed=0)
         model = DenseModel.from_state_dict(cfg, sd, dev, tp_rank=rank, tp_world=world)
         tp = TensorParallel(dist.group.WORLD, dev, fused=fused)
         tp.attach(model, max_rows=256)
+        if split:
+            assert tp.split_head(model)
         eng = Engine(model, EngineLimits(max_slots=2, max_ctx=512, prefill_chunk=128, max_decode_rows=16))
         g = torch.Generator().manual_seed(1)
         prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
@@ -52,16 +56,20 @@ def _worker(rank, world, port, q, fused):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [True, False])
-def test_tp2_gpu_tokens_equal_single_gpu(fused):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("fused,split,mega,world", [(True, False, False, 2), (False, False, False, 2), (True, True, False, 2),
+                                                    (False, True, False, 2), (True, True, True, 2), (True, True, False, 4),
+                                                    (True, True, False, 8)])
+def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world):
+    """fused: one-shot all-reduce in the projection kernels (False = the NCCL composition); split: vocabulary-split lm_head
+    with the (value, index) candidate exchange; mega: the persistent phase kernel with its in-kernel all-reduce."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from grimoire_b200.engine.engine import Engine, EngineLimits
     from grimoire_b200.models.config import small_dense
     from grimoire_b200.models.dense import DenseModel
     from grimoire_b200.models.synthetic import random_state_dict
 
-    cfg = small_dense(layers=3)
+    cfg = small_dense(layers=3, wide=world > 2)
     sd = random_state_dict(cfg, seed=0)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
@@ -70,7 +78,7 @@ def test_tp2_gpu_tokens_equal_single_gpu(fused):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, fused)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, fused, split, mega)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -83,12 +91,14 @@ def test_tp2_gpu_tokens_equal_single_gpu(fused):
             if p.is_alive():
                 p.kill()
                 p.join(timeout=10)
-    assert codes == [0, 0], codes
+    assert codes == [0] * world, codes
     outs = {r: o for r, o, _, _ in res}
-    assert outs[0] == outs[1]                       # ranks never drift
+    assert all(outs[r] == outs[0] for r in range(world))      # ranks never drift
     agree = sum(int(a == b) for a, b in zip(outs[0], single))
     assert agree >= 14, (outs[0], single)           # fp32 summation order differs from one GPU
     for _, _, stats, status in res:
         assert status[0] == 0
-        if fused:
+        if fused and not mega:
             assert stats["fused_allreduce"] > 0
+        if split:
+            assert stats["head_pick"] >= 15

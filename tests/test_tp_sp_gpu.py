@@ -21,15 +21,17 @@ def _free_port():
     return p
 
 
-def _setup():
+def _setup(world=2):
+    """The fused path needs whole 128-row tiles per rank: chunks of 128 * world rows, two of them plus a ragged tail."""
     from grimoire_b200.models.config import small_dense
     from grimoire_b200.models.synthetic import random_state_dict
 
-    cfg = small_dense(layers=3)
+    cfg = small_dense(layers=3, wide=world > 2)
     sd = random_state_dict(cfg, seed=0)
     g = torch.Generator().manual_seed(3)
-    prompt = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
-    return cfg, sd, prompt
+    chunk = 128 * world
+    prompt = torch.randint(0, cfg.vocab_size, (2 * chunk + 88,), generator=g).tolist()
+    return cfg, sd, prompt, chunk
 
 
 def _worker(rank, world, port, q):
@@ -44,11 +46,11 @@ def _worker(rank, world, port, q):
         from grimoire_b200.ops.core import status_read
         from grimoire_b200.parallel.tp import TensorParallel
 
-        cfg, sd, prompt = _setup()
+        cfg, sd, prompt, chunk = _setup(world)
         model = DenseModel.from_state_dict(cfg, sd, dev, tp_rank=rank, tp_world=world)
         tp = TensorParallel(dist.group.WORLD, dev, fused=True)
-        tp.attach(model, max_rows=256)
-        eng = Engine(model, EngineLimits(max_slots=2, max_ctx=1024, prefill_chunk=256, max_decode_rows=16))
+        tp.attach(model, max_rows=chunk)
+        eng = Engine(model, EngineLimits(max_slots=2, max_ctx=len(prompt) + 128, prefill_chunk=chunk, max_decode_rows=16))
         s = eng.open()
         lg = eng.prefill(s, prompt).float().cpu()
         torch.cuda.synchronize()
@@ -60,20 +62,22 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_fused_sp_prefill_matches_single_gpu():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_sp_prefill_matches_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from grimoire_b200.engine.engine import Engine, EngineLimits
     from grimoire_b200.models.dense import DenseModel
 
-    cfg, sd, prompt = _setup()
-    eng = Engine(DenseModel.from_state_dict(cfg, sd, "cuda:0"), EngineLimits(max_slots=2, max_ctx=1024, prefill_chunk=256, max_decode_rows=16))
+    cfg, sd, prompt, chunk = _setup(world)
+    eng = Engine(DenseModel.from_state_dict(cfg, sd, "cuda:0"), EngineLimits(max_slots=2, max_ctx=len(prompt) + 128, prefill_chunk=chunk,
+                                                                            max_decode_rows=16))
     want = eng.prefill(eng.open(), prompt).float().cpu()
     del eng
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     [p.start() for p in procs]
     try:
         res = [q.get(timeout=240) for _ in procs]
@@ -84,11 +88,11 @@ def test_fused_sp_prefill_matches_single_gpu():
             if p.is_alive():
                 p.kill()
                 p.join(timeout=10)
-    assert codes == [0, 0], codes
+    assert codes == [0] * world, codes
     for rank, lg, rs_expect, status in res:
         assert status[0] == 0, status
         assert rs_expect > 0                                    # the fused path really ran
         scale = float(want.abs().max())
         assert float((lg - want).abs().max()) < 0.03 * max(scale, 1.0), (rank, float((lg - want).abs().max()), scale)
         assert int(lg.argmax()) == int(want.argmax())
-    assert torch.equal(res[0][1], res[1][1])                    # both ranks hold identical logits
+    assert all(torch.equal(res[0][1], r[1]) for r in res[1:])    # every rank holds identical logits
