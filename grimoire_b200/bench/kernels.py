@@ -96,6 +96,34 @@ def bench_smallm(args) -> None:
               f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
 
 
+def bench_tc(args) -> None:
+    """Single-row int4 projections as a tensor-core weight stream (gemv_w4_tc.cu), same shapes and byte count."""
+    from ..formats.w4_rowblock import STAGE_BYTES, W4RowBlock
+
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        nbytes = (N // 128) * (K_ // 128) * STAGE_BYTES
+        copies = max(2, int(L2_BYTES * 2 // nbytes) + 1)
+        lins = []
+        for _ in range(copies):
+            lin = _synthetic_w4(32, 64, sw, dev)
+            lin.N, lin.K, lin.Np, lin.out_features = N, K_, N, N // 2 if sw else N
+            data = torch.randint(0, 256, (N // 128, K_ // 128, STAGE_BYTES), dtype=torch.uint8, device=dev)
+            szw = torch.tensor([0x00, 0x1C, 0x08, 0x43], dtype=torch.uint8, device=dev).repeat(128)     # scale 2^-8, zero 8
+            data[:, :, 8192:] = szw
+            lin.rb = W4RowBlock(data, N, K_, N)
+            lins.append(lin)
+        x = torch.randn(1, K_, device=dev).bfloat16()
+        out = torch.zeros(1, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        us = timed(lambda i: lins[i % copies]._tc_row(x, None, None, out, epi, 0.0, 0.0), args.iters)
+        gbs = nbytes / 1e9 / (us * 1e-6)
+        print(f"gemv_w4_tc {name:8s} M= 1 N={N:6d} K={K_:6d} copies={copies:2d}  {us:8.2f} us  {gbs:7.0f} GB/s  "
+              f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
+
+
 def bench_mx(args) -> None:
     """MXFP4 small-M kernel on the same shapes (bytes = packed e2m1 + e8m0 scales)."""
     from ..formats.codecs import Fmt
@@ -221,7 +249,7 @@ def bench_prefill(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["smallm", "mx", "rowq", "gemm", "attn", "prefill"])
+    ap.add_argument("what", choices=["smallm", "tc", "mx", "rowq", "gemm", "attn", "prefill"])
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
@@ -229,7 +257,7 @@ def main(argv=None) -> None:
     ap.add_argument("--fmt", default="int8", help="rowq: int8 / bf16 / fp8_e4m3 / fp8_e5m2 / mxfp8")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
-    {"smallm": bench_smallm, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
+    {"smallm": bench_smallm, "tc": bench_tc, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
     print(f"launches={_native.launch_count}", flush=True)
 
 

@@ -40,6 +40,7 @@ struct DecParams {
   const float* k_norm_w;           // [D] or null
   float norm_eps, norm_offset;
   int rot;
+  int prefetch;                    // 1: the kernel before this one in the stream writes only the qkv rows (see the kernel)
   unsigned int* status;            // device status block (bounded waits report here)
   int cluster;                     // 1: the splits of a (row, kv head) are one thread-block cluster and merge through DSMEM
   unsigned long long* tl;          // optional per-CTA timeline (8 words per CTA, thread 0: clock64 at the marks below)
@@ -240,8 +241,27 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  // The page loads start after the q prologue.  Requesting the first pages before it was measured and does not pay: the
-  // prologue's own global loads then return behind the page traffic, and prologue + page phase take as long as before.
+  // Programmatic dependent launch: this kernel may start while its predecessor (the q|k|v projection) is still running.
+  // Everything the predecessor does not write -- the row tables, the block table, the pages of earlier tokens -- may be
+  // read before grm_pdl_wait(): with p.prefetch every warp requests its first STAGES-1 pages here, so they are in shared
+  // memory by the time the projection has finished.  The one page that receives this step's K / V (the last page, in
+  // the CTA that appends to it) is requested after the append.  Without PDL (or with p.prefetch 0) the loads start
+  // after the q prologue: requesting them right before it in the same kernel was measured and does not pay, the
+  // prologue's own global loads then return behind the page traffic.
+  grm_pdl_trigger();
+  const int hot_page = (fused && pbeg < pend && pend == page_hi) ? (len - 1) / kPage : -1;
+  int pg = pbeg + warp;
+  bool late = false;                 // this warp owns the page that is loaded after the append
+  if (p.prefetch) {
+#pragma unroll
+    for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+      const int pgs = pg + s0 * kWarps;
+      const bool defer = pgs == hot_page;
+      late = late || defer;
+      issue(defer ? pend : pgs, s0);           // a page index >= pend commits an empty group
+    }
+  }
+  grm_pdl_wait();
   if (fused && pbeg < pend && pend == page_hi && warp < 2) {
     // This CTA's split holds the last page: append the row's K (warp 0: norm, RoPE) and V (warp 1) to it -- int8 with a
     // scale per (token, head) -- before the barrier below; the page loads start after it.
@@ -324,12 +344,18 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(const DecParams p
   float o[DT][4];
 #pragma unroll
   for (int j = 0; j < DT; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
-  int pg = pbeg + warp;
+  if (!p.prefetch) {
 #pragma unroll
-  for (int s0 = 0; s0 < STAGES - 1; ++s0) issue(pg + s0 * kWarps, s0);
+    for (int s0 = 0; s0 < STAGES - 1; ++s0) issue(pg + s0 * kWarps, s0);
+  } else if (late) {
+    // the appended page is this warp's last one and is visible now (barrier above): one more group; the loop then
+    // waits for all groups instead of all but the newest ones
+    issue(hot_page, ((hot_page - pg) / kWarps) % STAGES);
+  }
   int st = 0;
   for (; pg < pend; pg += kWarps) {
-    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    if (late) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    else asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncwarp();
     issue(pg + (STAGES - 1) * kWarps, (st + STAGES - 1) % STAGES);
     const uint8_t* sb = ring + st * STAGE_BYTES;
@@ -636,15 +662,18 @@ int launch(const DecParams& p_in, int splits, cudaStream_t st) {
   if (p.cluster) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kRing; cfg.stream = st;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = (unsigned)splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = (grm_pdl_enabled() & GRM_PDL_ATTN) ? 1 : 0;
+    cfg.attrs = at; cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attn_kernel<D, G>, p);
     if (e != cudaSuccess) return (int)e;
     GRM_LAUNCH_RET();
   }
-  decode_attn_kernel<D, G><<<grid, kThreads, kRing, st>>>(p);
+  cudaError_t e = grm_launch_pdl(GRM_PDL_ATTN, decode_attn_kernel<D, G>, grid, dim3(kThreads), (size_t)kRing, st, p);
+  if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }
 
@@ -687,7 +716,7 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
   p.gate = (const bf16*)gate; p.out = (bf16*)out; p.ld_o = ld_o; p.part_o = (float*)part_o; p.part_ml = (float*)part_ml;
   p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
   p.qkv = nullptr; p.ld_qkv = 0; p.inv_freq = nullptr; p.q_norm_w = p.k_norm_w = nullptr; p.norm_eps = p.norm_offset = 0.f; p.rot = 0;
-  p.tl = g_attn_timeline;
+  p.tl = g_attn_timeline; p.prefetch = 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int G = Hq / Hkv;
   switch (D) {
@@ -701,11 +730,14 @@ GRM_API int grm_paged_decode_attn(const void* q, int ld_q, const void* row_seq, 
 // The same attention with the q/k norm, RoPE and the KV append of the rows' own tokens folded in (the work of
 // grm_rope_kvwrite): qkv is the raw fused projection output [M][(Hq + 2 Hkv) * D] (ungated q).  Valid when no row
 // attends to a token that another row of the same launch appends, i.e. every row is a different sequence.
+// prefetch != 0 promises that the kernel launched before this one in the stream writes nothing this kernel reads except
+// the qkv rows (it is the q|k|v projection): the pages of earlier tokens are then requested while that kernel is still
+// running (programmatic dependent launch).
 GRM_API int grm_paged_decode_attn_fused(const void* qkv, int ld_qkv, const void* inv_freq, const void* q_norm_w, const void* k_norm_w,
                                         float norm_eps, float norm_offset, int rot, const void* row_seq, const void* row_pos,
                                         const void* block_table, int max_pages, void* k_pages, void* v_pages, void* k_scale,
                                         void* v_scale, void* out, int ld_o, void* part_o, void* part_ml, void* counters, int M,
-                                        int Hq, int Hkv, int D, int splits, int window, float scale, void* stream) {
+                                        int Hq, int Hkv, int D, int splits, int window, float scale, int prefetch, void* stream) {
   if (M < 1 || Hkv < 1 || Hq % Hkv || splits < 1 || splits > kMaxSplits || (ld_o & 3) || !qkv || !inv_freq || (rot & 63) || rot > D ||
       rot < 64)
     return -2;
@@ -718,7 +750,7 @@ GRM_API int grm_paged_decode_attn_fused(const void* qkv, int ld_qkv, const void*
   p.counters = (unsigned int*)counters; p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale;
   p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.inv_freq = (const float*)inv_freq; p.q_norm_w = (const float*)q_norm_w;
   p.k_norm_w = (const float*)k_norm_w; p.norm_eps = norm_eps; p.norm_offset = norm_offset; p.rot = rot;
-  p.tl = g_attn_timeline;
+  p.tl = g_attn_timeline; p.prefetch = (prefetch && (grm_pdl_enabled() & GRM_PDL_ATTN) && (grm_pdl_enabled() & GRM_PDL_ATTN_PREFETCH)) ? 1 : 0;
   cudaStream_t st = (cudaStream_t)stream;
   const int G = Hq / Hkv;
   switch (D) {

@@ -21,6 +21,32 @@ typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through grm_launch_pdl may start while the kernel before it in the
+// stream is still running; it must call grm_pdl_wait() before it reads anything that kernel writes and before it writes
+// anything at all (the wait returns when the predecessor has completed and its memory is visible), and it calls
+// grm_pdl_trigger() first thing so that its own successor may be scheduled as soon as SM resources free up.  What runs
+// before the wait -- weight prefetch, reads of data older than the predecessor -- overlaps the predecessor's tail and
+// the launch latency.  Both instructions are no-ops in a kernel launched the plain way.  Works inside stream capture
+// (the edge becomes a programmatic dependency of the graph).  grm_set_pdl(mask) selects the kernel families launched
+// this way (GRM_PDL_* bits); 0 launches everything the plain way.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grm_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grm_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+extern "C" int grm_pdl_enabled();
+enum { GRM_PDL_GEMV = 1, GRM_PDL_ATTN = 2, GRM_PDL_ATTN_PREFETCH = 4, GRM_PDL_MISC = 8 };
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t grm_launch_pdl(int which, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = (grm_pdl_enabled() & which) ? 1 : 0;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// ---------------------------------------------------------------------------------------------
 // status block: one per device context, read by grm_status_read().  Slot 0 = first error code
 // (0 = none), slot 1 = detail word, slot 2 = number of timeouts seen.
 // ---------------------------------------------------------------------------------------------

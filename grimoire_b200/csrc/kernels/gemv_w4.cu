@@ -88,12 +88,15 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
   const uint4* wp = p.w + ((size_t)(tile >> 1) * KT * 2 + (tile & 1)) * 32 + lane;   // + kt * 64
   const uint32_t* szp = p.sz + (size_t)tile * G * 16 + g;
 
-  // first weights in flight before the activations are staged
+  // first weights in flight before the activations are staged -- and, under a programmatic dependent launch, before the
+  // kernel that produces the activations has finished: everything above and these loads touch only the weights
+  grm_pdl_trigger();
   uint4 cur[G64];
   if (gbeg < gend) {
 #pragma unroll
     for (int u = 0; u < G64; ++u) cur[u] = ldg_stream_v4(wp + (size_t)(gbeg * G64 + u) * 64);
   }
+  grm_pdl_wait();
   // activations -> fp16 in shared memory.  Without SwiGLU every K slice belongs to one warp, which stages just its
   // own columns and needs no CTA barrier; the gate and up warps of a SwiGLU CTA share slices and stage together.
   float rnorm = 0.f;
@@ -377,12 +380,14 @@ int launch_epi(const GemvW4Params& p, cudaStream_t st) {
     else if (p.g64 == 4) oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_w4_kernel<EPI, 4>, kGvWarps * 32, smem);
     if (oe != cudaSuccess || (long)per_sm * sms < (long)grid) return -2;
   }
+  cudaError_t e;
   switch (p.g64) {
-    case 1: gemv_w4_kernel<EPI, 1><<<grid, kGvWarps * 32, smem, st>>>(p); break;
-    case 2: gemv_w4_kernel<EPI, 2><<<grid, kGvWarps * 32, smem, st>>>(p); break;
-    case 4: gemv_w4_kernel<EPI, 4><<<grid, kGvWarps * 32, smem, st>>>(p); break;
+    case 1: e = grm_launch_pdl(GRM_PDL_GEMV, gemv_w4_kernel<EPI, 1>, dim3(grid), dim3(kGvWarps * 32), smem, st, p); break;
+    case 2: e = grm_launch_pdl(GRM_PDL_GEMV, gemv_w4_kernel<EPI, 2>, dim3(grid), dim3(kGvWarps * 32), smem, st, p); break;
+    case 4: e = grm_launch_pdl(GRM_PDL_GEMV, gemv_w4_kernel<EPI, 4>, dim3(grid), dim3(kGvWarps * 32), smem, st, p); break;
     default: return -2;
   }
+  if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }
 

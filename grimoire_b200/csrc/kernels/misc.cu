@@ -11,6 +11,8 @@ namespace {
 // status block: the access is skipped, never made.
 __global__ void embed_kernel(const int* __restrict__ ids, const bf16* __restrict__ table, float* __restrict__ h, int H, int V,
                              int ldh, float scale, unsigned int* status) {
+  grm_pdl_trigger();
+  grm_pdl_wait();      // the ids may come from the previous step's token pick
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool ok = id >= 0 && id < V;
@@ -40,6 +42,8 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
                                                      float* __restrict__ out_val, float* __restrict__ part_val,
                                                      int* __restrict__ part_idx, unsigned int* __restrict__ counters, int V,
                                                      int ld) {
+  grm_pdl_trigger();
+  grm_pdl_wait();      // the logits come from the launch before this one
   __shared__ float sv[8];
   __shared__ int si[8];
   __shared__ int s_last;
@@ -108,7 +112,9 @@ __global__ void incr_pos_kernel(int* __restrict__ pos, int n, int by) {
 
 GRM_API int grm_embed(const void* ids, const void* table, void* h, int M, int H, int V, int ldh, float scale, void* stream) {
   if (H & 3) return -2;
-  embed_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const int*)ids, (const bf16*)table, (float*)h, H, V, ldh, scale, grm_status_ptr());
+  cudaError_t e = grm_launch_pdl(GRM_PDL_MISC, embed_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, (const int*)ids, (const bf16*)table, (float*)h, H,
+                                 V, ldh, scale, grm_status_ptr());
+  if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }
 
@@ -117,8 +123,9 @@ GRM_API int grm_argmax(const void* logits, void* out_id, void* out_val, void* pa
                        int V, int ld, void* stream) {
   if (!part_val || !part_idx || !counters || M < 1) return -2;
   dim3 grid(kArgChunks, M);
-  argmax_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)logits, (int*)out_id, (float*)out_val, (float*)part_val,
-                                                        (int*)part_idx, (unsigned int*)counters, V, ld);
+  cudaError_t e = grm_launch_pdl(GRM_PDL_MISC, argmax_kernel, grid, dim3(256), 0, (cudaStream_t)stream, (const float*)logits, (int*)out_id, (float*)out_val,
+                                 (float*)part_val, (int*)part_idx, (unsigned int*)counters, V, ld);
+  if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }
 

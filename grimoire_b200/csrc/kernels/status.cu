@@ -5,7 +5,12 @@
 
 namespace {
 __device__ unsigned int g_status_words[8];
+int g_pdl = 6;
 }
+
+// Programmatic dependent launch of the decode kernels (see common.cuh): a mask of GRM_PDL_* bits, 0 = plain launches.
+GRM_API void grm_set_pdl(int mask) { g_pdl = mask; }
+GRM_API int grm_pdl_enabled() { return g_pdl; }
 
 // Device address of the status block of the current device (resolved once per device).
 GRM_API unsigned int* grm_status_ptr() {

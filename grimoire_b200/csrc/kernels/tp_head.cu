@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(kThreads) tp_head_pick_kernel(const PickParams
   __shared__ int ci[8];
   __shared__ int s_fail;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  grm_pdl_trigger();
+  grm_pdl_wait();        // the logits come from the launch before this one
   const float* lg = p.logits + (size_t)row * p.ld;
   float bv = -INFINITY;
   int bi = kNone;
@@ -119,6 +121,7 @@ GRM_API int grm_tp_head_pick(const void* logits, int ld, int M, int vn, int v0, 
   p.status = grm_status_ptr();
   p.world = world; p.rank = rank; p.max_rows = max_rows;
   p.spin = spin ? spin : 4000000u;
-  tp_head_pick_kernel<<<M, kThreads, 0, (cudaStream_t)stream>>>(p);
+  cudaError_t e = grm_launch_pdl(GRM_PDL_MISC, tp_head_pick_kernel, dim3(M), dim3(kThreads), 0, (cudaStream_t)stream, p);
+  if (e != cudaSuccess) return (int)e;
   GRM_LAUNCH_RET();
 }

@@ -37,6 +37,7 @@ class Engine:
         self.device = model.device
         self.limits = limits or EngineLimits()
         lim = self.limits
+        K.apply_pdl_switch()
         n_attn = getattr(model, "kv_layer_count", len(model.layers)) + lim.extra_kv_layers   # attention layers of this stage
         self.mtp = None                  # models.mtp.MtpDrafter attaches itself here
         pages = lim.kv_pages or (lim.max_slots * ((lim.max_ctx + PAGE - 1) // PAGE))

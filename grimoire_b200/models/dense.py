@@ -388,7 +388,7 @@ class DenseModel:
         for li, L in enumerate(self.layers):
             kvl = kv_layers[li]
             if not K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos, block_table, kvl, geom,
-                                             attn, rb.splits, self.ws):
+                                             attn, rb.splits, self.ws, prefetch=True):
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, None)
                 K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, None)
             last = li == n - 1
@@ -441,7 +441,7 @@ class DenseModel:
                                gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
                 K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
             elif not ((M == 1 or rb.distinct) and gate is None and K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos,
-                                                                          block_table, kvl, geom, attn, rb.splits, self.ws)):
+                                                                          block_table, kvl, geom, attn, rb.splits, self.ws, prefetch=True)):
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
                 K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
             if tl: trace.mark("o_proj")

@@ -234,16 +234,30 @@ def paged_decode_attn(q: torch.Tensor, row_seq: torch.Tensor, row_pos: torch.Ten
 
 
 FUSED_ROPE_ATTN = os.environ.get("GRIMOIRE_FUSED_ROPE_ATTN", "1") != "0"
+# programmatic dependent launch of the decode kernels (a kernel's weight / KV prefetch overlaps its predecessor's tail)
+PDL = int(os.environ.get("GRIMOIRE_PDL", "6"))       # mask: 1 GEMV, 2 attention, 4 attention KV prefetch, 8 embed / token pick
+_pdl_applied = False
+
+
+def apply_pdl_switch() -> None:
+    """Hand GRIMOIRE_PDL to the kernel library once (the library's default is on)."""
+    global _pdl_applied
+    if not _pdl_applied and _native.cuda_available():
+        _native.cuda().grm_set_pdl(ctypes.c_int(PDL))
+        _pdl_applied = True
 
 
 def paged_decode_attn_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, q_norm_w, k_norm_w, row_seq: torch.Tensor,
                             row_pos: torch.Tensor, block_table: torch.Tensor, kv: KvLayer, geom: AttnGeom, out: torch.Tensor,
-                            splits: int, ws: Optional[Workspace]) -> bool:
+                            splits: int, ws: Optional[Workspace], prefetch: bool = False) -> bool:
     """``rope_kvwrite`` + ``paged_decode_attn`` in one launch for rows of different sequences (ungated q): the kernel
     norms / rotates q itself and the CTA that reads a row's last page appends the row's K / V first.  Returns False
-    when the case is not served (CPU tensors, gated q, switch off); the caller then runs the two kernels."""
+    when the case is not served (CPU tensors, gated q, switch off); the caller then runs the two kernels.  ``prefetch``:
+    the launch right before this one is the projection that writes ``qkv`` and nothing else this kernel reads, so the
+    kernel may fetch the pages of earlier tokens while that launch is still running."""
     if not (qkv.is_cuda and FUSED_ROPE_ATTN) or geom.q_gated or geom.rot < 64:
         return False
+    apply_pdl_switch()
     M = qkv.shape[0]
     Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
     part_o = part_ml = counters = None
@@ -258,7 +272,7 @@ def paged_decode_attn_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, q_norm_w,
         _f(geom.norm_offset), _c(geom.rot), _native.ptr(row_seq), _native.ptr(row_pos), _native.ptr(block_table),
         _c(block_table.stride(0)), _native.ptr(kv.k), _native.ptr(kv.v), _native.ptr(kv.ks), _native.ptr(kv.vs), _native.ptr(out),
         _c(out.stride(0)), _native.ptr(part_o), _native.ptr(part_ml), _native.ptr(counters), _c(M), _c(Hq), _c(Hkv), _c(D), _c(splits),
-        _c(geom.window), _f(geom.scale), _native.stream_ptr())
+        _c(geom.window), _f(geom.scale), _c(1 if prefetch else 0), _native.stream_ptr())
     if code == -2:
         return False
     _native.check(code, "paged_decode_attn_fused")

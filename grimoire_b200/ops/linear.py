@@ -19,6 +19,7 @@ from .. import _native
 from ..formats.codecs import Fmt
 from ..formats.quantize import QuantWeight
 from ..formats.w4_tile_layout import W4Tiled, tile_w4
+from ..formats import w4_rowblock
 from .workspace import Workspace, default_workspace
 
 EPI = {"bf16": 0, "f32": 1, "add_f32": 2, "swiglu": 3, "rs_push": 4}
@@ -43,6 +44,9 @@ GEMV_W4 = os.environ.get("GRIMOIRE_GEMV_W4", "1") != "0"   # single-row int4 pro
 
 
 FUSED_NORM = os.environ.get("GRIMOIRE_FUSED_NORM", "1") != "0"   # RMSNorm inside the single-row GEMV prologue
+# single-row int4 g128 projections as a tensor-core weight stream (gemv_w4_tc.cu; needs a second copy of the weight in the
+# row-block layout): 0 off, 1 on
+W4_TC = os.environ.get("GRIMOIRE_W4_TC", "0") != "0"
 # every CTA of the fused form re-reads the residual row and the norm weights (60 KB at H = 5120): worth it for a layer's
 # projections (a few hundred CTAs), not for a vocabulary-sized head (~9,500 CTAs)
 FUSED_NORM_MAX_N = int(os.environ.get("GRIMOIRE_FUSED_NORM_MAX_N", "40960"))
@@ -88,6 +92,7 @@ class W4Linear:
                  workspace: Optional[Workspace] = None):
         self.name = name
         self.N, self.K, self.group = qw.N, qw.K, qw.group
+        self.rb = None                             # row-block copy for the tensor-core single-row stream (W4_TC)
         self.swiglu = swiglu                       # rows are gate/up interleaved per 16
         self.device = torch.device(device)
         self.ws = workspace or default_workspace(device)
@@ -96,6 +101,8 @@ class W4Linear:
             self.tiled: Optional[W4Tiled] = t
             self.Np = t.N
             self.w_ref = None
+            if W4_TC and w4_rowblock.supported(qw) and (not swiglu or qw.N % 32 == 0):
+                self.rb = w4_rowblock.pack_rowblock(qw).to(self.device)
         else:
             self.tiled = None
             self.Np = qw.N
@@ -150,6 +157,8 @@ class W4Linear:
             return self._forward_ref(x, out, epi)
         t = self.tiled
         lib = _native.cuda()
+        if M == 1 and getattr(self, "rb", None) is not None and self._tc_row(x, None, None, out, epi, 0.0, 0.0):
+            return out
         if M == 1 and GEMV_W4 and t.K <= 20480:
             # one row: CUDA-core weight stream (gemv_w4.cu); the tensor-core kernel below serves 2..64 rows
             code = lib.grm_gemv_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(x), _native.ptr(out), _c(t.N), _c(t.K), _c(t.group),
@@ -187,10 +196,29 @@ class W4Linear:
 
     __call__ = forward
 
+    def _tc_row(self, x, h, norm_w, out, epi: str, eps: float, offset: float) -> bool:
+        """One row through the tensor-core weight stream (gemv_w4_tc.cu); False when the launcher refuses the shape."""
+        rb = self.rb
+        lib = _native.cuda()
+        lib.grm_gemv_w4_tc_scratch_floats.restype = ctypes.c_long
+        lib.grm_gemv_w4_tc_scratch_flags.restype = ctypes.c_long
+        partial = self.ws.get("w4tc_partial", int(lib.grm_gemv_w4_tc_scratch_floats(_c(rb.N))), torch.float32)
+        flags = self.ws.get("w4tc_flags", max(4096, int(lib.grm_gemv_w4_tc_scratch_flags(_c(rb.N)))), torch.int32, zero=True)
+        code = lib.grm_gemv_w4_tc(_native.ptr(rb.data), _native.ptr(x), _native.ptr(h), _native.ptr(norm_w), ctypes.c_float(eps),
+                                  ctypes.c_float(offset), _native.ptr(out), _c(self.N), _c(self.K), _c(EPI[epi]), _native.ptr(partial),
+                                  _native.ptr(flags), ctypes.c_uint(0), _native.stream_ptr())
+        if code == -2:
+            return False
+        _native.check(code, f"gemv_w4_tc {self.name} N={self.N} K={self.K}")
+        return True
+
     def fused_norm(self, h: torch.Tensor, norm_w: torch.Tensor, out: torch.Tensor, epi: str, eps: float, offset: float) -> bool:
         """``out = epi(RMSNorm(h) @ W^T)`` for one fp32 residual row with the norm inside the GEMV prologue (one launch
         instead of two).  Returns False when the shape or device is not served; the caller then runs norm + forward."""
         t = self.tiled
+        if (getattr(self, "rb", None) is not None and FUSED_NORM and h.shape[0] == 1 and h.dtype == torch.float32 and h.shape[1] == self.K
+                and self._tc_row(None, h, norm_w, out, epi, eps, offset)):
+            return True
         if (not GEMV_W4 or not FUSED_NORM or self.device.type != "cuda" or t is None or h.shape[0] != 1 or t.K > 20480
                 or h.dtype != torch.float32 or h.shape[1] != t.K or t.N > FUSED_NORM_MAX_N):
             return False
