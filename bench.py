@@ -250,6 +250,35 @@ def main() -> int:
         e2e = {"value": round(B * 1000.0 / max(e2e_ms, wall_ms), 2), "unit": "tok/s", "h2d_bytes_per_step": 12 * B,
                "d2h_bytes_per_step": 4 * B, "ms_per_step_device": round(e2e_ms, 4), "ms_per_step_wall": round(wall_ms, 4)}
 
+    if not args.skip_extras and world > 1 and args.prompt % world == 0:
+        # ---- prompt read with context parallelism: whole-model replicas, the chunk's rows split over the ranks ----
+        from grimoire_b200.parallel.cp import ContextParallel
+
+        del eng
+        torch.cuda.empty_cache()
+        cmodel = DenseModel.random(cfg, dev, seed=0)
+        cp = ContextParallel(dist.group.WORLD, dev)
+        cp.attach(cmodel, max_rows=args.prompt)
+        ceng = Engine(cmodel, EngineLimits(max_slots=2, max_ctx=args.prompt + 64, prefill_chunk=args.prompt, max_decode_rows=8))
+        cs = [ceng.open(), ceng.open()]
+        ceng.prefill(cs[0], prompts[0].pin_memory())
+        cp_times = []
+        for u in (1, 2, 3):
+            ceng.release(cs[1])
+            cs[1] = ceng.open()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ceng.prefill(cs[1], prompts[u].pin_memory())
+            e1.record()
+            barrier()
+            cp_times.append(max_over_ranks(e0.elapsed_time(e1)))
+        cp_ms = statistics.median(cp_times)
+        extras["pp4096_cp_tok_s"] = round(args.prompt * 1000.0 / cp_ms, 1)
+        extras["pp4096_cp_ms"] = round(cp_ms, 2)
+        extras["pp4096_cp_vs_baseline"] = round(args.prompt * 1000.0 / cp_ms / BASELINE_PP4096, 2)
+        extras["device_status_cp"] = list(K.status_read())
+
     if rank == 0:
         sampler.stop()
         clocks = sampler.summary(c_lo, c_hi)

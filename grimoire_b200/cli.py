@@ -1,4 +1,4 @@
-"""Command line: ``generate`` (default), ``serve``, ``multi TP|PP|DP``, ``quantize``, ``inspect``.
+"""Command line: ``generate`` (default), ``serve``, ``multi TP|PP|EP|CP|DP``, ``quantize``, ``inspect``.
 
 Flags of the single-prompt CLI follow tools/grimoire_main.cpp:66-167 (``-m --proj --ctx -p -n
 --prefill-only --prefix-cache-test --score-ids/--score-out --ppl ...``); no ``-p`` prints the load
@@ -114,7 +114,7 @@ def _generate(argv) -> int:
 
 def _multi(argv) -> int:
     ap = argparse.ArgumentParser(prog="grimoire multi")
-    ap.add_argument("mode", choices=["TP", "PP", "EP", "DP", "tp", "pp", "ep", "dp"])
+    ap.add_argument("mode", choices=["TP", "PP", "EP", "CP", "DP", "tp", "pp", "ep", "cp", "dp"])
     ap.add_argument("--gpus", type=int, default=0, help="ranks to start (default: all visible GPUs)")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--master-port", type=int, default=29555)

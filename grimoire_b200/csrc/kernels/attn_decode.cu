@@ -12,8 +12,11 @@
 //   arrive for a (row, kv head) merges the splits in split order (deterministic) and applies the
 //   optional sigmoid output gate of gated attention.
 #include "common.cuh"
+#include "attn_mma.cuh"
 
 namespace {
+
+using namespace attn_mma;
 
 constexpr int kPage = 16;
 constexpr int kWarps = 4;
@@ -114,25 +117,6 @@ __device__ __forceinline__ void head_norm_rope(float (&v)[D / 32], const float* 
   }
 }
 
-// int8 x int8 -> int32 tensor-core MMA (K rows are int8 already; q is split in two int8 levels)
-__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
-}
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-  const __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 // Tensor-core formulation.  Per 16-token page and warp:
 //   S[head][token] = Q K^T with the G query heads of the group as MMA rows (8 of 16 rows used), the page's
 //     tokens as two n8 tiles and int8 operands: K bytes go from global memory straight into the B
@@ -145,20 +129,6 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 //     the end with the running sum of the rounded P values (exact in fp32).
 __device__ __forceinline__ int bt_page(const DecParams& p, int seq, int page_index) {
   return p.block_table[(size_t)seq * p.max_pages + page_index];
-}
-
-// Rotation of the float4 chunks of lane (g, t)'s window in the per-warp output staging (see the store in the kernel).
-template <int D>
-__device__ __forceinline__ int so_rot(int g, int t) {
-  return D == 64 ? ((t >> 1) + 2 * g) : (2 * t + g);
-}
-// Position of dim d of head g inside sm_o[warp][g][]: the inverse of that rotation.
-template <int D>
-__device__ __forceinline__ int so_index(int g, int d) {
-  constexpr int W = D / 4;                       // dims per lane window
-  const int t = d / W, m = d % W;
-  const int chunk = ((m >> 2) + so_rot<D>(g, t)) & (D / 16 - 1);
-  return t * W + 4 * chunk + (m & 3);
 }
 
 template <int D, int G>

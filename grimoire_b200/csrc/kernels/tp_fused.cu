@@ -126,3 +126,86 @@ GRM_API int grm_rs_reduce_norm_ag(void* h, int ldh, const void* recv, const void
   rs_reduce_norm_ag_kernel<<<R, kThreads, 0, (cudaStream_t)stream>>>(p);
   GRM_LAUNCH_RET();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Context-parallel exchange of a prefill chunk's fresh k | v rows (parallel/cp.py): every rank pushes the rows it projected
+// into each peer's receive buffer with plain peer stores, counts its arrival there, waits (bounded) until the rows of all
+// ranks have arrived in its own buffer and copies them into its q|k|v matrix.  One launch; the grid is at most one CTA per
+// SM so that CTAs waiting for remote rows never keep CTAs that still have rows to push off the machine.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct CpParams {
+  bf16* qkv; int ld, qsz, width, a, b, M;
+  bf16* peer_buf[8];            // every rank's receive buffer [2 parity][rows_cap][width]
+  unsigned int* peer_cnt[8];    // every rank's arrival counters [source rank], monotonic
+  int parity;
+  unsigned int target;          // arrivals per source expected after this launch
+  int rows_cap, world, rank;
+  unsigned int spin;
+  unsigned int* status;
+};
+
+__global__ void __launch_bounds__(256) cp_push_rows_kernel(const CpParams p) {
+  __shared__ int s_fail;
+  const int tid = threadIdx.x;
+  const int vec = p.width / 8;                                  // 16-byte vectors per row
+  if (tid == 0) s_fail = 0;
+  for (int row = p.a + blockIdx.x; row < p.b; row += gridDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.qkv + (size_t)row * p.ld + p.qsz);
+    for (int r = 0; r < p.world; ++r) {
+      if (r == p.rank) continue;
+      uint4* dst = reinterpret_cast<uint4*>(p.peer_buf[r] + ((size_t)p.parity * p.rows_cap + row) * p.width);
+      for (int i = tid; i < vec; i += 256) dst[i] = src[i];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.world && tid != p.rank) red_rel_add(p.peer_cnt[tid] + p.rank, 1u);
+  if (tid < p.world && tid != p.rank) {
+    const unsigned int* c = p.peer_cnt[p.rank] + tid;
+    bool ok = false;
+    for (unsigned int i = 0; i < p.spin; ++i) {
+      if ((int)(ld_acq(c) - p.target) >= 0) { ok = true; break; }
+      __nanosleep(100);
+    }
+    if (!ok) { s_fail = 1; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x80000u | ((unsigned int)tid << 12)); }
+  }
+  __syncthreads();
+  if (s_fail) return;
+  const bf16* mine = p.peer_buf[p.rank] + (size_t)p.parity * p.rows_cap * p.width;
+  for (int row = blockIdx.x; row < p.M; row += gridDim.x) {
+    if (row >= p.a && row < p.b) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(mine + (size_t)row * p.width);
+    uint4* dst = reinterpret_cast<uint4*>(p.qkv + (size_t)row * p.ld + p.qsz);
+    for (int i = tid; i < vec; i += 256) dst[i] = __ldcg(src + i);
+  }
+}
+
+}  // namespace
+
+// Number of CTAs grm_cp_push_rows launches for `rows_local` rows per rank (every rank must use the same value: the
+// arrival target counts them).
+GRM_API int grm_cp_push_grid(int rows_local) { return rows_local < 128 ? (rows_local < 1 ? 1 : rows_local) : 128; }
+
+// qkv: this rank's [M][ld] bf16 matrix whose rows [a, b) hold fresh k | v columns [qsz, qsz + width); on return (in stream
+// order) all M rows do.  peer_buf / peer_cnt: `world` peer-mapped pointers; target: total arrivals per source after this
+// launch (the caller adds grm_cp_push_grid(b - a) per exchange).  width and ld * 2 must be multiples of 16 bytes.
+GRM_API int grm_cp_push_rows(void* qkv, int ld, int qsz, int width, int a, int b, int M, const void* const* peer_buf,
+                             const void* const* peer_cnt, int parity, unsigned int target, int rows_cap, int world, int rank,
+                             unsigned int spin, void* stream) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || (width & 7) || (ld & 7) || (qsz & 7) || a < 0 || b <= a || b > M ||
+      M > rows_cap || !peer_buf || !peer_cnt)
+    return -2;
+  CpParams p;
+  p.qkv = (bf16*)qkv; p.ld = ld; p.qsz = qsz; p.width = width; p.a = a; p.b = b; p.M = M;
+  for (int i = 0; i < 8; ++i) {
+    p.peer_buf[i] = i < world ? (bf16*)const_cast<void*>(peer_buf[i]) : nullptr;
+    p.peer_cnt[i] = i < world ? (unsigned int*)const_cast<void*>(peer_cnt[i]) : nullptr;
+  }
+  p.parity = parity & 1; p.target = target; p.rows_cap = rows_cap; p.world = world; p.rank = rank;
+  p.spin = spin ? spin : 20000000u;
+  p.status = grm_status_ptr();
+  cp_push_rows_kernel<<<grm_cp_push_grid(b - a), 256, 0, (cudaStream_t)stream>>>(p);
+  GRM_LAUNCH_RET();
+}

@@ -52,6 +52,9 @@ class Engine:
         self.d_tokens, self.d_row_seq, self.d_row_pos = i32(lim.max_decode_rows), i32(lim.max_decode_rows), i32(lim.max_decode_rows)
         pin = self.device.type == "cuda"
         self.h_stage = torch.zeros(3, lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
+        # verify blocks of a step as groups of rows for the one-pass verify attention: slot, first row, rows, first position
+        self.h_groups = torch.zeros(4, lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
+        self.d_groups = torch.zeros(4, lim.max_decode_rows, dtype=torch.int32, device=self.device)
         self.h_next = torch.zeros(lim.max_decode_rows, dtype=torch.int32, pin_memory=pin)
         self.prefix_cache = None
         self._verify: dict = {}           # slot -> (handle, first row, rows, first position) of its last verify block
@@ -212,10 +215,10 @@ class Engine:
     def _splits_for(self, M: int, max_len: int) -> int:
         return K.decode_splits(max_len, M, self.model.geom.Hkv)
 
-    def _run_rows(self, M: int, splits: int, distinct: bool = False, runs=None, full_logits: bool = True) -> torch.Tensor:
+    def _run_rows(self, M: int, splits: int, distinct: bool = False, runs=None, full_logits: bool = True, ngroups: int = 0) -> torch.Tensor:
         hs = getattr(self.model, "head_split", None)
         rb = RowBatch(self.d_tokens[:M], self.d_row_seq[:M], self.d_row_pos[:M], mode="decode", splits=splits, distinct=distinct, runs=runs,
-                      full_logits=full_logits or hs is None)
+                      full_logits=full_logits or hs is None, verify=(self.d_groups, ngroups) if ngroups else None)
         logits = self.model.forward(rb, self.decode_buf, self.kv.layers, self.kv.table)
         pp = getattr(self.model, "pp", None)
         if logits is not None and hs is not None and not rb.full_logits:
@@ -266,6 +269,17 @@ class Engine:
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
         distinct = len({s.slot for s in seqs}) == M      # no verify block: the attention kernel may append K / V itself
+        shape = ()
+        if not distinct and self.device.type == "cuda" and isinstance(self.model, DenseModel):
+            # verify blocks: groups of consecutive rows of one conversation share one pass over its cache
+            per = K.verify_rows_per_group(self.model.geom)
+            if per >= 1:
+                groups = K.verify_groups([s.slot for s in seqs], list(positions), per)
+                n = len(groups)
+                self.h_groups[:, :n] = torch.tensor(groups, dtype=torch.int32).t()
+                self.d_groups[:, :n].copy_(self.h_groups[:, :n], non_blocking=True)
+                shape = tuple(g[2] for g in groups)
+                splits = K.decode_splits(max_len, n, self.model.geom.Hkv)
         tp = getattr(self.model, "tp", None)
         ep = getattr(self.model, "ep", None)
         if (tp is not None and not tp.fused) or (ep is not None and not ep.fused) or getattr(self.model, "pp", None) is not None:
@@ -274,14 +288,14 @@ class Engine:
         if full and getattr(self.model, "head_split", None) is not None:
             use_graph = False        # whole logits rows of a split head are gathered by a library collective
         if use_graph and self.device.type == "cuda":
-            key = (M, splits, distinct)
+            key = (M, splits, distinct) + ((shape,) if shape else ())
             g = self.graphs.get(key)
             if g is None:
-                g = self._capture(M, splits, distinct)
+                g = self._capture(M, splits, distinct, len(shape), key)
             g.replay()
             self.counters["graph_replays"] += 1
         else:
-            self._run_rows(M, splits, distinct, runs, full_logits=full)
+            self._run_rows(M, splits, distinct, runs, full_logits=full, ngroups=len(shape))
         if runs is not None:
             self.model.end_verify()
         self.h_next[:M].copy_(self.decode_buf.next_ids[:M], non_blocking=True)
@@ -329,18 +343,18 @@ class Engine:
         if saved is not None:
             self.model.restore_recurrent(saved)
 
-    def _capture(self, M: int, splits: int, distinct: bool = False):
+    def _capture(self, M: int, splits: int, distinct: bool = False, ngroups: int = 0, key=None):
         # warm the allocator / workspace outside capture, then record; a model with recurrent state
         # must not keep the warm-up run's update
         saved = self._save_recurrent(M)
         full = getattr(self.model, "head_split", None) is None     # a split head is captured with its (value, index) pick
-        self._run_rows(M, splits, distinct, full_logits=full)
+        self._run_rows(M, splits, distinct, full_logits=full, ngroups=ngroups)
         torch.cuda.current_stream().synchronize()
         self._restore_recurrent(saved)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            self._run_rows(M, splits, distinct, full_logits=full)
-        self.graphs[(M, splits, distinct)] = g
+            self._run_rows(M, splits, distinct, full_logits=full, ngroups=ngroups)
+        self.graphs[key if key is not None else (M, splits, distinct)] = g
         return g
 
     # ------------------------------------------------------------------------------------------

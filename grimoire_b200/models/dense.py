@@ -68,6 +68,9 @@ class RowBatch:
     # vocabulary-split lm_head (tensor parallel): True = the returned logits rows are gathered over the ranks; False = only
     # this rank's column slice is valid and the caller picks the token with the (value, index) exchange
     full_logits: bool = True
+    # decode step with verify blocks: (int32 device tensor [4][n] of groups -- slot, first row, rows, first position --, n);
+    # the attention then reads the cache once per group of rows (attn_verify.cu) instead of once per row
+    verify: Optional[tuple] = None
 
 
 class Buffers:
@@ -108,6 +111,7 @@ class DenseModel:
         self.layer_begin = pp_rank * per + min(pp_rank, extra)
         self.layer_end = self.layer_begin + per + (1 if pp_rank < extra else 0)
         self.pp = None          # parallel.pp.PipelineParallel when pp_world > 1
+        self.cp = None          # parallel.cp.ContextParallel: prefill chunks split by rows over whole-model replicas
         self.head_split = None  # (first vocabulary row, rows) of this rank's lm_head shard (TensorParallel.split_head)
         self.ws = workspace or Workspace(device)
         if cfg.num_attention_heads % tp_world or cfg.num_key_value_heads % tp_world or cfg.intermediate_size % tp_world:
@@ -400,8 +404,50 @@ class DenseModel:
             self.tp.gather_head(logits)
         return logits
 
+    def forward_prefill_cp(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
+        """Prefill chunk under context parallelism (parallel/cp.py): this rank runs rows [a, b) of the chunk through every
+        layer; per layer the ranks exchange the chunk's raw k | v rows, every rank appends the whole chunk's K / V to its
+        own cache, and the local query rows attend over past and present keys.  Same arithmetic per row as ``forward``."""
+        cfg, geom, cp = self.cfg, self.geom, self.cp
+        M = rb.tokens.shape[0]
+        a, b = cp.local_rows(M)
+        n = b - a
+        eps, off = cfg.rms_norm_eps, cfg.norm_offset
+        h, x = buf.h[:n], buf.x[:n]
+        qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:n], buf.act[:n]
+        gate = buf.gate[:M] if buf.gate is not None else None
+        qsz = geom.Hq * geom.D * (2 if geom.q_gated else 1)
+        K.embed(rb.tokens[a:b], self.embed, h)
+        T = rb.q_pos0 + M
+        cp.stats["chunks"] += 1
+        for li, L in enumerate(self.layers):
+            kvl = kv_layers[li]
+            self._norm_linear(L.qkv, h, L.in_norm, x, qkv[a:b], "bf16", eps, off)
+            cp.exchange_kv(qkv, M, qsz, li & 1)
+            if rb.q_pos0 > 0:
+                K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
+            # norm + RoPE + cache append for the whole chunk (q of the other ranks' rows is computed from stale columns and
+            # never read)
+            K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
+                           gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+            K.flash_prefill(q[a:b], buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0 + a, None if gate is None else gate[a:b])
+            L.o(attn, h, "add_f32")
+            self._norm_linear(L.gate_up, h, L.post_norm, x, act, "swiglu", eps, off)
+            L.down(act, h, "add_f32")
+        # rows that need logits live on their owners: collect them on every rank
+        rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
+        nl = rows.shape[0]
+        sel = torch.zeros(nl, cfg.hidden_size, dtype=torch.float32, device=self.device)
+        mine = (rows >= a) & (rows < b)
+        if bool(mine.any()):
+            sel[mine] = h.index_select(0, rows[mine] - a)
+        torch.distributed.all_reduce(sel, group=cp.group)
+        return self._head(sel, buf, nl, rb)
+
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
+        if (rb.mode == "prefill" and rb.segments is None and getattr(self, "cp", None) is not None and self.cp.ready(rb.tokens.shape[0])):
+            return self.forward_prefill_cp(rb, buf, kv_layers, block_table)
         if (rb.mode == "prefill" and rb.segments is None and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)
                 and isinstance(self.layers[0].qkv, (W4Linear, RowQLinear)) and self.tp.sp_ready(rb.tokens.shape[0]) and self.tp.sp_enabled):
             return self.forward_prefill_sp(rb, buf, kv_layers, block_table)
@@ -443,7 +489,9 @@ class DenseModel:
             elif not ((M == 1 or rb.distinct) and gate is None and K.paged_decode_attn_fused(qkv, self.inv_freq, L.q_norm, L.k_norm, rb.row_seq, rb.row_pos,
                                                                           block_table, kvl, geom, attn, rb.splits, self.ws, prefetch=True)):
                 K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
-                K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+                if not (rb.verify is not None and K.paged_verify_attn(q, rb.verify[0], rb.verify[1], block_table, kvl, geom, attn,
+                                                                      rb.splits, self.ws, gate)):
+                    K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
             if tl: trace.mark("o_proj")
             self._row_parallel(L.o, attn, h)
             if tl: trace.mark("norm+gate_up")

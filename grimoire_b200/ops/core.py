@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -276,6 +276,56 @@ def paged_decode_attn_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, q_norm_w,
     if code == -2:
         return False
     _native.check(code, "paged_decode_attn_fused")
+    return True
+
+
+VERIFY_ATTN = os.environ.get("GRIMOIRE_VERIFY_ATTN", "1") != "0"     # verify blocks: (row, head) pairs in the MMA rows
+
+
+def verify_rows_per_group(geom: AttnGeom) -> int:
+    """Rows of one verify block that share a pass over the cache (floor(16 / G), attn_verify.cu)."""
+    G = geom.Hq // geom.Hkv
+    return 16 // G if G <= 16 else 0
+
+
+def verify_groups(slots: Sequence[int], positions: Sequence[int], per: int):
+    """Cut the rows of a step into groups for ``paged_verify_attn``: maximal runs of consecutive positions of one
+    sequence, at most ``per`` rows each.  Returns lists (slot, first row, rows, first position)."""
+    out = []
+    i, M = 0, len(slots)
+    while i < M:
+        n = 1
+        while i + n < M and n < per and slots[i + n] == slots[i] and positions[i + n] == positions[i] + n:
+            n += 1
+        out.append((int(slots[i]), i, n, int(positions[i])))
+        i += n
+    return out
+
+
+def paged_verify_attn(q: torch.Tensor, blocks: torch.Tensor, nblocks: int, block_table: torch.Tensor, kv: KvLayer, geom: AttnGeom,
+                      out: torch.Tensor, splits: int, ws: Workspace, gate: Optional[torch.Tensor] = None) -> bool:
+    """Attention of verify blocks in one pass over the pages per group of rows (attn_verify.cu; launch_verify_attn_dpas,
+    src/attn_verify.hpp:48-69).  ``blocks`` is an int32 device tensor [4][>= nblocks]: sequence slot, first row, rows,
+    first position of every group (``verify_groups``).  K / V of the rows must already be in the cache.  Returns False
+    when the case is not served (CPU tensors, switch off); the caller then runs the per-row kernel."""
+    if not (q.is_cuda and VERIFY_ATTN) or verify_rows_per_group(geom) < 1:
+        return False
+    Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
+    part_o = part_ml = counters = None
+    if splits > 1:
+        part_o = ws.get("vattn_part_o", nblocks * Hkv * splits * 16 * D, torch.float32)
+        part_ml = ws.get("vattn_part_ml", nblocks * Hkv * splits * 16 * 2, torch.float32)
+        counters = ws.get("vattn_counters", 4096, torch.int32, zero=True)
+        if nblocks * Hkv > 4096:
+            return False
+    code = _native.cuda().grm_paged_verify_attn(
+        _native.ptr(q), _c(q.stride(0)), _native.ptr(blocks[0]), _native.ptr(blocks[1]), _native.ptr(blocks[2]), _native.ptr(blocks[3]),
+        _c(nblocks), _native.ptr(block_table), _c(block_table.stride(0)), _native.ptr(kv.k), _native.ptr(kv.v), _native.ptr(kv.ks),
+        _native.ptr(kv.vs), _native.ptr(gate), _native.ptr(out), _c(out.stride(0)), _native.ptr(part_o), _native.ptr(part_ml),
+        _native.ptr(counters), _c(Hq), _c(Hkv), _c(D), _c(splits), _c(geom.window), _f(geom.scale), _native.stream_ptr())
+    if code == -2:
+        return False
+    _native.check(code, "paged_verify_attn")
     return True
 
 

@@ -29,6 +29,8 @@ class ParallelLayout:
     ep_rank: int = 0
     ep_world: int = 1
     ep_group: Optional[object] = None
+    cp_world: int = 1
+    cp_group: Optional[object] = None
     control_group: Optional[object] = None
     device: Optional[torch.device] = None
 
@@ -37,15 +39,18 @@ class ParallelLayout:
         return self.rank == 0
 
 
-def init_parallel(tp_world: int = 1, pp_world: int = 1, backend: Optional[str] = None, ep_world: int = 1) -> ParallelLayout:
-    """``ep_world`` > 1 (expert parallelism of the hybrid MoE family) uses every rank as one expert shard; it does not
-    combine with tensor or pipeline stages."""
+def init_parallel(tp_world: int = 1, pp_world: int = 1, backend: Optional[str] = None, ep_world: int = 1, cp_world: int = 1) -> ParallelLayout:
+    """``ep_world`` > 1 (expert parallelism of the hybrid MoE family) uses every rank as one expert shard; ``cp_world`` > 1
+    (context parallelism: prompt chunks split by rows) uses every rank as a whole-model replica.  Neither combines with
+    tensor or pipeline stages."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if ep_world > 1 and (tp_world != 1 or pp_world != 1 or ep_world != world):
         raise ValueError(f"expert parallel {ep_world} must span the whole world ({world}) without tp / pp")
-    if ep_world == 1 and tp_world * pp_world != world:
+    if cp_world > 1 and (tp_world != 1 or pp_world != 1 or ep_world != 1 or cp_world != world):
+        raise ValueError(f"context parallel {cp_world} must span the whole world ({world}) without tp / pp / ep")
+    if ep_world == 1 and cp_world == 1 and tp_world * pp_world != world:
         raise ValueError(f"tp {tp_world} x pp {pp_world} != world size {world}")
     cuda = torch.cuda.is_available()
     backend = backend or ("nccl" if cuda else "gloo")
@@ -58,7 +63,7 @@ def init_parallel(tp_world: int = 1, pp_world: int = 1, backend: Optional[str] =
             dist.init_process_group("nccl", device_id=dev)
         else:
             dist.init_process_group(backend)
-    tp_rank, pp_rank = (rank % tp_world, rank // tp_world) if ep_world == 1 else (0, 0)
+    tp_rank, pp_rank = (rank % tp_world, rank // tp_world) if ep_world == 1 and cp_world == 1 else (0, 0)
     lay = ParallelLayout(rank, world, tp_rank, tp_world, pp_rank, pp_world, device=dev)
     # every rank must create every group, in the same order
     for p in range(pp_world):
@@ -73,5 +78,7 @@ def init_parallel(tp_world: int = 1, pp_world: int = 1, backend: Optional[str] =
             lay.pp_group = g
     if ep_world > 1:
         lay.ep_rank, lay.ep_world, lay.ep_group = rank, ep_world, dist.new_group(list(range(world)))
+    if cp_world > 1:
+        lay.cp_world, lay.cp_group = cp_world, dist.new_group(list(range(world)))
     lay.control_group = dist.new_group(list(range(world)), backend="gloo") if world > 1 else None
     return lay

@@ -521,3 +521,40 @@ def test_gemv_w4_single_row_saturates_instead_of_overflowing():
     out = torch.empty(1, lin.Np, dtype=torch.float32, device=DEV)
     lin(x.to(DEV).bfloat16(), out, "f32")
     assert torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,gated,window", [(40, 8, 128, False, 0), (32, 8, 128, False, 0), (8, 8, 64, False, 0),
+                                                     (16, 2, 256, True, 0), (8, 2, 128, False, 64)])
+def test_verify_attention_one_pass_equals_row_wise(Hq, Hkv, D, gated, window):
+    """A verify block's rows x the GQA group's heads as MMA rows, one pass over the pages per group of rows
+    (attn_verify.cu), against the per-row kernel on the same cache: causal inside the block, several blocks and a
+    single row in one launch, with and without split-KV (launch_verify_attn_dpas, src/attn_verify.hpp:48-69)."""
+    torch.manual_seed(9)
+    S, max_ctx = 3, 512
+    geom = K.AttnGeom(Hq, Hkv, D, min(D, 128), 1.0 / math.sqrt(D), gated, window, 1e-6, 0.0)
+    kv, table = _mk_kv(S, max_ctx, Hkv, D)
+    kv.k.random_(-127, 127)
+    kv.v.random_(-127, 127)
+    kv.ks.uniform_(0.005, 0.02)
+    kv.vs.uniform_(0.005, 0.02)
+    per = K.verify_rows_per_group(geom)
+    assert per == 16 // (Hq // Hkv)
+    # a 5-row block on sequence 1 near a page boundary, a 2-row block on sequence 0, one plain row on sequence 2
+    rows = [(1, p) for p in range(300, 305)] + [(0, 14), (0, 15)] + [(2, 499)]
+    M = len(rows)
+    groups = K.verify_groups([r[0] for r in rows], [r[1] for r in rows], per)
+    assert sum(g[2] for g in groups) == M and all(g[2] <= per for g in groups)
+    blocks = torch.tensor(groups, dtype=torch.int32).t().contiguous().to(DEV)
+    q = (torch.randn(M, Hq * D) * 0.7).bfloat16().to(DEV)
+    gate = torch.randn(M, Hq * D).bfloat16().to(DEV) if gated else None
+    rs = torch.tensor([r[0] for r in rows], dtype=torch.int32, device=DEV)
+    rp = torch.tensor([r[1] for r in rows], dtype=torch.int32, device=DEV)
+    ws = Workspace(DEV)
+    want = torch.zeros(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+    K.paged_decode_attn(q, rs, rp, table, kv, geom, want, 1, ws, gate)
+    for splits in (1, 4):
+        out = torch.zeros(M, Hq * D, dtype=torch.bfloat16, device=DEV)
+        assert K.paged_verify_attn(q, blocks, len(groups), table, kv, geom, out, splits, ws, gate)
+        err = float((out.float() - want.float()).abs().max())
+        assert err < 2e-2 * max(1.0, float(want.float().abs().max())), (splits, err)
+    _assert_clean()

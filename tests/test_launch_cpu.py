@@ -1,6 +1,6 @@
-"""``grimoire multi PP 2`` end to end on CPU ranks: the launcher starts two gloo ranks, rank 0 serves HTTP over a
-ControlledEngine, rank 1 mirrors the engine calls and runs the second pipeline stage; the completion must equal the
-single-process one (tools/test_pp_server.cpp in the reference: same tokens through a two-stage server)."""
+"""``grimoire multi PP 2`` / ``multi CP 2`` end to end on CPU ranks: the launcher starts two gloo ranks, rank 0 serves HTTP
+over a ControlledEngine, rank 1 mirrors the engine calls and runs the second pipeline stage (PP) or its half of every
+prompt chunk's rows (CP); the completion must equal the single-process one (tools/test_pp_server.cpp in the reference: same tokens through a two-stage server)."""
 import http.client
 import json
 import os
@@ -35,7 +35,8 @@ def _post(port, body, timeout=120):
     return r.status, json.loads(data)
 
 
-def test_multi_pp2_server_matches_single_process(tmp_path):
+@pytest.mark.parametrize("mode", ["PP", "CP"])
+def test_multi_2_rank_server_matches_single_process(tmp_path, mode):
     d = tmp_path / "model"
     cfg = tiny_dense()
     cfg.num_hidden_layers = 3
@@ -57,7 +58,7 @@ def test_multi_pp2_server_matches_single_process(tmp_path):
     env = dict(os.environ, GRIMOIRE_SEQ_SLOTS="2", GRIMOIRE_MAX_BATCH="2", GRIMOIRE_PREFILL_CHUNK="64", GRIMOIRE_ADMIT_HOLD_MS="1",
                GRIMOIRE_COPY="0", GRIMOIRE_MTP="0", CUDA_VISIBLE_DEVICES="", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(mport), "-m", "grimoire_b200.parallel.launch", "--mode", "PP", "--model", str(d), "--ctx", "256",
+           "--master-port", str(mport), "-m", "grimoire_b200.parallel.launch", "--mode", mode, "--model", str(d), "--ctx", "256",
            "--host", "127.0.0.1", "--port", str(port)]
     proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
     try:
@@ -73,7 +74,7 @@ def test_multi_pp2_server_matches_single_process(tmp_path):
                     break
             except OSError:
                 time.sleep(0.5)
-        assert up, "the two-stage server did not come up: " + (proc.stdout.read() if proc.poll() is not None else "timeout")
+        assert up, "the two-rank server did not come up: " + (proc.stdout.read() if proc.poll() is not None else "timeout")
         st, got = _post(port, body)
         assert st == 200
         assert got["choices"][0]["text"] == want["choices"][0]["text"]
