@@ -233,6 +233,39 @@ def bench_attn(args) -> None:
           flush=True)
 
 
+def bench_vattn(args) -> None:
+    """A verify block of ``--rows`` consecutive positions at the end of a ``--ctx``-token context: the one-pass verify
+    kernel (attn_verify.cu) against the per-row decode kernel on the same rows, and one row alone."""
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    geom = K.AttnGeom(Hq=40, Hkv=8, D=128, rot=128, scale=128 ** -0.5)
+    R = args.rows
+    slots = int(L2_BYTES * 2 // (args.ctx * geom.Hkv * geom.D * 2)) + 1
+    pool, seqs = _paged_kv(args.ctx, slots, geom, dev)
+    ws = Workspace(dev)
+    q = torch.randn(R, geom.Hq * geom.D, device=dev).bfloat16()
+    out = torch.zeros_like(q)
+    pos = torch.arange(args.ctx - R, args.ctx, dtype=torch.int32, device=dev)
+    per = K.verify_rows_per_group(geom)
+    row_seq, blocks = [], []
+    for i in range(slots):
+        row_seq.append(torch.full((R,), i, dtype=torch.int32, device=dev))
+        groups = K.verify_groups([i] * R, list(range(args.ctx - R, args.ctx)), per)
+        blocks.append(torch.tensor(groups, dtype=torch.int32).t().contiguous().to(dev))
+    ngroups = blocks[0].shape[1]
+    s_rows = K.decode_splits(args.ctx, R, geom.Hkv)
+    s_blk = K.decode_splits(args.ctx, ngroups, geom.Hkv)
+    s_one = K.decode_splits(args.ctx, 1, geom.Hkv)
+    us_rows = timed(lambda i: K.paged_decode_attn(q, row_seq[i % slots], pos, pool.table, pool.layers[0], geom, out, s_rows, ws), args.iters)
+    us_blk = timed(lambda i: K.paged_verify_attn(q, blocks[i % slots], ngroups, pool.table, pool.layers[0], geom, out, s_blk, ws), args.iters)
+    us_one = timed(lambda i: K.paged_decode_attn(q[:1], row_seq[i % slots][:1], pos[-1:], pool.table, pool.layers[0], geom, out[:1], s_one, ws),
+                   args.iters)
+    nbytes = args.ctx * geom.Hkv * (geom.D + 4) * 2
+    print(f"verify block rows={R} ctx={args.ctx}: one pass per group of {per} rows ({ngroups} groups, splits {s_blk}) {us_blk:8.2f} us "
+          f"({ngroups * nbytes / 1e9 / (us_blk * 1e-6):6.0f} GB/s, {ngroups * nbytes / 1e9 / (us_blk * 1e-6) / hbm:.3f} {tag} copy bandwidth) | "
+          f"row by row (splits {s_rows}) {us_rows:8.2f} us | one row {us_one:8.2f} us | block / one row = {us_blk / us_one:.2f}", flush=True)
+
+
 def bench_prefill(args) -> None:
     _, tf, tag = peaks()
     dev = "cuda"
@@ -249,7 +282,7 @@ def bench_prefill(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["smallm", "tc", "mx", "rowq", "gemm", "attn", "prefill"])
+    ap.add_argument("what", choices=["smallm", "tc", "mx", "rowq", "gemm", "attn", "vattn", "prefill"])
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
@@ -257,7 +290,7 @@ def main(argv=None) -> None:
     ap.add_argument("--fmt", default="int8", help="rowq: int8 / bf16 / fp8_e4m3 / fp8_e5m2 / mxfp8")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
-    {"smallm": bench_smallm, "tc": bench_tc, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "prefill": bench_prefill}[args.what](args)
+    {"smallm": bench_smallm, "tc": bench_tc, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "vattn": bench_vattn, "prefill": bench_prefill}[args.what](args)
     print(f"launches={_native.launch_count}", flush=True)
 
 

@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 from ..engine.engine import Engine, EngineLimits
 from ..ops import linear as _linear
-from ..engine.generation import GenerationOptions, generate_tokens
+from ..engine.generation import GenerationOptions, OracleDrafter, generate_tokens
 from ..models.config import dense_27b
 from ..models.dense import DenseModel
 from ..models.mtp import MtpDrafter, MtpHead
@@ -39,6 +39,8 @@ def main(argv=None) -> int:
     ap.add_argument("--depth", type=int, default=3)
     ap.add_argument("--quant", default="mxfp4", choices=["mxfp4", "int4"])
     ap.add_argument("--draft-vocab", type=int, default=65536)
+    ap.add_argument("--oracle-accept", type=float, default=0.7,
+                    help="per-draft acceptance probability of the oracle drafter (0 = skip that measurement)")
     ns = ap.parse_args(argv)
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     dev = torch.device("cuda", local)
@@ -55,8 +57,8 @@ def main(argv=None) -> int:
     g = torch.Generator().manual_seed(100 + rank)
     prompt = torch.randint(0, cfg.vocab_size, (ns.prompt,), generator=g).tolist()
 
-    def timed(depth: int):
-        opts = GenerationOptions(max_new=ns.out, draft_depth=depth, drafter=drafter if depth else None)
+    def timed(depth: int, dr=None):
+        opts = GenerationOptions(max_new=ns.out, draft_depth=depth, drafter=(dr or drafter) if depth else None)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
@@ -76,6 +78,14 @@ def main(argv=None) -> int:
     generate_tokens(eng, prompt[:64], GenerationOptions(max_new=8))
     plain, plain_ms, _ = timed(0)
     spec, spec_ms, st = timed(ns.depth)
+    oracle = None
+    if ns.oracle_accept > 0:
+        # the verify path at a realistic accepted length: a drafter that knows the greedy continuation and is wrong with a
+        # dialled probability (the random-weight MTP head is never right, so it only measures the cost of rejection)
+        od = OracleDrafter(prompt + plain, accept=ns.oracle_accept, vocab=cfg.vocab_size, seed=rank)
+        otoks, oms, ost = timed(ns.depth, od)
+        oracle = {"accept_probability": ns.oracle_accept, "tok_s": round(world * len(otoks) * 1000.0 / oms, 1),
+                  "accepted_length": round(ost.accept_length, 3), "rounds": ost.rounds, "tokens_equal_plain": otoks == plain}
     if rank == 0:
         print(json.dumps({"model": f"27B dense {ns.quant} + MTP head ({ns.layers} layers)", "n_gpus": world, "users": world,
                           "parallelism": "single" if world == 1 else f"dp{world}", "prompt": ns.prompt, "out": ns.out, "draft_depth": ns.depth,
@@ -85,6 +95,7 @@ def main(argv=None) -> int:
                           # one row runs the CUDA-core GEMV, verify rows the tensor-core kernel: equal to rounding only
                           # (GRIMOIRE_GEMV_W4=0 puts every width on the batch-invariant kernel and the streams are equal)
                           "batch_invariant_kernels": not _linear.GEMV_W4,
+                          "oracle_drafter": oracle,
                           "includes_prefill": True, "mtp_bytes": drafter.head.nbytes(), "build_s": round(build_s, 1),
                           "device_status": list(K.status_read()), "data": "synthetic"}), flush=True)
     if world > 1:

@@ -188,11 +188,7 @@ class W4Linear:
                                      _c(ksplit), _native.stream_ptr())
             _native.check(code, f"smallm_w4 {self.name} M={M} N={t.N} K={t.K}")
             return out
-        wbuf = self.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
-        code = lib.grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
-                                  _c(t.K), _native.stream_ptr())
-        _native.check(code, f"dequant_w4 {self.name}")
-        return gemm_bf16(x, wbuf[: self.N], out, epi)
+        return gemm_bf16(x, w4_dequant_into(self), out, epi)
 
     __call__ = forward
 
@@ -361,15 +357,51 @@ def gemm_bf16_tp(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], 
     return nt.value
 
 
+# Resident bf16 copies of int4 projections for the prompt path.  Expanding a weight on every prefill call costs its bf16
+# size in writes and again in reads (0.3 ms per 27B layer, a tenth of a 4,096-row chunk on one GPU and a third of it when
+# the rows are split over 8 context-parallel replicas); 180 GB holds the 27B model twice over in bf16, so the expansion
+# is kept after the first use while free device memory stays above a reserve.  GRIMOIRE_W4_BF16_CACHE_GB: 0 = never,
+# N = at most N GB, unset = whatever leaves 24 GB free.
+_BF16_CACHE_ENV = os.environ.get("GRIMOIRE_W4_BF16_CACHE_GB", "")
+_bf16_cached_bytes = 0
+
+
+def _bf16_cache_admit(nbytes: int, device) -> bool:
+    global _bf16_cached_bytes
+    if _BF16_CACHE_ENV == "0":
+        return False
+    if torch.cuda.is_current_stream_capturing():
+        return False
+    if _BF16_CACHE_ENV:
+        if _bf16_cached_bytes + nbytes > float(_BF16_CACHE_ENV) * 1e9:
+            return False
+    free, _ = torch.cuda.mem_get_info(device)
+    if free - nbytes < 24e9:
+        return False
+    _bf16_cached_bytes += nbytes
+    return True
+
+
 def w4_dequant_into(lin: "W4Linear") -> torch.Tensor:
-    """Dequantize an int4 (or byte-per-weight) projection into the shared bf16 scratch and return the [N][K] view."""
+    """The bf16 [N][K] form of an int4 (or byte-per-weight) projection for the tcgen05 GEMM: the resident copy when there
+    is (room for) one, else an expansion into the shared scratch."""
     if isinstance(lin, RowQLinear):
         return lin.dequant_into_scratch()
     t = lin.tiled
-    wbuf = lin.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
+    cached = getattr(lin, "_bf16", None)
+    if cached is not None:
+        return cached[: lin.N]
+    keep = not getattr(lin, "_bf16_refused", False) and _bf16_cache_admit(t.N * t.K * 2, lin.device)
+    if keep:
+        wbuf = torch.empty(t.N, t.K, dtype=torch.bfloat16, device=lin.device)
+    else:
+        lin._bf16_refused = True
+        wbuf = lin.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
     code = _native.cuda().grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
                                          _c(t.K), _native.stream_ptr())
     _native.check(code, f"dequant_w4 {lin.name}")
+    if keep:
+        lin._bf16 = wbuf
     return wbuf[: lin.N]
 
 

@@ -22,6 +22,24 @@ class Tokenizer:
         p = Path(path)
         self.dir = p if p.is_dir() else p.parent
         tj = p / "tokenizer.json" if p.is_dir() else p
+        self._spm = None
+        meta0 = json.loads(tj.read_text())
+        from .tokenizer_spm import SpmBpe, is_spm_bpe
+
+        if is_spm_bpe(meta0):
+            # SentencePiece-style BPE (spaces as U+2581, byte fallback pieces): Python path, see tokenizer_spm.py
+            self._spm = SpmBpe(meta0)
+            self._h, self._lib = None, None
+            self.nfc = False
+            self.cfg = {}
+            tc = self.dir / "tokenizer_config.json"
+            if tc.exists():
+                try:
+                    self.cfg = json.loads(tc.read_text())
+                except json.JSONDecodeError:
+                    self.cfg = {}
+            self.vocab_size = self._spm.vocab_size
+            return
         lib = _native.host()
         lib.grm_tok_load.restype = ctypes.c_void_p
         err = ctypes.create_string_buffer(512)
@@ -56,6 +74,8 @@ class Tokenizer:
 
     # ---- core ----
     def encode(self, text: str, allow_special: bool = True) -> list[int]:
+        if self._spm is not None:
+            return self._spm.encode(text, allow_special)
         if self.nfc:
             text = unicodedata.normalize("NFC", text)
         raw = text.encode("utf-8")
@@ -68,6 +88,8 @@ class Tokenizer:
         return list(buf[:n])
 
     def decode_bytes(self, ids: Sequence[int], skip_special: bool = True) -> bytes:
+        if self._spm is not None:
+            return self._spm.decode_bytes(ids, skip_special)
         arr = (ctypes.c_int * len(ids))(*ids)
         cap = 16 * len(ids) + 64
         out = ctypes.create_string_buffer(cap)
@@ -81,9 +103,13 @@ class Tokenizer:
         return self.decode_bytes(ids, skip_special).decode("utf-8", errors="replace")
 
     def special_id(self, token: str) -> int:
+        if self._spm is not None:
+            return self._spm.token_id(token)
         return self._lib.grm_tok_token_id(self._h, token.encode())
 
     def is_special(self, tok_id: int) -> bool:
+        if self._spm is not None:
+            return tok_id in self._spm.special_ids
         return bool(self._lib.grm_tok_is_special(self._h, tok_id))
 
     def eos(self) -> Optional[int]:
