@@ -38,6 +38,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--prompts", default="", help="comma-separated prompt lengths measured one after the other on one model build "
+                                                  "(one JSON line each), e.g. 4096,16384,32768,65536")
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--users", type=int, default=1)
     ap.add_argument("--nccl", action="store_true", help="all-reduce composition instead of the fused expert-parallel kernels")
@@ -53,7 +55,20 @@ def main(argv=None) -> int:
     ep = model.attach_ep(dist.group.WORLD, max_rows=4096, fused=not ns.nccl) if world > 1 else None
     torch.cuda.synchronize()
     build_s = time.time() - t0
-    eng = Engine(model, EngineLimits(max_slots=max(ns.users, 2), max_ctx=ns.prompt + ns.decode + 64, prefill_chunk=4096, max_decode_rows=16))
+    lengths = [int(v) for v in ns.prompts.split(",") if v] or [ns.prompt]
+    eng = Engine(model, EngineLimits(max_slots=max(ns.users, 2), max_ctx=max(lengths) + ns.decode + 64, prefill_chunk=4096, max_decode_rows=16))
+    for plen in lengths:
+        ns.prompt = plen
+        _measure(ns, eng, model, ep, cfg, world, rank, dev, build_s)
+    if world > 1:
+        eng.graphs.clear()
+        dist.barrier()
+        torch.cuda.synchronize()
+        dist.destroy_process_group()
+    return 0
+
+
+def _measure(ns, eng, model, ep, cfg, world, rank, dev, build_s) -> None:
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (ns.prompt,), generator=g, dtype=torch.int32) for _ in range(ns.users + 1)]
     s0 = eng.open()
@@ -105,12 +120,9 @@ def main(argv=None) -> int:
                           "decode_tok_s": round(ns.users * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 3),
                           "weights_gb_per_gpu": round(model.weight_bytes() / 1e9, 2), "build_s": round(build_s, 1),
                           "device_status": status}), flush=True)
-    if world > 1:
-        eng.graphs.clear()
-        dist.barrier()
-        torch.cuda.synchronize()
-        dist.destroy_process_group()
-    return 0
+    for s in seqs:
+        eng.release(s)
+    eng.graphs.clear()
 
 
 if __name__ == "__main__":

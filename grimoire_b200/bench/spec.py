@@ -92,9 +92,8 @@ def main(argv=None) -> int:
                           "spec_tok_s": round(world * len(spec) * 1000.0 / spec_ms, 1), "accepted_length": round(st.accept_length, 3),
                           "rounds": st.rounds, "drafted": st.drafted, "accepted": st.accepted,
                           "plain_tok_s": round(world * len(plain) * 1000.0 / plain_ms, 1), "tokens_equal_plain": spec == plain,
-                          # one row runs the CUDA-core GEMV, verify rows the tensor-core kernel: equal to rounding only
-                          # (GRIMOIRE_GEMV_W4=0 puts every width on the batch-invariant kernel and the streams are equal)
-                          "batch_invariant_kernels": not _linear.GEMV_W4,
+                          # attaching the drafter switched every height to the batch-invariant kernels (both timed runs)
+                          "batch_invariant_kernels": _linear.BATCH_INVARIANT,
                           "oracle_drafter": oracle,
                           "includes_prefill": True, "mtp_bytes": drafter.head.nbytes(), "build_s": round(build_s, 1),
                           "device_status": list(K.status_read()), "data": "synthetic"}), flush=True)

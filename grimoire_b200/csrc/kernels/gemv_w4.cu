@@ -50,6 +50,46 @@ struct GemvW4Params {
   unsigned int ar_spin;
 };
 
+// One-shot all-reduce of a tile's 16 partial sums by warp 0, without fences: every partial sum travels as one 8-byte
+// {value, epoch} store into the slot (parity, source rank, tile, row) of each peer's receive region; an aligned 8-byte
+// store lands as a whole, so the receiver polls the slot itself until its epoch word is this launch's and then holds the
+// value (the low-latency protocol of collective libraries).  The cost is one one-way NVLink latency instead of two
+// system-scope fences plus a flag.  Partials are added in rank order, so every rank holds the same bits.  A peer can be at
+// most one launch ahead (its next launch needs this rank's next push), hence the two parities.  out (fp32) += the sum.
+template <typename P>
+__device__ __forceinline__ void gemv_allreduce_tile(const P& p, float mine, int tile, int lane, float* out) {
+  const int W = p.ar_world;
+  const unsigned int e = p.ar_epochs[tile] + 1u;
+  const size_t tiles = gridDim.x, par = e & 1u;
+  bool ok = true;
+  if (lane < 16) {
+    const size_t slot = ((par * W + p.ar_rank) * tiles + tile) * 16 + lane;
+    for (int r = 0; r < W; ++r) {
+      if (r == p.ar_rank) continue;
+      uint2* dst = reinterpret_cast<uint2*>(p.ar_recv[r]) + slot;
+      asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(mine)), "r"(e) : "memory");
+    }
+    float s = 0.f;
+    const uint2* base = reinterpret_cast<const uint2*>(p.ar_recv[p.ar_rank]);
+    for (int r = 0; r < W; ++r) {
+      if (r == p.ar_rank) { s += mine; continue; }
+      const uint2* src = base + ((par * W + r) * tiles + tile) * 16 + lane;
+      uint32_t vx = 0u, vy = 0u;
+      bool got = false;
+      for (unsigned int i = 0; i < p.ar_spin; ++i) {
+        asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
+        if (vy == e) { got = true; break; }
+        if (i > 64) __nanosleep(20);
+      }
+      if (!got) { ok = false; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x20000u | (r << 12) | (tile & 0xfff)); break; }
+      s += __uint_as_float(vx);
+    }
+    if (ok) out[(size_t)tile * 16 + lane] += s;
+  }
+  __syncwarp();
+  if (lane == 0) p.ar_epochs[tile] = e;   // advance even after a timeout so later launches stay aligned
+}
+
 __device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xea;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));   // (a & mask) | orv
@@ -175,46 +215,13 @@ __global__ void __launch_bounds__(kGvWarps * 32) gemv_w4_kernel(const GemvW4Para
   if (t == 0) { red[warp][g] = f0 * kGvXInv; red[warp][g + 8] = f1 * kGvXInv; }
   __syncthreads();
   if (EPI == 4) {
-    // One-shot all-reduce by warp 0 without fences: every partial sum travels as one 8-byte {value, epoch} store into
-    // the slot (parity, source rank, tile, row) of each peer's receive region; an aligned 8-byte store lands as a
-    // whole, so the receiver polls the slot itself until its epoch word is this launch's and then holds the value
-    // (the low-latency protocol of collective libraries).  The cost is one one-way NVLink latency instead of two
-    // system-scope fences plus a flag.  Partials are added in rank order, so every rank holds the same bits.  A peer
-    // can be at most one launch ahead (its next launch needs this rank's next push), hence the two parities.
     if (warp != 0) return;
-    const int W = p.ar_world;
-    const unsigned int e = p.ar_epochs[tile] + 1u;
-    const size_t tiles = gridDim.x, par = e & 1u;
-    bool ok = true;
+    float mine = 0.f;
     if (lane < 16) {
-      float mine = 0.f;
 #pragma unroll
       for (int k = 0; k < SLICES; ++k) mine += red[k][lane];
-      const size_t slot = ((par * W + p.ar_rank) * tiles + tile) * 16 + lane;
-      for (int r = 0; r < W; ++r) {
-        if (r == p.ar_rank) continue;
-        uint2* dst = reinterpret_cast<uint2*>(p.ar_recv[r]) + slot;
-        asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(mine)), "r"(e) : "memory");
-      }
-      float s = 0.f;
-      const uint2* base = reinterpret_cast<const uint2*>(p.ar_recv[p.ar_rank]);
-      for (int r = 0; r < W; ++r) {
-        if (r == p.ar_rank) { s += mine; continue; }
-        const uint2* src = base + ((par * W + r) * tiles + tile) * 16 + lane;
-        uint32_t vx = 0u, vy = 0u;
-        bool got = false;
-        for (unsigned int i = 0; i < p.ar_spin; ++i) {
-          asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(vx), "=r"(vy) : "l"(src) : "memory");
-          if (vy == e) { got = true; break; }
-          if (i > 64) __nanosleep(20);
-        }
-        if (!got) { ok = false; grm_set_error(p.status, GRM_ERR_FLAG_TIMEOUT, 0x20000u | (r << 12) | (tile & 0xfff)); break; }
-        s += __uint_as_float(vx);
-      }
-      if (ok) reinterpret_cast<float*>(p.out)[(size_t)tile * 16 + lane] += s;
     }
-    __syncwarp();
-    if (lane == 0) p.ar_epochs[tile] = e;   // advance even after a timeout so later launches stay aligned
+    gemv_allreduce_tile(p, mine, tile, lane, reinterpret_cast<float*>(p.out));
     return;
   }
   if (tid < 16) {
@@ -250,6 +257,12 @@ struct GemvMxParams {
   const float* h;
   const float* nw;
   float eps, offset;
+  // EPI 4: fused tensor-parallel all-reduce, see gemv_allreduce_tile
+  float* ar_recv[8];
+  unsigned int* ar_epochs;
+  unsigned int* status;
+  int ar_world, ar_rank;
+  unsigned int ar_spin;
 };
 
 template <int EPI>
@@ -348,6 +361,16 @@ __global__ void __launch_bounds__(256) gemv_mx_kernel(const GemvMxParams p) {
   f1 += __shfl_xor_sync(0xffffffffu, f1, 1); f1 += __shfl_xor_sync(0xffffffffu, f1, 2);
   if (t == 0) { red[warp][g] = f0; red[warp][g + 8] = f1; }
   __syncthreads();
+  if (EPI == 4) {
+    if (warp != 0) return;
+    float mine = 0.f;
+    if (lane < 16) {
+#pragma unroll
+      for (int k = 0; k < SLICES; ++k) mine += red[k][lane];
+    }
+    gemv_allreduce_tile(p, mine, (int)blockIdx.x, lane, reinterpret_cast<float*>(p.out));
+    return;
+  }
   if (tid < 16) {
     float s = 0.f, u = 0.f;
 #pragma unroll
@@ -467,5 +490,30 @@ GRM_API int grm_gemv_mx(const void* w, const void* sz, const void* x, const void
     case 2: gemv_mx_kernel<2><<<tiles, 256, smem, st>>>(p); break;
     default: gemv_mx_kernel<3><<<tiles / 2, 256, smem, st>>>(p); break;
   }
+  GRM_LAUNCH_RET();
+}
+
+// Row-parallel MXFP4 projection of one activation row with the all-reduce over the tensor-parallel ranks in its epilogue:
+// h (fp32 [N], replicated) += sum over ranks of x_rank . W_rank^T -- the MXFP4 counterpart of grm_gemv_w4_allreduce (same
+// receive region layout and epoch counters, which the two kernels may share: launches are ordered on the stream).
+GRM_API int grm_gemv_mx_allreduce(const void* w, const void* sz, const void* x, void* h, int N, int K, const void* const* recv,
+                                  long recv_off, void* epochs, int world, int rank, unsigned int spin, void* stream) {
+  if ((N % 32) || (K % 64) || K > 20480 || ((uintptr_t)x & 15)) return -2;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || !recv || !epochs || (recv_off & 1)) return -2;
+  GemvMxParams p;
+  p.w = (const uint4*)w; p.sz = (const uint8_t*)sz; p.x = (const bf16*)x; p.out = h; p.N = N; p.K = K;
+  p.h = nullptr; p.nw = nullptr; p.eps = 0.f; p.offset = 0.f;
+  for (int i = 0; i < 8; ++i) p.ar_recv[i] = i < world ? (float*)const_cast<void*>(recv[i]) + recv_off : nullptr;
+  p.ar_epochs = (unsigned int*)epochs; p.status = grm_status_ptr(); p.ar_world = world; p.ar_rank = rank;
+  p.ar_spin = spin ? spin : 2000000u;
+  const int tiles = N / 16;
+  const size_t smem = (size_t)K * 2;
+  // CTAs of different ranks wait for one another's pushes: the whole grid must be resident at once
+  int per_sm = 0, dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_mx_kernel<4>, 256, smem) != cudaSuccess || (long)per_sm * sms < (long)tiles)
+    return -2;
+  gemv_mx_kernel<4><<<tiles, 256, smem, (cudaStream_t)stream>>>(p);
   GRM_LAUNCH_RET();
 }

@@ -201,6 +201,16 @@ class Engine:
     # ------------------------------------------------------------------------------------------
     # batched decode / verify rows
     # ------------------------------------------------------------------------------------------
+    def enable_speculation(self) -> None:
+        """Speculative decoding is about to run on this engine: put every batch height on the batch-invariant projection
+        kernels (ops/linear.py: set_batch_invariant), so that a token verified inside a block is the token plain greedy
+        decoding would have produced, and drop decode graphs captured in the other mode."""
+        from ..ops import linear as _lin
+
+        if not _lin.BATCH_INVARIANT:
+            _lin.set_batch_invariant(True)
+            self.graphs.clear()
+
     def _stage_rows(self, tokens, slots, positions) -> int:
         M = len(tokens)
         st = self.h_stage
@@ -266,11 +276,30 @@ class Engine:
         for s, p in zip(seqs, positions):
             self.kv.ensure(s, p + 1)
             max_len = max(max_len, p + 1)
+        if (runs is None and M > 1 and len({s.slot for s in seqs}) == 1 and max_len < K.VERIFY_ATTN_MIN_CTX
+                and len({self._splits_for(1, p + 1) for p in positions}) > 1):
+            # one conversation's verify block whose rows sit on both sides of a length at which the single-row split factor changes (once
+            # per doubling of the context): score the rows one launch each, which is what plain decoding would do
+            outs, lgs = [], []
+            for t, s, p in zip(tokens, seqs, positions):
+                r = self.decode_rows([t], [s], [p], use_graph=use_graph, return_logits=return_logits)
+                if return_logits:
+                    outs.append(r[0][0])
+                    lgs.append(r[1][0].clone())
+                else:
+                    outs.append(r[0])
+            return (outs, torch.stack(lgs)) if return_logits else outs
         self._stage_rows(tokens, [s.slot for s in seqs], positions)
         splits = self._splits_for(M, max_len)
         distinct = len({s.slot for s in seqs}) == M      # no verify block: the attention kernel may append K / V itself
         shape = ()
-        if not distinct and self.device.type == "cuda" and isinstance(self.model, DenseModel):
+        if not distinct and max_len < K.VERIFY_ATTN_MIN_CTX:
+            # Short contexts: every row of a verify block is scored exactly as a single-row step at its position would be
+            # (the per-row kernel with the single-row split factor, whose page partition depends on the row's own length
+            # only), so that speculative output reproduces plain greedy output bit for bit; the one-pass kernel is no
+            # faster below this length anyway.
+            splits = self._splits_for(1, max_len)
+        elif not distinct and self.device.type == "cuda" and isinstance(self.model, DenseModel):
             # verify blocks: groups of consecutive rows of one conversation share one pass over its cache
             per = K.verify_rows_per_group(self.model.geom)
             if per >= 1:

@@ -153,6 +153,8 @@ def generate_tokens(engine: EngineLike, prompt: Sequence[int], opts: GenerationO
     """Run one request to completion.  ``on_token(tok)`` returning False cancels at that token
     (client disconnect / stop signal).  Returns (tokens, finish_reason)."""
     own = seq is None
+    if opts.draft_depth > 0 and opts.drafter is not None and hasattr(engine, "enable_speculation"):
+        engine.enable_speculation()            # verify blocks and single rows on the same arithmetic from here on
     if own:
         seq = engine.open()
     out: list[int] = []

@@ -371,6 +371,10 @@ class DenseModel:
         return self._head(sel, buf, n, rb)
 
     def _mega_ready(self) -> bool:
+        from ..ops import linear as _lin
+
+        if _lin.BATCH_INVARIANT:
+            return False                # every height on the batch-invariant kernels (speculative decoding is on)
         ok = getattr(self, "_mega_ok", None)
         if ok is None:
             from ..ops import mega

@@ -194,6 +194,7 @@ class MtpDrafter:
         self._ids = torch.zeros(16, dtype=torch.int32, device=dev)
         self._drafts = torch.zeros(16, dtype=torch.int32, device=dev)
         engine.mtp = self
+        engine.enable_speculation()
 
     # ---- prefill: fill the head's KV from the target's hidden states of the chunk ----
     def warm_chunk(self, seq, tokens_dev: torch.Tensor, done: int, m: int, pos0: int, buf, last: bool) -> None:

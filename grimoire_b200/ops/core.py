@@ -280,6 +280,10 @@ def paged_decode_attn_fused(qkv: torch.Tensor, inv_freq: torch.Tensor, q_norm_w,
 
 
 VERIFY_ATTN = os.environ.get("GRIMOIRE_VERIFY_ATTN", "1") != "0"     # verify blocks: (row, head) pairs in the MMA rows
+# context length from which verify blocks take the one-pass kernel (measured, 4 rows of the 40 / 8 head split, one pass
+# against row by row: 4,096 tokens 23.3 / 17.9 us, 8,192 23.8 / 25.5, 32,768 49.2 / 65.6, 65,536 84.0 / 122.5); below it the
+# rows are scored one by one with exactly the arithmetic of single-row steps
+VERIFY_ATTN_MIN_CTX = int(os.environ.get("GRIMOIRE_VERIFY_ATTN_MIN_CTX", "8192"))
 
 
 def verify_rows_per_group(geom: AttnGeom) -> int:

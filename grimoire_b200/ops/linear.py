@@ -44,6 +44,24 @@ GEMV_W4 = os.environ.get("GRIMOIRE_GEMV_W4", "1") != "0"   # single-row int4 pro
 
 
 FUSED_NORM = os.environ.get("GRIMOIRE_FUSED_NORM", "1") != "0"   # RMSNorm inside the single-row GEMV prologue
+# Batch-invariant mode: every batch height (1 row as well as verify blocks and user batches) runs the tensor-core small-M
+# kernels, whose per-row arithmetic does not depend on the height, so a row scored alone and the same row scored inside a
+# verify block give the same bits -- the contract speculative decoding needs to reproduce plain greedy decoding exactly
+# (tools/test_spec_e2e.cpp in the reference).  Switched on by whatever enables speculation (a draft head, copy drafts in
+# the scheduler); costs ~20 us of projections per layer on single-row steps, which are rare once drafts are accepted.
+BATCH_INVARIANT = False
+_GEMV_W4_DEFAULT = GEMV_W4
+
+
+def set_batch_invariant(on: bool) -> bool:
+    """Returns the previous state.  Decode graphs captured in the other mode must be dropped by the caller."""
+    global BATCH_INVARIANT, GEMV_W4
+    prev = BATCH_INVARIANT
+    BATCH_INVARIANT = bool(on)
+    GEMV_W4 = False if on else _GEMV_W4_DEFAULT
+    return prev
+
+
 # single-row int4 g128 projections as a tensor-core weight stream (gemv_w4_tc.cu; needs a second copy of the weight in the
 # row-block layout): 0 off, 1 on
 W4_TC = os.environ.get("GRIMOIRE_W4_TC", "0") != "0"
@@ -157,7 +175,7 @@ class W4Linear:
             return self._forward_ref(x, out, epi)
         t = self.tiled
         lib = _native.cuda()
-        if M == 1 and getattr(self, "rb", None) is not None and self._tc_row(x, None, None, out, epi, 0.0, 0.0):
+        if M == 1 and not BATCH_INVARIANT and getattr(self, "rb", None) is not None and self._tc_row(x, None, None, out, epi, 0.0, 0.0):
             return out
         if M == 1 and GEMV_W4 and t.K <= 20480:
             # one row: CUDA-core weight stream (gemv_w4.cu); the tensor-core kernel below serves 2..64 rows
@@ -212,7 +230,7 @@ class W4Linear:
         """``out = epi(RMSNorm(h) @ W^T)`` for one fp32 residual row with the norm inside the GEMV prologue (one launch
         instead of two).  Returns False when the shape or device is not served; the caller then runs norm + forward."""
         t = self.tiled
-        if (getattr(self, "rb", None) is not None and FUSED_NORM and h.shape[0] == 1 and h.dtype == torch.float32 and h.shape[1] == self.K
+        if (not BATCH_INVARIANT and getattr(self, "rb", None) is not None and FUSED_NORM and h.shape[0] == 1 and h.dtype == torch.float32 and h.shape[1] == self.K
                 and self._tc_row(None, h, norm_w, out, epi, eps, offset)):
             return True
         if (not GEMV_W4 or not FUSED_NORM or self.device.type != "cuda" or t is None or h.shape[0] != 1 or t.K > 20480

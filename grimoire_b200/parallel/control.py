@@ -105,6 +105,9 @@ class ControlledEngine:
         self.ch.send(ROLLBACK, seq.slot, length)
         self.engine.rollback(seq, length)
 
+    def enable_speculation(self) -> None:
+        self.engine.enable_speculation()         # every rank switched at start-up (parallel/launch.py); local no-op then
+
     def sample_rows(self, logits, opts, positions):
         return self.engine.sample_rows(logits, opts, positions)      # every rank holds the same logits: the front end draws
 

@@ -47,6 +47,8 @@ def main(argv=None) -> int:
         from .cp import ContextParallel
 
         ContextParallel(lay.cp_group, lay.device).attach(g.model, max_rows=ec.prefill_chunk)
+    if (ec.copy_drafts or g.drafter is not None) and getattr(g.model, "supports_verify_rows", True):
+        g.engine.enable_speculation()            # on every rank: verify blocks and single rows on the same kernels
     ch = ControlChannel(lay.control_group)
     if not lay.is_front_end:
         served = worker_loop(g.engine, ch)

@@ -191,6 +191,17 @@ class TensorParallel:
                 _native.check(code, f"gemv_w4_allreduce {lin.name}")
                 self.stats["fused_allreduce"] += 1
                 return
+        if (self.fused and M == 1 and L.GEMV_W4 and isinstance(lin, L.MXLinear) and getattr(lin, "tw", None) is not None and lin.K <= 20480
+                and not lin.swiglu):
+            # MXFP4, one row: the same one-shot all-reduce in the MXFP4 GEMV's epilogue (region and epochs shared with int4)
+            code = _native.cuda().grm_gemv_mx_allreduce(
+                _native.ptr(lin.tw), _native.ptr(lin.tsz), _native.ptr(x), _native.ptr(h), ctypes.c_int(lin.N), ctypes.c_int(lin.K),
+                self.recv.ptr_array(), ctypes.c_long(self.gemv_off), _native.ptr(self.epochs), ctypes.c_int(self.world),
+                ctypes.c_int(self.rank), ctypes.c_uint(self.spin), _native.stream_ptr())
+            if code != -2:
+                _native.check(code, f"gemv_mx_allreduce {lin.name}")
+                self.stats["fused_allreduce"] += 1
+                return
         if self.fused and M <= SMALLM_MAX and isinstance(lin, W4Linear) and lin.tiled is not None:
             t = lin.tiled
             code = _native.cuda().grm_smallm_w4_allreduce(

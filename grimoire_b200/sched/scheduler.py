@@ -74,6 +74,8 @@ class Scheduler:
         self.clock = clock
         # any object with the Drafter protocol (engine/generation.py): the MTP head's drafter, or prompt-lookup copy drafts
         self.drafter = drafter if drafter is not None else (CopyDrafter() if copy_drafts else None)
+        if self.drafter is not None and any(d > 0 for d in depths) and hasattr(engine, "enable_speculation"):
+            engine.enable_speculation()
         self.jobs: dict[int, SchedJob] = {}
         self._ids = itertools.count(1)
         self._lock = threading.Lock()

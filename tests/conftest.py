@@ -23,3 +23,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _reset_batch_invariant_mode():
+    """Speculative-decoding tests switch the projection kernels to their batch-invariant mode process-wide; later tests
+    start from the default again."""
+    yield
+    try:
+        from grimoire_b200.ops import linear
+
+        linear.set_batch_invariant(False)
+    except Exception:
+        pass

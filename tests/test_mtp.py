@@ -17,7 +17,9 @@ def _run(device, quant="int4", draft_vocab=0, K=3, n_new=24):
     cfg = dataclasses.replace(tiny_dense(), quant=quant, tie_word_embeddings=False)
     lim = EngineLimits(max_slots=2, max_ctx=160, prefill_chunk=16, max_decode_rows=8, extra_kv_layers=1)
     prompt = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(3)).tolist()
-    plain = Engine(DenseModel.random(cfg, device, seed=1, gen_device="cpu"), lim).generate(prompt, n_new, use_graph=False)
+    e0 = Engine(DenseModel.random(cfg, device, seed=1, gen_device="cpu"), lim)
+    e0.enable_speculation()           # what attaching a drafter does: plain and speculative steps on the same kernels
+    plain = e0.generate(prompt, n_new, use_graph=False)
     model = DenseModel.random(cfg, device, seed=1, gen_device="cpu")
     eng = Engine(model, lim)
     drafter = MtpDrafter(eng, MtpHead.random_from_target(model, seed=1, noise=0.01, draft_vocab=draft_vocab, gen_device="cpu"))
@@ -41,14 +43,13 @@ def test_mtp_draft_vocab_head_cpu():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("quant", ["int4", "mxfp4"])
-def test_mtp_speculation_reproduces_greedy_gpu(quant, monkeypatch):
-    """Exact reproduction needs the same kernel for one row and for verify rows (GRIMOIRE_GEMV_W4=0: every width on the
-    batch-invariant tensor-core kernel); with the single-row GEMV the two agree to rounding, which a random tiny model
-    with near-tied logits does not survive token for token."""
+def test_mtp_speculation_reproduces_greedy_gpu(quant):
+    """Exact reproduction needs the same kernel for one row and for verify rows: attaching a drafter puts the engine in
+    its batch-invariant mode (every height on the tensor-core small-M kernels), with no environment override."""
     from grimoire_b200.ops import core as K
     from grimoire_b200.ops import linear
-    monkeypatch.setattr(linear, "GEMV_W4", False)
     plain, toks, stats, drafter = _run("cuda", quant=quant)
+    assert linear.BATCH_INVARIANT and not linear.GEMV_W4
     assert toks == plain
     assert stats.rounds > 0 and drafter.stats["warm_rows"] == 36
     assert K.status_read()[0] == 0

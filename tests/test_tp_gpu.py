@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, q, fused, split=False, mega=False):
+def _worker(rank, world, port, q, fused, split=False, mega=False, quant="int4"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     if mega:
@@ -35,7 +35,9 @@ def _worker(rank, world, port, q, fused, split=False, mega=False):
         from grimoire_b200.ops.core import status_read
         from grimoire_b200.parallel.tp import TensorParallel
 
-        cfg = small_dense(layers=3, wide=world > 2)
+        import dataclasses
+
+        cfg = dataclasses.replace(small_dense(layers=3, wide=world > 2), quant=quant)
         sd = random_state_dict(cfg, seed=0)
         model = DenseModel.from_state_dict(cfg, sd, dev, tp_rank=rank, tp_world=world)
         tp = TensorParallel(dist.group.WORLD, dev, fused=fused)
@@ -46,8 +48,20 @@ def _worker(rank, world, port, q, fused, split=False, mega=False):
         g = torch.Generator().manual_seed(1)
         prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
         out = eng.generate(prompt, 16, use_graph=True)
+        # library all-reduces issued by decode steps alone (the fused epilogues should leave none)
+        s2 = eng.open()
+        lg = eng.prefill(s2, prompt[:20])
+        n0 = tp.stats["nccl_allreduce"]
+        tok = int(lg.argmax())
+        for _ in range(3):
+            pos = s2.length
+            nxt = eng.decode_rows([tok], [s2], [pos], use_graph=False)[0]
+            eng.commit_rows([s2], [tok], [pos])
+            tok = nxt
+        stats = dict(tp.stats)
+        stats["decode_nccl"] = tp.stats["nccl_allreduce"] - n0
         torch.cuda.synchronize()
-        q.put((rank, out, dict(tp.stats), status_read()))
+        q.put((rank, out, stats, status_read()))
         eng.graphs.clear()
         del eng, model
         dist.barrier()
@@ -56,10 +70,11 @@ def _worker(rank, world, port, q, fused, split=False, mega=False):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused,split,mega,world", [(True, False, False, 2), (False, False, False, 2), (True, True, False, 2),
-                                                    (False, True, False, 2), (True, True, True, 2), (True, True, False, 4),
-                                                    (True, True, False, 8)])
-def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world):
+@pytest.mark.parametrize("fused,split,mega,world,quant", [(True, False, False, 2, "int4"), (False, False, False, 2, "int4"),
+                                                          (True, True, False, 2, "int4"), (False, True, False, 2, "int4"),
+                                                          (True, True, True, 2, "int4"), (True, True, False, 2, "mxfp4"),
+                                                          (True, True, False, 4, "int4"), (True, True, False, 8, "int4")])
+def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world, quant):
     """fused: one-shot all-reduce in the projection kernels (False = the NCCL composition); split: vocabulary-split lm_head
     with the (value, index) candidate exchange; mega: the persistent phase kernel with its in-kernel all-reduce."""
     if torch.cuda.device_count() < world:
@@ -69,7 +84,9 @@ def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world):
     from grimoire_b200.models.dense import DenseModel
     from grimoire_b200.models.synthetic import random_state_dict
 
-    cfg = small_dense(layers=3, wide=world > 2)
+    import dataclasses
+
+    cfg = dataclasses.replace(small_dense(layers=3, wide=world > 2), quant=quant)
     sd = random_state_dict(cfg, seed=0)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
@@ -78,7 +95,7 @@ def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, fused, split, mega)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, fused, split, mega, quant)) for r in range(world)]
     for p in procs:
         p.start()
     try:
@@ -100,5 +117,7 @@ def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world):
         assert status[0] == 0
         if fused and not mega:
             assert stats["fused_allreduce"] > 0
+        if fused:
+            assert stats["decode_nccl"] == 0             # single-row steps all-reduce inside the projection kernels
         if split:
             assert stats["head_pick"] >= 1          # counted per recorded launch: graph replays do not pass through Python
