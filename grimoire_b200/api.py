@@ -153,7 +153,8 @@ class Grimoire:
                 if why:
                     raise UnsupportedModel(why)
                 if is_hybrid(cfg):
-                    model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
+                    model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
+                                                        expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""))
                 else:
                     model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
                                                        proj=ec.proj, pp_rank=ec.pp_rank, pp_world=ec.pp_world)

@@ -118,6 +118,7 @@ class HybridModel:
         self.tp_rank, self.tp_world, self.pp_rank, self.pp_world = 0, 1, 0, 1
         self.tp = self.pp = None
         self.ep = None                   # parallel.ep.ExpertParallel when the experts are sharded over ranks
+        self.expert_perm = None          # per layer: physical -> logical expert (set_expert_placement), None = identity
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = True       # verify blocks: rows run as one recurrent run, rejected rows are undone by replay
@@ -293,6 +294,21 @@ class HybridModel:
     # ------------------------------------------------------------------------------------------
     # checkpoints
     # ------------------------------------------------------------------------------------------
+    def set_expert_placement(self, heat_file: str) -> bool:
+        """Balanced expert ownership from a routing-heat file (models/expert_placement.py: the hit counts a serving run
+        saved): per layer the hottest experts are dealt onto the least-loaded rank, so that the ranks of an expert-parallel
+        group see even traffic instead of whatever the checkpoint's expert order gives.  Must be called before the layers
+        are added; every rank must use the same file.  Returns False (identity placement) when the file does not match
+        the model.  Reference: the heat / hit-file manager of the tiered-MoE path (src/moe_tier.cpp)."""
+        from .expert_placement import ExpertHeat, balanced_placement
+
+        cfg = self.cfg
+        heat = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts)
+        if self.layers or not heat.load(heat_file):
+            return False
+        self.expert_perm = [balanced_placement(heat.h[l], self.ep_world) for l in range(cfg.num_hidden_layers)]
+        return True
+
     def _add_layer(self, i: int, w: dict) -> None:
         """One layer from logical fp32 tensors (``[out][in]``; stored block-fp8 QuantWeights are used as they are).
         Keys: in_norm, post_norm, router [E][H], shared_gate [1][H], gate_up [E][2I][H], down [E][H][I], shared_gate_proj,
@@ -303,6 +319,15 @@ class HybridModel:
         e0, e1 = self.ep_rank * (E // self.ep_world), (self.ep_rank + 1) * (E // self.ep_world)
         f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
         dense = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
+        perm = self.expert_perm[i] if self.expert_perm is not None else None
+        if perm is not None:
+            # Placement: physical expert j of this layer is logical expert perm[j].  The experts' weights and the router's
+            # rows are permuted together, so routing yields physical ids and nothing downstream changes; rank r owns
+            # physical experts [r E / W, (r + 1) E / W), i.e. the logical set the placement gave it.
+            idx = torch.as_tensor(perm, dtype=torch.long)
+            w = dict(w)
+            w["gate_up"], w["down"] = w["gate_up"][idx], w["down"][idx]
+            w["router"] = dense(w["router"])[idx]
         fp8 = lambda t, name: Hb.FP8BlockLinear(t, dev, name)
 
         def experts(t3):
@@ -332,7 +357,8 @@ class HybridModel:
         self.layers.append(L)
 
     @staticmethod
-    def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1) -> "HybridModel":
+    def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1, expert_heat: str = "",
+                        expert_perm=None) -> "HybridModel":
         """Load a HF directory of the hybrid family.  Tensor names follow the reference's resolver
         (src/qwen35_loader.cpp:1149-1169 ``linear_attn.{in_proj_qkv,in_proj_z,in_proj_a,in_proj_b,conv1d,A_log,dt_bias,norm,
         out_proj}``, :1320-1380 ``mlp.gate``, ``mlp.shared_expert*``, per-expert ``mlp.experts.N.*`` or the fused
@@ -346,6 +372,10 @@ class HybridModel:
             raise ValueError("from_checkpoint: not a hybrid MoE configuration or experts do not split over the ranks")
         m = HybridModel(cfg, device, max_slots=max_slots)
         m.ep_rank, m.ep_world = ep_rank, ep_world
+        if expert_perm is not None:
+            m.expert_perm = [list(p) for p in expert_perm]       # explicit placement (per layer: physical -> logical expert)
+        elif expert_heat:
+            m.set_expert_placement(expert_heat)
         E = cfg.num_experts
 
         def need(v, name):

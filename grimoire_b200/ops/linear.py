@@ -338,6 +338,21 @@ class RowQLinear:
         _native.check(code, f"dequant_rowq {self.name}")
         return wb
 
+    def bf16_weights(self, resident_only: bool = False):
+        """The bf16 [N][K] form for the tcgen05 GEMM: the resident copy (made on first use while device memory allows, see
+        ``_bf16_cache_admit``), else an expansion into the shared scratch (None with ``resident_only``)."""
+        cached = getattr(self, "_bf16", None)
+        if cached is not None:
+            return cached
+        if self.kind == 0:
+            return None if resident_only else self.dequant_into_scratch()
+        if not getattr(self, "_bf16_refused", False) and _bf16_cache_admit(self.N * self.K * 2, self.device):
+            self._bf16 = self.dequant_into_scratch().clone()
+            return self._bf16
+        if not torch.cuda.is_current_stream_capturing():
+            self._bf16_refused = True            # (a refusal during graph capture is only "not now")
+        return None if resident_only else self.dequant_into_scratch()
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
         M = x.shape[0]
         if self.swiglu and epi != "swiglu":
@@ -345,7 +360,12 @@ class RowQLinear:
         if self.device.type != "cuda":
             return W4Linear._forward_ref(self, x, out, epi)
         if M > SMALLM_MAX:
-            return gemm_bf16(x, self.dequant_into_scratch(), out, epi)
+            return gemm_bf16(x, self.bf16_weights(), out, epi)
+        if M >= 4 and self.kind != 0 and not BATCH_INVARIANT and self.bf16_weights(resident_only=True) is not None:
+            # 4..64 rows: the row kernel's cost grows with the rows (int8, 27B gate|up: 28-41 us at one row, 184-193 us at
+            # eight) and it makes one weight pass per 8 rows; with a resident bf16 copy one pass of the tcgen05 GEMM over 2
+            # bytes per weight is cheaper
+            return gemm_bf16(x, self.bf16_weights(resident_only=True), out, epi)
         lib = _native.cuda()
         for m0 in range(0, M, 8):
             m = min(8, M - m0)
@@ -413,7 +433,8 @@ def w4_dequant_into(lin: "W4Linear") -> torch.Tensor:
     if keep:
         wbuf = torch.empty(t.N, t.K, dtype=torch.bfloat16, device=lin.device)
     else:
-        lin._bf16_refused = True
+        if not torch.cuda.is_current_stream_capturing():
+            lin._bf16_refused = True             # (a refusal during graph capture is only "not now")
         wbuf = lin.ws.get("dequant_bf16", t.N * t.K, torch.bfloat16).view(-1)[: t.N * t.K].view(t.N, t.K)
     code = _native.cuda().grm_dequant_w4(_native.ptr(t.w), _native.ptr(t.sz), _native.ptr(wbuf), _c(t.N), _c(t.K), _c(t.group),
                                          _c(t.K), _native.stream_ptr())

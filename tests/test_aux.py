@@ -125,3 +125,19 @@ def test_dflash_config_attention_shape_rules():
     assert "only 2 entries" in resolve_dflash_config(json.dumps(dict(base, layer_types=lt[:2]))).error
     assert resolve_dflash_config("{nope").error and resolve_dflash_config("[1]").error
     assert resolve_dflash_config(json.dumps({"hidden_size": 8})).error
+
+
+def test_verify_groups_and_split_heuristic():
+    """Host-side planning of a decode step's attention: verify blocks are cut into groups of at most 16 // G rows of one
+    conversation at consecutive positions; the split-KV factor follows the measured table."""
+    from grimoire_b200.ops import core as K
+
+    slots = [3, 3, 3, 3, 3, 1, 2, 2, 2]
+    pos = [10, 11, 12, 13, 14, 99, 7, 8, 20]
+    assert K.verify_groups(slots, pos, 3) == [(3, 0, 3, 10), (3, 3, 2, 13), (1, 5, 1, 99), (2, 6, 2, 7), (2, 8, 1, 20)]
+    assert K.verify_groups(slots, pos, 16)[0] == (3, 0, 5, 10)
+    assert K.verify_rows_per_group(K.AttnGeom(40, 8, 128, 128, 0.1)) == 3
+    assert K.verify_rows_per_group(K.AttnGeom(32, 8, 128, 128, 0.1)) == 4
+    # one row, 8 kv heads: 16 splits up to 8,192 tokens (cluster merge), 32 from 16,384; never fewer than 8 pages a split
+    assert [K.decode_splits(n, 1, 8) for n in (100, 512, 1024, 4096, 8192, 16384, 32768, 131072)] == [1, 4, 8, 16, 16, 32, 32, 32]
+    assert K.decode_splits(4096, 8, 8) == 4 and K.decode_splits(4096, 1, 1) == 16

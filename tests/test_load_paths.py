@@ -143,3 +143,47 @@ def test_artifact_round_trip_serves_same_logits(tmp_path):
     c.close()
     assert torch.allclose(la, lb, atol=1e-4), float((la - lb).abs().max())
     assert torch.allclose(lb, lc, atol=1e-6)
+
+
+def test_expert_placement_from_heat_file_keeps_logits_and_balances_ranks(hybrid_dirs, tmp_path, monkeypatch):
+    """A routing-heat file (models/expert_placement.py) permutes expert ownership at load: the experts' weights and the
+    router rows move together, so the logits do not change, and the hot experts spread over the expert-parallel ranks."""
+    from grimoire_b200.models.expert_placement import ExpertHeat, rank_loads
+
+    cfg, _, split_dir, _ = hybrid_dirs
+    ids = _prompt(21, 9)
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    base = g.score_ids(ids)
+    g.close()
+    heat = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts)
+    gen = torch.Generator().manual_seed(2)
+    for l in range(cfg.num_hidden_layers):
+        # skewed traffic: the first quarter of the experts takes most of it
+        hot = torch.randint(0, cfg.num_experts // 4, (400,), generator=gen).tolist()
+        cold = torch.randint(0, cfg.num_experts, (100,), generator=gen).tolist()
+        heat.credit(l, hot + cold)
+    path = str(tmp_path / "hits.json")
+    heat.save(path)
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HEAT", path)
+    g = Grimoire.load(_ec(split_dir), device="cpu")            # one rank: the file is read, the placement is the identity
+    assert g.model.expert_perm is not None and g.model.expert_perm[0] == list(range(cfg.num_experts))
+    g.close()
+    # any placement leaves the logits alone (bit for bit: the experts' weights and the router rows move together)
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+
+    def last_logits(perms):
+        m = HybridModel.from_checkpoint(split_dir, "cpu", max_slots=2, expert_perm=perms)
+        eng = Engine(m, EngineLimits(max_slots=2, max_ctx=64, prefill_chunk=32, max_decode_rows=4))
+        return eng.prefill(eng.open(), ids).float()
+
+    perms = [torch.randperm(cfg.num_experts, generator=gen).tolist() for _ in range(cfg.num_hidden_layers)]
+    assert torch.equal(last_logits(perms), last_logits(None))
+    # the same file, two ranks: each rank's share of the recorded traffic is close to half (identity order: ~0.85 / 0.15)
+    m = HybridModel(cfg, "cpu", max_slots=2)
+    m.ep_rank, m.ep_world = 0, 2
+    assert m.set_expert_placement(path)
+    h2 = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts)
+    assert h2.load(path)
+    loads = rank_loads(h2.h[0], m.expert_perm[0], 2)
+    ident = rank_loads(h2.h[0], list(range(cfg.num_experts)), 2)
+    assert max(loads) / sum(loads) < 0.56 < max(ident) / sum(ident)

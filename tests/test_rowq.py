@@ -43,7 +43,8 @@ def test_rowq_gpu_matches_dequant(fmt, M, N, K):
     lin = RowQLinear(qw, "cuda")
     x = torch.randn(M, K, generator=g).bfloat16()
     ref = _ref(x, qw, False)
-    tol = (0.03 if M > 64 else 2e-3) * max(1.0, float(ref.abs().max()))
+    # from 4 rows the byte-per-weight formats may run the tcgen05 GEMM over a resident bf16 expansion of the weight
+    tol = (0.03 if M >= 4 else 2e-3) * max(1.0, float(ref.abs().max()))
     out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
     lin(x.cuda(), out, "f32")
     assert float((out.cpu() - ref).abs().max()) < tol

@@ -43,7 +43,8 @@ def _worker(rank, world, port, q, fused, split=False, mega=False, quant="int4"):
         tp = TensorParallel(dist.group.WORLD, dev, fused=fused)
         tp.attach(model, max_rows=256)
         if split:
-            assert tp.split_head(model)
+            did = tp.split_head(model)
+            assert did or quant != "int4"           # projection types without row slicing keep the head replicated
         eng = Engine(model, EngineLimits(max_slots=2, max_ctx=512, prefill_chunk=128, max_decode_rows=16))
         g = torch.Generator().manual_seed(1)
         prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
@@ -119,5 +120,5 @@ def test_tp_gpu_tokens_equal_single_gpu(fused, split, mega, world, quant):
             assert stats["fused_allreduce"] > 0
         if fused:
             assert stats["decode_nccl"] == 0             # single-row steps all-reduce inside the projection kernels
-        if split:
+        if split and quant == "int4":
             assert stats["head_pick"] >= 1          # counted per recorded launch: graph replays do not pass through Python
