@@ -123,8 +123,9 @@ class Grimoire:
                     raise UnsupportedModel(why)
                 model, mtp_src = load_artifact_model(art, cfg, dev, ec)
             elif ec.model.endswith(".gguf"):
-                # GGUF: config and tokenizer from the metadata, tensors dequantised block by block and re-quantised
-                # to the serving format (the reference's native GGUF path keeps the file's blocks; this one does not)
+                # GGUF: config and tokenizer from the metadata.  --proj native on one rank keeps the file's blocks and runs
+                # the projections over the raw bytes (when every projection's block type is served); otherwise tensors
+                # are dequantised block by block and re-quantised to the serving format
                 import dataclasses
                 import json as _json
                 import tempfile
@@ -137,8 +138,11 @@ class Grimoire:
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world, pp_rank=ec.pp_rank,
-                                                   pp_world=ec.pp_world)
+                if ec.proj == "native" and ec.tp_world == 1 and ec.pp_world == 1 and G.native_ok(gf, cfg):
+                    model = DenseModel.from_gguf_native(cfg, gf, dev)
+                else:
+                    model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world, pp_rank=ec.pp_rank,
+                                                       pp_world=ec.pp_world)
                 tj = G.tokenizer_json_from_gguf(gf)
                 if tj is not None:
                     tdir = tempfile.mkdtemp(prefix="grimoire_tok_")

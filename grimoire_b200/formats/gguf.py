@@ -81,6 +81,18 @@ class GGUFFile:
             n *= d
         return dequantize(typ, self.raw(name), n).reshape(tuple(reversed(dims)))
 
+    def raw_rows(self, name: str) -> tuple[torch.Tensor, int]:
+        """A 2-D tensor as its stored blocks: (uint8 [rows][bytes per row], ggml type id).  ggml keeps the input dimension
+        innermost, so a weight's output rows are contiguous runs of whole blocks."""
+        i, typ, dims, nb = self.tensors[name]
+        if len(dims) != 2:
+            raise ValueError(f"{name}: not a matrix")
+        rows = dims[1]
+        if nb % rows:
+            raise ValueError(f"{name}: {nb} bytes do not split into {rows} rows")
+        buf = torch.frombuffer(bytearray(self.raw(name)), dtype=torch.uint8)
+        return buf.reshape(rows, nb // rows), typ
+
     @property
     def arch(self) -> str:
         return self.metadata.get("general.architecture", "")
@@ -146,3 +158,16 @@ def tokenizer_json_from_gguf(g: GGUFFile) -> Optional[dict]:
     added = [{"id": i, "content": t, "special": True} for i, (t, ty) in enumerate(zip(toks, types)) if ty in (3, 4)]
     return {"added_tokens": added, "normalizer": {"type": "NFC"},
             "model": {"type": "BPE", "vocab": {t: i for i, t in enumerate(toks)}, "merges": merges}}
+
+
+NATIVE_TYPES = (2, 8, 12, 13, 14)       # block types the raw-block kernels serve (csrc/kernels/gemv_gguf.cu)
+
+
+def native_ok(g: GGUFFile, cfg) -> bool:
+    """Every projection of every layer is stored in a block type the raw-block kernels serve."""
+    for i in range(cfg.num_hidden_layers):
+        for stem in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"):
+            t = g.tensors.get(f"blk.{i}.{stem}.weight")
+            if t is None or t[1] not in NATIVE_TYPES:
+                return False
+    return True

@@ -227,6 +227,37 @@ class DenseModel:
             self._linear(self._quant(wd_s), f"L{i}.down"),
             f32(q_norm), f32(k_norm)))
 
+    @staticmethod
+    def from_gguf_native(cfg: ModelConfig, gf, device, workspace: Optional[Workspace] = None) -> "DenseModel":
+        """A dense decoder whose projections stay the raw ggml blocks of its GGUF file (``--proj native``): q|k|v, o, gate|up
+        and down become ``GgufLinear``s over the stored bytes (formats/gguf.py: raw_rows), norms and the embedding table are
+        decoded, the lm_head stays raw when its block type is served.  Single rank.  Reference: the native GGUF path of the
+        loader (src/native_model.cpp) + gemv_native_qk (src/gemv_decode.cpp:1216)."""
+        from ..formats import gguf as G
+        from ..ops.linear import GgufLinear
+
+        m = DenseModel(cfg, device, 0, 1, workspace)
+        H = cfg.hidden_size
+        f32 = lambda name: gf.tensor(name).to(device=m.device, dtype=torch.float32).contiguous() if name in gf.tensors else None
+        for i in range(cfg.num_hidden_layers):
+            p = f"blk.{i}."
+            rr = lambda stem: gf.raw_rows(p + stem + ".weight")
+            qkv = GgufLinear([rr("attn_q"), rr("attn_k"), rr("attn_v")], H, m.device, f"L{i}.qkv", workspace=m.ws)
+            o = GgufLinear([rr("attn_output")], cfg.num_attention_heads * cfg.head_dim, m.device, f"L{i}.o", workspace=m.ws)
+            gu = GgufLinear([rr("ffn_gate"), rr("ffn_up")], H, m.device, f"L{i}.gate_up", swiglu=True, workspace=m.ws)
+            dn = GgufLinear([rr("ffn_down")], cfg.intermediate_size, m.device, f"L{i}.down", workspace=m.ws)
+            m.layers.append(DenseLayer(f32(p + "attn_norm.weight"), f32(p + "ffn_norm.weight"), qkv, o, gu, dn,
+                                       f32(p + "attn_q_norm.weight"), f32(p + "attn_k_norm.weight")))
+        m.embed = gf.tensor("token_embd.weight").to(device=m.device, dtype=torch.bfloat16).contiguous()
+        m.final_norm = f32("output_norm.weight")
+        if "output.weight" in gf.tensors and gf.tensors["output.weight"][1] in G.NATIVE_TYPES:
+            m.lm_head = GgufLinear([gf.raw_rows("output.weight")], H, m.device, "lm_head", workspace=m.ws)
+        elif "output.weight" in gf.tensors:
+            m.lm_head = BF16Linear(gf.tensor("output.weight"), m.device, "lm_head(bf16)")
+        else:
+            m.lm_head = BF16Linear(m.embed, m.device, "lm_head(tied)")
+        return m
+
     def set_embeddings(self, embed: torch.Tensor, final_norm: torch.Tensor, lm_head: Optional[torch.Tensor]):
         dev = self.device
         self.embed = embed.to(device=dev, dtype=torch.bfloat16).contiguous()
@@ -346,19 +377,29 @@ class DenseModel:
         qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]
         gate = buf.gate[:M] if buf.gate is not None else None
         T = rb.q_pos0 + M
+        tl = trace.timeline.on
         for li, L in enumerate(self.layers):
             kvl = kv_layers[li]
+            if tl: trace.mark("reduce+norm+allgather")
             x_full, agc, age = tp.sp_reduce_norm_allgather(hs, L.in_norm, eps, off, reduce=li > 0, M=M)
+            if tl: trace.mark("qkv gemm (dequant + ag-wait)")
             tp.sp_gemm_allgathered(L.qkv, x_full, agc, age, qkv, "bf16")
+            if tl: trace.mark("rope + kv write")
             if rb.q_pos0 > 0:
                 K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
             K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
                            gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+            if tl: trace.mark("flash prefill")
             K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0, gate)
+            if tl: trace.mark("o gemm + rs push")
             tp.sp_gemm_reduce_scatter(L.o, attn, M, H)
+            if tl: trace.mark("reduce+norm+allgather")
             x_full, agc, age = tp.sp_reduce_norm_allgather(hs, L.post_norm, eps, off, reduce=True, M=M)
+            if tl: trace.mark("gate_up gemm (dequant + ag-wait)")
             tp.sp_gemm_allgathered(L.gate_up, x_full, agc, age, act, "swiglu")
+            if tl: trace.mark("down gemm + rs push")
             tp.sp_gemm_reduce_scatter(L.down, act, M, H)
+        if tl: trace.mark("tail")
         tp.sp_reduce_norm_allgather(hs, None, eps, off, reduce=True, M=M)
         # the rows that need logits live on their owners: collect them on every rank
         rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
@@ -426,18 +467,27 @@ class DenseModel:
         cp.stats["chunks"] += 1
         for li, L in enumerate(self.layers):
             kvl = kv_layers[li]
+            tl = trace.timeline.on
+            if tl: trace.mark("norm + qkv gemm")
             self._norm_linear(L.qkv, h, L.in_norm, x, qkv[a:b], "bf16", eps, off)
+            if tl: trace.mark("k|v exchange")
             cp.exchange_kv(qkv, M, qsz, li & 1)
+            if tl: trace.mark("rope + kv write")
             if rb.q_pos0 > 0:
                 K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
             # norm + RoPE + cache append for the whole chunk (q of the other ranks' rows is computed from stale columns and
             # never read)
             K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
                            gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+            if tl: trace.mark("flash prefill")
             K.flash_prefill(q[a:b], buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0 + a, None if gate is None else gate[a:b])
+            if tl: trace.mark("o gemm")
             L.o(attn, h, "add_f32")
+            if tl: trace.mark("norm + gate_up gemm")
             self._norm_linear(L.gate_up, h, L.post_norm, x, act, "swiglu", eps, off)
+            if tl: trace.mark("down gemm")
             L.down(act, h, "add_f32")
+        if trace.timeline.on: trace.mark("tail")
         # rows that need logits live on their owners: collect them on every rank
         rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
         nl = rows.shape[0]

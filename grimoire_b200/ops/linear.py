@@ -530,3 +530,91 @@ class MXLinear:
         return True
 
     __call__ = forward
+
+
+class GgufLinear:
+    """A projection kept as the raw ggml blocks of its GGUF checkpoint (``--proj native`` on a .gguf file): decode steps
+    (<= 8 rows) read the stored bytes directly (gemv_gguf.cu; gemv_native_qk, src/gemv_decode.cpp:1216-1274 in the
+    reference), taller inputs expand the rows to bf16 for the tcgen05 GEMM.  ``parts`` are (raw uint8 [n][row_bytes], ggml
+    type id) in output-row order: fused q|k|v (and gate, up) keep their own block types, each part is one launch writing
+    its slice of the output columns.  ``swiglu``: parts are (gate, up) of equal height and the output is silu(gate) * up."""
+
+    def __init__(self, parts, K: int, device, name: str = "", swiglu: bool = False, workspace: Optional[Workspace] = None):
+        self.name, self.K, self.swiglu = name, K, swiglu
+        self.device = torch.device(device)
+        self.ws = workspace or default_workspace(device)
+        self.parts = [(raw.to(self.device).contiguous(), int(t)) for raw, t in parts]
+        self.N = sum(raw.shape[0] for raw, _ in self.parts)
+        if swiglu and (len(self.parts) != 2 or self.parts[0][0].shape[0] != self.parts[1][0].shape[0]):
+            raise ValueError("a SwiGLU GgufLinear takes exactly (gate, up) of equal height")
+        self.out_features = self.N // 2 if swiglu else self.N
+
+    def nbytes(self) -> int:
+        return sum(raw.numel() for raw, _ in self.parts)
+
+    def dequant(self) -> torch.Tensor:
+        """fp32 [N][K] through the host decoder (oracle, CPU path)."""
+        from ..formats.gguf import dequantize
+
+        return torch.cat([dequantize(t, raw.cpu(), raw.shape[0] * self.K).reshape(raw.shape[0], self.K) for raw, t in self.parts])
+
+    def _rows(self, x, out, epi_code: int, ldo: int, col0: int, part) -> None:
+        raw, t = part
+        lib = _native.cuda()
+        M = x.shape[0]
+        esz = out.element_size()
+        for m0 in range(0, M, 8):
+            m = min(8, M - m0)
+            optr = ctypes.c_void_p(out.data_ptr() + (m0 * ldo + col0) * esz)
+            code = lib.grm_gemv_gguf(_c(t), _native.ptr(raw), ctypes.c_long(raw.stride(0)), _native.ptr(x[m0: m0 + m]), _c(x.stride(0)), optr,
+                                     _c(ldo), _c(m), _c(raw.shape[0]), _c(self.K), _c(epi_code), _native.stream_ptr())
+            _native.check(code, f"gemv_gguf {self.name} type={t} M={m} N={raw.shape[0]} K={self.K}")
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epi: str = "bf16") -> torch.Tensor:
+        M = x.shape[0]
+        if self.swiglu != (epi == "swiglu"):
+            raise ValueError("the swiglu epilogue goes with a (gate, up) weight and nothing else does")
+        if self.device.type != "cuda":
+            w = self.dequant()
+            y = x.bfloat16().float() @ w.t()
+            if self.swiglu:
+                I = self.N // 2
+                out.copy_((torch.nn.functional.silu(y[:, :I]) * y[:, I:]).to(out.dtype))
+            elif epi == "add_f32":
+                out.add_(y)
+            else:
+                out.copy_(y.to(out.dtype))
+            return out
+        lib = _native.cuda()
+        if M > SMALLM_MAX:
+            # taller inputs: expand to bf16 once per call and run the tcgen05 GEMM (gate | up as two GEMMs + the product)
+            wb = self.ws.get("dequant_bf16", self.N * self.K, torch.bfloat16).view(-1)[: self.N * self.K].view(self.N, self.K)
+            r0 = 0
+            for raw, t in self.parts:
+                code = lib.grm_dequant_gguf(_c(t), _native.ptr(raw), ctypes.c_long(raw.stride(0)), _native.ptr(wb[r0:]), ctypes.c_long(self.K),
+                                            _c(raw.shape[0]), _c(self.K), _native.stream_ptr())
+                _native.check(code, f"dequant_gguf {self.name}")
+                r0 += raw.shape[0]
+            if not self.swiglu:
+                return gemm_bf16(x, wb, out, epi)
+            tmp = self.ws.get("gguf_gu", M * self.N, torch.float32).view(-1)[: M * self.N].view(M, self.N)
+            gemm_bf16(x, wb, tmp, "f32")
+            I = self.N // 2
+            _native.check(lib.grm_swiglu_mul(_native.ptr(tmp), ctypes.c_void_p(tmp.data_ptr() + 4 * I), _native.ptr(out), _c(M), _c(I), _c(self.N),
+                                             _c(out.stride(0)), _native.stream_ptr()), "swiglu_mul")
+            return out
+        if self.swiglu:
+            I = self.N // 2
+            tmp = self.ws.get("gguf_gu", M * self.N, torch.float32).view(-1)[: M * self.N].view(M, self.N)
+            self._rows(x, tmp, 1, self.N, 0, self.parts[0])
+            self._rows(x, tmp, 1, self.N, I, self.parts[1])
+            _native.check(lib.grm_swiglu_mul(_native.ptr(tmp), ctypes.c_void_p(tmp.data_ptr() + 4 * I), _native.ptr(out), _c(M), _c(I), _c(self.N),
+                                             _c(out.stride(0)), _native.stream_ptr()), "swiglu_mul")
+            return out
+        col = 0
+        for part in self.parts:
+            self._rows(x, out, EPI[epi], out.stride(0), col, part)
+            col += part[0].shape[0]
+        return out
+
+    __call__ = forward

@@ -140,3 +140,57 @@ def test_gguf_file_loads_into_the_engine(tmp_path):
     want = Engine(DenseModel.from_state_dict(cfg, sd, "cpu"), EngineLimits(max_slots=2, max_ctx=64, prefill_chunk=32, max_decode_rows=4)).generate(prompt, 6)
     assert list(got) == list(want)
     llm.close()
+
+
+def _q8_0_rows(w: torch.Tensor) -> bytes:
+    out = b""
+    for row in w:
+        for blk in row.reshape(-1, 32):
+            d = float(blk.abs().max()) / 127 or 1.0
+            out += struct.pack("<e", d) + bytes((torch.round(blk / d).clamp(-127, 127).to(torch.int8).view(torch.uint8)).tolist())
+    return out
+
+
+def test_gguf_native_projections_keep_the_files_blocks(tmp_path):
+    """``--proj native`` on a GGUF file: the projections stay the stored Q8_0 blocks (GgufLinear over the raw rows) and the
+    logits agree with the same file loaded through the dequantise-and-requantise path at bf16."""
+    from grimoire_b200.api import Grimoire
+    from grimoire_b200.config import EngineConfig
+    from grimoire_b200.ops.linear import GgufLinear
+
+    H, I, L, V, Hq, Hkv, D = 128, 256, 2, 64, 2, 1, 64
+    g = torch.Generator().manual_seed(1)
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.05
+    tensors = {}
+    f32 = lambda name, t: tensors.__setitem__(name, (0, tuple(reversed(t.shape)), t.contiguous().numpy().tobytes()))
+    q8 = lambda name, t: tensors.__setitem__(name, (8, tuple(reversed(t.shape)), _q8_0_rows(t)))
+    f32("token_embd.weight", rnd(V, H))
+    f32("output_norm.weight", torch.ones(H))
+    q8("output.weight", rnd(V, H))
+    for i in range(L):
+        for gn, shape in (("attn_q", (Hq * D, H)), ("attn_k", (Hkv * D, H)), ("attn_v", (Hkv * D, H)), ("attn_output", (H, Hq * D)),
+                          ("ffn_gate", (I, H)), ("ffn_up", (I, H)), ("ffn_down", (H, I))):
+            q8(f"blk.{i}.{gn}.weight", rnd(*shape))
+        f32(f"blk.{i}.attn_norm.weight", torch.ones(H))
+        f32(f"blk.{i}.ffn_norm.weight", torch.ones(H))
+    toks = [chr(0x100 + i) for i in range(V)]
+    kv = {"general.architecture": (8, "qwen3"), "qwen3.block_count": (4, L), "qwen3.embedding_length": (4, H),
+          "qwen3.attention.head_count": (4, Hq), "qwen3.attention.head_count_kv": (4, Hkv), "qwen3.attention.key_length": (4, D),
+          "qwen3.feed_forward_length": (4, I), "qwen3.rope.freq_base": (6, 1e6), "tokenizer.ggml.model": (8, "gpt2"),
+          "tokenizer.ggml.tokens": (9, (8, toks)), "tokenizer.ggml.merges": (9, (8, [])), "tokenizer.ggml.token_type": (9, (5, [1] * V))}
+    path = tmp_path / "q8.gguf"
+    _write_gguf(path, kv, tensors)
+    gf = gguf.GGUFFile(path)
+    raw, typ = gf.raw_rows("blk.0.ffn_down.weight")
+    assert typ == 8 and raw.shape == (H, I // 32 * 34) and gguf.native_ok(gf, gguf.config_from_gguf(gf))
+    gf.close()
+    ids = torch.randint(0, V, (19,), generator=g).tolist()
+    nat = Grimoire.load(EngineConfig(model=str(path), proj="native", ctx=64, seq_slots=2, prefill_chunk=32), device="cpu")
+    assert all(isinstance(l.qkv, GgufLinear) and isinstance(l.down, GgufLinear) for l in nat.model.layers)
+    assert isinstance(nat.model.lm_head, GgufLinear) and len(nat.model.layers[0].qkv.parts) == 3
+    a = nat.score_ids(ids)
+    ref = Grimoire.load(EngineConfig(model=str(path), proj="bf16", ctx=64, seq_slots=2, prefill_chunk=32), device="cpu")
+    b = ref.score_ids(ids)
+    assert float((a - b).abs().max()) < 0.03 * max(1.0, float(b.abs().max()))
+    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) >= 0.9
+    nat.close(), ref.close()
