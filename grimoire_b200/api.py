@@ -43,14 +43,14 @@ def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     if cfg.head_dim not in (64, 128, 256):
         return f"head_dim {cfg.head_dim} is not supported (64, 128, 256)"
     if is_hybrid(cfg):
-        if not cfg.is_moe or not cfg.shared_expert_intermediate_size:
-            return "linear-attention layers are served with the MoE FFN (+ shared expert) of the hybrid family only"
+        if not cfg.is_moe and ec.ep_world > 1:
+            return "expert parallelism needs an MoE FFN"
         if ec.tp_world > 1 or ec.pp_world > 1:
             return "the hybrid (DeltaNet + MoE) family scales by expert parallelism (multi EP); tensor / pipeline stages are not built for it"
         if cfg.num_experts % max(1, ec.ep_world):
             return f"expert parallel {ec.ep_world} does not divide {cfg.num_experts} experts"
-        if cfg.hidden_size % 128 or cfg.moe_intermediate_size % 128:
-            return "block-scaled fp8 projections need widths that are multiples of 128"
+        if cfg.hidden_size % 128 or cfg.moe_intermediate_size % 128 or (not cfg.is_moe and cfg.intermediate_size % 128):
+            return "block-scaled fp8 / int4 g128 projections need widths that are multiples of 128"
         return None
     if ec.ep_world > 1:
         return "expert parallelism needs an MoE model"
@@ -158,7 +158,8 @@ class Grimoire:
                     raise UnsupportedModel(why)
                 if is_hybrid(cfg):
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
-                                                        expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""))
+                                                        expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
+                                                        proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))
                 else:
                     model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
                                                        proj=ec.proj, pp_rank=ec.pp_rank, pp_world=ec.pp_world)

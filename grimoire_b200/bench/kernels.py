@@ -181,6 +181,35 @@ def bench_rowq(args) -> None:
               f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
 
 
+def bench_gguf(args) -> None:
+    """Projections over raw GGUF blocks (--fmt q4_0 / q8_0 / q4_k / q5_k / q6_k / iq4_nl / iq4_xs) at the 27B shapes."""
+    from ..ops.linear import GgufLinear
+
+    hbm, _, tag = peaks()
+    dev = "cuda"
+    t, bb, bw = {"q4_0": (2, 18, 32), "q8_0": (8, 34, 32), "q4_k": (12, 144, 256), "q5_k": (13, 176, 256), "q6_k": (14, 210, 256),
+                 "iq4_nl": (20, 18, 32), "iq4_xs": (23, 136, 256)}[args.fmt]
+    for name, N, K_, sw, epi in SHAPES:
+        if args.only and name != args.only:
+            continue
+        row_bytes = K_ // bw * bb
+        nbytes = N * row_bytes
+        copies = max(2, int(L2_BYTES * 2 // nbytes) + 1)
+        lins = []
+        for _ in range(copies):
+            raw = torch.randint(0, 64, (N, row_bytes), dtype=torch.uint8, device=dev)     # small bytes: fp16 scales stay finite
+            parts = [(raw[: N // 2], t), (raw[N // 2:], t)] if sw else [(raw, t)]
+            lins.append(GgufLinear(parts, K_, dev, name, swiglu=sw))
+        x = torch.randn(args.rows, K_, device=dev).bfloat16()
+        out = torch.zeros(args.rows, N // 2 if sw else N, dtype=torch.float32 if epi == "add_f32" else torch.bfloat16, device=dev)
+        for lin in lins:
+            lin(x, out, epi)
+        us = timed(lambda i: lins[i % copies](x, out, epi), args.iters)
+        gbs = nbytes / 1e9 / (us * 1e-6)
+        print(f"gemv_gguf {args.fmt:7s} {name:8s} M={args.rows:2d} N={N:6d} K={K_:6d} copies={copies:2d}  {us:8.2f} us  {gbs:7.0f} GB/s  "
+              f"{gbs / hbm:.3f} {tag} copy bandwidth", flush=True)
+
+
 def bench_gemm(args) -> None:
     _, tf, tag = peaks()
     dev = "cuda"
@@ -284,15 +313,15 @@ def bench_prefill(args) -> None:
 
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["smallm", "tc", "mx", "rowq", "gemm", "attn", "vattn", "prefill"])
+    ap.add_argument("what", choices=["smallm", "tc", "mx", "rowq", "gguf", "gemm", "attn", "vattn", "prefill"])
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--splits", type=int, default=0, help="attn: split-KV factor (0 = the engine's heuristic)")
-    ap.add_argument("--fmt", default="int8", help="rowq: int8 / bf16 / fp8_e4m3 / fp8_e5m2 / mxfp8")
+    ap.add_argument("--fmt", default="int8", help="rowq: int8 / bf16 / fp8_e4m3 / fp8_e5m2 / mxfp8; gguf: q4_0 / q8_0 / q4_k / q5_k / q6_k / iq4_nl / iq4_xs")
     ap.add_argument("--only", default="", help="one of qkv / o / gate_up / down")
     args = ap.parse_args(argv)
-    {"smallm": bench_smallm, "tc": bench_tc, "mx": bench_mx, "rowq": bench_rowq, "gemm": bench_gemm, "attn": bench_attn, "vattn": bench_vattn, "prefill": bench_prefill}[args.what](args)
+    {"smallm": bench_smallm, "tc": bench_tc, "mx": bench_mx, "rowq": bench_rowq, "gguf": bench_gguf, "gemm": bench_gemm, "attn": bench_attn, "vattn": bench_vattn, "prefill": bench_prefill}[args.what](args)
     print(f"launches={_native.launch_count}", flush=True)
 
 

@@ -1,7 +1,8 @@
 // gemv_gguf: projections straight over raw GGUF blocks -- decode steps of a model that keeps its checkpoint's ggml
 // quantisation (``--proj native`` on a .gguf file) read the stored bytes as they are instead of a re-quantised copy.
 // Reference: gemv_native_qk (src/gemv_decode.cpp:1216-1274) with the per-type block readers of
-// include/b70/native_qk_*.hpp.  Types served: Q4_0 (2), Q8_0 (8), Q4_K (12), Q5_K (13), Q6_K (14); the block layouts are
+// include/b70/native_qk_*.hpp.  Types served: Q4_0 (2), Q8_0 (8), Q4_K (12), Q5_K (13), Q6_K (14), IQ4_NL (20), IQ4_XS (23);
+// the block layouts are
 // ggml's (the host decoder csrc/host/gguf.cpp is the oracle the tests compare with).
 //
 // One warp per output row, 8 rows per CTA.  A lane takes 32-weight pieces -- a whole block of the 32-weight types, one of
@@ -31,8 +32,17 @@ __device__ __forceinline__ void scale_min_k4(int j, const uint8_t* q, int& sc, i
 }
 
 // bytes per block, weights per block
-__host__ __device__ inline int blk_bytes(int type) { return type == 2 ? 18 : type == 8 ? 34 : type == 12 ? 144 : type == 13 ? 176 : type == 14 ? 210 : 0; }
-__host__ __device__ inline int blk_weights(int type) { return (type == 2 || type == 8) ? 32 : 256; }
+__host__ __device__ inline int blk_bytes(int type) {
+  return type == 2 ? 18 : type == 8 ? 34 : type == 12 ? 144 : type == 13 ? 176 : type == 14 ? 210 : type == 20 ? 18 : type == 23 ? 136 : 0;
+}
+__host__ __device__ inline int blk_weights(int type) { return (type == 2 || type == 8 || type == 20) ? 32 : 256; }
+
+// the 16 levels of ggml's non-linear 4-bit code (IQ4_NL / IQ4_XS), four per word, read with a byte extract
+__device__ __forceinline__ float iq4_level(int q) {
+  constexpr uint32_t t0 = 0xBFAD9881u, t1 = 0xF6EADDCFu, t2 = 0x26190D01u, t3 = 0x71594535u;   // -127 -104 -83 -65 | -49 -35 -22 -10 | 1 13 25 38 | 53 69 89 113
+  const uint32_t word = (q & 8) ? ((q & 4) ? t3 : t2) : ((q & 4) ? t1 : t0);
+  return (float)(int8_t)((word >> (8 * (q & 3))) & 0xFF);
+}
 
 // Decode piece ``piece`` (32 weights: columns 32 * piece .. 32 * piece + 31) of a row stored at ``row`` into w[32].
 template <int TYPE>
@@ -47,6 +57,30 @@ __device__ __forceinline__ void decode_piece(const uint8_t* row, int piece, floa
       w[2 * j + 1] = (float)((int)((v >> 8) & 0xF) - 8) * d;
       w[2 * j + 16] = (float)((int)((v >> 4) & 0xF) - 8) * d;
       w[2 * j + 17] = (float)((int)((v >> 12) & 0xF) - 8) * d;
+    }
+  } else if (TYPE == 20 || TYPE == 23) {   // IQ4_NL: d, 16 bytes | IQ4_XS: d, 16 high scale bits, 4 low scale bytes, 8 x 16 bytes
+    const uint8_t* b;
+    const uint8_t* q;
+    float d;
+    if (TYPE == 20) {
+      b = row + (size_t)piece * 18;
+      q = b + 2;
+      d = h2f_dev(b);
+    } else {
+      b = row + (size_t)(piece >> 3) * 136;
+      const int ib = piece & 7;
+      const uint32_t sh = ld16(b + 2);
+      const int ls = (int)((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (int)(((sh >> (2 * ib)) & 3) << 4);
+      q = b + 8 + 16 * ib;
+      d = h2f_dev(b) * (float)(ls - 32);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t v = ld16(q + 2 * j);
+      w[2 * j] = iq4_level((int)(v & 0xF)) * d;
+      w[2 * j + 1] = iq4_level((int)((v >> 8) & 0xF)) * d;
+      w[2 * j + 16] = iq4_level((int)((v >> 4) & 0xF)) * d;
+      w[2 * j + 17] = iq4_level((int)((v >> 12) & 0xF)) * d;
     }
   } else if (TYPE == 8) {   // Q8_0: d, 32 int8
     const uint8_t* b = row + (size_t)piece * 34;
@@ -213,6 +247,8 @@ GRM_API int grm_gemv_gguf(int type, const void* w, long row_bytes, const void* x
     case 12: return launch_gemv<12>(p, st);
     case 13: return launch_gemv<13>(p, st);
     case 14: return launch_gemv<14>(p, st);
+    case 20: return launch_gemv<20>(p, st);
+    case 23: return launch_gemv<23>(p, st);
     default: return -2;
   }
 }
@@ -230,6 +266,8 @@ GRM_API int grm_dequant_gguf(int type, const void* w, long row_bytes, void* out,
     case 12: dequant_gguf_kernel<12><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, (bf16*)out, ldo, N, K); break;
     case 13: dequant_gguf_kernel<13><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, (bf16*)out, ldo, N, K); break;
     case 14: dequant_gguf_kernel<14><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, (bf16*)out, ldo, N, K); break;
+    case 20: dequant_gguf_kernel<20><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, (bf16*)out, ldo, N, K); break;
+    case 23: dequant_gguf_kernel<23><<<grid, 256, 0, st>>>((const uint8_t*)w, row_bytes, (bf16*)out, ldo, N, K); break;
     default: return -2;
   }
   GRM_LAUNCH_RET();

@@ -160,7 +160,7 @@ def tokenizer_json_from_gguf(g: GGUFFile) -> Optional[dict]:
             "model": {"type": "BPE", "vocab": {t: i for i, t in enumerate(toks)}, "merges": merges}}
 
 
-NATIVE_TYPES = (2, 8, 12, 13, 14)       # block types the raw-block kernels serve (csrc/kernels/gemv_gguf.cu)
+NATIVE_TYPES = (2, 8, 12, 13, 14, 20, 23)       # block types the raw-block kernels serve (csrc/kernels/gemv_gguf.cu)
 
 
 def native_ok(g: GGUFFile, cfg) -> bool:

@@ -208,5 +208,34 @@ def tiny_hybrid_moe(layers: int = 4) -> ModelConfig:
                        shared_expert_intermediate_size=128, quant="fp8_block")
 
 
-PRESETS = {"tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+def hybrid_dense_27b(layers: int = 64) -> ModelConfig:
+    """The 27B hybrid with a dense FFN: 3 Gated DeltaNet layers then 1 gated full-attention layer (16 of 64), hidden 5120,
+    24q / 4kv x 256, FFN 17408, DeltaNet 16 key / 48 value heads x 128 (the reference's own 27B: src/kernels.hpp:70-72,
+    src/gemm_fast.cpp:812-816), int4 g128 projections."""
+    lt = [FULL_ATTN if (i % 4) == 3 else LINEAR_ATTN for i in range(layers)]
+    return ModelConfig(model_type="qwen3_5", hidden_size=5120, num_hidden_layers=layers, num_attention_heads=24,
+                       num_key_value_heads=4, head_dim=256, vocab_size=151936, intermediate_size=17408,
+                       partial_rotary_factor=0.25, attn_output_gate=True, qk_norm=True, norm_zero_centered=True,
+                       layer_types=lt, linear_num_key_heads=16, linear_num_value_heads=48, linear_key_head_dim=128,
+                       linear_value_head_dim=128, linear_conv_kernel_dim=4, gdn_chunk=64, rope_theta=1e7, quant="int4")
+
+
+def tiny_hybrid_dense(layers: int = 4) -> ModelConfig:
+    lt = [FULL_ATTN if (i % 4) == 3 else LINEAR_ATTN for i in range(layers)]
+    return ModelConfig(model_type="qwen3_5", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=512,
+                       partial_rotary_factor=1.0, attn_output_gate=True, qk_norm=True, norm_zero_centered=True,
+                       layer_types=lt, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64,
+                       linear_value_head_dim=64, quant="int4")
+
+
+def tiny_moe(layers: int = 2) -> ModelConfig:
+    """A Qwen3-MoE-style decoder: plain (ungated) attention in every layer, routed experts without a shared expert."""
+    return ModelConfig(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=0, qk_norm=True,
+                       num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128, shared_expert_intermediate_size=0,
+                       quant="fp8_block")
+
+
+PRESETS = {"hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
            "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}

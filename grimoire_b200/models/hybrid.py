@@ -1,5 +1,7 @@
-"""Hybrid linear-attention MoE decoder (Qwen3-Next / Qwen3.5 family): repeating 3 Gated DeltaNet
-layers + 1 gated full-attention layer, every FFN a top-k MoE with one shared expert.
+"""Hybrid linear-attention decoders (Qwen3-Next / Qwen3.5 family): repeating 3 Gated DeltaNet
+layers + 1 gated full-attention layer, every FFN a top-k MoE with one shared expert.  The same class
+serves the family's neighbours: the 27B hybrid with a dense SwiGLU FFN (int4 projections), and
+Qwen3-MoE-style decoders (plain attention in every layer, routed experts without a shared expert).
 
 Layer math and conventions follow the reference engine's forward() for this family
 (grimoire.cpp:15105-15202 DeltaNet mixer, :15207-15351 gated attention, :15364-15453 MoE) and the
@@ -19,11 +21,12 @@ from typing import Optional
 import torch
 
 from ..formats.codecs import Fmt
-from ..formats.quantize import quantize
+from ..formats.quantize import QuantWeight, quantize
+from ..formats.w4_tile_layout import interleave_gate_up_q
 from ..ops import core as K
 from ..ops import hybrid as Hb
 from ..ops import ref
-from ..ops.linear import BF16Linear
+from ..ops.linear import BF16Linear, W4Linear
 from ..ops.workspace import Workspace
 from .config import ModelConfig
 from .dense import RowBatch
@@ -39,8 +42,8 @@ class MoEBlock:
     gate_up_scale: torch.Tensor   # fp32  [E][2I][H/128]
     down: torch.Tensor            # uint8 [E][H][I]
     down_scale: torch.Tensor      # fp32  [E][H][I/128]
-    shared_gu: Hb.FP8BlockLinear
-    shared_down: Hb.FP8BlockLinear
+    shared_gu: Optional[Hb.FP8BlockLinear]      # None: no shared expert (Qwen3-MoE)
+    shared_down: Optional[Hb.FP8BlockLinear]
 
 
 @dataclass
@@ -48,7 +51,9 @@ class HybridLayer:
     kind: str                     # "gdn" | "attn"
     in_norm: torch.Tensor
     post_norm: torch.Tensor
-    moe: MoEBlock
+    moe: Optional[MoEBlock]       # None: dense FFN (ffn_gu / ffn_down)
+    ffn_gu: Optional[object] = None
+    ffn_down: Optional[object] = None
     # gdn
     in_qkv: Optional[Hb.FP8BlockLinear] = None
     in_z: Optional[Hb.FP8BlockLinear] = None
@@ -75,7 +80,7 @@ class HybridBuffers:
         mk = lambda *s, dt: torch.zeros(*s, dtype=dt, device=dev)
         k = cfg.num_experts_per_tok
         self.h, self.x = mk(max_rows, H, dt=f32), mk(max_rows, H, dt=bf)
-        self.qkv = mk(max_rows, g.Hq * g.D * 2 + 2 * g.Hkv * g.D, dt=bf)
+        self.qkv = mk(max_rows, cfg.q_size + 2 * cfg.kv_size, dt=bf)
         self.q, self.gate, self.attn = (mk(max_rows, g.Hq * g.D, dt=bf) for _ in range(3))
         self.gdn_qkv, self.gdn_conv = mk(max_rows, m.gdn_channels, dt=bf), mk(max_rows, m.gdn_channels, dt=bf)
         self.gdn_z, self.gdn_o = mk(max_rows, m.Hv * m.Dv, dt=bf), mk(max_rows, m.Hv * m.Dv, dt=bf)
@@ -85,7 +90,7 @@ class HybridBuffers:
         self.ids, self.wts = mk(max_rows, k, dt=torch.int32), mk(max_rows, k + 1, dt=f32)
         self.act = mk(max_rows * k, cfg.moe_intermediate_size, dt=bf)
         self.y = mk(max_rows * (k + 1), H, dt=f32)
-        self.act_s = mk(max_rows, cfg.shared_expert_intermediate_size, dt=bf)
+        self.act_s = mk(max_rows, max(cfg.shared_expert_intermediate_size, 0 if cfg.is_moe else cfg.intermediate_size), dt=bf)
         self.pos = mk(max_rows, k + 1, dt=torch.int32)
         self.xf, self.logits = mk(max_logit_rows, H, dt=bf), mk(max_logit_rows, cfg.vocab_size, dt=f32)
         self.next_ids = mk(max_logit_rows, dt=torch.int32)
@@ -112,7 +117,7 @@ class HybridBuffers:
 
 
 class HybridModel:
-    def __init__(self, cfg: ModelConfig, device, workspace: Optional[Workspace] = None, max_slots: int = 8):
+    def __init__(self, cfg: ModelConfig, device, workspace: Optional[Workspace] = None, max_slots: int = 8, proj: Optional[str] = None):
         self.cfg, self.device = cfg, torch.device(device)
         self.ws = workspace or Workspace(device)
         self.tp_rank, self.tp_world, self.pp_rank, self.pp_world = 0, 1, 0, 1
@@ -127,7 +132,9 @@ class HybridModel:
         self.Hk, self.Hv, self.Dk, self.Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.gdn_channels = 2 * self.Hk * self.Dk + self.Hv * self.Dv
         self.geom = K.AttnGeom(self.Hq, self.Hkv, cfg.head_dim, cfg.rot_dim, cfg.softmax_scale or ref.softmax_scale(cfg.head_dim),
-                               True, cfg.sliding_window, cfg.rms_norm_eps, cfg.norm_offset)
+                               bool(cfg.attn_output_gate), cfg.sliding_window, cfg.rms_norm_eps, cfg.norm_offset)
+        # projections outside the experts: block fp8 beside fp8 experts, int4 g128 for the dense-FFN hybrid, unless told
+        self.proj = proj if proj in ("int4", "fp8") else ("fp8" if cfg.is_moe or cfg.quant == "fp8_block" else "int4")
         self.inv_freq = ref.rope_inv_freq(cfg.rot_dim, cfg.rope_theta).to(self.device)
         self.layers: list[HybridLayer] = []          # all layers, in order
         self.kv_layer_count = cfg.num_attention_layers()
@@ -236,7 +243,7 @@ class HybridModel:
         [ep_rank * E/W, (ep_rank + 1) * E/W) of every layer (same values as the unsharded model)."""
         m = HybridModel(cfg, device, max_slots=max_slots)
         m.ep_rank, m.ep_world = ep_rank, ep_world
-        if cfg.num_experts % ep_world:
+        if cfg.num_experts % ep_world or (not cfg.is_moe and ep_world > 1):
             raise ValueError("experts do not split evenly over the expert-parallel ranks")
         e0, e1 = ep_rank * (cfg.num_experts // ep_world), (ep_rank + 1) * (cfg.num_experts // ep_world)
         dev = m.device
@@ -249,33 +256,42 @@ class HybridModel:
             g.manual_seed(seed * 1000003 + tag)
             return (torch.randn(*shape, generator=g, device=gdev, dtype=torch.float32) * scale).to(dev)
 
-        def fp8(w, name):
-            return Hb.FP8BlockLinear(w, dev, name)
-
+        fp8 = m._lin
         nw = (lambda n: torch.zeros(n, device=dev)) if cfg.norm_zero_centered else (lambda n: torch.ones(n, device=dev))
         kv_i = st_i = 0
         for i in range(cfg.num_hidden_layers):
             t = i * 64
-            gu = rnd(E, 2 * I, H, tag=t + 20)
-            dn = rnd(E, H, I, tag=t + 21)
-            gq = [quantize(gu[e], Fmt.FP8_BLOCK) for e in range(E)] if E <= 64 else None
-            if gq is not None:
-                dq = [quantize(dn[e], Fmt.FP8_BLOCK) for e in range(E)]
-                gu8, gus = torch.stack([q.payload for q in gq]), torch.stack([q.scales for q in gq])
-                dn8, dns = torch.stack([q.payload for q in dq]), torch.stack([q.scales for q in dq])
-            else:   # many experts: quantize as one [E*N][K] matrix (1x128 blocks never cross rows)
-                q1 = quantize(gu.reshape(E * 2 * I, H), Fmt.FP8_BLOCK)
-                q2 = quantize(dn.reshape(E * H, I), Fmt.FP8_BLOCK)
-                gu8, gus = q1.payload.reshape(E, 2 * I, H), q1.scales.reshape(E, 2 * I, H // 128)
-                dn8, dns = q2.payload.reshape(E, H, I), q2.scales.reshape(E, H, I // 128)
-            del gu, dn
-            gu8, gus, dn8, dns = gu8[e0:e1], gus[e0:e1], dn8[e0:e1], dns[e0:e1]
-            moe = MoEBlock(BF16Linear(rnd(E + 1, H, tag=t + 22, scale=0.5), dev, f"L{i}.router"), gu8.contiguous(), gus.float().contiguous(),
-                           dn8.contiguous(), dns.float().contiguous(), fp8(rnd(2 * Is, H, tag=t + 23), f"L{i}.shared_gu"),
-                           fp8(rnd(H, Is, tag=t + 24), f"L{i}.shared_down"))
+            moe, ffn = None, {}
+            if not cfg.is_moe:
+                Id = cfg.intermediate_size
+                ffn = dict(ffn_gu=m._lin_gate_up(rnd(Id, H, tag=t + 25), rnd(Id, H, tag=t + 26), f"L{i}.gate_up"),
+                           ffn_down=fp8(rnd(H, Id, tag=t + 27), f"L{i}.down"))
+            else:
+                gu = rnd(E, 2 * I, H, tag=t + 20)
+                dn = rnd(E, H, I, tag=t + 21)
+                gq = [quantize(gu[e], Fmt.FP8_BLOCK) for e in range(E)] if E <= 64 else None
+                if gq is not None:
+                    dq = [quantize(dn[e], Fmt.FP8_BLOCK) for e in range(E)]
+                    gu8, gus = torch.stack([q.payload for q in gq]), torch.stack([q.scales for q in gq])
+                    dn8, dns = torch.stack([q.payload for q in dq]), torch.stack([q.scales for q in dq])
+                else:   # many experts: quantize as one [E*N][K] matrix (1x128 blocks never cross rows)
+                    q1 = quantize(gu.reshape(E * 2 * I, H), Fmt.FP8_BLOCK)
+                    q2 = quantize(dn.reshape(E * H, I), Fmt.FP8_BLOCK)
+                    gu8, gus = q1.payload.reshape(E, 2 * I, H), q1.scales.reshape(E, 2 * I, H // 128)
+                    dn8, dns = q2.payload.reshape(E, H, I), q2.scales.reshape(E, H, I // 128)
+                del gu, dn
+                gu8, gus, dn8, dns = gu8[e0:e1], gus[e0:e1], dn8[e0:e1], dns[e0:e1]
+                router = rnd(E + 1, H, tag=t + 22, scale=0.5)
+                if not Is:
+                    router[E].zero_()
+                moe = MoEBlock(BF16Linear(router, dev, f"L{i}.router"), gu8.contiguous(), gus.float().contiguous(),
+                               dn8.contiguous(), dns.float().contiguous(),
+                               Hb.FP8BlockLinear(rnd(2 * Is, H, tag=t + 23), dev, f"L{i}.shared_gu") if Is else None,
+                               Hb.FP8BlockLinear(rnd(H, Is, tag=t + 24), dev, f"L{i}.shared_down") if Is else None)
             if cfg.is_attention_layer(i):
                 L = HybridLayer("attn", nw(H), nw(H), moe, qkv=fp8(rnd(cfg.q_size + 2 * cfg.kv_size, H, tag=t + 1), f"L{i}.qkv"),
-                                o=fp8(rnd(H, m.Hq * D, tag=t + 2), f"L{i}.o"), q_norm=nw(D), k_norm=nw(D), kv_index=kv_i)
+                                o=fp8(rnd(H, m.Hq * D, tag=t + 2), f"L{i}.o"), q_norm=nw(D) if cfg.qk_norm else None,
+                                k_norm=nw(D) if cfg.qk_norm else None, kv_index=kv_i, **ffn)
                 kv_i += 1
             else:
                 L = HybridLayer("gdn", nw(H), nw(H), moe, in_qkv=fp8(rnd(m.gdn_channels, H, tag=t + 3), f"L{i}.in_qkv"),
@@ -283,7 +299,7 @@ class HybridModel:
                                 in_ab=BF16Linear(rnd(2 * m.Hv, H, tag=t + 5, scale=0.2), dev, f"L{i}.in_ab"),
                                 conv_w=rnd(m.gdn_channels, 4, tag=t + 6, scale=0.4), A_log=rnd(m.Hv, tag=t + 7, scale=0.5),
                                 dt_bias=rnd(m.Hv, tag=t + 8, scale=0.5), gdn_norm=torch.ones(m.Dv, device=dev),
-                                out_proj=fp8(rnd(H, m.Hv * m.Dv, tag=t + 9), f"L{i}.out_proj"), state_index=st_i)
+                                out_proj=fp8(rnd(H, m.Hv * m.Dv, tag=t + 9), f"L{i}.out_proj"), state_index=st_i, **ffn)
                 st_i += 1
             m.layers.append(L)
         m.embed = rnd(cfg.vocab_size, H, tag=900001).bfloat16()
@@ -294,6 +310,22 @@ class HybridModel:
     # ------------------------------------------------------------------------------------------
     # checkpoints
     # ------------------------------------------------------------------------------------------
+    def _lin(self, w, name: str):
+        """Runtime projection outside the experts: int4 g128 (W4Linear) or block-scaled fp8, by the model's format."""
+        if self.proj == "int4":
+            if not (isinstance(w, QuantWeight) and w.fmt == Fmt.INT4):
+                w = quantize(w.dequant() if hasattr(w, "dequant") else w.float(), Fmt.INT4, group=self.cfg.quant_group)
+            return W4Linear(w, self.device, name, workspace=self.ws)
+        return Hb.FP8BlockLinear(w, self.device, name)
+
+    def _lin_gate_up(self, g, u, name: str):
+        """(gate, up) of a SwiGLU FFN as one projection with the swiglu epilogue."""
+        dense = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
+        if self.proj == "int4":
+            q = lambda t: t if isinstance(t, QuantWeight) and t.fmt == Fmt.INT4 else quantize(dense(t), Fmt.INT4, group=self.cfg.quant_group)
+            return W4Linear(interleave_gate_up_q(q(g), q(u)), self.device, name, swiglu=True, workspace=self.ws)
+        return Hb.FP8BlockLinear(torch.cat([dense(g), dense(u)], dim=0), self.device, name)
+
     def set_expert_placement(self, heat_file: str) -> bool:
         """Balanced expert ownership from a routing-heat file (models/expert_placement.py: the hit counts a serving run
         saved): per layer the hottest experts are dealt onto the least-loaded rank, so that the ranks of an expert-parallel
@@ -311,15 +343,16 @@ class HybridModel:
 
     def _add_layer(self, i: int, w: dict) -> None:
         """One layer from logical fp32 tensors (``[out][in]``; stored block-fp8 QuantWeights are used as they are).
-        Keys: in_norm, post_norm, router [E][H], shared_gate [1][H], gate_up [E][2I][H], down [E][H][I], shared_gate_proj,
-        shared_up_proj, shared_down_proj, then either q, k, v, o, q_norm, k_norm or in_qkv, in_z, in_a, in_b, conv [C][4],
+        Keys: in_norm, post_norm; for an MoE FFN router [E][H], gate_up [E][2I][H], down [E][H][I] and, with a shared
+        expert, shared_gate [1][H], shared_gate_proj, shared_up_proj, shared_down_proj; for a dense FFN ffn_gate, ffn_up,
+        ffn_down; then either q, k, v, o, q_norm, k_norm or in_qkv, in_z, in_a, in_b, conv [C][4],
         A_log, dt_bias, gdn_norm, out_proj."""
         cfg, dev = self.cfg, self.device
         E = cfg.num_experts
         e0, e1 = self.ep_rank * (E // self.ep_world), (self.ep_rank + 1) * (E // self.ep_world)
         f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()
         dense = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
-        perm = self.expert_perm[i] if self.expert_perm is not None else None
+        perm = self.expert_perm[i] if self.expert_perm is not None and cfg.is_moe else None
         if perm is not None:
             # Placement: physical expert j of this layer is logical expert perm[j].  The experts' weights and the router's
             # rows are permuted together, so routing yields physical ids and nothing downstream changes; rank r owns
@@ -328,49 +361,59 @@ class HybridModel:
             w = dict(w)
             w["gate_up"], w["down"] = w["gate_up"][idx], w["down"][idx]
             w["router"] = dense(w["router"])[idx]
-        fp8 = lambda t, name: Hb.FP8BlockLinear(t, dev, name)
+        fp8 = self._lin
 
         def experts(t3):
             n, k = t3.shape[1], t3.shape[2]
             q = quantize(t3[e0:e1].reshape((e1 - e0) * n, k).float(), Fmt.FP8_BLOCK)
             return q.payload.reshape(e1 - e0, n, k).to(dev).contiguous(), q.scales.reshape(e1 - e0, n, k // 128).float().to(dev).contiguous()
 
-        gu8, gus = experts(w["gate_up"])
-        dn8, dns = experts(w["down"])
-        sg = w.get("shared_gate")
-        router = torch.cat([dense(w["router"]), dense(sg) if sg is not None else torch.zeros(1, cfg.hidden_size)], dim=0)
-        shared_gu = torch.cat([dense(w["shared_gate_proj"]), dense(w["shared_up_proj"])], dim=0)
-        moe = MoEBlock(BF16Linear(router, dev, f"L{i}.router"), gu8, gus, dn8, dns, fp8(shared_gu, f"L{i}.shared_gu"),
-                       fp8(w["shared_down_proj"], f"L{i}.shared_down"))
+        moe, ffn = None, {}
+        if not cfg.is_moe:
+            ffn = dict(ffn_gu=self._lin_gate_up(w["ffn_gate"], w["ffn_up"], f"L{i}.gate_up"), ffn_down=fp8(w["ffn_down"], f"L{i}.down"))
+        else:
+            gu8, gus = experts(w["gate_up"])
+            dn8, dns = experts(w["down"])
+            sg = w.get("shared_gate")
+            router = torch.cat([dense(w["router"]), dense(sg) if sg is not None else torch.zeros(1, cfg.hidden_size)], dim=0)
+            shared = w.get("shared_gate_proj") is not None
+            if shared and sg is None:
+                raise KeyError(f"layer {i}: a shared expert without its gate (mlp.shared_expert_gate)")
+            moe = MoEBlock(BF16Linear(router, dev, f"L{i}.router"), gu8, gus, dn8, dns,
+                           Hb.FP8BlockLinear(torch.cat([dense(w["shared_gate_proj"]), dense(w["shared_up_proj"])], dim=0), dev,
+                                             f"L{i}.shared_gu") if shared else None,
+                           Hb.FP8BlockLinear(w["shared_down_proj"], dev, f"L{i}.shared_down") if shared else None)
         if cfg.is_attention_layer(i):
             qkv = torch.cat([dense(w["q"]), dense(w["k"]), dense(w["v"])], dim=0)
             L = HybridLayer("attn", f32(w["in_norm"]), f32(w["post_norm"]), moe, qkv=fp8(qkv, f"L{i}.qkv"), o=fp8(w["o"], f"L{i}.o"),
                             q_norm=f32(w.get("q_norm")), k_norm=f32(w.get("k_norm")),
-                            kv_index=sum(1 for l in self.layers if l.kind == "attn"))
+                            kv_index=sum(1 for l in self.layers if l.kind == "attn"), **ffn)
         else:
             ab = torch.cat([dense(w["in_a"]), dense(w["in_b"])], dim=0)
             L = HybridLayer("gdn", f32(w["in_norm"]), f32(w["post_norm"]), moe, in_qkv=fp8(w["in_qkv"], f"L{i}.in_qkv"),
                             in_z=fp8(w["in_z"], f"L{i}.in_z"), in_ab=BF16Linear(ab, dev, f"L{i}.in_ab"),
                             conv_w=f32(w["conv"].reshape(self.gdn_channels, -1)), A_log=f32(w["A_log"]), dt_bias=f32(w["dt_bias"]),
                             gdn_norm=f32(w["gdn_norm"]), out_proj=fp8(w["out_proj"], f"L{i}.out_proj"),
-                            state_index=sum(1 for l in self.layers if l.kind == "gdn"))
+                            state_index=sum(1 for l in self.layers if l.kind == "gdn"), **ffn)
         self.layers.append(L)
 
     @staticmethod
     def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1, expert_heat: str = "",
-                        expert_perm=None) -> "HybridModel":
+                        expert_perm=None, proj: Optional[str] = None) -> "HybridModel":
         """Load a HF directory of the hybrid family.  Tensor names follow the reference's resolver
         (src/qwen35_loader.cpp:1149-1169 ``linear_attn.{in_proj_qkv,in_proj_z,in_proj_a,in_proj_b,conv1d,A_log,dt_bias,norm,
         out_proj}``, :1320-1380 ``mlp.gate``, ``mlp.shared_expert*``, per-expert ``mlp.experts.N.*`` or the fused
-        ``mlp.experts.gate_up_proj`` [E][2I][H] / ``mlp.experts.down_proj`` [E][H][I]); projections are served as
-        block-scaled fp8, the a / b gates and the router stay bf16 (keep_qwen_bf16, :129-159)."""
+        ``mlp.experts.gate_up_proj`` [E][2I][H] / ``mlp.experts.down_proj`` [E][H][I]; a dense FFN under ``mlp.gate_proj`` /
+        ``up_proj`` / ``down_proj``).  Experts are served as block-scaled fp8; the other projections as block-scaled fp8 beside
+        an MoE FFN and int4 g128 beside a dense one (``proj`` "int4" / "fp8" overrides); the a / b gates and the router stay
+        bf16 (keep_qwen_bf16, :129-159)."""
         from ..formats.checkpoint import Checkpoint
 
         ck = Checkpoint(path) if isinstance(path, (str, bytes)) or hasattr(path, "__fspath__") else path    # or any tensor resolver
         cfg = ck.cfg
-        if not cfg.is_moe or cfg.num_experts % ep_world:
-            raise ValueError("from_checkpoint: not a hybrid MoE configuration or experts do not split over the ranks")
-        m = HybridModel(cfg, device, max_slots=max_slots)
+        if (cfg.is_moe and cfg.num_experts % ep_world) or (not cfg.is_moe and ep_world > 1):
+            raise ValueError("from_checkpoint: the experts do not split over the expert-parallel ranks")
+        m = HybridModel(cfg, device, max_slots=max_slots, proj=proj)
         m.ep_rank, m.ep_world = ep_rank, ep_world
         if expert_perm is not None:
             m.expert_perm = [list(p) for p in expert_perm]       # explicit placement (per layer: physical -> logical expert)
@@ -387,21 +430,25 @@ class HybridModel:
             p = f"{ck.prefix}layers.{i}."
             lin = lambda k: need(ck.linear(p + k), p + k)
             w = {"in_norm": need(ck.plain(p + "input_layernorm.weight"), p + "input_layernorm"),
-                 "post_norm": need(ck.plain(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm"),
-                 "router": lin("mlp.gate"), "shared_gate": ck.linear(p + "mlp.shared_expert_gate"),
-                 "shared_gate_proj": lin("mlp.shared_expert.gate_proj"), "shared_up_proj": lin("mlp.shared_expert.up_proj"),
-                 "shared_down_proj": lin("mlp.shared_expert.down_proj")}
-            fused_gu, fused_dn = ck.tensor(p + "mlp.experts.gate_up_proj"), ck.tensor(p + "mlp.experts.down_proj")
+                 "post_norm": need(ck.plain(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm")}
             dq = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
-            if fused_gu is not None and fused_dn is not None:
-                w["gate_up"], w["down"] = fused_gu.float(), fused_dn.float()
+            if not cfg.is_moe:
+                w.update(ffn_gate=lin("mlp.gate_proj"), ffn_up=lin("mlp.up_proj"), ffn_down=lin("mlp.down_proj"))
             else:
-                gu, dn = [], []
-                for e in range(E):
-                    x = f"mlp.experts.{e}."
-                    gu.append(torch.cat([dq(lin(x + "gate_proj")), dq(lin(x + "up_proj"))], dim=0))
-                    dn.append(dq(lin(x + "down_proj")))
-                w["gate_up"], w["down"] = torch.stack(gu), torch.stack(dn)
+                w["router"] = lin("mlp.gate")
+                if cfg.shared_expert_intermediate_size:
+                    w.update(shared_gate=ck.linear(p + "mlp.shared_expert_gate"), shared_gate_proj=lin("mlp.shared_expert.gate_proj"),
+                             shared_up_proj=lin("mlp.shared_expert.up_proj"), shared_down_proj=lin("mlp.shared_expert.down_proj"))
+                fused_gu, fused_dn = ck.tensor(p + "mlp.experts.gate_up_proj"), ck.tensor(p + "mlp.experts.down_proj")
+                if fused_gu is not None and fused_dn is not None:
+                    w["gate_up"], w["down"] = fused_gu.float(), fused_dn.float()
+                else:
+                    gu, dn = [], []
+                    for e in range(E):
+                        x = f"mlp.experts.{e}."
+                        gu.append(torch.cat([dq(lin(x + "gate_proj")), dq(lin(x + "up_proj"))], dim=0))
+                        dn.append(dq(lin(x + "down_proj")))
+                    w["gate_up"], w["down"] = torch.stack(gu), torch.stack(dn)
             if cfg.is_attention_layer(i):
                 a = "self_attn."
                 w.update(q=lin(a + "q_proj"), k=lin(a + "k_proj"), v=lin(a + "v_proj"), o=lin(a + "o_proj"),
@@ -416,14 +463,16 @@ class HybridModel:
         m.embed = ck.embedding().to(device=m.device, dtype=torch.bfloat16).contiguous()
         m.final_norm = need(ck.plain(ck.prefix + "norm.weight"), "norm.weight").to(m.device)
         head = ck.linear("lm_head")
-        m.lm_head = Hb.FP8BlockLinear(head if head is not None else ck.embedding(), m.device, "lm_head")
+        m.lm_head = m._lin(head if head is not None else ck.embedding(), "lm_head")
         return m
 
     def weight_bytes(self) -> int:
         n = self.lm_head.nbytes()
         for L in self.layers:
-            n += L.moe.gate_up.numel() + L.moe.down.numel() + 4 * (L.moe.gate_up_scale.numel() + L.moe.down_scale.numel())
-            for lin in (L.in_qkv, L.in_z, L.out_proj, L.qkv, L.o, L.moe.shared_gu, L.moe.shared_down):
+            moe = L.moe
+            if moe is not None:
+                n += moe.gate_up.numel() + moe.down.numel() + 4 * (moe.gate_up_scale.numel() + moe.down_scale.numel())
+            for lin in (L.in_qkv, L.in_z, L.out_proj, L.qkv, L.o, L.ffn_gu, L.ffn_down, moe and moe.shared_gu, moe and moe.shared_down):
                 if lin is not None:
                     n += lin.nbytes()
         return n
@@ -457,7 +506,9 @@ class HybridModel:
             r0, src = buf.tile_row0[: M * k], buf.tile_src[: M * k]
             Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu", small=True)
             Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32", small=True)
-            if ep.rank == 0:
+            if moe.shared_gu is None:
+                y[M * k: M * (k + 1)].zero_()
+            elif ep.rank == 0:
                 moe.shared_gu(x, buf.act_s[:M], "swiglu")
                 moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
             ep.combine_allreduce(h, y, pos, wts, M)
@@ -491,9 +542,12 @@ class HybridModel:
             te, r0, nr = (t.to(torch.int32).to(x.device) for t in (te, r0c, nrc))
         Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu", small=decode)
         Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32", small=decode)
-        # shared expert as slot k of the combine
-        moe.shared_gu(x, buf.act_s[:M], "swiglu")
-        moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
+        # shared expert as slot k of the combine (a zero contribution when the model has none)
+        if moe.shared_gu is None:
+            y[M * k: M * (k + 1)].zero_()
+        else:
+            moe.shared_gu(x, buf.act_s[:M], "swiglu")
+            moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
         if not decode:
             pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
         Hb.moe_combine(h, y, pos, wts)
@@ -534,7 +588,8 @@ class HybridModel:
                 L.out_proj(buf.gdn_o[:M], h, "add_f32")
             else:
                 kvl = kv_layers[L.kv_index]
-                qkv, q, gate, attn = buf.qkv[:M], buf.q[:M], buf.gate[:M], buf.attn[:M]
+                qkv, q, attn = buf.qkv[:M], buf.q[:M], buf.attn[:M]
+                gate = buf.gate[:M] if geom.q_gated else None
                 L.qkv(x, qkv, "bf16")
                 if prefill:
                     if rb.q_pos0 > 0:
@@ -547,7 +602,12 @@ class HybridModel:
                     K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
                 L.o(attn, h, "add_f32")
             K.add_rmsnorm(h, L.post_norm, x, eps, off)
-            self._moe(L, x, h, buf, M, decode=not prefill)
+            if L.moe is None:
+                act = buf.act_s[:M]
+                L.ffn_gu(x, act, "swiglu")
+                L.ffn_down(act, h, "add_f32")
+            else:
+                self._moe(L, x, h, buf, M, decode=not prefill)
         if rb.logits_rows is None:
             hsel, n = h, M
         else:

@@ -77,10 +77,15 @@ def random_hybrid_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02,
             sd[a + "norm.weight"] = 1.0 + rnd(Dv, scale=0.05)
             sd[a + "out_proj.weight"] = rnd(H, Hv * Dv)
         m = p + "mlp."
+        if not cfg.is_moe:                         # dense FFN (the 27B hybrid)
+            sd[m + "gate_proj.weight"], sd[m + "up_proj.weight"] = rnd(cfg.intermediate_size, H), rnd(cfg.intermediate_size, H)
+            sd[m + "down_proj.weight"] = rnd(H, cfg.intermediate_size)
+            continue
         sd[m + "gate.weight"] = rnd(E, H, scale=0.5)
-        sd[m + "shared_expert_gate.weight"] = rnd(1, H, scale=0.5)
-        sd[m + "shared_expert.gate_proj.weight"], sd[m + "shared_expert.up_proj.weight"] = rnd(Is, H), rnd(Is, H)
-        sd[m + "shared_expert.down_proj.weight"] = rnd(H, Is)
+        if Is:
+            sd[m + "shared_expert_gate.weight"] = rnd(1, H, scale=0.5)
+            sd[m + "shared_expert.gate_proj.weight"], sd[m + "shared_expert.up_proj.weight"] = rnd(Is, H), rnd(Is, H)
+            sd[m + "shared_expert.down_proj.weight"] = rnd(H, Is)
         gu, dn = rnd(E, 2 * I, H), rnd(E, H, I)
         if fused_experts:
             sd[m + "experts.gate_up_proj"], sd[m + "experts.down_proj"] = gu, dn

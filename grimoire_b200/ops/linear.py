@@ -563,8 +563,9 @@ class GgufLinear:
         lib = _native.cuda()
         M = x.shape[0]
         esz = out.element_size()
-        for m0 in range(0, M, 8):
-            m = min(8, M - m0)
+        step = max(1, min(8, (200 * 1024) // (2 * self.K)))       # the kernel stages the rows' activations in shared memory
+        for m0 in range(0, M, step):
+            m = min(step, M - m0)
             optr = ctypes.c_void_p(out.data_ptr() + (m0 * ldo + col0) * esz)
             code = lib.grm_gemv_gguf(_c(t), _native.ptr(raw), ctypes.c_long(raw.stride(0)), _native.ptr(x[m0: m0 + m]), _c(x.stride(0)), optr,
                                      _c(ldo), _c(m), _c(raw.shape[0]), _c(self.K), _c(epi_code), _native.stream_ptr())

@@ -1,4 +1,5 @@
-"""fp32 whole-model oracle of the hybrid (Gated DeltaNet + gated attention, MoE FFN) decoder, written against the HF
+"""fp32 whole-model oracle of the hybrid family (Gated DeltaNet and / or full attention, gated or plain; MoE FFN with or
+without a shared expert, or a dense FFN), written against the HF
 tensor names: one sequence, all positions at once for attention, token by token for the recurrence.  It is the
 host-side counterpart of the reference engine's model-matrix gate (tools/test_model_matrix.cpp) and of its per-family
 forward (src/grimoire.cpp:15105-15453); ``HybridModel`` must agree with it up to its weight / KV quantisation."""
@@ -33,15 +34,19 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
         x = bf(ref.rmsnorm(h, sd[p + "input_layernorm.weight"].float(), eps, off))
         if cfg.is_attention_layer(i):
             a = p + "self_attn."
-            qg = (x @ wf(sd[a + "q_proj.weight"]).t()).reshape(T, Hq, 2 * D)
-            q, gate = qg[..., :D], qg[..., D:].reshape(T, Hq * D)
+            if cfg.attn_output_gate:
+                qg = (x @ wf(sd[a + "q_proj.weight"]).t()).reshape(T, Hq, 2 * D)
+                q, gate = qg[..., :D], qg[..., D:].reshape(T, Hq * D)
+            else:
+                q, gate = (x @ wf(sd[a + "q_proj.weight"]).t()).reshape(T, Hq, D), None
             k = (x @ wf(sd[a + "k_proj.weight"]).t()).reshape(T, Hkv, D)
             v = (x @ wf(sd[a + "v_proj.weight"]).t()).reshape(T, Hkv, D)
             qn, kn = sd.get(a + "q_norm.weight"), sd.get(a + "k_norm.weight")
             q = ref.apply_rope(ref.head_rmsnorm(bf(q), None if qn is None else qn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
             k = ref.apply_rope(ref.head_rmsnorm(bf(k), None if kn is None else kn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
             o = ref.attention_rows(q, k, bf(v), pos, scale, cfg.sliding_window).reshape(T, Hq * D)
-            o = o * torch.sigmoid(bf(gate))
+            if gate is not None:
+                o = o * torch.sigmoid(bf(gate))
             h = h + bf(o) @ wf(sd[a + "o_proj.weight"]).t()
         else:
             a = p + "linear_attn."
@@ -62,6 +67,10 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
             h = h + o @ wf(sd[a + "out_proj.weight"]).t()
         x = bf(ref.rmsnorm(h, sd[p + "post_attention_layernorm.weight"].float(), eps, off))
         m = p + "mlp."
+        if not cfg.is_moe:
+            act = bf(F.silu(x @ wf(sd[m + "gate_proj.weight"]).t()) * (x @ wf(sd[m + "up_proj.weight"]).t()))
+            h = h + act @ wf(sd[m + "down_proj.weight"]).t()
+            continue
         E, I = cfg.num_experts, cfg.moe_intermediate_size
         if m + "experts.gate_up_proj" in sd:
             gu, dn = sd[m + "experts.gate_up_proj"], sd[m + "experts.down_proj"]
@@ -69,10 +78,12 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
         else:
             experts = [(wf(sd[f"{m}experts.{e}.gate_proj.weight"]), wf(sd[f"{m}experts.{e}.up_proj.weight"]),
                         wf(sd[f"{m}experts.{e}.down_proj.weight"])) for e in range(E)]
-        shared = (wf(sd[m + "shared_expert.gate_proj.weight"]), wf(sd[m + "shared_expert.up_proj.weight"]),
-                  wf(sd[m + "shared_expert.down_proj.weight"]))
-        y, _, _ = moe_ref.moe_forward(x, bf(sd[m + "gate.weight"]), experts, cfg.num_experts_per_tok, shared,
-                                      bf(sd[m + "shared_expert_gate.weight"]), cfg.norm_topk_prob)
+        shared = sgate = None
+        if m + "shared_expert.gate_proj.weight" in sd:
+            shared = (wf(sd[m + "shared_expert.gate_proj.weight"]), wf(sd[m + "shared_expert.up_proj.weight"]),
+                      wf(sd[m + "shared_expert.down_proj.weight"]))
+            sgate = bf(sd[m + "shared_expert_gate.weight"]) if m + "shared_expert_gate.weight" in sd else None
+        y, _, _ = moe_ref.moe_forward(x, bf(sd[m + "gate.weight"]), experts, cfg.num_experts_per_tok, shared, sgate, cfg.norm_topk_prob)
         h = h + y
     xf = bf(ref.rmsnorm(h, sd[pfx + "norm.weight"].float(), eps, off))
     head = sd.get("lm_head.weight", sd[pfx + "embed_tokens.weight"])

@@ -60,7 +60,8 @@ def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "
 
 
 def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_experts: bool = False):
-    """A hybrid (Gated DeltaNet + gated attention + MoE) checkpoint under the HF names of that family."""
+    """A checkpoint of the hybrid family (Gated DeltaNet / gated or plain attention; MoE with or without a shared expert, or a
+    dense FFN) under the HF names of that family."""
     path.mkdir(parents=True, exist_ok=True)
     sd = random_hybrid_state_dict(cfg, seed, fused_experts=fused_experts)
     hf = {"model_type": cfg.model_type, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
@@ -72,7 +73,9 @@ def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_e
           "linear_key_head_dim": cfg.linear_key_head_dim, "linear_value_head_dim": cfg.linear_value_head_dim,
           "linear_conv_kernel_dim": cfg.linear_conv_kernel_dim, "num_experts": cfg.num_experts,
           "num_experts_per_tok": cfg.num_experts_per_tok, "moe_intermediate_size": cfg.moe_intermediate_size,
-          "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob}
+          "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
+          "intermediate_size": cfg.intermediate_size, "attn_output_gate": cfg.attn_output_gate, "qk_norm": cfg.qk_norm,
+          "norm_zero_centered": cfg.norm_zero_centered}
     (path / "config.json").write_text(json.dumps(hf))
     save_file({k: v.bfloat16() for k, v in sd.items()}, path / "model.safetensors", {"format": "pt"})
     return sd

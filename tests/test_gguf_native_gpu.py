@@ -7,7 +7,7 @@ import torch
 
 from grimoire_b200.formats.gguf import dequantize
 
-BLOCK = {2: (18, 32), 8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256)}      # type -> (bytes, weights)
+BLOCK = {2: (18, 32), 8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256), 20: (18, 32), 23: (136, 256)}      # type -> (bytes, weights)
 
 
 def _raw_rows(t: int, N: int, K: int, seed: int) -> torch.Tensor:
@@ -18,7 +18,7 @@ def _raw_rows(t: int, N: int, K: int, seed: int) -> torch.Tensor:
     h = lambda v: torch.tensor(np.frombuffer(np.float16(v).tobytes(), dtype=np.uint8).copy())
     d = torch.rand(N, nb, generator=g) * 0.02 + 0.005
     dbytes = torch.tensor(np.frombuffer(d.numpy().astype(np.float16).tobytes(), dtype=np.uint8).copy()).reshape(N, nb, 2)
-    if t in (2, 8):
+    if t in (2, 8, 20, 23):
         raw[:, :, 0:2] = dbytes
     elif t in (12, 13):
         raw[:, :, 0:2] = dbytes
@@ -33,7 +33,7 @@ def _oracle(t: int, raw: torch.Tensor, K: int) -> torch.Tensor:
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [2, 8, 12, 13, 14])
+@pytest.mark.parametrize("t", [2, 8, 12, 13, 14, 20, 23])
 @pytest.mark.parametrize("M", [1, 3, 8, 13])
 def test_gemv_over_raw_blocks_matches_host_decoder(t, M):
     from grimoire_b200.ops.linear import GgufLinear

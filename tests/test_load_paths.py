@@ -69,6 +69,36 @@ def test_hybrid_checkpoint_matches_fp32_oracle(hybrid_dirs):
     g.close(), g2.close()
 
 
+@pytest.mark.parametrize("preset", ["tiny_hybrid_dense", "tiny_moe"])
+def test_hybrid_family_neighbours_match_fp32_oracle(preset, tmp_path):
+    """The 27B-style hybrid with a dense FFN (int4 projections) and a Qwen3-MoE-style decoder (plain attention, no shared
+    expert) load through the same class and agree with the fp32 oracle under their own weight round trip; greedy
+    continuation through the engine (prefill + decode steps, recurrent state included) follows the oracle's argmax."""
+    from grimoire_b200.models.config import PRESETS
+
+    cfg = PRESETS[preset]()
+    sd = write_hybrid_checkpoint(tmp_path / preset, cfg, seed=9)
+    g = Grimoire.load(_ec(tmp_path / preset), device="cpu")
+    assert isinstance(g.model, HybridModel)
+    dense_ffn = not cfg.is_moe
+    assert g.model.proj == ("int4" if dense_ffn else "fp8")
+    assert all((l.moe is None) == dense_ffn for l in g.model.layers)
+    if not dense_ffn:
+        assert all(l.moe.shared_gu is None and l.kind == "attn" for l in g.model.layers) and not g.model.geom.q_gated
+    ids = _prompt(23, 11)
+    got = g.score_ids(ids)
+    fmt = Fmt.INT4 if dense_ffn else Fmt.FP8_BLOCK
+    q = lambda w: quantize(w.bfloat16().float(), fmt).dequant().float()
+    want = hybrid_reference.forward_logits(cfg, {k: v.bfloat16().float() for k, v in sd.items()}, ids, weight_fn=q)
+    err = float((got - want).abs().max())
+    assert err < 0.06 * float(want.abs().max()), (err, float(want.abs().max()))
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.9
+    out, _ = g.generate(ids, 4)
+    full = g.score_ids(ids + out)
+    assert [int(full[len(ids) - 1 + j].argmax()) for j in range(4)] == out
+    g.close()
+
+
 def test_hybrid_prefix_cache_restores_recurrent_state(hybrid_dirs):
     _, _, split_dir, _ = hybrid_dirs
     g = Grimoire.load(_ec(split_dir, prefix_cache=1), device="cpu")
