@@ -192,6 +192,13 @@ class Grimoire:
             from .models.mtp import MtpDrafter, MtpHead
 
             g.drafter = MtpDrafter(eng, MtpHead.from_checkpoint(model, mtp_src, draft_vocab=ec.mtp_draft_vocab))
+        elif ec.dflash_model:
+            # --dflash-model: a block drafter over the target's residual taps (dense family, one GPU)
+            if hybrid or ec.tp_world > 1 or ec.pp_world > 1:
+                raise UnsupportedModel("the block drafter (--dflash-model) runs beside a single-GPU dense target")
+            from .models.dflash_drafter import load_dflash
+
+            g.drafter = load_dflash(ec.dflash_model, eng)
         g.banner()
         return g
 
@@ -204,7 +211,7 @@ class Grimoire:
             f"  parallel   : tp={m.tp_world} (fused all-reduce={'on' if getattr(m, 'tp', None) and m.tp.fused else 'off'}) pp={ec.pp_world} "
             f"ep={getattr(m, 'ep_world', 1)} dp={ec.dp_world}",
             f"  weights    : {'block-scaled fp8 (e4m3, 1x128)' if getattr(m, 'kv_layer_count', None) is not None else ec.proj + ' g' + str(m.cfg.quant_group)} "
-            f"({m.weight_bytes() / 1e9:.2f} GB on this rank), draft head={'mtp' if self.drafter is not None else 'none'}",
+            f"({m.weight_bytes() / 1e9:.2f} GB on this rank), draft head={type(self.drafter).__name__ if self.drafter is not None else 'none'}",
             f"  kv cache   : int8 paged, {self.engine.kv.num_pages} pages x 16 tokens, {self.engine.kv.bytes_per_token()} B/token",
             f"  batching   : width {ec.width()}, prefill chunk {ec.prefill_chunk}, interleave chunk {ec.interleave_chunk}",
             f"  speculation: copy drafts={'on' if ec.copy_drafts else 'off'} depth table {ec.spec_depth_table()}",

@@ -271,6 +271,227 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// Warp-specialised form of the same kernel: warps 0-3 are the 128 softmax rows, warp 4 owns every TMA request and every
+// tcgen05.mma.  The row threads never issue or wait for a copy, and S(j+1) is issued as soon as S(j) has left the K buffer
+// -- while the rows are still in the softmax of block j -- instead of after it, so the S product's latency is off the
+// critical path.  Hand-overs: bars[4/5] S(j) complete (rows and the MMA warp wait), bars[7] P(j) stored (128 arrivals, the
+// MMA warp waits), bars[6] PV(j) complete (rows wait before touching O / P, the MMA warp before refilling V).
+constexpr int kThreadsWs = 160;
+
+__global__ void __launch_bounds__(kThreadsWs, 2)
+flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                           const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kQBytes;
+  uint8_t* sV = sK + kKBytes;
+  uint8_t* sP = sV + 2 * kVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kPBytes);     // 0 Q, 1 K, 2/3 V[0/1], 4/5 S[0/1] done, 6 PV done, 7 P stored
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y;
+  const int kvh = h / (p.Hq / p.Hkv);
+  const int row = qb * BQ + tid;
+  const bool row_ok = warp < 4 && row < p.M;
+  const int q_pos = p.q_pos0 + row;
+  const int last_q = p.q_pos0 + min(p.M, (qb + 1) * BQ) - 1;
+  const int first_q = p.q_pos0 + qb * BQ;
+  const int kb_lo = p.window > 0 ? max(0, first_q - p.window + 1) / BKV : 0;
+  const int kb_hi = last_q / BKV;
+  const int nblk = kb_hi - kb_lo + 1;
+
+  if (tid == 0) {
+    for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
+    mbar_init(&bars[7], 128);
+    *s_abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  constexpr uint32_t idesc_s = make_idesc(BQ, BKV, 1, 1);
+  constexpr uint32_t idesc_o = make_idesc(BQ, D, 1, 1);
+
+  if (warp == 4) {
+    if (lane == 0) {
+      auto load_k = [&](int kb) {
+        mbar_expect_tx(&bars[1], kKBytes);
+        tma_load_2d(sK, &tmK, &bars[1], kvh * D, kb * BKV);
+        tma_load_2d(sK + kKBytes / 2, &tmK, &bars[1], kvh * D + 64, kb * BKV);
+      };
+      auto load_v = [&](int kb, int buf) {
+        mbar_expect_tx(&bars[2 + buf], kVBytes);
+        tma_load_2d(sV + buf * kVBytes, &tmV, &bars[2 + buf], kb * BKV, kvh * D);
+      };
+      auto issue_s = [&](int j) -> bool {
+        if (!mbar_wait(&bars[1], (uint32_t)j & 1u, p.status, 0x811u)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
+        const uint32_t td = tmem_base + ((j & 1) ? 192u : 0u);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * (kQBytes / 2)) + (uint64_t)((k & 3) * 2);
+          const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * (kKBytes / 2)) + (uint64_t)((k & 3) * 2);
+          tc_mma_f16(td, da, db, idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(&bars[4 + (j & 1)]);
+        return true;
+      };
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(&bars[0], kQBytes);
+      tma_load_2d(sQ, &tmQ, &bars[0], h * D, qb * BQ);
+      tma_load_2d(sQ + kQBytes / 2, &tmQ, &bars[0], h * D + 64, qb * BQ);
+      load_k(kb_lo);
+      load_v(kb_lo, 0);
+      bool good = mbar_wait(&bars[0], 0u, p.status, 0x810u) && issue_s(0);
+      for (int j = 0; j < nblk && good; ++j) {
+        const int kb = kb_lo + j, b = j & 1;
+        // S(j) has left the K buffer: fetch K(j+1) and issue S(j+1) at once.  Its TMEM buffer was last read by the rows'
+        // softmax of block j-1, which all of them finished before they reported P(j-1) -- awaited below one round ago.
+        good = mbar_wait(&bars[4 + b], (uint32_t)(j >> 1) & 1u, p.status, 0x813u);
+        if (!good) break;
+        if (j + 1 < nblk) {
+          load_k(kb + 1);
+          good = issue_s(j + 1);
+          if (!good) break;
+        }
+        // PV(j-1) done: its V buffer can take V(j+1)
+        if (j > 0) {
+          good = mbar_wait(&bars[6], (uint32_t)(j - 1) & 1u, p.status, 0x814u);
+          if (!good) break;
+        }
+        if (j + 1 < nblk) load_v(kb + 1, b ^ 1);
+        good = mbar_wait(&bars[7], (uint32_t)j & 1u, p.status, 0x815u) && mbar_wait(&bars[2 + b], (uint32_t)(j >> 1) & 1u, p.status, 0x812u);
+        if (!good) break;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + b * kVBytes);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_f16(tmem_base + 64, make_sw128_kmajor_desc(pa) + (uint64_t)(k * 2), make_sw128_kmajor_desc(va) + (uint64_t)(k * 2), idesc_o,
+                     (k != 0 || j != 0) ? 1u : 0u);
+        tc_commit(&bars[6]);
+      }
+      if (!good) {
+        *s_abort = 1;
+        // let copies in flight land before the shared memory is handed to another CTA (bounded)
+        for (int b = 1; b <= 3; ++b)
+          for (int i = 0; i < 200000 && !mbar_try_wait(&bars[b], 0u) && !mbar_try_wait(&bars[b], 1u); ++i) __nanosleep(64);
+      }
+    }
+  } else {
+    const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int kb = kb_lo + j, b = j & 1;
+      if (!mbar_wait(&bars[4 + b], (uint32_t)(j >> 1) & 1u, p.status, 0x803u)) { ok = false; break; }
+      tc_fence_after();
+      float sv[BKV];
+      {
+        const uint32_t ts = t_row + (b ? 192u : 0u);
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(ts, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[i] = __uint_as_float(r[i]);
+        tmem_ld_32x32b_x32(ts + 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sv[32 + i] = __uint_as_float(r[i]);
+      }
+      float mx = -INFINITY;
+      const int key0 = kb * BKV;
+      const bool need_mask = (key0 + BKV - 1 > first_q) || (p.window > 0) || !row_ok;
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) {
+        float sc = sv[i] * p.scale_log2;
+        if (need_mask) {
+          const int kp = key0 + i;
+          const bool vis = row_ok && kp <= q_pos && (p.window <= 0 || kp > q_pos - p.window);
+          sc = vis ? sc : -INFINITY;
+        }
+        sv[i] = sc;
+        mx = fmaxf(mx, sc);
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      float psum = 0.f;
+      uint32_t pk[BKV / 2];
+#pragma unroll
+      for (int i = 0; i < BKV; i += 2) {
+        const float p0 = ex2(sv[i] - m_use), p1 = ex2(sv[i + 1] - m_use);
+        psum += p0 + p1;
+        pk[i >> 1] = pack_bf16x2(p0, p1);
+      }
+      m_run = m_new;
+      l_run = l_run * alpha + psum;
+      // PV(j-1) must have finished before O is rescaled and P is overwritten
+      if (j > 0) {
+        if (!mbar_wait(&bars[6], (uint32_t)(j - 1) & 1u, p.status, 0x804u)) { ok = false; break; }
+        tc_fence_after();
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32b_x32(t_row + 64 + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      {
+        uint8_t* prow = sP + tid * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(&bars[7]);
+    }
+    if (ok) {
+      if (!mbar_wait(&bars[6], (uint32_t)(nblk - 1) & 1u, p.status, 0x805u)) ok = false;
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      bf16* dst = p.out + (size_t)row * p.ld_o + (size_t)h * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + 64 + c * 32, r);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
+}
+
 // v [T][ld] (this kv head block of 128 columns at col0) -> vt [128][ldt]: 32x32 tiles through shared memory
 __global__ void __launch_bounds__(256) kv_transpose_kernel(const bf16* __restrict__ v, int ld, bf16* __restrict__ vt, int ldt, int T, int cols) {
   __shared__ bf16 tile[32][33];
@@ -340,6 +561,15 @@ GRM_API int grm_flash_prefill_tc(const void* q, int ld_q, const void* k, const v
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  flash_prefill_tc_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreads, kSmem, st>>>(tq, tk, tv, p);
+  static int ws = -1;
+  if (ws < 0) {
+    const char* e = getenv("GRIMOIRE_FLASH_WS");
+    ws = (e && e[0] == '0') ? 0 : 1;
+    if (ws && cudaFuncSetAttribute(flash_prefill_tc_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) ws = 0;
+  }
+  if (ws)
+    flash_prefill_tc_ws_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreadsWs, kSmem, st>>>(tq, tk, tv, p);
+  else
+    flash_prefill_tc_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreads, kSmem, st>>>(tq, tk, tv, p);
   GRM_LAUNCH_RET();
 }

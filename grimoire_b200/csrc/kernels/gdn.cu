@@ -200,14 +200,18 @@ struct GdnChunkParams {
   int Hk, Hv;
 };
 
-__global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkParams p) {
+static_assert(2 * CH * (CH + 1) <= CH * LDK, "L and M must fit in the Q tile");
+
+__global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_kernel(const GdnChunkParams p) {
   extern __shared__ __align__(16) float smc[];
   float* Ks = smc;                          // [CH][LDK]
   float* Qs = Ks + CH * LDK;                // [CH][LDK]
   float* Vs = Qs + CH * LDK;                // [CH][DVL]
-  float* Lm = Vs + CH * DVL;                // [CH][CH + 1]
+  // the two C x C matrices live where the Q tile was: Q is last read (K S_0^T / Q S_0^T and q.k below) before they are
+  // written, which keeps a CTA under half of an SM's shared memory so that two CTAs share an SM
+  float* Lm = Qs;                           // [CH][CH + 1]
   float* Mm = Lm + CH * (CH + 1);           // [CH][CH + 1]
-  float* Us = Mm + CH * (CH + 1);           // [CH][DVL + 1]
+  float* Us = Vs + CH * DVL;                // [CH][DVL + 1]
   float* Ps = Us + CH * UP;          // [CH][DVL + 1]  (K S_0^T) for this CTA's dv rows
   float* Rs = Ps + CH * UP;          // [CH][DVL + 1]  (Q S_0^T)
   float* Gs = Rs + CH * UP;          // [CH] cumulative log decay
@@ -282,32 +286,6 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
       float acc = 0.f;
       for (int t = 0; t < CH; ++t) { acc += Gs[t]; Gs[t] = acc; }
     }
-    // ---- k_t.k_j and q_t.k_j: thread = (row t, half of the j range) ----
-    {
-      const int t = tid >> 1, jh = (tid & 1) * 32;
-      float akk[32], aqk[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) { akk[j] = 0.f; aqk[j] = 0.f; }
-      for (int kb = 0; kb < D / 4; ++kb) {
-        const float4 kt = *reinterpret_cast<const float4*>(Ks + t * LDK + kb * 4);
-        const float4 qt = *reinterpret_cast<const float4*>(Qs + t * LDK + kb * 4);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float4 kj = *reinterpret_cast<const float4*>(Ks + (jh + j) * LDK + kb * 4);
-          akk[j] = fmaf(kt.x, kj.x, fmaf(kt.y, kj.y, fmaf(kt.z, kj.z, fmaf(kt.w, kj.w, akk[j]))));
-          aqk[j] = fmaf(qt.x, kj.x, fmaf(qt.y, kj.y, fmaf(qt.z, kj.z, fmaf(qt.w, kj.w, aqk[j]))));
-        }
-      }
-      __syncthreads();                                     // Gs is complete
-      const float gt = Gs[t], bt = Bs[t];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int jj = jh + j;
-        const float ratio = jj <= t ? __expf(gt - Gs[jj]) : 0.f;
-        Lm[t * (CH + 1) + jj] = jj < t ? bt * ratio * akk[j] : 0.f;
-        Mm[t * (CH + 1) + jj] = ratio * aqk[j];
-      }
-    }
     // ---- p_t = (K S_0^T)[t][dv], r_t = (Q S_0^T)[t][dv]: partial over this thread's 32 k, quad-reduced; thread
     //      `part` keeps the values of its 16 tokens ----
     // (results go to shared memory so the token loops below stay rolled: the code of a chunk fits the
@@ -325,6 +303,32 @@ __global__ void __launch_bounds__(kChThreads) gdn_chunked_kernel(const GdnChunkP
       a1 += __shfl_xor_sync(0xffffffffu, a1, 1); a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
       a2 += __shfl_xor_sync(0xffffffffu, a2, 1); a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
       if (part == 0) { Ps[t * UP + dvl] = a1; Rs[t * UP + dvl] = a2; }
+    }
+    // ---- k_t.k_j and q_t.k_j: thread = (row t, half of the j range) ----
+    {
+      const int t = tid >> 1, jh = (tid & 1) * 32;
+      float akk[32], aqk[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) { akk[j] = 0.f; aqk[j] = 0.f; }
+      for (int kb = 0; kb < D / 4; ++kb) {
+        const float4 kt = *reinterpret_cast<const float4*>(Ks + t * LDK + kb * 4);
+        const float4 qt = *reinterpret_cast<const float4*>(Qs + t * LDK + kb * 4);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float4 kj = *reinterpret_cast<const float4*>(Ks + (jh + j) * LDK + kb * 4);
+          akk[j] = fmaf(kt.x, kj.x, fmaf(kt.y, kj.y, fmaf(kt.z, kj.z, fmaf(kt.w, kj.w, akk[j]))));
+          aqk[j] = fmaf(qt.x, kj.x, fmaf(qt.y, kj.y, fmaf(qt.z, kj.z, fmaf(qt.w, kj.w, aqk[j]))));
+        }
+      }
+      __syncthreads();                                     // Gs is complete; nobody reads the Q tile any more
+      const float gt = Gs[t], bt = Bs[t];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int jj = jh + j;
+        const float ratio = jj <= t ? __expf(gt - Gs[jj]) : 0.f;
+        Lm[t * (CH + 1) + jj] = jj < t ? bt * ratio * akk[j] : 0.f;
+        Mm[t * (CH + 1) + jj] = ratio * aqk[j];
+      }
     }
     __syncthreads();                                       // Lm / Mm / Ps / Rs are complete
     // ---- forward substitution for this dv column of U (in Us); the four threads of a quad split the sum over j ----
@@ -416,7 +420,12 @@ GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_
   p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias; p.state = (float*)state;
   p.run_slot = (const int*)run_slot; p.run_start = (const int*)run_start; p.run_len = (const int*)run_len;
   p.o_raw = (float*)o_raw; p.ld_o = Hv * D; p.Hk = Hk; p.Hv = Hv;
-  const size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 2 * CH * (CH + 1) + 3 * CH * UP + 2 * CH);
+  size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 3 * CH * UP + 2 * CH);
+  // GRIMOIRE_GDN_SOLO=1 asks for more than half of an SM's shared memory, so that every CTA gets an SM to itself
+  // (measurement switch for the two-CTAs-per-SM layout)
+  static int solo = -1;
+  if (solo < 0) { const char* e = getenv("GRIMOIRE_GDN_SOLO"); solo = (e && e[0] == '1') ? 1 : 0; }
+  if (solo) smem = 120 * 1024;
   static bool configured = false;
   cudaStream_t st = (cudaStream_t)stream;
   if (!configured) {

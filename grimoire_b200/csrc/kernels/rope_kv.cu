@@ -30,6 +30,8 @@ struct RopeKvParams {
   bf16* k_out; bf16* v_out; int ld_kv;   // [M][Hkv*D] or null
   int8_t* k_pages; int8_t* v_pages; float* k_scale; float* v_scale;
   int M, Hq, Hkv, D, rot, q_gated;
+  int dense_pos0;            // >= 0: dense k / v rows are indexed by row_pos[row] - dense_pos0 instead of by row
+  int q_row0, q_rows;        // q (and gate) are produced for rows [q_row0, q_row0 + q_rows) only (q_rows < 0: every row)
 };
 
 constexpr int kPage = 16;
@@ -44,6 +46,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeKvParams p) {
   const bf16* src;
   int kind;  // 0 q, 1 k, 2 v
   int h;
+  if (hd < p.Hq && p.q_rows >= 0 && (row < p.q_row0 || row >= p.q_row0 + p.q_rows)) return;
   if (hd < p.Hq) { kind = 0; h = hd; src = p.qkv + (size_t)row * p.ld_qkv + (size_t)h * qstride; }
   else if (hd < p.Hq + p.Hkv) { kind = 1; h = hd - p.Hq; src = p.qkv + (size_t)row * p.ld_qkv + (size_t)p.Hq * qstride + (size_t)h * D; }
   else { kind = 2; h = hd - p.Hq - p.Hkv; src = p.qkv + (size_t)row * p.ld_qkv + (size_t)p.Hq * qstride + (size_t)(p.Hkv + h) * D; }
@@ -92,8 +95,11 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeKvParams p) {
     return;
   }
   bf16* dense = kind == 1 ? p.k_out : p.v_out;
-  if (dense)
-    for (int i = 0; i < per; ++i) dense[(size_t)row * p.ld_kv + (size_t)h * D + lane + 32 * i] = __float2bfloat16(v[i]);
+  if (dense) {
+    const int drow = p.dense_pos0 >= 0 ? p.row_pos[row] - p.dense_pos0 : row;
+    if (drow >= 0)
+      for (int i = 0; i < per; ++i) dense[(size_t)drow * p.ld_kv + (size_t)h * D + lane + 32 * i] = __float2bfloat16(v[i]);
+  }
   if (!p.row_seq || !p.k_pages) return;
   const int seq = p.row_seq[row];
   if (seq < 0) return;
@@ -133,11 +139,14 @@ __global__ void kv_gather_dequant_kernel(const int8_t* __restrict__ pages, const
 
 }  // namespace
 
-GRM_API int grm_rope_kvwrite(const void* qkv, int ld_qkv, const void* row_pos, const void* row_seq, const void* block_table,
+// Extended form: dense_pos0 >= 0 writes the dense k / v row of a token at index row_pos - dense_pos0 (rows may then come in any
+// order; the caller guarantees row_pos - dense_pos0 < the dense buffers' height); q_rows >= 0 limits q / gate to rows
+// [q_row0, q_row0 + q_rows) (context-parallel prefill: the other rows' queries belong to other ranks).
+GRM_API int grm_rope_kvwrite_ex(const void* qkv, int ld_qkv, const void* row_pos, const void* row_seq, const void* block_table,
                              int max_pages, const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float norm_eps,
                              float norm_offset, void* q_out, int ld_q, void* gate_out, void* k_out, void* v_out, int ld_kv,
                              void* k_pages, void* v_pages, void* k_scale, void* v_scale, int M, int Hq, int Hkv, int D, int rot,
-                             int q_gated, void* stream) {
+                             int q_gated, int dense_pos0, int q_row0, int q_rows, void* stream) {
   if ((D & 31) || D > 256 || (rot & 63) || rot > D || M < 1) return -2;
   RopeKvParams p;
   p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.row_pos = (const int*)row_pos; p.row_seq = (const int*)row_seq;
@@ -146,11 +155,22 @@ GRM_API int grm_rope_kvwrite(const void* qkv, int ld_qkv, const void* row_pos, c
   p.q_out = (bf16*)q_out; p.ld_q = ld_q; p.gate_out = (bf16*)gate_out; p.k_out = (bf16*)k_out; p.v_out = (bf16*)v_out; p.ld_kv = ld_kv;
   p.k_pages = (int8_t*)k_pages; p.v_pages = (int8_t*)v_pages; p.k_scale = (float*)k_scale; p.v_scale = (float*)v_scale;
   p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.q_gated = q_gated;
+  p.dense_pos0 = dense_pos0; p.q_row0 = q_row0; p.q_rows = q_rows;
   const long warps = (long)M * (Hq + 2 * Hkv);
   const int threads = 256;
   const long blocks = (warps * 32 + threads - 1) / threads;
   rope_kv_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(p);
   GRM_LAUNCH_RET();
+}
+
+GRM_API int grm_rope_kvwrite(const void* qkv, int ld_qkv, const void* row_pos, const void* row_seq, const void* block_table,
+                             int max_pages, const void* inv_freq, const void* q_norm_w, const void* k_norm_w, float norm_eps,
+                             float norm_offset, void* q_out, int ld_q, void* gate_out, void* k_out, void* v_out, int ld_kv,
+                             void* k_pages, void* v_pages, void* k_scale, void* v_scale, int M, int Hq, int Hkv, int D, int rot,
+                             int q_gated, void* stream) {
+  return grm_rope_kvwrite_ex(qkv, ld_qkv, row_pos, row_seq, block_table, max_pages, inv_freq, q_norm_w, k_norm_w, norm_eps, norm_offset,
+                             q_out, ld_q, gate_out, k_out, v_out, ld_kv, k_pages, v_pages, k_scale, v_scale, M, Hq, Hkv, D, rot, q_gated,
+                             -1, 0, -1, stream);
 }
 
 GRM_API int grm_kv_gather_dequant(const void* pages, const void* scales, const void* block_table, void* out, int T, int Hkv,

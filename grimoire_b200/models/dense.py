@@ -97,6 +97,7 @@ class Buffers:
         self.dense_v = mk(dense_kv_tokens, geom.Hkv * geom.D, dt=bf) if dense_kv_tokens else None
         self.max_rows = max_rows
         self.max_logit_rows = max_logit_rows
+        self.taps = None            # [max_rows][taps][H] fp32 when the model keeps residual taps (DenseModel.set_taps)
 
 
 class DenseModel:
@@ -113,6 +114,7 @@ class DenseModel:
         self.pp = None          # parallel.pp.PipelineParallel when pp_world > 1
         self.cp = None          # parallel.cp.ContextParallel: prefill chunks split by rows over whole-model replicas
         self.head_split = None  # (first vocabulary row, rows) of this rank's lm_head shard (TensorParallel.split_head)
+        self.tap_index: dict[int, int] = {}   # layer id -> slot of buf.taps (set_taps): residual after that layer is kept per row
         self.ws = workspace or Workspace(device)
         if cfg.num_attention_heads % tp_world or cfg.num_key_value_heads % tp_world or cfg.intermediate_size % tp_world:
             raise ValueError("tensor parallel degree must divide heads, kv heads and the FFN width")
@@ -151,6 +153,17 @@ class DenseModel:
         if isinstance(w, QuantWeight):
             return w if w.fmt == Fmt.INT4 else quantize(w.dequant(), Fmt.INT4, group=cfg.quant_group)
         return quantize(w, Fmt.INT4, group=cfg.quant_group, symmetric=getattr(cfg, "quant_symmetric", False))
+
+    def set_taps(self, layer_ids) -> None:
+        """Keep the residual stream after each of ``layer_ids`` for every row of every pass (``buf.taps`` [rows][taps][H]
+        fp32): the inputs of a block drafter (models/dflash_drafter.py).  A tap is the stream at ENTRY of layer id + 1
+        (grimoire.cpp:9325), so the last layer cannot be tapped.  Buffers made before this call get their tap rows here."""
+        ids = [int(i) for i in layer_ids]
+        if any(i < 0 or i >= self.cfg.num_hidden_layers - 1 for i in ids):
+            raise ValueError("a tap names a layer outside [0, layers - 2]")
+        if self.tp_world > 1 or self.pp_world > 1 or self.cp is not None:
+            raise ValueError("residual taps are kept on single-GPU models only")
+        self.tap_index = {lid: j for j, lid in enumerate(ids)}
 
     def _linear(self, qw: QuantWeight, name: str, swiglu: bool = False):
         """Runtime projection for a quantized weight: int4 -> W4Linear, MXFP4 -> MXLinear, block-scaled fp8 ->
@@ -351,7 +364,13 @@ class DenseModel:
         return n
 
     def make_buffers(self, max_rows: int, max_logit_rows: int, dense_kv_tokens: int = 0) -> Buffers:
-        return Buffers(self.cfg, self.geom, self.I, max_rows, max_logit_rows, self.device, dense_kv_tokens)
+        b = Buffers(self.cfg, self.geom, self.I, max_rows, max_logit_rows, self.device, dense_kv_tokens)
+        self.add_tap_rows(b)
+        return b
+
+    def add_tap_rows(self, b: Buffers) -> None:
+        if self.tap_index and getattr(b, "taps", None) is None:
+            b.taps = torch.zeros(b.max_rows, len(self.tap_index), self.cfg.hidden_size, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------------------------------
     # forward over M rows
@@ -450,19 +469,25 @@ class DenseModel:
         return logits
 
     def forward_prefill_cp(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
-        """Prefill chunk under context parallelism (parallel/cp.py): this rank runs rows [a, b) of the chunk through every
-        layer; per layer the ranks exchange the chunk's raw k | v rows, every rank appends the whole chunk's K / V to its
+        """Prefill chunk under context parallelism (parallel/cp.py): this rank runs its share of the chunk's rows (one early
+        and one late piece, so that causal attention costs every rank the same) through every layer; per layer the ranks exchange the chunk's raw k | v rows, every rank appends the whole chunk's K / V to its
         own cache, and the local query rows attend over past and present keys.  Same arithmetic per row as ``forward``."""
         cfg, geom, cp = self.cfg, self.geom, self.cp
         M = rb.tokens.shape[0]
-        a, b = cp.local_rows(M)
+        a, b = cp.local_rows(M)              # exchange order: this rank's rows are contiguous there
+        segs, perm = cp.layout(M)            # chunk rows behind them (two pieces under the balanced split)
         n = b - a
         eps, off = cfg.rms_norm_eps, cfg.norm_offset
         h, x = buf.h[:n], buf.x[:n]
         qkv, q, attn, act = buf.qkv[:M], buf.q[:M], buf.attn[:n], buf.act[:n]
         gate = buf.gate[:M] if buf.gate is not None else None
         qsz = geom.Hq * geom.D * (2 if geom.q_gated else 1)
-        K.embed(rb.tokens[a:b], self.embed, h)
+        if perm is None:
+            toks, row_pos, row_seq = rb.tokens[a:b], rb.row_pos, rb.row_seq
+        else:
+            toks = rb.tokens.index_select(0, perm[a:b])
+            row_pos, row_seq = rb.row_pos.index_select(0, perm), rb.row_seq.index_select(0, perm)
+        K.embed(toks, self.embed, h)
         T = rb.q_pos0 + M
         cp.stats["chunks"] += 1
         for li, L in enumerate(self.layers):
@@ -475,12 +500,16 @@ class DenseModel:
             if tl: trace.mark("rope + kv write")
             if rb.q_pos0 > 0:
                 K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
-            # norm + RoPE + cache append for the whole chunk (q of the other ranks' rows is computed from stale columns and
-            # never read)
-            K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
-                           gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+            # norm + RoPE + cache append for the whole chunk's keys (dense K / V land by position, whatever the row order);
+            # queries for the local rows only
+            K.rope_kvwrite(qkv, row_pos, row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm,
+                           gate, buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T], dense_pos0=rb.q_pos0, q_rows=(a, n))
             if tl: trace.mark("flash prefill")
-            K.flash_prefill(q[a:b], buf.dense_k, buf.dense_v, geom, attn, rb.q_pos0 + a, None if gate is None else gate[a:b])
+            o0 = 0
+            for g0, cnt in segs:
+                K.flash_prefill(q[a + o0: a + o0 + cnt], buf.dense_k, buf.dense_v, geom, attn[o0: o0 + cnt], rb.q_pos0 + g0,
+                                None if gate is None else gate[a + o0: a + o0 + cnt])
+                o0 += cnt
             if tl: trace.mark("o gemm")
             L.o(attn, h, "add_f32")
             if tl: trace.mark("norm + gate_up gemm")
@@ -492,9 +521,10 @@ class DenseModel:
         rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
         nl = rows.shape[0]
         sel = torch.zeros(nl, cfg.hidden_size, dtype=torch.float32, device=self.device)
-        mine = (rows >= a) & (rows < b)
+        owner, local = cp.owner_index(rows.long(), M)
+        mine = owner == cp.rank
         if bool(mine.any()):
-            sel[mine] = h.index_select(0, rows[mine] - a)
+            sel[mine] = h.index_select(0, local[mine])
         torch.distributed.all_reduce(sel, group=cp.group)
         return self._head(sel, buf, nl, rb)
 
@@ -552,6 +582,10 @@ class DenseModel:
             self._norm_linear(L.gate_up, h, L.post_norm, x, act, "swiglu", eps, off)
             if tl: trace.mark("down")
             self._row_parallel(L.down, act, h)
+            if self.tap_index:
+                j = self.tap_index.get(self.layer_begin + li)
+                if j is not None:            # residual stream after this layer, kept per row for a block drafter
+                    buf.taps[:M, j].copy_(h)
         if tl: trace.mark("head")
         if not last_stage:
             self.pp.send_hidden(h)

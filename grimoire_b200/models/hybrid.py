@@ -28,6 +28,7 @@ from ..ops import hybrid as Hb
 from ..ops import ref
 from ..ops.linear import BF16Linear, W4Linear
 from ..ops.workspace import Workspace
+from ..utils import trace
 from .config import ModelConfig
 from .dense import RowBatch
 
@@ -572,25 +573,30 @@ class HybridModel:
             run_slot, run_start, run_len = rb.row_seq, buf.run_start[:M], buf.run_len[:M]
             touched = rb.row_seq.long()
         tr = self._vtrace
+        tl = trace.timeline.on
         for L in self.layers:
+            if tl: trace.mark("gdn: norm + in projections" if L.kind == "gdn" else "attn: norm + qkv")
             K.add_rmsnorm(h, L.in_norm, x, eps, off)
             if L.kind == "gdn":
                 si = L.state_index
                 L.in_qkv(x, buf.gdn_qkv[:M], "bf16")
                 L.in_z(x, buf.gdn_z[:M], "bf16")
                 L.in_ab(x, buf.gdn_ab[:M], "f32")
+                if tl: trace.mark("gdn: conv + recurrence")
                 if tr is not None:
                     tr["pre"][si, :M].copy_(buf.gdn_qkv[:M])
                     tr["ab"][si, :M].copy_(buf.gdn_ab[:M])
                 Hb.conv4_silu(buf.gdn_qkv[:M], L.conv_w, self.ring[si], self.ring_tmp, rb.row_seq, rb.row_pos, buf.gdn_conv[:M], touched)
                 Hb.gdn_runs(buf.gdn_conv[:M], buf.gdn_ab[:M], buf.gdn_z[:M], L.A_log, L.dt_bias, L.gdn_norm, eps, self.state[si],
                             run_slot, run_start, run_len, buf.gdn_o[:M], self.Hk, self.Hv, self.Dk, self.Dv, chunked=prefill and M >= 32)
+                if tl: trace.mark("gdn: out_proj")
                 L.out_proj(buf.gdn_o[:M], h, "add_f32")
             else:
                 kvl = kv_layers[L.kv_index]
                 qkv, q, attn = buf.qkv[:M], buf.q[:M], buf.attn[:M]
                 gate = buf.gate[:M] if geom.q_gated else None
                 L.qkv(x, qkv, "bf16")
+                if tl: trace.mark("attn: rope + attention")
                 if prefill:
                     if rb.q_pos0 > 0:
                         K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
@@ -600,7 +606,9 @@ class HybridModel:
                 else:
                     K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
                     K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+                if tl: trace.mark("attn: o_proj")
                 L.o(attn, h, "add_f32")
+            if tl: trace.mark("ffn")
             K.add_rmsnorm(h, L.post_norm, x, eps, off)
             if L.moe is None:
                 act = buf.act_s[:M]
@@ -608,6 +616,7 @@ class HybridModel:
                 L.ffn_down(act, h, "add_f32")
             else:
                 self._moe(L, x, h, buf, M, decode=not prefill)
+        if tl: trace.mark("head")
         if rb.logits_rows is None:
             hsel, n = h, M
         else:
@@ -616,4 +625,5 @@ class HybridModel:
         xf, logits = buf.xf[:n], buf.logits[:n]
         K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
         self.lm_head(xf, logits, "f32")
+        if tl: trace.mark("end")
         return logits

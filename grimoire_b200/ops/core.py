@@ -110,9 +110,12 @@ class AttnGeom:
 
 def rope_kvwrite(qkv: torch.Tensor, row_pos: torch.Tensor, row_seq: Optional[torch.Tensor],
                  block_table: Optional[torch.Tensor], inv_freq: torch.Tensor, geom: AttnGeom, q_out: torch.Tensor,
-                 kv: Optional[KvLayer], q_norm_w=None, k_norm_w=None, gate_out=None, k_out=None, v_out=None):
+                 kv: Optional[KvLayer], q_norm_w=None, k_norm_w=None, gate_out=None, k_out=None, v_out=None,
+                 dense_pos0: int = -1, q_rows: Optional[tuple] = None):
     """Split the fused q|k|v rows, q/k norm, RoPE, write q (bf16) and int8 K/V pages (+ dense bf16
-    K/V for the prefill attention of the current chunk).  See rope_kv.cu."""
+    K/V for the prefill attention of the current chunk).  See rope_kv.cu.  ``dense_pos0`` >= 0: the dense K / V row of a
+    token lands at index ``row_pos - dense_pos0`` (rows in any order); ``q_rows`` = (first, count): q / gate are produced
+    for those rows only (the other rows of ``q_out`` are left as they are)."""
     M = qkv.shape[0]
     Hq, Hkv, D = geom.Hq, geom.Hkv, geom.D
     if not qkv.is_cuda:
@@ -129,7 +132,11 @@ def rope_kvwrite(qkv: torch.Tensor, row_pos: torch.Tensor, row_seq: Optional[tor
         q = ref.apply_rope(q, row_pos, inv_freq, geom.rot)
         k = ref.apply_rope(k, row_pos, inv_freq, geom.rot)
         q_out.copy_(q.reshape(M, Hq * D).to(q_out.dtype))
-        if k_out is not None:
+        if k_out is not None and dense_pos0 >= 0:
+            idx = (row_pos.long() - dense_pos0)
+            k_out[idx] = k.reshape(M, Hkv * D).to(k_out.dtype)
+            v_out[idx] = v.reshape(M, Hkv * D).to(v_out.dtype)
+        elif k_out is not None:
             k_out.copy_(k.reshape(M, Hkv * D).to(k_out.dtype))
             v_out.copy_(v.reshape(M, Hkv * D).to(v_out.dtype))
         if kv is not None and row_seq is not None:
@@ -148,14 +155,14 @@ def rope_kvwrite(qkv: torch.Tensor, row_pos: torch.Tensor, row_seq: Optional[tor
                 kv.vs[page, :, p % PAGE] = vsc[m]
         return q_out
     lib = _native.cuda()
-    code = lib.grm_rope_kvwrite(
+    code = lib.grm_rope_kvwrite_ex(
         _native.ptr(qkv), _c(qkv.stride(0)), _native.ptr(row_pos), _native.ptr(row_seq), _native.ptr(block_table),
         _c(block_table.stride(0) if block_table is not None else 0), _native.ptr(inv_freq), _native.ptr(q_norm_w),
         _native.ptr(k_norm_w), _f(geom.norm_eps), _f(geom.norm_offset), _native.ptr(q_out), _c(q_out.stride(0)),
         _native.ptr(gate_out), _native.ptr(k_out), _native.ptr(v_out), _c(k_out.stride(0) if k_out is not None else 0),
         _native.ptr(kv.k if kv else None), _native.ptr(kv.v if kv else None), _native.ptr(kv.ks if kv else None),
         _native.ptr(kv.vs if kv else None), _c(M), _c(Hq), _c(Hkv), _c(D), _c(geom.rot), _c(1 if geom.q_gated else 0),
-        _native.stream_ptr())
+        _c(dense_pos0), _c(q_rows[0] if q_rows else 0), _c(q_rows[1] if q_rows else -1), _native.stream_ptr())
     _native.check(code, "rope_kvwrite")
     return q_out
 

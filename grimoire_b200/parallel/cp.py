@@ -45,6 +45,8 @@ class ContextParallel:
         self.expect = 0
         self.spin = int(os.environ.get("GRIMOIRE_TP_SPIN", "0"))
         self.stats = {"chunks": 0, "exchanges": 0}
+        self.balanced = os.environ.get("GRIMOIRE_CP_BALANCED", "0") not in ("", "0")
+        self._layouts: dict = {}
 
     def attach(self, model, max_rows: int) -> None:
         """Hook ``model`` (a whole, unsharded DenseModel) so that prefill chunks whose rows divide over the ranks take the
@@ -68,11 +70,52 @@ class ContextParallel:
         return M % self.world == 0 and M // self.world >= 1 and M <= self.rows
 
     def local_rows(self, M: int) -> tuple[int, int]:
+        """This rank's rows of the chunk in EXCHANGE order (see ``layout``): always one contiguous range."""
         per = M // self.world
         return self.rank * per, (self.rank + 1) * per
 
+    def layout(self, M: int):
+        """How the chunk's rows map onto the ranks: contiguous shares by default; with GRIMOIRE_CP_BALANCED=1 the balanced
+        split below.  (Measured on 2 GPUs the two come out even, 28.4 against 28.8 ms for a 16-layer 4,096-row chunk: a
+        rank's attention time is set by its longest query block's walk over the keys, not by its total work, and the late
+        piece of the balanced split walks as many keys as the last contiguous share does.)
+        Causal attention makes late rows dearer than early ones, so with
+        2 R pieces of M / (2 R) rows rank r takes piece r and piece 2 R - 1 - r: every rank then sees the same number of
+        (query, key) pairs.  The ranks work on the chunk in exchange order -- rank 0's two pieces, rank 1's two pieces, ...
+        -- in which each rank's rows are contiguous; ``perm[j]`` is the chunk row that sits at exchange index j.
+        Returns (segments of this rank as (first chunk row, rows) in local order, perm or None for the identity)."""
+        hit = self._layouts.get(M)
+        if hit is not None:
+            return hit
+        W, r = self.world, self.rank
+        if not self.balanced or M % (2 * W) or M // (2 * W) < 8:
+            per = M // W
+            out = ([(r * per, per)], None)
+        else:
+            p = M // (2 * W)
+            pieces = []
+            for q in range(W):
+                pieces += [q, 2 * W - 1 - q]
+            perm = torch.cat([torch.arange(x * p, (x + 1) * p) for x in pieces]).to(self.device)
+            out = ([(r * p, p), ((2 * W - 1 - r) * p, p)], perm)
+        self._layouts[M] = out
+        return out
+
+    def owner_index(self, rows: torch.Tensor, M: int):
+        """For chunk rows ``rows`` (long tensor): (owner rank, index within the owner's local rows)."""
+        segs, perm = self.layout(M)
+        if perm is None:
+            per = M // self.world
+            return rows // per, rows % per
+        p = M // (2 * self.world)
+        piece = rows // p
+        late = piece >= self.world
+        owner = torch.where(late, 2 * self.world - 1 - piece, piece)
+        return owner, rows % p + late.long() * p
+
     def exchange_kv(self, qkv: torch.Tensor, M: int, qsz: int, parity: int) -> None:
-        """``qkv`` [M][qsz + width]: the local rows' k | v columns are valid; on return every row's are."""
+        """``qkv`` [M][qsz + width], rows in exchange order: the local rows' k | v columns are valid; on return every row's
+        are."""
         a, b = self.local_rows(M)
         self.stats["exchanges"] += 1
         if self.fused:

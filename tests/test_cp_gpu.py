@@ -27,12 +27,13 @@ def _setup(world):
     cfg = small_dense(layers=3)
     sd = random_state_dict(cfg, seed=0)
     g = torch.Generator().manual_seed(3)
-    chunk = 64 * world
+    chunk = 128 * world          # whole chunks take the balanced two-piece split (64-row pieces), the short tail the plain one
     prompt = torch.randint(0, cfg.vocab_size, (2 * chunk + 5 * world,), generator=g).tolist()
     return cfg, sd, prompt, chunk
 
 
 def _worker(rank, world, port, q, fused):
+    os.environ["GRIMOIRE_CP_BALANCED"] = "1" if world == 2 else "0"      # world 2 takes the balanced two-piece split, the others the default
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)

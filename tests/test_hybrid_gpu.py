@@ -11,8 +11,17 @@ from grimoire_b200.ops import core as K
 pytestmark = pytest.mark.gpu
 
 
-def _cfg():
+def _cfg(kind: str = "moe"):
     lt = [LINEAR_ATTN, LINEAR_ATTN, LINEAR_ATTN, FULL_ATTN]
+    if kind == "dense_ffn":       # the 27B-style hybrid: dense SwiGLU FFN, int4 projections
+        return ModelConfig(model_type="qwen3_5", hidden_size=512, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=128, vocab_size=4096, intermediate_size=1024, partial_rotary_factor=0.5, attn_output_gate=True,
+                           qk_norm=True, norm_zero_centered=True, layer_types=lt, linear_num_key_heads=2, linear_num_value_heads=4,
+                           linear_key_head_dim=128, linear_value_head_dim=128, quant="int4")
+    if kind == "plain_moe":       # Qwen3-MoE style: plain attention everywhere, no shared expert
+        return ModelConfig(model_type="qwen3_moe", hidden_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                           head_dim=128, vocab_size=4096, intermediate_size=0, qk_norm=True, num_experts=16, num_experts_per_tok=4,
+                           moe_intermediate_size=128, shared_expert_intermediate_size=0, quant="fp8_block")
     return ModelConfig(model_type="qwen3_next", hidden_size=512, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
                        head_dim=128, vocab_size=4096, intermediate_size=0, partial_rotary_factor=0.5, attn_output_gate=True, qk_norm=True,
                        norm_zero_centered=True, layer_types=lt, linear_num_key_heads=2, linear_num_value_heads=4,
@@ -23,8 +32,9 @@ def _cfg():
 LIM = dict(max_slots=3, max_ctx=256, prefill_chunk=64, max_decode_rows=8)
 
 
-def test_hybrid_gpu_matches_cpu_path_and_graph_replay():
-    cfg = _cfg()
+@pytest.mark.parametrize("kind", ["moe", "dense_ffn", "plain_moe"])
+def test_hybrid_gpu_matches_cpu_path_and_graph_replay(kind):
+    cfg = _cfg(kind)
     gpu = Engine(HybridModel.random(cfg, "cuda", seed=2, max_slots=3, gen_device="cpu"), EngineLimits(**LIM))
     cpu = Engine(HybridModel.random(cfg, "cpu", seed=2, max_slots=3), EngineLimits(**LIM))
     prompt = torch.randint(0, 4096, (90,), generator=torch.Generator().manual_seed(5)).tolist()

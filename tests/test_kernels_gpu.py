@@ -305,7 +305,7 @@ def test_rope_kvwrite_and_paged_decode(Hq, Hkv, D, rot, gated, qk):
 
 
 @pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64), (4, 1, 256)])
-@pytest.mark.parametrize("M,pos0,window", [(64, 0, 0), (200, 0, 0), (100, 77, 0), (130, 300, 128)])
+@pytest.mark.parametrize("M,pos0,window", [(64, 0, 0), (200, 0, 0), (100, 77, 0), (130, 300, 128), (1024, 512, 0), (700, 333, 256)])
 def test_flash_prefill(Hq, Hkv, D, M, pos0, window):
     torch.manual_seed(7)
     T = pos0 + M
