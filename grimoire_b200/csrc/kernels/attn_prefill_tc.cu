@@ -407,33 +407,40 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
 #pragma unroll
         for (int i = 0; i < 32; ++i) sv[32 + i] = __uint_as_float(r[i]);
       }
-      float mx = -INFINITY;
+      // The raw scores stay unscaled: the scale is positive, so the maximum commutes with it and the scaling rides in the
+      // multiply-add in front of each exp2.  Four independent maxima / sums keep the dependent chains short.
       const int key0 = kb * BKV;
       const bool need_mask = (key0 + BKV - 1 > first_q) || (p.window > 0) || !row_ok;
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < BKV; ++i) {
-        float sc = sv[i] * p.scale_log2;
-        if (need_mask) {
+        for (int i = 0; i < BKV; ++i) {
           const int kp = key0 + i;
           const bool vis = row_ok && kp <= q_pos && (p.window <= 0 || kp > q_pos - p.window);
-          sc = vis ? sc : -INFINITY;
+          sv[i] = vis ? sv[i] : -INFINITY;
         }
-        sv[i] = sc;
-        mx = fmaxf(mx, sc);
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < BKV; i += 4) {
+        mx4[0] = fmaxf(mx4[0], sv[i]); mx4[1] = fmaxf(mx4[1], sv[i + 1]);
+        mx4[2] = fmaxf(mx4[2], sv[i + 2]); mx4[3] = fmaxf(mx4[3], sv[i + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       const float m_new = fmaxf(m_run, mx);
       const float alpha = (m_new == -INFINITY) ? 1.f : ex2(m_run - m_new);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      float psum = 0.f;
+      const float m_neg = (m_new == -INFINITY) ? 0.f : -m_new;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[BKV / 2];
 #pragma unroll
-      for (int i = 0; i < BKV; i += 2) {
-        const float p0 = ex2(sv[i] - m_use), p1 = ex2(sv[i + 1] - m_use);
-        psum += p0 + p1;
+      for (int i = 0; i < BKV; i += 4) {
+        const float p0 = ex2(fmaf(sv[i], p.scale_log2, m_neg)), p1 = ex2(fmaf(sv[i + 1], p.scale_log2, m_neg));
+        const float p2 = ex2(fmaf(sv[i + 2], p.scale_log2, m_neg)), p3 = ex2(fmaf(sv[i + 3], p.scale_log2, m_neg));
+        ps4[0] += p0; ps4[1] += p1; ps4[2] += p2; ps4[3] += p3;
         pk[i >> 1] = pack_bf16x2(p0, p1);
+        pk[(i >> 1) + 1] = pack_bf16x2(p2, p3);
       }
       m_run = m_new;
-      l_run = l_run * alpha + psum;
+      l_run = l_run * alpha + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
       // PV(j-1) must have finished before O is rescaled and P is overwritten
       if (j > 0) {
         if (!mbar_wait(&bars[6], (uint32_t)(j - 1) & 1u, p.status, 0x804u)) { ok = false; break; }

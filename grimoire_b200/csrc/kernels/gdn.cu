@@ -368,6 +368,281 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_kernel(const GdnChu
     reinterpret_cast<float4*>(sp)[4 * i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The chunked form with its matrix products on the tensor cores (mma.sync m16n8k8, tf32 operands, fp32 accumulation): the
+// default.  Same algebra, same CTA = (run, v head, 32 Dv rows), 4 warps.  Per 64-token chunk
+//   P = K S_0^T, R = Q S_0^T      [t][dv]  warp w owns token rows 16 w .. 16 w + 15; S_0 is read from a shared-memory copy
+//   K K^T, Q K^T                  [t][j]   same rows, only the 8-column tiles at or below the diagonal; shares the K / Q
+//                                          fragments of the first product (one pass over k)
+//   forward substitution for U    (scalar, a quad per dv column, as in the fp32 kernel)
+//   O^T = U^T M^T                 [dv][t]  warp w owns token tiles w and 7 - w (balanced under the causal cut)
+//   S = gamma_C S_0 + (E U)^T K   [dv][k]  the state lives in the accumulator registers of this product across the run:
+//                                          warp w owns k in [32 w, 32 w + 32)
+// Shared memory: K and Q tiles (tf32-rounded at staging), L and M where Q was, the S_0 copy where V and U are staged
+// afterwards -- 105 KB, two CTAs per SM.  Operand rounding is tf32 (10-bit mantissa; the reference's chunk kernel uses
+// bf16 operands, src/gemm_fast.cpp:3021-3362); the state and every accumulation stay fp32.
+// ---------------------------------------------------------------------------------------------
+constexpr int PL = CH;             // row pitch of L (read by quads that share a row: no padding needed)
+constexpr int PM = CH + 4;         // row pitch of M (read as an MMA B operand: 8 rows x 4 columns hit 32 banks)
+static_assert(CH * PL + CH * PM <= CH * LDK, "L and M must fit in the Q tile");
+static_assert(DVL * LDK <= CH * DVL + CH * UP, "the S_0 copy must fit where V and U are staged");
+
+__device__ __forceinline__ uint32_t tf32r(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32r(x)); }
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const GdnChunkParams p) {
+  extern __shared__ __align__(16) float smc[];
+  float* Ks = smc;                          // [CH][LDK]  tf32-rounded, L2-normalised k rows
+  float* Qs = Ks + CH * LDK;                // [CH][LDK]  same for q; dead after the first pass over k
+  float* Lm = Qs;                           // [CH][PL]
+  float* Mm = Lm + CH * PL;                 // [CH][PM]
+  float* Vs = Qs + CH * LDK;                // [CH][DVL]
+  float* Us = Vs + CH * DVL;                // [CH][UP]
+  float* Ss = Vs;                           // [DVL][LDK] copy of S_0 for the first pass (V and U are staged after it)
+  float* Ps = Us + CH * UP;                 // [CH][UP]  K S_0^T
+  float* Rs = Ps + CH * UP;                 // [CH][UP]  Q S_0^T
+  float* Gs = Rs + CH * UP;                 // [CH] cumulative log decay
+  float* Bs = Gs + CH;                      // [CH] beta
+  float* Es = Bs + CH;                      // [CH] gamma_C / gamma_j
+  const int run = blockIdx.x, vh = blockIdx.y, dvs = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;               // MMA fragment coordinates
+  const int dvl = tid >> 2, part = tid & 3;             // substitution: thread = (dv column, quarter of the j range)
+  const int slot = p.run_slot[run], r0 = p.run_start[run], n = p.run_len[run];
+  const int kh = vh / (p.Hv / p.Hk);
+  // state tile (m = dv tile mt, n = k tile 4 warp + ntl) in accumulator layout: [0],[1] = (dv 16 mt + g, k 8 nt + 2 t4 (+1)),
+  // [2],[3] = the same columns of row dv + 8
+  float Sr[2][4][4];
+  float* sbase = p.state + (((size_t)slot * p.Hv + vh) * D + (size_t)dvs * DVL) * D;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ntl = 0; ntl < 4; ++ntl) {
+      const int k = 8 * (4 * warp + ntl) + 2 * t4;
+      const float2 lo = *reinterpret_cast<const float2*>(sbase + (size_t)(16 * mt + g) * D + k);
+      const float2 hi = *reinterpret_cast<const float2*>(sbase + (size_t)(16 * mt + g + 8) * D + k);
+      Sr[mt][ntl][0] = lo.x; Sr[mt][ntl][1] = lo.y; Sr[mt][ntl][2] = hi.x; Sr[mt][ntl][3] = hi.y;
+    }
+  const float neg_expA = -__expf(p.A_log[vh]);
+  const float dtb = p.dt_bias[vh];
+  const float inv_sqrt_d = rsqrtf((float)D);
+  const int qoff = kh * D, koff = p.Hk * D + kh * D, voff = 2 * p.Hk * D + vh * D + dvs * DVL;
+
+  for (int c0 = 0; c0 < n; c0 += CH) {
+    const int nc = min(CH, n - c0);
+    __syncthreads();
+    // ---- stage: L2-normalised q / k rows (a warp per token), gates, and the S_0 copy ----
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint2 qa[8], ka[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = warp + 4 * (half * 8 + i);
+        qa[i] = ka[i] = make_uint2(0u, 0u);
+        if (t < nc) {
+          const bf16* xr = p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv;
+          qa[i] = *reinterpret_cast<const uint2*>(xr + qoff + lane * 4);
+          ka[i] = *reinterpret_cast<const uint2*>(xr + koff + lane * 4);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int t = warp + 4 * (half * 8 + i);
+        const float4 qv = make_float4(bf16lo_to_f(qa[i].x), bf16hi_to_f(qa[i].x), bf16lo_to_f(qa[i].y), bf16hi_to_f(qa[i].y));
+        const float4 kv = make_float4(bf16lo_to_f(ka[i].x), bf16hi_to_f(ka[i].x), bf16lo_to_f(ka[i].y), bf16hi_to_f(ka[i].y));
+        const float qs = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+        const float ks = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+        const float qr = t < nc ? rsqrtf(qs + 1e-6f) : 0.f, kr = t < nc ? rsqrtf(ks + 1e-6f) : 0.f;
+        *reinterpret_cast<float4*>(Qs + t * LDK + lane * 4) = make_float4(tf32f(qv.x * qr), tf32f(qv.y * qr), tf32f(qv.z * qr), tf32f(qv.w * qr));
+        *reinterpret_cast<float4*>(Ks + t * LDK + lane * 4) = make_float4(tf32f(kv.x * kr), tf32f(kv.y * kr), tf32f(kv.z * kr), tf32f(kv.w * kr));
+      }
+    }
+    if (tid < CH) {
+      float la = 0.f, be = 0.f;
+      if (tid < nc) {
+        const size_t row = (size_t)(r0 + c0 + tid);
+        const float xs = p.ab[row * p.ld_ab + vh] + dtb;
+        const float spl = xs > 20.f ? xs : log1pf(__expf(xs));
+        la = neg_expA * spl;
+        be = sigmoid_f(p.ab[row * p.ld_ab + p.Hv + vh]);
+      }
+      Gs[tid] = la; Bs[tid] = be;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int ntl = 0; ntl < 4; ++ntl) {
+        const int k = 8 * (4 * warp + ntl) + 2 * t4;
+        *reinterpret_cast<float2*>(Ss + (16 * mt + g) * LDK + k) = make_float2(tf32f(Sr[mt][ntl][0]), tf32f(Sr[mt][ntl][1]));
+        *reinterpret_cast<float2*>(Ss + (16 * mt + g + 8) * LDK + k) = make_float2(tf32f(Sr[mt][ntl][2]), tf32f(Sr[mt][ntl][3]));
+      }
+    __syncthreads();
+    if (tid == 0) {
+      float acc = 0.f;
+      for (int t = 0; t < CH; ++t) { acc += Gs[t]; Gs[t] = acc; }
+    }
+    // ---- one pass over k: P, R (against S_0) and K K^T, Q K^T (tiles at or below the diagonal) for token rows 16 warp .. ----
+    float accP[4][4], accR[4][4], akk[8][4], aqk[8][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { accP[i][j] = 0.f; accR[i][j] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { akk[i][j] = 0.f; aqk[i][j] = 0.f; }
+    const int nt_hi = 2 * warp + 1;                       // last 8-column tile this warp's rows can see
+    {
+      const float* ka0 = Ks + (16 * warp + g) * LDK + t4;
+      const float* qa0 = Qs + (16 * warp + g) * LDK + t4;
+#pragma unroll 2
+      for (int ks = 0; ks < D / 8; ++ks) {
+        const int k0 = 8 * ks;
+        uint32_t aK[4], aQ[4];
+        aK[0] = __float_as_uint(ka0[k0]); aK[1] = __float_as_uint(ka0[8 * LDK + k0]);
+        aK[2] = __float_as_uint(ka0[k0 + 4]); aK[3] = __float_as_uint(ka0[8 * LDK + k0 + 4]);
+        aQ[0] = __float_as_uint(qa0[k0]); aQ[1] = __float_as_uint(qa0[8 * LDK + k0]);
+        aQ[2] = __float_as_uint(qa0[k0 + 4]); aQ[3] = __float_as_uint(qa0[8 * LDK + k0 + 4]);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const float* sb = Ss + (8 * nt + g) * LDK + k0 + t4;
+          const uint32_t b0 = __float_as_uint(sb[0]), b1 = __float_as_uint(sb[4]);
+          mma_tf32(accP[nt], aK, b0, b1);
+          mma_tf32(accR[nt], aQ, b0, b1);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          if (nt <= nt_hi) {
+            const float* kb = Ks + (8 * nt + g) * LDK + k0 + t4;
+            const uint32_t b0 = __float_as_uint(kb[0]), b1 = __float_as_uint(kb[4]);
+            mma_tf32(akk[nt], aK, b0, b1);
+            mma_tf32(aqk[nt], aQ, b0, b1);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int ra = 16 * warp + g, dc = 8 * nt + 2 * t4;
+      *reinterpret_cast<float2*>(Ps + ra * UP + dc) = make_float2(accP[nt][0], accP[nt][1]);
+      *reinterpret_cast<float2*>(Ps + (ra + 8) * UP + dc) = make_float2(accP[nt][2], accP[nt][3]);
+      *reinterpret_cast<float2*>(Rs + ra * UP + dc) = make_float2(accR[nt][0], accR[nt][1]);
+      *reinterpret_cast<float2*>(Rs + (ra + 8) * UP + dc) = make_float2(accR[nt][2], accR[nt][3]);
+    }
+    __syncthreads();                                       // Gs complete; Q tile and the S_0 copy are dead
+    // ---- L, M into the Q tile; V slice and gamma_C / gamma_j into their places ----
+    {
+      const int ra = 16 * warp + g, rb = ra + 8;
+      const float ga = Gs[ra], gb = Gs[rb], ba = Bs[ra], bb = Bs[rb];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        if (nt <= nt_hi) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = 8 * nt + 2 * t4 + e;
+            const float gc = Gs[col];
+            const float rta = col <= ra ? __expf(ga - gc) : 0.f, rtb = col <= rb ? __expf(gb - gc) : 0.f;
+            Lm[ra * PL + col] = col < ra ? ba * rta * akk[nt][e] : 0.f;
+            Lm[rb * PL + col] = col < rb ? bb * rtb * akk[nt][2 + e] : 0.f;
+            Mm[ra * PM + col] = tf32f(rta * aqk[nt][e]);
+            Mm[rb * PM + col] = tf32f(rtb * aqk[nt][2 + e]);
+          }
+        }
+      }
+    }
+    for (int i = tid; i < CH * DVL; i += kChThreads) {
+      const int t = i / DVL, d = i - t * DVL;
+      Vs[i] = t < nc ? __bfloat162float(p.qkv[(size_t)(r0 + c0 + t) * p.ld_qkv + voff + d]) : 0.f;
+    }
+    const float gC = Gs[CH - 1];
+    if (tid < CH) Es[tid] = __expf(gC - Gs[tid]);
+    __syncthreads();
+    // ---- forward substitution for this dv column of U; the four threads of a quad split the sum over j ----
+#pragma unroll 1
+    for (int t = 0; t < CH; ++t) {
+      float sacc = 0.f;
+      for (int j = part; j < t; j += 4) sacc = fmaf(Lm[t * PL + j], Us[j * UP + dvl], sacc);
+      sacc += __shfl_xor_sync(0xffffffffu, sacc, 1); sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
+      if (part == 0) Us[t * UP + dvl] = Bs[t] * (Vs[t * DVL + dvl] - __expf(Gs[t]) * Ps[t * UP + dvl]) - sacc;
+      __syncwarp();
+    }
+    __syncthreads();                                       // every dv column of U is in place
+    // ---- outputs: O^T[dv][t] = sum_{j <= t} U[j][dv] M[t][j] for token tiles `warp` and 7 - warp ----
+#pragma unroll
+    for (int side = 0; side < 2; ++side) {
+      const int nt = side ? 7 - warp : warp;
+      float acc[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[mt][j] = 0.f;
+      for (int ks = 0; ks <= nt; ++ks) {
+        const int j0 = 8 * ks;
+        const float* mb = Mm + (8 * nt + g) * PM + j0 + t4;
+        const uint32_t b0 = __float_as_uint(mb[0]), b1 = __float_as_uint(mb[4]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          const float* ua = Us + (j0 + t4) * UP + 16 * mt + g;
+          uint32_t a[4];
+          a[0] = tf32r(ua[0]); a[1] = tf32r(ua[8]); a[2] = tf32r(ua[4 * UP]); a[3] = tf32r(ua[4 * UP + 8]);
+          mma_tf32(acc[mt], a, b0, b1);
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int dvr = 16 * mt + g + ((e & 2) ? 8 : 0), t = 8 * nt + 2 * t4 + (e & 1);
+          if (t < nc)
+            p.o_raw[(size_t)(r0 + c0 + t) * p.ld_o + vh * D + dvs * DVL + dvr] = (__expf(Gs[t]) * Rs[t * UP + dvr] + acc[mt][e]) * inv_sqrt_d;
+        }
+    }
+    // ---- state: S = gamma_C S + sum_j (gamma_C / gamma_j) u_j k_j^T for this warp's k range ----
+    const float gamC = __expf(gC);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int ntl = 0; ntl < 4; ++ntl)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) Sr[mt][ntl][e] *= gamC;
+#pragma unroll 2
+    for (int ks = 0; ks < CH / 8; ++ks) {
+      const int j0 = 8 * ks;
+      const float e0 = Es[j0 + t4], e1 = Es[j0 + t4 + 4];
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const float* ua = Us + (j0 + t4) * UP + 16 * mt + g;
+        a[mt][0] = tf32r(e0 * ua[0]); a[mt][1] = tf32r(e0 * ua[8]); a[mt][2] = tf32r(e1 * ua[4 * UP]); a[mt][3] = tf32r(e1 * ua[4 * UP + 8]);
+      }
+#pragma unroll
+      for (int ntl = 0; ntl < 4; ++ntl) {
+        const float* kb = Ks + (j0 + t4) * LDK + 8 * (4 * warp + ntl) + g;
+        const uint32_t b0 = __float_as_uint(kb[0]), b1 = __float_as_uint(kb[4 * LDK]);
+        mma_tf32(Sr[0][ntl], a[0], b0, b1);
+        mma_tf32(Sr[1][ntl], a[1], b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int ntl = 0; ntl < 4; ++ntl) {
+      const int k = 8 * (4 * warp + ntl) + 2 * t4;
+      *reinterpret_cast<float2*>(sbase + (size_t)(16 * mt + g) * D + k) = make_float2(Sr[mt][ntl][0], Sr[mt][ntl][1]);
+      *reinterpret_cast<float2*>(sbase + (size_t)(16 * mt + g + 8) * D + k) = make_float2(Sr[mt][ntl][2], Sr[mt][ntl][3]);
+    }
+}
+
 // out = rms_norm(o_raw) * w * silu(z) per (row, v head)
 __global__ void __launch_bounds__(128) gdn_gated_norm_kernel(const float* __restrict__ o_raw, int ld_o, const bf16* __restrict__ z, int ld_z,
                                                              const float* __restrict__ w, float eps, bf16* __restrict__ out, int ld_out) {
@@ -433,7 +708,19 @@ GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  gdn_chunked_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem, st>>>(p);
+  static int use_mma = -1;
+  if (use_mma < 0) {
+    const char* ev = getenv("GRIMOIRE_GDN_MMA");
+    use_mma = (ev && ev[0] == '0') ? 0 : 1;
+    if (use_mma && cudaFuncSetAttribute(gdn_chunked_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024) != cudaSuccess)
+      use_mma = 0;
+  }
+  if (use_mma) {
+    const size_t smem_mma = solo ? smem : sizeof(float) * (2 * CH * LDK + CH * DVL + 3 * CH * UP + 3 * CH);
+    gdn_chunked_mma_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem_mma, st>>>(p);
+  } else {
+    gdn_chunked_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem, st>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   gdn_gated_norm_kernel<<<dim3(M, Hv), 128, 0, st>>>((const float*)o_raw, Hv * D, (const bf16*)z, ld_z, (const float*)norm_w, norm_eps,
