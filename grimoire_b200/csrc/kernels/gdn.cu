@@ -198,6 +198,7 @@ struct GdnChunkParams {
   const int* run_slot; const int* run_start; const int* run_len;
   float* o_raw; int ld_o;          // fp32 [M][Hv*Dv], un-normalised outputs
   int Hk, Hv;
+  long long* tl;                   // debug: clock64 stamps of CTA (0, 0, 0), 8 per chunk (null: off)
 };
 
 static_assert(2 * CH * (CH + 1) <= CH * LDK, "L and M must fit in the Q tile");
@@ -379,12 +380,12 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_kernel(const GdnChu
 //   S = gamma_C S_0 + (E U)^T K   [dv][k]  the state lives in the accumulator registers of this product across the run:
 //                                          warp w owns k in [32 w, 32 w + 32)
 // Shared memory: K and Q tiles (tf32-rounded at staging), L and M where Q was, the S_0 copy where V and U are staged
-// afterwards -- 105 KB, two CTAs per SM.  Operand rounding is tf32 (10-bit mantissa; the reference's chunk kernel uses
+// afterwards -- 106 KB, two CTAs per SM.  Operand rounding is tf32 (10-bit mantissa; the reference's chunk kernel uses
 // bf16 operands, src/gemm_fast.cpp:3021-3362); the state and every accumulation stay fp32.
 // ---------------------------------------------------------------------------------------------
-constexpr int PL = CH;             // row pitch of L (read by quads that share a row: no padding needed)
-constexpr int PM = CH + 4;         // row pitch of M (read as an MMA B operand: 8 rows x 4 columns hit 32 banks)
-static_assert(CH * PL + CH * PM <= CH * LDK, "L and M must fit in the Q tile");
+constexpr int PL = CH + 4;         // row pitch of L and of M: both are read as MMA operands (8 rows x 4 columns hit 32 banks)
+constexpr int PM = CH + 4;
+constexpr int QREG = (CH * PL + CH * PM > CH * LDK) ? (CH * PL + CH * PM) : (CH * LDK);      // the Q tile, then L and M
 static_assert(DVL * LDK <= CH * DVL + CH * UP, "the S_0 copy must fit where V and U are staged");
 
 __device__ __forceinline__ uint32_t tf32r(float x) {
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
   float* Qs = Ks + CH * LDK;                // [CH][LDK]  same for q; dead after the first pass over k
   float* Lm = Qs;                           // [CH][PL]
   float* Mm = Lm + CH * PL;                 // [CH][PM]
-  float* Vs = Qs + CH * LDK;                // [CH][DVL]
+  float* Vs = Qs + QREG;                    // [CH][DVL]
   float* Us = Vs + CH * DVL;                // [CH][UP]
   float* Ss = Vs;                           // [DVL][LDK] copy of S_0 for the first pass (V and U are staged after it)
   float* Ps = Us + CH * UP;                 // [CH][UP]  K S_0^T
@@ -413,6 +414,7 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
   float* Gs = Rs + CH * UP;                 // [CH] cumulative log decay
   float* Bs = Gs + CH;                      // [CH] beta
   float* Es = Bs + CH;                      // [CH] gamma_C / gamma_j
+  bf16* Vh = reinterpret_cast<bf16*>(Es + CH);   // [CH][DVL] this CTA's v slice as loaded (read once, by the substitution's right side)
   const int run = blockIdx.x, vh = blockIdx.y, dvs = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;               // MMA fragment coordinates
@@ -437,33 +439,69 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
   const float inv_sqrt_d = rsqrtf((float)D);
   const int qoff = kh * D, koff = p.Hk * D + kh * D, voff = 2 * p.Hk * D + vh * D + dvs * DVL;
 
+  const bool stamp = p.tl != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 32;
   for (int c0 = 0; c0 < n; c0 += CH) {
     const int nc = min(CH, n - c0);
+    long long* tlc = p.tl + (c0 / CH) * 8;
     __syncthreads();
-    // ---- stage: L2-normalised q / k rows (a warp per token), gates, and the S_0 copy ----
+    if (stamp) tlc[0] = clock64();
+    // ---- stage: every global load of the chunk is issued before the first use (v slice, q / k rows); then the
+    //      L2-normalised q / k rows (a thread per row), gates, and the S_0 copy ----
+    {
+      uint2 vv[4];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint2 qa[8], ka[8];
+      for (int r = 0; r < 4; ++r) {
+        const int t = (tid >> 3) + 16 * r;
+        vv[r] = make_uint2(0u, 0u);
+        if (t < nc) vv[r] = *reinterpret_cast<const uint2*>(p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv + voff + (tid & 7) * 4);
+      }
+      // q / k rows: a thread owns one whole row (threads 0-63: q of token tid, 64-127: k of token tid - 64), so the sum of
+      // squares needs no shuffles and the 16-byte stores of eight neighbouring tokens fall into 32 different banks
+      uint4 rw[16];
+      const int tok = tid & 63;
+      {
+        const bf16* xr = p.qkv + (size_t)(r0 + c0 + tok) * p.ld_qkv + (tid < 64 ? qoff : koff);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int t = warp + 4 * (half * 8 + i);
-        qa[i] = ka[i] = make_uint2(0u, 0u);
-        if (t < nc) {
-          const bf16* xr = p.qkv + (size_t)(r0 + c0 + t) * p.ld_qkv;
-          qa[i] = *reinterpret_cast<const uint2*>(xr + qoff + lane * 4);
-          ka[i] = *reinterpret_cast<const uint2*>(xr + koff + lane * 4);
+        for (int i = 0; i < 16; ++i) rw[i] = tok < nc ? *reinterpret_cast<const uint4*>(xr + 8 * i) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      // the next chunk's rows are asked into L2 now, a whole chunk of compute ahead of their use
+      if (c0 + CH < n) {
+        const int nn = min(CH, n - c0 - CH);
+        if (lane < 4) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int t = warp + 4 * i;
+            if (t < nn) {
+              const bf16* xr = p.qkv + (size_t)(r0 + c0 + CH + t) * p.ld_qkv + ((lane & 2) ? koff : qoff) + (lane & 1) * 64;
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(xr));
+            }
+          }
+        }
+        if (tid < nn) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.qkv + (size_t)(r0 + c0 + CH + tid) * p.ld_qkv + voff));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.ab + (size_t)(r0 + c0 + CH + tid) * p.ld_ab + vh));
         }
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int t = warp + 4 * (half * 8 + i);
-        const float4 qv = make_float4(bf16lo_to_f(qa[i].x), bf16hi_to_f(qa[i].x), bf16lo_to_f(qa[i].y), bf16hi_to_f(qa[i].y));
-        const float4 kv = make_float4(bf16lo_to_f(ka[i].x), bf16hi_to_f(ka[i].x), bf16lo_to_f(ka[i].y), bf16hi_to_f(ka[i].y));
-        const float qs = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
-        const float ks = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
-        const float qr = t < nc ? rsqrtf(qs + 1e-6f) : 0.f, kr = t < nc ? rsqrtf(ks + 1e-6f) : 0.f;
-        *reinterpret_cast<float4*>(Qs + t * LDK + lane * 4) = make_float4(tf32f(qv.x * qr), tf32f(qv.y * qr), tf32f(qv.z * qr), tf32f(qv.w * qr));
-        *reinterpret_cast<float4*>(Ks + t * LDK + lane * 4) = make_float4(tf32f(kv.x * kr), tf32f(kv.y * kr), tf32f(kv.z * kr), tf32f(kv.w * kr));
+      for (int r = 0; r < 4; ++r) *reinterpret_cast<uint2*>(Vh + ((tid >> 3) + 16 * r) * DVL + (tid & 7) * 4) = vv[r];
+      {
+        float ss0 = 0.f, ss1 = 0.f, ss2 = 0.f, ss3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float x0 = bf16lo_to_f(rw[i].x), x1 = bf16hi_to_f(rw[i].x), x2 = bf16lo_to_f(rw[i].y), x3 = bf16hi_to_f(rw[i].y);
+          const float x4 = bf16lo_to_f(rw[i].z), x5 = bf16hi_to_f(rw[i].z), x6 = bf16lo_to_f(rw[i].w), x7 = bf16hi_to_f(rw[i].w);
+          ss0 = fmaf(x0, x0, fmaf(x4, x4, ss0)); ss1 = fmaf(x1, x1, fmaf(x5, x5, ss1));
+          ss2 = fmaf(x2, x2, fmaf(x6, x6, ss2)); ss3 = fmaf(x3, x3, fmaf(x7, x7, ss3));
+        }
+        const float rn = tok < nc ? rsqrtf((ss0 + ss1) + (ss2 + ss3) + 1e-6f) : 0.f;
+        float* dst = (tid < 64 ? Qs : Ks) + tok * LDK;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          *reinterpret_cast<float4*>(dst + 8 * i) = make_float4(tf32f(bf16lo_to_f(rw[i].x) * rn), tf32f(bf16hi_to_f(rw[i].x) * rn),
+                                                                tf32f(bf16lo_to_f(rw[i].y) * rn), tf32f(bf16hi_to_f(rw[i].y) * rn));
+          *reinterpret_cast<float4*>(dst + 8 * i + 4) = make_float4(tf32f(bf16lo_to_f(rw[i].z) * rn), tf32f(bf16hi_to_f(rw[i].z) * rn),
+                                                                    tf32f(bf16lo_to_f(rw[i].w) * rn), tf32f(bf16hi_to_f(rw[i].w) * rn));
+        }
       }
     }
     if (tid < CH) {
@@ -486,6 +524,7 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
         *reinterpret_cast<float2*>(Ss + (16 * mt + g + 8) * LDK + k) = make_float2(tf32f(Sr[mt][ntl][2]), tf32f(Sr[mt][ntl][3]));
       }
     __syncthreads();
+    if (stamp) tlc[1] = clock64();
     if (tid == 0) {
       float acc = 0.f;
       for (int t = 0; t < CH; ++t) { acc += Gs[t]; Gs[t] = acc; }
@@ -538,8 +577,10 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
       *reinterpret_cast<float2*>(Rs + ra * UP + dc) = make_float2(accR[nt][0], accR[nt][1]);
       *reinterpret_cast<float2*>(Rs + (ra + 8) * UP + dc) = make_float2(accR[nt][2], accR[nt][3]);
     }
+    if (stamp) tlc[2] = clock64();
     __syncthreads();                                       // Gs complete; Q tile and the S_0 copy are dead
-    // ---- L, M into the Q tile; V slice and gamma_C / gamma_j into their places ----
+    if (stamp) tlc[3] = clock64();
+    // ---- L, M into the Q tile; gamma_C / gamma_j ----
     {
       const int ra = 16 * warp + g, rb = ra + 8;
       const float ga = Gs[ra], gb = Gs[rb], ba = Bs[ra], bb = Bs[rb];
@@ -559,23 +600,85 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
         }
       }
     }
-    for (int i = tid; i < CH * DVL; i += kChThreads) {
-      const int t = i / DVL, d = i - t * DVL;
-      Vs[i] = t < nc ? __bfloat162float(p.qkv[(size_t)(r0 + c0 + t) * p.ld_qkv + voff + d]) : 0.f;
-    }
     const float gC = Gs[CH - 1];
     if (tid < CH) Es[tid] = __expf(gC - Gs[tid]);
     __syncthreads();
-    // ---- forward substitution for this dv column of U; the four threads of a quad split the sum over j ----
+    if (stamp) tlc[4] = clock64();
+    // ---- (I + L) U = rhs, in place in Us, in four blocks of 16 rows.
+    //      (a) every warp inverts one 16 x 16 diagonal block exactly (fp32 forward substitution on the matrix: a lane owns
+    //          a column of the inverse in registers, the L entries are shared-memory broadcasts, no shuffles) and writes
+    //          the inverse over the block; the right side rhs_t = beta_t (v_t - gamma_t p_t) goes into Us meanwhile;
+    //      (b) a warp then solves its own 8 dv columns block by block with two small tensor-core products per block,
+    //          rhs_b - L_b,<b U_<b and T_bb times that, each as three tf32 products of split operands (fp32 accuracy).
+    //      The 64 dependent steps of a plain substitution become 16 + 4. ----
+    for (int t = part; t < CH; t += 4) Us[t * UP + dvl] = Bs[t] * (__bfloat162float(Vh[t * DVL + dvl]) - __expf(Gs[t]) * Ps[t * UP + dvl]);
+    {
+      const int col = lane & 15;
+      const float* lb = Lm + (16 * warp) * PL + 16 * warp;
+      float Tc[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float a0 = (i == col) ? 1.f : 0.f, a1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) {
+          if (j & 1) a1 = fmaf(-lb[i * PL + j], Tc[j], a1);
+          else a0 = fmaf(-lb[i * PL + j], Tc[j], a0);
+        }
+        Tc[i] = a0 + a1;
+      }
+      __syncwarp();                                        // every lane has read the block before it is overwritten
+      if (lane < 16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) Lm[(16 * warp + i) * PL + 16 * warp + col] = Tc[i];
+      }
+    }
+    __syncthreads();                                       // the four inverses and the right sides are in place
 #pragma unroll 1
-    for (int t = 0; t < CH; ++t) {
-      float sacc = 0.f;
-      for (int j = part; j < t; j += 4) sacc = fmaf(Lm[t * PL + j], Us[j * UP + dvl], sacc);
-      sacc += __shfl_xor_sync(0xffffffffu, sacc, 1); sacc += __shfl_xor_sync(0xffffffffu, sacc, 2);
-      if (part == 0) Us[t * UP + dvl] = Bs[t] * (Vs[t * DVL + dvl] - __expf(Gs[t]) * Ps[t * UP + dvl]) - sacc;
+    for (int blk = 0; blk < CH / 16; ++blk) {
+      float* ur = Us + (16 * blk + g) * UP + 8 * warp + 2 * t4;
+      float c[4] = {ur[0], ur[1], ur[8 * UP], ur[8 * UP + 1]};
+      const float* la = Lm + (16 * blk + g) * PL + t4;
+      for (int ks = 0; ks < 2 * blk; ++ks) {               // c -= L[block rows][earlier rows] U[earlier rows]
+        const int j0 = 8 * ks;
+        const float av[4] = {-la[j0], -la[8 * PL + j0], -la[j0 + 4], -la[8 * PL + j0 + 4]};
+        const float* ub = Us + (j0 + t4) * UP + 8 * warp + g;
+        const float bv0 = ub[0], bv1 = ub[4 * UP];
+        uint32_t ah[4], al[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { ah[e] = tf32r(av[e]); al[e] = tf32r(av[e] - __uint_as_float(ah[e])); }
+        const uint32_t bh0 = tf32r(bv0), bh1 = tf32r(bv1);
+        const uint32_t bl0 = tf32r(bv0 - __uint_as_float(bh0)), bl1 = tf32r(bv1 - __uint_as_float(bh1));
+        mma_tf32(c, al, bh0, bh1);
+        mma_tf32(c, ah, bl0, bl1);
+        mma_tf32(c, ah, bh0, bh1);
+      }
+      __syncwarp();
+      ur[0] = c[0]; ur[1] = c[1]; ur[8 * UP] = c[2]; ur[8 * UP + 1] = c[3];
+      __syncwarp();
+      float u[4] = {0.f, 0.f, 0.f, 0.f};
+      const float* ta = Lm + (16 * blk + g) * PL + 16 * blk + t4;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {                     // U_b = T_bb (that)
+        const int j0 = 8 * ks;
+        const float av[4] = {ta[j0], ta[8 * PL + j0], ta[j0 + 4], ta[8 * PL + j0 + 4]};
+        const float* ub = Us + (16 * blk + j0 + t4) * UP + 8 * warp + g;
+        const float bv0 = ub[0], bv1 = ub[4 * UP];
+        uint32_t ah[4], al[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { ah[e] = tf32r(av[e]); al[e] = tf32r(av[e] - __uint_as_float(ah[e])); }
+        const uint32_t bh0 = tf32r(bv0), bh1 = tf32r(bv1);
+        const uint32_t bl0 = tf32r(bv0 - __uint_as_float(bh0)), bl1 = tf32r(bv1 - __uint_as_float(bh1));
+        mma_tf32(u, al, bh0, bh1);
+        mma_tf32(u, ah, bl0, bl1);
+        mma_tf32(u, ah, bh0, bh1);
+      }
+      __syncwarp();                                        // every lane has read the block's right side
+      ur[0] = u[0]; ur[1] = u[1]; ur[8 * UP] = u[2]; ur[8 * UP + 1] = u[3];
       __syncwarp();
     }
+    if (stamp) tlc[5] = clock64();
     __syncthreads();                                       // every dv column of U is in place
+    if (stamp) tlc[6] = clock64();
     // ---- outputs: O^T[dv][t] = sum_{j <= t} U[j][dv] M[t][j] for token tiles `warp` and 7 - warp ----
 #pragma unroll
     for (int side = 0; side < 2; ++side) {
@@ -606,6 +709,7 @@ __global__ void __launch_bounds__(kChThreads, 2) gdn_chunked_mma_kernel(const Gd
             p.o_raw[(size_t)(r0 + c0 + t) * p.ld_o + vh * D + dvs * DVL + dvr] = (__expf(Gs[t]) * Rs[t * UP + dvr] + acc[mt][e]) * inv_sqrt_d;
         }
     }
+    if (stamp) tlc[7] = clock64();
     // ---- state: S = gamma_C S + sum_j (gamma_C / gamma_j) u_j k_j^T for this warp's k range ----
     const float gamC = __expf(gC);
 #pragma unroll
@@ -685,6 +789,12 @@ GRM_API int grm_gdn_runs(const void* qkv, int ld_qkv, const void* ab, int ld_ab,
 }
 
 // Chunked (prompt) form: same contract as grm_gdn_runs plus an fp32 scratch o_raw [M][Hv*Dv]; M = total rows.
+static long long* g_gdn_timeline = nullptr;
+// Debug aid: while set, CTA (0, 0, 0) of the tensor-core chunk kernel writes 8 clock64 stamps per chunk (chunk start, after
+// staging, after the pass over k, after its barrier, after L / M, after the substitution, after its barrier, after the
+// outputs); the buffer must hold 8 words per chunk of the first run.  Null switches it off.
+GRM_API void grm_gdn_set_timeline(void* buf) { g_gdn_timeline = (long long*)buf; }
+
 GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_ab, const void* z, int ld_z, const void* A_log,
                             const void* dt_bias, const void* norm_w, float norm_eps, void* state, const void* run_slot,
                             const void* run_start, const void* run_len, int n_runs, void* o_raw, void* out, int ld_out, int M,
@@ -694,7 +804,7 @@ GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_
   p.qkv = (const bf16*)qkv; p.ld_qkv = ld_qkv; p.ab = (const float*)ab; p.ld_ab = ld_ab;
   p.A_log = (const float*)A_log; p.dt_bias = (const float*)dt_bias; p.state = (float*)state;
   p.run_slot = (const int*)run_slot; p.run_start = (const int*)run_start; p.run_len = (const int*)run_len;
-  p.o_raw = (float*)o_raw; p.ld_o = Hv * D; p.Hk = Hk; p.Hv = Hv;
+  p.o_raw = (float*)o_raw; p.ld_o = Hv * D; p.Hk = Hk; p.Hv = Hv; p.tl = g_gdn_timeline;
   size_t smem = sizeof(float) * (2 * CH * LDK + CH * DVL + 3 * CH * UP + 2 * CH);
   // GRIMOIRE_GDN_SOLO=1 asks for more than half of an SM's shared memory, so that every CTA gets an SM to itself
   // (measurement switch for the two-CTAs-per-SM layout)
@@ -715,8 +825,8 @@ GRM_API int grm_gdn_chunked(const void* qkv, int ld_qkv, const void* ab, int ld_
     if (use_mma && cudaFuncSetAttribute(gdn_chunked_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024) != cudaSuccess)
       use_mma = 0;
   }
-  if (use_mma) {
-    const size_t smem_mma = solo ? smem : sizeof(float) * (2 * CH * LDK + CH * DVL + 3 * CH * UP + 3 * CH);
+  if (use_mma && !(ld_qkv & 7)) {
+    const size_t smem_mma = solo ? smem : sizeof(float) * (CH * LDK + QREG + CH * DVL + 3 * CH * UP + 3 * CH) + sizeof(bf16) * CH * DVL;
     gdn_chunked_mma_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem_mma, st>>>(p);
   } else {
     gdn_chunked_kernel<<<dim3(n_runs, Hv, D / DVL), kChThreads, smem, st>>>(p);
