@@ -30,7 +30,7 @@ from ..ops.linear import BF16Linear, W4Linear
 from ..ops.workspace import Workspace
 from ..utils import trace
 from .config import ModelConfig
-from .dense import RowBatch
+from .dense import DenseModel, RowBatch
 
 # expert-parallel decode of <= 8 rows through replicated routing + the all-reducing combine kernel (0: dispatch chain)
 EP_DECODE_LL = os.environ.get("GRIMOIRE_EP_DECODE_LL", "1") != "0"
@@ -576,8 +576,8 @@ class HybridModel:
         tl = trace.timeline.on
         for L in self.layers:
             if tl: trace.mark("gdn: norm + in projections" if L.kind == "gdn" else "attn: norm + qkv")
-            K.add_rmsnorm(h, L.in_norm, x, eps, off)
             if L.kind == "gdn":
+                K.add_rmsnorm(h, L.in_norm, x, eps, off)
                 si = L.state_index
                 L.in_qkv(x, buf.gdn_qkv[:M], "bf16")
                 L.in_z(x, buf.gdn_z[:M], "bf16")
@@ -595,7 +595,7 @@ class HybridModel:
                 kvl = kv_layers[L.kv_index]
                 qkv, q, attn = buf.qkv[:M], buf.q[:M], buf.attn[:M]
                 gate = buf.gate[:M] if geom.q_gated else None
-                L.qkv(x, qkv, "bf16")
+                DenseModel._norm_linear(L.qkv, h, L.in_norm, x, qkv, "bf16", eps, off)      # norm inside the one-row GEMV when it can
                 if tl: trace.mark("attn: rope + attention")
                 if prefill:
                     if rb.q_pos0 > 0:
@@ -609,12 +609,12 @@ class HybridModel:
                 if tl: trace.mark("attn: o_proj")
                 L.o(attn, h, "add_f32")
             if tl: trace.mark("ffn")
-            K.add_rmsnorm(h, L.post_norm, x, eps, off)
             if L.moe is None:
                 act = buf.act_s[:M]
-                L.ffn_gu(x, act, "swiglu")
+                DenseModel._norm_linear(L.ffn_gu, h, L.post_norm, x, act, "swiglu", eps, off)
                 L.ffn_down(act, h, "add_f32")
             else:
+                K.add_rmsnorm(h, L.post_norm, x, eps, off)
                 self._moe(L, x, h, buf, M, decode=not prefill)
         if tl: trace.mark("head")
         if rb.logits_rows is None:
