@@ -42,6 +42,12 @@ def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     """Refusal by name before any weight is read (unsupported_reason, grimoire.cpp:6969)."""
     if cfg.head_dim not in (64, 128, 256):
         return f"head_dim {cfg.head_dim} is not supported (64, 128, 256)"
+    if cfg.is_gemma4:
+        from .models.gemma4 import unsupported_gemma4
+
+        if ec.tp_world > 1 or ec.pp_world > 1 or ec.ep_world > 1:
+            return "the gemma4 family is served on one GPU (no tensor / pipeline / expert parallel path is built for it)"
+        return unsupported_gemma4(cfg)
     if is_hybrid(cfg):
         if not cfg.is_moe and ec.ep_world > 1:
             return "expert parallelism needs an MoE FFN"
@@ -102,7 +108,11 @@ class Grimoire:
             why = unsupported_reason(cfg, ec)
             if why:
                 raise UnsupportedModel(why)
-            if is_hybrid(cfg):
+            if cfg.is_gemma4:
+                from .models.gemma4 import Gemma4Model
+
+                model = Gemma4Model.random(cfg, dev, seed=0)
+            elif is_hybrid(cfg):
                 model = HybridModel.random(cfg, dev, seed=0, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
             else:
                 model = DenseModel.random(cfg, dev, seed=0, tp_rank=ec.tp_rank, tp_world=ec.tp_world, pp_rank=ec.pp_rank,
@@ -138,7 +148,11 @@ class Grimoire:
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                if ec.proj == "native" and ec.tp_world == 1 and ec.pp_world == 1 and G.native_ok(gf, cfg):
+                if cfg.is_gemma4:
+                    from .models.gemma4 import Gemma4Model
+
+                    model = Gemma4Model.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev)
+                elif ec.proj == "native" and ec.tp_world == 1 and ec.pp_world == 1 and G.native_ok(gf, cfg):
                     model = DenseModel.from_gguf_native(cfg, gf, dev)
                 else:
                     model = DenseModel.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev, ec.tp_rank, ec.tp_world, pp_rank=ec.pp_rank,
@@ -156,7 +170,11 @@ class Grimoire:
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                if is_hybrid(cfg):
+                if cfg.is_gemma4:
+                    from .models.gemma4 import Gemma4Model
+
+                    model = Gemma4Model.from_checkpoint(ec.model, dev)
+                elif is_hybrid(cfg):
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
                                                         proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))

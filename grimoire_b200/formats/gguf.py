@@ -105,7 +105,20 @@ _LAYER_MAP = {"attn_norm": "input_layernorm", "ffn_norm": "post_attention_layern
               "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj"}
 
 
-def hf_name(gguf_name: str) -> Optional[str]:
+# gemma4: the same projections under other norm names, plus the per-layer output scale (src/gguf_qwen35.cpp:700-760)
+_GEMMA4_LAYER_MAP = dict(_LAYER_MAP, ffn_norm="pre_feedforward_layernorm", post_attention_norm="post_attention_layernorm",
+                         post_ffw_norm="post_feedforward_layernorm")
+
+
+def hf_name(gguf_name: str, arch: str = "") -> Optional[str]:
+    if arch == "gemma4" and gguf_name.startswith("blk."):
+        _, layer, rest = gguf_name.split(".", 2)
+        stem, _, suffix = rest.rpartition(".")
+        if stem == "layer_output_scale":
+            return f"model.layers.{layer}.layer_scalar"
+        if stem in _GEMMA4_LAYER_MAP:
+            return f"model.layers.{layer}.{_GEMMA4_LAYER_MAP[stem]}.{suffix}"
+        return None
     if gguf_name == "token_embd.weight":
         return "model.embed_tokens.weight"
     if gguf_name == "output_norm.weight":
@@ -125,6 +138,8 @@ def config_from_gguf(g: GGUFFile):
     from ..models.config import ModelConfig
 
     a, m = g.arch, g.metadata
+    if a == "gemma4":
+        return _gemma4_config_from_gguf(g)
     heads = int(m[f"{a}.attention.head_count"])
     hidden = int(m[f"{a}.embedding_length"])
     emb = g.tensors.get("token_embd.weight")
@@ -138,11 +153,51 @@ def config_from_gguf(g: GGUFFile):
                        qk_norm="blk.0.attn_q_norm.weight" in g.tensors)
 
 
+def _gemma4_config_from_gguf(g: GGUFFile):
+    """``gemma4.*`` metadata -> ModelConfig (gguf_gemma4_config, src/gguf_qwen35.cpp:568-690): per-type key / rope keys
+    (``*_swa`` for the sliding layers), per-layer ``head_count_kv`` and ``sliding_window_pattern`` arrays, and the
+    ``rope_freqs.weight`` tensor whose ones mark the rotated pairs of the global layers' proportional RoPE."""
+    from ..models.config import ModelConfig
+
+    m, p = g.metadata, "gemma4."
+    L, hidden, heads = int(m[p + "block_count"]), int(m[p + "embedding_length"]), int(m[p + "attention.head_count"])
+    hd_full, hd_swa = int(m[p + "attention.key_length"]), int(m[p + "attention.key_length_swa"])
+    if int(m.get(p + "attention.shared_kv_layers", 0)) or int(m.get(p + "embedding_length_per_layer_input", 0)) or (p + "expert_count") in m:
+        raise ValueError("gemma4 GGUF: shared KV layers, per-layer input embeddings and MoE variants are not served")
+    pattern = [int(v) for v in m[p + "attention.sliding_window_pattern"]]
+    kv = m[p + "attention.head_count_kv"]
+    kv = [int(v) for v in kv] if isinstance(kv, (list, tuple)) else [int(kv)] * L
+    if len(pattern) != L or len(kv) != L:
+        raise ValueError("gemma4 GGUF: per-layer head_count_kv / sliding_window_pattern must have block_count entries")
+    sliding = [bool(v) for v in pattern]
+    kv_swa = {kv[i] for i in range(L) if sliding[i]} or {kv[0]}
+    kv_full = {kv[i] for i in range(L) if not sliding[i]} or kv_swa
+    if len(kv_swa) != 1 or len(kv_full) != 1:
+        raise ValueError("gemma4 GGUF: head_count_kv differs within an attention type")
+    partial = 1.0
+    if "rope_freqs.weight" in g.tensors:
+        f = g.tensor("rope_freqs.weight").float()
+        partial = float((f == 1.0).sum()) / max(1, f.numel())        # ones on the rotated pairs, a huge factor on the rest
+    has_v_full = all(f"blk.{i}.attn_v.weight" in g.tensors for i in range(L) if not sliding[i])
+    emb = g.tensors.get("token_embd.weight")
+    n_swa, n_full = next(iter(kv_swa)), next(iter(kv_full))
+    return ModelConfig(
+        model_type="gemma4_text", hidden_size=hidden, num_hidden_layers=L, num_attention_heads=heads, num_key_value_heads=n_swa,
+        head_dim=hd_swa, vocab_size=int(m.get(p + "vocab_size", emb[2][1] if emb else 0)),
+        intermediate_size=int(m[p + "feed_forward_length"]), rms_norm_eps=float(m[p + "attention.layer_norm_rms_epsilon"]),
+        rope_theta=float(m[p + "rope.freq_base_swa"]), tie_word_embeddings="output.weight" not in g.tensors, qk_norm=True,
+        sliding_window=int(m[p + "attention.sliding_window"]), softmax_scale=1.0, embed_scale=float(hidden) ** 0.5,
+        logit_softcap=float(m.get(p + "final_logit_softcapping", 0.0)), geglu=True, sandwich_norms=True, layer_scalar=True, v_norm=True,
+        k_eq_v=not has_v_full, sliding_layers=sliding, global_rope_theta=float(m[p + "rope.freq_base"]), global_partial_rotary=partial,
+        global_rope_proportional=True, global_head_dim=hd_full if hd_full != hd_swa else 0,
+        num_global_key_value_heads=n_full if n_full != n_swa else 0)
+
+
 def state_dict_from_gguf(g: GGUFFile) -> dict[str, torch.Tensor]:
     """Every tensor with a known HF name, dequantized to fp32."""
     out = {}
     for name in g.tensors:
-        hn = hf_name(name)
+        hn = hf_name(name, g.arch)
         if hn is not None:
             out[hn] = g.tensor(name)
     return out

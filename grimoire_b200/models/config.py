@@ -51,6 +51,21 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     shared_expert_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # Gemma-4 family (sandwich norms, GeGLU, two attention layer types with their own RoPE)
+    embed_scale: float = 1.0                # embeddings are multiplied by this on lookup (sqrt(hidden))
+    logit_softcap: float = 0.0              # final logits = cap * tanh(logits / cap) (0: none)
+    geglu: bool = False                     # gelu_tanh(gate) * up instead of silu(gate) * up
+    sandwich_norms: bool = False            # post-attention / pre- and post-feed-forward norms around the residual adds
+    layer_scalar: bool = False              # hidden *= layer_scalar at the end of every layer
+    v_norm: bool = False                    # weightless per-head RMSNorm of v
+    k_eq_v: bool = False                    # global layers have no v_proj: v is the k projection before its norm and RoPE
+    sliding_layers: list[bool] = field(default_factory=list)     # per layer: sliding-window attention (others are global)
+    global_rope_theta: float = 0.0          # RoPE of the global layers (0: same as the sliding layers)
+    global_partial_rotary: float = 1.0
+    global_rope_factor: float = 1.0
+    global_rope_proportional: bool = False  # frequencies over the whole head, the tail left unrotated, pairs d <-> d + D/2
+    global_head_dim: int = 0                # global layers' own head_dim / kv heads (0: same as the sliding layers)
+    num_global_key_value_heads: int = 0
     # MTP draft head
     mtp_num_hidden_layers: int = 0
     # quantization of the projections in a synthetic / converted model
@@ -83,6 +98,10 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def is_gemma4(self) -> bool:
+        return self.model_type.startswith("gemma4")
 
     def is_attention_layer(self, i: int) -> bool:
         return self.layer_types[i] == FULL_ATTN
@@ -128,6 +147,8 @@ class ModelConfig:
         lt = list(cfg.get("layer_types") or [])
         lt = [LINEAR_ATTN if t in ("linear_attention", "linear") else FULL_ATTN for t in lt]
         family35 = mt.startswith("qwen3_5") or mt.startswith("qwen3_next") or mt.startswith("qwen3.5")
+        if mt.startswith("gemma4"):
+            return ModelConfig._gemma4_from_hf(cfg, mt, n_layers, heads, hd)
         return ModelConfig(
             model_type=mt,
             hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
@@ -154,6 +175,31 @@ class ModelConfig:
             norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
             mtp_num_hidden_layers=int(cfg.get("mtp_num_hidden_layers", 0)),
         )
+
+    @staticmethod
+    def _gemma4_from_hf(cfg: dict, mt: str, n_layers: int, heads: int, hd: int) -> "ModelConfig":
+        """Gemma-4 text config (src/qwen35_loader.cpp:360-480): ``layer_types`` of sliding_attention / full_attention,
+        ``rope_parameters`` keyed BY LAYER TYPE (sliding: plain RoPE; full: proportional RoPE with a partial factor),
+        scaling 1.0, sqrt(hidden) embedding scale, GeGLU, sandwich norms, per-layer scalar, final logit soft cap."""
+        lt = list(cfg.get("layer_types") or [])
+        if len(lt) != n_layers:
+            raise ValueError("a gemma4 config must list layer_types for every layer")
+        sliding = [t == "sliding_attention" for t in lt]
+        rp = cfg.get("rope_parameters") or {}
+        rs, rg = rp.get("sliding_attention") or {}, rp.get("full_attention") or {}
+        return ModelConfig(
+            model_type=mt, hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
+            num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd, vocab_size=int(cfg["vocab_size"]),
+            intermediate_size=int(cfg.get("intermediate_size", 0)), rms_norm_eps=float(cfg.get("rms_norm_eps", 1e-6)),
+            rope_theta=float(rs.get("rope_theta", cfg.get("rope_local_base_freq", 1e4))), partial_rotary_factor=1.0,
+            tie_word_embeddings=bool(cfg.get("tie_word_embeddings", True)), qk_norm=True, norm_zero_centered=False,
+            sliding_window=int(cfg.get("sliding_window") or 0), softmax_scale=1.0,
+            embed_scale=float(cfg["hidden_size"]) ** 0.5, logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0),
+            geglu=True, sandwich_norms=True, layer_scalar=True, v_norm=True, k_eq_v=bool(cfg.get("attention_k_eq_v", False)),
+            sliding_layers=sliding, global_rope_theta=float(rg.get("rope_theta", 1e6)),
+            global_partial_rotary=float(rg.get("partial_rotary_factor", 1.0)), global_rope_factor=float(rg.get("factor", 1.0)),
+            global_rope_proportional=rg.get("rope_type", "proportional") == "proportional",
+            global_head_dim=int(cfg.get("global_head_dim") or 0), num_global_key_value_heads=int(cfg.get("num_global_key_value_heads") or 0))
 
     @staticmethod
     def from_dir(path: str | Path) -> "ModelConfig":
@@ -237,5 +283,16 @@ def tiny_moe(layers: int = 2) -> ModelConfig:
                        quant="fp8_block")
 
 
-PRESETS = {"hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+def tiny_gemma4(layers: int = 4) -> ModelConfig:
+    """A small Gemma-4-style decoder: 3 sliding-window layers then 1 global layer (no v_proj, proportional RoPE over a
+    quarter of the head), sandwich norms, GeGLU, layer scalars, logit soft cap; one head geometry for both layer types."""
+    sliding = [(i % 4) != 3 for i in range(layers)]
+    return ModelConfig(model_type="gemma4_text", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=512, tie_word_embeddings=True,
+                       rope_theta=1e4, qk_norm=True, sliding_window=16, softmax_scale=1.0, embed_scale=16.0, logit_softcap=30.0,
+                       geglu=True, sandwich_norms=True, layer_scalar=True, v_norm=True, k_eq_v=True, sliding_layers=sliding,
+                       global_rope_theta=1e6, global_partial_rotary=0.25, global_rope_proportional=True, quant="int4")
+
+
+PRESETS = {"tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
            "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}
