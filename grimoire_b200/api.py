@@ -42,11 +42,11 @@ def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     """Refusal by name before any weight is read (unsupported_reason, grimoire.cpp:6969)."""
     if cfg.head_dim not in (64, 128, 256):
         return f"head_dim {cfg.head_dim} is not supported (64, 128, 256)"
-    if cfg.is_gemma4:
+    if cfg.is_sandwich:
         from .models.gemma4 import unsupported_gemma4
 
         if ec.tp_world > 1 or ec.pp_world > 1 or ec.ep_world > 1:
-            return "the gemma4 family is served on one GPU (no tensor / pipeline / expert parallel path is built for it)"
+            return "the gemma4 / muse families are served on one GPU (no tensor / pipeline / expert parallel path is built for them)"
         return unsupported_gemma4(cfg)
     if is_hybrid(cfg):
         if not cfg.is_moe and ec.ep_world > 1:
@@ -108,10 +108,10 @@ class Grimoire:
             why = unsupported_reason(cfg, ec)
             if why:
                 raise UnsupportedModel(why)
-            if cfg.is_gemma4:
-                from .models.gemma4 import Gemma4Model
+            if cfg.is_sandwich:
+                from .models.gemma4 import Gemma4Model, MuseModel
 
-                model = Gemma4Model.random(cfg, dev, seed=0)
+                model = (MuseModel if cfg.is_muse else Gemma4Model).random(cfg, dev, seed=0)
             elif is_hybrid(cfg):
                 model = HybridModel.random(cfg, dev, seed=0, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
             else:
@@ -170,10 +170,10 @@ class Grimoire:
                 why = unsupported_reason(cfg, ec)
                 if why:
                     raise UnsupportedModel(why)
-                if cfg.is_gemma4:
-                    from .models.gemma4 import Gemma4Model
+                if cfg.is_sandwich:
+                    from .models.gemma4 import Gemma4Model, MuseModel
 
-                    model = Gemma4Model.from_checkpoint(ec.model, dev)
+                    model = (MuseModel if cfg.is_muse else Gemma4Model).from_checkpoint(ec.model, dev)
                 elif is_hybrid(cfg):
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),

@@ -66,6 +66,11 @@ class ModelConfig:
     global_rope_proportional: bool = False  # frequencies over the whole head, the tail left unrotated, pairs d <-> d + D/2
     global_head_dim: int = 0                # global layers' own head_dim / kv heads (0: same as the sliding layers)
     num_global_key_value_heads: int = 0
+    # Muse-Glimmer family (the sandwich layer of above with these switches)
+    embed_norm: bool = False                # weightless RMSNorm of the embedding row before the first layer
+    qk_norm_weightless: bool = False        # q / k per-head RMSNorm without a learned weight
+    global_nope: bool = False               # global layers apply no rotary embedding at all
+    attn_gate_proj: str = ""                # "sigmoid": attention output *= sigmoid(gate_proj(normed layer input))
     # MTP draft head
     mtp_num_hidden_layers: int = 0
     # quantization of the projections in a synthetic / converted model
@@ -102,6 +107,15 @@ class ModelConfig:
     @property
     def is_gemma4(self) -> bool:
         return self.model_type.startswith("gemma4")
+
+    @property
+    def is_muse(self) -> bool:
+        return "muse_glimmer" in self.model_type
+
+    @property
+    def is_sandwich(self) -> bool:
+        """Served by the sandwich-norm decoder class (models/gemma4.py)."""
+        return self.is_gemma4 or self.is_muse
 
     def is_attention_layer(self, i: int) -> bool:
         return self.layer_types[i] == FULL_ATTN
@@ -149,6 +163,8 @@ class ModelConfig:
         family35 = mt.startswith("qwen3_5") or mt.startswith("qwen3_next") or mt.startswith("qwen3.5")
         if mt.startswith("gemma4"):
             return ModelConfig._gemma4_from_hf(cfg, mt, n_layers, heads, hd)
+        if "muse_glimmer" in mt:
+            return ModelConfig._muse_from_hf(cfg, mt, n_layers, heads, hd)
         return ModelConfig(
             model_type=mt,
             hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
@@ -200,6 +216,27 @@ class ModelConfig:
             global_partial_rotary=float(rg.get("partial_rotary_factor", 1.0)), global_rope_factor=float(rg.get("factor", 1.0)),
             global_rope_proportional=rg.get("rope_type", "proportional") == "proportional",
             global_head_dim=int(cfg.get("global_head_dim") or 0), num_global_key_value_heads=int(cfg.get("num_global_key_value_heads") or 0))
+
+    @staticmethod
+    def _muse_from_hf(cfg: dict, mt: str, n_layers: int, heads: int, hd: int) -> "ModelConfig":
+        """Muse-Glimmer text config (src/qwen35_loader.cpp:667-680): sliding RoPE layers and full NoPE layers from
+        ``layer_types``, query prescale from ``scale_query_by`` / ``qk_scale_factor``, attention output gate, (1 + w) norms."""
+        lt = list(cfg.get("layer_types") or [])
+        if len(lt) != n_layers:
+            raise ValueError("a muse_glimmer config must list layer_types for every layer")
+        rp = cfg.get("rope_parameters") or cfg.get("rope_scaling") or {}
+        ex, qk = float(cfg.get("scale_query_by") or 0.0), float(cfg.get("qk_scale_factor") or 0.0)
+        prescale = ex if ex > 0 else (qk if qk > 0 else 1.0)
+        return ModelConfig(
+            model_type=mt, hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
+            num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd, vocab_size=int(cfg["vocab_size"]),
+            intermediate_size=int(cfg.get("intermediate_size", 0)), rms_norm_eps=float(cfg.get("rms_norm_eps", 1e-6)),
+            rope_theta=float(rp.get("rope_theta", cfg.get("rope_theta", 1e6))),
+            partial_rotary_factor=float(rp.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 1.0))),
+            tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)), qk_norm=True, norm_zero_centered=True,
+            sliding_window=int(cfg.get("sliding_window") or 0), softmax_scale=prescale / float(hd) ** 0.5,
+            sandwich_norms=True, sliding_layers=[t == "sliding_attention" for t in lt], embed_norm=True, qk_norm_weightless=True,
+            global_nope=True, attn_gate_proj="sigmoid")
 
     @staticmethod
     def from_dir(path: str | Path) -> "ModelConfig":
@@ -294,5 +331,15 @@ def tiny_gemma4(layers: int = 4) -> ModelConfig:
                        global_rope_theta=1e6, global_partial_rotary=0.25, global_rope_proportional=True, quant="int4")
 
 
-PRESETS = {"tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+def tiny_muse(layers: int = 4) -> ModelConfig:
+    """A small Muse-Glimmer-style decoder: 3 sliding RoPE layers then 1 full layer without positional embedding, sandwich
+    norms in the (1 + w) convention, weightless q / k norms, a sigmoid output gate projection, SwiGLU, normalised embeddings."""
+    return ModelConfig(model_type="muse_glimmer_text", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=512, tie_word_embeddings=False,
+                       rope_theta=1e6, qk_norm=True, norm_zero_centered=True, sliding_window=16, softmax_scale=0.5 / 8.0,
+                       sandwich_norms=True, sliding_layers=[(i % 4) != 3 for i in range(layers)], embed_norm=True,
+                       qk_norm_weightless=True, global_nope=True, attn_gate_proj="sigmoid", quant="int4")
+
+
+PRESETS = {"tiny_muse": tiny_muse, "tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
            "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}

@@ -1,4 +1,4 @@
-"""Gemma-4 text decoder on the dense engine path.
+"""Sandwich-norm decoders on the dense engine path: the Gemma-4 text decoder and the Muse-Glimmer text decoder.
 
 What differs from the Qwen3-style dense decoder (reference: ``forward_gemma4``, src/grimoire.cpp:14086-14270, config notes in
 include/b70/qwen35.hpp:141-290, oracle ref/gemma4.py):
@@ -13,6 +13,12 @@ include/b70/qwen35.hpp:141-290, oracle ref/gemma4.py):
 * sandwich norms: the attention output and the feed-forward output are normalised before they are added to the residual
   stream, and the feed-forward has its own input norm; GeGLU (tanh approximation); the stream is multiplied by a per-layer
   scalar at the end of the layer; the final logits are soft-capped.
+
+The Muse-Glimmer decoder (``forward_muse``, src/grimoire.cpp:13867-14084) is the same sandwich layer with other switches:
+the embedding row is RMS-normalised (no weight) before the first layer, q and k get a weightless per-head norm, sliding
+layers use RoPE and the full layers no positional embedding at all, the attention output is multiplied by
+sigmoid(gate_proj(normed layer input)), the feed-forward is SwiGLU, norms follow the (1 + w) convention and the softmax
+scale carries the checkpoint's query prescale.  ``MuseModel`` is this class under that configuration.
 
 Projections, RoPE + KV append, paged decode attention, prompt attention and the head are the engine's kernels; the pieces
 only this family has (v norm, sandwich norms, GeGLU product, layer scalar, soft cap) are elementwise torch operations on the
@@ -52,6 +58,7 @@ class Gemma4Layer:
     scalar: float
     is_global: bool
     k_eq_v: bool
+    gate: object = None         # attention output gate projection [Hq * D][H] (Muse)
 
 
 def proportional_inv_freq(head_dim: int, theta: float, partial: float, factor: float = 1.0) -> torch.Tensor:
@@ -83,7 +90,11 @@ class Gemma4Model(DenseModel):
         # the proportional table
         self.geom_global = dataclasses.replace(self.geom, window=0, rot=D)
         theta_g = cfg.global_rope_theta or cfg.rope_theta
-        if cfg.global_rope_proportional:
+        # weightless q / k norm: a unit weight under the model's norm convention
+        self.unit_norm = (torch.zeros(D) if cfg.norm_zero_centered else torch.ones(D)).to(self.device) if cfg.qk_norm_weightless else None
+        if cfg.global_nope:
+            self.inv_freq_global = torch.zeros(D // 2, device=self.device)      # angle 0 everywhere: the rotation is the identity
+        elif cfg.global_rope_proportional:
             self.inv_freq_global = proportional_inv_freq(D, theta_g, cfg.global_partial_rotary, cfg.global_rope_factor).to(self.device)
         else:
             rot = int(D * cfg.global_partial_rotary) // 2 * 2
@@ -107,12 +118,16 @@ class Gemma4Model(DenseModel):
             f32(w["in_norm"]), f32(w["post_attn_norm"]), f32(w["pre_ff_norm"]), f32(w["post_ff_norm"]),
             self._linear(concat_rows(parts), f"L{i}.qkv"), self._linear(self._quant(w["o"]), f"L{i}.o"),
             self._linear(concat_rows([self._quant(w["gate"]), self._quant(w["up"])]), f"L{i}.gate_up"),
-            self._linear(self._quant(w["down"]), f"L{i}.down"), f32(w.get("q_norm")), f32(w.get("k_norm")),
-            1.0 if sc is None else float(torch.as_tensor(sc).float().reshape(-1)[0]), is_global, k_eq_v))
+            self._linear(self._quant(w["down"]), f"L{i}.down"),
+            self.unit_norm if cfg.qk_norm_weightless else f32(w.get("q_norm")), self.unit_norm if cfg.qk_norm_weightless else f32(w.get("k_norm")),
+            1.0 if sc is None else float(torch.as_tensor(sc).float().reshape(-1)[0]), is_global, k_eq_v,
+            self._linear(self._quant(w["attn_gate"]), f"L{i}.attn_gate") if w.get("attn_gate") is not None else None))
+        if cfg.attn_gate_proj and self.layers[-1].gate is None:
+            raise KeyError(f"layer {i} has no attention gate projection (self_attn.gate_proj)")
 
-    @staticmethod
-    def from_state_dict(cfg: ModelConfig, sd: dict, device, workspace: Optional[Workspace] = None) -> "Gemma4Model":
-        m = Gemma4Model(cfg, device, workspace)
+    @classmethod
+    def from_state_dict(cls, cfg: ModelConfig, sd: dict, device, workspace: Optional[Workspace] = None) -> "Gemma4Model":
+        m = cls(cfg, device, workspace)
         pfx = "model.language_model." if any(k.startswith("model.language_model.") for k in sd) else "model."
         for i in range(cfg.num_hidden_layers):
             p = f"{pfx}layers.{i}."
@@ -122,18 +137,19 @@ class Gemma4Model(DenseModel):
                 o=g("self_attn.o_proj.weight"), gate=g("mlp.gate_proj.weight"), up=g("mlp.up_proj.weight"), down=g("mlp.down_proj.weight"),
                 in_norm=g("input_layernorm.weight"), post_attn_norm=g("post_attention_layernorm.weight"),
                 pre_ff_norm=g("pre_feedforward_layernorm.weight"), post_ff_norm=g("post_feedforward_layernorm.weight"),
-                q_norm=g("self_attn.q_norm.weight"), k_norm=g("self_attn.k_norm.weight"), scalar=g("layer_scalar")))
+                q_norm=g("self_attn.q_norm.weight"), k_norm=g("self_attn.k_norm.weight"), scalar=g("layer_scalar"),
+                attn_gate=g("self_attn.gate_proj.weight")))
         m.set_embeddings(sd[pfx + "embed_tokens.weight"], sd[pfx + "norm.weight"], sd.get("lm_head.weight"))
         return m
 
-    @staticmethod
-    def from_checkpoint(path, device, workspace: Optional[Workspace] = None) -> "Gemma4Model":
-        """HF directory with the family's tensor names (src/qwen35_loader.cpp:1172-1240)."""
+    @classmethod
+    def from_checkpoint(cls, path, device, workspace: Optional[Workspace] = None) -> "Gemma4Model":
+        """HF directory with the family's tensor names (src/qwen35_loader.cpp:1165-1240)."""
         from ..formats.checkpoint import Checkpoint
 
         ck = Checkpoint(path) if isinstance(path, (str, bytes)) or hasattr(path, "__fspath__") else path
         cfg = ck.cfg
-        m = Gemma4Model(cfg, device, workspace)
+        m = cls(cfg, device, workspace)
         for i in range(cfg.num_hidden_layers):
             p = f"{ck.prefix}layers.{i}."
             lin = lambda k: ck.linear(p + k)
@@ -143,16 +159,16 @@ class Gemma4Model(DenseModel):
                 in_norm=ck.plain(p + "input_layernorm.weight"), post_attn_norm=ck.plain(p + "post_attention_layernorm.weight"),
                 pre_ff_norm=ck.plain(p + "pre_feedforward_layernorm.weight"), post_ff_norm=ck.plain(p + "post_feedforward_layernorm.weight"),
                 q_norm=ck.plain(p + "self_attn.q_norm.weight"), k_norm=ck.plain(p + "self_attn.k_norm.weight"),
-                scalar=ck.plain(p + "layer_scalar")))
+                scalar=ck.plain(p + "layer_scalar"), attn_gate=lin("self_attn.gate_proj") if cfg.attn_gate_proj else None))
         head = None if cfg.tie_word_embeddings else ck.linear("lm_head")
         m.set_embeddings(ck.embedding(), ck.plain(ck.prefix + "norm.weight"), head)
         return m
 
-    @staticmethod
-    def random(cfg: ModelConfig, device, seed: int = 0, **_kw) -> "Gemma4Model":
+    @classmethod
+    def random(cls, cfg: ModelConfig, device, seed: int = 0, **_kw) -> "Gemma4Model":
         from .synthetic import random_gemma4_state_dict
 
-        return Gemma4Model.from_state_dict(cfg, random_gemma4_state_dict(cfg, seed), device)
+        return cls.from_state_dict(cfg, random_gemma4_state_dict(cfg, seed), device)
 
     def make_buffers(self, max_rows: int, max_logit_rows: int, dense_kv_tokens: int = 0):
         b = super().make_buffers(max_rows, max_logit_rows, dense_kv_tokens)
@@ -175,6 +191,8 @@ class Gemma4Model(DenseModel):
         Hq, Hkv, D, I = self.Hq, self.Hkv, cfg.head_dim, self.I
         qw, kw = Hq * D, Hkv * D
         K.embed(rb.tokens, self.embed, h, cfg.embed_scale)
+        if cfg.embed_norm:
+            h.copy_(h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps))
         prefill = rb.mode == "prefill"
         if prefill and rb.segments is not None:
             raise NotImplementedError("several prompts in one pass are not built for this family")
@@ -202,12 +220,16 @@ class Gemma4Model(DenseModel):
                 if not (rb.verify is not None and K.paged_verify_attn(q, rb.verify[0], rb.verify[1], block_table, kvl, geom, attn,
                                                                       rb.splits, self.ws, None)):
                     K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, None)
+            if L.gate is not None:                                        # output gate from the normed layer input (x is still it)
+                L.gate(x, q, "bf16")
+                attn.copy_((attn.float() * torch.sigmoid(q.float())).to(attn.dtype))
             # sandwich: the normalised attention output joins the stream
             L.o(attn, part, "f32")
             h.add_(ref.rmsnorm(part, L.post_attn_norm, eps, off))
             K.add_rmsnorm(h, L.pre_ff_norm, x, eps, off)
             L.gate_up(x, gu, "bf16")
-            act.copy_((F.gelu(gu[:, :I].float(), approximate="tanh") * gu[:, I:].float()).to(act.dtype))
+            gate_act = F.gelu(gu[:, :I].float(), approximate="tanh") if cfg.geglu else F.silu(gu[:, :I].float())
+            act.copy_((gate_act * gu[:, I:].float()).to(act.dtype))
             L.down(act, part, "f32")
             h.add_(ref.rmsnorm(part, L.post_ff_norm, eps, off))
             if L.scalar != 1.0:
@@ -225,3 +247,7 @@ class Gemma4Model(DenseModel):
         if cfg.logit_softcap > 0:
             logits.copy_(torch.tanh(logits / cfg.logit_softcap) * cfg.logit_softcap)
         return logits
+
+
+class MuseModel(Gemma4Model):
+    """Muse-Glimmer text decoder: the sandwich layer above under the Muse switches of the configuration."""

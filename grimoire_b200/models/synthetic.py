@@ -118,12 +118,12 @@ def random_mtp_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02) ->
 
 
 def random_gemma4_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
-    """fp32 logical weights of a Gemma-4-style decoder under its checkpoint names (src/qwen35_loader.cpp:1172-1240): the four
+    """fp32 logical weights of a sandwich-norm decoder (Gemma-4 or Muse-Glimmer style) under its checkpoint names (src/qwen35_loader.cpp:1172-1240): the four
     layer norms, q / k norms, ``layer_scalar``, no ``v_proj`` on global layers when the config sets attention_k_eq_v."""
     g = torch.Generator().manual_seed(seed)
     H, D, I = cfg.hidden_size, cfg.head_dim, cfg.intermediate_size
     rnd = lambda *shape, scale=std: torch.randn(*shape, generator=g, dtype=torch.float32) * scale
-    nw = lambda n: 1.0 + rnd(n, scale=0.05)
+    nw = (lambda n: rnd(n, scale=0.05)) if cfg.norm_zero_centered else (lambda n: 1.0 + rnd(n, scale=0.05))
     sd = {"model.embed_tokens.weight": rnd(cfg.vocab_size, H), "model.norm.weight": nw(H)}
     if not cfg.tie_word_embeddings:
         sd["lm_head.weight"] = rnd(cfg.vocab_size, H)
@@ -138,7 +138,9 @@ def random_gemma4_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02)
         sd[a + "o_proj.weight"] = rnd(H, cfg.num_attention_heads * D)
         # the softmax scale is 1.0 and q, k are normalised per head: norm weights near 1 would give scores of ~sqrt(D) and a
         # near one-hot, chaotic softmax; trained checkpoints keep them small, so the synthetic ones do too
-        sd[a + "q_norm.weight"], sd[a + "k_norm.weight"] = 0.25 * nw(D), 0.25 * nw(D)
+        sd[a + "q_norm.weight"], sd[a + "k_norm.weight"] = 0.25 * (1.0 + rnd(D, scale=0.05)), 0.25 * (1.0 + rnd(D, scale=0.05))
+        if cfg.attn_gate_proj:
+            sd[a + "gate_proj.weight"] = rnd(cfg.num_attention_heads * D, H)
         sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"], sd[p + "mlp.down_proj.weight"] = rnd(I, H), rnd(I, H), rnd(H, I)
         if cfg.layer_scalar:
             sd[p + "layer_scalar"] = torch.tensor([1.0 + 0.1 * ((i % 3) - 1)])

@@ -95,16 +95,68 @@ def test_synthetic_preset_and_refusal_of_per_type_geometry(tmp_path):
         Grimoire.load(_ec(d), device="cpu")
 
 
+def _muse_hf_config(cfg: ModelConfig) -> dict:
+    return {"model_type": "muse_glimmer", "text_config": {
+        "model_type": "muse_glimmer_text", "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
+        "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+        "vocab_size": cfg.vocab_size, "intermediate_size": cfg.intermediate_size, "rms_norm_eps": cfg.rms_norm_eps,
+        "tie_word_embeddings": False, "sliding_window": cfg.sliding_window, "scale_query_by": 0.5, "rope_theta": cfg.rope_theta,
+        "layer_types": ["sliding_attention" if s else "full_attention" for s in cfg.sliding_layers]}}
+
+
+def test_muse_checkpoint_matches_fp32_oracle(tmp_path):
+    """Muse-Glimmer switches of the sandwich decoder: normalised embeddings, weightless q / k norms, RoPE on the sliding
+    layers only, sigmoid output gate projection, SwiGLU, (1 + w) norms, query prescale in the softmax scale."""
+    from grimoire_b200.models.config import tiny_muse
+    from grimoire_b200.models.gemma4 import MuseModel
+
+    cfg = tiny_muse()
+    path = tmp_path / "muse"
+    path.mkdir()
+    sd = random_gemma4_state_dict(cfg, 8)
+    (path / "config.json").write_text(json.dumps(_muse_hf_config(cfg)))
+    save_file({k: v.bfloat16() for k, v in sd.items()}, path / "model.safetensors", {"format": "pt"})
+    parsed = ModelConfig.from_dir(path)
+    for f in ("sliding_layers", "sliding_window", "softmax_scale", "embed_norm", "qk_norm_weightless", "global_nope", "attn_gate_proj",
+              "norm_zero_centered", "geglu", "rope_theta", "tie_word_embeddings"):
+        assert getattr(parsed, f) == getattr(cfg, f), f
+    g = Grimoire.load(_ec(path), device="cpu")
+    assert isinstance(g.model, MuseModel) and all(L.gate is not None for L in g.model.layers)
+    assert float(g.model.inv_freq_global.abs().max()) == 0.0
+    ids = torch.randint(0, 4096, (45,), generator=torch.Generator().manual_seed(7)).tolist()
+    got = g.score_ids(ids)
+    q = lambda w: quantize(w.bfloat16().float(), Fmt.INT4).dequant().float()
+    want = gemma4_reference.forward_logits(cfg, {k: v.bfloat16().float() for k, v in sd.items()}, ids, weight_fn=q)
+    err = float((got - want).abs().max())
+    assert err < 0.06 * float(want.abs().max()), (err, float(want.abs().max()))
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.9
+    out, _ = g.generate(ids, 5)
+    full = g.score_ids(ids + out)
+    assert [int(full[len(ids) - 1 + j].argmax()) for j in range(5)] == out
+    g.close()
+    g = Grimoire.load(_ec("synthetic:tiny_muse"), device="cpu")
+    assert isinstance(g.model, MuseModel) and len(g.generate(list(range(9, 30)), 3)[0]) == 3
+    g.close()
+
+
 @pytest.mark.gpu
-def test_gemma4_gpu_matches_cpu_path_and_graph_replay():
+@pytest.mark.parametrize("family", ["gemma4", "muse"])
+def test_gemma4_gpu_matches_cpu_path_and_graph_replay(family):
     from grimoire_b200.engine.engine import Engine, EngineLimits
+    from grimoire_b200.models.config import tiny_muse
+    from grimoire_b200.models.gemma4 import MuseModel
     from grimoire_b200.ops import core as K
 
-    cfg = dataclasses.replace(tiny_gemma4(), hidden_size=512, head_dim=128, intermediate_size=1024, embed_scale=512 ** 0.5)
+    if family == "muse":
+        cfg = dataclasses.replace(tiny_muse(), hidden_size=512, head_dim=128, intermediate_size=1024, softmax_scale=0.5 / 128 ** 0.5)
+        cls = MuseModel
+    else:
+        cfg = dataclasses.replace(tiny_gemma4(), hidden_size=512, head_dim=128, intermediate_size=1024, embed_scale=512 ** 0.5)
+        cls = Gemma4Model
     sd = random_gemma4_state_dict(cfg, seed=2)
     lim = dict(max_slots=2, max_ctx=256, prefill_chunk=64, max_decode_rows=8)
-    gpu = Engine(Gemma4Model.from_state_dict(cfg, sd, "cuda"), EngineLimits(**lim))
-    cpu = Engine(Gemma4Model.from_state_dict(cfg, sd, "cpu"), EngineLimits(**lim))
+    gpu = Engine(cls.from_state_dict(cfg, sd, "cuda"), EngineLimits(**lim))
+    cpu = Engine(cls.from_state_dict(cfg, sd, "cpu"), EngineLimits(**lim))
     prompt = torch.randint(0, 4096, (90,), generator=torch.Generator().manual_seed(5)).tolist()
     sg, sc = gpu.open(), cpu.open()
     lg, lc = gpu.prefill(sg, prompt).float().cpu(), cpu.prefill(sc, prompt).float()
