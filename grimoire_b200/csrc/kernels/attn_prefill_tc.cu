@@ -29,6 +29,7 @@ constexpr uint32_t kTmemCols = 256;       // S buffer 0: columns [0, 64), O: [64
 
 struct TcParams {
   bf16* out; int ld_o;
+  const bf16* gate; int ld_g;     // optional [M][Hq*D] gate (output *= sigmoid(gate)); warp-specialised kernel only
   int M, T, Hq, Hkv, q_pos0, window;
   float scale_log2;
   unsigned int* status;
@@ -276,11 +277,25 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 // -- while the rows are still in the softmax of block j -- instead of after it, so the S product's latency is off the
 // critical path.  Hand-overs: bars[4/5] S(j) complete (rows and the MMA warp wait), bars[7] P(j) stored (128 arrivals, the
 // MMA warp waits), bars[6] PV(j) complete (rows wait before touching O / P, the MMA warp before refilling V).
+// Templated on the head dimension: 128 (two CTAs per SM) or 256 (one CTA per SM: 176 KB of tiles, 384 TMEM columns); an
+// optional gate multiplies the output by sigmoid(gate) in the epilogue (gated attention of the hybrid family).
 constexpr int kThreadsWs = 160;
+template <int DH> struct WsGeom {
+  static constexpr int kQB = BQ * DH * 2, kKB = BKV * DH * 2, kVB = DH * BKV * 2;
+  static constexpr int kQBox = BQ * 128, kKBox = BKV * 128;            // one 64-dim box of the Q / K tile
+  static constexpr int kSmemBytes = kQB + kKB + 2 * kVB + kPBytes + 256 + 1024;
+  static constexpr uint32_t kCols = DH == 128 ? 256u : 512u;           // S0 [0, 64), O [64, 64 + DH), S1 [64 + DH, 128 + DH)
+  static constexpr uint32_t kS1 = 64u + DH;
+};
 
-__global__ void __launch_bounds__(kThreadsWs, 2)
+template <int DH>
+__global__ void __launch_bounds__(kThreadsWs, DH == 128 ? 2 : 1)
 flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                            const __grid_constant__ CUtensorMap tmV, const TcParams p) {
+  using G = WsGeom<DH>;
+  constexpr int D = DH;                        // shadows the file-wide 128 inside this kernel
+  constexpr int kQBytes = G::kQB, kKBytes = G::kKB, kVBytes = G::kVB;
+  constexpr uint32_t kTmemCols = G::kCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -324,8 +339,8 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     if (lane == 0) {
       auto load_k = [&](int kb) {
         mbar_expect_tx(&bars[1], kKBytes);
-        tma_load_2d(sK, &tmK, &bars[1], kvh * D, kb * BKV);
-        tma_load_2d(sK + kKBytes / 2, &tmK, &bars[1], kvh * D + 64, kb * BKV);
+#pragma unroll
+        for (int bx = 0; bx < D / 64; ++bx) tma_load_2d(sK + bx * G::kKBox, &tmK, &bars[1], kvh * D + 64 * bx, kb * BKV);
       };
       auto load_v = [&](int kb, int buf) {
         mbar_expect_tx(&bars[2 + buf], kVBytes);
@@ -335,11 +350,11 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         if (!mbar_wait(&bars[1], (uint32_t)j & 1u, p.status, 0x811u)) return false;
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
-        const uint32_t td = tmem_base + ((j & 1) ? 192u : 0u);
+        const uint32_t td = tmem_base + ((j & 1) ? G::kS1 : 0u);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * (kQBytes / 2)) + (uint64_t)((k & 3) * 2);
-          const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * (kKBytes / 2)) + (uint64_t)((k & 3) * 2);
+          const uint64_t da = make_sw128_kmajor_desc(qa + (k >> 2) * G::kQBox) + (uint64_t)((k & 3) * 2);
+          const uint64_t db = make_sw128_kmajor_desc(ka + (k >> 2) * G::kKBox) + (uint64_t)((k & 3) * 2);
           tc_mma_f16(td, da, db, idesc_s, k != 0 ? 1u : 0u);
         }
         tc_commit(&bars[4 + (j & 1)]);
@@ -347,8 +362,8 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       };
       tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
       mbar_expect_tx(&bars[0], kQBytes);
-      tma_load_2d(sQ, &tmQ, &bars[0], h * D, qb * BQ);
-      tma_load_2d(sQ + kQBytes / 2, &tmQ, &bars[0], h * D + 64, qb * BQ);
+#pragma unroll
+      for (int bx = 0; bx < D / 64; ++bx) tma_load_2d(sQ + bx * G::kQBox, &tmQ, &bars[0], h * D + 64 * bx, qb * BQ);
       load_k(kb_lo);
       load_v(kb_lo, 0);
       bool good = mbar_wait(&bars[0], 0u, p.status, 0x810u) && issue_s(0);
@@ -396,7 +411,7 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
       tc_fence_after();
       float sv[BKV];
       {
-        const uint32_t ts = t_row + (b ? 192u : 0u);
+        const uint32_t ts = t_row + (b ? G::kS1 : 0u);
         uint32_t r[32];
         tmem_ld_32x32b_x32(ts, r);
         tmem_ld_wait();
@@ -475,6 +490,7 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
     if (ok) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = p.out + (size_t)row * p.ld_o + (size_t)h * D;
+      const bf16* gsrc = p.gate ? p.gate + (size_t)row * p.ld_g + (size_t)h * D : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -483,11 +499,19 @@ flash_prefill_tc_ws_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[i + e]) * inv;
+            if (gsrc) {                                      // gated attention: o *= sigmoid(gate)
+              const uint4 gv = *reinterpret_cast<const uint4*>(gsrc + c * 32 + i);
+              const float gf[8] = {bf16lo_to_f(gv.x), bf16hi_to_f(gv.x), bf16lo_to_f(gv.y), bf16hi_to_f(gv.y),
+                                   bf16lo_to_f(gv.z), bf16hi_to_f(gv.z), bf16lo_to_f(gv.w), bf16hi_to_f(gv.w)};
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] *= 1.f / (1.f + __expf(-gf[e]));
+            }
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            v.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            v.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            v.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            v.x = pack_bf16x2(f[0], f[1]); v.y = pack_bf16x2(f[2], f[3]);
+            v.z = pack_bf16x2(f[4], f[5]); v.w = pack_bf16x2(f[6], f[7]);
             *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
           }
         }
@@ -546,37 +570,53 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, ui
 
 }  // namespace
 
-// vt: scratch bf16 [Hkv*128][ldt] with ldt >= T rounded up to 64 (filled here from v).  head_dim must be 128.
-GRM_API int grm_flash_prefill_tc(const void* q, int ld_q, const void* k, const void* v, int ld_kv, void* vt, int ldt, void* out, int ld_o,
-                                 int M, int T, int Hq, int Hkv, int Dh, int q_pos0, int window, float scale, void* stream) {
-  if (Dh != D || M < 1 || T < M || Hq % Hkv || (ld_o & 7) || (ldt & 63) || ldt < ((T + 63) / 64) * 64) return -2;
+// vt: scratch bf16 [Hkv*Dh][ldt] with ldt >= T rounded up to 64 (filled here from v).  head_dim 128, or 256 with the
+// warp-specialised kernel; gate (optional, [M][Hq*Dh] bf16 with row pitch ld_g): output *= sigmoid(gate), warp-specialised
+// kernel only.  Returns -2 for anything else (the caller then takes the warp-MMA kernel).
+GRM_API int grm_flash_prefill_tc_gated(const void* q, int ld_q, const void* k, const void* v, int ld_kv, void* vt, int ldt, const void* gate,
+                                       int ld_g, void* out, int ld_o, int M, int T, int Hq, int Hkv, int Dh, int q_pos0, int window,
+                                       float scale, void* stream) {
+  if ((Dh != 128 && Dh != 256) || M < 1 || T < M || Hq % Hkv || (ld_o & 7) || (ldt & 63) || ldt < ((T + 63) / 64) * 64 ||
+      (gate && ((ld_g & 7) || ((uintptr_t)gate & 15))))
+    return -2;
+  static int ws = -1;
+  if (ws < 0) {
+    const char* ev = getenv("GRIMOIRE_FLASH_WS");
+    ws = (ev && ev[0] == '0') ? 0 : 1;
+    if (ws && (cudaFuncSetAttribute(flash_prefill_tc_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<128>::kSmemBytes) != cudaSuccess ||
+               cudaFuncSetAttribute(flash_prefill_tc_ws_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<256>::kSmemBytes) != cudaSuccess))
+      ws = 0;
+  }
+  if (!ws && (Dh != 128 || gate)) return -2;
   cudaStream_t st = (cudaStream_t)stream;
-  kv_transpose_kernel<<<dim3((ldt + 31) / 32, (Hkv * D + 31) / 32), 256, 0, st>>>((const bf16*)v, ld_kv, (bf16*)vt, ldt, T, Hkv * D);
+  kv_transpose_kernel<<<dim3((ldt + 31) / 32, (Hkv * Dh + 31) / 32), 256, 0, st>>>((const bf16*)v, ld_kv, (bf16*)vt, ldt, T, Hkv * Dh);
   CUtensorMap tq, tk, tv;
-  int e = make_map(&tq, q, (uint64_t)M, (uint64_t)Hq * D, (uint64_t)ld_q, BQ);
+  int e = make_map(&tq, q, (uint64_t)M, (uint64_t)Hq * Dh, (uint64_t)ld_q, BQ);
   if (e) return e;
-  e = make_map(&tk, k, (uint64_t)T, (uint64_t)Hkv * D, (uint64_t)ld_kv, BKV);
+  e = make_map(&tk, k, (uint64_t)T, (uint64_t)Hkv * Dh, (uint64_t)ld_kv, BKV);
   if (e) return e;
-  e = make_map(&tv, vt, (uint64_t)Hkv * D, (uint64_t)ldt, (uint64_t)ldt, D);
+  e = make_map(&tv, vt, (uint64_t)Hkv * Dh, (uint64_t)ldt, (uint64_t)ldt, (uint32_t)Dh);
   if (e) return e;
   TcParams p;
-  p.out = (bf16*)out; p.ld_o = ld_o; p.M = M; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.q_pos0 = q_pos0; p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f; p.status = grm_status_ptr();
+  p.out = (bf16*)out; p.ld_o = ld_o; p.gate = (const bf16*)gate; p.ld_g = ld_g; p.M = M; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.q_pos0 = q_pos0;
+  p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = grm_status_ptr();
+  const dim3 grid((M + BQ - 1) / BQ, Hq);
+  if (ws) {
+    if (Dh == 128) flash_prefill_tc_ws_kernel<128><<<grid, kThreadsWs, WsGeom<128>::kSmemBytes, st>>>(tq, tk, tv, p);
+    else flash_prefill_tc_ws_kernel<256><<<grid, kThreadsWs, WsGeom<256>::kSmemBytes, st>>>(tq, tk, tv, p);
+    GRM_LAUNCH_RET();
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t ce = cudaFuncSetAttribute(flash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (ce != cudaSuccess) return (int)ce;
     configured = true;
   }
-  static int ws = -1;
-  if (ws < 0) {
-    const char* e = getenv("GRIMOIRE_FLASH_WS");
-    ws = (e && e[0] == '0') ? 0 : 1;
-    if (ws && cudaFuncSetAttribute(flash_prefill_tc_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) ws = 0;
-  }
-  if (ws)
-    flash_prefill_tc_ws_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreadsWs, kSmem, st>>>(tq, tk, tv, p);
-  else
-    flash_prefill_tc_kernel<<<dim3((M + BQ - 1) / BQ, Hq), kThreads, kSmem, st>>>(tq, tk, tv, p);
+  flash_prefill_tc_kernel<<<grid, kThreads, kSmem, st>>>(tq, tk, tv, p);
   GRM_LAUNCH_RET();
+}
+
+GRM_API int grm_flash_prefill_tc(const void* q, int ld_q, const void* k, const void* v, int ld_kv, void* vt, int ldt, void* out, int ld_o,
+                                 int M, int T, int Hq, int Hkv, int Dh, int q_pos0, int window, float scale, void* stream) {
+  return grm_flash_prefill_tc_gated(q, ld_q, k, v, ld_kv, vt, ldt, nullptr, 0, out, ld_o, M, T, Hq, Hkv, Dh, q_pos0, window, scale, stream);
 }

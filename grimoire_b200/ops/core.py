@@ -354,17 +354,20 @@ def flash_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, geom: AttnG
             o = o * torch.sigmoid(gate.float())
         out.copy_(o.to(out.dtype))
         return out
-    if D == 128 and gate is None and FLASH_TC and M >= 64:
-        # tcgen05 / TMEM kernel; it consumes V transposed, built per call in a workspace buffer
+    if D in (128, 256) and FLASH_TC and M >= 64 and (gate is None or gate.stride(0) % 8 == 0):
+        # tcgen05 / TMEM kernel (head_dim 128, or 256 / gated through its warp-specialised form); it consumes V transposed,
+        # built per call in a workspace buffer.  -2: this shape is not served here -> the warp-MMA kernel below
         from .workspace import default_workspace
 
         ldt = (T + 63) // 64 * 64
         vt = default_workspace(q.device).get("flash_vt", Hkv * D * ldt, torch.bfloat16)
-        code = _native.cuda().grm_flash_prefill_tc(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
-                                                   _native.ptr(vt), _c(ldt), _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq),
-                                                   _c(Hkv), _c(D), _c(q_pos0), _c(geom.window), _f(geom.scale), _native.stream_ptr())
-        _native.check(code, "flash_prefill_tc")
-        return out
+        code = _native.cuda().grm_flash_prefill_tc_gated(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
+                                                         _native.ptr(vt), _c(ldt), _native.ptr(gate), _c(gate.stride(0) if gate is not None else 0),
+                                                         _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq), _c(Hkv), _c(D),
+                                                         _c(q_pos0), _c(geom.window), _f(geom.scale), _native.stream_ptr())
+        if code != -2:
+            _native.check(code, "flash_prefill_tc")
+            return out
     code = _native.cuda().grm_flash_prefill(_native.ptr(q), _c(q.stride(0)), _native.ptr(k), _native.ptr(v), _c(k.stride(0)),
                                             _native.ptr(gate), _native.ptr(out), _c(out.stride(0)), _c(M), _c(T), _c(Hq),
                                             _c(Hkv), _c(D), _c(q_pos0), _c(geom.window), _f(geom.scale),

@@ -304,7 +304,7 @@ def test_rope_kvwrite_and_paged_decode(Hq, Hkv, D, rot, gated, qk):
     _assert_clean()
 
 
-@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64), (4, 1, 256)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 2, 128), (4, 2, 64), (4, 1, 256), (6, 2, 256)])
 @pytest.mark.parametrize("M,pos0,window", [(64, 0, 0), (200, 0, 0), (100, 77, 0), (130, 300, 128), (1024, 512, 0), (700, 333, 256)])
 def test_flash_prefill(Hq, Hkv, D, M, pos0, window):
     torch.manual_seed(7)
@@ -317,6 +317,12 @@ def test_flash_prefill(Hq, Hkv, D, M, pos0, window):
     K.flash_prefill(q, k, v, geom, want, pos0)
     out = torch.zeros(M, Hq * D, dtype=torch.bfloat16, device=DEV)
     K.flash_prefill(q.to(DEV), k.to(DEV), v.to(DEV), geom, out, pos0)
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
+    # gated form (output *= sigmoid(gate)): head_dim 128 / 256 take the tensor-core kernel's epilogue, 64 the warp-MMA kernel
+    gate = torch.randn(M, Hq * D).bfloat16()
+    K.flash_prefill(q, k, v, geom, want, pos0, gate)
+    out.zero_()
+    K.flash_prefill(q.to(DEV), k.to(DEV), v.to(DEV), geom, out, pos0, gate.to(DEV))
     assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2), float((out.float().cpu() - want).abs().max())
 
 
