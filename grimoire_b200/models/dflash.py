@@ -8,8 +8,7 @@ the drafter's own knobs; the attention shape is read from ``layer_types`` / ``df
 / ``is_causal`` / ``dflash_config.causal`` only; a silent config means full, non-causal attention;
 the default RoPE theta is 1e6.  Every one of these is a silent failure when wrong (the verifier just
 rejects the drafts), so each default that is not a checkpoint fact is reported in ``notes`` and
-impossible combinations in ``error``.  The 6-layer draft model itself is not built in this engine;
-speculative decoding uses the MTP head (models/mtp.py) or copy drafts.
+impossible combinations in ``error``.  The draft model itself is models/dflash_drafter.py.
 """
 from __future__ import annotations
 
@@ -36,6 +35,11 @@ class DFlashSettings:
     mask_token: int = -1
     selector_top_k: int = 0
     selector_rank: int = 0
+    conv_kernel_size: int = 0      # second-generation drafter: taps of the grouped dynamic convolutions (0: none)
+    conv_group_size: int = 0
+    input_embedding_scale: float = 1.0
+    output_multiplier: float = 1.0
+    final_logit_softcapping: float = 0.0
     block_size: int = 16
     config_window: int = 0
     rope_theta: float = 1.0e6
@@ -105,6 +109,14 @@ def resolve_dflash_config(text: str) -> DFlashSettings:
     s.use_aux_hidden_state = flag_or("use_aux_hidden_state", True)
     s.selector_top_k = number_or("selector_top_k", 0)
     s.selector_rank = number_or("selector_rank", 0)
+    s.conv_kernel_size = number_or("conv_kernel_size", 0)
+    s.conv_group_size = number_or("conv_group_size", 0)
+    for key in ("input_embedding_scale", "output_multiplier", "final_logit_softcapping"):
+        v = lookup(key, _is_num)
+        if v is not None:
+            setattr(s, key, float(v))
+    if (s.conv_kernel_size > 0) != (s.conv_group_size > 0) and not s.error:
+        s.error = "conv_kernel_size and conv_group_size must be given together"
     s.block_size = number_or("block_size", 16)
     if s.block_size <= 0:
         s.block_size = 16

@@ -16,7 +16,13 @@ layer of tools/ref_qwen3_dflash.py):
 The drafter is small (6 layers) and runs once per speculative round, so its projections are plain bf16 matrix products;
 the block is verified by the target through the engine's batched verify path like any other draft.  Block width: 8 rows
 by default including the bonus row (the reference's measured optimum, grimoire.cpp:16500; ``GRIMOIRE_DFLASH_M`` = 2..16).
-The candidate selector and grouped convolutions of the second-generation drafter are not part of this module.
+
+Second generation (``conv_kernel_size`` / ``selector_rank`` in the draft config; ref/qwen3_dflash2.py, selector kernels
+src/ops.cpp:1885-1940): every layer wraps its attention and its MLP in a grouped dynamic convolution over the block's rows
+(coefficients = a per-(tap, group) base plus a projection of the sublayer's input; row r mixes rows r - tap .. r of the SAME
+block, never across the block start), the block embeddings are scaled, and the head proposes ``selector_top_k`` candidates
+per position whose pair scores unary[c] + <pred[prev] * proj(hidden), succ[c]> are walked greedily from the bonus token, so a
+draft token is chosen given the token drafted before it.
 """
 from __future__ import annotations
 
@@ -48,6 +54,35 @@ class DFlashLayer:
     w_down: torch.Tensor      # [H][I]
     window: int = 0
     causal: bool = False
+    attn_conv: Optional["GroupedConv"] = None      # second generation: dynamic convolutions around attention and MLP
+    mlp_conv: Optional["GroupedConv"] = None
+
+
+@dataclass
+class GroupedConv:
+    base: torch.Tensor        # fp32 [2][taps][H]: side 0 before the sublayer, side 1 after it
+    proj: torch.Tensor        # [2 * taps * groups][H]
+    taps: int
+    group: int
+
+    def _conv(self, x: torch.Tensor, delta: torch.Tensor, side: int) -> torch.Tensor:
+        """x [rows][H] (one block), delta [rows][taps][groups]: out[r] = sum_tap coef[r][tap] * x[r - tap] for r >= tap."""
+        rows, H = x.shape
+        G = H // self.group
+        xb = x.reshape(rows, G, self.group)
+        coef = self.base[side].reshape(1, self.taps, G, self.group) + delta.unsqueeze(-1)
+        out = coef[:, 0] * xb
+        for tap in range(1, min(self.taps, rows)):
+            out[tap:] += coef[tap:, tap] * xb[:-tap]
+        return out.reshape(rows, H)
+
+    def prepare(self, x: torch.Tensor, lin):
+        rows = x.shape[0]
+        co = lin(x, self.proj).reshape(rows, 2, self.taps, x.shape[1] // self.group)
+        return self._conv(x, co[:, 0], 0), co[:, 1]
+
+    def finish(self, y: torch.Tensor, co: torch.Tensor) -> torch.Tensor:
+        return self._conv(y, co, 1)
 
 
 class DFlashModel:
@@ -88,7 +123,17 @@ class DFlashModel:
         self.mask_embedding = mat(get("mask_embedding", required=False))
         d2t = sd.get("d2t")
         self.d2t = None if d2t is None else d2t.to(device=self.device, dtype=torch.long)
+        self.selector = None
+        if st.selector_rank > 0 and st.selector_top_k > 0:
+            self.selector = (mat(get("candidate_selector.predecessor_codebook")), mat(get("candidate_selector.successor_codebook")),
+                             mat(get("candidate_selector.hidden_projection.weight")))
         self.layers: list[DFlashLayer] = []
+
+        def conv(p):
+            if st.conv_kernel_size <= 0:
+                return None
+            return GroupedConv(vec(get(p + "base_kernel")), mat(get(p + "kernel_projection.weight")), st.conv_kernel_size, st.conv_group_size)
+
         for i in range(st.n_layers):
             p = f"layers.{i}."
             at = st.layers[i] if i < len(st.layers) else None
@@ -97,7 +142,8 @@ class DFlashModel:
                 mat(get(p + "self_attn.q_proj.weight")), mat(get(p + "self_attn.k_proj.weight")), mat(get(p + "self_attn.v_proj.weight")),
                 mat(get(p + "self_attn.o_proj.weight")), vec(get(p + "self_attn.q_norm.weight", False)),
                 vec(get(p + "self_attn.k_norm.weight", False)), mat(get(p + "mlp.gate_proj.weight")), mat(get(p + "mlp.up_proj.weight")),
-                mat(get(p + "mlp.down_proj.weight")), window=at.window if at else 0, causal=at.causal if at else False))
+                mat(get(p + "mlp.down_proj.weight")), window=at.window if at else 0, causal=at.causal if at else False,
+                attn_conv=conv(p + "attention_conv."), mlp_conv=conv(p + "mlp_conv.")))
         self.inv_freq = ref.rope_inv_freq(self.D, st.rope_theta).to(self.device)
         self.scale = self.D ** -0.5
 
@@ -129,7 +175,7 @@ class DFlashModel:
         e = table[ids.long()].float()
         if self.mask_embedding is not None and self.st.mask_token >= 0:
             e = torch.where((ids == self.st.mask_token)[:, None], self.mask_embedding.float()[None, :], e)
-        return e
+        return e * self.st.input_embedding_scale
 
     def block(self, h: torch.Tensor, pos: torch.Tensor, ctx_kv, ctx_len: int) -> torch.Tensor:
         """Run the block rows ``h`` [M][H] (embedded) at positions ``pos`` over per-layer context (k, v) of which the first
@@ -140,6 +186,9 @@ class DFlashModel:
         kpos = torch.cat([torch.arange(ctx_len, device=h.device), pos.long()])
         for L, (ck, cv) in zip(self.layers, ctx_kv):
             x = ref.rmsnorm(h, L.in_norm, eps, 0.0)
+            co = None
+            if L.attn_conv is not None:
+                x, co = L.attn_conv.prepare(x, self._lin)
             q = self._heads(self._lin(x, L.wq), self.Hq, L.q_norm, pos)
             k = self._heads(self._lin(x, L.wk), self.Hkv, L.k_norm, pos)
             v = self._lin(x, L.wv).reshape(M, self.Hkv, self.D)
@@ -154,14 +203,41 @@ class DFlashModel:
                 ok &= kpos[None, :] > qp - L.window
             s = s.masked_fill(~ok[:, None, :], float("-inf"))
             o = torch.einsum("mht,thd->mhd", torch.softmax(s, dim=-1), vv).reshape(M, self.Hq * self.D)
-            h = h + self._lin(o, L.wo)
+            a = self._lin(o, L.wo)
+            h = h + (L.attn_conv.finish(a, co) if co is not None else a)
             x = ref.rmsnorm(h, L.post_norm, eps, 0.0)
+            co = None
+            if L.mlp_conv is not None:
+                x, co = L.mlp_conv.prepare(x, self._lin)
             act = F.silu(self._lin(x, L.w_gate)) * self._lin(x, L.w_up)
-            h = h + self._lin(act, L.w_down)
+            y = self._lin(act, L.w_down)
+            h = h + (L.mlp_conv.finish(y, co) if co is not None else y)
         return ref.rmsnorm(h, self.norm, eps, 0.0)
 
     def logits(self, hidden: torch.Tensor, head: torch.Tensor) -> torch.Tensor:
-        return self._lin(hidden, head)
+        lg = self._lin(hidden, head) * self.st.output_multiplier
+        cap = self.st.final_logit_softcapping
+        return torch.tanh(lg / cap) * cap if cap > 0 else lg
+
+    def select(self, hidden: torch.Tensor, head: torch.Tensor, anchor: int) -> torch.Tensor:
+        """Second-generation choice of the draft tokens for the rows ``hidden`` [steps][H] (the mask rows, final-normed):
+        top-k candidates per step, pair scores against the previous step's candidates (the bonus token before step 0), and a
+        greedy walk that picks each step's best candidate given the candidate picked before it.  Draft-vocabulary ids."""
+        pred, succ, proj = self.selector
+        k = self.st.selector_top_k
+        unary, cand = torch.topk(self.logits(hidden, head), k, dim=-1)                 # [steps][k]
+        hp = self._lin(hidden, proj)                                                    # [steps][rank]
+        steps = hidden.shape[0]
+        prev_ids = torch.cat([torch.full((1, k), int(anchor), dtype=torch.long, device=hidden.device), cand[:-1]], dim=0)
+        gated = (pred[prev_ids].float() * hp[:, None, :]).to(self.dtype).float()        # [steps][k prev][rank]
+        pair = torch.einsum("lpr,lcr->lpc", gated, succ[cand].float()).to(self.dtype).float()
+        scores = unary[:, None, :] + pair                                               # [steps][prev][cand]
+        out, previous = [], 0
+        sc = scores.cpu()
+        for step in range(steps):
+            previous = int(sc[step, previous].argmax())
+            out.append(cand[step, previous])
+        return torch.stack(out)
 
     def to_target_ids(self, ids: torch.Tensor) -> torch.Tensor:
         return ids if self.d2t is None else ids + self.d2t[ids]
@@ -257,8 +333,10 @@ class DFlashDrafter:
         h = self.m.embed_block(ids, self.table)
         ctx = [(self.ck[li][seq.slot], self.cv[li][seq.slot]) for li in range(len(self.m.layers))]
         hid = self.m.block(h, pos, ctx, L)
-        lg = self.m.logits(hid[1:], self.head)
-        out = self.m.to_target_ids(lg.argmax(dim=-1))
+        if self.m.selector is not None:
+            out = self.m.to_target_ids(self.m.select(hid[1:], self.head, int(last_token)))
+        else:
+            out = self.m.to_target_ids(self.m.logits(hid[1:], self.head).argmax(dim=-1))
         self.stats["blocks"] += 1
         return [int(t) for t in out.tolist()]
 
@@ -299,6 +377,17 @@ def random_dflash_state_dict(st: DFlashSettings, target_hidden: int, seed: int =
         sd[p + "self_attn.q_norm.weight"], sd[p + "self_attn.k_norm.weight"] = 1 + rnd(D), 1 + rnd(D)
         sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"] = rnd(st.inter, H), rnd(st.inter, H)
         sd[p + "mlp.down_proj.weight"] = rnd(H, st.inter)
+        if st.conv_kernel_size > 0:
+            G = H // st.conv_group_size
+            for c in ("attention_conv.", "mlp_conv."):
+                base = rnd(2, st.conv_kernel_size, H)
+                base[:, 0] += 1.0                      # near the identity: tap 0 carries the row itself
+                sd[p + c + "base_kernel"] = base
+                sd[p + c + "kernel_projection.weight"] = rnd(2 * st.conv_kernel_size * G, H)
+    if st.selector_rank > 0:
+        sd["candidate_selector.predecessor_codebook"] = rnd(st.vocab, st.selector_rank) * 10
+        sd["candidate_selector.successor_codebook"] = rnd(st.draft_vocab, st.selector_rank) * 10
+        sd["candidate_selector.hidden_projection.weight"] = rnd(st.selector_rank, H) * 10
     return sd
 
 

@@ -182,3 +182,72 @@ def test_drafter_on_gpu_keeps_greedy_output_with_graphs():
     assert out == plain
     assert d.stats["blocks"] >= 3 and d.have[seq.slot] == seq.length
     assert K.status_read()[0] == 0
+
+
+DRAFT2_JSON = json.dumps({"num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 4, "num_key_value_heads": 2,
+                          "head_dim": 32, "intermediate_size": 256, "vocab_size": 4096, "rope_theta": 10000.0,
+                          "dflash_config": {"mask_token_id": 4095, "target_layer_ids": [0, 2], "block_size": 8, "conv_kernel_size": 3,
+                                            "conv_group_size": 32, "selector_rank": 16, "selector_top_k": 4,
+                                            "input_embedding_scale": 1.5, "output_multiplier": 0.5, "final_logit_softcapping": 20.0}})
+
+
+def _naive_conv(x, delta, base, taps, gs):
+    rows, H = x.shape
+    out = torch.zeros_like(x)
+    for r in range(rows):
+        for tap in range(taps):
+            if r - tap < 0:
+                continue
+            for c in range(H):
+                out[r, c] += (base[tap, c] + delta[r, tap, c // gs]) * x[r - tap, c]
+    return out
+
+
+def test_second_generation_convolutions_and_selector_match_a_plain_restatement():
+    from grimoire_b200.models.dflash_drafter import GroupedConv
+
+    st = resolve_dflash_config(DRAFT2_JSON)
+    assert not st.error and st.conv_kernel_size == 3 and st.conv_group_size == 32 and st.selector_top_k == 4 and st.selector_rank == 16
+    assert st.input_embedding_scale == 1.5 and st.output_multiplier == 0.5 and st.final_logit_softcapping == 20.0
+    sd = random_dflash_state_dict(st, TARGET.hidden_size, seed=5)
+    m = DFlashModel(st, sd, "cpu", TARGET.hidden_size)
+    assert m.selector is not None and all(L.attn_conv is not None and L.mlp_conv is not None for L in m.layers)
+    # the grouped convolution alone
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(6, 128, generator=g)
+    cv = m.layers[0].attn_conv
+    y, co = cv.prepare(x, m._lin)
+    delta = m._lin(x, cv.proj).reshape(6, 2, 3, 4)
+    assert torch.allclose(y, _naive_conv(x, delta[:, 0], cv.base[0], 3, 32), atol=1e-5)
+    assert torch.allclose(cv.finish(x, co), _naive_conv(x, delta[:, 1], cv.base[1], 3, 32), atol=1e-5)
+    # row 0 of a block never sees an earlier row: the same rows as a block of their own start afresh
+    y2, _ = cv.prepare(x[2:], m._lin)
+    assert torch.allclose(y2[0], (cv.base[0][0] + delta[2, 0, 0].repeat_interleave(32)) * x[2], atol=1e-5)
+    # the selector: pair scores and the greedy walk, restated the way the reference's two kernels do it
+    hidden = torch.randn(5, 128, generator=g)
+    head = m.head
+    got = m.select(hidden, head, anchor=77)
+    lg = m.logits(hidden, head)
+    assert float(lg.abs().max()) <= 20.0
+    unary, cand = torch.topk(lg, 4, dim=-1)
+    pred, succ, proj = (t.float() for t in m.selector)
+    hp = (hidden.bfloat16() @ m.selector[2].t()).float()
+    previous, want = 0, []
+    for step in range(5):
+        pid = 77 if step == 0 else int(cand[step - 1, previous])
+        best, pick = -float("inf"), 0
+        for c in range(4):
+            gated = (pred[pid] * hp[step]).bfloat16().float()
+            s = float(unary[step, c]) + float((gated * succ[int(cand[step, c])]).sum().bfloat16())
+            if s > best:
+                best, pick = s, c
+        want.append(int(cand[step, pick]))
+        previous = pick
+    assert [int(t) for t in got] == want
+    # and through the engine: the output stays the plain greedy output
+    prompt = torch.randint(0, 4000, (45,), generator=torch.Generator().manual_seed(2)).tolist()
+    plain, _ = generate_tokens(_engine(), prompt, GenerationOptions(max_new=12))
+    eng = _engine()
+    d = DFlashDrafter(eng, m, block_rows=5)
+    out, _ = generate_tokens(eng, prompt, GenerationOptions(max_new=12, draft_depth=4, drafter=d))
+    assert out == plain and d.stats["blocks"] >= 2
