@@ -279,6 +279,48 @@ def main() -> int:
         extras["pp4096_cp_vs_baseline"] = round(args.prompt * 1000.0 / cp_ms / BASELINE_PP4096, 2)
         extras["device_status_cp"] = list(K.status_read())
 
+    if not args.skip_extras and world == 1 and args.layers == 64:
+        # ---- the 27B HYBRID (3 Gated DeltaNet : 1 gated attention, head_dim 256, dense FFN, int4): the architecture the
+        #      reference's published 27B numbers were taken on; same prompt length, one user, device-timed ----
+        try:
+            from grimoire_b200.models.config import hybrid_dense_27b
+            from grimoire_b200.models.hybrid import HybridModel
+
+            del eng
+            torch.cuda.empty_cache()
+            hcfg = hybrid_dense_27b(64)
+            hmodel = HybridModel.random(hcfg, dev, seed=0, max_slots=2)
+            heng = Engine(hmodel, EngineLimits(max_slots=2, max_ctx=args.prompt + args.steps + 96, prefill_chunk=args.prompt, max_decode_rows=8))
+            hs = heng.open()
+            heng.prefill(hs, prompts[0])
+            heng.release(hs)
+            hs = heng.open()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            lg = heng.prefill(hs, prompts[1])
+            e1.record()
+            torch.cuda.synchronize()
+            hpp = e0.elapsed_time(e1)
+            graph = heng.build_step_graph([hs], [int(lg.argmax())], steps_ahead=args.steps + 16)
+            for _ in range(max(3, args.warmup)):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            hms = e0.elapsed_time(e1) / args.steps
+            extras["hybrid27b"] = {"model": "27B hybrid (48 Gated DeltaNet + 16 gated attention layers x head_dim 256, dense FFN 17408, int4 g128)",
+                                   "decode_tok_s": round(1000.0 / hms, 2), "decode_ms_per_step": round(hms, 3),
+                                   "pp4096_tok_s": round(args.prompt * 1000.0 / hpp, 1), "pp4096_ms": round(hpp, 2),
+                                   "weight_bytes": hmodel.weight_bytes(), "device_status": list(K.status_read())}
+            del heng, hmodel
+        except Exception as exc:                         # the side measurement must never take the headline line down with it
+            extras["hybrid27b"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+
     if rank == 0:
         sampler.stop()
         clocks = sampler.summary(c_lo, c_hi)
