@@ -51,6 +51,8 @@ def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
     if is_hybrid(cfg):
         if not cfg.is_moe and ec.ep_world > 1:
             return "expert parallelism needs an MoE FFN"
+        if cfg.is_k2 and ec.ep_world > 1:
+            return "the K2-Horizon family is served on one GPU (its router is not built into the expert-parallel chain)"
         if ec.tp_world > 1 or ec.pp_world > 1:
             return "the hybrid (DeltaNet + MoE) family scales by expert parallelism (multi EP); tensor / pipeline stages are not built for it"
         if cfg.num_experts % max(1, ec.ep_world):

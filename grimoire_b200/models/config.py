@@ -71,6 +71,15 @@ class ModelConfig:
     qk_norm_weightless: bool = False        # q / k per-head RMSNorm without a learned weight
     global_nope: bool = False               # global layers apply no rotary embedding at all
     attn_gate_proj: str = ""                # "sigmoid": attention output *= sigmoid(gate_proj(normed layer input))
+    # K2-Horizon family (a Qwen3-MoE with grouped norms, a softplus attention gate, a sigmoid router and a routed value projection)
+    norm_groups: int = 1                    # RMSNorm variance per contiguous group of the row
+    router_sigmoid: bool = False            # sigmoid scores; a router bias steers the selection only
+    router_scale: float = 1.0               # routed weights are multiplied by this after normalisation
+    num_shared_experts: int = 0             # ungated shared expert of width moe_intermediate_size * this
+    mova_experts: int = 0                   # sparse layers replace v_proj by a routed bank of value experts
+    mova_top_k: int = 0
+    mlp_only_layers: list[int] = field(default_factory=list)     # layers with a dense FFN in an MoE model
+    decoder_sparse_step: int = 1            # layer i is sparse when (i + 1) % step == 0 and it is not mlp-only
     # MTP draft head
     mtp_num_hidden_layers: int = 0
     # quantization of the projections in a synthetic / converted model
@@ -107,6 +116,16 @@ class ModelConfig:
     @property
     def is_gemma4(self) -> bool:
         return self.model_type.startswith("gemma4")
+
+    @property
+    def is_k2(self) -> bool:
+        return "k2_horizon" in self.model_type
+
+    def layer_is_sparse(self, i: int) -> bool:
+        """MoE FFN (and, for K2, the routed value projection) on layer i; dense FFN otherwise."""
+        if not self.is_moe or i in self.mlp_only_layers or self.decoder_sparse_step <= 0:
+            return False
+        return (i + 1) % self.decoder_sparse_step == 0
 
     @property
     def is_muse(self) -> bool:
@@ -165,6 +184,8 @@ class ModelConfig:
             return ModelConfig._gemma4_from_hf(cfg, mt, n_layers, heads, hd)
         if "muse_glimmer" in mt:
             return ModelConfig._muse_from_hf(cfg, mt, n_layers, heads, hd)
+        if "k2_horizon" in mt:
+            return ModelConfig._k2_from_hf(cfg, mt, n_layers, heads, hd)
         return ModelConfig(
             model_type=mt,
             hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
@@ -216,6 +237,29 @@ class ModelConfig:
             global_partial_rotary=float(rg.get("partial_rotary_factor", 1.0)), global_rope_factor=float(rg.get("factor", 1.0)),
             global_rope_proportional=rg.get("rope_type", "proportional") == "proportional",
             global_head_dim=int(cfg.get("global_head_dim") or 0), num_global_key_value_heads=int(cfg.get("num_global_key_value_heads") or 0))
+
+    @staticmethod
+    def _k2_from_hf(cfg: dict, mt: str, n_layers: int, heads: int, hd: int) -> "ModelConfig":
+        """K2-Horizon config (src/qwen35_loader.cpp:681-735): grouped norms, attention gate function, sigmoid router with
+        bias and scaling, shared experts as one MLP of moe_intermediate_size * num_shared_experts, MoVA value experts on the
+        sparse layers, dense FFN on ``mlp_only_layers`` / off-step layers; plain-w norms."""
+        rp = cfg.get("rope_parameters") or {}
+        gate = str(cfg.get("attention_gate_func") or "")
+        n_shared, moe_i = int(cfg.get("num_shared_experts", 0)), int(cfg.get("moe_intermediate_size", 0))
+        return ModelConfig(
+            model_type=mt, hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
+            num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd, vocab_size=int(cfg["vocab_size"]),
+            intermediate_size=int(cfg.get("intermediate_size", 0)), rms_norm_eps=float(cfg.get("rms_norm_eps", 1e-6)),
+            rope_theta=float(rp.get("rope_theta", cfg.get("rope_theta", 1e6))), tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+            qk_norm=bool(cfg.get("query_key_norm", False)), norm_zero_centered=False,
+            attn_gate_proj="softplus" if "softplus" in gate else ("sigmoid" if gate else ""),
+            num_experts=int(cfg.get("num_experts", 0)), num_experts_per_tok=int(cfg.get("num_experts_per_tok", 0)),
+            moe_intermediate_size=moe_i, shared_expert_intermediate_size=moe_i * n_shared, num_shared_experts=n_shared,
+            norm_topk_prob=bool(cfg.get("norm_topk_prob", True)), norm_groups=int(cfg.get("layernorm_num_groups", 1)),
+            router_sigmoid="sigmoid" in str(cfg.get("router_score_func") or ""), router_scale=float(cfg.get("router_scaling_factor", 1.0)),
+            mova_experts=int(cfg.get("mova_num_experts", 0)), mova_top_k=int(cfg.get("mova_num_experts_per_tok", 0)),
+            mlp_only_layers=[int(v) for v in (cfg.get("mlp_only_layers") or [])], decoder_sparse_step=int(cfg.get("decoder_sparse_step", 1)),
+            quant="fp8_block")
 
     @staticmethod
     def _muse_from_hf(cfg: dict, mt: str, n_layers: int, heads: int, hd: int) -> "ModelConfig":
@@ -341,5 +385,15 @@ def tiny_muse(layers: int = 4) -> ModelConfig:
                        qk_norm_weightless=True, global_nope=True, attn_gate_proj="sigmoid", quant="int4")
 
 
-PRESETS = {"tiny_muse": tiny_muse, "tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+def tiny_k2(layers: int = 3) -> ModelConfig:
+    """A small K2-Horizon-style decoder: layer 0 dense, the rest sparse (routed value projection + MoE with an ungated
+    shared expert), two-group norms, softplus attention gate, sigmoid router with a selection bias and a scaling factor."""
+    return ModelConfig(model_type="k2_horizon", hidden_size=256, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=4096, intermediate_size=512, qk_norm=True,
+                       attn_gate_proj="softplus", num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=128, num_shared_experts=1, norm_topk_prob=True, norm_groups=2, router_sigmoid=True,
+                       router_scale=2.5, mova_experts=8, mova_top_k=2, mlp_only_layers=[0], decoder_sparse_step=1, quant="fp8_block")
+
+
+PRESETS = {"tiny_k2": tiny_k2, "tiny_muse": tiny_muse, "tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
            "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}

@@ -55,6 +55,10 @@ class HybridLayer:
     moe: Optional[MoEBlock]       # None: dense FFN (ffn_gu / ffn_down)
     ffn_gu: Optional[object] = None
     ffn_down: Optional[object] = None
+    # K2-Horizon: separate attention gate projection (softplus), routed value projection, router selection bias
+    gate_proj: Optional[object] = None
+    mova: Optional[object] = None
+    router_bias: Optional[torch.Tensor] = None
     # gdn
     in_qkv: Optional[Hb.FP8BlockLinear] = None
     in_z: Optional[Hb.FP8BlockLinear] = None
@@ -92,6 +96,9 @@ class HybridBuffers:
         self.act = mk(max_rows * k, cfg.moe_intermediate_size, dt=bf)
         self.y = mk(max_rows * (k + 1), H, dt=f32)
         self.act_s = mk(max_rows, max(cfg.shared_expert_intermediate_size, 0 if cfg.is_moe else cfg.intermediate_size), dt=bf)
+        # dense-FFN layers inside an MoE model (mlp-only / off-step layers) get their own activation rows
+        mixed = cfg.is_moe and not all(cfg.layer_is_sparse(i) for i in range(cfg.num_hidden_layers))
+        self.act_d = mk(max_rows, cfg.intermediate_size, dt=bf) if mixed else self.act_s
         self.pos = mk(max_rows, k + 1, dt=torch.int32)
         self.xf, self.logits = mk(max_logit_rows, H, dt=bf), mk(max_logit_rows, cfg.vocab_size, dt=f32)
         self.next_ids = mk(max_logit_rows, dt=torch.int32)
@@ -115,6 +122,25 @@ class HybridBuffers:
             t[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=dev)
             self._decode_pos[M] = t
         return t
+
+
+class _DictSource:
+    """A state dict behind the tensor-resolver interface ``from_checkpoint`` reads (synthetic weights, tests)."""
+
+    def __init__(self, cfg: ModelConfig, sd: dict):
+        self.cfg, self.sd = cfg, sd
+        self.prefix = "model.language_model." if any(k.startswith("model.language_model.") for k in sd) else "model."
+
+    def linear(self, name: str):
+        return self.sd.get(name + ".weight")
+
+    def plain(self, name: str):
+        return self.sd.get(name)
+
+    tensor = plain
+
+    def embedding(self):
+        return self.sd[self.prefix + "embed_tokens.weight"]
 
 
 class HybridModel:
@@ -242,6 +268,11 @@ class HybridModel:
         """Random-init weights.  ``gen_device`` picks where the numbers are drawn (draw on "cpu" to get
         the same model on a GPU and on the CPU path).  With ``ep_world`` > 1 the rank keeps experts
         [ep_rank * E/W, (ep_rank + 1) * E/W) of every layer (same values as the unsharded model)."""
+        if cfg.is_k2:
+            # the K2 layer mix (dense and sparse layers, routed value experts) is built from named tensors
+            from .synthetic import random_hybrid_state_dict
+
+            return HybridModel.from_checkpoint(_DictSource(cfg, random_hybrid_state_dict(cfg, seed)), device, max_slots=max_slots)
         m = HybridModel(cfg, device, max_slots=max_slots)
         m.ep_rank, m.ep_world = ep_rank, ep_world
         if cfg.num_experts % ep_world or (not cfg.is_moe and ep_world > 1):
@@ -344,6 +375,8 @@ class HybridModel:
 
     def _add_layer(self, i: int, w: dict) -> None:
         """One layer from logical fp32 tensors (``[out][in]``; stored block-fp8 QuantWeights are used as they are).
+        K2-Horizon layers add attn_gate (the softplus gate projection), router_bias, and on sparse layers v_router, v_router_bias,
+        v_experts [Ev][kv][H] instead of v.
         Keys: in_norm, post_norm; for an MoE FFN router [E][H], gate_up [E][2I][H], down [E][H][I] and, with a shared
         expert, shared_gate [1][H], shared_gate_proj, shared_up_proj, shared_down_proj; for a dense FFN ffn_gate, ffn_up,
         ffn_down; then either q, k, v, o, q_norm, k_norm or in_qkv, in_z, in_a, in_b, conv [C][4],
@@ -370,7 +403,7 @@ class HybridModel:
             return q.payload.reshape(e1 - e0, n, k).to(dev).contiguous(), q.scales.reshape(e1 - e0, n, k // 128).float().to(dev).contiguous()
 
         moe, ffn = None, {}
-        if not cfg.is_moe:
+        if not cfg.layer_is_sparse(i):
             ffn = dict(ffn_gu=self._lin_gate_up(w["ffn_gate"], w["ffn_up"], f"L{i}.gate_up"), ffn_down=fp8(w["ffn_down"], f"L{i}.down"))
         else:
             gu8, gus = experts(w["gate_up"])
@@ -378,14 +411,25 @@ class HybridModel:
             sg = w.get("shared_gate")
             router = torch.cat([dense(w["router"]), dense(sg) if sg is not None else torch.zeros(1, cfg.hidden_size)], dim=0)
             shared = w.get("shared_gate_proj") is not None
-            if shared and sg is None:
+            if shared and sg is None and not cfg.is_k2:          # K2's shared experts are ungated
                 raise KeyError(f"layer {i}: a shared expert without its gate (mlp.shared_expert_gate)")
+            if w.get("router_bias") is not None:
+                ffn["router_bias"] = f32(w["router_bias"])
             moe = MoEBlock(BF16Linear(router, dev, f"L{i}.router"), gu8, gus, dn8, dns,
                            Hb.FP8BlockLinear(torch.cat([dense(w["shared_gate_proj"]), dense(w["shared_up_proj"])], dim=0), dev,
                                              f"L{i}.shared_gu") if shared else None,
                            Hb.FP8BlockLinear(w["shared_down_proj"], dev, f"L{i}.shared_down") if shared else None)
         if cfg.is_attention_layer(i):
-            qkv = torch.cat([dense(w["q"]), dense(w["k"]), dense(w["v"])], dim=0)
+            if w.get("v_experts") is not None:
+                # K2 sparse layer: q | k from one projection, v from the routed bank of value experts
+                from ..ops.k2 import MovaValue
+
+                qkv = torch.cat([dense(w["q"]), dense(w["k"])], dim=0)
+                ffn["mova"] = MovaValue(dense(w["v_router"]), w.get("v_router_bias"), w["v_experts"].float(), cfg.mova_top_k, dev)
+            else:
+                qkv = torch.cat([dense(w["q"]), dense(w["k"]), dense(w["v"])], dim=0)
+            if w.get("attn_gate") is not None:
+                ffn["gate_proj"] = fp8(w["attn_gate"], f"L{i}.attn_gate")
             L = HybridLayer("attn", f32(w["in_norm"]), f32(w["post_norm"]), moe, qkv=fp8(qkv, f"L{i}.qkv"), o=fp8(w["o"], f"L{i}.o"),
                             q_norm=f32(w.get("q_norm")), k_norm=f32(w.get("k_norm")),
                             kv_index=sum(1 for l in self.layers if l.kind == "attn"), **ffn)
@@ -433,11 +477,16 @@ class HybridModel:
             w = {"in_norm": need(ck.plain(p + "input_layernorm.weight"), p + "input_layernorm"),
                  "post_norm": need(ck.plain(p + "post_attention_layernorm.weight"), p + "post_attention_layernorm")}
             dq = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
-            if not cfg.is_moe:
+            if not cfg.layer_is_sparse(i):
                 w.update(ffn_gate=lin("mlp.gate_proj"), ffn_up=lin("mlp.up_proj"), ffn_down=lin("mlp.down_proj"))
             else:
                 w["router"] = lin("mlp.gate")
-                if cfg.shared_expert_intermediate_size:
+                if cfg.is_k2:
+                    w["router_bias"] = ck.plain(p + "mlp.gate.bias")
+                    if cfg.shared_expert_intermediate_size:
+                        w.update(shared_gate_proj=lin("mlp.shared_experts.gate_proj"), shared_up_proj=lin("mlp.shared_experts.up_proj"),
+                                 shared_down_proj=lin("mlp.shared_experts.down_proj"))
+                elif cfg.shared_expert_intermediate_size:
                     w.update(shared_gate=ck.linear(p + "mlp.shared_expert_gate"), shared_gate_proj=lin("mlp.shared_expert.gate_proj"),
                              shared_up_proj=lin("mlp.shared_expert.up_proj"), shared_down_proj=lin("mlp.shared_expert.down_proj"))
                 fused_gu, fused_dn = ck.tensor(p + "mlp.experts.gate_up_proj"), ck.tensor(p + "mlp.experts.down_proj")
@@ -452,8 +501,15 @@ class HybridModel:
                     w["gate_up"], w["down"] = torch.stack(gu), torch.stack(dn)
             if cfg.is_attention_layer(i):
                 a = "self_attn."
-                w.update(q=lin(a + "q_proj"), k=lin(a + "k_proj"), v=lin(a + "v_proj"), o=lin(a + "o_proj"),
+                w.update(q=lin(a + "q_proj"), k=lin(a + "k_proj"), o=lin(a + "o_proj"),
                          q_norm=ck.plain(p + a + "q_norm.weight"), k_norm=ck.plain(p + a + "k_norm.weight"))
+                if cfg.attn_gate_proj:
+                    w["attn_gate"] = lin(a + "gate_proj")
+                if cfg.mova_experts and cfg.layer_is_sparse(i):
+                    w.update(v_router=lin(a + "v_router"), v_router_bias=ck.plain(p + a + "v_router.bias"),
+                             v_experts=torch.stack([dq(lin(a + f"v_experts.{e}")) for e in range(cfg.mova_experts)]))
+                else:
+                    w["v"] = lin(a + "v_proj")
             else:
                 a = "linear_attn."
                 w.update(in_qkv=lin(a + "in_proj_qkv"), in_z=lin(a + "in_proj_z"), in_a=lin(a + "in_proj_a"), in_b=lin(a + "in_proj_b"),
@@ -473,7 +529,9 @@ class HybridModel:
             moe = L.moe
             if moe is not None:
                 n += moe.gate_up.numel() + moe.down.numel() + 4 * (moe.gate_up_scale.numel() + moe.down_scale.numel())
-            for lin in (L.in_qkv, L.in_z, L.out_proj, L.qkv, L.o, L.ffn_gu, L.ffn_down, moe and moe.shared_gu, moe and moe.shared_down):
+            if L.mova is not None:
+                n += L.mova.w.numel() + 4 * L.mova.scale.numel()
+            for lin in (L.in_qkv, L.in_z, L.out_proj, L.qkv, L.o, L.ffn_gu, L.ffn_down, L.gate_proj, moe and moe.shared_gu, moe and moe.shared_down):
                 if lin is not None:
                     n += lin.nbytes()
         return n
@@ -487,6 +545,8 @@ class HybridModel:
         E, k, H = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size
         lg = buf.router[:M, : cfg.num_experts + 1]
         moe.router(x, lg, "f32")
+        if cfg.router_sigmoid:
+            return self._moe_k2(L, x, h, buf, M, decode, lg)
         if self.ep is None and not decode and x.is_cuda and M > 64:
             # a prompt chunk on one GPU: group the rows by expert on the device (the expert-parallel chain with
             # this GPU as its only rank) instead of sorting on the host, which would stall the stream every layer
@@ -553,6 +613,57 @@ class HybridModel:
             pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
         Hb.moe_combine(h, y, pos, wts)
 
+    def _moe_k2(self, L: HybridLayer, x, h, buf: HybridBuffers, M: int, decode: bool, lg) -> None:
+        """K2 routing (sigmoid scores, selection-only bias, normalised and scaled weights) with an ungated shared expert, on the
+        plain grouped-GEMM path of one GPU (rows grouped by expert on the host for prompt chunks)."""
+        from ..ops import k2 as K2
+
+        cfg, moe = self.cfg, L.moe
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        if self.ep is not None:
+            raise NotImplementedError("the K2 router is not built into the expert-parallel chain")
+        ids, wts = buf.ids[:M], buf.wts[:M]
+        K2.router_topk_bias(lg[:, :E], L.router_bias, k, ids, wts, True, cfg.norm_topk_prob, cfg.router_scale)
+        wts[:, k] = 1.0
+        act, y, pos = buf.act[: M * k], buf.y[: M * (k + 1)], buf.pos[:M]
+        if decode:
+            te, r0, nr, src = ids.reshape(-1), buf.tile_row0[: M * k], buf.tile_rows[: M * k], buf.tile_src[: M * k]
+            pos = buf.decode_pos(M)
+        else:
+            flat = ids.reshape(-1).long()
+            order = torch.sort(flat, stable=True).indices
+            counts = torch.bincount(flat, minlength=E).cpu()
+            src = (order // k).to(torch.int32)
+            inv = torch.empty_like(order)
+            inv[order] = torch.arange(order.numel(), device=order.device)
+            pos[:, :k] = inv.reshape(M, k).to(torch.int32)
+            tiles_per = (counts + 15) // 16
+            starts = torch.cumsum(counts, 0) - counts
+            te = torch.repeat_interleave(torch.arange(E), tiles_per)
+            within = torch.arange(int(tiles_per.sum())) - torch.repeat_interleave(torch.cumsum(tiles_per, 0) - tiles_per, tiles_per)
+            r0c = starts[te] + within * 16
+            nrc = torch.minimum(torch.full_like(r0c, 16), counts[te] - within * 16)
+            te, r0, nr = (t.to(torch.int32).to(x.device) for t in (te, r0c, nrc))
+        Hb.grouped_gemm_fp8(x, src, te, r0, nr, moe.gate_up, moe.gate_up_scale, act, "swiglu", small=decode)
+        Hb.grouped_gemm_fp8(act, None, te, r0, nr, moe.down, moe.down_scale, y, "f32", small=decode)
+        if moe.shared_gu is None:
+            y[M * k: M * (k + 1)].zero_()
+        else:
+            moe.shared_gu(x, buf.act_s[:M], "swiglu")
+            moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
+        if not decode:
+            pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
+        Hb.moe_combine(h, y, pos, wts)
+
+    def _norm(self, h, w, x) -> None:
+        cfg = self.cfg
+        if cfg.norm_groups > 1:
+            from ..ops import k2 as K2
+
+            K2.rmsnorm_grouped(h, w, x, cfg.norm_groups, cfg.rms_norm_eps)
+        else:
+            K.add_rmsnorm(h, w, x, cfg.rms_norm_eps, cfg.norm_offset)
+
     def forward(self, rb: RowBatch, buf: HybridBuffers, kv_layers, block_table) -> torch.Tensor:
         cfg, geom = self.cfg, self.geom
         M = rb.tokens.shape[0]
@@ -577,7 +688,7 @@ class HybridModel:
         for L in self.layers:
             if tl: trace.mark("gdn: norm + in projections" if L.kind == "gdn" else "attn: norm + qkv")
             if L.kind == "gdn":
-                K.add_rmsnorm(h, L.in_norm, x, eps, off)
+                self._norm(h, L.in_norm, x)
                 si = L.state_index
                 L.in_qkv(x, buf.gdn_qkv[:M], "bf16")
                 L.in_z(x, buf.gdn_z[:M], "bf16")
@@ -595,7 +706,19 @@ class HybridModel:
                 kvl = kv_layers[L.kv_index]
                 qkv, q, attn = buf.qkv[:M], buf.q[:M], buf.attn[:M]
                 gate = buf.gate[:M] if geom.q_gated else None
-                DenseModel._norm_linear(L.qkv, h, L.in_norm, x, qkv, "bf16", eps, off)      # norm inside the one-row GEMV when it can
+                if L.mova is not None or L.gate_proj is not None or cfg.norm_groups > 1:
+                    # K2: the normed input feeds q | k, the routed value projection and the gate projection
+                    self._norm(h, L.in_norm, x)
+                    if L.mova is not None:
+                        nqk = L.qkv.N
+                        L.qkv(x, qkv[:, :nqk], "bf16")
+                        L.mova(x, qkv[:, nqk:])
+                    else:
+                        L.qkv(x, qkv, "bf16")
+                    if L.gate_proj is not None:
+                        L.gate_proj(x, buf.gate[:M], "bf16")
+                else:
+                    DenseModel._norm_linear(L.qkv, h, L.in_norm, x, qkv, "bf16", eps, off)   # norm inside the one-row GEMV when it can
                 if tl: trace.mark("attn: rope + attention")
                 if prefill:
                     if rb.q_pos0 > 0:
@@ -606,15 +729,23 @@ class HybridModel:
                 else:
                     K.rope_kvwrite(qkv, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, gate)
                     K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn, rb.splits, self.ws, gate)
+                if L.gate_proj is not None:
+                    from ..ops import k2 as K2
+
+                    K2.softplus_gate(attn, buf.gate[:M], attn)
                 if tl: trace.mark("attn: o_proj")
                 L.o(attn, h, "add_f32")
             if tl: trace.mark("ffn")
             if L.moe is None:
-                act = buf.act_s[:M]
-                DenseModel._norm_linear(L.ffn_gu, h, L.post_norm, x, act, "swiglu", eps, off)
+                act = buf.act_d[:M]
+                if cfg.norm_groups > 1:
+                    self._norm(h, L.post_norm, x)
+                    L.ffn_gu(x, act, "swiglu")
+                else:
+                    DenseModel._norm_linear(L.ffn_gu, h, L.post_norm, x, act, "swiglu", eps, off)
                 L.ffn_down(act, h, "add_f32")
             else:
-                K.add_rmsnorm(h, L.post_norm, x, eps, off)
+                self._norm(h, L.post_norm, x)
                 self._moe(L, x, h, buf, M, decode=not prefill)
         if tl: trace.mark("head")
         if rb.logits_rows is None:
@@ -623,7 +754,7 @@ class HybridModel:
             n = rb.logits_rows.shape[0]
             hsel = h.index_select(0, rb.logits_rows) if n != M else h
         xf, logits = buf.xf[:n], buf.logits[:n]
-        K.add_rmsnorm(hsel, self.final_norm, xf, eps, off)
+        self._norm(hsel, self.final_norm, xf)
         self.lm_head(xf, logits, "f32")
         if tl: trace.mark("end")
         return logits

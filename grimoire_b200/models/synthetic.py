@@ -76,13 +76,27 @@ def random_hybrid_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02,
             sd[a + "A_log"], sd[a + "dt_bias"] = rnd(Hv, scale=0.5), rnd(Hv, scale=0.5)
             sd[a + "norm.weight"] = 1.0 + rnd(Dv, scale=0.05)
             sd[a + "out_proj.weight"] = rnd(H, Hv * Dv)
+        if cfg.attn_gate_proj and cfg.is_attention_layer(i):
+            sd[p + "self_attn.gate_proj.weight"] = rnd(cfg.num_attention_heads * D, H)
+        if cfg.mova_experts and cfg.layer_is_sparse(i) and cfg.is_attention_layer(i):
+            # K2 sparse layer: the value projection is a routed bank of experts with its own sigmoid router
+            sd.pop(p + "self_attn.v_proj.weight", None)
+            sd[p + "self_attn.v_router.weight"] = rnd(cfg.mova_experts, H, scale=0.1)      # sigmoid scores: keep the logits off saturation
+            sd[p + "self_attn.v_router.bias"] = rnd(cfg.mova_experts, scale=0.2)
+            for e in range(cfg.mova_experts):
+                sd[p + f"self_attn.v_experts.{e}.weight"] = rnd(cfg.kv_size, H, scale=0.1)
         m = p + "mlp."
-        if not cfg.is_moe:                         # dense FFN (the 27B hybrid)
+        if not cfg.layer_is_sparse(i):             # dense FFN (the 27B hybrid; the mlp-only layers of an MoE model)
             sd[m + "gate_proj.weight"], sd[m + "up_proj.weight"] = rnd(cfg.intermediate_size, H), rnd(cfg.intermediate_size, H)
             sd[m + "down_proj.weight"] = rnd(H, cfg.intermediate_size)
             continue
-        sd[m + "gate.weight"] = rnd(E, H, scale=0.5)
-        if Is:
+        sd[m + "gate.weight"] = rnd(E, H, scale=0.1 if cfg.router_sigmoid else 0.5)
+        if cfg.is_k2:
+            sd[m + "gate.bias"] = rnd(E, scale=0.2)
+            if Is:
+                sd[m + "shared_experts.gate_proj.weight"], sd[m + "shared_experts.up_proj.weight"] = rnd(Is, H), rnd(Is, H)
+                sd[m + "shared_experts.down_proj.weight"] = rnd(H, Is)
+        elif Is:
             sd[m + "shared_expert_gate.weight"] = rnd(1, H, scale=0.5)
             sd[m + "shared_expert.gate_proj.weight"], sd[m + "shared_expert.up_proj.weight"] = rnd(Is, H), rnd(Is, H)
             sd[m + "shared_expert.down_proj.weight"] = rnd(H, Is)

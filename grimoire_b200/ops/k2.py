@@ -87,8 +87,10 @@ class MovaValue:
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """x bf16 [M][H] -> out bf16 [M][kv_heads * head_dim] (M <= max_rows: decode rows / verify blocks)."""
         M, k = x.shape[0], self.top_k
-        if M > self.max_rows:
-            raise ValueError("MovaValue serves decode-sized inputs")
+        if M > self.max_rows:                      # prompt chunks: in pieces of the staging buffers' height
+            for m0 in range(0, M, self.max_rows):
+                self.forward(x[m0: m0 + self.max_rows], out[m0: m0 + self.max_rows])
+            return out
         lg = self.logits[:M, : self.E]
         self.router(x, lg, "f32")
         ids, wts = self.ids[:M], self.wts[:M]

@@ -11,7 +11,7 @@ import torch
 import torch.nn.functional as F
 
 from ..models.config import ModelConfig
-from . import gdn_ref, moe_ref
+from . import gdn_ref, k2_ref, moe_ref
 from ..ops import ref
 
 
@@ -29,9 +29,12 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
     scale = cfg.softmax_scale or ref.softmax_scale(D)
     h = sd[pfx + "embed_tokens.weight"].bfloat16().float()[torch.tensor(tokens, dtype=torch.long)]
     bf = lambda t: t.bfloat16().float()
+    # K2: the variance of every RMSNorm over the residual is taken per contiguous group of the row
+    rms = (lambda t, w: k2_ref.rmsnorm_grouped(t, w.float(), cfg.norm_groups, eps)) if cfg.norm_groups > 1 else \
+          (lambda t, w: ref.rmsnorm(t, w.float(), eps, off))
     for i in range(cfg.num_hidden_layers):
         p = f"{pfx}layers.{i}."
-        x = bf(ref.rmsnorm(h, sd[p + "input_layernorm.weight"].float(), eps, off))
+        x = bf(rms(h, sd[p + "input_layernorm.weight"]))
         if cfg.is_attention_layer(i):
             a = p + "self_attn."
             if cfg.attn_output_gate:
@@ -40,13 +43,19 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
             else:
                 q, gate = (x @ wf(sd[a + "q_proj.weight"]).t()).reshape(T, Hq, D), None
             k = (x @ wf(sd[a + "k_proj.weight"]).t()).reshape(T, Hkv, D)
-            v = (x @ wf(sd[a + "v_proj.weight"]).t()).reshape(T, Hkv, D)
+            if a + "v_router.weight" in sd:          # K2 sparse layer: routed value projection
+                ex = torch.stack([wf(sd[a + f"v_experts.{e}.weight"]) for e in range(cfg.mova_experts)])
+                v = k2_ref.mova_value(x, bf(sd[a + "v_router.weight"]), sd.get(a + "v_router.bias"), ex, cfg.mova_top_k).reshape(T, Hkv, D)
+            else:
+                v = (x @ wf(sd[a + "v_proj.weight"]).t()).reshape(T, Hkv, D)
             qn, kn = sd.get(a + "q_norm.weight"), sd.get(a + "k_norm.weight")
             q = ref.apply_rope(ref.head_rmsnorm(bf(q), None if qn is None else qn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
             k = ref.apply_rope(ref.head_rmsnorm(bf(k), None if kn is None else kn.float(), eps, off), pos, inv_freq, cfg.rot_dim)
             o = ref.attention_rows(q, k, bf(v), pos, scale, cfg.sliding_window).reshape(T, Hq * D)
             if gate is not None:
                 o = o * torch.sigmoid(bf(gate))
+            if cfg.attn_gate_proj == "softplus":     # K2: a separate gate projection of the normed layer input, softplus(beta = ln 2)
+                o = k2_ref.softplus_gate(bf(o), bf(x @ wf(sd[a + "gate_proj.weight"]).t()))
             h = h + bf(o) @ wf(sd[a + "o_proj.weight"]).t()
         else:
             a = p + "linear_attn."
@@ -65,9 +74,9 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
             o = gdn_ref.gdn_sequence(S, q, k, v, al, be)
             o = bf(gdn_ref.gated_rmsnorm(o, z, sd[a + "norm.weight"], eps)).reshape(T, Hv * Dv)
             h = h + o @ wf(sd[a + "out_proj.weight"]).t()
-        x = bf(ref.rmsnorm(h, sd[p + "post_attention_layernorm.weight"].float(), eps, off))
+        x = bf(rms(h, sd[p + "post_attention_layernorm.weight"]))
         m = p + "mlp."
-        if not cfg.is_moe:
+        if not cfg.layer_is_sparse(i):
             act = bf(F.silu(x @ wf(sd[m + "gate_proj.weight"]).t()) * (x @ wf(sd[m + "up_proj.weight"]).t()))
             h = h + act @ wf(sd[m + "down_proj.weight"]).t()
             continue
@@ -78,6 +87,19 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
         else:
             experts = [(wf(sd[f"{m}experts.{e}.gate_proj.weight"]), wf(sd[f"{m}experts.{e}.up_proj.weight"]),
                         wf(sd[f"{m}experts.{e}.down_proj.weight"])) for e in range(E)]
+        if cfg.is_k2:
+            # sigmoid router, bias on the selection only, normalised and scaled weights; ungated shared expert
+            ids, w = k2_ref.router_topk(x.bfloat16().float() @ bf(sd[m + "gate.weight"]).t(), sd.get(m + "gate.bias"), cfg.num_experts_per_tok,
+                                        cfg.router_sigmoid, cfg.norm_topk_prob, cfg.router_scale)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                for j in range(cfg.num_experts_per_tok):
+                    y[t] += w[t, j] * moe_ref.expert_ffn(x[t: t + 1], *experts[int(ids[t, j])])[0]
+            if m + "shared_experts.gate_proj.weight" in sd:
+                y += moe_ref.expert_ffn(x, wf(sd[m + "shared_experts.gate_proj.weight"]), wf(sd[m + "shared_experts.up_proj.weight"]),
+                                        wf(sd[m + "shared_experts.down_proj.weight"]))
+            h = h + y
+            continue
         shared = sgate = None
         if m + "shared_expert.gate_proj.weight" in sd:
             shared = (wf(sd[m + "shared_expert.gate_proj.weight"]), wf(sd[m + "shared_expert.up_proj.weight"]),
@@ -85,6 +107,6 @@ def forward_logits(cfg: ModelConfig, sd: dict, tokens, weight_fn=None) -> torch.
             sgate = bf(sd[m + "shared_expert_gate.weight"]) if m + "shared_expert_gate.weight" in sd else None
         y, _, _ = moe_ref.moe_forward(x, bf(sd[m + "gate.weight"]), experts, cfg.num_experts_per_tok, shared, sgate, cfg.norm_topk_prob)
         h = h + y
-    xf = bf(ref.rmsnorm(h, sd[pfx + "norm.weight"].float(), eps, off))
+    xf = bf(rms(h, sd[pfx + "norm.weight"]))
     head = sd.get("lm_head.weight", sd[pfx + "embed_tokens.weight"])
     return xf @ wf(head).t()

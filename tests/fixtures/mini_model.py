@@ -76,6 +76,13 @@ def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_e
           "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
           "intermediate_size": cfg.intermediate_size, "attn_output_gate": cfg.attn_output_gate, "qk_norm": cfg.qk_norm,
           "norm_zero_centered": cfg.norm_zero_centered}
+    if cfg.is_k2:
+        hf.update({"layernorm_num_groups": cfg.norm_groups, "attention_gate_func": "softplus" if cfg.attn_gate_proj == "softplus" else "",
+                   "router_score_func": "sigmoid" if cfg.router_sigmoid else "softmax", "router_scaling_factor": cfg.router_scale,
+                   "num_shared_experts": cfg.num_shared_experts, "mova_num_experts": cfg.mova_experts,
+                   "mova_num_experts_per_tok": cfg.mova_top_k, "mlp_only_layers": cfg.mlp_only_layers,
+                   "decoder_sparse_step": cfg.decoder_sparse_step, "query_key_norm": cfg.qk_norm, "moe_gate_bias": True})
+        hf.pop("layer_types")
     (path / "config.json").write_text(json.dumps(hf))
     save_file({k: v.bfloat16() for k, v in sd.items()}, path / "model.safetensors", {"format": "pt"})
     return sd

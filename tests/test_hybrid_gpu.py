@@ -57,6 +57,34 @@ def test_hybrid_gpu_matches_cpu_path_and_graph_replay(kind):
     assert K.status_read()[0] == 0
 
 
+def test_k2_horizon_layers_on_gpu():
+    """K2-Horizon layer mix on the GPU (grouped norms, routed value projection, softplus gate, sigmoid router with selection
+    bias: csrc/kernels/k2_ops.cu) against the CPU path of the same weights.  The routers are random, so a near-tie may pick
+    another expert on the two devices; the bound is therefore looser than for the other families (exactness against the fp32
+    oracle is pinned on the CPU path, tests/test_load_paths.py), while graph replay must equal eager execution exactly."""
+    cfg = ModelConfig(model_type="k2_horizon", hidden_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                      head_dim=128, vocab_size=4096, intermediate_size=1024, qk_norm=True, attn_gate_proj="softplus", num_experts=16,
+                      num_experts_per_tok=4, moe_intermediate_size=128, shared_expert_intermediate_size=128, num_shared_experts=1,
+                      norm_groups=2, router_sigmoid=True, router_scale=2.5, mova_experts=8, mova_top_k=2, mlp_only_layers=[0],
+                      quant="fp8_block")
+    gpu = Engine(HybridModel.random(cfg, "cuda", seed=14, max_slots=3), EngineLimits(**LIM))
+    cpu = Engine(HybridModel.random(cfg, "cpu", seed=14, max_slots=3), EngineLimits(**LIM))
+    assert [(L.moe is not None, L.mova is not None) for L in gpu.model.layers] == [(False, False), (True, True), (True, True)]
+    prompt = torch.randint(0, 4096, (90,), generator=torch.Generator().manual_seed(5)).tolist()
+    sg, sc = gpu.open(), cpu.open()
+    lg, lc = gpu.prefill(sg, prompt).float().cpu(), cpu.prefill(sc, prompt).float()
+    scale = max(1.0, float(lc.abs().max()))
+    assert float((lg - lc).abs().max()) < 0.15 * scale, (float((lg - lc).abs().max()), scale)
+    tok = int(lc.argmax())
+    pos = sc.length
+    _, l2c = cpu.decode_rows([tok], [sc], [pos], return_logits=True)
+    _, l2g = gpu.decode_rows([tok], [sg], [pos], use_graph=False, return_logits=True)
+    assert float((l2g[0].float().cpu() - l2c[0]).abs().max()) < 0.15 * scale
+    gpu.release(sg); cpu.release(sc)
+    assert gpu.generate(prompt, 8, use_graph=False) == gpu.generate(prompt, 8, use_graph=True)
+    assert K.status_read()[0] == 0
+
+
 @pytest.mark.parametrize("keep", [1, 2, 4])
 def test_hybrid_verify_block_rollback_equals_sequential_gpu(keep):
     """A four-row verify block through the DeltaNet layers, rolled back to ``keep`` rows: the next single step must see the
