@@ -211,6 +211,9 @@ class ModelConfig:
             shared_expert_intermediate_size=int(cfg.get("shared_expert_intermediate_size", 0)),
             norm_topk_prob=bool(cfg.get("norm_topk_prob", True)),
             mtp_num_hidden_layers=int(cfg.get("mtp_num_hidden_layers", 0)),
+            # Qwen3-MoE: dense FFN on the listed layers and on the layers off the sparse step
+            mlp_only_layers=[int(v) for v in (cfg.get("mlp_only_layers") or [])],
+            decoder_sparse_step=int(cfg.get("decoder_sparse_step", 1) or 1),
         )
 
     @staticmethod

@@ -76,6 +76,8 @@ def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_e
           "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
           "intermediate_size": cfg.intermediate_size, "attn_output_gate": cfg.attn_output_gate, "qk_norm": cfg.qk_norm,
           "norm_zero_centered": cfg.norm_zero_centered}
+    if cfg.mlp_only_layers or cfg.decoder_sparse_step != 1:
+        hf.update({"mlp_only_layers": cfg.mlp_only_layers, "decoder_sparse_step": cfg.decoder_sparse_step})
     if cfg.is_k2:
         hf.update({"layernorm_num_groups": cfg.norm_groups, "attention_gate_func": "softplus" if cfg.attn_gate_proj == "softplus" else "",
                    "router_score_func": "sigmoid" if cfg.router_sigmoid else "softmax", "router_scaling_factor": cfg.router_scale,

@@ -99,6 +99,27 @@ def test_hybrid_family_neighbours_match_fp32_oracle(preset, tmp_path):
     g.close()
 
 
+def test_qwen3_moe_with_dense_layers_on_the_sparse_step(tmp_path):
+    """Qwen3-MoE's ``mlp_only_layers`` / ``decoder_sparse_step``: dense and MoE feed-forwards in one model."""
+    import dataclasses
+
+    from grimoire_b200.models.config import ModelConfig, tiny_moe
+
+    cfg = dataclasses.replace(tiny_moe(4), intermediate_size=384, mlp_only_layers=[0], decoder_sparse_step=2)
+    assert [cfg.layer_is_sparse(i) for i in range(4)] == [False, True, False, True]
+    sd = write_hybrid_checkpoint(tmp_path / "m", cfg, seed=3)
+    parsed = ModelConfig.from_dir(tmp_path / "m")
+    assert parsed.mlp_only_layers == [0] and parsed.decoder_sparse_step == 2
+    g = Grimoire.load(_ec(tmp_path / "m"), device="cpu")
+    assert [L.moe is not None for L in g.model.layers] == [False, True, False, True]
+    ids = _prompt(19, 4)
+    got = g.score_ids(ids)
+    q = lambda w: quantize(w.bfloat16().float(), Fmt.FP8_BLOCK).dequant().float()
+    want = hybrid_reference.forward_logits(cfg, {k: v.bfloat16().float() for k, v in sd.items()}, ids, weight_fn=q)
+    assert float((got - want).abs().max()) < 0.06 * float(want.abs().max())
+    g.close()
+
+
 def test_k2_horizon_checkpoint_matches_fp32_oracle(tmp_path):
     """K2-Horizon: dense first layer, sparse layers with the routed value projection and the sigmoid / selection-bias router,
     two-group norms, softplus attention gate, ungated shared expert -- config parsing, loading by the family's tensor names,
