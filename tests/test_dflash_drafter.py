@@ -251,3 +251,31 @@ def test_second_generation_convolutions_and_selector_match_a_plain_restatement()
     d = DFlashDrafter(eng, m, block_rows=5)
     out, _ = generate_tokens(eng, prompt, GenerationOptions(max_new=12, draft_depth=4, drafter=d))
     assert out == plain and d.stats["blocks"] >= 2
+
+
+def test_block_drafter_under_the_continuous_batching_scheduler():
+    """Two conversations decoded together by the scheduler with the block drafter attached: per-conversation context caches
+    stay in step through interleaved verify blocks, and every conversation's output equals its plain greedy output."""
+    import threading
+
+    from grimoire_b200.sched.scheduler import Scheduler
+
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 4000, (n,), generator=g).tolist() for n in (21, 40)]
+    alone = [generate_tokens(_engine(), p, GenerationOptions(max_new=12))[0] for p in prompts]
+    eng = _engine()
+    st = resolve_dflash_config(DRAFT_JSON)
+    d = DFlashDrafter(eng, DFlashModel(st, random_dflash_state_dict(st, TARGET.hidden_size, seed=3), "cpu", TARGET.hidden_size), block_rows=4)
+    s = Scheduler(eng, width=2, interleave_chunk=32, prefill_chunk=32, hold_ms=20.0, depths=(3, 3), spec_rows=16, drafter=d)
+    res = [None, None]
+
+    def work(i):
+        res[i] = s.generate(prompts[i], 12)
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    [t.start() for t in ts]
+    [t.join(timeout=180) for t in ts]
+    s.shutdown()
+    for i in range(2):
+        assert res[i] is not None and res[i][0] == alone[i], (i, res[i], alone[i])
+    assert d.stats["blocks"] >= 2
