@@ -279,3 +279,24 @@ def test_block_drafter_under_the_continuous_batching_scheduler():
     for i in range(2):
         assert res[i] is not None and res[i][0] == alone[i], (i, res[i], alone[i])
     assert d.stats["blocks"] >= 2
+
+
+def test_block_drafter_taps_a_sandwich_norm_target():
+    """The reference taps Muse-Glimmer and Gemma-4 targets for its block drafter (forward_muse / forward_gemma4 store the
+    taps): the sandwich decoder keeps the same residual taps, so the drafter attaches to it unchanged."""
+    from grimoire_b200.models.config import tiny_muse
+    from grimoire_b200.models.gemma4 import MuseModel
+    from grimoire_b200.models.synthetic import random_gemma4_state_dict
+
+    cfg = tiny_muse()
+    sd = random_gemma4_state_dict(cfg, 3)
+    lim = EngineLimits(max_slots=2, max_ctx=160, prefill_chunk=32, max_decode_rows=16)
+    prompt = torch.randint(0, 4000, (45,), generator=torch.Generator().manual_seed(2)).tolist()
+    plain, _ = generate_tokens(Engine(MuseModel.from_state_dict(cfg, sd, "cpu"), lim), prompt, GenerationOptions(max_new=10))
+    eng = Engine(MuseModel.from_state_dict(cfg, sd, "cpu"), lim)
+    st = resolve_dflash_config(DRAFT_JSON)
+    d = DFlashDrafter(eng, DFlashModel(st, random_dflash_state_dict(st, cfg.hidden_size, seed=3), "cpu", cfg.hidden_size), block_rows=4)
+    seq = eng.open()
+    out, _ = generate_tokens(eng, prompt, GenerationOptions(max_new=10, draft_depth=3, drafter=d), seq=seq)
+    assert out == plain and d.stats["blocks"] >= 2 and d.have[seq.slot] == seq.length
+    assert float(eng.decode_buf.taps.abs().max()) > 0
