@@ -90,7 +90,7 @@ class Grimoire:
 
     # ---- construction ----
     @classmethod
-    def load(cls, ec: EngineConfig, device: Optional[str] = None, tp=None, pp=None, ep_group=None) -> "Grimoire":
+    def load(cls, ec: EngineConfig, device: Optional[str] = None, tp=None, pp=None, ep_group=None, up_group=None) -> "Grimoire":
         """Build model + engine for ``ec.model``: ``synthetic:<preset>``, a HF directory (dense or hybrid family), a
         ``.gguf`` file, or a pre-quantised artifact (``model-v3.grm`` / its bundle directory).  ``tp`` / ``pp`` are this
         rank's TensorParallel / PipelineParallel objects, ``ep_group`` the expert-parallel process group."""
@@ -200,6 +200,13 @@ class Grimoire:
             pp.attach(model)
         if hybrid and ep_group is not None and ec.ep_world > 1:
             model.attach_ep(ep_group, max_rows=max(ec.prefill_chunk, 64))
+        if up_group is not None:
+            # head / sequence exchange over whole-model replicas: the KV pool below is sized from the (now local) head geometry
+            from .parallel.ulysses import UlyssesParallel
+
+            if hybrid or cfg.is_sandwich or ec.tp_world > 1 or ec.pp_world > 1:
+                raise UnsupportedModel("the head / sequence exchange (multi UP) runs over whole replicas of the dense decoder family")
+            UlyssesParallel(up_group, dev).attach(model)
         # draft head: only on a single-stage, single-rank dense model (the reference drafts on the last stage)
         want_mtp = mtp_src is not None and ec.tp_world == 1 and ec.pp_world == 1
         lim = EngineLimits(max_slots=ec.seq_slots, max_ctx=ec.ctx, prefill_chunk=ec.prefill_chunk, max_decode_rows=64,

@@ -114,7 +114,7 @@ def _generate(argv) -> int:
 
 def _multi(argv) -> int:
     ap = argparse.ArgumentParser(prog="grimoire multi")
-    ap.add_argument("mode", choices=["TP", "PP", "EP", "CP", "DP", "tp", "pp", "ep", "cp", "dp"])
+    ap.add_argument("mode", choices=["TP", "PP", "EP", "CP", "UP", "DP", "tp", "pp", "ep", "cp", "up", "dp"])
     ap.add_argument("--gpus", type=int, default=0, help="ranks to start (default: all visible GPUs)")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--master-port", type=int, default=29555)

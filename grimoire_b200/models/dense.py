@@ -113,6 +113,7 @@ class DenseModel:
         self.layer_end = self.layer_begin + per + (1 if pp_rank < extra else 0)
         self.pp = None          # parallel.pp.PipelineParallel when pp_world > 1
         self.cp = None          # parallel.cp.ContextParallel: prefill chunks split by rows over whole-model replicas
+        self.up = None          # parallel.ulysses.UlyssesParallel: head-parallel attention, KV heads sharded over replicas
         self.head_split = None  # (first vocabulary row, rows) of this rank's lm_head shard (TensorParallel.split_head)
         self.tap_index: dict[int, int] = {}   # layer id -> slot of buf.taps (set_taps): residual after that layer is kept per row
         self.ws = workspace or Workspace(device)
@@ -528,8 +529,64 @@ class DenseModel:
         torch.distributed.all_reduce(sel, group=cp.group)
         return self._head(sel, buf, nl, rb)
 
+    def forward_ulysses(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
+        """Head-parallel attention over whole-model replicas (parallel/ulysses.py).  ``self.geom`` and the KV cache hold this
+        rank's heads only.  A prompt chunk whose rows divide over the ranks is row-split outside attention (two all-to-alls per
+        layer); every other pass runs its projections replicated and all-gathers the attention output."""
+        cfg, geom, up = self.cfg, self.geom, self.up
+        M = rb.tokens.shape[0]
+        eps, off = cfg.rms_norm_eps, cfg.norm_offset
+        prefill = rb.mode == "prefill"
+        if prefill and rb.segments is not None:
+            raise NotImplementedError("several prompts in one pass are not built for the head / sequence exchange")
+        split = prefill and up.split_ready(M)
+        a, b = up.local_rows(M) if split else (0, M)
+        n = b - a
+        h, x, act = buf.h[:n], buf.x[:n], buf.act[:n]
+        qkv_h, q, attn_h = buf.qkv[:M], buf.q[:M], buf.attn[:M]                  # local-head layouts, all M rows
+        qw_full = up.full.Hq * up.full.D
+        qkv_full = up.scratch("qkv_full", n, qw_full + 2 * up.full.Hkv * up.full.D)
+        K.embed(rb.tokens[a:b], self.embed, h)
+        T = rb.q_pos0 + M
+        up.stats["split_chunks" if split else "replicated_passes"] += 1
+        for li, L in enumerate(self.layers):
+            kvl = kv_layers[li]
+            self._norm_linear(L.qkv, h, L.in_norm, x, qkv_full, "bf16", eps, off)
+            if split:
+                qkv_h.copy_(up.rows_to_heads(qkv_full, M))
+            else:
+                qkv_h.copy_(up.head_columns(qkv_full, up.rank))
+            if prefill:
+                if rb.q_pos0 > 0:
+                    K.gather_kv_dense(kvl, block_table[rb.seq_slot], rb.q_pos0, buf.dense_k, buf.dense_v)
+                K.rope_kvwrite(qkv_h, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, None,
+                               buf.dense_k[rb.q_pos0: T], buf.dense_v[rb.q_pos0: T])
+                K.flash_prefill(q, buf.dense_k, buf.dense_v, geom, attn_h, rb.q_pos0, None)
+            else:
+                K.rope_kvwrite(qkv_h, rb.row_pos, rb.row_seq, block_table, self.inv_freq, geom, q, kvl, L.q_norm, L.k_norm, None)
+                if not (rb.verify is not None and K.paged_verify_attn(q, rb.verify[0], rb.verify[1], block_table, kvl, geom, attn_h,
+                                                                      rb.splits, self.ws, None)):
+                    K.paged_decode_attn(q, rb.row_seq, rb.row_pos, block_table, kvl, geom, attn_h, rb.splits, self.ws, None)
+            attn = up.heads_to_rows(attn_h, M) if split else up.gather_heads(attn_h)
+            L.o(attn, h, "add_f32")
+            self._norm_linear(L.gate_up, h, L.post_norm, x, act, "swiglu", eps, off)
+            L.down(act, h, "add_f32")
+        rows = rb.logits_rows if rb.logits_rows is not None else torch.arange(M, device=self.device)
+        nl = rows.shape[0]
+        if not split:
+            hsel = h.index_select(0, rows.long()) if nl != M else h
+            return self._head(hsel, buf, nl, rb)
+        sel = torch.zeros(nl, cfg.hidden_size, dtype=torch.float32, device=self.device)
+        mine = (rows >= a) & (rows < b)
+        if bool(mine.any()):
+            sel[mine] = h.index_select(0, (rows[mine] - a).long())
+        torch.distributed.all_reduce(sel, group=up.group)
+        return self._head(sel, buf, nl, rb)
+
     def forward(self, rb: RowBatch, buf: Buffers, kv_layers, block_table) -> torch.Tensor:
         """Run all layers for the rows of ``rb``; returns fp32 logits [rows needing logits][V]."""
+        if getattr(self, "up", None) is not None:
+            return self.forward_ulysses(rb, buf, kv_layers, block_table)
         if (rb.mode == "prefill" and rb.segments is None and getattr(self, "cp", None) is not None and self.cp.ready(rb.tokens.shape[0])):
             return self.forward_prefill_cp(rb, buf, kv_layers, block_table)
         if (rb.mode == "prefill" and rb.segments is None and self.tp is not None and self.pp_world == 1 and getattr(self.tp, "sp_ready", None)

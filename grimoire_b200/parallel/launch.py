@@ -14,7 +14,7 @@ from .. import config as cfgmod
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="grimoire_b200.parallel.launch")
     cfgmod.add_engine_flags(ap)
-    ap.add_argument("--mode", choices=["TP", "PP", "EP", "CP"], default="TP")
+    ap.add_argument("--mode", choices=["TP", "PP", "EP", "CP", "UP"], default="TP")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--host", default="0.0.0.0")
     ns = ap.parse_args(argv)
@@ -28,7 +28,7 @@ def main(argv=None) -> int:
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     lay = init_parallel(tp_world=world if ns.mode == "TP" else 1, pp_world=world if ns.mode == "PP" else 1,
-                        ep_world=world if ns.mode == "EP" else 1, cp_world=world if ns.mode == "CP" else 1)
+                        ep_world=world if ns.mode == "EP" else 1, cp_world=world if ns.mode in ("CP", "UP") else 1)
     ec = cfgmod.from_args(ns)
     ec.tp_rank, ec.tp_world, ec.pp_rank, ec.pp_world = lay.tp_rank, lay.tp_world, lay.pp_rank, lay.pp_world
     ec.ep_rank, ec.ep_world = lay.ep_rank, lay.ep_world
@@ -41,8 +41,9 @@ def main(argv=None) -> int:
         from .pp import PipelineParallel
 
         pp = PipelineParallel(lay.pp_group, lay.device)
-    g = Grimoire.load(ec, device=str(lay.device), tp=tp, pp=pp, ep_group=lay.ep_group)
-    if lay.cp_world > 1:
+    g = Grimoire.load(ec, device=str(lay.device), tp=tp, pp=pp, ep_group=lay.ep_group,
+                      up_group=lay.cp_group if ns.mode == "UP" else None)
+    if lay.cp_world > 1 and ns.mode == "CP":
         # whole-model replicas: prompt chunks split by rows, caches replicated, decode steps replicated
         from .cp import ContextParallel
 

@@ -1,4 +1,4 @@
-"""``grimoire multi PP 2`` / ``multi CP 2`` end to end on CPU ranks: the launcher starts two gloo ranks, rank 0 serves HTTP
+"""``grimoire multi PP 2`` / ``multi CP 2`` / ``multi UP 2`` end to end on CPU ranks: the launcher starts two gloo ranks, rank 0 serves HTTP
 over a ControlledEngine, rank 1 mirrors the engine calls and runs the second pipeline stage (PP) or its half of every
 prompt chunk's rows (CP); the completion must equal the single-process one (tools/test_pp_server.cpp in the reference: same tokens through a two-stage server)."""
 import http.client
@@ -35,7 +35,7 @@ def _post(port, body, timeout=120):
     return r.status, json.loads(data)
 
 
-@pytest.mark.parametrize("mode", ["PP", "CP"])
+@pytest.mark.parametrize("mode", ["PP", "CP", "UP"])
 def test_multi_2_rank_server_matches_single_process(tmp_path, mode):
     d = tmp_path / "model"
     cfg = tiny_dense()
