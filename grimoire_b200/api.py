@@ -154,6 +154,14 @@ class Grimoire:
                     from .models.gemma4 import Gemma4Model
 
                     model = Gemma4Model.from_state_dict(cfg, G.state_dict_from_gguf(gf), dev)
+                elif is_hybrid(cfg):
+                    # qwen35 / qwen35moe / qwen3moe files: the converter's tensor transforms are undone on the way in
+                    from .models.hybrid import _DictSource
+
+                    model = HybridModel.from_checkpoint(_DictSource(cfg, G.state_dict_from_gguf(gf, cfg)), dev, max_slots=ec.seq_slots,
+                                                        ep_rank=ec.ep_rank, ep_world=ec.ep_world,
+                                                        expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
+                                                        proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))
                 elif ec.proj == "native" and ec.tp_world == 1 and ec.pp_world == 1 and G.native_ok(gf, cfg):
                     model = DenseModel.from_gguf_native(cfg, gf, dev)
                 else:

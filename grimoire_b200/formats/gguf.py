@@ -140,6 +140,10 @@ def config_from_gguf(g: GGUFFile):
     a, m = g.arch, g.metadata
     if a == "gemma4":
         return _gemma4_config_from_gguf(g)
+    if a in ("qwen35", "qwen35moe"):
+        return _qwen35_config_from_gguf(g)
+    if a == "qwen3moe":
+        return _qwen3moe_config_from_gguf(g)
     heads = int(m[f"{a}.attention.head_count"])
     hidden = int(m[f"{a}.embedding_length"])
     emb = g.tensors.get("token_embd.weight")
@@ -193,8 +197,202 @@ def _gemma4_config_from_gguf(g: GGUFFile):
         num_global_key_value_heads=n_full if n_full != n_swa else 0)
 
 
-def state_dict_from_gguf(g: GGUFFile) -> dict[str, torch.Tensor]:
-    """Every tensor with a known HF name, dequantized to fp32."""
+def _qwen35_config_from_gguf(g: GGUFFile):
+    """``qwen35.*`` / ``qwen35moe.*`` metadata -> ModelConfig of the hybrid (Gated DeltaNet + gated attention) family
+    (gguf_qwen35_config, src/gguf_qwen35.cpp:80-212).  llama.cpp's ssm names carry the DeltaNet geometry: ``ssm.group_count``
+    key heads, ``ssm.time_step_rank`` value heads, ``ssm.state_size`` key width, ``ssm.inner_size`` = value heads x value
+    width; every ``full_attention_interval``-th layer attends; a trailing ``nextn_predict_layers`` block is the draft head
+    and does not count as a decoder layer; a q projection with twice the query rows carries the output gate."""
+    from ..models.config import ModelConfig
+
+    a, m = g.arch, g.metadata
+    moe, p = a == "qwen35moe", a + "."
+    blocks, mtp = int(m[p + "block_count"]), int(m.get(p + "nextn_predict_layers", 0))
+    hidden, heads, kv = int(m[p + "embedding_length"]), int(m[p + "attention.head_count"]), int(m[p + "attention.head_count_kv"])
+    hd, vd, rope = int(m[p + "attention.key_length"]), int(m[p + "attention.value_length"]), int(m[p + "rope.dimension_count"])
+    nk, nv, dk = int(m[p + "ssm.group_count"]), int(m[p + "ssm.time_step_rank"]), int(m[p + "ssm.state_size"])
+    inner, conv, interval = int(m[p + "ssm.inner_size"]), int(m[p + "ssm.conv_kernel"]), int(m[p + "full_attention_interval"])
+    L = blocks - mtp
+    if mtp >= blocks or not hd or hd != vd or not nk or not nv or nv % nk or inner % nv or not interval:
+        raise ValueError(f"inconsistent {a} GGUF geometry")
+    emb = g.tensors.get("token_embd.weight")
+    if emb is None or len(emb[2]) != 2 or emb[2][0] != hidden:
+        raise ValueError("GGUF token_embd.weight shape disagrees with embedding_length")
+    gate = None
+    for i in range(L):
+        q = g.tensors.get(f"blk.{i}.attn_q.weight")
+        if q is None:
+            continue
+        if len(q[2]) != 2 or q[2][0] != hidden or q[2][1] not in (heads * hd, 2 * heads * hd):
+            raise ValueError("GGUF attn_q.weight has invalid query width")
+        this = q[2][1] == 2 * heads * hd
+        if gate is not None and gate != this:
+            raise ValueError("GGUF attn_q output gate differs across layers")
+        gate = this
+    if gate is None:
+        raise ValueError("GGUF has no full-attention attn_q.weight")
+    types = ["linear_attention" if (i + 1) % interval else "full_attention" for i in range(L)]
+    rec = m.get(p + "recurrent_layers")
+    if rec is not None and [bool(v) for v in rec] != [t == "linear_attention" for t in types]:
+        raise ValueError("GGUF recurrent_layers contradicts full_attention_interval")
+    tc = {"model_type": "qwen3_5_moe_text" if moe else "qwen3_5_text", "num_hidden_layers": L, "hidden_size": hidden,
+          "vocab_size": emb[2][1], "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd,
+          "rms_norm_eps": float(m[p + "attention.layer_norm_rms_epsilon"]), "linear_num_key_heads": nk, "linear_num_value_heads": nv,
+          "linear_key_head_dim": dk, "linear_value_head_dim": inner // nv, "linear_conv_kernel_dim": conv, "mtp_num_hidden_layers": mtp,
+          "attn_output_gate": gate, "tie_word_embeddings": "output.weight" not in g.tensors, "layer_types": types,
+          "rope_parameters": {"rope_theta": float(m[p + "rope.freq_base"]), "partial_rotary_factor": rope / hd}}
+    if moe:
+        tc.update(num_experts=int(m[p + "expert_count"]), num_experts_per_tok=int(m[p + "expert_used_count"]),
+                  moe_intermediate_size=int(m[p + "expert_feed_forward_length"]),
+                  shared_expert_intermediate_size=int(m[p + "expert_shared_feed_forward_length"]))
+    else:
+        tc["intermediate_size"] = int(m[p + "feed_forward_length"])
+    return ModelConfig.from_hf({"model_type": "qwen3_5_moe" if moe else "qwen3_5", "text_config": tc})
+
+
+def _qwen3moe_config_from_gguf(g: GGUFFile):
+    """``qwen3moe.*`` metadata -> ModelConfig of a Qwen3-MoE decoder (gguf_qwen3_config, src/gguf_qwen35.cpp:214-326): plain
+    attention, no shared expert; a layer without a router tensor carries a dense FFN and is listed as ``mlp_only``."""
+    from ..models.config import ModelConfig
+
+    m, p = g.metadata, "qwen3moe."
+    L, hidden, heads = int(m[p + "block_count"]), int(m[p + "embedding_length"]), int(m[p + "attention.head_count"])
+    kv, hd = int(m[p + "attention.head_count_kv"]), int(m[p + "attention.key_length"])
+    ne, top = int(m[p + "expert_count"]), int(m[p + "expert_used_count"])
+    if int(m.get(p + "expert_shared_feed_forward_length", 0)):
+        raise ValueError("qwen3moe expert_shared_feed_forward_length is nonzero; Qwen3-MoE has no shared expert")
+    if not ne or not top or top > ne or heads % kv or hd != int(m.get(p + "attention.value_length", hd)):
+        raise ValueError("inconsistent qwen3moe GGUF geometry")
+    emb = g.tensors.get("token_embd.weight")
+    if emb is None or len(emb[2]) != 2 or emb[2][0] != hidden:
+        raise ValueError("qwen3moe token_embd.weight shape disagrees with embedding_length")
+    dense_layers = []
+    for i in range(L):
+        if f"blk.{i}.ffn_gate_inp.weight" not in g.tensors:
+            for role in ("ffn_gate", "ffn_up", "ffn_down"):
+                if f"blk.{i}.{role}.weight" not in g.tensors:
+                    raise ValueError(f"qwen3moe layer {i} has neither a router nor {role}.weight")
+            dense_layers.append(i)
+    return ModelConfig.from_hf({
+        "model_type": "qwen3_moe", "num_hidden_layers": L, "hidden_size": hidden, "intermediate_size": int(m[p + "feed_forward_length"]),
+        "vocab_size": emb[2][1], "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd,
+        "rope_theta": float(m[p + "rope.freq_base"]), "rms_norm_eps": float(m[p + "attention.layer_norm_rms_epsilon"]),
+        "attn_output_gate": False, "tie_word_embeddings": "output.weight" not in g.tensors, "num_experts": ne,
+        "num_experts_per_tok": top, "moe_intermediate_size": int(m[p + "expert_feed_forward_length"]),
+        "shared_expert_intermediate_size": 0, "decoder_sparse_step": 1, "norm_topk_prob": True, "mlp_only_layers": dense_layers})
+
+
+_HYBRID_LAYER_MAP = dict(_LAYER_MAP, post_attention_norm="post_attention_layernorm", attn_qkv="linear_attn.in_proj_qkv",
+                         attn_gate="linear_attn.in_proj_z", ssm_alpha="linear_attn.in_proj_a", ssm_beta="linear_attn.in_proj_b",
+                         ssm_conv1d="linear_attn.conv1d", ssm_norm="linear_attn.norm", ssm_out="linear_attn.out_proj",
+                         ffn_gate_inp="mlp.gate", ffn_gate_inp_shexp="mlp.shared_expert_gate", ffn_gate_shexp="mlp.shared_expert.gate_proj",
+                         ffn_up_shexp="mlp.shared_expert.up_proj", ffn_down_shexp="mlp.shared_expert.down_proj")
+_NEXTN_MAP = {"nextn.eh_proj.weight": "mtp.fc.weight", "nextn.enorm.weight": "mtp.pre_fc_norm_embedding.weight",
+              "nextn.hnorm.weight": "mtp.pre_fc_norm_hidden.weight", "nextn.shared_head_norm.weight": "mtp.norm.weight"}
+_ZERO_CENTRED = ("attn_norm", "post_attention_norm", "attn_q_norm", "attn_k_norm")
+
+
+def v_head_order(nk: int, nv: int, width: int = 1) -> torch.Tensor:
+    """Source index of every element of a value-head axis: HF groups the ``nv`` value heads by key head (head = key * r + j,
+    r = nv / nk), llama.cpp's converter stores them tiled (j * nk + key) so that a head repeat broadcasts
+    (gguf_v_tiled_index, src/gguf_qwen35.cpp:51).  ``width`` elements per head move together."""
+    r = nv // nk
+    h = torch.arange(nv)
+    tiled = (h % r) * nk + h // r
+    return (tiled[:, None] * width + torch.arange(width)[None, :]).reshape(-1)
+
+
+def _hybrid_state_dict(g: GGUFFile, cfg) -> dict[str, torch.Tensor]:
+    """HF-named fp32 tensors of a ``qwen35`` / ``qwen35moe`` / ``qwen3moe`` file with the converter's transforms undone
+    (gguf_qwen35_index + read_gguf_f32, src/gguf_qwen35.cpp:328-563): value heads back into key-grouped order on the rows
+    of in_proj_qkv's v part / in_proj_z / in_proj_a / in_proj_b / conv1d, the columns of out_proj and the entries of
+    dt_bias / A; ``ssm_a`` = -exp(A_log) back to A_log; the stored ``1 + w`` of every zero-centred norm back to w (both
+    rounded to bf16, the checkpoint's precision); the stacked expert tensors split into gate_up / down."""
+    a = g.arch
+    q35 = a != "qwen3moe"
+    pre = "model.language_model." if q35 else "model."
+    L, mtp = cfg.num_hidden_layers, cfg.mtp_num_hidden_layers
+    nk, nv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    qk = 2 * nk * dk
+    bf = lambda t: t.bfloat16().float()
+    unnorm = (lambda t: bf(t - 1.0)) if q35 else (lambda t: t)
+    out: dict[str, torch.Tensor] = {}
+    experts: dict[str, dict[str, torch.Tensor]] = {}
+    for name in g.tensors:
+        if name == "token_embd.weight":
+            out[pre + "embed_tokens.weight"] = g.tensor(name)
+            continue
+        if name == "output.weight":
+            out["lm_head.weight"] = g.tensor(name)
+            continue
+        if name == "output_norm.weight":
+            out[pre + "norm.weight"] = unnorm(g.tensor(name))
+            continue
+        if name.startswith("nextn.") or name == "rope_freqs.weight":
+            continue
+        if not name.startswith("blk."):
+            raise ValueError(f"unmapped GGUF tensor: {name}")
+        _, layer, role = name.split(".", 2)
+        l = int(layer)
+        if l == L and mtp < 1:
+            continue                                     # a draft block the metadata does not declare stays unused
+        if l > L or l < 0:
+            raise ValueError(f"unmapped GGUF layer tensor: {name}")
+        if l == L:
+            if role in _NEXTN_MAP:
+                t = g.tensor(name)
+                out[_NEXTN_MAP[role]] = t if role == "nextn.eh_proj.weight" else unnorm(t)
+                continue
+            if role in ("nextn.embed_tokens.weight", "nextn.shared_head_head.weight"):
+                continue                                 # the draft head shares the main embedding and output head
+            if role.startswith("nextn."):
+                raise ValueError(f"unmapped GGUF MTP tensor: {name}")
+        b = "mtp.layers.0." if l == L else f"{pre}layers.{l}."
+        stem, _, suffix = role.rpartition(".")
+        if role == "ssm_a":
+            out[b + "linear_attn.A_log"] = bf(torch.log(-g.tensor(name).reshape(-1)[v_head_order(nk, nv)].double()).float())
+            continue
+        if role == "ssm_dt.bias":
+            out[b + "linear_attn.dt_bias"] = g.tensor(name).reshape(-1)[v_head_order(nk, nv)]
+            continue
+        if stem in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
+            t = g.tensor(name)                           # [E][rows][cols]
+            if t.dim() != 3 or t.shape[0] != cfg.num_experts:
+                raise ValueError(f"GGUF expert shape mismatch: {name}")
+            experts.setdefault(b, {})[stem] = t
+            continue
+        hf = _HYBRID_LAYER_MAP.get(stem) if not (stem == "ffn_norm" and q35) else None
+        if hf is None:
+            raise ValueError(f"unmapped GGUF tensor: {name}")
+        t = g.tensor(name)
+        if stem in _ZERO_CENTRED:
+            t = unnorm(t)
+        elif stem in ("attn_qkv", "ssm_conv1d"):
+            t = torch.cat([t[:qk], t[qk:][v_head_order(nk, nv, dv)]])
+            if stem == "ssm_conv1d":
+                t = t.reshape(t.shape[0], 1, -1)         # HF keeps the depthwise filter as [C][1][K]
+        elif stem == "attn_gate":
+            t = t[v_head_order(nk, nv, dv)]
+        elif stem in ("ssm_alpha", "ssm_beta"):
+            t = t[v_head_order(nk, nv)]
+        elif stem == "ssm_out":
+            t = t[:, v_head_order(nk, nv, dv)]
+        elif stem == "ffn_gate_inp_shexp" and t.dim() == 1:
+            t = t.reshape(1, -1)
+        out[f"{b}{hf}.{suffix}"] = t
+    for b, e in experts.items():
+        if set(e) != {"ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"}:
+            raise ValueError(f"GGUF layer {b} lacks one of the stacked expert tensors")
+        out[b + "mlp.experts.gate_up_proj"] = torch.cat([e["ffn_gate_exps"], e["ffn_up_exps"]], dim=1)
+        out[b + "mlp.experts.down_proj"] = e["ffn_down_exps"]
+    return out
+
+
+def state_dict_from_gguf(g: GGUFFile, cfg=None) -> dict[str, torch.Tensor]:
+    """Every tensor with a known HF name, dequantized to fp32 (the hybrid and MoE families need their config for the
+    converter's inverse transforms)."""
+    if g.arch in ("qwen35", "qwen35moe", "qwen3moe"):
+        return _hybrid_state_dict(g, cfg if cfg is not None else config_from_gguf(g))
     out = {}
     for name in g.tensors:
         hn = hf_name(name, g.arch)

@@ -194,3 +194,133 @@ def test_gguf_native_projections_keep_the_files_blocks(tmp_path):
     assert float((a - b).abs().max()) < 0.03 * max(1.0, float(b.abs().max()))
     assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) >= 0.9
     nat.close(), ref.close()
+
+
+def _hybrid_gguf(path, cfg, sd, arch):
+    """Write ``sd`` (HF names, key-grouped value heads) the way llama.cpp's converter stores the hybrid family: value heads
+    tiled, ``ssm_a`` = -exp(A_log), zero-centred norms as 1 + w, experts stacked per layer, conv filter as [C][K]."""
+    q35 = arch != "qwen3moe"
+    L, H = cfg.num_hidden_layers, cfg.hidden_size
+    nk, nv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    tensors = {}
+
+    def put(name, t):
+        t = t.float().contiguous()
+        tensors[name] = (0, tuple(reversed(t.shape)), t.numpy().tobytes())
+
+    def tile(t, width, dim=0):                 # forward transform: stored[order[g]] = hf[g]
+        order = gguf.v_head_order(nk, nv, width)
+        out = torch.empty_like(t)
+        out.index_copy_(dim, order, t)
+        return out
+
+    bf = lambda t: t.bfloat16().float()
+    norm = (lambda t: 1.0 + bf(t)) if q35 else bf
+    put("token_embd.weight", bf(sd["model.embed_tokens.weight"]))
+    put("output_norm.weight", norm(sd["model.norm.weight"]))
+    if "lm_head.weight" in sd:
+        put("output.weight", bf(sd["lm_head.weight"]))
+    for i in range(L):
+        p, b = f"model.layers.{i}.", f"blk.{i}."
+        w = lambda k: bf(sd[p + k])
+        put(b + "attn_norm.weight", norm(sd[p + "input_layernorm.weight"]))
+        put(b + ("post_attention_norm.weight" if q35 else "ffn_norm.weight"), norm(sd[p + "post_attention_layernorm.weight"]))
+        if cfg.is_attention_layer(i):
+            for hf, gg in (("q_proj", "attn_q"), ("k_proj", "attn_k"), ("v_proj", "attn_v"), ("o_proj", "attn_output")):
+                put(b + gg + ".weight", w(f"self_attn.{hf}.weight"))
+            put(b + "attn_q_norm.weight", norm(sd[p + "self_attn.q_norm.weight"]))
+            put(b + "attn_k_norm.weight", norm(sd[p + "self_attn.k_norm.weight"]))
+        else:
+            a, qk = "linear_attn.", 2 * nk * dk
+            qkv, conv = w(a + "in_proj_qkv.weight"), w(a + "conv1d.weight").reshape(-1, cfg.linear_conv_kernel_dim)
+            put(b + "attn_qkv.weight", torch.cat([qkv[:qk], tile(qkv[qk:], dv)]))
+            put(b + "ssm_conv1d.weight", torch.cat([conv[:qk], tile(conv[qk:], dv)]))
+            put(b + "attn_gate.weight", tile(w(a + "in_proj_z.weight"), dv))
+            put(b + "ssm_alpha.weight", tile(w(a + "in_proj_a.weight"), 1))
+            put(b + "ssm_beta.weight", tile(w(a + "in_proj_b.weight"), 1))
+            put(b + "ssm_a", tile(-torch.exp(w(a + "A_log")), 1))
+            put(b + "ssm_dt.bias", tile(w(a + "dt_bias"), 1))
+            put(b + "ssm_norm.weight", w(a + "norm.weight"))
+            put(b + "ssm_out.weight", tile(w(a + "out_proj.weight"), dv, dim=1))
+        if not cfg.layer_is_sparse(i):
+            for hf, gg in (("gate_proj", "ffn_gate"), ("up_proj", "ffn_up"), ("down_proj", "ffn_down")):
+                put(b + gg + ".weight", w(f"mlp.{hf}.weight"))
+            continue
+        put(b + "ffn_gate_inp.weight", w("mlp.gate.weight"))
+        if cfg.shared_expert_intermediate_size:
+            put(b + "ffn_gate_inp_shexp.weight", w("mlp.shared_expert_gate.weight").reshape(-1))       # stored as a vector
+            for hf, gg in (("gate_proj", "ffn_gate_shexp"), ("up_proj", "ffn_up_shexp"), ("down_proj", "ffn_down_shexp")):
+                put(b + gg + ".weight", w(f"mlp.shared_expert.{hf}.weight"))
+        E = cfg.num_experts
+        for hf, gg in (("gate_proj", "ffn_gate_exps"), ("up_proj", "ffn_up_exps"), ("down_proj", "ffn_down_exps")):
+            put(b + gg + ".weight", torch.stack([w(f"mlp.experts.{e}.{hf}.weight") for e in range(E)]))
+    toks = [chr(0x100 + i) for i in range(cfg.vocab_size)]
+    a = arch + "."
+    kv = {"general.architecture": (8, arch), a + "block_count": (4, L), a + "embedding_length": (4, H),
+          a + "attention.head_count": (4, cfg.num_attention_heads), a + "attention.head_count_kv": (4, cfg.num_key_value_heads),
+          a + "attention.key_length": (4, cfg.head_dim), a + "attention.value_length": (4, cfg.head_dim),
+          a + "rope.dimension_count": (4, int(cfg.head_dim * cfg.partial_rotary_factor)), a + "rope.freq_base": (6, cfg.rope_theta),
+          a + "attention.layer_norm_rms_epsilon": (6, cfg.rms_norm_eps), a + "context_length": (4, 4096),
+          "tokenizer.ggml.model": (8, "gpt2"), "tokenizer.ggml.tokens": (9, (8, toks)), "tokenizer.ggml.merges": (9, (8, [])),
+          "tokenizer.ggml.token_type": (9, (5, [1] * cfg.vocab_size))}
+    if q35:
+        kv.update({a + "ssm.group_count": (4, nk), a + "ssm.time_step_rank": (4, nv), a + "ssm.state_size": (4, dk),
+                   a + "ssm.inner_size": (4, nv * dv), a + "ssm.conv_kernel": (4, cfg.linear_conv_kernel_dim),
+                   a + "full_attention_interval": (4, 4), a + "rope.dimension_sections": (9, (5, [11, 11, 10, 0]))})
+    if cfg.is_moe:
+        kv.update({a + "expert_count": (4, cfg.num_experts), a + "expert_used_count": (4, cfg.num_experts_per_tok),
+                   a + "expert_feed_forward_length": (4, cfg.moe_intermediate_size)})
+        if q35:
+            kv[a + "expert_shared_feed_forward_length"] = (4, cfg.shared_expert_intermediate_size)
+    if not cfg.is_moe or not q35:
+        kv[a + "feed_forward_length"] = (4, cfg.intermediate_size or 512)
+    _write_gguf(path, kv, tensors)
+
+
+def test_value_head_order_undoes_the_converters_tiling():
+    # 2 key heads x 3 value heads each: HF head key*3+j sits at stored position j*2+key
+    assert gguf.v_head_order(2, 6).tolist() == [0, 2, 4, 1, 3, 5]
+    assert gguf.v_head_order(2, 4, 2).tolist() == [0, 1, 4, 5, 2, 3, 6, 7]
+
+
+@pytest.mark.parametrize("preset,arch", [("tiny_hybrid_dense", "qwen35"), ("tiny_hybrid_moe", "qwen35moe"), ("tiny_moe", "qwen3moe")])
+def test_hybrid_family_gguf_files_load_like_their_hf_checkpoints(preset, arch, tmp_path):
+    """The hybrid / MoE architecture adapters: metadata -> config, converter names -> HF names, and the converter's tensor
+    transforms undone, so that a file serves the same logits as the HF directory it was converted from."""
+    import dataclasses
+
+    from grimoire_b200.api import Grimoire
+    from grimoire_b200.config import EngineConfig
+    from grimoire_b200.models import config as C
+    from grimoire_b200.models.hybrid import HybridModel
+
+    from .fixtures.mini_model import write_hybrid_checkpoint
+
+    cfg = getattr(C, preset)()
+    if arch == "qwen35":
+        cfg = dataclasses.replace(cfg, linear_num_value_heads=6, partial_rotary_factor=0.5)      # 3 value heads per key head: the tiling is no involution
+    sd = write_hybrid_checkpoint(tmp_path / "hf", cfg, seed=4)
+    path = tmp_path / "m.gguf"
+    _hybrid_gguf(path, cfg, sd, arch)
+    gf = gguf.GGUFFile(path)
+    got = gguf.config_from_gguf(gf)
+    for f in ("num_hidden_layers", "layer_types", "linear_num_key_heads", "linear_num_value_heads", "linear_key_head_dim",
+              "linear_value_head_dim", "linear_conv_kernel_dim", "num_experts", "num_experts_per_tok", "moe_intermediate_size",
+              "shared_expert_intermediate_size", "attn_output_gate", "norm_zero_centered", "partial_rotary_factor", "head_dim",
+              "tie_word_embeddings", "vocab_size"):
+        assert getattr(got, f) == getattr(cfg, f), f
+    back = gguf.state_dict_from_gguf(gf, got)
+    gf.close()
+    pre = "model.language_model." if arch != "qwen3moe" else "model."
+    for k, v in sd.items():
+        if ".mlp.experts." in k:
+            continue
+        t = back[pre + k[len("model."):] if k.startswith("model.") else k]
+        assert torch.equal(t, v.bfloat16().float().reshape(t.shape)), k       # bit-exact round trip, A_log and the norms included
+    ec = lambda m: EngineConfig(model=str(m), ctx=128, seq_slots=2, prefill_chunk=32)
+    ids = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(2)).tolist()
+    a, b = Grimoire.load(ec(path), device="cpu"), Grimoire.load(ec(tmp_path / "hf"), device="cpu")
+    assert isinstance(a.model, HybridModel) and a.tokenizer is not None
+    la, lb = a.score_ids(ids), b.score_ids(ids)
+    assert torch.allclose(la, lb, atol=1e-4), float((la - lb).abs().max())
+    a.close(), b.close()
