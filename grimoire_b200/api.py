@@ -158,10 +158,13 @@ class Grimoire:
                     # qwen35 / qwen35moe / qwen3moe files: the converter's tensor transforms are undone on the way in
                     from .models.hybrid import _DictSource
 
-                    model = HybridModel.from_checkpoint(_DictSource(cfg, G.state_dict_from_gguf(gf, cfg)), dev, max_slots=ec.seq_slots,
+                    model_src = _DictSource(cfg, G.state_dict_from_gguf(gf, cfg))
+                    model = HybridModel.from_checkpoint(model_src, dev, max_slots=ec.seq_slots,
                                                         ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
                                                         proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))
+                    if ec.mtp and cfg.mtp_num_hidden_layers > 0 and not cfg.is_moe and "mtp.fc.weight" in model_src.sd:
+                        mtp_src = model_src              # the file's nextn block under the mtp.* names
                 elif ec.proj == "native" and ec.tp_world == 1 and ec.pp_world == 1 and G.native_ok(gf, cfg):
                     model = DenseModel.from_gguf_native(cfg, gf, dev)
                 else:
@@ -188,6 +191,12 @@ class Grimoire:
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
                                                         proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))
+                    if ec.mtp and cfg.mtp_num_hidden_layers > 0 and not cfg.is_moe and ec.ep_world == 1:
+                        from .formats.checkpoint import Checkpoint
+
+                        ck = Checkpoint(ec.model)
+                        if ck.has("mtp.fc.weight"):
+                            mtp_src = ck                 # the 27B-style hybrid's draft layer: full attention + dense FFN
                 else:
                     model = DenseModel.from_checkpoint(ec.model, dev, ec.tp_rank, ec.tp_world, lm_head_bf16=bool(ec.lm_head_bf16),
                                                        proj=ec.proj, pp_rank=ec.pp_rank, pp_world=ec.pp_world)
@@ -215,7 +224,7 @@ class Grimoire:
             if hybrid or cfg.is_sandwich or ec.tp_world > 1 or ec.pp_world > 1:
                 raise UnsupportedModel("the head / sequence exchange (multi UP) runs over whole replicas of the dense decoder family")
             UlyssesParallel(up_group, dev).attach(model)
-        # draft head: only on a single-stage, single-rank dense model (the reference drafts on the last stage)
+        # draft head: on a single-stage, single-rank dense model or dense-FFN hybrid (the reference drafts on the last stage)
         want_mtp = mtp_src is not None and ec.tp_world == 1 and ec.pp_world == 1
         lim = EngineLimits(max_slots=ec.seq_slots, max_ctx=ec.ctx, prefill_chunk=ec.prefill_chunk, max_decode_rows=64,
                            kv_pages=ec.kv_pages, extra_kv_layers=1 if want_mtp else 0)

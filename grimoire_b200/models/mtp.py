@@ -27,10 +27,16 @@ from .dense import DenseModel, RowBatch
 
 
 class MtpHead:
-    def __init__(self, target: DenseModel, draft_vocab: int = 0):
+    def __init__(self, target, draft_vocab: int = 0):
+        """``target``: a ``DenseModel``, or a ``HybridModel`` with a dense FFN (the 27B-style hybrid, whose draft layer is one
+        gated full-attention layer with a dense FFN: the head reads only the target's residual rows, embedding and output
+        head, and borrows the attention-side scratch the two buffer classes name alike)."""
         cfg = target.cfg
+        if cfg.is_moe:
+            raise ValueError("the draft head's layer carries a dense FFN: targets with an MoE FFN are not served")
         self.target, self.cfg, self.device = target, cfg, target.device
-        self.inner = DenseModel(dataclasses.replace(cfg, num_hidden_layers=1, layer_types=[]), target.device, workspace=target.ws)
+        self.inner = DenseModel(dataclasses.replace(cfg, num_hidden_layers=1, layer_types=[], mtp_num_hidden_layers=0), target.device,
+                                workspace=target.ws)
         self.enorm = self.hnorm = self.final_norm = None
         self.fc = None
         self.head = None
@@ -151,7 +157,8 @@ class MtpHead:
         eps, off = cfg.rms_norm_eps, cfg.norm_offset
         hA, hB, catb = self._bufs(buf)
         h2, cat = (hB if flip else hA)[:M], catb[:M]
-        x, qkv, q, attn, act = buf.x[:M], buf.qkv[:M], buf.q[:M], buf.attn[:M], buf.act[:M]
+        x, qkv, q, attn = buf.x[:M], buf.qkv[:M], buf.q[:M], buf.attn[:M]
+        act = (buf.act_d if hasattr(buf, "act_d") else buf.act)[:M]        # a hybrid target keeps its dense-FFN rows under act_d
         gate = buf.gate[:M] if buf.gate is not None else None
         K.embed(rb.tokens, self.target.embed, h2)
         K.add_rmsnorm(h2, self.enorm, cat[:, :H], eps, off)

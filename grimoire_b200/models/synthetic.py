@@ -107,6 +107,8 @@ def random_hybrid_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02,
             for e in range(E):
                 x = m + f"experts.{e}."
                 sd[x + "gate_proj.weight"], sd[x + "up_proj.weight"], sd[x + "down_proj.weight"] = gu[e, :I], gu[e, I:], dn[e]
+    if mtp:
+        sd.update(random_mtp_state_dict(cfg, seed, std))       # the draft layer: full attention + dense FFN under mtp.*
     return sd
 
 

@@ -59,12 +59,12 @@ def write_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, quant: str = "
     return sd
 
 
-def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_experts: bool = False):
+def write_hybrid_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0, fused_experts: bool = False, mtp: bool = False):
     """A checkpoint of the hybrid family (Gated DeltaNet / gated or plain attention; MoE with or without a shared expert, or a
     dense FFN) under the HF names of that family."""
     path.mkdir(parents=True, exist_ok=True)
-    sd = random_hybrid_state_dict(cfg, seed, fused_experts=fused_experts)
-    hf = {"model_type": cfg.model_type, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
+    sd = random_hybrid_state_dict(cfg, seed, fused_experts=fused_experts, mtp=mtp)
+    hf = {"mtp_num_hidden_layers": 1 if mtp else 0, "model_type": cfg.model_type, "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
           "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
           "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
           "partial_rotary_factor": cfg.partial_rotary_factor, "tie_word_embeddings": cfg.tie_word_embeddings,

@@ -254,9 +254,23 @@ def _hybrid_gguf(path, cfg, sd, arch):
         E = cfg.num_experts
         for hf, gg in (("gate_proj", "ffn_gate_exps"), ("up_proj", "ffn_up_exps"), ("down_proj", "ffn_down_exps")):
             put(b + gg + ".weight", torch.stack([w(f"mlp.experts.{e}.{hf}.weight") for e in range(E)]))
+    mtp = 1 if "mtp.fc.weight" in sd else 0
+    if mtp:
+        # the draft head travels as one more block: its layer under the decoder layers' roles, the rest under nextn.*
+        p, b = "mtp.layers.0.", f"blk.{L}."
+        for hf, gg in (("self_attn.q_proj", "attn_q"), ("self_attn.k_proj", "attn_k"), ("self_attn.v_proj", "attn_v"),
+                       ("self_attn.o_proj", "attn_output"), ("mlp.gate_proj", "ffn_gate"), ("mlp.up_proj", "ffn_up"), ("mlp.down_proj", "ffn_down")):
+            put(b + gg + ".weight", bf(sd[p + hf + ".weight"]))
+        for hf, gg in (("input_layernorm", "attn_norm"), ("post_attention_layernorm", "post_attention_norm"),
+                       ("self_attn.q_norm", "attn_q_norm"), ("self_attn.k_norm", "attn_k_norm")):
+            put(b + gg + ".weight", norm(sd[p + hf + ".weight"]))
+        put(b + "nextn.eh_proj.weight", bf(sd["mtp.fc.weight"]))
+        put(b + "nextn.enorm.weight", norm(sd["mtp.pre_fc_norm_embedding.weight"]))
+        put(b + "nextn.hnorm.weight", norm(sd["mtp.pre_fc_norm_hidden.weight"]))
+        put(b + "nextn.shared_head_norm.weight", norm(sd["mtp.norm.weight"]))
     toks = [chr(0x100 + i) for i in range(cfg.vocab_size)]
     a = arch + "."
-    kv = {"general.architecture": (8, arch), a + "block_count": (4, L), a + "embedding_length": (4, H),
+    kv = {"general.architecture": (8, arch), a + "block_count": (4, L + mtp), a + "embedding_length": (4, H),
           a + "attention.head_count": (4, cfg.num_attention_heads), a + "attention.head_count_kv": (4, cfg.num_key_value_heads),
           a + "attention.key_length": (4, cfg.head_dim), a + "attention.value_length": (4, cfg.head_dim),
           a + "rope.dimension_count": (4, int(cfg.head_dim * cfg.partial_rotary_factor)), a + "rope.freq_base": (6, cfg.rope_theta),
@@ -267,6 +281,8 @@ def _hybrid_gguf(path, cfg, sd, arch):
         kv.update({a + "ssm.group_count": (4, nk), a + "ssm.time_step_rank": (4, nv), a + "ssm.state_size": (4, dk),
                    a + "ssm.inner_size": (4, nv * dv), a + "ssm.conv_kernel": (4, cfg.linear_conv_kernel_dim),
                    a + "full_attention_interval": (4, 4), a + "rope.dimension_sections": (9, (5, [11, 11, 10, 0]))})
+    if mtp:
+        kv[a + "nextn_predict_layers"] = (4, mtp)
     if cfg.is_moe:
         kv.update({a + "expert_count": (4, cfg.num_experts), a + "expert_used_count": (4, cfg.num_experts_per_tok),
                    a + "expert_feed_forward_length": (4, cfg.moe_intermediate_size)})
@@ -299,7 +315,7 @@ def test_hybrid_family_gguf_files_load_like_their_hf_checkpoints(preset, arch, t
     cfg = getattr(C, preset)()
     if arch == "qwen35":
         cfg = dataclasses.replace(cfg, linear_num_value_heads=6, partial_rotary_factor=0.5)      # 3 value heads per key head: the tiling is no involution
-    sd = write_hybrid_checkpoint(tmp_path / "hf", cfg, seed=4)
+    sd = write_hybrid_checkpoint(tmp_path / "hf", cfg, seed=4, mtp=arch == "qwen35")
     path = tmp_path / "m.gguf"
     _hybrid_gguf(path, cfg, sd, arch)
     gf = gguf.GGUFFile(path)
@@ -323,4 +339,13 @@ def test_hybrid_family_gguf_files_load_like_their_hf_checkpoints(preset, arch, t
     assert isinstance(a.model, HybridModel) and a.tokenizer is not None
     la, lb = a.score_ids(ids), b.score_ids(ids)
     assert torch.allclose(la, lb, atol=1e-4), float((la - lb).abs().max())
-    a.close(), b.close()
+    a.close()
+    if arch == "qwen35":
+        # the file's nextn block is the draft head: speculation keeps the plain greedy tokens
+        want, _ = b.generate(ids, 12)
+        c = Grimoire.load(EngineConfig(model=str(path), ctx=128, seq_slots=2, prefill_chunk=32, mtp=1), device="cpu")
+        assert c.drafter is not None and got.mtp_num_hidden_layers == 1
+        out, _ = c.generate(ids, 12, draft_depth=3)
+        assert out == want
+        c.close()
+    b.close()

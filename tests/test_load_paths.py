@@ -270,3 +270,28 @@ def test_expert_placement_from_heat_file_keeps_logits_and_balances_ranks(hybrid_
     loads = rank_loads(h2.h[0], m.expert_perm[0], 2)
     ident = rank_loads(h2.h[0], list(range(cfg.num_experts)), 2)
     assert max(loads) / sum(loads) < 0.56 < max(ident) / sum(ident)
+
+
+def test_mtp_head_on_a_dense_ffn_hybrid_target_keeps_greedy(tmp_path):
+    """The 27B-style hybrid (Gated DeltaNet + gated attention, dense FFN) with its checkpoint's one-layer draft head:
+    speculative decoding returns the plain greedy tokens, the head's KV layer sits after the target's attention layers,
+    and rejected rows leave the recurrent state as plain decoding would."""
+    from grimoire_b200.engine.generation import SpecStats
+    from grimoire_b200.models.config import tiny_hybrid_dense
+
+    cfg = tiny_hybrid_dense(4)
+    write_hybrid_checkpoint(tmp_path, cfg, seed=6, mtp=True)
+    plain = Grimoire.load(_ec(tmp_path), device="cpu")
+    assert plain.drafter is None
+    ids = _prompt(45, 8)
+    want, _ = plain.generate(ids, 20)
+    plain.close()
+    g = Grimoire.load(_ec(tmp_path, mtp=1), device="cpu")
+    assert isinstance(g.model, HybridModel) and g.drafter is not None
+    assert len(g.engine.kv.layers) == cfg.num_attention_layers() + 1
+    st = SpecStats()
+    got, _ = g.generate(ids, 20, draft_depth=3, stats=st)
+    assert got == want and st.rounds > 0 and st.drafted > 0
+    out, why, job = g.scheduler().generate(ids, 20)
+    assert out == want
+    g.close()
