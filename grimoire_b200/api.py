@@ -209,6 +209,8 @@ class Grimoire:
             if ck_dir and tok is None and os.path.exists(os.path.join(ck_dir, "tokenizer.json")):
                 tok = Tokenizer(ck_dir)
         hybrid = isinstance(model, HybridModel)
+        if hybrid and os.environ.get("GRIMOIRE_EXPERT_HITS"):
+            model.record_expert_hits(os.environ["GRIMOIRE_EXPERT_HITS"])     # the file GRIMOIRE_EXPERT_HEAT reads at the next load
         if tp is not None:
             tp.attach(model, max_rows=max(ec.prefill_chunk, 64))
             if not hybrid and pp is None:
@@ -311,6 +313,9 @@ class Grimoire:
         if self._sched is not None:
             self._sched.shutdown()
             self._sched = None
+        save = getattr(self.model, "save_expert_hits", None)
+        if save is not None:
+            save()
 
     # ---- CLI helpers: load report / micro benchmarks / scoring ----
     def bench_prefill(self, n_tokens: int, repeats: int = 2) -> float:

@@ -156,6 +156,9 @@ class Engine:
             done += m
             self.counters["prefill_rows"] += m
             logits = out
+        hook = getattr(self.model, "on_tokens", None)
+        if hook is not None:
+            hook(n)
         seq.tokens.extend(int(t) for t in tokens.tolist())
         pp = getattr(self.model, "pp", None)
         if pp is not None:
@@ -363,6 +366,9 @@ class Engine:
             if p == s.length:
                 s.length += 1
                 s.tokens.append(int(t))
+        hook = getattr(self.model, "on_tokens", None)        # hybrid models flush their routing counts every few hundred tokens
+        if hook is not None:
+            hook(len(tokens))
 
     def _save_recurrent(self, M: int):
         fn = getattr(self.model, "save_recurrent", None)

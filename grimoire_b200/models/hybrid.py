@@ -152,6 +152,8 @@ class HybridModel:
         self.ep = None                   # parallel.ep.ExpertParallel when the experts are sharded over ranks
         self.expert_perm = None          # per layer: physical -> logical expert (set_expert_placement), None = identity
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
+        self._hits = None                # [layers][experts] int64 routing counts on the device (record_expert_hits)
+        self._cur_layer = 0
         self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = True       # verify blocks: rows run as one recurrent run, rejected rows are undone by replay
         self._vtrace = None                    # per-layer conv inputs / gate inputs of the verify step in flight
@@ -546,7 +548,8 @@ class HybridModel:
         lg = buf.router[:M, : cfg.num_experts + 1]
         moe.router(x, lg, "f32")
         if cfg.router_sigmoid:
-            return self._moe_k2(L, x, h, buf, M, decode, lg)
+            self._moe_k2(L, x, h, buf, M, decode, lg)
+            return self._credit(ids=buf.ids[:M])
         if self.ep is None and not decode and x.is_cuda and M > 64:
             # a prompt chunk on one GPU: group the rows by expert on the device (the expert-parallel chain with
             # this GPU as its only rank) instead of sorting on the host, which would stall the stream every layer
@@ -555,7 +558,7 @@ class HybridModel:
 
                 self._local_moe = ExpertParallel(None, self.device, E, k, H, cfg.moe_intermediate_size, buf.max_rows, fused=True)
             self._local_moe.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
-            return
+            return self._credit(counts=self._local_moe.counts)
         if self.ep is not None and self.ep.fused and decode and M <= self.ep.ll_rows and EP_DECODE_LL:
             # a few decode rows: every rank runs the chosen experts it owns on the replicated rows and the combine
             # kernel all-reduces the weighted sums (no dispatch / return traffic, one exchange per layer)
@@ -573,13 +576,13 @@ class HybridModel:
                 moe.shared_gu(x, buf.act_s[:M], "swiglu")
                 moe.shared_down(buf.act_s[:M], y[M * k: M * (k + 1)], "f32")
             ep.combine_allreduce(h, y, pos, wts, M)
-            return
+            return self._credit(ids=ids) if ep.rank == 0 else None      # every rank routed the same rows: one of them counts
         if self.ep is not None:
             if self.ep.fused:
                 self.ep.moe_fused(moe, x, h, lg, buf.ids, buf.wts, buf.act_s, M, cfg.norm_topk_prob)
-            else:
-                self.ep.moe_allreduce(moe, x, h, lg, M, cfg.norm_topk_prob)
-            return
+                return self._credit(counts=self.ep.counts)          # this rank's share of the rows
+            self.ep.moe_allreduce(moe, x, h, lg, M, cfg.norm_topk_prob, ids_out=buf.ids[:M])
+            return self._credit(ids=buf.ids[:M]) if self.ep.rank == 0 else None
         ids, wts = buf.ids[:M], buf.wts[:M]
         Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts, shared_gate=True)
         act, y, pos = buf.act[: M * k], buf.y[: M * (k + 1)], buf.pos[:M]
@@ -612,6 +615,68 @@ class HybridModel:
         if not decode:
             pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
         Hb.moe_combine(h, y, pos, wts)
+        self._credit(ids=ids)
+
+    # ---- routing counts for the placement file ----
+    def record_expert_hits(self, path: str, every: int = 256) -> None:
+        """Count every routing decision on the device ([layer][expert]) and add the counts to the hit file ``path`` every
+        ``every`` served tokens and at ``save_expert_hits`` (tm_save_hits, src/grimoire.cpp:14295-14320: each process adds
+        what it counted since its last save).  The file is the one ``set_expert_placement`` reads at the next load."""
+        cfg = self.cfg
+        if not cfg.is_moe:
+            return
+        self._hits = torch.zeros(cfg.num_hidden_layers, cfg.num_experts, dtype=torch.int64, device=self.device)
+        self._hits_saved = torch.zeros(cfg.num_hidden_layers, cfg.num_experts, dtype=torch.int64)
+        self._hits_one = torch.ones(1, dtype=torch.int64, device=self.device)
+        self._hits_path, self._hits_every, self._hits_tokens = path, max(1, int(every)), 0
+
+    def _credit(self, ids=None, counts=None) -> None:
+        if self._hits is None:
+            return
+        row = self._hits[self._cur_layer]
+        if counts is not None:
+            row.add_(counts[: row.numel()])
+        else:
+            flat = ids.reshape(-1).long()
+            row.index_add_(0, flat, self._hits_one.expand(flat.numel()))
+
+    def on_tokens(self, n: int) -> None:
+        """Host-side step boundary (the engine calls it with the rows it committed)."""
+        if self._hits is None:
+            return
+        self._hits_tokens += n
+        if self._hits_tokens >= self._hits_every:
+            self.save_expert_hits()
+
+    def save_expert_hits(self) -> None:
+        """Add the counts since the last save to the hit file under an exclusive lock (several expert-parallel ranks write
+        the same file).  Counts are kept per physical expert and land on the logical expert the placement maps it to."""
+        if self._hits is None:
+            return
+        import fcntl
+        import json
+        import os
+
+        from .expert_placement import ExpertHeat
+
+        cfg = self.cfg
+        now = self._hits.cpu()
+        delta = now - self._hits_saved
+        self._hits_saved, self._hits_tokens = now, 0
+        if self.expert_perm is not None:
+            logical = torch.zeros_like(delta)
+            for l, perm in enumerate(self.expert_perm):
+                logical[l, torch.tensor(perm, dtype=torch.long)] = delta[l]
+            delta = logical
+        if not int(delta.sum()):
+            return
+        with open(self._hits_path + ".lock", "w") as lock:
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            heat = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts)
+            if os.path.exists(self._hits_path) and not heat.load(self._hits_path):
+                return                                   # another model's file: left alone
+            heat.hits = heat.hits + delta.numpy()
+            heat.save(self._hits_path)
 
     def _moe_k2(self, L: HybridLayer, x, h, buf: HybridBuffers, M: int, decode: bool, lg) -> None:
         """K2 routing (sigmoid scores, selection-only bias, normalised and scaled weights) with an ungated shared expert, on the
@@ -685,7 +750,7 @@ class HybridModel:
             touched = rb.row_seq.long()
         tr = self._vtrace
         tl = trace.timeline.on
-        for L in self.layers:
+        for li, L in enumerate(self.layers):
             if tl: trace.mark("gdn: norm + in projections" if L.kind == "gdn" else "attn: norm + qkv")
             if L.kind == "gdn":
                 self._norm(h, L.in_norm, x)
@@ -746,6 +811,7 @@ class HybridModel:
                 L.ffn_down(act, h, "add_f32")
             else:
                 self._norm(h, L.post_norm, x)
+                self._cur_layer = li
                 self._moe(L, x, h, buf, M, decode=not prefill)
         if tl: trace.mark("head")
         if rb.logits_rows is None:

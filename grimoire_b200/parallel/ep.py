@@ -179,11 +179,12 @@ class ExpertParallel:
         _native.check(code, "ep_combine_allreduce")
         self.stats["fused_layers"] += 1
 
-    def moe_allreduce(self, moe, x: torch.Tensor, h: torch.Tensor, lg: torch.Tensor, M: int, renorm: bool) -> None:
-        """Local experts for all rows, partial sums all-reduced (CPU ranks, and the NCCL baseline)."""
+    def moe_allreduce(self, moe, x: torch.Tensor, h: torch.Tensor, lg: torch.Tensor, M: int, renorm: bool, ids_out=None) -> None:
+        """Local experts for all rows, partial sums all-reduced (CPU ranks, and the NCCL baseline).  ``ids_out`` int32 [M][k]
+        receives the routing decision (every rank makes the same one)."""
         E, k, H = self.E, self.k, self.H
         dev = x.device
-        ids = torch.empty(M, k, dtype=torch.int32, device=dev)
+        ids = ids_out if ids_out is not None else torch.empty(M, k, dtype=torch.int32, device=dev)
         wts = torch.empty(M, k, dtype=torch.float32, device=dev)
         Hb.moe_route(lg, E, k, renorm, ids, wts)
         e0, e1 = self.expert_range()

@@ -295,3 +295,48 @@ def test_mtp_head_on_a_dense_ffn_hybrid_target_keeps_greedy(tmp_path):
     out, why, job = g.scheduler().generate(ids, 20)
     assert out == want
     g.close()
+
+
+def test_live_routing_counts_land_in_the_hit_file(hybrid_dirs, tmp_path, monkeypatch):
+    """``GRIMOIRE_EXPERT_HITS``: a serving process counts its routing decisions per (layer, expert) and adds them to the hit
+    file; a second process adds to the same file; counts are per logical expert whatever placement the model was loaded
+    with; the file is the one the placement reads at the next load."""
+    import json
+
+    from grimoire_b200.engine.engine import Engine, EngineLimits
+
+    cfg, _, split_dir, _ = hybrid_dirs
+    path = tmp_path / "hits.json"
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HITS", str(path))
+    ids = _prompt(40, 5)
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    out, _ = g.generate(ids, 8)
+    g.close()
+    first = torch.tensor(json.loads(path.read_text())["hits"])
+    k = cfg.num_experts_per_tok
+    rows = len(ids) + len(out) - 1                         # every prompt row and every decode step but the last token's
+    assert first.shape == (cfg.num_hidden_layers, cfg.num_experts)
+    assert all(int(first[l].sum()) == rows * k for l in range(cfg.num_hidden_layers)), first.sum(1)
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    g.generate(ids, 8)
+    g.close()
+    assert torch.equal(torch.tensor(json.loads(path.read_text())["hits"]), 2 * first)
+    # a permuted placement routes the same logical experts
+    gen = torch.Generator().manual_seed(4)
+    perms = [torch.randperm(cfg.num_experts, generator=gen).tolist() for _ in range(cfg.num_hidden_layers)]
+    counted = []
+    for tag, pm in (("plain", None), ("perm", perms)):
+        p2 = tmp_path / f"{tag}.json"
+        m = HybridModel.from_checkpoint(split_dir, "cpu", max_slots=2, expert_perm=pm)
+        m.record_expert_hits(str(p2), every=16)
+        eng = Engine(m, EngineLimits(max_slots=2, max_ctx=64, prefill_chunk=32, max_decode_rows=4))
+        eng.generate(ids, 8)
+        assert p2.exists()                                  # flushed on the way, every 16 tokens
+        m.save_expert_hits()
+        counted.append(torch.tensor(json.loads(p2.read_text())["hits"]))
+    assert torch.equal(counted[0], counted[1]) and int(counted[0].sum()) > 0
+    monkeypatch.delenv("GRIMOIRE_EXPERT_HITS")
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HEAT", str(path))
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    assert g.model.expert_perm is not None
+    g.close()
