@@ -53,6 +53,8 @@ def unsupported_reason(cfg: ModelConfig, ec: EngineConfig) -> Optional[str]:
             return "expert parallelism needs an MoE FFN"
         if cfg.is_k2 and ec.ep_world > 1:
             return "the K2-Horizon family is served on one GPU (its router is not built into the expert-parallel chain)"
+        if cfg.is_qwen4_exp and ec.ep_world > 1:
+            return "the Qwen4-Exp family is served on one GPU (its residual streams are not built into the expert-parallel chain)"
         if ec.tp_world > 1 or ec.pp_world > 1:
             return "the hybrid (DeltaNet + MoE) family scales by expert parallelism (multi EP); tensor / pipeline stages are not built for it"
         if cfg.num_experts % max(1, ec.ep_world):
@@ -114,6 +116,10 @@ class Grimoire:
                 from .models.gemma4 import Gemma4Model, MuseModel
 
                 model = (MuseModel if cfg.is_muse else Gemma4Model).random(cfg, dev, seed=0)
+            elif cfg.is_qwen4_exp:
+                from .models.qwen4_exp import Qwen4ExpModel
+
+                model = Qwen4ExpModel.random(cfg, dev, seed=0, max_slots=ec.seq_slots)
             elif is_hybrid(cfg):
                 model = HybridModel.random(cfg, dev, seed=0, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world)
             else:
@@ -187,6 +193,10 @@ class Grimoire:
                     from .models.gemma4 import Gemma4Model, MuseModel
 
                     model = (MuseModel if cfg.is_muse else Gemma4Model).from_checkpoint(ec.model, dev)
+                elif cfg.is_qwen4_exp:
+                    from .models.qwen4_exp import Qwen4ExpModel
+
+                    model = Qwen4ExpModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots)
                 elif is_hybrid(cfg):
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
@@ -231,7 +241,7 @@ class Grimoire:
         lim = EngineLimits(max_slots=ec.seq_slots, max_ctx=ec.ctx, prefill_chunk=ec.prefill_chunk, max_decode_rows=64,
                            kv_pages=ec.kv_pages, extra_kv_layers=1 if want_mtp else 0)
         eng = Engine(model, lim)
-        if ec.prefix_cache:
+        if ec.prefix_cache and not cfg.is_qwen4_exp:       # that family's n-gram history and convolution tails are not snapshotted
             eng.enable_prefix_cache()
         g = cls(model, eng, tok, ec)
         if want_mtp:

@@ -319,6 +319,8 @@ class Engine:
         full = return_logits or getattr(self.model, "head_split", None) is None
         if full and getattr(self.model, "head_split", None) is not None:
             use_graph = False        # whole logits rows of a split head are gathered by a library collective
+        if not getattr(self.model, "graph_safe", True):
+            use_graph = False        # the model does host work per step (n-gram ids from the step's tokens)
         if use_graph and self.device.type == "cuda":
             key = (M, splits, distinct) + ((shape,) if shape else ())
             g = self.graphs.get(key)

@@ -80,6 +80,21 @@ class ModelConfig:
     mova_top_k: int = 0
     mlp_only_layers: list[int] = field(default_factory=list)     # layers with a dense FFN in an MoE model
     decoder_sparse_step: int = 1            # layer i is sparse when (i + 1) % step == 0 and it is not mlp-only
+    # Qwen4-Exp family (the hybrid decoder under a multi-stream residual, sparse attention and per-layer n-gram embeddings)
+    hc_count: int = 0                       # residual streams (0: a plain residual)
+    hc_lowrank: int = 0                     # width of the mix's low-rank gate
+    ple_layer_ids: list[int] = field(default_factory=list)       # 1-based layers that add the n-gram embedding before their block
+    ple_embed_dim: int = 0
+    ple_conv_kernel_size: int = 4
+    ngram_size: int = 3
+    heads_per_ngram: int = 8
+    ngram_vocab_size_base: int = 0
+    ngram_seed: int = 1234
+    eos_token_id: int = 0
+    indexer_n_heads: int = 0                # sparse attention: indexer heads (0: dense attention)
+    indexer_head_dim: int = 0
+    indexer_budget: int = 0                 # tokens a query attends to (plus the block still being filled)
+    indexer_compress_ratio: int = 0         # tokens per pooled key block
     # MTP draft head
     mtp_num_hidden_layers: int = 0
     # quantization of the projections in a synthetic / converted model
@@ -116,6 +131,10 @@ class ModelConfig:
     @property
     def is_gemma4(self) -> bool:
         return self.model_type.startswith("gemma4")
+
+    @property
+    def is_qwen4_exp(self) -> bool:
+        return self.hc_count > 1
 
     @property
     def is_k2(self) -> bool:
@@ -186,7 +205,13 @@ class ModelConfig:
             return ModelConfig._muse_from_hf(cfg, mt, n_layers, heads, hd)
         if "k2_horizon" in mt:
             return ModelConfig._k2_from_hf(cfg, mt, n_layers, heads, hd)
+        q4 = {}
+        if "qwen4_exp" in mt:
+            q4 = ModelConfig._qwen4_exp_fields(cfg)
+            lt = [LINEAR_ATTN if t == LINEAR_ATTN else FULL_ATTN for t in lt]     # "qsa_attention" layers are full-attention layers
+            family35 = True
         return ModelConfig(
+            **q4,
             model_type=mt,
             hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
             num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd,
@@ -215,6 +240,36 @@ class ModelConfig:
             mlp_only_layers=[int(v) for v in (cfg.get("mlp_only_layers") or [])],
             decoder_sparse_step=int(cfg.get("decoder_sparse_step", 1) or 1),
         )
+
+    @staticmethod
+    def _qwen4_exp_fields(cfg: dict) -> dict:
+        """The family's own keys (src/qwen35_loader.cpp:617-660; defaults of ref/qwen4_exp_config.py:41-49).  The five indexer keys
+        come together or not at all; ``ple_layer_ids`` are 1-based; a sigmoid DeltaNet output gate is not served."""
+        idx = {k: int(cfg.get(k) or 0) for k in ("indexer_n_heads", "indexer_kv_heads", "indexer_head_dim", "indexer_budget",
+                                                  "indexer_compress_ratio")}
+        if any(idx.values()):
+            if not all(idx.values()):
+                raise ValueError("qwen4_exp: the five indexer_* keys must be given together: " + ", ".join(k for k, v in idx.items() if not v))
+            if idx["indexer_kv_heads"] != 1 or idx["indexer_budget"] % idx["indexer_compress_ratio"]:
+                raise ValueError("qwen4_exp: the indexer needs one key head and a budget that is a multiple of the compression ratio")
+        if cfg.get("output_gate_type") == "sigmoid":
+            raise ValueError("qwen4_exp: a sigmoid DeltaNet output gate is not served")
+        eos = cfg.get("eos_token_id", 0)
+        eos = eos[0] if isinstance(eos, (list, tuple)) else eos
+        n = int(cfg["num_hidden_layers"])
+        ple = sorted({int(v) for v in (cfg.get("ple_layer_ids") or [])})
+        if any(v < 1 or v > n for v in ple):
+            raise ValueError("qwen4_exp: ple_layer_ids are 1-based and must name existing layers")
+        hc = int(cfg.get("hc_count", 4))
+        if hc <= 1:
+            raise ValueError("qwen4_exp: hc_count must be above 1")
+        return dict(hc_count=hc, hc_lowrank=int(cfg.get("hc_lowrank", 320)), ple_layer_ids=ple,
+                    ple_embed_dim=int(cfg.get("ple_embed_dim") or cfg["hidden_size"]),
+                    ple_conv_kernel_size=int(cfg.get("ple_conv_kernel_size", 4)), ngram_size=int(cfg.get("ngram_size", 3)),
+                    heads_per_ngram=int(cfg.get("heads_per_ngram", 8)), ngram_vocab_size_base=int(cfg.get("ngram_vocab_size_base", 20_000_000)),
+                    ngram_seed=int(cfg.get("seed", 1234)), eos_token_id=int(eos or 0), indexer_n_heads=idx["indexer_n_heads"],
+                    indexer_head_dim=idx["indexer_head_dim"], indexer_budget=idx["indexer_budget"],
+                    indexer_compress_ratio=idx["indexer_compress_ratio"])
 
     @staticmethod
     def _gemma4_from_hf(cfg: dict, mt: str, n_layers: int, heads: int, hd: int) -> "ModelConfig":
@@ -367,6 +422,20 @@ def tiny_moe(layers: int = 2) -> ModelConfig:
                        quant="fp8_block")
 
 
+def tiny_qwen4_exp(layers: int = 4) -> ModelConfig:
+    """The hybrid MoE decoder under three residual streams, sparse attention (budget 16 tokens in blocks of 4) and an n-gram
+    embedding before layers 1 and 3."""
+    lt = [FULL_ATTN if (i % 2) == 1 else LINEAR_ATTN for i in range(layers)]
+    return ModelConfig(model_type="qwen4_exp_text", hidden_size=128, num_hidden_layers=layers, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, vocab_size=512, intermediate_size=0,
+                       partial_rotary_factor=0.5, attn_output_gate=True, qk_norm=True, norm_zero_centered=True,
+                       layer_types=lt, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64,
+                       linear_value_head_dim=64, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=128, quant="fp8_block", hc_count=3, hc_lowrank=16, ple_layer_ids=[1, 3],
+                       ple_embed_dim=32, ple_conv_kernel_size=3, ngram_size=3, heads_per_ngram=2, ngram_vocab_size_base=50,
+                       ngram_seed=7, eos_token_id=2, indexer_n_heads=2, indexer_head_dim=64, indexer_budget=16, indexer_compress_ratio=4)
+
+
 def tiny_gemma4(layers: int = 4) -> ModelConfig:
     """A small Gemma-4-style decoder: 3 sliding-window layers then 1 global layer (no v_proj, proportional RoPE over a
     quarter of the head), sandwich norms, GeGLU, layer scalars, logit soft cap; one head geometry for both layer types."""
@@ -398,5 +467,5 @@ def tiny_k2(layers: int = 3) -> ModelConfig:
                        router_scale=2.5, mova_experts=8, mova_top_k=2, mlp_only_layers=[0], decoder_sparse_step=1, quant="fp8_block")
 
 
-PRESETS = {"tiny_k2": tiny_k2, "tiny_muse": tiny_muse, "tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
+PRESETS = {"tiny_qwen4_exp": tiny_qwen4_exp, "tiny_k2": tiny_k2, "tiny_muse": tiny_muse, "tiny_gemma4": tiny_gemma4, "hybrid_dense_27b": hybrid_dense_27b, "tiny_hybrid_dense": tiny_hybrid_dense, "tiny_moe": tiny_moe, "tiny_dense": tiny_dense, "dense_27b": dense_27b, "small_dense": small_dense,
            "hybrid_moe_80b": hybrid_moe_80b, "tiny_hybrid_moe": tiny_hybrid_moe}

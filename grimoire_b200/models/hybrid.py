@@ -446,7 +446,7 @@ class HybridModel:
 
     @staticmethod
     def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1, expert_heat: str = "",
-                        expert_perm=None, proj: Optional[str] = None) -> "HybridModel":
+                        expert_perm=None, proj: Optional[str] = None, model_cls=None) -> "HybridModel":
         """Load a HF directory of the hybrid family.  Tensor names follow the reference's resolver
         (src/qwen35_loader.cpp:1149-1169 ``linear_attn.{in_proj_qkv,in_proj_z,in_proj_a,in_proj_b,conv1d,A_log,dt_bias,norm,
         out_proj}``, :1320-1380 ``mlp.gate``, ``mlp.shared_expert*``, per-expert ``mlp.experts.N.*`` or the fused
@@ -460,7 +460,7 @@ class HybridModel:
         cfg = ck.cfg
         if (cfg.is_moe and cfg.num_experts % ep_world) or (not cfg.is_moe and ep_world > 1):
             raise ValueError("from_checkpoint: the experts do not split over the expert-parallel ranks")
-        m = HybridModel(cfg, device, max_slots=max_slots, proj=proj)
+        m = (model_cls or HybridModel)(cfg, device, max_slots=max_slots, proj=proj)      # a family built on these blocks passes its class
         m.ep_rank, m.ep_world = ep_rank, ep_world
         if expert_perm is not None:
             m.expert_perm = [list(p) for p in expert_perm]       # explicit placement (per layer: physical -> logical expert)

@@ -161,3 +161,46 @@ def random_gemma4_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02)
         if cfg.layer_scalar:
             sd[p + "layer_scalar"] = torch.tensor([1.0 + 0.1 * ((i % 3) - 1)])
     return sd
+
+
+def random_qwen4_exp_state_dict(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> dict[str, torch.Tensor]:
+    """fp32 logical weights of a Qwen4-Exp decoder under its checkpoint names (src/qwen35_loader.cpp:1060-1145): the hybrid
+    family's blocks without any layernorm, two hyper-connections per layer and the tail mixer, an indexer on every attention
+    layer and the n-gram embedding layers of ``ple_layer_ids`` (table sized by the prime layout of that layer's heads)."""
+    from ..ref import qwen4_exp_ref as R
+
+    sd = random_hybrid_state_dict(cfg, seed, std)
+    for k in [k for k in sd if k.endswith("layernorm.weight") or k == "model.norm.weight"]:
+        del sd[k]
+    g = torch.Generator().manual_seed(seed + 9090)
+    rnd = lambda *shape, scale=std: torch.randn(*shape, generator=g, dtype=torch.float32) * scale
+    H, hc, low = cfg.hidden_size, cfg.hc_count, cfg.hc_lowrank
+    wide = hc * H
+
+    def connection(p: str, inject: bool):
+        sd[p + "hc_norm.weight"] = rnd(wide, scale=0.05)
+        sd[p + "input_mix_weight_down.weight"] = rnd(low, wide, scale=0.1)
+        sd[p + "input_mix_weight_up.weight"] = rnd(wide, low, scale=0.3)
+        if inject:
+            sd[p + "block_inject_weight.weight"] = rnd(hc, wide, scale=0.1)
+
+    ple_ids = sorted(set(cfg.ple_layer_ids))
+    heads = (cfg.ngram_size - 1) * cfg.heads_per_ngram
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        connection(p + "attn_hyper_connection.", True)
+        connection(p + "mlp_hyper_connection.", True)
+        if cfg.is_attention_layer(i) and cfg.indexer_n_heads:
+            ix, d = p + "self_attn.indexer.", cfg.indexer_head_dim
+            sd[ix + "index_qk_proj.weight"] = rnd((cfg.indexer_n_heads + 1) * d, H, scale=0.3)
+            sd[ix + "q_layernorm.weight"], sd[ix + "k_layernorm.weight"] = rnd(d, scale=0.05), rnd(d, scale=0.05)
+        if (i + 1) in ple_ids:
+            pl = p + "ple."
+            _, _, total = R.ngram_vocab_layout(cfg.ngram_vocab_size_base, heads, ple_ids.index(i + 1))
+            sd[pl + "ple_embedding.ngram_embedding.weight"] = rnd(total, cfg.ple_embed_dim // heads, scale=0.5)
+            sd[pl + "key_proj.weight"], sd[pl + "value_proj.weight"] = rnd(wide, cfg.ple_embed_dim, scale=0.2), rnd(H, cfg.ple_embed_dim, scale=0.05)
+            for k in ("norm_key", "norm_query", "norm_conv"):
+                sd[pl + k + ".weight"] = rnd(wide, scale=0.05)
+            sd[pl + "conv1d.weight"] = rnd(wide, 1, cfg.ple_conv_kernel_size, scale=0.3)
+    connection("model.hyper_connection_mixer.", False)
+    return sd

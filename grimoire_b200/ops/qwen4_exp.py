@@ -24,14 +24,25 @@ _c, _f = ctypes.c_int, ctypes.c_float
 
 
 class HyperConnection:
-    def __init__(self, norm_w: torch.Tensor, down: torch.Tensor, up: torch.Tensor, inj: torch.Tensor, hc: int, eps: float, device,
-                 max_rows: int = 64):
+    def __init__(self, norm_w: torch.Tensor, down: torch.Tensor, up: torch.Tensor, inj: Optional[torch.Tensor], hc: int, eps: float, device,
+                 max_rows: int = 64, scratch: Optional["HyperConnection"] = None):
+        """``inj`` None: a mixer that only reads the streams (the model's tail).  ``scratch``: another connection of the same
+        geometry whose row buffers this one borrows -- a model runs mix -> block -> combine of one connection before the
+        next one's mix, so one set of buffers serves them all."""
         self.device = torch.device(device)
         self.hc, self.eps = hc, eps
         self.wide = norm_w.shape[0]
         self.H, self.low = self.wide // hc, down.shape[0]
         self.norm_w = norm_w.to(device=self.device, dtype=torch.float32).contiguous()
-        self.down, self.up, self.inj = (BF16Linear(t, self.device, n) for t, n in ((down, "hc.down"), (up, "hc.up"), (inj, "hc.inj")))
+        self.down, self.up = BF16Linear(down, self.device, "hc.down"), BF16Linear(up, self.device, "hc.up")
+        self.inj = BF16Linear(inj, self.device, "hc.inj") if inj is not None else None
+        if scratch is not None:
+            if (scratch.wide, scratch.low, scratch.hc) != (self.wide, self.low, self.hc) or scratch.max_rows < max_rows:
+                raise ValueError("borrowed hyper-connection buffers do not fit")
+            for name in ("normed_f", "normed_b", "g_f", "g_b", "u", "injl"):
+                setattr(self, name, getattr(scratch, name))
+            self.max_rows = scratch.max_rows
+            return
         mk = lambda *s, dt: torch.zeros(*s, dtype=dt, device=self.device)
         self.normed_f, self.normed_b = mk(max_rows, self.wide, dt=torch.float32), mk(max_rows, self.wide, dt=torch.bfloat16)
         self.g_f, self.g_b = mk(max_rows, (self.low + 7) // 8 * 8, dt=torch.float32), mk(max_rows, (self.low + 7) // 8 * 8, dt=torch.bfloat16)

@@ -106,3 +106,31 @@ def write_tokenizer(path: Path, vocab_size: int):
     tok.train_from_iterator(corpus, tr)
     tok.save(str(path / "tokenizer.json"))
     (path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
+
+
+def write_qwen4_exp_checkpoint(path: Path, cfg: ModelConfig, seed: int = 0):
+    """A Qwen4-Exp checkpoint under the family's names: nested ``text_config`` with the hyper-connection, n-gram and indexer
+    keys (1-based ``ple_layer_ids``, ``eos_token_id`` as a list the way Qwen configs write it)."""
+    from grimoire_b200.models.synthetic import random_qwen4_exp_state_dict
+
+    path.mkdir(parents=True, exist_ok=True)
+    sd = random_qwen4_exp_state_dict(cfg, seed)
+    tc = {"model_type": "qwen4_exp_text", "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_hidden_layers,
+          "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+          "vocab_size": cfg.vocab_size, "rms_norm_eps": cfg.rms_norm_eps,
+          "rope_parameters": {"rope_theta": cfg.rope_theta, "partial_rotary_factor": cfg.partial_rotary_factor},
+          "layer_types": ["linear_attention" if t != "full_attention" else "qsa_attention" for t in cfg.layer_types],
+          "linear_num_key_heads": cfg.linear_num_key_heads, "linear_num_value_heads": cfg.linear_num_value_heads,
+          "linear_key_head_dim": cfg.linear_key_head_dim, "linear_value_head_dim": cfg.linear_value_head_dim,
+          "linear_conv_kernel_dim": cfg.linear_conv_kernel_dim, "num_experts": cfg.num_experts,
+          "num_experts_per_tok": cfg.num_experts_per_tok, "moe_intermediate_size": cfg.moe_intermediate_size,
+          "shared_expert_intermediate_size": cfg.shared_expert_intermediate_size, "norm_topk_prob": cfg.norm_topk_prob,
+          "intermediate_size": cfg.intermediate_size, "hc_count": cfg.hc_count, "hc_lowrank": cfg.hc_lowrank,
+          "ple_layer_ids": cfg.ple_layer_ids, "ple_embed_dim": cfg.ple_embed_dim, "ple_conv_kernel_size": cfg.ple_conv_kernel_size,
+          "ngram_size": cfg.ngram_size, "heads_per_ngram": cfg.heads_per_ngram, "ngram_vocab_size_base": cfg.ngram_vocab_size_base,
+          "seed": cfg.ngram_seed, "eos_token_id": [cfg.eos_token_id, cfg.eos_token_id + 1], "indexer_n_heads": cfg.indexer_n_heads,
+          "indexer_kv_heads": 1, "indexer_head_dim": cfg.indexer_head_dim, "indexer_budget": cfg.indexer_budget,
+          "indexer_compress_ratio": cfg.indexer_compress_ratio}
+    (path / "config.json").write_text(json.dumps({"model_type": "qwen4_exp", "tie_word_embeddings": cfg.tie_word_embeddings, "text_config": tc}))
+    save_file({k: v.bfloat16() for k, v in sd.items()}, path / "model.safetensors", {"format": "pt"})
+    return sd
