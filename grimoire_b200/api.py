@@ -369,21 +369,60 @@ class Grimoire:
             self.engine.release(s)
         return torch.stack(out)
 
-    def perplexity(self, ids: Sequence[int], ctx: int = 512, chunks: int = 0) -> dict:
-        """Perplexity over fixed windows (``--ppl FILE --ppl-ctx --ppl-chunks``, grimoire_perplexity
-        grimoire.cpp:23734)."""
+    def perplexity(self, ids: Sequence[int], ctx: int = 512, chunks: int = 0, dump: str = "", selfcheck: bool = False) -> dict:
+        """Perplexity over complete ``ctx``-token chunks, teacher-forced one row per step from a fresh conversation, scoring
+        the second half of each chunk (positions ctx/2 .. ctx-2 predict their successors) with a running mean and its standard
+        error (``--ppl FILE --ppl-ctx --ppl-chunks --ppl-dump --ppl-selfcheck``, grimoire_perplexity grimoire.cpp:23734-23905).
+        ``dump``: a TSV line per scored token -- chunk, position, target, its log-probability, the best token and its
+        log-probability, then the eight best ``id:logprob``.  ``selfcheck``: the decode logits of the first chunk's last
+        scored position against a batched prefill of the same prefix."""
         import math
 
-        nll, n = 0.0, 0
-        windows = [ids[i: i + ctx] for i in range(0, len(ids) - 1, ctx)]
+        V = self.model.cfg.vocab_size
+        count = len(ids) // ctx
         if chunks:
-            windows = windows[:chunks]
-        for w in windows:
-            if len(w) < 2:
-                continue
-            lg = self.score_ids(w)
-            lp = torch.log_softmax(lg[:-1].double(), dim=-1)
-            tgt = torch.tensor(w[1:])
-            nll -= float(lp[torch.arange(len(w) - 1), tgt].sum())
-            n += len(w) - 1
-        return {"ppl": math.exp(nll / max(n, 1)), "tokens": n, "nll": nll}
+            count = min(count, chunks)
+        if count < 1:
+            raise ValueError(f"{len(ids)} tokens, no complete {ctx}-token chunk")
+        if any(t < 0 or t >= V for t in ids[: count * ctx]):
+            raise ValueError("a token id lies outside the model's vocabulary")
+        if dump and V < 8:
+            raise ValueError("the dump lists eight candidates: the vocabulary is smaller")
+        out = open(dump, "w") if dump else None
+        scored, mean, m2 = 0, 0.0, 0.0
+        res: dict = {}
+        try:
+            for c in range(count):
+                w = list(ids[c * ctx: (c + 1) * ctx])
+                lg = self.score_ids(w[:-1]).double()                    # row p predicts token p + 1
+                for pos in range(ctx // 2, ctx - 1):
+                    row = lg[pos]
+                    if not bool(torch.isfinite(row).all()):
+                        raise ValueError(f"non-finite logits at position {pos}")
+                    lp = row - torch.logsumexp(row, 0)
+                    nll = -float(lp[w[pos + 1]])
+                    scored += 1
+                    delta = nll - mean
+                    mean += delta / scored
+                    m2 += delta * (nll - mean)
+                    if out is not None:
+                        top = torch.topk(lp, 8)
+                        best = int(top.indices[0])
+                        out.write("\t".join([str(c + 1), str(pos), str(w[pos + 1]), f"{-nll:.12g}", str(best), f"{float(lp[best]):.12g}"]
+                                            + [f"{int(i)}:{float(v):.12g}" for v, i in zip(top.values, top.indices)]) + "\n")
+                if selfcheck and c == 0:
+                    s = self.engine.open()
+                    try:
+                        pre = self.engine.prefill(s, w[:-1]).double().cpu()
+                    finally:
+                        self.engine.release(s)
+                    if not bool(torch.isfinite(pre).all()):
+                        raise ValueError("non-finite prefill logits")
+                    res["selfcheck_max_abs_diff"] = float((pre - lg[ctx - 2]).abs().max())
+        finally:
+            if out is not None:
+                out.close()
+        ppl = math.exp(mean)
+        se = math.sqrt(m2 / (scored - 1) / scored) if scored > 1 else 0.0
+        res.update({"ppl": ppl, "ppl_stderr": ppl * se, "tokens": scored, "chunks": count, "nll": mean * scored})
+        return res

@@ -31,6 +31,8 @@ def _generate(argv) -> int:
     ap.add_argument("--ppl-ctx", type=int, default=512)
     ap.add_argument("--ppl-chunks", type=int, default=0)
     ap.add_argument("--ppl-kld-base", default="", help="logits of a baseline run (.pt) to compare with")
+    ap.add_argument("--ppl-dump", default="", metavar="FILE", help="per-token TSV: target and best log-probabilities, eight candidates")
+    ap.add_argument("--ppl-selfcheck", action="store_true", help="compare the last scored decode logits with a batched prefill")
     ap.add_argument("--spec-depth", type=int, default=0)
     ns = ap.parse_args(argv)
     if not ns.model:
@@ -53,7 +55,7 @@ def _generate(argv) -> int:
         if ns.ppl:
             text = open(ns.ppl).read()
             ids = tok.encode(text) if tok else [int(t) for t in text.split()]
-            res = g.perplexity(ids, ns.ppl_ctx, ns.ppl_chunks)
+            res = g.perplexity(ids, ns.ppl_ctx, ns.ppl_chunks, dump=ns.ppl_dump, selfcheck=ns.ppl_selfcheck)
             if ns.ppl_kld_base:
                 import torch
 

@@ -1,6 +1,7 @@
 """Auxiliary subsystems: timeline / probe tracing, expert heat + placement, DFlash config resolution."""
 import json
 
+import pytest
 import torch
 
 from grimoire_b200.models.dflash import resolve_dflash_config
@@ -141,3 +142,40 @@ def test_verify_groups_and_split_heuristic():
     # one row, 8 kv heads: 16 splits up to 8,192 tokens (cluster merge), 32 from 16,384; never fewer than 8 pages a split
     assert [K.decode_splits(n, 1, 8) for n in (100, 512, 1024, 4096, 8192, 16384, 32768, 131072)] == [1, 4, 8, 16, 16, 32, 32, 32]
     assert K.decode_splits(4096, 8, 8) == 4 and K.decode_splits(4096, 1, 1) == 16
+
+
+def test_perplexity_scores_second_halves_and_dumps_candidates(tmp_path):
+    """``--ppl``: complete chunks only, positions ctx/2 .. ctx-2 scored, running mean with its standard error; ``--ppl-dump``
+    writes a line per scored token with the eight best candidates; ``--ppl-selfcheck`` compares decode with batched prefill."""
+    import math
+
+    import torch
+
+    from grimoire_b200.api import Grimoire
+    from grimoire_b200.config import EngineConfig
+
+    g = Grimoire.load(EngineConfig(model="synthetic:tiny_dense", ctx=64, seq_slots=2, prefill_chunk=32), device="cpu")
+    V = g.model.cfg.vocab_size
+    ids = torch.randint(0, V, (2 * 16 + 5,), generator=torch.Generator().manual_seed(0)).tolist()
+    dump = tmp_path / "ppl.tsv"
+    res = g.perplexity(ids, ctx=16, dump=str(dump), selfcheck=True)
+    assert res["chunks"] == 2 and res["tokens"] == 2 * 7                     # positions 8..14 of each 16-token chunk; 5 tokens dropped
+    want = []
+    for c in range(2):
+        w = ids[c * 16: (c + 1) * 16]
+        lp = torch.log_softmax(g.score_ids(w[:-1]).double(), -1)
+        want += [-float(lp[p, w[p + 1]]) for p in range(8, 15)]
+    mean = sum(want) / len(want)
+    assert res["ppl"] == pytest.approx(math.exp(mean), rel=1e-9)
+    var = sum((x - mean) ** 2 for x in want) / (len(want) - 1)
+    assert res["ppl_stderr"] == pytest.approx(math.exp(mean) * math.sqrt(var / len(want)), rel=1e-6)
+    assert res["selfcheck_max_abs_diff"] < 0.05
+    lines = dump.read_text().splitlines()
+    assert len(lines) == 14
+    f = lines[0].split("\t")
+    assert f[:3] == ["1", "8", str(ids[9])] and len(f) == 6 + 8 and float(f[3]) == pytest.approx(-want[0], rel=1e-9)
+    assert f[6].split(":")[0] == f[4] and float(f[6].split(":")[1]) == pytest.approx(float(f[5]))
+    assert g.perplexity(ids, ctx=16, chunks=1)["tokens"] == 7
+    with pytest.raises(ValueError, match="no complete"):
+        g.perplexity(ids[:10], ctx=16)
+    g.close()
