@@ -369,16 +369,30 @@ class Grimoire:
             self.engine.release(s)
         return torch.stack(out)
 
-    def perplexity(self, ids: Sequence[int], ctx: int = 512, chunks: int = 0, dump: str = "", selfcheck: bool = False) -> dict:
+    def perplexity(self, ids: Sequence[int], ctx: int = 512, chunks: int = 0, dump: str = "", selfcheck: bool = False,
+                   kld_base: str = "") -> dict:
         """Perplexity over complete ``ctx``-token chunks, teacher-forced one row per step from a fresh conversation, scoring
         the second half of each chunk (positions ctx/2 .. ctx-2 predict their successors) with a running mean and its standard
         error (``--ppl FILE --ppl-ctx --ppl-chunks --ppl-dump --ppl-selfcheck``, grimoire_perplexity grimoire.cpp:23734-23905).
         ``dump``: a TSV line per scored token -- chunk, position, target, its log-probability, the best token and its
         log-probability, then the eight best ``id:logprob``.  ``selfcheck``: the decode logits of the first chunk's last
-        scored position against a batched prefill of the same prefix."""
+        scored position against a batched prefill of the same prefix.  ``kld_base``: a llama-perplexity
+        ``--kl-divergence-base`` file; the chunks, their tokens and the context length come from it (``ids`` is unused), and
+        the result carries the KL-divergence / probability statistics against its rows under ``"kld"``."""
         import math
 
         V = self.model.cfg.vocab_size
+        base = kstats = None
+        if kld_base:
+            from .utils.kld import KldBase, KldStats
+
+            base, kstats = KldBase(kld_base), KldStats()
+            if base.vocab != V:
+                raise ValueError(f"vocabulary mismatch (base {base.vocab}, model {V})")
+            if chunks > base.chunks:
+                raise ValueError(f"more chunks asked than the base file has ({base.chunks})")
+            ctx = base.ctx
+            ids = [int(t) for c in range(base.chunks) for t in base.read_chunk(c)[0]]
         count = len(ids) // ctx
         if chunks:
             count = min(count, chunks)
@@ -395,6 +409,9 @@ class Grimoire:
             for c in range(count):
                 w = list(ids[c * ctx: (c + 1) * ctx])
                 lg = self.score_ids(w[:-1]).double()                    # row p predicts token p + 1
+                if base is not None:
+                    _, sc, mn, q = base.read_chunk(c)
+                    kstats.add_rows(lg[ctx // 2: ctx - 1].float().numpy(), sc, mn, q, w[ctx // 2 + 1: ctx])
                 for pos in range(ctx // 2, ctx - 1):
                     row = lg[pos]
                     if not bool(torch.isfinite(row).all()):
@@ -425,4 +442,7 @@ class Grimoire:
         ppl = math.exp(mean)
         se = math.sqrt(m2 / (scored - 1) / scored) if scored > 1 else 0.0
         res.update({"ppl": ppl, "ppl_stderr": ppl * se, "tokens": scored, "chunks": count, "nll": mean * scored})
+        if kstats is not None:
+            res["kld"] = kstats.summary()
+            res["kld_report"] = kstats.report()
         return res

@@ -30,7 +30,7 @@ def _generate(argv) -> int:
     ap.add_argument("--ppl", default="", metavar="FILE")
     ap.add_argument("--ppl-ctx", type=int, default=512)
     ap.add_argument("--ppl-chunks", type=int, default=0)
-    ap.add_argument("--ppl-kld-base", default="", help="logits of a baseline run (.pt) to compare with")
+    ap.add_argument("--ppl-kld-base", default="", help="a llama-perplexity --kl-divergence-base file, or baseline logits (.pt)")
     ap.add_argument("--ppl-dump", default="", metavar="FILE", help="per-token TSV: target and best log-probabilities, eight candidates")
     ap.add_argument("--ppl-selfcheck", action="store_true", help="compare the last scored decode logits with a batched prefill")
     ap.add_argument("--spec-depth", type=int, default=0)
@@ -55,14 +55,20 @@ def _generate(argv) -> int:
         if ns.ppl:
             text = open(ns.ppl).read()
             ids = tok.encode(text) if tok else [int(t) for t in text.split()]
-            res = g.perplexity(ids, ns.ppl_ctx, ns.ppl_chunks, dump=ns.ppl_dump, selfcheck=ns.ppl_selfcheck)
-            if ns.ppl_kld_base:
+            llama_base = bool(ns.ppl_kld_base) and open(ns.ppl_kld_base, "rb").read(8) == b"_logits_"
+            res = g.perplexity(ids, ns.ppl_ctx, ns.ppl_chunks, dump=ns.ppl_dump, selfcheck=ns.ppl_selfcheck,
+                               kld_base=ns.ppl_kld_base if llama_base else "")
+            if ns.ppl_kld_base and not llama_base:
+                # a torch file of baseline logits (--score-out of another run): distances over the first window
                 import torch
 
                 from .utils.kld import kld_stats
 
                 res["kld"] = kld_stats(torch.load(ns.ppl_kld_base), g.score_ids(ids[: ns.ppl_ctx]))
+            report = res.pop("kld_report", "")
             print(json.dumps(res))
+            if report:
+                print(report)
             return 0
         if ns.prefill_only:
             print(json.dumps({"pp": ns.prefill_only, "tok_s": round(g.bench_prefill(ns.prefill_only), 1)}))

@@ -179,3 +179,45 @@ def test_perplexity_scores_second_halves_and_dumps_candidates(tmp_path):
     with pytest.raises(ValueError, match="no complete"):
         g.perplexity(ids[:10], ctx=16)
     g.close()
+
+
+def test_kld_base_file_round_trip_and_statistics(tmp_path):
+    """The llama-perplexity base format (header, tokens, quantised log-probability rows) and its statistics: a model scored
+    against its own base gives a near-zero divergence and full top-1 agreement; a perturbed one does not."""
+    import numpy as np
+    import torch
+
+    from grimoire_b200.api import Grimoire
+    from grimoire_b200.config import EngineConfig
+    from grimoire_b200.utils.kld import KldBase, KldStats, write_kld_base
+
+    g = Grimoire.load(EngineConfig(model="synthetic:tiny_dense", ctx=64, seq_slots=2, prefill_chunk=32), device="cpu")
+    V, ctx = g.model.cfg.vocab_size, 16
+    ids = torch.randint(0, V, (3 * ctx,), generator=torch.Generator().manual_seed(1)).tolist()
+    chunks = [ids[c * ctx: (c + 1) * ctx] for c in range(3)]
+    rows = [g.score_ids(w[:-1])[ctx // 2: ctx - 1].float().numpy() for w in chunks]
+    path = tmp_path / "base.kld"
+    write_kld_base(str(path), ctx, chunks, rows)
+    b = KldBase(str(path))
+    assert (b.ctx, b.vocab, b.chunks, b.scored) == (ctx, V, 3, 7)
+    tok, sc, mn, q = b.read_chunk(1)
+    assert tok.tolist() == chunks[1] and q.shape == (7, V)
+    lp = torch.log_softmax(torch.tensor(rows[1]).double(), -1).numpy()
+    back = sc[:, None] * q.astype(np.float32) + mn[:, None]
+    keep = lp > lp.max(1, keepdims=True) - 15.9
+    assert np.abs(back - lp)[keep].max() < 2e-3                     # 16 nats over 65,535 steps
+    res = g.perplexity([], kld_base=str(path))
+    k = res["kld"]
+    assert res["chunks"] == 3 and k["count"] == 21 and k["kld_mean"] < 1e-5 and k["same_top"] == 1.0 and abs(k["ln_ppl_ratio"]) < 1e-3
+    assert res["kld_report"] == ""                                  # under 100 scored tokens nothing is printed, as in llama.cpp
+    st = KldStats()
+    noisy = rows[0] + np.random.default_rng(0).normal(0, 1.0, rows[0].shape).astype(np.float32)
+    _, sc0, mn0, q0 = b.read_chunk(0)
+    st.add_rows(noisy, sc0, mn0, q0, chunks[0][ctx // 2 + 1:])
+    s = st.summary()
+    assert s["kld_mean"] > 0.05 and s["kld_max"] >= s["kld_median"] >= s["kld_min"] >= 0 and s["dp_rms"] > 0
+    bad = tmp_path / "bad.kld"
+    bad.write_bytes(path.read_bytes()[:-2])
+    with pytest.raises(ValueError, match="size mismatch"):
+        KldBase(str(bad))
+    g.close()
