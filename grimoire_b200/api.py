@@ -200,6 +200,7 @@ class Grimoire:
                 elif is_hybrid(cfg):
                     model = HybridModel.from_checkpoint(ec.model, dev, max_slots=ec.seq_slots, ep_rank=ec.ep_rank, ep_world=ec.ep_world,
                                                         expert_heat=os.environ.get("GRIMOIRE_EXPERT_HEAT", ""),
+                                                        vram_experts=int(os.environ.get("GRIMOIRE_EXPERT_VRAM_PER_LAYER", "0") or 0),
                                                         proj=None if cfg.is_moe else {"int4": "int4", "fp8": "fp8"}.get(ec.proj))
                     if ec.mtp and cfg.mtp_num_hidden_layers > 0 and not cfg.is_moe and ec.ep_world == 1:
                         from .formats.checkpoint import Checkpoint

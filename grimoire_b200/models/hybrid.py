@@ -53,6 +53,7 @@ class HybridLayer:
     in_norm: torch.Tensor
     post_norm: torch.Tensor
     moe: Optional[MoEBlock]       # None: dense FFN (ffn_gu / ffn_down)
+    cx: Optional[object] = None   # ops.cpu_experts.CpuExperts: this layer's experts that live in host memory
     ffn_gu: Optional[object] = None
     ffn_down: Optional[object] = None
     # K2-Horizon: separate attention gate projection (softplus), routed value projection, router selection bias
@@ -153,6 +154,7 @@ class HybridModel:
         self.expert_perm = None          # per layer: physical -> logical expert (set_expert_placement), None = identity
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self._hits = None                # [layers][experts] int64 routing counts on the device (record_expert_hits)
+        self.vram_experts = 0            # > 0: experts per layer kept on the device, the rest computed on the host
         self._cur_layer = 0
         self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = True       # verify blocks: rows run as one recurrent run, rejected rows are undone by replay
@@ -410,6 +412,13 @@ class HybridModel:
         else:
             gu8, gus = experts(w["gate_up"])
             dn8, dns = experts(w["down"])
+            nres = self.vram_experts
+            if 0 < nres < E:
+                # RAM tier: physical experts [nres, E) stay in host memory (the placement put the hottest first)
+                from ..ops.cpu_experts import CpuExperts
+
+                ffn["cx"] = CpuExperts(nres, gu8[nres:], gus[nres:], dn8[nres:], dns[nres:], pin=self.device.type == "cuda")
+                gu8, gus, dn8, dns = (t[:nres].contiguous() for t in (gu8, gus, dn8, dns))
             sg = w.get("shared_gate")
             router = torch.cat([dense(w["router"]), dense(sg) if sg is not None else torch.zeros(1, cfg.hidden_size)], dim=0)
             shared = w.get("shared_gate_proj") is not None
@@ -446,7 +455,7 @@ class HybridModel:
 
     @staticmethod
     def from_checkpoint(path, device, max_slots: int = 8, ep_rank: int = 0, ep_world: int = 1, expert_heat: str = "",
-                        expert_perm=None, proj: Optional[str] = None, model_cls=None) -> "HybridModel":
+                        expert_perm=None, proj: Optional[str] = None, model_cls=None, vram_experts: int = 0) -> "HybridModel":
         """Load a HF directory of the hybrid family.  Tensor names follow the reference's resolver
         (src/qwen35_loader.cpp:1149-1169 ``linear_attn.{in_proj_qkv,in_proj_z,in_proj_a,in_proj_b,conv1d,A_log,dt_bias,norm,
         out_proj}``, :1320-1380 ``mlp.gate``, ``mlp.shared_expert*``, per-expert ``mlp.experts.N.*`` or the fused
@@ -462,6 +471,19 @@ class HybridModel:
             raise ValueError("from_checkpoint: the experts do not split over the expert-parallel ranks")
         m = (model_cls or HybridModel)(cfg, device, max_slots=max_slots, proj=proj)      # a family built on these blocks passes its class
         m.ep_rank, m.ep_world = ep_rank, ep_world
+        if vram_experts and cfg.is_moe and vram_experts < cfg.num_experts:
+            # RAM tier (one GPU): ``vram_experts`` experts per layer on the device -- the hottest of the heat file when there
+            # is one, the first ones otherwise -- and the rest in host memory behind the CPU pool
+            if ep_world > 1 or cfg.is_k2:
+                raise ValueError("host-resident experts are served on one GPU with the softmax router")
+            m.vram_experts = int(vram_experts)
+            m.graph_safe = False                                  # the routes come back to the host every layer
+            if expert_perm is None and expert_heat:
+                from .expert_placement import ExpertHeat
+
+                heat = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts)
+                if heat.load(expert_heat):
+                    expert_perm = [sorted(range(cfg.num_experts), key=lambda e, l=l: (-float(heat.h[l][e]), e)) for l in range(cfg.num_hidden_layers)]
         if expert_perm is not None:
             m.expert_perm = [list(p) for p in expert_perm]       # explicit placement (per layer: physical -> logical expert)
         elif expert_heat:
@@ -550,7 +572,7 @@ class HybridModel:
         if cfg.router_sigmoid:
             self._moe_k2(L, x, h, buf, M, decode, lg)
             return self._credit(ids=buf.ids[:M])
-        if self.ep is None and not decode and x.is_cuda and M > 64:
+        if self.ep is None and not decode and x.is_cuda and M > 64 and L.cx is None:
             # a prompt chunk on one GPU: group the rows by expert on the device (the expert-parallel chain with
             # this GPU as its only rank) instead of sorting on the host, which would stall the stream every layer
             if self._local_moe is None or self._local_moe.max_rows < buf.max_rows:
@@ -585,6 +607,16 @@ class HybridModel:
             return self._credit(ids=buf.ids[:M]) if self.ep.rank == 0 else None
         ids, wts = buf.ids[:M], buf.wts[:M]
         Hb.moe_route(lg, E, k, cfg.norm_topk_prob, ids, wts, shared_gate=True)
+        self._credit(ids=ids)
+        host_part = None
+        if L.cx is not None:
+            # routes to host experts: the CPU pool computes them from host copies of the rows while the device runs the
+            # resident ones; on the device they become expert 0 with weight 0
+            ids_h, wts_h, x_h = (t.to("cpu", copy=True) for t in (ids, wts, x))       # copies even when the model itself runs on the CPU path
+            away = ids >= L.cx.first
+            wts[:, :k].masked_fill_(away, 0.0)
+            ids.masked_fill_(away, 0)
+            host_part = L.cx.run(x_h, ids_h, wts_h)
         act, y, pos = buf.act[: M * k], buf.y[: M * (k + 1)], buf.pos[:M]
         if decode:
             te, r0, nr, src = ids.reshape(-1), buf.tile_row0[: M * k], buf.tile_rows[: M * k], buf.tile_src[: M * k]
@@ -615,7 +647,8 @@ class HybridModel:
         if not decode:
             pos[:, k] = torch.arange(M * k, M * (k + 1), dtype=torch.int32, device=x.device)
         Hb.moe_combine(h, y, pos, wts)
-        self._credit(ids=ids)
+        if host_part is not None:
+            h.add_(host_part.to(h.device, non_blocking=True))
 
     # ---- routing counts for the placement file ----
     def record_expert_hits(self, path: str, every: int = 256) -> None:

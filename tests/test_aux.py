@@ -221,3 +221,51 @@ def test_kld_base_file_round_trip_and_statistics(tmp_path):
     with pytest.raises(ValueError, match="size mismatch"):
         KldBase(str(bad))
     g.close()
+
+
+def test_host_expert_rows_match_a_plain_product():
+    """csrc/host/cpu_experts.cpp: block-scaled e4m3 expert FFN rows on CPU threads -- same numbers for any thread count,
+    refusal of unsorted pairs and of widths that are no multiple of the scale block."""
+    import ctypes
+
+    import torch
+
+    from grimoire_b200 import _native
+    from grimoire_b200.formats.codecs import Fmt
+    from grimoire_b200.formats.quantize import quantize
+    from grimoire_b200.ops.cpu_experts import CpuExperts
+
+    torch.manual_seed(0)
+    E, H, I, M, k = 3, 256, 128, 6, 2
+    gu, dn = torch.randn(E, 2 * I, H) * 0.05, torch.randn(E, H, I) * 0.05
+
+    def q3(t):
+        n, kk = t.shape[1], t.shape[2]
+        q = quantize(t.reshape(E * n, kk), Fmt.FP8_BLOCK)
+        return q.payload.reshape(E, n, kk), q.scales.reshape(E, n, kk // 128).float(), q.dequant().float().reshape(E, n, kk)
+
+    g8, gs, gd = q3(gu)
+    d8, ds, dd = q3(dn)
+    x = torch.randn(M, H).bfloat16()
+    ids = torch.tensor([[0, 1], [2, 1], [0, 0], [1, 2], [2, 0], [1, 1]], dtype=torch.int32)
+    w = torch.rand(M, k + 1)
+    want = torch.zeros(M, H)
+    for m in range(M):
+        for j in range(k):
+            e = int(ids[m, j])
+            if e >= 1:
+                xf = x[m].float()
+                a = (torch.nn.functional.silu(gd[e, :I] @ xf) * (gd[e, I:] @ xf)).bfloat16().float()
+                want[m] += w[m, j] * (dd[e] @ a)
+    outs = [CpuExperts(1, g8[1:], gs[1:], d8[1:], ds[1:], threads=t).run(x, ids, w) for t in (1, 3, 16)]
+    assert float((outs[0] - want).abs().max()) < 1e-5
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])          # one writer per row, pairs in order
+    assert CpuExperts(3, g8[:0], gs[:0], d8[:0], ds[:0]).run(x, ids, w) is None       # no route names a host expert
+    lib = _native.host()
+    rows, exp, wt = torch.tensor([1, 0], dtype=torch.int32), torch.zeros(2, dtype=torch.int32), torch.ones(2)
+    out = torch.zeros(M, H)
+    args = lambda h, i: (_native.ptr(g8), _native.ptr(gs), _native.ptr(d8), _native.ptr(ds), _native.ptr(x), ctypes.c_int(H), _native.ptr(rows),
+                         _native.ptr(exp), _native.ptr(wt), ctypes.c_int(2), _native.ptr(out), ctypes.c_int(H), ctypes.c_int(h), ctypes.c_int(i),
+                         ctypes.c_int(2))
+    assert lib.grm_cx_moe_rows(*args(H, I)) == -2                                     # rows must not decrease
+    assert lib.grm_cx_moe_rows(*args(H + 64, I)) == -2

@@ -340,3 +340,51 @@ def test_live_routing_counts_land_in_the_hit_file(hybrid_dirs, tmp_path, monkeyp
     g = Grimoire.load(_ec(split_dir), device="cpu")
     assert g.model.expert_perm is not None
     g.close()
+
+
+def test_host_resident_experts_give_the_same_logits(hybrid_dirs, tmp_path, monkeypatch):
+    """The RAM tier: with ``GRIMOIRE_EXPERT_VRAM_PER_LAYER`` experts per layer on the device the others stay in host memory
+    as the same fp8 blocks and the CPU pool computes their routes -- same logits and tokens as the all-device model; with a
+    heat file the hottest experts are the resident ones, so fewer routes leave the device."""
+    import json
+
+    from grimoire_b200.ops.cpu_experts import CpuExperts
+
+    cfg, _, split_dir, _ = hybrid_dirs
+    ids = _prompt(70, 13)                                  # longer than a decode block: prompt rows go through the sorted path
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    base = g.score_ids(ids[:24])
+    s = g.engine.open()
+    base_last = g.engine.prefill(s, ids).float()
+    g.engine.release(s)
+    want, _ = g.generate(ids, 6)
+    g.close()
+    hits = tmp_path / "hits.json"
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HITS", str(hits))
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    g.generate(ids, 6)
+    g.close()
+    monkeypatch.delenv("GRIMOIRE_EXPERT_HITS")
+    served = {}
+    for tag, heat in (("first", ""), ("hot", str(hits))):
+        monkeypatch.setenv("GRIMOIRE_EXPERT_VRAM_PER_LAYER", "4")
+        if heat:
+            monkeypatch.setenv("GRIMOIRE_EXPERT_HEAT", heat)
+        g = Grimoire.load(_ec(split_dir), device="cpu")
+        pools = [L.cx for L in g.model.layers]
+        assert all(isinstance(c, CpuExperts) and c.n == cfg.num_experts - 4 for c in pools)
+        assert all(L.moe.gate_up.shape[0] == 4 for L in g.model.layers) and g.model.graph_safe is False
+        got = g.score_ids(ids[:24])
+        assert float((got - base).abs().max()) < 1e-2 * float(base.abs().max()), float((got - base).abs().max())   # summation order differs; bf16 activations and the int8 cache amplify it
+        s = g.engine.open()
+        last = g.engine.prefill(s, ids).float()
+        g.engine.release(s)
+        assert float((last - base_last).abs().max()) < 1e-2 * float(base_last.abs().max())
+        assert float((got.argmax(-1) == base.argmax(-1)).float().mean()) >= 0.95
+        out, _ = g.generate(ids, 6)
+        assert out[0] == want[0] and len(out) == 6              # a random model's near-ties may part later tokens
+        served[tag] = sum(c.rows_served for c in pools)
+        g.close()
+    assert 0 < served["hot"] < served["first"], served
+    total = json.loads(hits.read_text())["hits"]
+    assert sum(map(sum, total)) > 0
