@@ -220,6 +220,8 @@ class Grimoire:
             if ck_dir and tok is None and os.path.exists(os.path.join(ck_dir, "tokenizer.json")):
                 tok = Tokenizer(ck_dir)
         hybrid = isinstance(model, HybridModel)
+        if hybrid and getattr(model, "vram_experts", 0) and int(os.environ.get("GRIMOIRE_EXPERT_SWAPS", "0") or 0) > 0:
+            model.enable_expert_swaps(int(os.environ["GRIMOIRE_EXPERT_SWAPS"]))      # hot host experts move onto the device as traffic shifts
         if hybrid and os.environ.get("GRIMOIRE_EXPERT_HITS"):
             model.record_expert_hits(os.environ["GRIMOIRE_EXPERT_HITS"])     # the file GRIMOIRE_EXPERT_HEAT reads at the next load
         if tp is not None:

@@ -155,6 +155,8 @@ class HybridModel:
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self._hits = None                # [layers][experts] int64 routing counts on the device (record_expert_hits)
         self.vram_experts = 0            # > 0: experts per layer kept on the device, the rest computed on the host
+        self.heat = None                 # expert_placement.ExpertHeat while the RAM tier swaps experts at run time
+        self.swaps_per_step, self.swaps_done = 0, 0
         self._cur_layer = 0
         self.ep_rank, self.ep_world = 0, 1
         self.supports_verify_rows = True       # verify blocks: rows run as one recurrent run, rejected rows are undone by replay
@@ -613,6 +615,9 @@ class HybridModel:
             # routes to host experts: the CPU pool computes them from host copies of the rows while the device runs the
             # resident ones; on the device they become expert 0 with weight 0
             ids_h, wts_h, x_h = (t.to("cpu", copy=True) for t in (ids, wts, x))       # copies even when the model itself runs on the CPU path
+            if self.heat is not None:
+                perm = self.expert_perm[self._cur_layer]
+                self.heat.credit(self._cur_layer, [perm[j] for j in ids_h.reshape(-1).tolist()])
             away = ids >= L.cx.first
             wts[:, :k].masked_fill_(away, 0.0)
             ids.masked_fill_(away, 0)
@@ -673,8 +678,67 @@ class HybridModel:
             flat = ids.reshape(-1).long()
             row.index_add_(0, flat, self._hits_one.expand(flat.numel()))
 
+    # ---- RAM tier: experts change places between the device and the host as the traffic moves ----
+    def enable_expert_swaps(self, swaps_per_step: int, params=None) -> None:
+        """Keep a decayed heat per (layer, expert) from the routes the host sees and, at every step boundary, promote up to
+        ``swaps_per_step`` hot host experts into the device slots of colder resident ones (hysteresis as in
+        ``ExpertHeat.propose_swaps``; within a layer: every layer owns its device slots).  Reference: the heat engine of the
+        tiered-MoE manager (include/b70/expert_heat.hpp:22-100; tm_heat_step, src/grimoire.cpp:14348)."""
+        from .expert_placement import ExpertHeat
+
+        cfg = self.cfg
+        if not self.vram_experts:
+            raise ValueError("expert swaps need host-resident experts (vram_experts)")
+        if self.expert_perm is None:
+            self.expert_perm = [list(range(cfg.num_experts)) for _ in range(cfg.num_hidden_layers)]
+        self.heat = ExpertHeat(cfg.num_hidden_layers, cfg.num_experts, params)
+        self.swaps_per_step = int(swaps_per_step)
+
+    def swap_experts(self, layer: int, hot: int, cold: int) -> None:
+        """Logical expert ``hot`` (in host memory) takes the device slot of logical expert ``cold``: weights, scales and
+        router rows change places, and so do the two entries of the layer's placement."""
+        L, perm = self.layers[layer], self.expert_perm[layer]
+        j, hh = perm.index(cold), perm.index(hot)
+        n = self.vram_experts
+        if not (j < n <= hh) or L.cx is None:
+            raise ValueError("swap_experts: hot must be host-resident and cold device-resident")
+        moe, cx = L.moe, L.cx
+        for dev_t, host_t in ((moe.gate_up, cx.gu), (moe.gate_up_scale, cx.gus), (moe.down, cx.dn), (moe.down_scale, cx.dns)):
+            tmp = dev_t[j].to("cpu", copy=True)
+            dev_t[j].copy_(host_t[hh - n])
+            host_t[hh - n].copy_(tmp)
+        rw = moe.router.w
+        tmp = rw[j].clone()
+        rw[j].copy_(rw[hh])
+        rw[hh].copy_(tmp)
+        perm[j], perm[hh] = hot, cold
+        if self._hits is not None:                           # the routing counts are kept per physical slot: they move along
+            for t in (self._hits[layer], self._hits_saved[layer]):
+                a = t[j].clone()
+                t[j] = t[hh]
+                t[hh] = a
+        self.swaps_done += 1
+
+    def heat_step(self) -> int:
+        """One step boundary of the heat engine; returns the number of swaps made."""
+        if self.heat is None or self.swaps_per_step <= 0:
+            return 0
+        n, made = self.vram_experts, 0
+        for l, L in enumerate(self.layers):
+            if L.cx is None or made >= self.swaps_per_step:
+                continue
+            perm = self.expert_perm[l]
+            where = {e: j for j, e in enumerate(perm)}
+            for sw in self.heat.propose_swaps(lambda ll, e: where[e] < n, lambda ll, e: ll == l):
+                if made >= self.swaps_per_step:
+                    break
+                self.swap_experts(l, sw.promote_expert, sw.demote_expert)
+                made += 1
+        return made
+
     def on_tokens(self, n: int) -> None:
         """Host-side step boundary (the engine calls it with the rows it committed)."""
+        self.heat_step()
         if self._hits is None:
             return
         self._hits_tokens += n

@@ -388,3 +388,47 @@ def test_host_resident_experts_give_the_same_logits(hybrid_dirs, tmp_path, monke
     assert 0 < served["hot"] < served["first"], served
     total = json.loads(hits.read_text())["hits"]
     assert sum(map(sum, total)) > 0
+
+
+def test_run_time_expert_swaps_follow_the_traffic(hybrid_dirs, tmp_path, monkeypatch):
+    """``GRIMOIRE_EXPERT_SWAPS``: the heat of the routes the host sees promotes hot host experts into device slots at step
+    boundaries -- weights, scales, router rows and the placement move together, so the logits stay, fewer routes leave the
+    device on the same traffic, and the routing counts still name logical experts."""
+    import json
+
+    cfg, _, split_dir, _ = hybrid_dirs
+    ids = _prompt(48, 21)
+    ref_hits = tmp_path / "ref.json"
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HITS", str(ref_hits))
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    base = g.score_ids(ids[:20])
+    g.close()
+    hits = tmp_path / "hits.json"
+    monkeypatch.setenv("GRIMOIRE_EXPERT_HITS", str(hits))
+    monkeypatch.setenv("GRIMOIRE_EXPERT_VRAM_PER_LAYER", "6")
+    monkeypatch.setenv("GRIMOIRE_EXPERT_SWAPS", "4")
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    m = g.model
+    assert m.heat is not None and m.expert_perm[0] == list(range(cfg.num_experts))
+    pools = [L.cx for L in m.layers]
+    served = []
+    for _ in range(4):                                   # the same traffic again and again: the placement adapts to it
+        before = sum(c.rows_served for c in pools)
+        s = g.engine.open()
+        g.engine.prefill(s, ids)
+        g.engine.release(s)
+        served.append(sum(c.rows_served for c in pools) - before)
+    assert m.swaps_done > 0 and any(p != list(range(cfg.num_experts)) for p in m.expert_perm)
+    assert all(sorted(p) == list(range(cfg.num_experts)) for p in m.expert_perm)
+    assert served[-1] < served[0], served
+    got = g.score_ids(ids[:20])
+    assert float((got - base).abs().max()) < 1e-2 * float(base.abs().max())
+    assert float((got.argmax(-1) == base.argmax(-1)).float().mean()) >= 0.95
+    with pytest.raises(ValueError):
+        m.swap_experts(0, m.expert_perm[0][0], m.expert_perm[0][1])           # both on the device
+    g.close()
+    # counts per logical expert: 4 prompt passes + one scoring pass here against one scoring pass of the all-device model
+    a, b = torch.tensor(json.loads(hits.read_text())["hits"]), torch.tensor(json.loads(ref_hits.read_text())["hits"])
+    assert int(a.sum()) == (4 * len(ids) + 20) * cfg.num_experts_per_tok * cfg.num_hidden_layers
+    assert int(b.sum()) == 20 * cfg.num_experts_per_tok * cfg.num_hidden_layers
+    assert float(torch.corrcoef(torch.stack([a.float().flatten(), b.float().flatten()]))[0, 1]) > 0.5
