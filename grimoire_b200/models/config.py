@@ -80,6 +80,7 @@ class ModelConfig:
     mova_top_k: int = 0
     mlp_only_layers: list[int] = field(default_factory=list)     # layers with a dense FFN in an MoE model
     decoder_sparse_step: int = 1            # layer i is sparse when (i + 1) % step == 0 and it is not mlp-only
+    parallel_ffn_intermediate_size: int = 0      # Agnes: width of the second SwiGLU of every mlp, folded into the first at load (intermediate_size counts it)
     # Qwen4-Exp family (the hybrid decoder under a multi-stream residual, sparse attention and per-layer n-gram embeddings)
     hc_count: int = 0                       # residual streams (0: a plain residual)
     hc_lowrank: int = 0                     # width of the mix's low-rank gate
@@ -131,6 +132,10 @@ class ModelConfig:
     @property
     def is_gemma4(self) -> bool:
         return self.model_type.startswith("gemma4")
+
+    @property
+    def is_agnes(self) -> bool:
+        return self.model_type.startswith("agnes")
 
     @property
     def is_qwen4_exp(self) -> bool:
@@ -196,8 +201,18 @@ class ModelConfig:
         n_layers = int(cfg["num_hidden_layers"])
         heads = int(cfg["num_attention_heads"])
         hd = int(cfg.get("head_dim") or cfg["hidden_size"] // heads)
-        lt = list(cfg.get("layer_types") or [])
-        lt = [LINEAR_ATTN if t in ("linear_attention", "linear") else FULL_ATTN for t in lt]
+        raw_types = list(cfg.get("layer_types") or [])
+
+        def kind(i: int, t: str) -> str:
+            # listed names only: an unknown spelling that fell through to full attention would load, generate fluent text
+            # and not be the model (src/qwen35_loader.cpp:800-858)
+            if t in ("linear_attention", "linear") or "delta" in t:
+                return LINEAR_ATTN
+            if t in ("full_attention", "sliding_attention", "attention", "qsa_attention", "qwen_sparse_attention") or "global" in t:
+                return FULL_ATTN
+            raise ValueError(f"config.json layer_types[{i}] is {t!r}, which is neither a known linear nor a known full attention layer")
+
+        lt = [kind(i, str(t)) for i, t in enumerate(raw_types)] if not (mt.startswith("gemma4") or "muse_glimmer" in mt) else raw_types
         family35 = mt.startswith("qwen3_5") or mt.startswith("qwen3_next") or mt.startswith("qwen3.5")
         if mt.startswith("gemma4"):
             return ModelConfig._gemma4_from_hf(cfg, mt, n_layers, heads, hd)
@@ -206,6 +221,13 @@ class ModelConfig:
         if "k2_horizon" in mt:
             return ModelConfig._k2_from_hf(cfg, mt, n_layers, heads, hd)
         q4 = {}
+        if mt.startswith("agnes"):
+            # Agnes: the 3.5-style hybrid under other names, with a second narrow SwiGLU inside every mlp that the loader
+            # folds into the main one (src/qwen35_loader.cpp:571-600, :749-777); its DeltaNet geometry must be present
+            family35 = True
+            q4 = dict(parallel_ffn_intermediate_size=int(cfg.get("parallel_ffn_intermediate_size", 0)))
+            if int(cfg.get("linear_num_key_heads", 0)) <= 0 or int(cfg.get("linear_num_value_heads", 0)) <= 0:
+                raise ValueError("Agnes: no gated-DeltaNet geometry in the config")
         if "qwen4_exp" in mt:
             q4 = ModelConfig._qwen4_exp_fields(cfg)
             lt = [LINEAR_ATTN if t == LINEAR_ATTN else FULL_ATTN for t in lt]     # "qsa_attention" layers are full-attention layers
@@ -215,7 +237,9 @@ class ModelConfig:
             model_type=mt,
             hidden_size=int(cfg["hidden_size"]), num_hidden_layers=n_layers, num_attention_heads=heads,
             num_key_value_heads=int(cfg.get("num_key_value_heads", heads)), head_dim=hd,
-            vocab_size=int(cfg["vocab_size"]), intermediate_size=int(cfg.get("intermediate_size", 0)),
+            vocab_size=int(cfg["vocab_size"]),
+            # Agnes: the served FFN is the main SwiGLU with the parallel one folded in, so its width is the sum
+            intermediate_size=int(cfg.get("intermediate_size", 0)) + q4.get("parallel_ffn_intermediate_size", 0),
             rms_norm_eps=float(cfg.get("rms_norm_eps", 1e-6)),
             rope_theta=float(rp.get("rope_theta", cfg.get("rope_theta", 1e6))),
             partial_rotary_factor=float(rp.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 1.0))),

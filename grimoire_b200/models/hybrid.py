@@ -144,6 +144,43 @@ class _DictSource:
         return self.sd[self.prefix + "embed_tokens.weight"]
 
 
+class _AgnesSource:
+    """An Agnes checkpoint seen through the hybrid family's names (src/qwen35_loader.cpp:1148-1165, :1264-1290): its two
+    attention submodules are ``delta_attn`` / ``global_attn``, and every mlp carries a second, narrow SwiGLU
+    (``mlp.parallel_ffn.{gate,up,down}_proj``) on the same normed input whose result lands in the same residual.  Two
+    SwiGLUs summed are one SwiGLU over the concatenated intermediate, so the fold is a load-time concatenation:
+    gate' = [gate ; pgate] and up' = [up ; pup] by rows, down' = [down | pdown] by columns."""
+
+    def __init__(self, src, cfg: ModelConfig):
+        self.src, self.cfg, self.prefix = src, cfg, src.prefix
+
+    def _name(self, name: str) -> str:
+        return name.replace(".linear_attn.", ".delta_attn.").replace(".self_attn.", ".global_attn.")
+
+    def plain(self, name: str):
+        return self.src.plain(self._name(name))
+
+    def tensor(self, name: str):
+        return self.src.tensor(self._name(name))
+
+    def embedding(self):
+        return self.src.embedding()
+
+    def linear(self, name: str):
+        dense = lambda t: t.dequant() if hasattr(t, "dequant") else t.float()
+        for role in ("gate_proj", "up_proj", "down_proj"):
+            if name.endswith(".mlp." + role) and self.cfg.parallel_ffn_intermediate_size > 0:
+                main = self.src.linear(name)
+                par = self.src.linear(name[: -len(role)] + "parallel_ffn." + role)
+                if main is None:
+                    return None
+                if par is None:
+                    raise KeyError(f"parallel_ffn_intermediate_size is {self.cfg.parallel_ffn_intermediate_size} but the checkpoint has no "
+                                   f"{name[: -len(role)]}parallel_ffn.{role}")
+                return torch.cat([dense(main), dense(par)], dim=1 if role == "down_proj" else 0)
+        return self.src.linear(self._name(name))
+
+
 class HybridModel:
     def __init__(self, cfg: ModelConfig, device, workspace: Optional[Workspace] = None, max_slots: int = 8, proj: Optional[str] = None):
         self.cfg, self.device = cfg, torch.device(device)
@@ -469,6 +506,8 @@ class HybridModel:
 
         ck = Checkpoint(path) if isinstance(path, (str, bytes)) or hasattr(path, "__fspath__") else path    # or any tensor resolver
         cfg = ck.cfg
+        if cfg.is_agnes and not isinstance(ck, _AgnesSource):
+            ck = _AgnesSource(ck, cfg)
         if (cfg.is_moe and cfg.num_experts % ep_world) or (not cfg.is_moe and ep_world > 1):
             raise ValueError("from_checkpoint: the experts do not split over the expert-parallel ranks")
         m = (model_cls or HybridModel)(cfg, device, max_slots=max_slots, proj=proj)      # a family built on these blocks passes its class

@@ -432,3 +432,65 @@ def test_run_time_expert_swaps_follow_the_traffic(hybrid_dirs, tmp_path, monkeyp
     assert int(a.sum()) == (4 * len(ids) + 20) * cfg.num_experts_per_tok * cfg.num_hidden_layers
     assert int(b.sum()) == 20 * cfg.num_experts_per_tok * cfg.num_hidden_layers
     assert float(torch.corrcoef(torch.stack([a.float().flatten(), b.float().flatten()]))[0, 1]) > 0.5
+
+
+def test_agnes_checkpoint_names_and_parallel_ffn_fold(tmp_path):
+    """Agnes: ``agnes_delta_attention`` / ``agnes_global_attention`` layer types, ``delta_attn`` / ``global_attn`` tensor names
+    and a second SwiGLU inside every mlp that is folded into the main one at load -- the served logits are those of the
+    oracle that adds the two SwiGLUs separately; an unknown layer type and a missing parallel projection are refused."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from grimoire_b200.models.config import ModelConfig, tiny_hybrid_dense
+
+    base = tiny_hybrid_dense(4)
+    I, P, H = 384, 128, base.hidden_size
+    cfg = dataclasses.replace(base, intermediate_size=I + P)
+    from grimoire_b200.models.synthetic import random_hybrid_state_dict
+
+    folded = random_hybrid_state_dict(cfg, seed=8)            # the equivalent model with one wide SwiGLU per layer
+    sd = {}
+    for k, v in folded.items():
+        k2 = k.replace(".linear_attn.", ".delta_attn.").replace(".self_attn.", ".global_attn.")
+        if k.endswith("mlp.gate_proj.weight") or k.endswith("mlp.up_proj.weight"):
+            sd[k2], sd[k2.replace("mlp.", "mlp.parallel_ffn.")] = v[:I].clone(), v[I:].clone()
+        elif k.endswith("mlp.down_proj.weight"):
+            sd[k2], sd[k2.replace("mlp.", "mlp.parallel_ffn.")] = v[:, :I].clone(), v[:, I:].clone()
+        else:
+            sd[k2] = v
+    tc = {"model_type": "agnes_text", "hidden_size": H, "num_hidden_layers": 4, "num_attention_heads": cfg.num_attention_heads,
+          "num_key_value_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "vocab_size": cfg.vocab_size, "intermediate_size": I,
+          "parallel_ffn_intermediate_size": P, "rms_norm_eps": cfg.rms_norm_eps,
+          "rope_parameters": {"rope_theta": cfg.rope_theta, "partial_rotary_factor": cfg.partial_rotary_factor, "mrope_section": [11, 11, 10]},
+          "layer_types": ["agnes_delta_attention" if t != "full_attention" else "agnes_global_attention" for t in cfg.layer_types],
+          "linear_num_key_heads": cfg.linear_num_key_heads, "linear_num_value_heads": cfg.linear_num_value_heads,
+          "linear_key_head_dim": cfg.linear_key_head_dim, "linear_value_head_dim": cfg.linear_value_head_dim,
+          "linear_conv_kernel_dim": cfg.linear_conv_kernel_dim}
+    d = tmp_path / "agnes"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps({"model_type": "agnes", "tie_word_embeddings": False, "text_config": tc}))
+    save_file({k: v.bfloat16() for k, v in sd.items()}, d / "model.safetensors", {"format": "pt"})
+    got_cfg = ModelConfig.from_dir(d)
+    assert got_cfg.is_agnes and got_cfg.intermediate_size == I + P and got_cfg.parallel_ffn_intermediate_size == P
+    assert got_cfg.layer_types == cfg.layer_types and got_cfg.attn_output_gate and got_cfg.norm_zero_centered
+    g = Grimoire.load(_ec(d), device="cpu")
+    assert isinstance(g.model, HybridModel)
+    ids = _prompt(26, 5)
+    got = g.score_ids(ids)
+    q = lambda w: quantize(w.bfloat16().float(), Fmt.INT4).dequant().float()
+    want = hybrid_reference.forward_logits(cfg, {k: v.bfloat16().float() for k, v in folded.items()}, ids, weight_fn=q)
+    err = float((got - want).abs().max())
+    assert err < 0.06 * float(want.abs().max()), (err, float(want.abs().max()))
+    assert float((got.argmax(-1) == want.argmax(-1)).float().mean()) >= 0.9
+    g.close()
+    with pytest.raises(ValueError, match="neither a known"):
+        ModelConfig.from_hf(dict(tc, layer_types=["agnes_delta_attention", "windowed_mixer", "x", "y"]))
+    with pytest.raises(ValueError, match="DeltaNet geometry"):
+        ModelConfig.from_hf({k: v for k, v in tc.items() if not k.startswith("linear_num")})
+    (tmp_path / "broken").mkdir()
+    (tmp_path / "broken" / "config.json").write_text((d / "config.json").read_text())
+    save_file({k: v.bfloat16() for k, v in sd.items() if "layers.2.mlp.parallel_ffn.up_proj" not in k}, tmp_path / "broken" / "model.safetensors",
+              {"format": "pt"})
+    with pytest.raises(KeyError, match="parallel_ffn.up_proj"):
+        Grimoire.load(_ec(tmp_path / "broken"), device="cpu")
