@@ -455,7 +455,11 @@ class HybridModel:
             if 0 < nres < E:
                 # RAM tier: physical experts [nres, E) stay in host memory (the placement put the hottest first)
                 from ..ops.cpu_experts import CpuExperts
+                from ..utils.host_budget import host_available_ram
 
+                need_b = sum(t[nres:].numel() * t.element_size() for t in (gu8, gus, dn8, dns))
+                if need_b + (1 << 30) > host_available_ram():
+                    raise MemoryError(f"layer {i}: {need_b >> 20} MiB of host-resident experts do not fit the RAM this process may take")
                 ffn["cx"] = CpuExperts(nres, gu8[nres:], gus[nres:], dn8[nres:], dns[nres:], pin=self.device.type == "cuda")
                 gu8, gus, dn8, dns = (t[:nres].contiguous() for t in (gu8, gus, dn8, dns))
             sg = w.get("shared_gate")

@@ -269,3 +269,21 @@ def test_host_expert_rows_match_a_plain_product():
                          ctypes.c_int(2))
     assert lib.grm_cx_moe_rows(*args(H, I)) == -2                                     # rows must not decrease
     assert lib.grm_cx_moe_rows(*args(H + 64, I)) == -2
+
+
+def test_host_memory_budget_honours_container_limits(tmp_path):
+    from grimoire_b200.utils.host_budget import host_available_ram, host_slot_limit
+
+    mem = tmp_path / "meminfo"
+    mem.write_text("MemTotal:       1000000 kB\nMemAvailable:    500000 kB\n")
+    assert host_available_ram(str(mem), cgroups=()) == 500000 * 1024
+    lim, cur = tmp_path / "max", tmp_path / "cur"
+    lim.write_text("300000000\n"), cur.write_text("100000000\n")
+    assert host_available_ram(str(mem), [(str(lim), str(cur))]) == 200000000          # the container's headroom is the smaller
+    lim.write_text("max\n")
+    assert host_available_ram(str(mem), [(str(lim), str(cur))]) == 500000 * 1024      # no limit set
+    assert host_available_ram(str(tmp_path / "none"), cgroups=()) == 0
+    assert host_available_ram() > 0
+    # the first buffer exists; three more are asked for, on two ranks, 10 units each, 55 free above the reserve
+    assert host_slot_limit(available=65, reserve=10, slot_bytes=10, ranks=2, requested=4) == 3
+    assert host_slot_limit(65, 10, 10, 2, 1) == 1 and host_slot_limit(5, 10, 10, 2, 4) == 1 and host_slot_limit(65, 10, 0, 2, 4) == 4
