@@ -35,7 +35,7 @@ def run_serving(eng: Engine, users: int, prompt_len: int, out_len: int, vocab: i
     g = torch.Generator().manual_seed(7)
     results = []
     try:
-        for rnd in range(rounds + 1):                 # round 0 is the warm-up (graph capture, allocator)
+        for rnd in range(rounds + 1):                 # the first pass is the warm-up (graph capture, allocator)
             prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(users)]
             ttft, done, lock = [0.0] * users, [0] * users, threading.Lock()
             start = threading.Barrier(users + 1)
