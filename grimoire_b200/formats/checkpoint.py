@@ -112,7 +112,9 @@ class Checkpoint:
         name = self.prefix + "embed_tokens.weight"
         t = self.tensor(name)
         if t is not None and t.dtype == torch.int8 and self.has(self.prefix + "embed_tokens.weight_scale"):
-            return t.float() * self.dir.get(self.prefix + "embed_tokens.weight_scale").float().reshape(-1, 1)
+            # both gathered operands are bf16 in the source model: the scale is rounded to bf16, and so is the product
+            scale = self.dir.get(self.prefix + "embed_tokens.weight_scale").bfloat16().float().reshape(-1, 1)
+            return (t.float() * scale).bfloat16().float()
         if t is None:
             raise KeyError(name)
         return t.float()

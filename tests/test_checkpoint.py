@@ -49,3 +49,22 @@ def test_hf_config_parsing_nested_text_config_and_hybrid_fields():
     c = ModelConfig.from_hf(raw)
     assert c.rope_theta == 5e6 and c.rot_dim == 64 and c.attn_output_gate and c.norm_zero_centered
     assert c.num_attention_layers() == 1 and c.is_moe and c.linear_num_value_heads == 32
+
+
+def test_int8_embedding_side_form_rounds_like_its_source_model(tmp_path):
+    """``embed_tokens.weight`` as int8 codes with a per-row ``weight_scale``: the served row is bf16(code * bf16(scale))."""
+    from safetensors.torch import save_file
+
+    cfg = tiny_dense()
+    write_checkpoint(tmp_path, cfg, seed=1)
+    from safetensors.torch import load_file
+
+    sd = load_file(tmp_path / "model.safetensors")
+    emb = sd["model.embed_tokens.weight"].float()
+    scale = (emb.abs().amax(dim=1) / 127).clamp_min(1e-8) * 1.0003            # not a bf16 number on purpose
+    codes = torch.round(emb / scale[:, None]).clamp(-127, 127).to(torch.int8)
+    sd["model.embed_tokens.weight"], sd["model.embed_tokens.weight_scale"] = codes, scale.float()
+    save_file(sd, tmp_path / "model.safetensors", {"format": "pt"})
+    got = Checkpoint(tmp_path).embedding()
+    want = (codes.float() * scale.bfloat16().float()[:, None]).bfloat16().float()
+    assert torch.equal(got, want) and not torch.equal(got, codes.float() * scale[:, None])
