@@ -181,6 +181,8 @@ class Grimoire:
                     tdir = tempfile.mkdtemp(prefix="grimoire_tok_")
                     with open(os.path.join(tdir, "tokenizer.json"), "w") as f:
                         _json.dump(tj, f)
+                    with open(os.path.join(tdir, "tokenizer_config.json"), "w") as f:
+                        _json.dump(G.tokenizer_config_from_gguf(gf), f)
                     tok = Tokenizer(tdir)
                 gf.close()
             else:

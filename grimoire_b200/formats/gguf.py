@@ -405,9 +405,25 @@ def tokenizer_json_from_gguf(g: GGUFFile) -> Optional[dict]:
     """The BPE tokenizer stored in the file as a tokenizer.json-shaped dict."""
     m = g.metadata
     toks, merges = m.get("tokenizer.ggml.tokens"), m.get("tokenizer.ggml.merges")
-    if not toks or merges is None or m.get("tokenizer.ggml.model") not in ("gpt2", "bpe"):
+    kind = m.get("tokenizer.ggml.model")
+    types = m.get("tokenizer.ggml.token_type") or [1] * len(toks or [])
+    if toks and kind in ("llama", "gemma4"):
+        # SentencePiece-style pieces: spaces as U+2581 (one prepended unless the file says otherwise), byte fallback pieces
+        # <0xNN>; "llama" files carry scores and no merge list, "gemma4" files carry merges and add no space prefix
+        prefix = bool(m.get("tokenizer.ggml.add_space_prefix", kind == "llama"))
+        if kind == "gemma4" and prefix:
+            raise ValueError("gemma4 tokenizer.ggml.add_space_prefix=true is unsupported")
+        norm = [{"type": "Prepend", "prepend": "\u2581"}] if prefix else []
+        norm.append({"type": "Replace", "pattern": {"String": " "}, "content": "\u2581"})
+        unk = m.get("tokenizer.ggml.unknown_token_id")
+        model = {"type": "BPE", "vocab": {t: i for i, t in enumerate(toks)}, "merges": list(merges or []), "byte_fallback": True,
+                 "unk_token": toks[int(unk)] if unk is not None and 0 <= int(unk) < len(toks) else "<unk>"}
+        if not merges:
+            model["scores"] = [float(v) for v in (m.get("tokenizer.ggml.scores") or [])]
+        added = [{"id": i, "content": t, "special": True} for i, (t, ty) in enumerate(zip(toks, types)) if ty in (3, 4)]
+        return {"added_tokens": added, "normalizer": {"type": "Sequence", "normalizers": norm}, "model": model}
+    if not toks or merges is None or kind not in ("gpt2", "bpe"):
         return None
-    types = m.get("tokenizer.ggml.token_type") or [1] * len(toks)
     added = [{"id": i, "content": t, "special": True} for i, (t, ty) in enumerate(zip(toks, types)) if ty in (3, 4)]
     return {"added_tokens": added, "normalizer": {"type": "NFC"},
             "model": {"type": "BPE", "vocab": {t: i for i, t in enumerate(toks)}, "merges": merges}}
@@ -424,3 +440,19 @@ def native_ok(g: GGUFFile, cfg) -> bool:
             if t is None or t[1] not in NATIVE_TYPES:
                 return False
     return True
+
+
+def tokenizer_config_from_gguf(g: GGUFFile) -> dict:
+    """The ``tokenizer_config.json`` keys the front end reads: bos / eos token texts and whether prompts start with BOS."""
+    m = g.metadata
+    toks = m.get("tokenizer.ggml.tokens") or []
+    out = {}
+    for key, name in (("tokenizer.ggml.bos_token_id", "bos_token"), ("tokenizer.ggml.eos_token_id", "eos_token")):
+        i = m.get(key)
+        if i is not None and 0 <= int(i) < len(toks):
+            out[name] = toks[int(i)]
+    if "tokenizer.ggml.add_bos_token" in m:
+        out["add_bos_token"] = bool(m["tokenizer.ggml.add_bos_token"])
+    if isinstance(m.get("tokenizer.chat_template"), str):
+        out["chat_template"] = m["tokenizer.chat_template"]
+    return out

@@ -205,8 +205,27 @@ class Tokenizer:
         out = "".join(f"{m['role']}: {_text(m)}\n" for m in messages)
         return out + ("assistant: " if add_generation_prompt else "")
 
+    def bos(self) -> int:
+        """Id of the beginning-of-sequence token (tokenizer_config.json ``bos_token``, else ``<bos>``), or -1."""
+        name = self.cfg.get("bos_token") if isinstance(self.cfg, dict) else None
+        if isinstance(name, dict):
+            name = name.get("content")
+        i = self.special_id(name) if name else -1
+        return i if i >= 0 else self.special_id("<bos>")
+
+    @property
+    def add_bos(self) -> bool:
+        """Prompts start with BOS: the tokenizer says so, or it is the Gemma-4 one and says nothing (src/tokenizer.cpp:218-220)."""
+        if isinstance(self.cfg, dict) and "add_bos_token" in self.cfg:
+            return bool(self.cfg["add_bos_token"])
+        return self.template_kind() == "gemma4"
+
     def encode_chat(self, messages, **kw) -> list[int]:
-        return self.encode(self.apply_chat_template(messages, **kw), allow_special=True)
+        ids = self.encode(self.apply_chat_template(messages, **kw), allow_special=True)
+        b = self.bos()
+        if self.add_bos and b >= 0 and (not ids or ids[0] != b):
+            ids = [b] + ids
+        return ids
 
 
 def _text(m: dict) -> str:

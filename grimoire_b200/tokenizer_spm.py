@@ -34,6 +34,22 @@ def is_spm_bpe(meta: dict) -> bool:
     return bool(model.get("byte_fallback")) or "Metaspace" in kinds(meta.get("pre_tokenizer")) or SPACE in str(meta.get("normalizer"))
 
 
+class _ScoreRanks:
+    """Merge priorities taken from piece scores: rank(a, b) = -score(a + b) when a + b is a piece (ties: the lower id)."""
+
+    def __init__(self, vocab: dict, scores: Sequence[float]):
+        self.vocab, self.scores = vocab, scores
+
+    def get(self, pair):
+        i = self.vocab.get(pair[0] + pair[1])
+        if i is None or i >= len(self.scores):
+            return None
+        return (-float(self.scores[i]), i)
+
+    def __bool__(self):
+        return True
+
+
 class SpmBpe:
     def __init__(self, meta: dict):
         model = meta["model"]
@@ -43,6 +59,10 @@ class SpmBpe:
         for r, m in enumerate(model.get("merges", [])):
             a, b = m if isinstance(m, (list, tuple)) else m.split(" ", 1)
             self.ranks[(a, b)] = r
+        if not self.ranks and model.get("scores"):
+            # SentencePiece pieces with scores and no merge list (GGUF "llama" tokenizers): two neighbours merge when their
+            # concatenation is a piece, the best-scored piece first (src/tokenizer.cpp:427 on)
+            self.ranks = _ScoreRanks(self.vocab, model["scores"])
         self.byte_fallback = bool(model.get("byte_fallback"))
         self.unk = self.vocab.get(model.get("unk_token") or "<unk>", -1)
         self.special: dict[str, int] = {}

@@ -2,6 +2,8 @@
 fallback, special tokens, round trip (src/tokenizer.cpp:427, :1627 in the reference)."""
 import json
 
+import pytest
+
 from grimoire_b200.tokenizer import Tokenizer
 from grimoire_b200.tokenizer_spm import SPACE, SpmBpe, is_spm_bpe
 
@@ -54,3 +56,51 @@ def test_spm_tokenizer_json_loads_through_the_front_end(tmp_path):
 def test_byte_level_tokenizer_json_is_not_taken_for_spm():
     meta = {"model": {"type": "BPE", "vocab": {}, "merges": []}, "pre_tokenizer": {"type": "ByteLevel"}, "normalizer": None}
     assert not is_spm_bpe(meta)
+
+
+def test_gguf_sentencepiece_tokenizers(tmp_path):
+    """GGUF ``llama`` (scores, no merges, space prefix) and ``gemma4`` (merges, no prefix) tokenizers through the GGUF
+    adapter: pieces merge best score first, unknown characters fall back to bytes, BOS is added when the file says so."""
+    import json
+
+    from grimoire_b200.formats import gguf as G
+    from grimoire_b200.tokenizer import Tokenizer
+
+    from .test_gguf import _write_gguf
+
+    toks = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)] + ["▁", "h", "e", "l", "o", "he", "ll", "hell", "hello", "▁hello", "▁h", "w"]
+    scores = [0.0] * 259 + [-1.0, -2.0, -2.0, -2.0, -2.0, -5.0, -4.0, -3.5, -3.0, -2.5, -6.0, -2.0]
+    types = [2, 3, 3] + [6] * 256 + [1] * 12
+    kv = {"general.architecture": (8, "llama"), "tokenizer.ggml.model": (8, "llama"), "tokenizer.ggml.tokens": (9, (8, toks)),
+          "tokenizer.ggml.token_type": (9, (5, types)), "tokenizer.ggml.bos_token_id": (4, 1), "tokenizer.ggml.eos_token_id": (4, 2),
+          "tokenizer.ggml.unknown_token_id": (4, 0)}
+    path = tmp_path / "t.gguf"
+    _write_gguf(path, kv, {})
+    g = G.GGUFFile(path)
+    g.metadata["tokenizer.ggml.scores"] = scores                 # the test writer has no float arrays: set what the parser would give
+    g.metadata["tokenizer.ggml.add_bos_token"] = True
+    tj, tc = G.tokenizer_json_from_gguf(g), G.tokenizer_config_from_gguf(g)
+    g.close()
+    assert tj["model"]["scores"][267] == -3.0 and tc == {"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True}
+    d = tmp_path / "tok"
+    d.mkdir()
+    (d / "tokenizer.json").write_text(json.dumps(tj))
+    (d / "tokenizer_config.json").write_text(json.dumps(tc))
+    tok = Tokenizer(d)
+    v = {t: i for i, t in enumerate(toks)}
+    assert tok.encode("hello") == [v["▁hello"]]                                  # a space is prepended, the best piece wins
+    assert tok.encode("hello hewo") == [v["▁hello"], v["▁"], v["he"], v["w"], v["o"]]      # "he" (-5) merges before "▁h" (-6)
+    assert tok.encode("hé") == [v["▁h"], v["<0xC3>"], v["<0xA9>"]]            # byte fallback
+    assert tok.decode(tok.encode("hello hé")) == "hello hé"
+    assert tok.bos() == 1 and tok.add_bos and tok.encode_chat([{"role": "user", "content": "hello"}])[0] == 1
+    # gemma4 flavour: merges instead of scores, no space prefix
+    g2 = G.GGUFFile(path)
+    g2.metadata.update({"tokenizer.ggml.model": "gemma4", "tokenizer.ggml.merges": ["h e", "l l", "he ll", "hell o", "▁ hello"]})
+    tj2 = G.tokenizer_json_from_gguf(g2)
+    g2.metadata["tokenizer.ggml.add_space_prefix"] = True
+    with pytest.raises(ValueError, match="add_space_prefix"):
+        G.tokenizer_json_from_gguf(g2)
+    g2.close()
+    (d / "tokenizer.json").write_text(json.dumps(tj2))
+    tok2 = Tokenizer(d)
+    assert tok2.encode("hello hello") == [v["hello"], v["▁hello"]]
