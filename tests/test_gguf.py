@@ -53,13 +53,15 @@ def _write_gguf(path, kv, tensors, version=3, alignment=32):
             out += struct.pack("<I", v)
         elif t == 6:
             out += struct.pack("<f", v)
+        elif t == 7:
+            out += struct.pack("<B", 1 if v else 0)
         elif t == 8:
             out += s(v)
         elif t == 9:
             et, items = v
             out += struct.pack("<IQ", et, len(items))
             for it in items:
-                out += s(it) if et == 8 else struct.pack("<i", it)
+                out += s(it) if et == 8 else struct.pack("<f", it) if et == 6 else struct.pack("<i", it)
     data, off = b"", 0
     for name, (typ, dims, raw) in tensors.items():
         out += s(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", typ, off)

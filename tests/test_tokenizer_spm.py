@@ -73,12 +73,10 @@ def test_gguf_sentencepiece_tokenizers(tmp_path):
     types = [2, 3, 3] + [6] * 256 + [1] * 12
     kv = {"general.architecture": (8, "llama"), "tokenizer.ggml.model": (8, "llama"), "tokenizer.ggml.tokens": (9, (8, toks)),
           "tokenizer.ggml.token_type": (9, (5, types)), "tokenizer.ggml.bos_token_id": (4, 1), "tokenizer.ggml.eos_token_id": (4, 2),
-          "tokenizer.ggml.unknown_token_id": (4, 0)}
+          "tokenizer.ggml.unknown_token_id": (4, 0), "tokenizer.ggml.scores": (9, (6, scores)), "tokenizer.ggml.add_bos_token": (7, True)}
     path = tmp_path / "t.gguf"
     _write_gguf(path, kv, {})
     g = G.GGUFFile(path)
-    g.metadata["tokenizer.ggml.scores"] = scores                 # the test writer has no float arrays: set what the parser would give
-    g.metadata["tokenizer.ggml.add_bos_token"] = True
     tj, tc = G.tokenizer_json_from_gguf(g), G.tokenizer_config_from_gguf(g)
     g.close()
     assert tj["model"]["scores"][267] == -3.0 and tc == {"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True}
