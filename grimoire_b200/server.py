@@ -113,7 +113,7 @@ class App:
         if req.chat:
             return self.tok.encode_chat(req.messages, tools=req.tools, enable_thinking=req.enable_thinking,
                                         reasoning_effort=req.reasoning_effort)
-        return self.tok.encode(req.prompt)
+        return self.tok.encode_prompt(req.prompt)
 
     def _piece(self, ids: list[int], state: dict) -> str:
         """Incremental detokenisation that never splits a UTF-8 sequence."""

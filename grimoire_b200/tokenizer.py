@@ -220,12 +220,16 @@ class Tokenizer:
             return bool(self.cfg["add_bos_token"])
         return self.template_kind() == "gemma4"
 
-    def encode_chat(self, messages, **kw) -> list[int]:
-        ids = self.encode(self.apply_chat_template(messages, **kw), allow_special=True)
+    def with_bos(self, ids: list[int]) -> list[int]:
         b = self.bos()
-        if self.add_bos and b >= 0 and (not ids or ids[0] != b):
-            ids = [b] + ids
-        return ids
+        return [b] + ids if self.add_bos and b >= 0 and (not ids or ids[0] != b) else ids
+
+    def encode_prompt(self, text: str) -> list[int]:
+        """A raw completion prompt: special tokens in the text are honoured, BOS goes first when the tokenizer asks for it."""
+        return self.with_bos(self.encode(text, allow_special=True))
+
+    def encode_chat(self, messages, **kw) -> list[int]:
+        return self.with_bos(self.encode(self.apply_chat_template(messages, **kw), allow_special=True))
 
 
 def _text(m: dict) -> str:
