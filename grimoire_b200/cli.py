@@ -54,7 +54,7 @@ def _generate(argv) -> int:
             return 0
         if ns.ppl:
             text = open(ns.ppl).read()
-            ids = tok.encode(text) if tok else [int(t) for t in text.split()]
+            ids = tok.with_bos(tok.encode(text)) if tok else [int(t) for t in text.split()]      # BOS first when the tokenizer asks for it
             llama_base = bool(ns.ppl_kld_base) and open(ns.ppl_kld_base, "rb").read(8) == b"_logits_"
             res = g.perplexity(ids, ns.ppl_ctx, ns.ppl_chunks, dump=ns.ppl_dump, selfcheck=ns.ppl_selfcheck,
                                kld_base=ns.ppl_kld_base if llama_base else "")
