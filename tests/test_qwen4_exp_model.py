@@ -114,6 +114,9 @@ def test_two_conversations_keep_their_own_history(ckpt):
     # a slot that is reused starts from nothing
     again = g.generate(a, 6)[0]
     assert again == alone[0]
+    # the continuous-batching scheduler serves the family too (no speculation: one row per conversation and step)
+    out, why, job = g.scheduler().generate(b, 6)
+    assert out == alone[1]
     g.close()
 
 
