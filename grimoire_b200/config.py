@@ -50,7 +50,7 @@ _ENV = {
     "GRIMOIRE_STEP_LOG": ("step_log", str),
 }
 # read elsewhere at the point of use (documented, not part of EngineConfig)
-_KNOWN_OTHER = {"GRIMOIRE_CP_BALANCED", "GRIMOIRE_FLASH_WS", "GRIMOIRE_GDN_SOLO", "GRIMOIRE_GDN_MMA", "GRIMOIRE_DFLASH_M", "GRIMOIRE_EXPERT_HEAT", "GRIMOIRE_EXPERT_HITS", "GRIMOIRE_EXPERT_VRAM_PER_LAYER", "GRIMOIRE_EXPERT_SWAPS", "GRIMOIRE_CPU_EXPERT_THREADS", "GRIMOIRE_PDL", "GRIMOIRE_TP_HEAD_SPLIT", "GRIMOIRE_W4_BF16_CACHE_GB", "GRIMOIRE_W4_TC", "GRIMOIRE_VERIFY_ATTN", "GRIMOIRE_VERIFY_ATTN_MIN_CTX", "GRIMOIRE_CP_FUSED", "GRIMOIRE_NO_AUTOBUILD", "GRIMOIRE_HOST_LIB", "GRIMOIRE_MEGA", "GRIMOIRE_MEGA_COOP", "GRIMOIRE_MEGA_SPIN", "GRIMOIRE_MEGA_SLOTS", "GRIMOIRE_MEGA_TUNE", "GRIMOIRE_GGUF_GOLDEN_DIR", "GRIMOIRE_TP_SPIN", "GRIMOIRE_TP_SOCKET", "GRIMOIRE_PP_SOCKET"}
+_KNOWN_OTHER = {"GRIMOIRE_CP_BALANCED", "GRIMOIRE_FLASH_WS", "GRIMOIRE_GDN_SOLO", "GRIMOIRE_GDN_MMA", "GRIMOIRE_DFLASH_M", "GRIMOIRE_EXPERT_HEAT", "GRIMOIRE_EXPERT_HITS", "GRIMOIRE_EXPERT_VRAM_PER_LAYER", "GRIMOIRE_EXPERT_SWAPS", "GRIMOIRE_ROUTE_TRACE", "GRIMOIRE_CPU_EXPERT_THREADS", "GRIMOIRE_PDL", "GRIMOIRE_TP_HEAD_SPLIT", "GRIMOIRE_W4_BF16_CACHE_GB", "GRIMOIRE_W4_TC", "GRIMOIRE_VERIFY_ATTN", "GRIMOIRE_VERIFY_ATTN_MIN_CTX", "GRIMOIRE_CP_FUSED", "GRIMOIRE_NO_AUTOBUILD", "GRIMOIRE_HOST_LIB", "GRIMOIRE_MEGA", "GRIMOIRE_MEGA_COOP", "GRIMOIRE_MEGA_SPIN", "GRIMOIRE_MEGA_SLOTS", "GRIMOIRE_MEGA_TUNE", "GRIMOIRE_GGUF_GOLDEN_DIR", "GRIMOIRE_TP_SPIN", "GRIMOIRE_TP_SOCKET", "GRIMOIRE_PP_SOCKET"}
 
 
 @dataclass

@@ -191,6 +191,11 @@ class HybridModel:
         self.expert_perm = None          # per layer: physical -> logical expert (set_expert_placement), None = identity
         self._local_moe = None           # single-GPU instance of the same chain for prompt chunks
         self._hits = None                # [layers][experts] int64 routing counts on the device (record_expert_hits)
+        rt = os.environ.get("GRIMOIRE_ROUTE_TRACE", "")
+        self._route_trace = open(rt, "ab") if rt and cfg.is_moe else None
+        self._trace_decode = False
+        if self._route_trace is not None:
+            self.graph_safe = False      # the trace reads the routes on the host every layer
         self.vram_experts = 0            # > 0: experts per layer kept on the device, the rest computed on the host
         self.heat = None                 # expert_placement.ExpertHeat while the RAM tier swaps experts at run time
         self.swaps_per_step, self.swaps_done = 0, 0
@@ -617,7 +622,7 @@ class HybridModel:
         if cfg.router_sigmoid:
             self._moe_k2(L, x, h, buf, M, decode, lg)
             return self._credit(ids=buf.ids[:M])
-        if self.ep is None and not decode and x.is_cuda and M > 64 and L.cx is None:
+        if self.ep is None and not decode and x.is_cuda and M > 64 and L.cx is None and self._route_trace is None:
             # a prompt chunk on one GPU: group the rows by expert on the device (the expert-parallel chain with
             # this GPU as its only rank) instead of sorting on the host, which would stall the stream every layer
             if self._local_moe is None or self._local_moe.max_rows < buf.max_rows:
@@ -712,6 +717,20 @@ class HybridModel:
         self._hits_path, self._hits_every, self._hits_tokens = path, max(1, int(every)), 0
 
     def _credit(self, ids=None, counts=None) -> None:
+        if self._route_trace is not None and ids is not None:
+            # diagnosis (GRIMOIRE_ROUTE_TRACE=<file>): int32 {layer, rows, top_k, kind (1 prompt rows, 2 decode rows)} then
+            # rows x top_k int32 logical expert ids -- the order in which experts were asked for, which the counts cannot
+            # give (route_trace, src/grimoire.cpp:14322-14338).  Costs a device-to-host read per layer.
+            import struct
+
+            h = ids.to("cpu", copy=True)
+            if self.expert_perm is not None:
+                perm = torch.tensor(self.expert_perm[self._cur_layer], dtype=torch.int32)
+                h = perm[h.long()]
+            M, k = h.shape
+            self._route_trace.write(struct.pack("<4i", self._cur_layer, M, k, 2 if M <= 64 and self._trace_decode else 1))
+            self._route_trace.write(h.to(torch.int32).contiguous().numpy().tobytes())
+            self._route_trace.flush()
         if self._hits is None:
             return
         row = self._hits[self._cur_layer]
@@ -951,7 +970,7 @@ class HybridModel:
                 L.ffn_down(act, h, "add_f32")
             else:
                 self._norm(h, L.post_norm, x)
-                self._cur_layer = li
+                self._cur_layer, self._trace_decode = li, not prefill
                 self._moe(L, x, h, buf, M, decode=not prefill)
         if tl: trace.mark("head")
         if rb.logits_rows is None:

@@ -494,3 +494,27 @@ def test_agnes_checkpoint_names_and_parallel_ffn_fold(tmp_path):
               {"format": "pt"})
     with pytest.raises(KeyError, match="parallel_ffn.up_proj"):
         Grimoire.load(_ec(tmp_path / "broken"), device="cpu")
+
+
+def test_route_trace_file_lists_the_experts_in_order(hybrid_dirs, tmp_path, monkeypatch):
+    """``GRIMOIRE_ROUTE_TRACE``: one record per MoE call -- layer, rows, top_k, kind -- followed by the routed expert ids."""
+    import struct
+
+    cfg, _, split_dir, _ = hybrid_dirs
+    path = tmp_path / "routes.bin"
+    monkeypatch.setenv("GRIMOIRE_ROUTE_TRACE", str(path))
+    g = Grimoire.load(_ec(split_dir), device="cpu")
+    ids = _prompt(9, 2)
+    out, _ = g.generate(ids, 3)
+    g.close()
+    blob, at, recs = path.read_bytes(), 0, []
+    while at < len(blob):
+        layer, rows, k, kind = struct.unpack_from("<4i", blob, at)
+        at += 16
+        e = struct.unpack_from(f"<{rows * k}i", blob, at)
+        at += 4 * rows * k
+        recs.append((layer, rows, k, kind))
+        assert k == cfg.num_experts_per_tok and all(0 <= v < cfg.num_experts for v in e)
+    L = cfg.num_hidden_layers
+    assert recs[:L] == [(l, 9, cfg.num_experts_per_tok, 1) for l in range(L)]               # the prompt, layer by layer
+    assert recs[L:] == [(l, 1, cfg.num_experts_per_tok, 2) for _ in range(2) for l in range(L)]   # two decode steps after the first token
