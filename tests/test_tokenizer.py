@@ -140,3 +140,25 @@ def test_xml_tool_template_family(toks, tmp_path):
     # a first tool call after an empty answer follows the think block directly
     empty = render_chatml_xml([{"role": "user", "content": "q"}, {"role": "assistant", "content": "", "tool_calls": [{"function": {"name": "f", "arguments": {"a": 1}}}]}])
     assert "<think>\n\n</think>\n\n<tool_call>\n<function=f>\n<parameter=a>\n1\n</parameter>\n</function>\n</tool_call><|im_end|>" in empty
+
+
+@pytest.mark.parametrize("specials,kind", [(["<bos>", "<|turn>", "<turn|>", "<|channel>", "<channel|>"], "gemma4"),
+                                           (["<|begin_of_text|>", "<|start|>", "<|message|>", "<|eot|>"], "muse"),
+                                           (["<|ifm|begin_of_text|>", "<|ifm|im_start|>", "<|ifm|im_end|>"], "k2")])
+def test_template_kind_follows_the_checkpoints_special_tokens(tmp_path, specials, kind):
+    hf = HFTok(models.BPE())
+    hf.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(PAT), behavior="isolated", invert=False),
+                                                pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    hf.decoder = decoders.ByteLevel()
+    hf.train_from_iterator(CORPUS, trainers.BpeTrainer(vocab_size=400, special_tokens=specials, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                                       show_progress=False))
+    hf.save(str(tmp_path / "tokenizer.json"))
+    tok = Tokenizer(tmp_path)
+    assert tok.template_kind() == kind
+    ids = tok.encode_chat([{"role": "user", "content": "Hello"}], enable_thinking=False)
+    first = hf.token_to_id(specials[0])
+    assert ids[0] == first and ids.count(first) == 1               # BOS once: added for gemma4, part of the template for the others
+    text = tok.apply_chat_template([{"role": "user", "content": "Hello"}], enable_thinking=False)
+    assert tok.decode(ids, skip_special=False).endswith(text[-12:])
+    with pytest.raises(ValueError, match="tool-call"):
+        tok.apply_chat_template([{"role": "user", "content": "x"}], tools=[{"type": "function"}])
